@@ -1,0 +1,135 @@
+/*
+ * llmrs_cuda.h — C ABI of the B200 (sm_100a) backend for llm-rs's Q4_K / Q6_K
+ * dequantize-matmul.
+ *
+ * These are the entry points a `src/backend/cuda/mod.rs` implementing the
+ * reference's `Backend` trait binds with `extern "C"`.  Each declaration names
+ * the reference interface it replaces (paths are inside the llm-rs project).
+ * Every function returns 0 on success or a negative llmrs_status; the message
+ * of the last failure on a context is available from llmrs_cuda_last_error().
+ * The library never aborts the process and has no CPU fallback: without a
+ * usable CUDA device llmrs_cuda_create fails.
+ *
+ * Conventions (src/backend/mod.rs:29-34, src/backend/metal/mod.rs:13-34,496-499):
+ *   weight  shape [K = in_features, N = out_features]: N rows of K/256 blocks
+ *   input   shape [K] or [K, M]: M rows of K contiguous elements
+ *   output  shape [N] or [N, M]: element (token s, row r) at s*N + r
+ *   1-D buffers carry dim1 = 0; M = max(input.dim1, 1).
+ *
+ * A context owns one device and one stream.  It is not thread-safe (the
+ * reference backend is `Send`, never `Sync`: metal/mod.rs:1005-1009); callers
+ * serialise.  Operations are enqueued on the context's stream in call order.
+ */
+#ifndef LLMRS_CUDA_H
+#define LLMRS_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* GGUF dtype ids used on this path (src/tensor/mod.rs:3-33). */
+enum llmrs_dtype {
+    LLMRS_F32 = 0,
+    LLMRS_Q4K = 12,
+    LLMRS_Q6K = 14,
+    LLMRS_BF16 = 30
+};
+
+/* Device layout of a buffer's bytes. */
+enum llmrs_layout {
+    LLMRS_LAYOUT_RAW = 0,        /* bytes exactly as in the GGUF file / dense row-major */
+    /* Q6_K, each weight row re-laid out as four planes so that every field is 16-byte
+     * aligned: with nb = K/256 blocks per row, [nb*128 B of ql][nb*64 B of qh]
+     * [nb*16 int8 scales][nb f16 d], block b's fields at b*128, b*64, b*16, b*2 inside
+     * their planes; rows are round_up(nb*210, 16) bytes apart.  Same bytes, new order. */
+    LLMRS_LAYOUT_Q6K_PLANES = 1
+};
+
+enum llmrs_status {
+    LLMRS_OK = 0,
+    LLMRS_ERR_CUDA = -1,         /* a CUDA runtime call failed */
+    LLMRS_ERR_SHAPE = -2,        /* shapes do not agree / K not a multiple of 256 */
+    LLMRS_ERR_DTYPE = -3,        /* dtype not supported on this path */
+    LLMRS_ERR_ARG = -4,          /* null pointer, bad size, wrong context */
+    LLMRS_ERR_NO_DEVICE = -5     /* no CUDA device / not an sm_100 device */
+};
+
+typedef struct llmrs_ctx llmrs_ctx;
+
+/* Mirrors MetalBuffer (src/backend/metal/mod.rs:13-24): device memory + dtype + dim0/dim1. */
+typedef struct llmrs_buf {
+    void *dptr;        /* device pointer */
+    uint64_t nbytes;   /* bytes allocated at dptr */
+    uint32_t dtype;    /* llmrs_dtype */
+    uint32_t dim0;     /* contiguous dimension: in_features for weights, dim for activations */
+    uint32_t dim1;     /* outer dimension: out_features for weights, seq_len for 2-D activations, 0 for 1-D */
+    uint32_t layout;   /* llmrs_layout */
+    uint32_t owned;    /* 1: llmrs_cuda_free releases dptr; 0: caller's memory (llmrs_cuda_wrap) */
+    uint32_t device;   /* CUDA device ordinal the memory lives on */
+} llmrs_buf;
+
+/* Replaces MetalBackend::new (src/backend/metal/mod.rs:185).  `stream` is a
+ * cudaStream_t to enqueue on, or NULL to let the context create its own. */
+int llmrs_cuda_create(int device, void *stream, llmrs_ctx **out);
+int llmrs_cuda_destroy(llmrs_ctx *ctx);
+
+/* Replaces Backend::upload_tensor (src/backend/mod.rs:18; metal/mod.rs:445-484).
+ * `host` holds the tensor bytes as stored in the GGUF file (TensorView.data,
+ * src/tensor/mod.rs:142-147).  The bytes are copied to the device; Q6_K is
+ * re-laid out there (LLMRS_LAYOUT_Q6K_PLANES), as the reference repacks Q4_K at
+ * upload (metal/mod.rs:38-81).  Host memory is not retained. */
+int llmrs_cuda_upload_tensor(llmrs_ctx *ctx, uint32_t dtype, const uint64_t *shape, int ndims,
+                             const void *host, size_t nbytes, llmrs_buf *out);
+
+/* Replaces Backend::alloc (src/backend/mod.rs:19; metal/mod.rs:486-494). */
+int llmrs_cuda_alloc(llmrs_ctx *ctx, uint32_t dtype, const uint64_t *shape, int ndims, llmrs_buf *out);
+
+/* Describes caller-owned device memory (for example a torch tensor used as the
+ * target of an all-gather) as a buffer.  No counterpart in the reference, whose
+ * buffers are always backend-allocated. */
+int llmrs_cuda_wrap(llmrs_ctx *ctx, void *dptr, uint32_t dtype, const uint64_t *shape, int ndims, llmrs_buf *out);
+
+/* Replaces Drop of MetalBuffer. */
+int llmrs_cuda_free(llmrs_ctx *ctx, llmrs_buf *buf);
+
+/* Replaces Backend::matmul (src/backend/mod.rs:29-34; metal/mod.rs:496-687):
+ * out[s*N + r] = sum_k W[r,k] * in[s*K + k].  Weight dtype Q4_K or Q6_K; input
+ * and output each F32 or BF16 (read from the buffers).  Enqueues only: no
+ * synchronisation and no allocation, so it may be captured in a CUDA graph. */
+int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input);
+
+/* Dequantises a Q4_K/Q6_K weight to float32 [N, K] in device memory `dev_out`
+ * (N*K floats).  The reference has no such op; it exposes, for testing, the
+ * values its kernels form in registers (tests/ops.rs:41-59, shaders/ops.metal:322-334). */
+int llmrs_cuda_dequantize(llmrs_ctx *ctx, const llmrs_buf *weight, float *dev_out);
+
+/* Host -> device copy into an existing buffer (same bytes as upload_tensor would
+ * store for a dense dtype).  Used to refresh activations each step. */
+int llmrs_cuda_write(llmrs_ctx *ctx, llmrs_buf *dst, const void *host, size_t nbytes);
+
+/* Replaces Backend::read_to_vec_f32 (src/backend/mod.rs:80; metal/mod.rs:979-994):
+ * waits for enqueued work, then copies n elements to `host`, widening BF16. */
+int llmrs_cuda_read_f32(llmrs_ctx *ctx, const llmrs_buf *buf, float *host, size_t n);
+
+/* Replaces Backend::sync (src/backend/mod.rs:88; metal/mod.rs:996-1002). */
+int llmrs_cuda_sync(llmrs_ctx *ctx);
+
+/* Replace Backend::gpu_secs_total / reset_gpu_secs (src/backend/mod.rs:84-85;
+ * metal/mod.rs:264-272,442-443): device time, from events on the context's
+ * stream, of the work enqueued between synchronisation points. */
+int llmrs_cuda_gpu_secs_total(llmrs_ctx *ctx, double *secs);
+int llmrs_cuda_reset_gpu_secs(llmrs_ctx *ctx);
+
+/* Number of kernels this library has launched on the context since creation. */
+int llmrs_cuda_launch_count(llmrs_ctx *ctx, uint64_t *count);
+
+/* Message of the last failure on `ctx` (or of the last failed create when ctx is NULL). */
+const char *llmrs_cuda_last_error(llmrs_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLMRS_CUDA_H */

@@ -1,0 +1,258 @@
+"""Host-side mirror of llm-rs's `Backend` trait for the Q4_K / Q6_K matmul path.
+
+Same names, argument meaning and error behaviour as the reference interface
+(src/backend/mod.rs:15-89) so that code written against `MetalBackend` reads the
+same here: `upload_tensor`, `alloc`, `matmul`, `read_to_vec_f32`, `sync`,
+`gpu_secs_total`, `reset_gpu_secs`.  Every call goes through the C ABI of
+include/llmrs_cuda.h (ctypes); there is no CPU path, and importing the library
+on a machine without the built .so, or creating a backend without a B200,
+raises.  Trait methods outside the matmul path raise NotImplementedError, as
+the reference does with `unimplemented!` for what a backend lacks
+(src/backend/metal/mod.rs:511).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+import os
+from dataclasses import dataclass
+from typing import Sequence
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libllmrs_cuda.so")
+
+
+class DType(enum.IntEnum):
+    """GGUF dtype ids (src/tensor/mod.rs:3-33); only the ones this path handles."""
+    F32 = 0
+    Q4K = 12
+    Q6K = 14
+    BF16 = 30
+
+    def block_elems(self) -> int:                     # src/tensor/mod.rs:37-50
+        return 256 if self in (DType.Q4K, DType.Q6K) else 1
+
+    def block_size_bytes(self) -> int:                # src/tensor/mod.rs:52-86
+        return {DType.F32: 4, DType.BF16: 2, DType.Q4K: 144, DType.Q6K: 210}[self]
+
+    def storage_size(self, n_elements: int) -> int:   # src/tensor/mod.rs:89-93
+        be = self.block_elems()
+        if n_elements % be:
+            raise ValueError(f"element count {n_elements} not divisible by block size {be}")
+        return n_elements // be * self.block_size_bytes()
+
+
+@dataclass
+class TensorView:
+    """Borrowed tensor bytes as they sit in a GGUF file (src/tensor/mod.rs:142-154)."""
+    name: str
+    dtype: DType
+    shape: Sequence[int]
+    data: np.ndarray            # uint8 (or any dtype; its bytes are used)
+
+    def n_elements(self) -> int:
+        n = 1
+        for d in self.shape:
+            n *= int(d)
+        return n
+
+
+class BackendError(RuntimeError):
+    """A C-ABI call returned a non-zero status (the Rust binding would panic here)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"llmrs_cuda error {code}: {message}")
+        self.code = code
+
+
+class _Buf(C.Structure):
+    _fields_ = [("dptr", C.c_void_p), ("nbytes", C.c_uint64), ("dtype", C.c_uint32), ("dim0", C.c_uint32),
+                ("dim1", C.c_uint32), ("layout", C.c_uint32), ("owned", C.c_uint32), ("device", C.c_uint32)]
+
+
+# Every symbol include/llmrs_cuda.h declares: (restype, argtypes).
+_VP, _U64P = C.c_void_p, C.POINTER(C.c_uint64)
+_BUFP = C.POINTER(_Buf)
+ABI = {
+    "llmrs_cuda_create": (C.c_int, [C.c_int, _VP, C.POINTER(_VP)]),
+    "llmrs_cuda_destroy": (C.c_int, [_VP]),
+    "llmrs_cuda_upload_tensor": (C.c_int, [_VP, C.c_uint32, _U64P, C.c_int, _VP, C.c_size_t, _BUFP]),
+    "llmrs_cuda_alloc": (C.c_int, [_VP, C.c_uint32, _U64P, C.c_int, _BUFP]),
+    "llmrs_cuda_wrap": (C.c_int, [_VP, _VP, C.c_uint32, _U64P, C.c_int, _BUFP]),
+    "llmrs_cuda_free": (C.c_int, [_VP, _BUFP]),
+    "llmrs_cuda_matmul": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
+    "llmrs_cuda_dequantize": (C.c_int, [_VP, _BUFP, _VP]),
+    "llmrs_cuda_write": (C.c_int, [_VP, _BUFP, _VP, C.c_size_t]),
+    "llmrs_cuda_read_f32": (C.c_int, [_VP, _BUFP, C.POINTER(C.c_float), C.c_size_t]),
+    "llmrs_cuda_sync": (C.c_int, [_VP]),
+    "llmrs_cuda_gpu_secs_total": (C.c_int, [_VP, C.POINTER(C.c_double)]),
+    "llmrs_cuda_reset_gpu_secs": (C.c_int, [_VP]),
+    "llmrs_cuda_launch_count": (C.c_int, [_VP, _U64P]),
+    "llmrs_cuda_last_error": (C.c_char_p, [_VP]),
+}
+
+_lib = None
+
+
+def load_library() -> C.CDLL:
+    """dlopen the in-tree CUDA library and bind every declared symbol.  Fails loudly when
+    the library has not been built (`python -m llm_rs_b200.build`): there is no fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python -m llm_rs_b200.build`")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in ABI.items():
+            fn = getattr(lib, name)          # AttributeError if the symbol is not exported
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+class CudaBuffer:
+    """Device buffer + dtype + dims: the counterpart of MetalBuffer (metal/mod.rs:13-34)."""
+
+    def __init__(self, backend: "CudaBackend", raw: _Buf, keepalive=None):
+        self._backend = backend
+        self._raw = raw
+        self._keepalive = keepalive       # e.g. the torch tensor whose memory is wrapped
+
+    dtype = property(lambda self: DType(self._raw.dtype))
+    dim0 = property(lambda self: int(self._raw.dim0))
+    dim1 = property(lambda self: int(self._raw.dim1))
+    layout = property(lambda self: int(self._raw.layout))
+    nbytes = property(lambda self: int(self._raw.nbytes))
+    data_ptr = property(lambda self: int(self._raw.dptr or 0))
+
+    def n_elements(self) -> int:
+        return self.dim0 * max(self.dim1, 1)
+
+    def seq_len(self) -> int:
+        return max(self.dim1, 1)
+
+    def free(self) -> None:
+        if self._raw.dptr and self._backend._ctx:
+            self._backend._check(self._backend._lib.llmrs_cuda_free(self._backend._ctx, C.byref(self._raw)))
+        self._keepalive = None
+
+    def __del__(self):                    # Drop
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class CudaBackend:
+    """The B200 backend.  One instance = one device + one stream; not thread-safe."""
+
+    Buffer = CudaBuffer
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self._lib = load_library()
+        self._ctx = None
+        ctx = C.c_void_p()
+        rc = self._lib.llmrs_cuda_create(device, C.c_void_p(stream) if stream else None, C.byref(ctx))
+        if rc != 0:
+            raise BackendError(rc, (self._lib.llmrs_cuda_last_error(None) or b"").decode())
+        self._ctx = ctx
+        self.device = device
+
+    # -- plumbing --
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise BackendError(rc, (self._lib.llmrs_cuda_last_error(self._ctx) or b"").decode())
+
+    @staticmethod
+    def _shape(shape: Sequence[int]):
+        arr = (C.c_uint64 * len(shape))(*[int(d) for d in shape])
+        return arr, len(shape)
+
+    def close(self) -> None:
+        if self._ctx:
+            self._lib.llmrs_cuda_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- Backend trait, matmul path --
+    def upload_tensor(self, tv: TensorView) -> CudaBuffer:
+        """src/backend/mod.rs:18."""
+        data = np.ascontiguousarray(tv.data)
+        shp, nd = self._shape(tv.shape)
+        raw = _Buf()
+        self._check(self._lib.llmrs_cuda_upload_tensor(self._ctx, int(tv.dtype), shp, nd,
+                                                       data.ctypes.data_as(C.c_void_p), data.nbytes, C.byref(raw)))
+        return CudaBuffer(self, raw)
+
+    def alloc(self, shape: Sequence[int], dtype: DType) -> CudaBuffer:
+        """src/backend/mod.rs:19."""
+        shp, nd = self._shape(shape)
+        raw = _Buf()
+        self._check(self._lib.llmrs_cuda_alloc(self._ctx, int(dtype), shp, nd, C.byref(raw)))
+        return CudaBuffer(self, raw)
+
+    def matmul(self, out: CudaBuffer, weight: CudaBuffer, input: CudaBuffer) -> None:
+        """`out = matmul(weight, input)`; src/backend/mod.rs:29-34."""
+        self._check(self._lib.llmrs_cuda_matmul(self._ctx, C.byref(out._raw), C.byref(weight._raw),
+                                                C.byref(input._raw)))
+
+    def read_to_vec_f32(self, buf: CudaBuffer) -> np.ndarray:
+        """src/backend/mod.rs:80."""
+        out = np.empty(buf.n_elements(), dtype=np.float32)
+        self._check(self._lib.llmrs_cuda_read_f32(self._ctx, C.byref(buf._raw),
+                                                  out.ctypes.data_as(C.POINTER(C.c_float)), out.size))
+        return out
+
+    def gpu_secs_total(self) -> float:
+        """src/backend/mod.rs:84."""
+        v = C.c_double()
+        self._check(self._lib.llmrs_cuda_gpu_secs_total(self._ctx, C.byref(v)))
+        return float(v.value)
+
+    def reset_gpu_secs(self) -> None:
+        """src/backend/mod.rs:85."""
+        self._check(self._lib.llmrs_cuda_reset_gpu_secs(self._ctx))
+
+    def sync(self) -> None:
+        """src/backend/mod.rs:88."""
+        self._check(self._lib.llmrs_cuda_sync(self._ctx))
+
+    # -- additions of this backend (no trait counterpart) --
+    def wrap(self, data_ptr: int, shape: Sequence[int], dtype: DType, keepalive=None) -> CudaBuffer:
+        """Describe caller-owned device memory (e.g. `tensor.data_ptr()`) as a buffer."""
+        shp, nd = self._shape(shape)
+        raw = _Buf()
+        self._check(self._lib.llmrs_cuda_wrap(self._ctx, C.c_void_p(data_ptr), int(dtype), shp, nd, C.byref(raw)))
+        return CudaBuffer(self, raw, keepalive)
+
+    def write(self, dst: CudaBuffer, host: np.ndarray) -> None:
+        """Enqueue a host->device copy of `host`'s bytes into `dst` (activations of a step)."""
+        self._check(self._lib.llmrs_cuda_write(self._ctx, C.byref(dst._raw), host.ctypes.data_as(C.c_void_p),
+                                               host.nbytes))
+
+    def dequantize(self, weight: CudaBuffer) -> np.ndarray:
+        """Weight -> float32 [N, K] on the device, copied back (testing aid)."""
+        K, N = weight.dim0, max(weight.dim1, 1)
+        tmp = self.alloc([K, N], DType.F32)
+        self._check(self._lib.llmrs_cuda_dequantize(self._ctx, C.byref(weight._raw), C.c_void_p(tmp.data_ptr)))
+        out = self.read_to_vec_f32(tmp).reshape(N, K)
+        tmp.free()
+        return out
+
+    def launch_count(self) -> int:
+        v = C.c_uint64()
+        self._check(self._lib.llmrs_cuda_launch_count(self._ctx, C.byref(v)))
+        return int(v.value)
+
+    # -- rest of the trait: outside the matmul path --
+    def _unimplemented(self, *_a, **_k):
+        raise NotImplementedError("only the matmul path of the Backend trait is implemented by the CUDA backend")
+
+    argmax = embed = rms_norm = rms_norm_heads = rope = attention = scatter_kv = gather = _unimplemented
+    upload_u32 = silu = mul = add = _unimplemented

@@ -1,0 +1,379 @@
+// Host side of the backend: the C++ mirror of the reference's MetalBackend for the
+// matmul path (src/backend/metal/mod.rs:163-176 state, :185 new, :445-494 upload/alloc,
+// :496-687 matmul dispatch, :979-1002 readback/sync, :264-272 GPU-time accounting), and
+// the extern "C" surface declared in include/llmrs_cuda.h.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/llmrs_cuda.h"
+#include "kernels.h"
+
+using namespace llmrs;
+
+namespace {
+thread_local std::string g_create_error;
+}
+
+// One device, one stream, event-based GPU time: the state MetalBackend keeps in
+// its device/queue/command-buffer fields.
+struct llmrs_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
+    bool span_open = false;      // work enqueued since the last synchronisation point
+    double gpu_secs = 0.0;
+    uint64_t launches = 0;
+    std::string error;
+
+    int fail(int code, const char *fmt, ...) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        error = buf;
+        return code;
+    }
+    int cuda_fail(cudaError_t e, const char *what) {
+        return fail(LLMRS_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    }
+    // Called before enqueueing: opens the timed span the way the reference opens a
+    // command buffer lazily on the first dispatch (metal/mod.rs:287-319).
+    cudaError_t begin_work() {
+        if (span_open) return cudaSuccess;
+        cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(stream, &st);
+        if (st != cudaStreamCaptureStatusNone) return cudaSuccess;   // no events inside a graph capture
+        cudaError_t e = cudaEventRecord(ev_begin, stream);
+        if (e == cudaSuccess) span_open = true;
+        return e;
+    }
+    // Synchronisation point: closes the span and adds its device time (metal/mod.rs:264-272).
+    cudaError_t finish_work() {
+        if (span_open) {
+            cudaError_t e = cudaEventRecord(ev_end, stream);
+            if (e != cudaSuccess) return e;
+            e = cudaEventSynchronize(ev_end);
+            if (e != cudaSuccess) return e;
+            float ms = 0.f;
+            e = cudaEventElapsedTime(&ms, ev_begin, ev_end);
+            if (e != cudaSuccess) return e;
+            gpu_secs += (double)ms * 1e-3;
+            span_open = false;
+            return cudaSuccess;
+        }
+        return cudaStreamSynchronize(stream);
+    }
+};
+
+namespace {
+
+size_t dense_elem_bytes(uint32_t dtype) {
+    return dtype == LLMRS_F32 ? 4 : dtype == LLMRS_BF16 ? 2 : 0;
+}
+
+// Bytes of the tensor as stored in a GGUF file (DType::storage_size, src/tensor/mod.rs:89-93).
+bool storage_size(uint32_t dtype, uint64_t n_elems, size_t *out) {
+    if (dtype == LLMRS_Q4K || dtype == LLMRS_Q6K) {
+        if (n_elems % QK_K) return false;
+        *out = (size_t)(n_elems / QK_K) * (dtype == LLMRS_Q4K ? Q4K_BLOCK_BYTES : Q6K_BLOCK_BYTES);
+        return true;
+    }
+    size_t eb = dense_elem_bytes(dtype);
+    if (!eb) return false;
+    *out = (size_t)n_elems * eb;
+    return true;
+}
+
+bool shape_dims(const uint64_t *shape, int ndims, uint32_t *d0, uint32_t *d1) {
+    if (!shape || ndims < 1 || ndims > 2) return false;
+    if (shape[0] == 0 || shape[0] > 0x7FFFFFFFull) return false;
+    if (ndims == 2 && (shape[1] == 0 || shape[1] > 0x7FFFFFFFull)) return false;
+    *d0 = (uint32_t)shape[0];
+    *d1 = ndims > 1 ? (uint32_t)shape[1] : 0;   // 1-D buffers carry dim1 = 0 (metal/mod.rs:460,493)
+    return true;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+}  // namespace
+
+extern "C" {
+
+int llmrs_cuda_create(int device, void *stream, llmrs_ctx **out) {
+    if (!out) { g_create_error = "llmrs_cuda_create: out is null"; return LLMRS_ERR_ARG; }
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        g_create_error = std::string("no CUDA device: ") + cudaGetErrorString(e);
+        return LLMRS_ERR_NO_DEVICE;
+    }
+    if (device < 0 || device >= count) { g_create_error = "device ordinal out of range"; return LLMRS_ERR_ARG; }
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) { g_create_error = cudaGetErrorString(e); return LLMRS_ERR_CUDA; }
+    if (prop.major != 10) {
+        char buf[160];
+        snprintf(buf, sizeof buf, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                 prop.major, prop.minor);
+        g_create_error = buf;
+        return LLMRS_ERR_NO_DEVICE;
+    }
+    llmrs_ctx *ctx = new (std::nothrow) llmrs_ctx();
+    if (!ctx) { g_create_error = "out of host memory"; return LLMRS_ERR_ARG; }
+    ctx->device = device;
+    DeviceGuard guard(device);
+    if (stream) {
+        ctx->stream = (cudaStream_t)stream;
+    } else {
+        e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) { g_create_error = cudaGetErrorString(e); delete ctx; return LLMRS_ERR_CUDA; }
+        ctx->own_stream = true;
+    }
+    e = cudaEventCreate(&ctx->ev_begin);
+    if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_end);
+    if (e != cudaSuccess) {
+        g_create_error = cudaGetErrorString(e);
+        llmrs_cuda_destroy(ctx);
+        return LLMRS_ERR_CUDA;
+    }
+    *out = ctx;
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_destroy(llmrs_ctx *ctx) {
+    if (!ctx) return LLMRS_OK;
+    DeviceGuard guard(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->ev_begin) cudaEventDestroy(ctx->ev_begin);
+    if (ctx->ev_end) cudaEventDestroy(ctx->ev_end);
+    if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return LLMRS_OK;
+}
+
+const char *llmrs_cuda_last_error(llmrs_ctx *ctx) {
+    return ctx ? ctx->error.c_str() : g_create_error.c_str();
+}
+
+int llmrs_cuda_alloc(llmrs_ctx *ctx, uint32_t dtype, const uint64_t *shape, int ndims, llmrs_buf *out) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!out) return ctx->fail(LLMRS_ERR_ARG, "alloc: out is null");
+    uint32_t d0, d1;
+    if (!shape_dims(shape, ndims, &d0, &d1)) return ctx->fail(LLMRS_ERR_SHAPE, "alloc: bad shape");
+    size_t eb = dense_elem_bytes(dtype);
+    if (!eb) return ctx->fail(LLMRS_ERR_DTYPE, "alloc: dtype %u is not F32/BF16", dtype);
+    size_t nbytes = (size_t)d0 * (d1 ? d1 : 1) * eb;
+    DeviceGuard guard(ctx->device);
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, nbytes);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "alloc: cudaMalloc");
+    *out = llmrs_buf{p, nbytes, dtype, d0, d1, LLMRS_LAYOUT_RAW, 1u, (uint32_t)ctx->device};
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_wrap(llmrs_ctx *ctx, void *dptr, uint32_t dtype, const uint64_t *shape, int ndims, llmrs_buf *out) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!out || !dptr) return ctx->fail(LLMRS_ERR_ARG, "wrap: null pointer");
+    uint32_t d0, d1;
+    if (!shape_dims(shape, ndims, &d0, &d1)) return ctx->fail(LLMRS_ERR_SHAPE, "wrap: bad shape");
+    size_t eb = dense_elem_bytes(dtype);
+    if (!eb) return ctx->fail(LLMRS_ERR_DTYPE, "wrap: dtype %u is not F32/BF16", dtype);
+    if ((uintptr_t)dptr % 16) return ctx->fail(LLMRS_ERR_ARG, "wrap: pointer must be 16-byte aligned");
+    *out = llmrs_buf{dptr, (size_t)d0 * (d1 ? d1 : 1) * eb, dtype, d0, d1, LLMRS_LAYOUT_RAW, 0u,
+                     (uint32_t)ctx->device};
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_free(llmrs_ctx *ctx, llmrs_buf *buf) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!buf) return LLMRS_OK;
+    if (buf->owned && buf->dptr) {
+        if (buf->device != (uint32_t)ctx->device) return ctx->fail(LLMRS_ERR_ARG, "free: buffer of another device");
+        DeviceGuard guard(ctx->device);
+        cudaError_t e = cudaStreamSynchronize(ctx->stream);   // nothing in flight may still read it
+        if (e == cudaSuccess) e = cudaFree(buf->dptr);
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "free");
+    }
+    memset(buf, 0, sizeof *buf);
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_upload_tensor(llmrs_ctx *ctx, uint32_t dtype, const uint64_t *shape, int ndims,
+                             const void *host, size_t nbytes, llmrs_buf *out) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!out || !host) return ctx->fail(LLMRS_ERR_ARG, "upload_tensor: null pointer");
+    uint32_t d0, d1;
+    if (!shape_dims(shape, ndims, &d0, &d1)) return ctx->fail(LLMRS_ERR_SHAPE, "upload_tensor: bad shape");
+    const uint64_t n_elems = (uint64_t)d0 * (d1 ? d1 : 1);
+    size_t want = 0;
+    const bool quant = dtype == LLMRS_Q4K || dtype == LLMRS_Q6K;
+    if (quant && d0 % QK_K)
+        return ctx->fail(LLMRS_ERR_SHAPE, "upload_tensor: in_features %u is not a multiple of 256", d0);
+    if (!storage_size(dtype, n_elems, &want))
+        return ctx->fail(LLMRS_ERR_DTYPE, "upload_tensor: dtype %u is not supported (F32, BF16, Q4_K, Q6_K)", dtype);
+    if (want != nbytes)
+        return ctx->fail(LLMRS_ERR_SHAPE, "upload_tensor: %zu bytes given, shape needs %zu", nbytes, want);
+    DeviceGuard guard(ctx->device);
+    const int K = (int)d0, N = (int)(d1 ? d1 : 1);
+    const size_t dev_bytes = quant ? weight_device_bytes((int)dtype, K, N) : nbytes;
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, dev_bytes);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "upload_tensor: cudaMalloc");
+    uint32_t layout = LLMRS_LAYOUT_RAW;
+    if (dtype == LLMRS_Q6K) {
+        // Re-layout on the device: raw bytes into a staging buffer, one kernel, staging freed.
+        void *stage = nullptr;
+        e = cudaMalloc(&stage, nbytes);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(stage, host, nbytes, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) {
+            e = launch_q6k_repack((const uint8_t *)stage, (uint8_t *)p, K, N, ctx->stream);
+            ctx->launches++;
+        }
+        cudaError_t e2 = cudaStreamSynchronize(ctx->stream);
+        if (stage) cudaFree(stage);
+        if (e == cudaSuccess) e = e2;
+        layout = LLMRS_LAYOUT_Q6K_PLANES;
+    } else {
+        e = cudaMemcpyAsync(p, host, nbytes, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);   // host memory is not retained
+    }
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return ctx->cuda_fail(e, "upload_tensor: copy");
+    }
+    *out = llmrs_buf{p, dev_bytes, dtype, d0, d1, layout, 1u, (uint32_t)ctx->device};
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_write(llmrs_ctx *ctx, llmrs_buf *dst, const void *host, size_t nbytes) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!dst || !dst->dptr || !host) return ctx->fail(LLMRS_ERR_ARG, "write: null pointer");
+    if (!dense_elem_bytes(dst->dtype)) return ctx->fail(LLMRS_ERR_DTYPE, "write: only F32/BF16 buffers");
+    if (nbytes > dst->nbytes) return ctx->fail(LLMRS_ERR_SHAPE, "write: %zu bytes into a %llu-byte buffer", nbytes,
+                                               (unsigned long long)dst->nbytes);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dst->dptr, host, nbytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "write");
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!out || !weight || !input || !out->dptr || !weight->dptr || !input->dptr)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul: null buffer");
+    // K = weight.dim0, N = weight.dim1, M = max(input.dim1, 1)  (metal/mod.rs:497-499)
+    const uint32_t K = weight->dim0, N = weight->dim1 ? weight->dim1 : 1, M = input->dim1 ? input->dim1 : 1;
+    if (weight->dtype != LLMRS_Q4K && weight->dtype != LLMRS_Q6K)
+        return ctx->fail(LLMRS_ERR_DTYPE, "matmul: weight dtype %u is not Q4_K/Q6_K", weight->dtype);
+    const uint32_t want_layout = weight->dtype == LLMRS_Q6K ? LLMRS_LAYOUT_Q6K_PLANES : LLMRS_LAYOUT_RAW;
+    if (weight->layout != want_layout)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul: weight was not created by upload_tensor (layout %u)", weight->layout);
+    if (!dense_elem_bytes(input->dtype) || !dense_elem_bytes(out->dtype))
+        return ctx->fail(LLMRS_ERR_DTYPE, "matmul: activations must be F32 or BF16 (got %u -> %u)", input->dtype,
+                         out->dtype);
+    if (K % QK_K) return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u is not a multiple of 256", K);
+    if (input->dim0 != K)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul: input has %u features, weight expects %u", input->dim0, K);
+    const uint32_t out_m = out->dim1 ? out->dim1 : 1;
+    if (out->dim0 != N || out_m != M)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul: output is [%u, %u], expected [%u, %u]", out->dim0, out_m, N, M);
+    if (weight->device != (uint32_t)ctx->device || input->device != (uint32_t)ctx->device ||
+        out->device != (uint32_t)ctx->device)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul: buffers belong to another device");
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: event");
+    e = launch_gemv((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
+                    (int)out->dtype, (int)K, (int)N, (int)M, ctx->stream, &ctx->launches);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: launch");
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_dequantize(llmrs_ctx *ctx, const llmrs_buf *weight, float *dev_out) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!weight || !weight->dptr || !dev_out) return ctx->fail(LLMRS_ERR_ARG, "dequantize: null pointer");
+    if (weight->dtype != LLMRS_Q4K && weight->dtype != LLMRS_Q6K)
+        return ctx->fail(LLMRS_ERR_DTYPE, "dequantize: weight dtype %u is not Q4_K/Q6_K", weight->dtype);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e == cudaSuccess) {
+        e = launch_dequant((int)weight->dtype, (const uint8_t *)weight->dptr, (int)weight->dim0,
+                           (int)(weight->dim1 ? weight->dim1 : 1), dev_out, ctx->stream);
+        ctx->launches++;
+    }
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "dequantize");
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_sync(llmrs_ctx *ctx) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->finish_work();
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "sync");
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_read_f32(llmrs_ctx *ctx, const llmrs_buf *buf, float *host, size_t n) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!buf || !buf->dptr || !host) return ctx->fail(LLMRS_ERR_ARG, "read_f32: null pointer");
+    const size_t eb = dense_elem_bytes(buf->dtype);
+    if (!eb) return ctx->fail(LLMRS_ERR_DTYPE, "read_f32: only F32/BF16 buffers");
+    if (n * eb > buf->nbytes) return ctx->fail(LLMRS_ERR_SHAPE, "read_f32: %zu elements exceed the buffer", n);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->finish_work();           // readback forces completion (metal/mod.rs:980)
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "read_f32: sync");
+    if (buf->dtype == LLMRS_F32) {
+        e = cudaMemcpy(host, buf->dptr, n * 4, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "read_f32: copy");
+        return LLMRS_OK;
+    }
+    std::vector<uint16_t> tmp;
+    try { tmp.resize(n); } catch (...) { return ctx->fail(LLMRS_ERR_ARG, "read_f32: out of host memory"); }
+    e = cudaMemcpy(tmp.data(), buf->dptr, n * 2, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "read_f32: copy");
+    for (size_t i = 0; i < n; i++) {              // bf16 -> f32 widening is exact (metal/mod.rs:985-990)
+        uint32_t u = (uint32_t)tmp[i] << 16;
+        memcpy(&host[i], &u, 4);
+    }
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_gpu_secs_total(llmrs_ctx *ctx, double *secs) {
+    if (!ctx || !secs) return LLMRS_ERR_ARG;
+    *secs = ctx->gpu_secs;
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_reset_gpu_secs(llmrs_ctx *ctx) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    ctx->gpu_secs = 0.0;
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_launch_count(llmrs_ctx *ctx, uint64_t *count) {
+    if (!ctx || !count) return LLMRS_ERR_ARG;
+    *count = ctx->launches;
+    return LLMRS_OK;
+}
+
+}  // extern "C"

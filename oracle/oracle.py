@@ -1,0 +1,195 @@
+"""ctypes binding of the CPU oracle (test infrastructure; see llmrs_oracle.c).
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs import this
+module.  The CUDA library and the llm_rs_b200 package never do.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SRC = os.path.join(_HERE, "llmrs_oracle.c")
+_LIB = os.path.join(_HERE, "libllmrs_oracle.so")
+
+Q4K, Q6K = 12, 14          # GGUF dtype ids (reference: src/tensor/mod.rs:14,16)
+BLOCK_BYTES = {Q4K: 144, Q6K: 210}
+
+# -ffp-contract=off and no -ffast-math: every float operation happens as written.
+_FLAGS = ["-O2", "-march=native", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-shared", "-Wall"]
+
+
+def build(force: bool = False) -> str:
+    """Compile llmrs_oracle.c next to this file.  OpenMP is used when a compiler
+    that has it is found (some gcc wrappers ship without libgomp)."""
+    if not force and os.path.exists(_LIB) and os.path.getmtime(_LIB) >= os.path.getmtime(_SRC):
+        return _LIB
+    errors = []
+    for cc in ("/usr/bin/gcc", "gcc", "cc"):
+        for omp in (["-fopenmp"], []):
+            cmd = [cc, *_FLAGS, *omp, "-o", _LIB, _SRC, "-lm"]
+            try:
+                r = subprocess.run(cmd, capture_output=True, text=True)
+            except FileNotFoundError as e:
+                errors.append(str(e))
+                continue
+            if r.returncode == 0:
+                return _LIB
+            errors.append(" ".join(cmd) + "\n" + r.stderr[-400:])
+    raise RuntimeError("could not build the oracle:\n" + "\n".join(errors))
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        L = C.CDLL(build())
+        u8p, f32p, u16p = C.POINTER(C.c_uint8), C.POINTER(C.c_float), C.POINTER(C.c_uint16)
+        L.llmrs_oracle_f16_to_f32.restype = C.c_float
+        L.llmrs_oracle_f16_to_f32.argtypes = [C.c_uint16]
+        L.llmrs_oracle_f32_to_f16.restype = C.c_uint16
+        L.llmrs_oracle_f32_to_f16.argtypes = [C.c_float]
+        L.llmrs_oracle_bf16_to_f32.restype = C.c_float
+        L.llmrs_oracle_bf16_to_f32.argtypes = [C.c_uint16]
+        L.llmrs_oracle_f32_to_bf16.restype = C.c_uint16
+        L.llmrs_oracle_f32_to_bf16.argtypes = [C.c_float]
+        L.llmrs_oracle_unpack_q4k_scale.restype = None
+        L.llmrs_oracle_unpack_q4k_scale.argtypes = [u8p, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]
+        L.llmrs_oracle_q6k_elem.restype = C.c_uint8
+        L.llmrs_oracle_q6k_elem.argtypes = [u8p, u8p, C.c_uint]
+        L.llmrs_oracle_dequant.restype = C.c_int
+        L.llmrs_oracle_dequant.argtypes = [C.c_int, u8p, C.c_size_t, C.c_size_t, f32p, C.c_int]
+        L.llmrs_oracle_matmul.restype = C.c_int
+        L.llmrs_oracle_matmul.argtypes = [C.c_int, u8p, C.c_size_t, C.c_size_t, f32p, C.c_size_t, f32p,
+                                          C.c_size_t, C.c_size_t, C.c_int, C.c_int]
+        L.llmrs_oracle_matmul_fast.restype = C.c_int
+        L.llmrs_oracle_matmul_fast.argtypes = [C.c_int, u8p, C.c_size_t, C.c_size_t, f32p, C.c_size_t, f32p,
+                                               C.c_size_t, C.c_size_t, C.c_int]
+        L.llmrs_oracle_ref_case_q4k.restype = C.c_int
+        L.llmrs_oracle_ref_case_q4k.argtypes = [C.c_size_t, C.c_size_t, C.c_size_t, u8p, u16p]
+        L.llmrs_oracle_ref_tolerance_failures.restype = C.c_size_t
+        L.llmrs_oracle_ref_tolerance_failures.argtypes = [f32p, f32p, C.c_size_t, C.c_size_t, f32p]
+        L.llmrs_oracle_max_threads.restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def _p(a: np.ndarray, ty):
+    return a.ctypes.data_as(C.POINTER(ty))
+
+
+def max_threads() -> int:
+    return int(lib().llmrs_oracle_max_threads())
+
+
+def f16_to_f32(h: int) -> float:
+    return float(lib().llmrs_oracle_f16_to_f32(h))
+
+
+def f32_to_f16(f: float) -> int:
+    return int(lib().llmrs_oracle_f32_to_f16(np.float32(f)))
+
+
+def bf16_to_f32(b: int) -> float:
+    return float(lib().llmrs_oracle_bf16_to_f32(b))
+
+
+def f32_to_bf16(f: float) -> int:
+    return int(lib().llmrs_oracle_f32_to_bf16(np.float32(f)))
+
+
+def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
+    """bf16 bit patterns (uint16) -> float32, exact."""
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """float32 -> bf16 bit patterns, round to nearest even (finite inputs)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = ((u >> 16) & 1) + np.uint32(0x7FFF)
+    return ((u + r) >> 16).astype(np.uint16)
+
+
+def unpack_q4k_scale(scales12: np.ndarray, sb: int) -> tuple[int, int]:
+    s = np.ascontiguousarray(scales12, dtype=np.uint8)
+    sc, m = C.c_uint32(), C.c_uint32()
+    lib().llmrs_oracle_unpack_q4k_scale(_p(s, C.c_uint8), sb, C.byref(sc), C.byref(m))
+    return sc.value, m.value
+
+
+def q6k_elem(ql: np.ndarray, qh: np.ndarray, i: int) -> int:
+    ql = np.ascontiguousarray(ql, dtype=np.uint8)
+    qh = np.ascontiguousarray(qh, dtype=np.uint8)
+    return int(lib().llmrs_oracle_q6k_elem(_p(ql, C.c_uint8), _p(qh, C.c_uint8), i))
+
+
+def _check_weight(dtype: int, w: np.ndarray, K: int, N: int) -> np.ndarray:
+    w = np.ascontiguousarray(w, dtype=np.uint8).reshape(-1)
+    assert K % 256 == 0 and w.size == N * (K // 256) * BLOCK_BYTES[dtype], (w.size, K, N)
+    return w
+
+
+def dequant(dtype: int, w: np.ndarray, K: int, N: int, threads: int | None = None) -> np.ndarray:
+    """Raw GGUF blocks of an [K, N] weight -> float32 [N, K] (row r = output feature r)."""
+    w = _check_weight(dtype, w, K, N)
+    out = np.empty((N, K), dtype=np.float32)
+    rc = lib().llmrs_oracle_dequant(dtype, _p(w, C.c_uint8), K, N, _p(out, C.c_float), threads or max_threads())
+    assert rc == 0, rc
+    return out
+
+
+def matmul(dtype: int, w: np.ndarray, K: int, N: int, x: np.ndarray, *, acc: str = "f64",
+           rows: tuple[int, int] | None = None, threads: int | None = None, fast: bool = False) -> np.ndarray:
+    """Out[M, N] = X[M, K] . W[N, K]^T.  acc="f32": the reference's sequential float
+    accumulate; acc="f64": products and sums in double (used as truth for relative-L2).
+    rows=(a, b) computes only output features a..b (the rest of `out` stays 0)."""
+    w = _check_weight(dtype, w, K, N)
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, K)
+    M = x.shape[0]
+    out = np.zeros((M, N), dtype=np.float32)
+    a, b = rows if rows is not None else (0, N)
+    t = threads or max_threads()
+    if fast:
+        rc = lib().llmrs_oracle_matmul_fast(dtype, _p(w, C.c_uint8), K, N, _p(x, C.c_float), M,
+                                            _p(out, C.c_float), a, b, t)
+    else:
+        rc = lib().llmrs_oracle_matmul(dtype, _p(w, C.c_uint8), K, N, _p(x, C.c_float), M,
+                                       _p(out, C.c_float), a, b, 1 if acc == "f64" else 0, t)
+    assert rc == 0, rc
+    return out
+
+
+def ref_case_q4k(in_f: int, out_f: int, seq_len: int) -> tuple[np.ndarray, np.ndarray]:
+    """The inputs check_matmul_q4k(in_f, out_f, seq_len) of the reference's test draws:
+    (Q4_K weight bytes, bf16 activation bit patterns)."""
+    w = np.empty(out_f * (in_f // 256) * 144, dtype=np.uint8)
+    x = np.empty(in_f * seq_len, dtype=np.uint16)
+    rc = lib().llmrs_oracle_ref_case_q4k(in_f, out_f, seq_len, _p(w, C.c_uint8), _p(x, C.c_uint16))
+    assert rc == 0, rc
+    return w, x
+
+
+def ref_tolerance_failures(expected: np.ndarray, got: np.ndarray, in_f: int) -> tuple[int, float]:
+    """Number of elements failing the reference test's criterion, and its max relative error."""
+    e = np.ascontiguousarray(expected, dtype=np.float32).reshape(-1)
+    g = np.ascontiguousarray(got, dtype=np.float32).reshape(-1)
+    assert e.size == g.size
+    mr = C.c_float()
+    bad = lib().llmrs_oracle_ref_tolerance_failures(_p(e, C.c_float), _p(g, C.c_float), e.size, in_f, C.byref(mr))
+    return int(bad), float(mr.value)
+
+
+def rel_l2(got: np.ndarray, truth: np.ndarray) -> float:
+    g = np.asarray(got, dtype=np.float64).reshape(-1)
+    t = np.asarray(truth, dtype=np.float64).reshape(-1)
+    return float(np.linalg.norm(g - t) / max(np.linalg.norm(t), 1e-300))
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv))
