@@ -1,0 +1,389 @@
+"""Benchmark of the Q4_K / Q6_K matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--tokens M]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Workload (the configuration the headline metric is quoted on): the Q6_K decode GEMV shaped like
+a Llama-3-8B output projection, K=4096 -> N=128256, M tokens (default 1), synthetic seeded
+blocks and N(0,1) activations (llm_rs_b200/synth.py).  A step is one `Backend::matmul` call on
+that weight.  With N GPUs the weight rows are split N ways and the output slices are
+all-gathered over NCCL (strong scaling: the total work is fixed).
+
+One JSON line on stdout (rank 0).  `value` is algorithmic GB/s (GGUF weight bytes + input +
+output, per step) with everything resident in HBM; `e2e` is the same metric through the public
+API with host buffers (activations copied in and the output copied out inside the timed region).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+K_IN, N_OUT = 4096, 128256
+Q6K, Q4K = 14, 12
+BLOCK_BYTES = {Q4K: 144, Q6K: 210}
+L2_BYTES = 126e6
+
+
+def algorithmic_bytes(dtype: int, K: int, N: int, M: int, in_bytes: int = 4, out_bytes: int = 4) -> int:
+    """GGUF weight bytes + activations in + outputs out (the figure the roofline uses)."""
+    return N * (K // 256) * BLOCK_BYTES[dtype] + M * K * in_bytes + M * N * out_bytes
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the GPU is busy."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake_slowdown": 0x80, "sw_power_cap": 0x4}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                try:
+                    r = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                except Exception:
+                    r = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def start(self):
+        if self._nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._thread:
+            self._thread.join(1.0)
+        med = int(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: the CPU restatement of the reference's op, on the host cores.
+# ------------------------------------------------------------------------------------------------
+def cpu_baseline(dtype: int, K: int, N: int, M: int, budget_s: float, rows: int | None = None):
+    """Times the oracle's all-cores matmul on `rows` output rows (default: all N) for about
+    budget_s seconds.  Returns (GB/s scaled to the algorithmic bytes of the sample, info)."""
+    from llm_rs_b200 import synth
+    from oracle import oracle as O
+    rows = min(rows or N, N)
+    w = synth.weight(dtype, K, rows, tid=2)
+    x = synth.activations(M, K, tid=3)
+    threads = O.max_threads()
+    O.matmul(dtype, w, K, rows, x, fast=True, threads=threads)          # warm-up
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        O.matmul(dtype, w, K, rows, x, fast=True, threads=threads)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s or reps >= 200:
+            break
+    per = dt / reps
+    gbs = algorithmic_bytes(dtype, K, rows, M) / per / 1e9
+    return gbs, per, {"cores": threads, "kind": "port",
+                      "sample": f"{rows} of {N} output rows x K={K}, M={M}; {reps} passes in {dt:.1f} s; "
+                                f"dequantise-then-dot over all rows, OpenMP over rows, -O2 -march=native"}
+
+
+def run_reference(args, rank: int, world: int):
+    """--impl reference: the reference's CPU implementation of the op (its Rust test code, restated in
+    C: oracle/llmrs_oracle.c; the Rust/Metal original cannot be built on this box) on the host cores."""
+    if rank != 0:
+        return
+    M = args.tokens
+    rows = min(N_OUT, 32064)          # a quarter of the rows per step keeps K steps within minutes
+    from llm_rs_b200 import synth
+    from oracle import oracle as O
+    w = synth.weight(Q6K, K_IN, rows, tid=2)
+    x = synth.activations(M, K_IN, tid=3)
+    threads = O.max_threads()
+    for _ in range(max(args.warmup, 1)):
+        O.matmul(Q6K, w, K_IN, rows, x, fast=True, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.matmul(Q6K, w, K_IN, rows, x, fast=True, threads=threads)
+    per = (time.perf_counter() - t0) / args.steps
+    gbs = algorithmic_bytes(Q6K, K_IN, rows, M) / per / 1e9
+    line = {
+        "impl": "reference", "metric": "q6k_gemv_algorithmic_GBps", "value": round(gbs, 3), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(per * 1e3 * N_OUT / rows, 4), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"configs[1]: Q6_K GEMV K={K_IN} N={N_OUT} M={M}", "sampled_rows": rows,
+                   "note": "ms_per_step is scaled from the row sample to all N rows"},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"{rows} of {N_OUT} rows per step"},
+        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# Our arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+
+    from llm_rs_b200 import CudaBackend, DType, TensorView, synth
+    from llm_rs_b200.shard import row_range
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    stream = torch.cuda.Stream(device=dev)
+    M = args.tokens
+    a, b = row_range(N_OUT, rank, world)
+    n_local = b - a
+    peak_gbs, peak_kind = measured_peaks()
+
+    with torch.cuda.stream(stream):
+        be = CudaBackend(local_rank, stream=stream.cuda_stream)
+        w_host = synth.weight(Q6K, K_IN, N_OUT, tid=2, rows=(a, b))
+        shard_bytes = w_host.nbytes
+        # Distinct copies of the shard, rotated per step, keep the working set above L2.
+        copies = max(1, int(np.ceil(3.2 * L2_BYTES / shard_bytes))) if shard_bytes < 3.2 * L2_BYTES else 1
+        weights = [be.upload_tensor(TensorView("output.weight", DType.Q6K, [K_IN, n_local], w_host))
+                   for _ in range(copies)]
+        x_host = synth.activations(M, K_IN, tid=3)
+        x_pinned = torch.from_numpy(x_host.copy()).pin_memory()
+        x_dev = torch.from_numpy(x_host).to(dev)
+        xbuf = be.wrap(x_dev.data_ptr(), [K_IN] if M == 1 else [K_IN, M], DType.F32, keepalive=x_dev)
+
+        per = N_OUT // world
+        full = torch.zeros(M, N_OUT, device=dev, dtype=torch.float32)
+        if M == 1 or world == 1:
+            local = full[:, a:b] if world > 1 else full
+            gathered = None
+        else:
+            local = torch.empty(M, per, device=dev, dtype=torch.float32)
+            gathered = torch.empty(world, M, per, device=dev, dtype=torch.float32)
+        obuf = be.wrap(local.data_ptr(), [n_local] if M == 1 else [n_local, M], DType.F32, keepalive=local)
+        out_pinned = torch.empty(M, N_OUT, dtype=torch.float32).pin_memory()
+
+        def gather():
+            if world == 1:
+                return
+            if M == 1:
+                dist.all_gather_into_tensor(full.view(-1), local.reshape(-1))
+            else:
+                dist.all_gather_into_tensor(gathered.view(-1), local.reshape(-1))
+                full.view(M, world, -1).copy_(gathered.permute(1, 0, 2))
+
+        def step(i):
+            be.matmul(obuf, weights[i % copies], xbuf)
+            gather()
+
+        def step_e2e(i):
+            be.write(xbuf, x_pinned.numpy())                       # H2D of this step's activations
+            be.matmul(obuf, weights[i % copies], xbuf)
+            gather()
+            out_pinned.copy_(full, non_blocking=True)              # D2H of the step's result
+            stream.synchronize()
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(dev)
+
+        def timed(fn, steps, warmup):
+            for i in range(warmup):
+                fn(i)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(steps):
+                fn(warmup + i)
+            e1.record(stream)
+            barrier()
+            ms = e0.elapsed_time(e1)
+            if world > 1:
+                t = torch.tensor([ms], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            return ms / steps
+
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        n0 = be.launch_count()
+        ms_step = timed(step, args.steps, max(args.warmup, 3))
+        launches = be.launch_count() - n0 - max(args.warmup, 3)
+        # the dominant kernel alone (no collective), same rotation: its launch duration
+        ms_kernel = timed(lambda i: be.matmul(obuf, weights[i % copies], xbuf), args.steps, 3)
+        ms_e2e = timed(step_e2e, args.steps, max(args.warmup, 3))
+        # keep the GPU busy long enough for the clock sampler to see it under this load
+        t_end = time.perf_counter() + 1.0
+        i = 0
+        while time.perf_counter() < t_end:
+            for _ in range(200):
+                step(i)
+                i += 1
+            stream.synchronize()
+        clocks = sampler.stop()
+        be.sync()
+
+        # correctness guard: a sample of rows against the CPU checker would import the oracle,
+        # which only the cpu_baseline leg may do; here just make sure the output is live.
+        assert bool(torch.isfinite(full).all()) and float(full.abs().sum()) > 0.0
+
+    alg = algorithmic_bytes(Q6K, K_IN, N_OUT, M)
+    alg_local = algorithmic_bytes(Q6K, K_IN, n_local, M)
+    value = alg / (ms_step * 1e-3) / 1e9
+    e2e_value = alg / (ms_e2e * 1e-3) / 1e9
+    achieved = alg_local / (ms_kernel * 1e-3) / 1e9
+
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            t = json.load(f).get("q6k_gemv_k4096_n128256_m1")
+        if t and M == 1:
+            traffic = int(t["dram_bytes_per_launch"] * n_local / N_OUT)
+
+    if rank != 0:
+        return
+    line = {
+        "metric": "q6k_gemv_algorithmic_GBps", "value": round(value, 2), "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int32+f32",
+        "data": "synthetic",
+        "config": {"workload": f"configs[1]: Q6_K GEMV K={K_IN} N={N_OUT} M={M} (Llama-3-8B output projection)",
+                   "parallelism": f"N-split x{world}" + (" + NCCL all-gather of output slices" if world > 1 else ""),
+                   "rows_per_gpu": n_local,
+                   "l2": (f"inputs larger than L2: the {shard_bytes / 1e6:.0f} MB weight shard is streamed every step "
+                          f"(L2 is 126 MB)" if copies == 1 else
+                          f"inputs larger than L2: {copies} distinct copies of the {shard_bytes / 1e6:.0f} MB weight "
+                          f"shard per GPU, rotated per step (L2 is 126 MB)"),
+                   "algorithmic_bytes_per_step": alg},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak_gbs, "unit": "GB/s",
+                     "frac": round(achieved / peak_gbs, 4), "traffic": traffic,
+                     "kernel": "gemv_kernel (Q6_K, 1 token)", "ms_per_launch": round(ms_kernel, 5),
+                     "peak_kind": f"of {peak_kind}", "bytes_per_launch": alg_local},
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": int(x_host.nbytes),
+                "d2h_bytes_per_step": int(M * N_OUT * 4), "ms_per_step": round(ms_e2e, 5)},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        gbs, per_s, info = cpu_baseline(Q6K, K_IN, N_OUT, M, budget_s=10.0)
+        line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", **info}
+    if world == 1 and args.extra:
+        line["extra"] = extra_measurements(be_factory=lambda: CudaBackend(local_rank, stream=stream.cuda_stream),
+                                           stream=stream, peak_gbs=peak_gbs)
+    print(json.dumps(line), flush=True)
+
+
+def extra_measurements(be_factory, stream, peak_gbs):
+    """Other shapes of the same op, kernel-only (device-resident inputs, L2-cold by rotation)."""
+    import torch
+
+    from llm_rs_b200 import DType, TensorView, synth
+    out = {}
+    with torch.cuda.stream(stream):
+        be = be_factory()
+        for name, dt, K, N, Ms in (("q4k_4096x4096", Q4K, 4096, 4096, (1,)),
+                                   ("q4k_4096x14336", Q4K, 4096, 14336, (1,)),
+                                   ("q6k_14336x4096", Q6K, 14336, 4096, (1,)),
+                                   ("q4k_4096x128256", Q4K, 4096, 128256, (1,)),
+                                   ("q6k_4096x128256", Q6K, 4096, 128256, (1, 2, 4, 8, 32, 64))):
+            w = synth.weight(dt, K, N, tid=5)
+            copies = min(48, max(1, int(np.ceil(3.2 * L2_BYTES / w.nbytes))))
+            ws = [be.upload_tensor(TensorView("w", DType(dt), [K, N], w)) for _ in range(copies)]
+            for M in Ms:
+                x = be.upload_tensor(TensorView("x", DType.F32, [K] if M == 1 else [K, M], synth.activations(M, K)))
+                o = be.alloc([N] if M == 1 else [N, M], DType.F32)
+                iters = 50 if N >= 100000 else 200
+                for i in range(5):
+                    be.matmul(o, ws[i % copies], x)
+                be.sync()
+                be.reset_gpu_secs()
+                for i in range(iters):
+                    be.matmul(o, ws[i % copies], x)
+                be.sync()
+                t = be.gpu_secs_total() / iters
+                alg = algorithmic_bytes(dt, K, N, M)
+                out[f"{name}_m{M}"] = {"us": round(t * 1e6, 2), "GBps": round(alg / t / 1e9, 1),
+                                       "frac_of_hbm_peak": round(alg / t / 1e9 / peak_gbs, 4),
+                                       "TFLOPs": round(2.0 * M * K * N / t / 1e12, 2)}
+                x.free()
+                o.free()
+            for b in ws:
+                b.free()
+        be.close()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=1, help="M, decode batch (1..64)")
+    ap.add_argument("--extra", action="store_true", help="also time the other shapes of the op (N=1 only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -41,11 +41,14 @@ enum llmrs_dtype {
 /* Device layout of a buffer's bytes. */
 enum llmrs_layout {
     LLMRS_LAYOUT_RAW = 0,        /* bytes exactly as in the GGUF file / dense row-major */
-    /* Q6_K, each weight row re-laid out as four planes so that every field is 16-byte
-     * aligned: with nb = K/256 blocks per row, [nb*128 B of ql][nb*64 B of qh]
-     * [nb*16 int8 scales][nb f16 d], block b's fields at b*128, b*64, b*16, b*2 inside
-     * their planes; rows are round_up(nb*210, 16) bytes apart.  Same bytes, new order. */
-    LLMRS_LAYOUT_Q6K_PLANES = 1
+    /* Q6_K regrouped for 16-byte aligned, bank-conflict-free reads; same bytes, new order.
+     * A row is cut into chunks of 16 blocks (the last may hold fewer, nbc); chunk ci starts at
+     * byte 3360*ci of its row and holds
+     *   4*nbc slices of 48 B: slice 4b+2h+c = ql[64h+16c..+16) | ql[64h+32+16c..+16) | qh[32h+16c..+16)
+     *                         of block b (h = half of the block, c = 0,1),
+     *   nbc*16 B: the int8 scales of block b at 16b,   nbc*2 B: the f16 d of block b at 2b.
+     * Rows are round_up(210*K/256, 16) bytes apart. */
+    LLMRS_LAYOUT_Q6K_SLICES = 1
 };
 
 enum llmrs_status {
@@ -54,7 +57,8 @@ enum llmrs_status {
     LLMRS_ERR_SHAPE = -2,        /* shapes do not agree / K not a multiple of 256 */
     LLMRS_ERR_DTYPE = -3,        /* dtype not supported on this path */
     LLMRS_ERR_ARG = -4,          /* null pointer, bad size, wrong context */
-    LLMRS_ERR_NO_DEVICE = -5     /* no CUDA device / not an sm_100 device */
+    LLMRS_ERR_NO_DEVICE = -5,    /* no CUDA device / not an sm_100 device */
+    LLMRS_ERR_KERNEL = -6        /* a kernel abandoned a bounded wait; reported at the next sync/read */
 };
 
 typedef struct llmrs_ctx llmrs_ctx;
@@ -79,7 +83,7 @@ int llmrs_cuda_destroy(llmrs_ctx *ctx);
 /* Replaces Backend::upload_tensor (src/backend/mod.rs:18; metal/mod.rs:445-484).
  * `host` holds the tensor bytes as stored in the GGUF file (TensorView.data,
  * src/tensor/mod.rs:142-147).  The bytes are copied to the device; Q6_K is
- * re-laid out there (LLMRS_LAYOUT_Q6K_PLANES), as the reference repacks Q4_K at
+ * re-laid out there (LLMRS_LAYOUT_Q6K_SLICES), as the reference repacks Q4_K at
  * upload (metal/mod.rs:38-81).  Host memory is not retained. */
 int llmrs_cuda_upload_tensor(llmrs_ctx *ctx, uint32_t dtype, const uint64_t *shape, int ndims,
                              const void *host, size_t nbytes, llmrs_buf *out);

@@ -30,6 +30,8 @@ struct llmrs_ctx {
     bool span_open = false;      // work enqueued since the last synchronisation point
     double gpu_secs = 0.0;
     uint64_t launches = 0;
+    int sm_count = 0;
+    uint32_t *dev_error = nullptr;   // device word: first KernelError reported by a kernel
     std::string error;
 
     int fail(int code, const char *fmt, ...) {
@@ -43,6 +45,15 @@ struct llmrs_ctx {
     }
     int cuda_fail(cudaError_t e, const char *what) {
         return fail(LLMRS_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    }
+    // After a synchronisation point: did a kernel abandon one of its bounded waits?
+    int check_kernel_error(const char *what) {
+        uint32_t code = 0;
+        cudaError_t e = cudaMemcpy(&code, dev_error, sizeof code, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) return cuda_fail(e, what);
+        if (code == 0) return LLMRS_OK;
+        cudaMemset(dev_error, 0, sizeof code);
+        return fail(LLMRS_ERR_KERNEL, "%s: a kernel gave up a bounded wait (code %u); results are incomplete", what, code);
     }
     // Called before enqueueing: opens the timed span the way the reference opens a
     // command buffer lazily on the first dispatch (metal/mod.rs:287-319).
@@ -148,8 +159,11 @@ int llmrs_cuda_create(int device, void *stream, llmrs_ctx **out) {
         if (e != cudaSuccess) { g_create_error = cudaGetErrorString(e); delete ctx; return LLMRS_ERR_CUDA; }
         ctx->own_stream = true;
     }
+    ctx->sm_count = prop.multiProcessorCount;
     e = cudaEventCreate(&ctx->ev_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_end);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->dev_error, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(ctx->dev_error, 0, sizeof(uint32_t));
     if (e != cudaSuccess) {
         g_create_error = cudaGetErrorString(e);
         llmrs_cuda_destroy(ctx);
@@ -166,6 +180,7 @@ int llmrs_cuda_destroy(llmrs_ctx *ctx) {
     if (ctx->ev_begin) cudaEventDestroy(ctx->ev_begin);
     if (ctx->ev_end) cudaEventDestroy(ctx->ev_end);
     if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    if (ctx->dev_error) cudaFree(ctx->dev_error);
     delete ctx;
     return LLMRS_OK;
 }
@@ -251,7 +266,7 @@ int llmrs_cuda_upload_tensor(llmrs_ctx *ctx, uint32_t dtype, const uint64_t *sha
         cudaError_t e2 = cudaStreamSynchronize(ctx->stream);
         if (stage) cudaFree(stage);
         if (e == cudaSuccess) e = e2;
-        layout = LLMRS_LAYOUT_Q6K_PLANES;
+        layout = LLMRS_LAYOUT_Q6K_SLICES;
     } else {
         e = cudaMemcpyAsync(p, host, nbytes, cudaMemcpyHostToDevice, ctx->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);   // host memory is not retained
@@ -285,13 +300,15 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
     const uint32_t K = weight->dim0, N = weight->dim1 ? weight->dim1 : 1, M = input->dim1 ? input->dim1 : 1;
     if (weight->dtype != LLMRS_Q4K && weight->dtype != LLMRS_Q6K)
         return ctx->fail(LLMRS_ERR_DTYPE, "matmul: weight dtype %u is not Q4_K/Q6_K", weight->dtype);
-    const uint32_t want_layout = weight->dtype == LLMRS_Q6K ? LLMRS_LAYOUT_Q6K_PLANES : LLMRS_LAYOUT_RAW;
+    const uint32_t want_layout = weight->dtype == LLMRS_Q6K ? LLMRS_LAYOUT_Q6K_SLICES : LLMRS_LAYOUT_RAW;
     if (weight->layout != want_layout)
         return ctx->fail(LLMRS_ERR_ARG, "matmul: weight was not created by upload_tensor (layout %u)", weight->layout);
     if (!dense_elem_bytes(input->dtype) || !dense_elem_bytes(out->dtype))
         return ctx->fail(LLMRS_ERR_DTYPE, "matmul: activations must be F32 or BF16 (got %u -> %u)", input->dtype,
                          out->dtype);
     if (K % QK_K) return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u is not a multiple of 256", K);
+    if (K > gemv_max_k())
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u exceeds the supported maximum %zu", K, gemv_max_k());
     if (input->dim0 != K)
         return ctx->fail(LLMRS_ERR_SHAPE, "matmul: input has %u features, weight expects %u", input->dim0, K);
     const uint32_t out_m = out->dim1 ? out->dim1 : 1;
@@ -304,7 +321,7 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
     cudaError_t e = ctx->begin_work();
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: event");
     e = launch_gemv((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
-                    (int)out->dtype, (int)K, (int)N, (int)M, ctx->stream, &ctx->launches);
+                    (int)out->dtype, (int)K, (int)N, (int)M, ctx->sm_count, ctx->dev_error, ctx->stream, &ctx->launches);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: launch");
     return LLMRS_OK;
 }
@@ -330,7 +347,7 @@ int llmrs_cuda_sync(llmrs_ctx *ctx) {
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->finish_work();
     if (e != cudaSuccess) return ctx->cuda_fail(e, "sync");
-    return LLMRS_OK;
+    return ctx->check_kernel_error("sync");
 }
 
 int llmrs_cuda_read_f32(llmrs_ctx *ctx, const llmrs_buf *buf, float *host, size_t n) {
@@ -342,6 +359,7 @@ int llmrs_cuda_read_f32(llmrs_ctx *ctx, const llmrs_buf *buf, float *host, size_
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->finish_work();           // readback forces completion (metal/mod.rs:980)
     if (e != cudaSuccess) return ctx->cuda_fail(e, "read_f32: sync");
+    if (int rc = ctx->check_kernel_error("read_f32")) return rc;
     if (buf->dtype == LLMRS_F32) {
         e = cudaMemcpy(host, buf->dptr, n * 4, cudaMemcpyDeviceToHost);
         if (e != cudaSuccess) return ctx->cuda_fail(e, "read_f32: copy");

@@ -35,55 +35,73 @@ __global__ void dequant_q4k_kernel(const uint8_t *__restrict__ w, float *__restr
     out[i] = d * (float)sc * q - dmin * (float)m;
 }
 
-// Reads the plane layout described at LLMRS_LAYOUT_Q6K_PLANES.
-__global__ void dequant_q6k_planes_kernel(const uint8_t *__restrict__ w, float *__restrict__ out,
-                                          int K, size_t row_stride, size_t n_elems) {
+// Position of source byte `o` (0..209) of block `b` inside a chunk of `nbc` blocks in the
+// slice-major layout described in kernels.h.
+__device__ __forceinline__ size_t q6k_chunk_offset(int nbc, int b, int o) {
+    if (o < 128) {                      // ql[o]: half h, 32-byte run u (0 = low groups, 1 = +32), column c
+        const int h = o >> 6, u = (o >> 5) & 1, c = (o >> 4) & 1, i = o & 15;
+        return (size_t)48 * (4 * b + 2 * h + c) + 16 * u + i;
+    }
+    if (o < 192) {                      // qh[o-128]
+        const int q = o - 128, h = q >> 5, c = (q >> 4) & 1, i = q & 15;
+        return (size_t)48 * (4 * b + 2 * h + c) + 32 + i;
+    }
+    if (o < 208) return (size_t)192 * nbc + 16 * b + (o - 192);
+    return (size_t)208 * nbc + 2 * b + (o - 208);
+}
+
+__device__ __forceinline__ uint8_t q6k_dev_byte(const uint8_t *row, int nb, int blk, int o) {
+    const int ci = blk / 16, b = blk % 16;
+    const int nbc = min(16, nb - 16 * ci);
+    return row[(size_t)3360 * ci + q6k_chunk_offset(nbc, b, o)];
+}
+
+// Reads the slice-major device layout.
+__global__ void dequant_q6k_dev_kernel(const uint8_t *__restrict__ w, float *__restrict__ out,
+                                       int K, size_t row_stride, size_t n_elems) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_elems) return;
     size_t row = i / (size_t)K;
     int k = (int)(i % (size_t)K);
     int nb = K / QK_K;
-    int b = k / QK_K, e = k % QK_K;
+    int blk = k / QK_K, e = k % QK_K;
     const uint8_t *r = w + row * row_stride;
-    const uint8_t *ql = r + (size_t)b * 128;
-    const uint8_t *qh = r + (size_t)nb * 128 + (size_t)b * 64;
-    const int8_t *sc = (const int8_t *)(r + (size_t)nb * 192 + (size_t)b * 16);
-    float d = f16_bits_to_f32(*(const uint16_t *)(r + (size_t)nb * 208 + (size_t)b * 2));
+    const uint16_t dbits = (uint16_t)(q6k_dev_byte(r, nb, blk, 208) | (q6k_dev_byte(r, nb, blk, 209) << 8));
+    const float d = f16_bits_to_f32(dbits);
+    const int sc = (int)(int8_t)q6k_dev_byte(r, nb, blk, 192 + e / 16);
     int h = e / 128, j = e % 128;
-    uint32_t lo = (j < 64) ? (ql[h * 64 + j] & 0x0Fu) : (uint32_t)(ql[h * 64 + j - 64] >> 4);
-    uint32_t hi = (qh[h * 32 + (j % 32)] >> (2 * (j / 32))) & 3u;
+    uint32_t lo = (j < 64) ? (q6k_dev_byte(r, nb, blk, h * 64 + j) & 0x0Fu)
+                           : (uint32_t)(q6k_dev_byte(r, nb, blk, h * 64 + j - 64) >> 4);
+    uint32_t hi = (q6k_dev_byte(r, nb, blk, 128 + h * 32 + (j % 32)) >> (2 * (j / 32))) & 3u;
     float q = (float)(int)(lo | (hi << 4));
-    out[i] = d * (float)sc[e / 16] * (q - 32.0f);
+    out[i] = d * (float)sc * (q - 32.0f);
 }
 
 // One thread per source byte of the raw GGUF Q6_K stream.
-__global__ void q6k_repack_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ planes,
+__global__ void q6k_repack_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ dev,
                                   int nb, size_t row_stride, size_t n_bytes) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_bytes) return;
     size_t blk = i / Q6K_BLOCK_BYTES;
     int o = (int)(i % Q6K_BLOCK_BYTES);
     size_t row = blk / (size_t)nb;
-    size_t b = blk % (size_t)nb;
-    size_t dst;
-    if (o < 128)      dst = b * 128 + o;
-    else if (o < 192) dst = (size_t)nb * 128 + b * 64 + (o - 128);
-    else if (o < 208) dst = (size_t)nb * 192 + b * 16 + (o - 192);
-    else              dst = (size_t)nb * 208 + b * 2 + (o - 208);
-    planes[row * row_stride + dst] = raw[i];
+    int b_in_row = (int)(blk % (size_t)nb);
+    const int ci = b_in_row / 16, b = b_in_row % 16;
+    const int nbc = min(16, nb - 16 * ci);
+    dev[row * row_stride + (size_t)3360 * ci + q6k_chunk_offset(nbc, b, o)] = raw[i];
 }
 
-cudaError_t launch_q6k_repack(const uint8_t *raw, uint8_t *planes, int K, int N, cudaStream_t s) {
+cudaError_t launch_q6k_repack(const uint8_t *raw, uint8_t *dev, int K, int N, cudaStream_t s) {
     int nb = K / QK_K;
     size_t n_bytes = (size_t)N * nb * Q6K_BLOCK_BYTES;
     if (n_bytes == 0) return cudaSuccess;
-    size_t stride = q6k_plane_row_stride(K);
+    size_t stride = q6k_row_stride(K);
     if (stride != (size_t)nb * Q6K_BLOCK_BYTES) {
-        cudaError_t e = cudaMemsetAsync(planes, 0, (size_t)N * stride, s);   // padding bytes
+        cudaError_t e = cudaMemsetAsync(dev, 0, weight_device_bytes(DT_Q6K, K, N), s);   // padding bytes
         if (e != cudaSuccess) return e;
     }
     unsigned grid = (unsigned)((n_bytes + 255) / 256);
-    q6k_repack_kernel<<<grid, 256, 0, s>>>(raw, planes, nb, stride, n_bytes);
+    q6k_repack_kernel<<<grid, 256, 0, s>>>(raw, dev, nb, stride, n_bytes);
     return cudaGetLastError();
 }
 
@@ -92,7 +110,7 @@ cudaError_t launch_dequant(int wdtype, const uint8_t *w, int K, int N, float *ou
     if (n == 0) return cudaSuccess;
     unsigned grid = (unsigned)((n + 255) / 256);
     if (wdtype == DT_Q4K) dequant_q4k_kernel<<<grid, 256, 0, s>>>(w, out, n);
-    else if (wdtype == DT_Q6K) dequant_q6k_planes_kernel<<<grid, 256, 0, s>>>(w, out, K, q6k_plane_row_stride(K), n);
+    else if (wdtype == DT_Q6K) dequant_q6k_dev_kernel<<<grid, 256, 0, s>>>(w, out, K, q6k_row_stride(K), n);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }

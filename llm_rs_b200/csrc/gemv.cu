@@ -1,39 +1,76 @@
-// Decode matmul (GEMV, a few tokens) for Q4_K and Q6_K weights on the CUDA cores of sm_100a.
+// Decode matmul (GEMV, a few tokens) for Q4_K and Q6_K weights on sm_100a.
 //
 //   out[s*N + r] = sum_k W[r,k] * x[s*K + k]        (src/backend/mod.rs:29-34)
 //
-// The kernels replace matvec_q4k_simd / matvec_q6k_simd / gemm_q4k / gemm_q6k of
-// the reference (shaders/ops.metal:239-289, 295-344, 357-424, 560-621) and are
-// HBM-bound by design: every weight byte is read once with 128-bit loads, and
-// the per-weight arithmetic is cut to about two instructions so the fp32 lanes
-// keep up with the memory system:
+// Replaces matvec_q4k_simd / matvec_q6k_simd / gemm_q4k / gemm_q6k of the reference
+// (shaders/ops.metal:239-289, 295-344, 357-424, 560-621).  The kernel is built to be bound by
+// HBM, not by instruction issue (integer/logic instructions run at half the fp32 rate on this
+// part, so a per-weight unpack + fma does not keep up with the memory system):
 //
-//  * A lane owns a 64-weight slice of a row (Q4_K: the 32 quant bytes of one
-//    sub-block pair; Q6_K: 16 qh bytes and the two 16-byte ql runs they pair
-//    with) and walks R rows over that slice, so the activations it needs are
-//    fetched once from shared memory per R rows.
-//  * Quant fields are never shifted down or converted: `w & mask` is used as a
-//    subnormal float operand (value q * 2^(shift-149)) and the activation copy
-//    in shared memory is pre-multiplied by 2^(96-shift) for the position it
-//    pairs with.  The accumulators therefore hold sum(q*x) * 2^-53, exactly
-//    rounded like an ordinary float dot product.
-//  * Block scales are applied once per sub-block, not per weight:
-//      Q4_K: sum_sb [ d*sc_sb * sum_j q_j x_j  -  dmin*m_sb * sum_j x_j ]
-//      Q6_K: sum_g  [ d*sc_g  * (sum_j q_j x_j - 32 * sum_j x_j) ]
-//    with the per-sub-block activation sums computed once per CTA.
+//  * Weights stream through shared memory.  One producer warp issues untiled bulk copies
+//    (cp.async.bulk, completion on an mbarrier) of whole row segments into an S-stage ring; the
+//    consumer warps never touch global memory for weights, so the bytes in flight are set by
+//    the ring (~100 KB per SM), not by registers or occupancy.  One persistent CTA per SM.
+//  * Activations are converted once per CTA to block fixed point: each group of 32 (Q4_K
+//    sub-block) or 16 (Q6_K scale group) values shares a power-of-two scale and becomes 21-bit
+//    integers, stored as three byte planes.  The quants stay integers too, so the inner product
+//    of a group is exact integer arithmetic: dp4a on 4 quants x 4 activation bytes, three
+//    planes, recombined in int32.  Unpacking costs 3 logic ops per 8 nibbles.
+//  * Block scales are applied once per group, in float:
+//      Q4_K: sum_sb [ d*sc_sb * sum_j q_j x_j  -  dmin*m_sb * sum_j x_j ]      (tests/ops.rs:41-59)
+//      Q6_K: sum_g  [ d*sc_g  * (sum_j q_j x_j - 32 * sum_j x_j) ]              (shaders/ops.metal:322-334)
 //
-// Accumulation is float32 throughout; results agree with a float64 evaluation
-// of the reference formula to ~1e-6 relative L2.
+// The only approximation is the 21-bit rounding of the activations relative to the largest
+// magnitude of their group (2^-21); sums over groups are float32.  Against a float64
+// evaluation of the reference formula the result is within ~1e-6 relative L2.
 #include "kernels.h"
 #include "llmrs_common.cuh"
+#include "pipeline.cuh"
 
 namespace llmrs {
 
-constexpr int SLICE = 64;          // weights per lane task
-constexpr int SLICE_STRIDE = 68;   // floats per slice in shared memory: 64 activations + 4 sums;
-                                   // 68 keeps 128-bit reads of consecutive lanes on distinct banks
-constexpr int X_EXP = 96;          // activations are staged as x * 2^(X_EXP - shift)
-constexpr float ACC_UNSCALE = 9007199254740992.0f;   // 2^53 = 2^(149 - X_EXP)
+namespace {
+
+constexpr int CHUNK_BLOCKS = 16;                       // blocks of a row per pipeline stage
+constexpr int SLICES_PER_CHUNK = CHUNK_BLOCKS * 4;     // a slice is the 64 weights one lane handles
+constexpr int MAX_STAGES = 8;
+constexpr int XBATCH = 8;                              // activation loads in flight per lane while staging
+
+// Activations become integers of 8*PLANES bits (two's complement, one byte plane each; the top
+// plane is signed).  |X| <= 2^XBITS keeps the integer dot product of a group inside int32.
+template <int PLANES> struct XFmt {
+    static constexpr int XBITS = PLANES == 3 ? 20 : 15;
+    static constexpr int XMAX = PLANES == 3 ? (1 << 20) : 32767;
+};
+
+template <int QT, int PLANES> struct Fmt;
+template <int PLANES> struct Fmt<0, PLANES> {          // Q4_K, raw GGUF blocks
+    static constexpr int BLOCK = Q4K_BLOCK_BYTES;
+    static constexpr int CHUNK_MAX = CHUNK_BLOCKS * Q4K_BLOCK_BYTES;   // 2304
+    static constexpr int GROUP_BYTES = PLANES * 32;    // one sub-block: PLANES planes of 32 bytes
+    static constexpr int META = 2 * GROUP_BYTES;       // float inv_lo, inv_hi, xsum_lo, xsum_hi
+    static constexpr int XSTRIDE = META + 16;          // 208 / 144: an odd number of 16-byte units,
+                                                       // so consecutive lanes hit distinct banks
+};
+template <int PLANES> struct Fmt<1, PLANES> {          // Q6_K, slice-major chunks (see kernels.h)
+    static constexpr int BLOCK = Q6K_BLOCK_BYTES;
+    static constexpr int CHUNK_MAX = CHUNK_BLOCKS * Q6K_BLOCK_BYTES;   // 3360
+    static constexpr int GROUP_BYTES = PLANES * 16;    // one scale group: PLANES planes of 16 bytes
+    static constexpr int META = 4 * GROUP_BYTES;       // float inv[4], float xsum[4]
+    static constexpr int XSTRIDE = META + 32 + 16;     // 240 / 176: odd number of 16-byte units
+};
+
+struct GemvParams {
+    const uint8_t *W;
+    const void *X;
+    void *Out;
+    uint32_t *err;
+    int K, N, m_valid;
+    int x_bf16, out_bf16;
+    size_t row_stride;      // bytes between weight rows
+    int n_row_tiles, n_chunks;
+    int stages;             // depth of the weight ring (<= MAX_STAGES)
+};
 
 __device__ __forceinline__ float load_x(const void *x, size_t idx, int is_bf16) {
     return is_bf16 ? bf16_bits_to_f32(__ldg((const uint16_t *)x + idx)) : __ldg((const float *)x + idx);
@@ -44,360 +81,512 @@ __device__ __forceinline__ void store_out(void *out, size_t idx, float v, int is
     else ((float *)out)[idx] = v;
 }
 
-// Left shift (in bits) of byte k of a 32-bit word when its fields are taken by masking:
-// bytes 0..2 stay in place, byte 3 is brought down with one shift.
-__device__ __forceinline__ int byte_shift(int k) { return k < 3 ? 8 * k : 0; }
+__device__ __forceinline__ uint32_t dp4a_uu(uint32_t a, uint32_t b, uint32_t c) { return __dp4a(a, b, c); }
 
-// (small unsigned integer < 2^23) -> float without an I2F: or into 2^23, subtract.
+// 4 unsigned bytes (quants) x 4 signed bytes (top activation plane).
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// (small unsigned integer < 2^23) -> float without a conversion instruction.
 __device__ __forceinline__ float small_uint_to_float(uint32_t v) {
     return __uint_as_float(0x4B000000u | v) - 8388608.0f;
 }
 
-// ---------------------------------------------------------------------------------------------
-// Q4_K.  Raw GGUF blocks (144 B: f16 d, f16 dmin, 12 B packed 6-bit scales/mins, 128 B nibbles;
-// tests/ops.rs:41-59).  Slice tau = 4*b + p is sub-block pair p of block b: quant bytes
-// 32p..32p+31, low nibbles = sub-block 2p, high nibbles = sub-block 2p+1.
-// Shared memory per token and slice: [0,32) x of sub-block 2p, [32,64) x of sub-block 2p+1 (both
-// pre-scaled), [64] sum of the true x over sub-block 2p, [65] over sub-block 2p+1.
-// ---------------------------------------------------------------------------------------------
-template <int MT, int R, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
-gemv_q4k_kernel(const uint8_t *__restrict__ W, const void *__restrict__ X, void *__restrict__ Out,
-                int K, int N, int M, int x_bf16, int out_bf16, int kc) {
-    extern __shared__ __align__(16) float xs[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t0 = blockIdx.y * MT;
-    const int row0 = (blockIdx.x * WARPS + warp) * R;
-    const int nb = K / QK_K;
-    const size_t row_bytes = (size_t)nb * Q4K_BLOCK_BYTES;
-    const int tok_stride = (kc / SLICE) * SLICE_STRIDE;
-    const int p = lane & 3;                 // pair index of every slice this lane visits
-    const int sel = (p & 1) * 16;           // which 16-bit half of the scale words holds this pair
-    const bool upper = p >= 2;              // sub-blocks 4..7 use the split 4+2 bit encoding
+// Power-of-two scale for a group whose largest magnitude is amax: returns e with
+// amax * 2^e < 2^X_BITS (clamped so that 2^e and 2^-e are normal floats).
+template <int PLANES>
+__device__ __forceinline__ int group_exponent(float amax) {
+    const int eb = (int)((__float_as_uint(amax) >> 23) & 0xFFu);      // amax < 2^(eb-126)
+    int e = XFmt<PLANES>::XBITS + 126 - eb;
+    return max(-126, min(126, e));
+}
 
-    float total[R][MT];
+// One activation -> byte planes of its integer, written to plane l at planes[l*plane_stride + pos].
+template <int PLANES>
+__device__ __forceinline__ int quantise_store(float x, float scale, uint8_t *planes, int plane_stride, int pos) {
+    const int X = min(__float2int_rn(x * scale), XFmt<PLANES>::XMAX);
 #pragma unroll
-    for (int r = 0; r < R; r++)
-#pragma unroll
-        for (int t = 0; t < MT; t++) total[r][t] = 0.0f;
-
-    for (int k0 = 0; k0 < K; k0 += kc) {
-        const int nsl = min(kc, K - k0) / SLICE;
-        if (k0) __syncthreads();
-        // ---- stage activations of this K-chunk ----
-        for (int s = warp; s < nsl; s += WARPS) {
-            const int k = lane & 3;
-            const float f_lo = exp2i(X_EXP - byte_shift(k));
-            const float f_hi = exp2i(X_EXP - byte_shift(k) - 4);
-#pragma unroll
-            for (int t = 0; t < MT; t++) {
-                const int tok = min(t0 + t, M - 1);
-                const size_t base = (size_t)tok * K + k0 + (size_t)s * SLICE;
-                float a = load_x(X, base + lane, x_bf16);
-                float b = load_x(X, base + 32 + lane, x_bf16);
-                float *dst = xs + t * tok_stride + s * SLICE_STRIDE;
-                dst[lane] = a * f_lo;
-                dst[32 + lane] = b * f_hi;
-#pragma unroll
-                for (int o = 16; o; o >>= 1) {
-                    a += __shfl_xor_sync(0xffffffffu, a, o);
-                    b += __shfl_xor_sync(0xffffffffu, b, o);
-                }
-                if (lane == 0) { dst[64] = a; dst[65] = b; }
-            }
-        }
-        __syncthreads();
-
-        // ---- stream the weights ----
-        for (int sl = lane; sl < nsl; sl += 32) {
-            const int blk = (k0 / SLICE + sl) >> 2;
-            uint4 hdr[R], qa[R], qb[R];
-#pragma unroll
-            for (int r = 0; r < R; r++) {
-                const int row = min(row0 + r, N - 1);
-                const uint8_t *b = W + (size_t)row * row_bytes + (size_t)blk * Q4K_BLOCK_BYTES;
-                hdr[r] = ldg128(b);
-                qa[r] = ldg128(b + 16 + 32 * p);
-                qb[r] = ldg128(b + 32 + 32 * p);
-            }
-            float acc_lo[R][MT], acc_hi[R][MT];
-#pragma unroll
-            for (int r = 0; r < R; r++)
-#pragma unroll
-                for (int t = 0; t < MT; t++) { acc_lo[r][t] = 0.0f; acc_hi[r][t] = 0.0f; }
-
-            const float *xsl = xs + sl * SLICE_STRIDE;
-#pragma unroll
-            for (int wi = 0; wi < 8; wi++) {
-                float4 xl[MT], xh[MT];
-#pragma unroll
-                for (int t = 0; t < MT; t++) {
-                    xl[t] = *reinterpret_cast<const float4 *>(xsl + t * tok_stride + 4 * wi);
-                    xh[t] = *reinterpret_cast<const float4 *>(xsl + t * tok_stride + 32 + 4 * wi);
-                }
-#pragma unroll
-                for (int r = 0; r < R; r++) {
-                    const uint4 &q = wi < 4 ? qa[r] : qb[r];
-                    const uint32_t w = (wi & 3) == 0 ? q.x : (wi & 3) == 1 ? q.y : (wi & 3) == 2 ? q.z : q.w;
-                    const uint32_t top = w >> 24;
-                    const float a0 = field_as_float(w & 0x0000000Fu), b0 = field_as_float(w & 0x000000F0u);
-                    const float a1 = field_as_float(w & 0x00000F00u), b1 = field_as_float(w & 0x0000F000u);
-                    const float a2 = field_as_float(w & 0x000F0000u), b2 = field_as_float(w & 0x00F00000u);
-                    const float a3 = field_as_float(top & 0x0Fu),     b3 = field_as_float(top & 0xF0u);
-#pragma unroll
-                    for (int t = 0; t < MT; t++) {
-                        float lo = acc_lo[r][t], hi = acc_hi[r][t];
-                        lo = fmaf(a0, xl[t].x, lo); hi = fmaf(b0, xh[t].x, hi);
-                        lo = fmaf(a1, xl[t].y, lo); hi = fmaf(b1, xh[t].y, hi);
-                        lo = fmaf(a2, xl[t].z, lo); hi = fmaf(b2, xh[t].z, hi);
-                        lo = fmaf(a3, xl[t].w, lo); hi = fmaf(b3, xh[t].w, hi);
-                        acc_lo[r][t] = lo; acc_hi[r][t] = hi;
-                    }
-                }
-            }
-            // ---- block scales: tests/ops.rs:29-39, two sub-blocks at a time ----
-            float2 xsum[MT];
-#pragma unroll
-            for (int t = 0; t < MT; t++) xsum[t] = *reinterpret_cast<const float2 *>(xsl + t * tok_stride + 64);
-#pragma unroll
-            for (int r = 0; r < R; r++) {
-                const float d = f16_bits_to_f32((uint16_t)(hdr[r].x & 0xFFFFu));
-                const float dmin = f16_bits_to_f32((uint16_t)(hdr[r].x >> 16));
-                const uint32_t A = (hdr[r].y >> sel) & 0xFFFFu;    // scales[2p'], scales[2p'+1]
-                const uint32_t B = (hdr[r].z >> sel) & 0xFFFFu;    // scales[4+2p'], ...
-                const uint32_t C = (hdr[r].w >> sel) & 0xFFFFu;    // scales[8+2p'], ...
-                const uint32_t scp = upper ? ((C & 0x0F0Fu) | ((A >> 2) & 0x3030u)) : (A & 0x3F3Fu);
-                const uint32_t mnp = upper ? (((C >> 4) & 0x0F0Fu) | ((B >> 2) & 0x3030u)) : (B & 0x3F3Fu);
-                const float d2 = d * ACC_UNSCALE;
-                const float s_lo = d2 * small_uint_to_float(scp & 0xFFu);
-                const float s_hi = d2 * small_uint_to_float(scp >> 8);
-                const float m_lo = dmin * small_uint_to_float(mnp & 0xFFu);
-                const float m_hi = dmin * small_uint_to_float(mnp >> 8);
-#pragma unroll
-                for (int t = 0; t < MT; t++) {
-                    float v = total[r][t];
-                    v = fmaf(s_lo, acc_lo[r][t], v);
-                    v = fmaf(s_hi, acc_hi[r][t], v);
-                    v = fmaf(-m_lo, xsum[t].x, v);
-                    v = fmaf(-m_hi, xsum[t].y, v);
-                    total[r][t] = v;
-                }
-            }
-        }
-    }
-
-#pragma unroll
-    for (int r = 0; r < R; r++)
-#pragma unroll
-        for (int t = 0; t < MT; t++) {
-            float v = total[r][t];
-#pragma unroll
-            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0 && row0 + r < N && t0 + t < M)
-                store_out(Out, (size_t)(t0 + t) * N + row0 + r, v, out_bf16);
-        }
+    for (int l = 0; l < PLANES; l++) planes[l * plane_stride + pos] = (uint8_t)((X >> (8 * l)) & 0xFF);
+    return X;
 }
 
 // ---------------------------------------------------------------------------------------------
-// Q6_K in the plane layout (LLMRS_LAYOUT_Q6K_PLANES).  Slice tau = 4*b + 2*h + c covers the
-// weights 256b + 128h + 32g + 16c + i  (g = 0..3, i = 0..15) of the row: qh bytes 32h+16c+i,
-// ql bytes 64h+16c+i (low nibble: g=0, high: g=2) and 64h+32+16c+i (low: g=1, high: g=3);
-// each g is one 16-weight scale group (shaders/ops.metal:28-42, 322-334).
-// Shared memory per token and slice: [16g+i] pre-scaled x, [64+g] sum of the true x over group g.
+// Staging of the activations (all consumer warps, once per CTA).
+// Q4_K slice (208 B): sub-block lo: plane0[32] plane1[32] plane2[32]; sub-block hi: same;
+//                     then float inv_scale_lo, inv_scale_hi, xsum_lo, xsum_hi.
+// Q6_K slice (240 B): group g = 0..3: plane0[16] plane1[16] plane2[16]; then float inv_scale[4],
+//                     float xsum[4]; 16 B unused (keeps consecutive lanes on distinct banks).
+// xsum is the sum of the rounded activations, so both terms of the formulas above see the same x.
 // ---------------------------------------------------------------------------------------------
-template <int MT, int R, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
-gemv_q6k_kernel(const uint8_t *__restrict__ W, const void *__restrict__ X, void *__restrict__ Out,
-                int K, int N, int M, int x_bf16, int out_bf16, int kc, size_t row_stride) {
-    extern __shared__ __align__(16) float xs[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t0 = blockIdx.y * MT;
-    const int row0 = (blockIdx.x * WARPS + warp) * R;
-    const int nb = K / QK_K;
-    const int tok_stride = (kc / SLICE) * SLICE_STRIDE;
-    const int c = lane & 1, h = (lane >> 1) & 1;
-    const size_t off_qh = (size_t)nb * 128, off_sc = (size_t)nb * 192, off_d = (size_t)nb * 208;
-
-    float total[R][MT];
+template <int QT, int PLANES>
+__device__ void stage_activations(uint8_t *xarea, size_t xtok_bytes, const GemvParams &p, int warp, int lane,
+                                  int n_warps) {
+    const int K = p.K;
+    for (int t = 0; t < p.m_valid; t++) {
+        uint8_t *xt = xarea + (size_t)t * xtok_bytes;
+        if (QT == 0) {
+            // a batch of loads is issued before any is used: one memory latency per batch
+            for (int sb0 = warp; sb0 < K / 32; sb0 += n_warps * XBATCH) {
+                float xv[XBATCH];
 #pragma unroll
-    for (int r = 0; r < R; r++)
-#pragma unroll
-        for (int t = 0; t < MT; t++) total[r][t] = 0.0f;
-
-    for (int k0 = 0; k0 < K; k0 += kc) {
-        const int nsl = min(kc, K - k0) / SLICE;
-        if (k0) __syncthreads();
-        // ---- stage activations: lane holds positions `lane` (g = lane/16) and `lane+32` (g+2) ----
-        for (int s = warp; s < nsl; s += WARPS) {
-            const int sb = s >> 2, sh = (s >> 1) & 1, sc = s & 1;
-            const int i = lane & 15, g = lane >> 4;
-            const float f = exp2i(X_EXP - byte_shift(i & 3));
-            const size_t e0 = (size_t)k0 + 256 * sb + 128 * sh + 16 * sc + i;
-#pragma unroll
-            for (int t = 0; t < MT; t++) {
-                const int tok = min(t0 + t, M - 1);
-                float a = load_x(X, (size_t)tok * K + e0 + 32 * g, x_bf16);
-                float b = load_x(X, (size_t)tok * K + e0 + 32 * (g + 2), x_bf16);
-                float *dst = xs + t * tok_stride + s * SLICE_STRIDE;
-                dst[lane] = a * f;
-                dst[32 + lane] = b * f;
-#pragma unroll
-                for (int o = 8; o; o >>= 1) {
-                    a += __shfl_xor_sync(0xffffffffu, a, o);
-                    b += __shfl_xor_sync(0xffffffffu, b, o);
+                for (int u = 0; u < XBATCH; u++) {
+                    const int sb = sb0 + u * n_warps;
+                    xv[u] = sb < K / 32 ? load_x(p.X, (size_t)t * K + 32 * sb + lane, p.x_bf16) : 0.0f;
                 }
-                if (i == 0) { dst[64 + g] = a; dst[66 + g] = b; }
-            }
-        }
-        __syncthreads();
-
-        for (int sl = lane; sl < nsl; sl += 32) {
-            const int blk = (k0 / SLICE + sl) >> 2;
-            uint4 l0[R], l1[R], qh[R];
-            uint2 scw[R];
-            uint16_t dh[R];
 #pragma unroll
-            for (int r = 0; r < R; r++) {
-                const int row = min(row0 + r, N - 1);
-                const uint8_t *b = W + (size_t)row * row_stride;
-                const uint8_t *ql = b + (size_t)blk * 128 + 64 * h + 16 * c;
-                l0[r] = ldg128(ql);
-                l1[r] = ldg128(ql + 32);
-                qh[r] = ldg128(b + off_qh + (size_t)blk * 64 + 32 * h + 16 * c);
-                scw[r] = __ldg(reinterpret_cast<const uint2 *>(b + off_sc + (size_t)blk * 16 + 8 * h));
-                dh[r] = __ldg(reinterpret_cast<const uint16_t *>(b + off_d + (size_t)blk * 2));
-            }
-            const float *xsl = xs + sl * SLICE_STRIDE;
-            float4 xsum[MT];
+                for (int u = 0; u < XBATCH; u++) {
+                    const int sb = sb0 + u * n_warps;
+                    if (sb >= K / 32) break;
+                    const float x = xv[u];
+                    float amax = fabsf(x);
 #pragma unroll
-            for (int t = 0; t < MT; t++) xsum[t] = *reinterpret_cast<const float4 *>(xsl + t * tok_stride + 64);
-
+                    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                    const int e = group_exponent<PLANES>(amax);
+                    uint8_t *sl = xt + (size_t)(sb >> 1) * Fmt<0, PLANES>::XSTRIDE;
+                    int X = quantise_store<PLANES>(x, exp2i(e), sl + (sb & 1) * Fmt<0, PLANES>::GROUP_BYTES, 32, lane);
 #pragma unroll
-            for (int g = 0; g < 4; g++) {
-                float acc[R][MT];
-#pragma unroll
-                for (int r = 0; r < R; r++)
-#pragma unroll
-                    for (int t = 0; t < MT; t++) acc[r][t] = 0.0f;
-#pragma unroll
-                for (int wi = 0; wi < 4; wi++) {
-                    float4 xv[MT];
-#pragma unroll
-                    for (int t = 0; t < MT; t++)
-                        xv[t] = *reinterpret_cast<const float4 *>(xsl + t * tok_stride + 16 * g + 4 * wi);
-#pragma unroll
-                    for (int r = 0; r < R; r++) {
-                        const uint4 &ql4 = (g & 1) ? l1[r] : l0[r];
-                        const uint32_t lw = wi == 0 ? ql4.x : wi == 1 ? ql4.y : wi == 2 ? ql4.z : ql4.w;
-                        const uint32_t hw = wi == 0 ? qh[r].x : wi == 1 ? qh[r].y : wi == 2 ? qh[r].z : qh[r].w;
-                        const uint32_t lo = (g < 2 ? lw : (lw >> 4)) & 0x0F0F0F0Fu;
-                        const uint32_t hs = g == 0 ? (hw << 4) : g == 1 ? (hw << 2) : g == 2 ? hw : (hw >> 2);
-                        const uint32_t v = lo | (hs & 0x30303030u);          // four 6-bit quants, one per byte
-                        const float q0 = field_as_float(v & 0x000000FFu);
-                        const float q1 = field_as_float(v & 0x0000FF00u);
-                        const float q2 = field_as_float(v & 0x00FF0000u);
-                        const float q3 = field_as_float(v >> 24);
-#pragma unroll
-                        for (int t = 0; t < MT; t++) {
-                            float a = acc[r][t];
-                            a = fmaf(q0, xv[t].x, a);
-                            a = fmaf(q1, xv[t].y, a);
-                            a = fmaf(q2, xv[t].z, a);
-                            a = fmaf(q3, xv[t].w, a);
-                            acc[r][t] = a;
-                        }
+                    for (int o = 16; o; o >>= 1) X += __shfl_xor_sync(0xffffffffu, X, o);
+                    if (lane == 0) {
+                        const float inv = isfinite(amax) ? exp2i(-e) : __uint_as_float(0x7FC00000u);
+                        float *f = reinterpret_cast<float *>(sl + Fmt<0, PLANES>::META);
+                        f[sb & 1] = inv;
+                        f[2 + (sb & 1)] = (float)X * inv;
                     }
                 }
-                // scale of group g: int8 at scales[8h + 2g + c]
+            }
+        } else {
+            // two 16-value groups per warp pass: lanes 0-15 take c = 0, lanes 16-31 take c = 1
+            for (int pr0 = warp; pr0 < K / 32; pr0 += n_warps * XBATCH) {
+                const int c = lane >> 4, i = lane & 15;
+                float xv[XBATCH];
 #pragma unroll
-                for (int r = 0; r < R; r++) {
-                    const uint32_t sw = (g < 2 ? scw[r].x : scw[r].y) ^ 0x80808080u;   // sc + 128 per byte
-                    const uint32_t sbyte = (sw >> (8 * (2 * (g & 1) + c))) & 0xFFu;
-                    const float scf = small_uint_to_float(sbyte) - 128.0f;
-                    const float ds = f16_bits_to_f32(dh[r]) * scf;
-                    const float ds2 = ds * ACC_UNSCALE;
-                    const float ds32 = ds * -32.0f;
+                for (int u = 0; u < XBATCH; u++) {
+                    const int pr = pr0 + u * n_warps;
+                    const int b = pr >> 3, h = (pr >> 2) & 1, g = pr & 3;
+                    xv[u] = pr < K / 32
+                                ? load_x(p.X, (size_t)t * K + 256 * b + 128 * h + 32 * g + 16 * c + i, p.x_bf16)
+                                : 0.0f;
+                }
 #pragma unroll
-                    for (int t = 0; t < MT; t++) {
-                        const float xg = g == 0 ? xsum[t].x : g == 1 ? xsum[t].y : g == 2 ? xsum[t].z : xsum[t].w;
-                        float v = total[r][t];
-                        v = fmaf(ds2, acc[r][t], v);
-                        v = fmaf(ds32, xg, v);
-                        total[r][t] = v;
+                for (int u = 0; u < XBATCH; u++) {
+                    const int pr = pr0 + u * n_warps;
+                    if (pr >= K / 32) break;
+                    const int b = pr >> 3, h = (pr >> 2) & 1, g = pr & 3;
+                    const float x = xv[u];
+                    float amax = fabsf(x);
+#pragma unroll
+                    for (int o = 8; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                    const int e = group_exponent<PLANES>(amax);
+                    uint8_t *sl = xt + (size_t)(4 * b + 2 * h + c) * Fmt<1, PLANES>::XSTRIDE;
+                    int X = quantise_store<PLANES>(x, exp2i(e), sl + g * Fmt<1, PLANES>::GROUP_BYTES, 16, i);
+#pragma unroll
+                    for (int o = 8; o; o >>= 1) X += __shfl_xor_sync(0xffffffffu, X, o);
+                    if (i == 0) {
+                        const float inv = isfinite(amax) ? exp2i(-e) : __uint_as_float(0x7FC00000u);
+                        float *f = reinterpret_cast<float *>(sl + Fmt<1, PLANES>::META);
+                        f[g] = inv;
+                        f[4 + g] = (float)X * inv;
                     }
                 }
             }
         }
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-slice arithmetic.  `row` points at the staged chunk of one weight row.
+// ---------------------------------------------------------------------------------------------
+
+// Q4_K: slice sl = 4*b + p is sub-block pair p of block b: quant bytes 32p..32p+31, low nibbles
+// are sub-block 2p, high nibbles sub-block 2p+1 (tests/ops.rs:41-59).
+template <int MT, int R, int PLANES>
+__device__ __forceinline__ void slice_q4k(const uint8_t *const (&row)[R], int sl, const uint8_t *xsl, size_t xtok_bytes,
+                                          float (&total)[R][MT]) {
+    const int b = sl >> 2, p = sl & 3;
+    const int sel = (p & 1) * 16;
+    const bool upper = p >= 2;
+    uint32_t lo[R][8], hi[R][8];
+    float s_lo[R], s_hi[R], m_lo[R], m_hi[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const uint8_t *blk = row[r] + b * Q4K_BLOCK_BYTES;
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+        const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * p);
+        const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * p);
+        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            lo[r][i] = w[i] & 0x0F0F0F0Fu;
+            hi[r][i] = (w[i] >> 4) & 0x0F0F0F0Fu;
+        }
+        // 6-bit scales and mins of the two sub-blocks (tests/ops.rs:29-39)
+        const float d = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu));
+        const float dmin = f16_bits_to_f32((uint16_t)(hdr.x >> 16));
+        const uint32_t A = (hdr.y >> sel) & 0xFFFFu;
+        const uint32_t B = (hdr.z >> sel) & 0xFFFFu;
+        const uint32_t C = (hdr.w >> sel) & 0xFFFFu;
+        const uint32_t scp = upper ? ((C & 0x0F0Fu) | ((A >> 2) & 0x3030u)) : (A & 0x3F3Fu);
+        const uint32_t mnp = upper ? (((C >> 4) & 0x0F0Fu) | ((B >> 2) & 0x3030u)) : (B & 0x3F3Fu);
+        s_lo[r] = d * small_uint_to_float(scp & 0xFFu);
+        s_hi[r] = d * small_uint_to_float(scp >> 8);
+        m_lo[r] = dmin * small_uint_to_float(mnp & 0xFFu);
+        m_hi[r] = dmin * small_uint_to_float(mnp >> 8);
+    }
+#pragma unroll
+    for (int t = 0; t < MT; t++) {
+        const uint8_t *xs = xsl + (size_t)t * xtok_bytes;
+        using F = Fmt<0, PLANES>;
+        const float4 meta = *reinterpret_cast<const float4 *>(xs + F::META);   // inv_lo, inv_hi, xsum_lo, xsum_hi
+        float val[R][2];
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+            uint32_t pl[PLANES][8];
+#pragma unroll
+            for (int l = 0; l < PLANES; l++) {
+                const uint4 u0 = *reinterpret_cast<const uint4 *>(xs + hf * F::GROUP_BYTES + l * 32);
+                const uint4 u1 = *reinterpret_cast<const uint4 *>(xs + hf * F::GROUP_BYTES + l * 32 + 16);
+                pl[l][0] = u0.x; pl[l][1] = u0.y; pl[l][2] = u0.z; pl[l][3] = u0.w;
+                pl[l][4] = u1.x; pl[l][5] = u1.y; pl[l][6] = u1.z; pl[l][7] = u1.w;
+            }
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                uint32_t s0 = 0, s1 = 0;
+                int st = 0;                                               // top (signed) plane
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint32_t q = hf ? hi[r][i] : lo[r][i];
+                    s0 = dp4a_uu(q, pl[0][i], s0);
+                    if (PLANES == 3) s1 = dp4a_uu(q, pl[1][i], s1);
+                    st = dp4a_us(q, pl[PLANES - 1][i], st);
+                }
+                // exact in int32: |S| <= 32*15*2^20
+                const int S = PLANES == 3 ? (st * 256 + (int)s1) * 256 + (int)s0 : st * 256 + (int)s0;
+                val[r][hf] = (float)S * (hf ? meta.y : meta.x);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            float v = total[r][t];
+            v = fmaf(s_lo[r], val[r][0], v);
+            v = fmaf(s_hi[r], val[r][1], v);
+            v = fmaf(-m_lo[r], meta.z, v);
+            v = fmaf(-m_hi[r], meta.w, v);
+            total[r][t] = v;
+        }
+    }
+}
+
+// Q6_K: slice sl = 4*b + 2*h + c covers weights 256b + 128h + 32g + 16c + i (g = 0..3, i = 0..15).
+// Staged bytes of the slice: ql[64h+16c+i] (low nibble: g=0, high: g=2), ql[64h+32+16c+i] (low: g=1,
+// high: g=3), qh[32h+16c+i] (bits 2g..2g+1); each g is one scale group (shaders/ops.metal:28-42).
+template <int MT, int R, int PLANES>
+__device__ __forceinline__ void slice_q6k(const uint8_t *const (&row)[R], int sl, int nbc, const uint8_t *xsl,
+                                          size_t xtok_bytes, float (&total)[R][MT]) {
+    const int b = sl >> 2, h = (sl >> 1) & 1, c = sl & 1;
+    uint32_t v[R][4][4];
+    float ds[R][4];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const uint8_t *s = row[r] + 48 * sl;
+        const uint4 l0 = *reinterpret_cast<const uint4 *>(s);
+        const uint4 l1 = *reinterpret_cast<const uint4 *>(s + 16);
+        const uint4 qh = *reinterpret_cast<const uint4 *>(s + 32);
+        const uint2 scw = *reinterpret_cast<const uint2 *>(row[r] + 192 * nbc + 16 * b + 8 * h);
+        const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(row[r] + 208 * nbc + 2 * b));
+        const uint32_t a0[4] = {l0.x, l0.y, l0.z, l0.w}, a1[4] = {l1.x, l1.y, l1.z, l1.w};
+        const uint32_t hh[4] = {qh.x, qh.y, qh.z, qh.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t qA = hh[i] & 0x33333333u;             // g=0 bits at 0-1, g=2 bits at 4-5
+            const uint32_t qB = (hh[i] >> 2) & 0x33333333u;      // g=1 bits at 0-1, g=3 bits at 4-5
+            v[r][0][i] = (a0[i] & 0x0F0F0F0Fu) | ((qA << 4) & 0xF0F0F0F0u);
+            v[r][1][i] = (a1[i] & 0x0F0F0F0Fu) | ((qB << 4) & 0xF0F0F0F0u);
+            v[r][2][i] = ((a0[i] >> 4) & 0x0F0F0F0Fu) | (qA & 0xF0F0F0F0u);
+            v[r][3][i] = ((a1[i] >> 4) & 0x0F0F0F0Fu) | (qB & 0xF0F0F0F0u);
+        }
+        // int8 scale of group g sits at scales[8h + 2g + c]
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            const uint32_t sw = (g < 2 ? scw.x : scw.y) ^ 0x80808080u;           // sc + 128 per byte
+            const uint32_t sbyte = (sw >> (8 * (2 * (g & 1) + c))) & 0xFFu;
+            ds[r][g] = d * (small_uint_to_float(sbyte) - 128.0f);
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < MT; t++) {
+        const uint8_t *xs = xsl + (size_t)t * xtok_bytes;
+        using F = Fmt<1, PLANES>;
+        const float4 inv = *reinterpret_cast<const float4 *>(xs + F::META);
+        const float4 xsum = *reinterpret_cast<const float4 *>(xs + F::META + 16);
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            const uint4 p0 = *reinterpret_cast<const uint4 *>(xs + g * F::GROUP_BYTES);
+            const uint4 p1 = *reinterpret_cast<const uint4 *>(xs + g * F::GROUP_BYTES + 16);
+            const uint4 p2 = *reinterpret_cast<const uint4 *>(xs + g * F::GROUP_BYTES + (PLANES - 1) * 16);
+            const uint32_t x0[4] = {p0.x, p0.y, p0.z, p0.w}, x1[4] = {p1.x, p1.y, p1.z, p1.w};
+            const uint32_t x2[4] = {p2.x, p2.y, p2.z, p2.w};                     // top (signed) plane
+            const float ig = g == 0 ? inv.x : g == 1 ? inv.y : g == 2 ? inv.z : inv.w;
+            const float xg = g == 0 ? xsum.x : g == 1 ? xsum.y : g == 2 ? xsum.z : xsum.w;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                uint32_t s0 = 0, s1 = 0;
+                int st = 0;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    s0 = dp4a_uu(v[r][g][i], x0[i], s0);
+                    if (PLANES == 3) s1 = dp4a_uu(v[r][g][i], x1[i], s1);
+                    st = dp4a_us(v[r][g][i], x2[i], st);
+                }
+                // exact in int32: |S| <= 16*63*2^20
+                const int S = PLANES == 3 ? (st * 256 + (int)s1) * 256 + (int)s0 : st * 256 + (int)s0;
+                const float val = fmaf((float)S, ig, -32.0f * xg);         // sum (q-32) x over the group
+                total[r][t] = fmaf(ds[r][g], val, total[r][t]);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel: warps 0..NCW-1 consume, warp NCW produces.  A row tile is RT = R*NCW rows; consumer
+// warp w owns rows R*w..R*w+R-1 of the tile and walks the row's K chunks as they land.
+// ---------------------------------------------------------------------------------------------
+template <int QT, int MT, int R, int NCW, int PLANES>
+__global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParams p) {
+    using F = Fmt<QT, PLANES>;
+    constexpr int RT = R * NCW;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+    uint64_t *empty = full + MAX_STAGES;
+    const int S = p.stages;
+    const int n_slices = p.K / 64;
+    const size_t xtok_bytes = (size_t)n_slices * F::XSTRIDE;
+    uint8_t *xarea = smem + 128;   // 2 * MAX_STAGES barriers of 8 bytes in front
+    uint8_t *stages = xarea + ((MT * xtok_bytes + 127) / 128) * 128;
+    const size_t stage_bytes = (size_t)RT * F::CHUNK_MAX;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], NCW);
+        }
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    const int nb = p.K / QK_K;
+    if (warp == NCW) {
+        // ---------------- producer ----------------
+        uint32_t it = 0;
+        for (int rt = blockIdx.x; rt < p.n_row_tiles; rt += gridDim.x) {
+            for (int c = 0; c < p.n_chunks; c++, it++) {
+                const int s = it % S;
+                if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1)) {
+                    report_error(p.err, KERR_EMPTY_WAIT);
+                    return;
+                }
+                const int nbc = min(CHUNK_BLOCKS, nb - c * CHUNK_BLOCKS);
+                const uint32_t bytes = (uint32_t)((nbc * F::BLOCK + 15) / 16 * 16);
+                if (lane == 0) mbar_arrive_expect_tx(&full[s], bytes * RT);
+                __syncwarp();
+                if (lane < RT) {
+                    const int row = min(rt * RT + lane, p.N - 1);
+                    bulk_copy_g2s(stages + s * stage_bytes + (size_t)lane * F::CHUNK_MAX,
+                                  p.W + (size_t)row * p.row_stride + (size_t)c * F::CHUNK_MAX, bytes, &full[s]);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    stage_activations<QT, PLANES>(xarea, xtok_bytes, p, warp, lane, NCW);
+    named_barrier_sync(1, NCW * 32);
+
+    uint32_t it = 0;
+    for (int rt = blockIdx.x; rt < p.n_row_tiles; rt += gridDim.x) {
+        float total[R][MT];
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int t = 0; t < MT; t++) total[r][t] = 0.0f;
+
+        for (int c = 0; c < p.n_chunks; c++, it++) {
+            const int s = it % S;
+            if (!mbar_wait(&full[s], (it / S) & 1)) {
+                report_error(p.err, KERR_FULL_WAIT);
+                return;
+            }
+            const int nbc = min(CHUNK_BLOCKS, nb - c * CHUNK_BLOCKS);
+            const uint8_t *row[R];
+#pragma unroll
+            for (int r = 0; r < R; r++) row[r] = stages + s * stage_bytes + (size_t)(warp * R + r) * F::CHUNK_MAX;
+            for (int sl = lane; sl < 4 * nbc; sl += 32) {
+                const uint8_t *xsl = xarea + (size_t)(c * SLICES_PER_CHUNK + sl) * F::XSTRIDE;
+                if (QT == 0) slice_q4k<MT, R, PLANES>(row, sl, xsl, xtok_bytes, total);
+                else slice_q6k<MT, R, PLANES>(row, sl, nbc, xsl, xtok_bytes, total);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
 
 #pragma unroll
-    for (int r = 0; r < R; r++)
+        for (int r = 0; r < R; r++)
 #pragma unroll
-        for (int t = 0; t < MT; t++) {
-            float v = total[r][t];
+            for (int t = 0; t < MT; t++) {
+                float v = total[r][t];
 #pragma unroll
-            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0 && row0 + r < N && t0 + t < M)
-                store_out(Out, (size_t)(t0 + t) * N + row0 + r, v, out_bf16);
-        }
+                for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                const int out_row = rt * RT + warp * R + r;
+                if (lane == 0 && out_row < p.N && t < p.m_valid)
+                    store_out(p.Out, (size_t)t * p.N + out_row, v, p.out_bf16);
+            }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
 // Launch
 // ---------------------------------------------------------------------------------------------
-namespace {
+constexpr int NCW_DEFAULT = 16;
+constexpr int PLANES_DEFAULT = 3;
+constexpr size_t SMEM_LIMIT = 227 * 1024;
 
-// Largest K-chunk whose staged activations fit the shared-memory budget for MT tokens.
-int chunk_elems(int K, int MT) {
-    int cap = MT == 1 ? 16384 : MT == 2 ? 8192 : 4096;
-    return K < cap ? K : cap;
+template <int QT, int MT, int R, int NCW, int PLANES>
+size_t smem_fixed(int K) {
+    return 128 + ((size_t)MT * (K / 64) * Fmt<QT, PLANES>::XSTRIDE + 127) / 128 * 128;
 }
 
-template <int MT, int R, int WARPS>
-cudaError_t launch_one(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                       int K, int N, int M, cudaStream_t s) {
-    const int kc = chunk_elems(K, MT);
-    const size_t smem = (size_t)MT * (kc / SLICE) * SLICE_STRIDE * sizeof(float);
-    dim3 grid((unsigned)((N + R * WARPS - 1) / (R * WARPS)), (unsigned)((M + MT - 1) / MT));
-    dim3 block(WARPS * 32);
-    cudaError_t e;
-    if (wdtype == DT_Q4K) {
-        auto kern = gemv_q4k_kernel<MT, R, WARPS>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        kern<<<grid, block, smem, s>>>(w, x, out, K, N, M, x_dtype == DT_BF16, out_dtype == DT_BF16, kc);
-    } else {
-        auto kern = gemv_q6k_kernel<MT, R, WARPS>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        kern<<<grid, block, smem, s>>>(w, x, out, K, N, M, x_dtype == DT_BF16, out_dtype == DT_BF16, kc,
-                                       q6k_plane_row_stride(K));
-    }
+// Ring depth that fits beside the staged activations (0: not even two stages fit).
+template <int QT, int MT, int R, int NCW, int PLANES>
+int ring_stages(int K, int want) {
+    const size_t stage = (size_t)R * NCW * Fmt<QT, PLANES>::CHUNK_MAX;
+    const size_t fixed = smem_fixed<QT, MT, R, NCW, PLANES>(K);
+    if (fixed + 2 * stage > SMEM_LIMIT) return 0;
+    int s = (int)((SMEM_LIMIT - fixed) / stage);
+    if (s > want) s = want;
+    return s > MAX_STAGES ? MAX_STAGES : s;
+}
+
+template <int QT, int MT, int R, int NCW, int PLANES>
+cudaError_t launch_cfg(const GemvParams &p0, int sm_count, int want_stages, cudaStream_t s) {
+    GemvParams p = p0;
+    constexpr int RT = R * NCW;
+    static_assert(RT <= 32, "one producer lane per row of the tile");
+    p.n_row_tiles = (p.N + RT - 1) / RT;
+    p.n_chunks = (p.K / QK_K + CHUNK_BLOCKS - 1) / CHUNK_BLOCKS;
+    p.stages = ring_stages<QT, MT, R, NCW, PLANES>(p.K, want_stages);
+    if (p.stages < 2) return cudaErrorInvalidConfiguration;
+    const size_t smem = smem_fixed<QT, MT, R, NCW, PLANES>(p.K) + (size_t)p.stages * RT * Fmt<QT, PLANES>::CHUNK_MAX;
+    auto kern = gemv_kernel<QT, MT, R, NCW, PLANES>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    const int grid = p.n_row_tiles < sm_count ? p.n_row_tiles : sm_count;
+    kern<<<grid, (NCW + 1) * 32, smem, s>>>(p);
     return cudaGetLastError();
 }
 
-template <int MT>
-cudaError_t launch_mt(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                      int K, int N, int M, cudaStream_t s) {
-    // Rows per warp trade activation re-reads against CTAs in flight; small N wants more CTAs.
-    if (N >= 16384) return launch_one<MT, 4, 8>(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, s);
-    if (N >= 2048) return launch_one<MT, 2, 8>(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, s);
-    return launch_one<MT, 1, 4>(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, s);
+// Rows per warp: two rows share the staged activations in registers (measured best at every
+// shape tried); one row per warp when the larger ring does not fit beside the activations.
+template <int QT, int MT>
+cudaError_t launch_mt(const GemvParams &p, int sm_count, cudaStream_t s, bool *fits) {
+    constexpr int W = NCW_DEFAULT, P = PLANES_DEFAULT;
+    *fits = true;
+    if (ring_stages<QT, MT, 2, W, P>(p.K, 4) >= 2) return launch_cfg<QT, MT, 2, W, P>(p, sm_count, 4, s);
+    if (ring_stages<QT, MT, 1, W, P>(p.K, 4) >= 2) return launch_cfg<QT, MT, 1, W, P>(p, sm_count, 4, s);
+    *fits = false;
+    return cudaSuccess;
+}
+
+template <int QT>
+cudaError_t launch_fmt(GemvParams p, int M, int x_elem, int out_elem, int sm_count, cudaStream_t s,
+                       uint64_t *launches) {
+    const uint8_t *X = (const uint8_t *)p.X;
+    uint8_t *Out = (uint8_t *)p.Out;
+    int t0 = 0;
+    int mt = M >= 4 ? 4 : M;
+    while (t0 < M) {
+        int m = M - t0 < mt ? M - t0 : mt;
+        p.X = X + (size_t)t0 * p.K * x_elem;
+        p.Out = Out + (size_t)t0 * p.N * out_elem;
+        p.m_valid = m;
+        bool fits = false;
+        cudaError_t e = cudaSuccess;
+        switch (m) {
+            case 1: e = launch_mt<QT, 1>(p, sm_count, s, &fits); break;
+            case 2: e = launch_mt<QT, 2>(p, sm_count, s, &fits); break;
+            case 3: e = launch_mt<QT, 3>(p, sm_count, s, &fits); break;
+            default: e = launch_mt<QT, 4>(p, sm_count, s, &fits); break;
+        }
+        if (e != cudaSuccess) return e;
+        if (!fits) {                 // staged activations of m tokens do not fit: fewer tokens per pass
+            if (m == 1) return cudaErrorInvalidValue;
+            mt = m - 1;
+            continue;
+        }
+        if (launches) (*launches)++;
+        t0 += m;
+    }
+    return cudaSuccess;
 }
 
 }  // namespace
 
-cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                        int K, int N, int M, cudaStream_t s, uint64_t *launches) {
-    if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
-    if (launches) (*launches)++;
-    const int mt = M >= 4 ? 4 : M;
-    switch (mt) {
-        case 1: return launch_mt<1>(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, s);
-        case 2: return launch_mt<2>(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, s);
-        case 3: return launch_mt<3>(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, s);
-        default: return launch_mt<4>(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, s);
-    }
+size_t gemv_max_k() {
+    // largest K whose single-token staging fits beside the smallest ring
+    size_t k = 0;
+    while (ring_stages<1, 1, 1, NCW_DEFAULT, PLANES_DEFAULT>((int)(k + 256), 2) >= 2 && k < (1u << 20)) k += 256;
+    return k;
 }
+
+cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
+                        int K, int N, int M, int sm_count, uint32_t *err_word, cudaStream_t s, uint64_t *launches) {
+    if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
+    GemvParams p{};
+    p.W = w; p.X = x; p.Out = out; p.err = err_word;
+    p.K = K; p.N = N;
+    p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;
+    const int xe = x_dtype == DT_BF16 ? 2 : 4, oe = out_dtype == DT_BF16 ? 2 : 4;
+    if (wdtype == DT_Q4K) {
+        p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
+        return launch_fmt<0>(p, M, xe, oe, sm_count, s, launches);
+    }
+    if (wdtype == DT_Q6K) {
+        p.row_stride = q6k_row_stride(K);
+        return launch_fmt<1>(p, M, xe, oe, sm_count, s, launches);
+    }
+    return cudaErrorInvalidValue;
+}
+
+#ifdef LLMRS_TUNING
+// Tuning hook (only in builds made with -DLLMRS_TUNING): launch one explicit configuration.
+namespace {
+template <int QT, int MT>
+cudaError_t tune_dispatch(const GemvParams &p, int sm, int R, int ncw, int planes, int stages, cudaStream_t s) {
+#define LLMRS_TRY(RR, WW, PP) \
+    if (R == RR && ncw == WW && planes == PP) return launch_cfg<QT, MT, RR, WW, PP>(p, sm, stages, s);
+    LLMRS_TRY(1, 8, 3) LLMRS_TRY(2, 8, 3) LLMRS_TRY(4, 8, 3) LLMRS_TRY(1, 8, 2) LLMRS_TRY(2, 8, 2) LLMRS_TRY(4, 8, 2)
+    LLMRS_TRY(1, 16, 3) LLMRS_TRY(2, 16, 3) LLMRS_TRY(1, 16, 2) LLMRS_TRY(2, 16, 2)
+    LLMRS_TRY(1, 12, 3) LLMRS_TRY(2, 12, 3) LLMRS_TRY(1, 12, 2) LLMRS_TRY(2, 12, 2)
+#undef LLMRS_TRY
+    return cudaErrorInvalidValue;
+}
+}  // namespace
+cudaError_t tune_gemv(int wdtype, const uint8_t *w, const void *x, void *out, int K, int N, int M, int sm_count,
+                      uint32_t *err, int R, int ncw, int planes, int stages, cudaStream_t s) {
+    GemvParams p{};
+    p.W = w; p.X = x; p.Out = out; p.err = err; p.K = K; p.N = N; p.m_valid = M;
+    if (wdtype == DT_Q4K) {
+        p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
+        return M == 1 ? tune_dispatch<0, 1>(p, sm_count, R, ncw, planes, stages, s)
+                      : tune_dispatch<0, 2>(p, sm_count, R, ncw, planes, stages, s);
+    }
+    p.row_stride = q6k_row_stride(K);
+    return M == 1 ? tune_dispatch<1, 1>(p, sm_count, R, ncw, planes, stages, s)
+                  : tune_dispatch<1, 2>(p, sm_count, R, ncw, planes, stages, s);
+}
+#endif
 
 }  // namespace llmrs

@@ -13,28 +13,42 @@ constexpr int Q6K_BLOCK_BYTES = 210; // src/tensor/mod.rs:73
 // GGUF dtype ids (src/tensor/mod.rs:3-33); same values as enum llmrs_dtype.
 constexpr int DT_F32 = 0, DT_Q4K = 12, DT_Q6K = 14, DT_BF16 = 30;
 
-// Byte distance between consecutive rows of a Q6_K weight in the plane layout.
-inline size_t q6k_plane_row_stride(int K) {
+// Device layout of Q6_K weights ("slice-major chunks", LLMRS_LAYOUT_Q6K_SLICES).  A row is cut
+// into chunks of 16 blocks (the last chunk of a row may hold fewer, nbc).  A chunk holds the same
+// 210*nbc bytes as the GGUF blocks it came from, regrouped so that every field a lane reads is
+// 16-byte aligned and consecutive lanes hit distinct shared-memory banks:
+//   [4*nbc slices of 48 B]  slice 4b+2h+c = ql[64h+16c .. +16) | ql[64h+32+16c .. +16) | qh[32h+16c .. +16)
+//                           of block b (h = 0,1 half of the block, c = 0,1)
+//   [nbc * 16 B]            the int8 scales of block b at 16b
+//   [nbc * 2 B]             the f16 d of block b at 2b
+// Chunk ci of a row starts at byte 3360*ci of the row; rows are round_up(210*nb, 16) bytes apart.
+inline size_t q6k_row_stride(int K) {
     size_t nb = (size_t)K / QK_K;
     return (nb * Q6K_BLOCK_BYTES + 15) / 16 * 16;
 }
 
-// Device bytes a [K, N] weight occupies in the layout the kernels read.
+// Device bytes a [K, N] weight occupies in the layout the kernels read (+16 so a bulk copy of
+// the last, padded row segment stays inside the allocation).
 inline size_t weight_device_bytes(int dtype, int K, int N) {
     if (dtype == DT_Q4K) return (size_t)N * (K / QK_K) * Q4K_BLOCK_BYTES;
-    if (dtype == DT_Q6K) return (size_t)N * q6k_plane_row_stride(K);
+    if (dtype == DT_Q6K) return (size_t)N * q6k_row_stride(K) + 16;
     return 0;
 }
 
-// Raw GGUF Q6_K rows -> plane layout (one-off, at upload).
-cudaError_t launch_q6k_repack(const uint8_t *raw, uint8_t *planes, int K, int N, cudaStream_t s);
+// Raw GGUF Q6_K rows -> slice-major chunks (one-off, at upload).
+cudaError_t launch_q6k_repack(const uint8_t *raw, uint8_t *dev, int K, int N, cudaStream_t s);
 
 // Weight -> float32 [N, K], bit-exact with the reference's CPU dequantisation.
 cudaError_t launch_dequant(int wdtype, const uint8_t *w, int K, int N, float *out, cudaStream_t s);
 
-// Decode matmul on CUDA cores, float32 accumulate; any M (tokens are processed in tiles of <= 4).
-// x_dtype / out_dtype are DT_F32 or DT_BF16.  *launches is incremented per kernel launched.
+// Decode matmul: integer dot products per scale group, float32 across groups; any M (tokens are
+// processed in passes of <= 4).  x_dtype / out_dtype are DT_F32 or DT_BF16.  err_word is a device
+// word that receives a KernelError if a bounded wait inside the kernel gives up.  *launches is
+// incremented per kernel launched.
 cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                        int K, int N, int M, cudaStream_t s, uint64_t *launches);
+                        int K, int N, int M, int sm_count, uint32_t *err_word, cudaStream_t s, uint64_t *launches);
+
+// Largest in_features the decode kernel can stage in shared memory.
+size_t gemv_max_k();
 
 }  // namespace llmrs

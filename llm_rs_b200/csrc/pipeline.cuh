@@ -1,0 +1,80 @@
+// mbarrier + bulk-copy (TMA, untiled) helpers for sm_100a.  Every wait is bounded: after
+// WAIT_LIMIT polls it gives up, the caller records an error code and leaves the kernel, so a
+// logic error can not spin a shared GPU forever.
+#pragma once
+#include <stdint.h>
+
+namespace llmrs {
+
+// Polls of mbarrier.try_wait before a wait is abandoned.  Each try_wait blocks for a
+// hardware-defined slice (on the order of a microsecond), so this is seconds, not cycles.
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+// Kernel error codes written to the context's device error word (first error wins).
+enum KernelError : uint32_t {
+    KERR_NONE = 0,
+    KERR_FULL_WAIT = 1,    // a consumer gave up waiting for a bulk copy to land
+    KERR_EMPTY_WAIT = 2,   // the producer gave up waiting for a stage to be released
+    KERR_MMA_WAIT = 3,     // a wait on tensor-core completion gave up
+    KERR_TMEM_ALLOC = 4
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+// Makes freshly initialised barriers visible to the async proxy (bulk copies, tensor cores).
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+// true when the phase with the given parity has completed; false after WAIT_LIMIT polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// Untiled bulk copy global -> shared, completion reported to `bar` in bytes.
+// dst, src and bytes must all be multiples of 16.
+__device__ __forceinline__ void bulk_copy_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Barrier over a subset of the CTA's warps (id 1..15; 0 is __syncthreads).
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ void report_error(uint32_t *err_word, uint32_t code) {
+    if (err_word) atomicCAS(err_word, 0u, code);
+}
+
+}  // namespace llmrs

@@ -125,8 +125,9 @@ def test_matmul_bf16_io(backend, dt, in_bf16, out_bf16):
     xe = O.bf16_bits_to_f32(synth.bf16_bits(x)).reshape(M, K) if in_bf16 else x
     got = run_matmul(backend, upload_weight(backend, dt, w, K, N), x, K, N, M, in_bf16, out_bf16)
     truth = O.matmul(dt, w, K, N, xe, acc="f64")
-    if out_bf16:   # one bf16 rounding of the output: half an ulp = 2^-9 relative
-        assert np.all(np.abs(got - truth) <= np.abs(truth) * 2.0 ** -8 + 1e-6)
+    if out_bf16:   # one bf16 rounding of the output (half an ulp = 2^-9 relative) on top of the float32 sum
+        floor = 1e-5 * float(np.sqrt(np.mean(truth.astype(np.float64) ** 2)))
+        assert np.all(np.abs(got - truth) <= np.abs(truth) * 2.0 ** -8 + floor)
     else:
         assert O.rel_l2(got, truth) <= GEMV_TOL
 
