@@ -6,6 +6,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -31,6 +32,9 @@ struct llmrs_ctx {
     double gpu_secs = 0.0;
     uint64_t launches = 0;
     int sm_count = 0;
+    int gemv_max_m = 64;             // M <= this: decode kernel (1e-4 class); above: tensor-core GEMM
+    void *scratch = nullptr;         // f16 copy of the activations for the tensor-core path
+    size_t scratch_bytes = 0;
     uint32_t *dev_error = nullptr;   // device word: first KernelError reported by a kernel
     std::string error;
 
@@ -54,6 +58,21 @@ struct llmrs_ctx {
         if (code == 0) return LLMRS_OK;
         cudaMemset(dev_error, 0, sizeof code);
         return fail(LLMRS_ERR_KERNEL, "%s: a kernel gave up a bounded wait (code %u); results are incomplete", what, code);
+    }
+    // Grows the scratch buffer (synchronises; never called while the stream is being captured).
+    cudaError_t reserve_scratch(size_t bytes) {
+        if (bytes <= scratch_bytes) return cudaSuccess;
+        cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(stream, &st);
+        if (st != cudaStreamCaptureStatusNone) return cudaErrorStreamCaptureUnsupported;
+        cudaError_t e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return e;
+        if (scratch) cudaFree(scratch);
+        scratch = nullptr;
+        scratch_bytes = 0;
+        e = cudaMalloc(&scratch, bytes);
+        if (e == cudaSuccess) scratch_bytes = bytes;
+        return e;
     }
     // Called before enqueueing: opens the timed span the way the reference opens a
     // command buffer lazily on the first dispatch (metal/mod.rs:287-319).
@@ -160,6 +179,10 @@ int llmrs_cuda_create(int device, void *stream, llmrs_ctx **out) {
         ctx->own_stream = true;
     }
     ctx->sm_count = prop.multiProcessorCount;
+    if (const char *env = getenv("LLMRS_GEMV_MAX_M")) {
+        int v = atoi(env);
+        if (v >= 0) ctx->gemv_max_m = v;
+    }
     e = cudaEventCreate(&ctx->ev_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_end);
     if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->dev_error, sizeof(uint32_t));
@@ -181,6 +204,7 @@ int llmrs_cuda_destroy(llmrs_ctx *ctx) {
     if (ctx->ev_end) cudaEventDestroy(ctx->ev_end);
     if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     if (ctx->dev_error) cudaFree(ctx->dev_error);
+    if (ctx->scratch) cudaFree(ctx->scratch);
     delete ctx;
     return LLMRS_OK;
 }
@@ -307,7 +331,8 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
         return ctx->fail(LLMRS_ERR_DTYPE, "matmul: activations must be F32 or BF16 (got %u -> %u)", input->dtype,
                          out->dtype);
     if (K % QK_K) return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u is not a multiple of 256", K);
-    if (K > gemv_max_k())
+    const bool decode = (int)M <= ctx->gemv_max_m;
+    if (decode && K > gemv_max_k())
         return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u exceeds the supported maximum %zu", K, gemv_max_k());
     if (input->dim0 != K)
         return ctx->fail(LLMRS_ERR_SHAPE, "matmul: input has %u features, weight expects %u", input->dim0, K);
@@ -320,8 +345,18 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: event");
-    e = launch_gemv((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
-                    (int)out->dtype, (int)K, (int)N, (int)M, ctx->sm_count, ctx->dev_error, ctx->stream, &ctx->launches);
+    if (decode) {
+        e = launch_gemv((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
+                        (int)out->dtype, (int)K, (int)N, (int)M, ctx->sm_count, ctx->dev_error, ctx->stream,
+                        &ctx->launches);
+    } else {
+        // The reference switches to its tiled GEMM kernels by seq_len too (metal/mod.rs:542-633).
+        e = ctx->reserve_scratch(gemm_scratch_bytes((int)K, (int)M));
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: scratch (grow it with one call outside graph capture)");
+        e = launch_gemm((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
+                        (int)out->dtype, (int)K, (int)N, (int)M, ctx->scratch, ctx->dev_error, ctx->stream,
+                        &ctx->launches);
+    }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: launch");
     return LLMRS_OK;
 }

@@ -51,4 +51,11 @@ cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype
 // Largest in_features the decode kernel can stage in shared memory.
 size_t gemv_max_k();
 
+// Prefill matmul on the tensor cores (tcgen05, f16 operands, fp32 accumulate in TMEM); M >= 1.
+// The activations are first converted to per-token-scaled f16 in `scratch`
+// (gemm_scratch_bytes() bytes of device memory owned by the caller).
+size_t gemm_scratch_bytes(int K, int M);
+cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
+                        int K, int N, int M, void *scratch, uint32_t *err_word, cudaStream_t s, uint64_t *launches);
+
 }  // namespace llmrs

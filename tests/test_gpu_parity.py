@@ -239,3 +239,102 @@ def test_wrap_torch_memory(backend):
     backend.matmul(out, upload_weight(backend, O.Q6K, w, K, N), xin)
     backend.sync()
     assert O.rel_l2(ot.cpu().numpy(), O.matmul(O.Q6K, w, K, N, x, acc="f64")) <= GEMV_TOL
+
+
+# ---------- prefill GEMM on the tensor cores (M > 64) ----------
+# Tolerance stated for this path: relative L2 <= 2e-3 against the float64 oracle.
+GEMM_TOL = 2e-3
+
+
+@pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
+@pytest.mark.parametrize("K,N,M", [
+    (256, 128, 65), (256, 1, 70), (512, 100, 128), (1024, 256, 200), (768, 130, 257), (4096, 384, 300),
+    (4096, 1000, 513), (14336, 128, 96), (2048, 129, 1000),
+])
+def test_gemm_f32_parity(backend, dt, K, N, M):
+    w = synth.weight(dt, K, N, tid=11 * K + N + M)
+    x = synth.activations(M, K, tid=3000 + M)
+    got = run_matmul(backend, upload_weight(backend, dt, w, K, N), x, K, N, M)
+    truth = O.matmul(dt, w, K, N, x, acc="f64")
+    assert got.shape == truth.shape
+    assert O.rel_l2(got, truth) <= GEMM_TOL
+
+
+@pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
+@pytest.mark.parametrize("in_bf16,out_bf16", [(True, False), (False, True), (True, True)])
+def test_gemm_bf16_io(backend, dt, in_bf16, out_bf16):
+    """bf16 activations in and out, as every call of the reference passes them (arch/llama.rs:61-66)."""
+    K, N, M = 1024, 300, 130
+    w = synth.weight(dt, K, N, tid=41)
+    x = synth.activations(M, K, tid=42)
+    xe = O.bf16_bits_to_f32(synth.bf16_bits(x)).reshape(M, K) if in_bf16 else x
+    got = run_matmul(backend, upload_weight(backend, dt, w, K, N), x, K, N, M, in_bf16, out_bf16)
+    truth = O.matmul(dt, w, K, N, xe, acc="f64")
+    tol = GEMM_TOL + (2.0 ** -8 if out_bf16 else 0.0)       # plus one bf16 rounding of the output
+    assert O.rel_l2(got, truth) <= tol
+
+
+def test_gemm_token_scaling(backend):
+    """Rows of activations with very different magnitudes, an all-zero row and huge values: the
+    per-token power-of-two scaling keeps every row inside f16 range at the same relative accuracy."""
+    K, N, M = 1024, 128, 72
+    w = synth.weight(O.Q4K, K, N, tid=51)
+    x = synth.activations(M, K, tid=52)
+    scales = np.float32(10.0) ** np.linspace(-20, 20, M).astype(np.float32)
+    x = x * scales[:, None]
+    x[5] = 0.0
+    got = run_matmul(backend, upload_weight(backend, O.Q4K, w, K, N), x, K, N, M)
+    truth = O.matmul(O.Q4K, w, K, N, x, acc="f64")
+    assert np.isfinite(got).all() and not got[5].any()
+    for t in range(M):
+        if t != 5:
+            assert O.rel_l2(got[t], truth[t]) <= GEMM_TOL, t
+
+
+@pytest.mark.parametrize("in_f,out_f,seq", [(256, 8, 80), (1024, 64, 100), (4096, 1024, 128)])
+def test_check_matmul_q4k_prefill_lengths(backend, in_f, out_f, seq):
+    """The reference's check (its generator, bf16 in/out, its tolerance) at prefill lengths its own
+    cases never reach (its largest seq is 16; tests/ops.rs:180-185)."""
+    w, xb = O.ref_case_q4k(in_f, out_f, seq)
+    x = O.bf16_bits_to_f32(xb).reshape(seq, in_f)
+    expected = O.matmul(O.Q4K, w, in_f, out_f, x, acc="f32")
+    weight = backend.upload_tensor(TensorView("w", DType.Q4K, [in_f, out_f], w))
+    inp = backend.upload_tensor(TensorView("x", DType.BF16, [in_f, seq], xb))
+    out = backend.alloc([out_f, seq], DType.BF16)
+    backend.matmul(out, weight, inp)
+    backend.sync()
+    bad, max_rel = O.ref_tolerance_failures(expected, backend.read_to_vec_f32(out), in_f)
+    assert bad == 0, f"{bad} elements outside the reference tolerance (max_rel {max_rel})"
+
+
+def test_config3_prefill_full_size(backend):
+    """Config 3 at M=2048: Q4_K 4096 -> 14336 then Q6_K 14336 -> 4096 (the second GEMM reads the
+    first one's bf16 output).  Sampled output rows against the oracle, and linearity in the input."""
+    M, K1, N1, N2 = 2048, 4096, 14336, 4096
+    w1 = synth.weight(O.Q4K, K1, N1, tid=61)
+    w2 = synth.weight(O.Q6K, N1, N2, tid=62)
+    x = synth.activations(M, K1, tid=63)
+    wb1 = upload_weight(backend, O.Q4K, w1, K1, N1)
+    wb2 = upload_weight(backend, O.Q6K, w2, N1, N2)
+    xb = upload_x(backend, x, M, K1)
+    h = backend.alloc([N1, M], DType.BF16)
+    y = backend.alloc([N2, M], DType.F32)
+    backend.matmul(h, wb1, xb)
+    backend.matmul(y, wb2, h)
+    backend.sync()
+    hg = backend.read_to_vec_f32(h).reshape(M, N1)
+    yg = backend.read_to_vec_f32(y).reshape(M, N2)
+    for a, b in [(0, 128), (7000, 7128), (N1 - 128, N1)]:
+        truth = O.matmul(O.Q4K, w1, K1, N1, x, acc="f64", rows=(a, b))
+        assert O.rel_l2(hg[:, a:b], truth[:, a:b]) <= GEMM_TOL + 2.0 ** -8
+    for a, b in [(0, 64), (N2 - 64, N2)]:
+        truth = O.matmul(O.Q6K, w2, N1, N2, hg, acc="f64", rows=(a, b))      # from the device's own h
+        assert O.rel_l2(yg[:, a:b], truth[:, a:b]) <= GEMM_TOL
+    # linearity at full size: matmul(2x) == 2 matmul(x) exactly (power-of-two token scaling)
+    xb2 = upload_x(backend, np.float32(2.0) * x, M, K1)
+    h2 = backend.alloc([N1, M], DType.F32)
+    h1 = backend.alloc([N1, M], DType.F32)
+    backend.matmul(h2, wb1, xb2)
+    backend.matmul(h1, wb1, xb)
+    backend.sync()
+    assert np.array_equal(backend.read_to_vec_f32(h2), np.float32(2.0) * backend.read_to_vec_f32(h1))
