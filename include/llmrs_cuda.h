@@ -105,6 +105,25 @@ int llmrs_cuda_free(llmrs_ctx *ctx, llmrs_buf *buf);
  * synchronisation and no allocation, so it may be captured in a CUDA graph. */
 int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input);
 
+/* The same product as llmrs_cuda_matmul, computed by the tensor-core kernel for any M, with that
+ * kernel's scratch (the activations converted to f16 and one scale per token) held in an 8 MiB
+ * device array that is built into the library instead of in memory the context allocates.  It has
+ * no counterpart in the reference; it exists for hosts that must not allocate device memory once
+ * they are running: a server that gave the whole GPU to its own memory pool, or a loop that cannot
+ * take the device-wide synchronisation a cudaMalloc or cudaFree causes.  This call never allocates
+ * or frees device memory.
+ *   - Limit: gemm scratch = round_up(2*K*M, 256) + 4*M bytes must fit 8 MiB (for example 1023
+ *     tokens at K=4096, 292 at K=14336); larger shapes fail with LLMRS_ERR_SHAPE and a message
+ *     that names both sizes.
+ *   - Every GPU that loads the library holds the 8 MiB until the process exits.
+ *   - The first call on a device looks up the array's device address; make that first call
+ *     before any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents (nothing in it
+ *     needs clearing: each call rewrites what it reads).  Two calls whose kernels may overlap on
+ *     the GPU (different streams or contexts on one device) race on it; serialise them. */
+int llmrs_cuda_matmul_static_scratch(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight,
+                                     const llmrs_buf *input);
+
 /* Dequantises a Q4_K/Q6_K weight to float32 [N, K] in device memory `dev_out`
  * (N*K floats).  The reference has no such op; it exposes, for testing, the
  * values its kernels form in registers (tests/ops.rs:41-59, shaders/ops.metal:322-334). */

@@ -83,6 +83,7 @@ ABI = {
     "llmrs_cuda_wrap": (C.c_int, [_VP, _VP, C.c_uint32, _U64P, C.c_int, _BUFP]),
     "llmrs_cuda_free": (C.c_int, [_VP, _BUFP]),
     "llmrs_cuda_matmul": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
+    "llmrs_cuda_matmul_static_scratch": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_dequantize": (C.c_int, [_VP, _BUFP, _VP]),
     "llmrs_cuda_write": (C.c_int, [_VP, _BUFP, _VP, C.c_size_t]),
     "llmrs_cuda_read_f32": (C.c_int, [_VP, _BUFP, C.POINTER(C.c_float), C.c_size_t]),
@@ -244,6 +245,14 @@ class CudaBackend:
         out = self.read_to_vec_f32(tmp).reshape(N, K)
         tmp.free()
         return out
+
+    def matmul_static_scratch(self, out: CudaBuffer, weight: CudaBuffer, input: CudaBuffer) -> None:
+        """`matmul` through the tensor-core kernel with its scratch in the 8 MiB device array built
+        into the library: for hosts that must not allocate device memory while running.  Raises
+        BackendError (-2) when 2*K*M + 4*M bytes do not fit; calls that may overlap on the GPU race
+        on the shared array."""
+        self._check(self._lib.llmrs_cuda_matmul_static_scratch(self._ctx, C.byref(out._raw), C.byref(weight._raw),
+                                                               C.byref(input._raw)))
 
     def launch_count(self) -> int:
         v = C.c_uint64()

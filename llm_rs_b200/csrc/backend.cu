@@ -361,6 +361,46 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
     return LLMRS_OK;
 }
 
+int llmrs_cuda_matmul_static_scratch(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight,
+                                     const llmrs_buf *input) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!out || !weight || !input || !out->dptr || !weight->dptr || !input->dptr)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul_static_scratch: null buffer");
+    const uint32_t K = weight->dim0, N = weight->dim1 ? weight->dim1 : 1, M = input->dim1 ? input->dim1 : 1;
+    if (weight->dtype != LLMRS_Q4K && weight->dtype != LLMRS_Q6K)
+        return ctx->fail(LLMRS_ERR_DTYPE, "matmul_static_scratch: weight dtype %u is not Q4_K/Q6_K", weight->dtype);
+    const uint32_t want_layout = weight->dtype == LLMRS_Q6K ? LLMRS_LAYOUT_Q6K_SLICES : LLMRS_LAYOUT_RAW;
+    if (weight->layout != want_layout)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul_static_scratch: weight was not created by upload_tensor");
+    if (!dense_elem_bytes(input->dtype) || !dense_elem_bytes(out->dtype))
+        return ctx->fail(LLMRS_ERR_DTYPE, "matmul_static_scratch: activations must be F32 or BF16");
+    if (K % QK_K) return ctx->fail(LLMRS_ERR_SHAPE, "matmul_static_scratch: in_features %u is not a multiple of 256", K);
+    if (input->dim0 != K)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_static_scratch: input has %u features, weight expects %u",
+                         input->dim0, K);
+    const uint32_t out_m = out->dim1 ? out->dim1 : 1;
+    if (out->dim0 != N || out_m != M)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_static_scratch: output is [%u, %u], expected [%u, %u]", out->dim0,
+                         out_m, N, M);
+    if (weight->device != (uint32_t)ctx->device || input->device != (uint32_t)ctx->device ||
+        out->device != (uint32_t)ctx->device)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul_static_scratch: buffers belong to another device");
+    const size_t need = gemm_scratch_bytes((int)K, (int)M), have = gemm_static_scratch_capacity();
+    if (need > have)
+        return ctx->fail(LLMRS_ERR_SHAPE,
+                         "matmul_static_scratch: %u tokens x %u features need %zu bytes of scratch, the built-in "
+                         "array holds %zu; use llmrs_cuda_matmul or fewer tokens per call",
+                         M, K, need, have);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_static_scratch: event");
+    e = launch_gemm_static_scratch((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype,
+                                   out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, ctx->device, ctx->dev_error,
+                                   ctx->stream, &ctx->launches);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_static_scratch: launch");
+    return LLMRS_OK;
+}
+
 int llmrs_cuda_dequantize(llmrs_ctx *ctx, const llmrs_buf *weight, float *dev_out) {
     if (!ctx) return LLMRS_ERR_ARG;
     if (!weight || !weight->dptr || !dev_out) return ctx->fail(LLMRS_ERR_ARG, "dequantize: null pointer");

@@ -31,8 +31,8 @@
 // its TMEM before it exits.
 #include <cuda.h>
 
-#include <cstdio>
 #include <cstdlib>
+#include <mutex>
 #include <type_traits>
 
 #include "kernels.h"
@@ -656,6 +656,48 @@ cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype
     }
     if (e == cudaSuccess && launches) (*launches)++;
     return e;
+}
+
+// ---- the same GEMM with its scratch in a fixed device array (nothing is allocated) -------------
+// The converted activations normally live in a buffer the context grows with cudaMalloc.  Some
+// callers cannot do that: a process that has handed all device memory to its own pool, or a
+// latency-critical loop in which the device-wide synchronisation of cudaMalloc/cudaFree is not
+// acceptable.  For them the scratch below is part of the library image: every GPU that loads the
+// library carries these 8 MiB until the process exits, and no call on this path allocates.
+constexpr size_t STATIC_SCRATCH_BYTES = 8u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+size_t gemm_static_scratch_capacity() { return STATIC_SCRATCH_BYTES; }
+
+// Device address of g_static_scratch on `device`, which must be the current device.  In host
+// code the array's name is only a handle for the runtime, not a device address, so the address
+// is looked up with cudaGetSymbolAddress, once per device, and cached.
+static cudaError_t static_scratch_address(int device, void **out) {
+    constexpr int MAX_DEVICES = 64;
+    static std::mutex lock;
+    static void *addr[MAX_DEVICES] = {};
+    if (device < 0 || device >= MAX_DEVICES) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> guard(lock);
+    if (!addr[device]) {
+        void *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_static_scratch);
+        if (e != cudaSuccess) return e;
+        addr[device] = ptr;
+    }
+    *out = addr[device];
+    return cudaSuccess;
+}
+
+cudaError_t launch_gemm_static_scratch(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out,
+                                       int out_dtype, int K, int N, int M, int device, uint32_t *err_word,
+                                       cudaStream_t s, uint64_t *launches) {
+    if (gemm_scratch_bytes(K, M) > STATIC_SCRATCH_BYTES) return cudaErrorInvalidValue;
+    void *scratch = nullptr;
+    cudaError_t e = static_scratch_address(device, &scratch);
+    if (e != cudaSuccess) return e;
+    // Nothing in the scratch has to start at zero: the conversion kernel rewrites every f16
+    // activation and every token scale the GEMM of this call reads.
+    return launch_gemm(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, scratch, err_word, s, launches);
 }
 
 }  // namespace llmrs

@@ -58,4 +58,13 @@ size_t gemm_scratch_bytes(int K, int M);
 cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                         int K, int N, int M, void *scratch, uint32_t *err_word, cudaStream_t s, uint64_t *launches);
 
+// The same GEMM with its scratch in a fixed 8 MiB device array that is part of the library image:
+// no allocation on this path.  `device` must be the current device; the first call on a device
+// resolves the array's address.  Fails with cudaErrorInvalidValue when gemm_scratch_bytes(K, M)
+// exceeds gemm_static_scratch_capacity().
+size_t gemm_static_scratch_capacity();
+cudaError_t launch_gemm_static_scratch(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out,
+                                       int out_dtype, int K, int N, int M, int device, uint32_t *err_word,
+                                       cudaStream_t s, uint64_t *launches);
+
 }  // namespace llmrs
