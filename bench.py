@@ -107,7 +107,7 @@ def cpu_baseline(dtype: int, K: int, N: int, M: int, budget_s: float, rows: int 
     rows = min(rows or N, N)
     w = synth.weight(dtype, K, rows, tid=2)
     x = synth.activations(M, K, tid=3)
-    threads = O.max_threads()
+    threads = len(os.sched_getaffinity(0))
     O.matmul(dtype, w, K, rows, x, fast=True, threads=threads)          # warm-up
     t0 = time.perf_counter()
     reps = 0
@@ -135,7 +135,7 @@ def run_reference(args, rank: int, world: int):
     from oracle import oracle as O
     w = synth.weight(Q6K, K_IN, rows, tid=2)
     x = synth.activations(M, K_IN, tid=3)
-    threads = O.max_threads()
+    threads = len(os.sched_getaffinity(0))      # all host cores (torchrun sets OMP_NUM_THREADS=1)
     for _ in range(max(args.warmup, 1)):
         O.matmul(Q6K, w, K_IN, rows, x, fast=True, threads=threads)
     t0 = time.perf_counter()
@@ -307,48 +307,116 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if world == 1 and not args.no_cpu_baseline:
         gbs, per_s, info = cpu_baseline(Q6K, K_IN, N_OUT, M, budget_s=10.0)
         line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", **info}
-    if world == 1 and args.extra:
+    if world == 1 and not args.no_extra:
         line["extra"] = extra_measurements(be_factory=lambda: CudaBackend(local_rank, stream=stream.cuda_stream),
                                            stream=stream, peak_gbs=peak_gbs)
     print(json.dumps(line), flush=True)
 
 
 def extra_measurements(be_factory, stream, peak_gbs):
-    """Other shapes of the same op, kernel-only (device-resident inputs, L2-cold by rotation)."""
+    """The other parts of the headline metric, kernel-only (device-resident inputs, CUDA-event time
+    from the context, weights rotated so every launch reads them from HBM, not L2):
+    decode GEMV at the reference bench's shapes, config 2 at M in {8, 32, 64}, the prefill GEMMs of
+    config 3, and the linear stack of one 8B decode step (config 4)."""
     import torch
 
     from llm_rs_b200 import DType, TensorView, synth
-    out = {}
+    tf_peak = 1658.7
+    ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(ppath):
+        with open(ppath) as f:
+            tf_peak = float(json.load(f).get("bf16_tflops", tf_peak))
+    out = {"gemv": {}, "gemm": {}, "decode_stack": {}, "peaks": {"hbm_gbs": peak_gbs, "dense_16bit_tflops": tf_peak}}
     with torch.cuda.stream(stream):
         be = be_factory()
+
+        def time_matmul(dt, K, N, M, in_dt, out_dt, iters):
+            w = synth.weight(dt, K, N, tid=5)
+            copies = min(48, max(1, int(np.ceil(3.2 * L2_BYTES / w.nbytes))))
+            ws = [be.upload_tensor(TensorView("w", DType(dt), [K, N], w)) for _ in range(copies)]
+            xh = synth.activations(M, K)
+            x = be.upload_tensor(TensorView("x", in_dt, [K] if M == 1 else [K, M],
+                                            synth.bf16_bits(xh) if in_dt == DType.BF16 else xh))
+            o = be.alloc([N] if M == 1 else [N, M], out_dt)
+            for i in range(5):
+                be.matmul(o, ws[i % copies], x)
+            be.sync()
+            be.reset_gpu_secs()
+            for i in range(iters):
+                be.matmul(o, ws[i % copies], x)
+            be.sync()
+            t = be.gpu_secs_total() / iters
+            for b in ws + [x, o]:
+                b.free()
+            return t
+
         for name, dt, K, N, Ms in (("q4k_4096x4096", Q4K, 4096, 4096, (1,)),
                                    ("q4k_4096x14336", Q4K, 4096, 14336, (1,)),
                                    ("q6k_14336x4096", Q6K, 14336, 4096, (1,)),
                                    ("q4k_4096x128256", Q4K, 4096, 128256, (1,)),
                                    ("q6k_4096x128256", Q6K, 4096, 128256, (1, 2, 4, 8, 32, 64))):
-            w = synth.weight(dt, K, N, tid=5)
-            copies = min(48, max(1, int(np.ceil(3.2 * L2_BYTES / w.nbytes))))
-            ws = [be.upload_tensor(TensorView("w", DType(dt), [K, N], w)) for _ in range(copies)]
             for M in Ms:
-                x = be.upload_tensor(TensorView("x", DType.F32, [K] if M == 1 else [K, M], synth.activations(M, K)))
-                o = be.alloc([N] if M == 1 else [N, M], DType.F32)
-                iters = 50 if N >= 100000 else 200
-                for i in range(5):
-                    be.matmul(o, ws[i % copies], x)
-                be.sync()
-                be.reset_gpu_secs()
-                for i in range(iters):
-                    be.matmul(o, ws[i % copies], x)
-                be.sync()
-                t = be.gpu_secs_total() / iters
+                t = time_matmul(dt, K, N, M, DType.F32, DType.F32, 50 if N >= 100000 else 200)
                 alg = algorithmic_bytes(dt, K, N, M)
-                out[f"{name}_m{M}"] = {"us": round(t * 1e6, 2), "GBps": round(alg / t / 1e9, 1),
-                                       "frac_of_hbm_peak": round(alg / t / 1e9 / peak_gbs, 4),
-                                       "TFLOPs": round(2.0 * M * K * N / t / 1e12, 2)}
-                x.free()
-                o.free()
-            for b in ws:
+                out["gemv"][f"{name}_m{M}"] = {"us": round(t * 1e6, 2), "GBps": round(alg / t / 1e9, 1),
+                                               "frac_of_hbm_peak": round(alg / t / 1e9 / peak_gbs, 4),
+                                               "kernel": "exact" if M <= 4 else "tensor-core f16"}
+        # config 3: Q4_K 4096 -> 14336 then Q6_K 14336 -> 4096, bf16 activations in and out
+        for M in (128, 512, 2048):
+            for name, dt, K, N in (("q4k_4096x14336", Q4K, 4096, 14336), ("q6k_14336x4096", Q6K, 14336, 4096)):
+                t = time_matmul(dt, K, N, M, DType.BF16, DType.BF16, 30)
+                fl = 2.0 * M * K * N
+                out["gemm"][f"{name}_m{M}"] = {"us": round(t * 1e6, 1), "TFLOPs": round(fl / t / 1e12, 1),
+                                               "frac_of_tensor_peak": round(fl / t / 1e12 / tf_peak, 4)}
+        # config 4: the 225 matmuls of one Llama-3-8B decode step (32 x {wq, wk, wv, wo, gate, up: Q4_K;
+        # down: Q6_K} + output: Q6_K), back to back; norms, rope and attention are outside this path.
+        layer = [(Q4K, 4096, 4096), (Q4K, 4096, 1024), (Q4K, 4096, 1024), (Q4K, 4096, 4096),
+                 (Q4K, 4096, 14336), (Q4K, 4096, 14336), (Q6K, 14336, 4096)]
+        lw = [be.upload_tensor(TensorView("w", DType(dt), [K, N], synth.weight(dt, K, N, tid=100 + i)))
+              for i, (dt, K, N) in enumerate(layer)]
+        n_layer_sets = 4            # 4 distinct layers (551 MB) rotated: > 4x L2, like 32 distinct ones
+        sets = [lw] + [[be.upload_tensor(TensorView("w", DType(dt), [K, N], synth.weight(dt, K, N, tid=200 + 10 * j + i)))
+                        for i, (dt, K, N) in enumerate(layer)] for j in range(n_layer_sets - 1)]
+        wout = be.upload_tensor(TensorView("w", DType.Q6K, [4096, 128256], synth.weight(Q6K, 4096, 128256, tid=300)))
+        weight_bytes = 32 * sum(N * (K // 256) * BLOCK_BYTES[dt] for dt, K, N in layer) + 128256 * 16 * 210
+        for M in (1, 4, 16, 64):
+            shp = (lambda d: [d] if M == 1 else [d, M])
+            xs = {4096: be.upload_tensor(TensorView("x", DType.BF16, shp(4096), synth.bf16_bits(synth.activations(M, 4096)))),
+                  14336: be.upload_tensor(TensorView("x", DType.BF16, shp(14336), synth.bf16_bits(synth.activations(M, 14336))))}
+            outs = {n: be.alloc(shp(n), DType.BF16) for n in (4096, 1024, 14336, 128256)}
+
+            def step():
+                for l in range(32):
+                    ws = sets[l % n_layer_sets]
+                    for (dt, K, N), wb in zip(layer, ws):
+                        be.matmul(outs[N], wb, xs[K])
+                be.matmul(outs[128256], wout, xs[4096])
+            for _ in range(2):
+                step()
+            be.sync()
+            # the 225 launches are captured once in a CUDA graph and replayed (matmul only enqueues)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step()
+            graph.replay()
+            stream.synchronize()
+            reps = 10
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+            t = e0.elapsed_time(e1) * 1e-3 / reps
+            del graph
+            out["decode_stack"][f"m{M}"] = {"ms_per_step": round(t * 1e3, 4), "tok_per_s": round(M / t, 1),
+                                            "weight_GBps": round(weight_bytes / t / 1e9, 1),
+                                            "frac_of_hbm_peak": round(weight_bytes / t / 1e9 / peak_gbs, 4),
+                                            "matmuls_per_step": 225}
+            for b in list(xs.values()) + list(outs.values()):
                 b.free()
+        out["decode_stack"]["note"] = ("linear stack only (225 matmuls, bf16 activations), one CUDA graph per step; "
+                                       "weight bytes per step 4 841 250 816")
         be.close()
     return out
 
@@ -360,7 +428,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=1, help="M, decode batch (1..64)")
-    ap.add_argument("--extra", action="store_true", help="also time the other shapes of the op (N=1 only)")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the other parts of the metric (other GEMV shapes, prefill GEMM TFLOP/s, decode stack)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 

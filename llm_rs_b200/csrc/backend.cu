@@ -32,7 +32,7 @@ struct llmrs_ctx {
     double gpu_secs = 0.0;
     uint64_t launches = 0;
     int sm_count = 0;
-    int gemv_max_m = 64;             // M <= this: decode kernel (1e-4 class); above: tensor-core GEMM
+    int gemv_max_m = 4;              // M <= this: exact decode kernel (1e-4 class); above: tensor-core GEMM (2e-3 class)
     void *scratch = nullptr;         // f16 copy of the activations for the tensor-core path
     size_t scratch_bytes = 0;
     uint32_t *dev_error = nullptr;   // device word: first KernelError reported by a kernel
