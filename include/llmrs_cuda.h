@@ -47,7 +47,7 @@ enum llmrs_layout {
      *   4*nbc slices of 48 B: slice 4b+2h+c = ql[64h+16c..+16) | ql[64h+32+16c..+16) | qh[32h+16c..+16)
      *                         of block b (h = half of the block, c = 0,1),
      *   nbc*16 B: the int8 scales of block b at 16b,   nbc*2 B: the f16 d of block b at 2b.
-     * Rows are round_up(210*K/256, 16) bytes apart. */
+     * Rows are round_up(210*K/256, 32) bytes apart. */
     LLMRS_LAYOUT_Q6K_SLICES = 1
 };
 

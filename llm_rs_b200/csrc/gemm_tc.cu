@@ -6,18 +6,20 @@
 // re-dequantise the weights for every 16 (or 4) tokens.  Here a CTA owns 128 weight rows and up
 // to 256 tokens and walks K in stages of 128:
 //
+//   (persistent: one CTA per SM walks the tiles; 14 warps)
 //   warps 0-7  dequantise the step's 128 x 64 weight tile straight from global memory (L2) to
 //              f16 and store it into TENSOR MEMORY (tcgen05.st; thread = weight row = TMEM lane),
 //              where the MMA reads it as its A operand.  Keeping the weights out of shared
 //              memory matters: with both operands in shared memory the operand reads plus the
 //              tile writes need ~180 B/clk of a 128 B/clk shared memory and the tensor pipe
-//              measured 42 % busy.  After the K loop the same warps are the epilogue
-//              (TMEM -> registers -> global).
+//              measured 42 % busy.
 //   warp  8    one lane issues the TMA tensor copy of the step's tokens x 64 f16 activation tile
 //              (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill past the last token).
 //   warp  9    allocates TMEM; one lane issues tcgen05.mma (kind::f16, f16 x bf16 -> fp32,
 //              M=128, N=tokens, K=16, four per step) with the accumulator in TMEM, and
 //              tcgen05.commit to hand shared-memory stages back and to publish the accumulator.
+//   warps 10-13 epilogue: tcgen05.ld -> token scale -> global, overlapping the next tile's K loop
+//              (the accumulator is double-buffered up to 128 tokens per tile).
 //
 // Weights are the UMMA "A" operand (rows = TMEM lanes), tokens the "B" operand (columns), so one
 // dequantised tile feeds up to 256 tokens.  Both operands are f16, not bf16: with bf16 x bf16 the
@@ -47,7 +49,10 @@ constexpr int TILE_ROWS = 128;        // weight rows per CTA = UMMA M
 constexpr int BK = 64;                // K elements per stage: 64 f16 = one 128-byte swizzled row
 constexpr int UMMA_K = 16;
 constexpr int DEQ_WARPS = 8;
-constexpr int GEMM_THREADS = (DEQ_WARPS + 2) * 32;
+constexpr int EPI_WARPS = 4;
+constexpr int EPI_TOK = 16;           // tokens an epilogue warp transposes at a time
+constexpr int TN_PAD = 256;           // floats reserved per epilogue warp for the tile's token factors
+constexpr int GEMM_THREADS = (DEQ_WARPS + 2 + EPI_WARPS) * 32;
 
 struct GemmParams {
     const uint8_t *W;
@@ -55,6 +60,7 @@ struct GemmParams {
     uint32_t *err;
     int K, N, M;
     int out_bf16;
+    int sm_count;
     size_t row_stride;
     const float *tok_scale;   // per token: factor that undoes the power-of-two scaling of its f16 activations
 };
@@ -210,18 +216,24 @@ constexpr uint32_t H2_1056 = 0x64206420u;     // (1056.0, 1056.0) = 1024 + 32
 __device__ __forceinline__ uint32_t h2_bcast_lo(uint32_t v) { return __byte_perm(v, 0, 0x1010u); }
 __device__ __forceinline__ uint32_t h2_bcast_hi(uint32_t v) { return __byte_perm(v, 0, 0x3232u); }
 
-// Q4_K: thread (row, h16) takes quant bytes 16*h16..16*h16+15 of every pair p: elements
-// 16*h16..+15 of sub-block 2p (low nibbles) and of sub-block 2p+1 (high nibbles) (tests/ops.rs:29-59).
+// Work split of the eight dequantising warps: warp w owns TMEM lanes 32*(w%4).. (a hardware rule:
+// a warp reaches only its own lane quarter), thread = weight row; group g = w/4 produces the
+// stages of parity g, i.e. half g (128 weights) of every 256-weight block of its row.  The two
+// groups run a stage apart, so the store/barrier latency of one hides behind the arithmetic of
+// the other.
+
+// Q4_K half-block g: pairs 2g and 2g+1, each 32 quant bytes = sub-blocks 2p (low nibbles) and
+// 2p+1 (high nibbles) (tests/ops.rs:29-59).
 struct RawQ4 {
     uint4 hdr;      // f16 d, f16 dmin, 12 packed scale bytes
-    uint4 q[4];     // this thread's 16 quant bytes of each pair
+    uint4 q[4];     // quant bytes of pair 2g (q[0], q[1]) and pair 2g+1 (q[2], q[3])
 };
-__device__ __forceinline__ RawQ4 load_raw_q4k(const uint8_t *row_ptr, int b, int h16) {
+__device__ __forceinline__ RawQ4 load_raw_q4k(const uint8_t *row_ptr, int b, int g) {
     const uint8_t *blk = row_ptr + (size_t)b * Q4K_BLOCK_BYTES;
     RawQ4 r;
-    r.hdr = ldg128(blk);
+    r.hdr = ldg128_pinned(blk);
 #pragma unroll
-    for (int i = 0; i < 4; i++) r.q[i] = ldg128(blk + 16 + 32 * i + 16 * h16);
+    for (int i = 0; i < 4; i++) r.q[i] = ldg128_pinned(blk + 16 + 64 * g + 16 * i);
     return r;
 }
 // The block's eight 6-bit scales and mins as bytes: sc[0..3], sc[4..7], mn[0..3], mn[4..7]
@@ -242,84 +254,97 @@ __device__ __forceinline__ ScalesQ4 unpack_scales_q4k(const uint4 &hdr) {
     s.dmin_pair = (dmin ^ 0x8000u) * 0x00010001u;                 // (-dmin, -dmin)
     return s;
 }
-// a_taddr: TMEM address (this warp's lane quarter, first column of the stage's weight tile).
-template <int P>
-__device__ __forceinline__ void dequant_q4k_step(const RawQ4 &raw, const ScalesQ4 &sq, int h16, uint32_t a_taddr) {
-    // sub-blocks 2P (low nibbles) and 2P+1 (high nibbles): bytes 2P&3, (2P+1)&3 of word P>>1
-    const uint32_t scw = sq.sc[P >> 1], mnw = sq.mn[P >> 1];
-    const uint32_t sc2 = h2_sub((P & 1) ? magic_hi(scw) : magic_lo(scw), H2_1024);    // (sc_lo, sc_hi) exact
-    const uint32_t mn2 = h2_sub((P & 1) ? magic_hi(mnw) : magic_lo(mnw), H2_1024);
+// One pair (64 weights) -> 32 TMEM columns at a_taddr: sub-block 2p in columns 0..15, 2p+1 in 16..31.
+// scw / mnw hold the pair's two scale bytes and two min bytes in their low 16 bits.
+__device__ __forceinline__ void dequant_q4k_pair(const uint4 &qa, const uint4 &qb, uint32_t scw, uint32_t mnw,
+                                                 const ScalesQ4 &sq, uint32_t a_taddr) {
+    const uint32_t sc2 = h2_sub(magic_lo(scw), H2_1024);          // (sc_lo, sc_hi) exact
+    const uint32_t mn2 = h2_sub(magic_lo(mnw), H2_1024);
     const uint32_t ds2 = h2_mul(sc2, sq.d_pair);                  // (d*sc_lo, d*sc_hi/16), rounded to f16
     const uint32_t dm2 = h2_mul(mn2, sq.dmin_pair);               // (-dmin*m_lo, -dmin*m_hi)
     const uint32_t s_lo = h2_bcast_lo(ds2), s_hi = h2_bcast_hi(ds2);
     const uint32_t m_lo = h2_bcast_lo(dm2), m_hi = h2_bcast_hi(dm2);
-    const uint4 q = raw.q[P];
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-    uint32_t lo[8], hi[8];
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    uint32_t lo[16], hi[16];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
+    for (int j = 0; j < 8; j++) {
         const uint32_t l4 = w[j] & 0x0F0F0F0Fu, h4 = w[j] & 0xF0F0F0F0u;
         lo[2 * j] = h2_fma(h2_sub(magic_lo(l4), H2_1024), s_lo, m_lo);
         lo[2 * j + 1] = h2_fma(h2_sub(magic_hi(l4), H2_1024), s_lo, m_lo);
         hi[2 * j] = h2_fma(h2_sub(magic_lo(h4), H2_1024), s_hi, m_hi);
         hi[2 * j + 1] = h2_fma(h2_sub(magic_hi(h4), H2_1024), s_hi, m_hi);
     }
-    // k-local positions: low sub-block 16*h16 + i -> columns 8*h16 + i/2; high: 32 + 16*h16 + i
-    tmem_st8(a_taddr + 8 * h16, lo);
-    tmem_st8(a_taddr + 16 + 8 * h16, hi);
+    tmem_st16(a_taddr, lo);
+    tmem_st16(a_taddr + 16, hi);
+}
+// Half-block G (template: the scale bytes are picked at compile time) -> 64 TMEM columns.
+template <int G>
+__device__ __forceinline__ void dequant_q4k_half(const RawQ4 &raw, const ScalesQ4 &sq, uint32_t a_taddr) {
+    // sub-blocks 4G..4G+3 are bytes 0..3 of word G of the unpacked scales
+    const uint32_t scw = sq.sc[G], mnw = sq.mn[G];
+    dequant_q4k_pair(raw.q[0], raw.q[1], scw, mnw, sq, a_taddr);
+    dequant_q4k_pair(raw.q[2], raw.q[3], scw >> 16, mnw >> 16, sq, a_taddr + 32);
 }
 
-// Q6_K (slice-major device layout, kernels.h): in K step 2h+s2 of a block, thread (row, gsel)
-// takes scale groups c = 0,1 of g = 2*s2 + gsel in half h (shaders/ops.metal:28-42, 322-334).
-// Both steps of a half read the same ql bytes (low nibbles for s2 = 0, high for s2 = 1).
+// Q6_K half h of a block in the slice-major device layout (kernels.h): slices (h, c = 0, 1), each
+// ql[64h+16c..+16) | ql[64h+32+16c..+16) | qh[32h+16c..+16).  Weight 128h + 32g + 16c + i has its
+// low nibble in ql run (g & 1), low half for g < 2 and high half for g >= 2, and bits 2g..2g+1 of
+// qh; group scale scales[8h + 2g + c] (shaders/ops.metal:28-42, 322-334).
 struct RawQ6 {
-    uint4 ql[2][2];   // [h][c]: ql run `gsel` of slice (h, c)
-    uint4 qh[2][2];   // [h][c]
-    uint4 sc;         // 16 int8 scales of the block
+    uint4 ql[2][2];   // [c][run]
+    uint4 qh[2];      // [c]
+    uint2 sc;         // int8 scales[8h .. 8h+8)
     uint32_t d;       // f16 bits
 };
-__device__ __forceinline__ RawQ6 load_raw_q6k(const uint8_t *row_ptr, int nb, int b, int gsel) {
+__device__ __forceinline__ RawQ6 load_raw_q6k(const uint8_t *row_ptr, int nb, int b, int h) {
     const int ci = b >> 4, bl = b & 15;
     const int nbc = min(16, nb - 16 * ci);
     const uint8_t *chunk = row_ptr + (size_t)3360 * ci;
     RawQ6 r;
-#pragma unroll
-    for (int h = 0; h < 2; h++)
-#pragma unroll
-        for (int c = 0; c < 2; c++) {
-            const uint8_t *sp = chunk + 48 * (4 * bl + 2 * h + c);
-            r.ql[h][c] = ldg128(sp + 16 * gsel);
-            r.qh[h][c] = ldg128(sp + 32);
-        }
-    r.sc = ldg128(chunk + 192 * nbc + 16 * bl);
-    r.d = __ldg(reinterpret_cast<const uint16_t *>(chunk + 208 * nbc + 2 * bl));
+    // slices (h, 0) and (h, 1) are 96 contiguous bytes at a multiple of 32: three whole sectors
+    const uint8_t *sp = chunk + 48 * (4 * bl + 2 * h);
+    ldg256_stream(sp, r.ql[0][0], r.ql[0][1]);
+    ldg256_stream(sp + 32, r.qh[0], r.ql[1][0]);
+    ldg256_stream(sp + 64, r.ql[1][1], r.qh[1]);
+    r.sc = ldg64_pinned(chunk + 192 * nbc + 16 * bl + 8 * h);
+    r.d = ldg16_pinned(chunk + 208 * nbc + 2 * bl);
     return r;
 }
-template <int P>
-__device__ __forceinline__ void dequant_q6k_step(const RawQ6 &raw, int gsel, uint32_t a_taddr) {
-    constexpr int h = P >> 1, s2 = P & 1;
-    const int g = 2 * s2 + gsel;
-    // int8 scales[8h + 4s2 + 2*gsel + c], c = 0,1: (sc + 128) as bytes -> f16 pair -> minus 128 -> times d
-    const uint32_t scw = (h ? (s2 ? raw.sc.w : raw.sc.z) : (s2 ? raw.sc.y : raw.sc.x)) ^ 0x80808080u;
-    const uint32_t sc2 = h2_sub(gsel ? magic_hi(scw) : magic_lo(scw), 0x64806480u);   // 1024 + 128
-    const uint32_t ds2 = h2_mul(sc2, raw.d * 0x00010001u);                            // (d*sc_c0, d*sc_c1)
-    uint32_t o[16];
+// Half-block -> 64 TMEM columns: K-local position 32g + 16c + i -> column 16g + 8c + i/2.
+__device__ __forceinline__ void dequant_q6k_half(const RawQ6 &raw, uint32_t a_taddr) {
+    const uint32_t d2 = raw.d * 0x00010001u;
+    // (sc + 128) as bytes -> f16 pairs -> minus 128 -> times d: scale pairs (g, c=0), (g, c=1)
+    const uint32_t s01 = raw.sc.x ^ 0x80808080u, s23 = raw.sc.y ^ 0x80808080u;
+    const uint32_t ds[4] = {h2_mul(h2_sub(magic_lo(s01), 0x64806480u), d2), h2_mul(h2_sub(magic_hi(s01), 0x64806480u), d2),
+                            h2_mul(h2_sub(magic_lo(s23), 0x64806480u), d2), h2_mul(h2_sub(magic_hi(s23), 0x64806480u), d2)};
+    uint32_t o[4][16];                            // [g][8c + 2i + {0,1}]
 #pragma unroll
     for (int c = 0; c < 2; c++) {
-        const uint4 ql = raw.ql[h][c], qh = raw.qh[h][c];
-        const uint32_t ds = c ? h2_bcast_hi(ds2) : h2_bcast_lo(ds2);
-        const uint32_t lw[4] = {ql.x, ql.y, ql.z, ql.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
+        const uint4 q0 = raw.ql[c][0], q1 = raw.ql[c][1], qh = raw.qh[c];
+        const uint32_t l0[4] = {q0.x, q0.y, q0.z, q0.w}, l1[4] = {q1.x, q1.y, q1.z, q1.w};
+        const uint32_t hw[4] = {qh.x, qh.y, qh.z, qh.w};
+        uint32_t dsc[4];
+#pragma unroll
+        for (int g = 0; g < 4; g++) dsc[g] = c ? h2_bcast_hi(ds[g]) : h2_bcast_lo(ds[g]);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const uint32_t lo = (s2 ? (lw[i] >> 4) : lw[i]) & 0x0F0F0F0Fu;
-            const uint32_t hi = ((hw[i] >> (2 * g)) & 0x03030303u) << 4;
-            const uint32_t q = lo | hi;                                   // four 6-bit quants
-            o[8 * c + 2 * i] = h2_mul(h2_sub(magic_lo(q), H2_1056), ds);   // (q - 32) * d*sc
-            o[8 * c + 2 * i + 1] = h2_mul(h2_sub(magic_hi(q), H2_1056), ds);
+            // four bytes of 6-bit quants for each of the four groups, 11 logic ops for 16 weights:
+            // qA keeps the g=0 bits at 0-1 and the g=2 bits at 4-5 of every qh byte, qB likewise g=1 / g=3
+            const uint32_t qA = hw[i] & 0x33333333u;
+            const uint32_t qB = (hw[i] >> 2) & 0x33333333u;
+            const uint32_t v[4] = {(l0[i] & 0x0F0F0F0Fu) | ((qA << 4) & 0xF0F0F0F0u),
+                                   (l1[i] & 0x0F0F0F0Fu) | ((qB << 4) & 0xF0F0F0F0u),
+                                   ((l0[i] >> 4) & 0x0F0F0F0Fu) | (qA & 0xF0F0F0F0u),
+                                   ((l1[i] >> 4) & 0x0F0F0F0Fu) | (qB & 0xF0F0F0F0u)};
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                o[g][8 * c + 2 * i] = h2_mul(h2_sub(magic_lo(v[g]), H2_1056), dsc[g]);      // (q - 32) * d*sc
+                o[g][8 * c + 2 * i + 1] = h2_mul(h2_sub(magic_hi(v[g]), H2_1056), dsc[g]);
+            }
         }
     }
-    // k-local positions 32*gsel + 16c + i -> columns 16*gsel + 8c + i/2
-    tmem_st16(a_taddr + 16 * gsel, o);
+#pragma unroll
+    for (int g = 0; g < 4; g++) tmem_st16(a_taddr + 16 * g, o[g]);
 }
 
 template <int QT> struct RawOf;
@@ -341,40 +366,58 @@ template <int TN> struct GemmCfg {
     static constexpr int STAGE_K = BK * KSUB;
     static constexpr int SUBTILE_BYTES = TN * BK * 2;
     static constexpr int STAGE_BYTES = SUBTILE_BYTES * KSUB;
-    static constexpr int STAGES = TN >= 256 ? 3 : 4;
-    static constexpr uint32_t A_STAGE_COLS = STAGE_K / 2;            // 64 TMEM columns
-    static constexpr uint32_t A_BASE_COL = TN;                       // accumulator in columns [0, TN)
+    static constexpr uint32_t A_STAGE_COLS = STAGE_K / 2;            // 64 TMEM columns per weight stage
+    // Tensor memory (512 columns): accumulators first, weight stages behind them.  Up to 128
+    // tokens the accumulator is double-buffered, so the epilogue of one tile overlaps the K loop
+    // of the next; a 256-token accumulator leaves room for one.
+    static constexpr int ACC_BUFS = TN <= 128 ? 2 : 1;
+    static constexpr uint32_t A_BASE_COL = ACC_BUFS * TN;
+    static constexpr int TMEM_STAGES = (512 - (int)A_BASE_COL) / (int)A_STAGE_COLS;
+    static constexpr int SMEM_STAGES = (227 * 1024 - 1280 - (EPI_WARPS * (EPI_TOK * 32 * 4) + EPI_WARPS * TN_PAD * 4)) / STAGE_BYTES;
+    static constexpr int STAGES = TMEM_STAGES < SMEM_STAGES ? (TMEM_STAGES < 4 ? TMEM_STAGES : 4)
+                                                            : (SMEM_STAGES < 4 ? SMEM_STAGES : 4);
+    static_assert(STAGES >= 2, "at least a double buffer");
     static constexpr uint32_t TMEM_USED = A_BASE_COL + STAGES * A_STAGE_COLS;
     static constexpr uint32_t TMEM_COLS = TMEM_USED <= 256 ? 256 : 512;
-    static_assert(TMEM_USED <= 512, "accumulator and weight stages must fit the 512 TMEM columns");
-    static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + 256;
+    static_assert(TMEM_USED <= 512, "accumulators and weight stages must fit the 512 TMEM columns");
+    // epilogue staging: per epilogue warp [EPI_TOK tokens][32 rows] of up to 4 bytes, plus TN token factors
+    static constexpr size_t EPI_BYTES = (size_t)EPI_WARPS * (EPI_TOK * 32 * 4) + (size_t)EPI_WARPS * TN_PAD * 4;
+    static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + 256 + EPI_BYTES;
+    static_assert(SMEM <= 227 * 1024, "shared memory budget");
 };
 
+// Persistent: one CTA per SM walks tiles (weight tile fastest, so the CTAs of a wave share one
+// activation tile through L2).  14 warps: 0-7 dequantise, 8 TMA, 9 MMA + TMEM owner, 10-13 epilogue.
 template <int QT, int TN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     using C = GemmCfg<TN>;
     constexpr int S = C::STAGES;
+    constexpr int AB = C::ACC_BUFS;
     constexpr uint32_t IDESC = umma_idesc_f16(TN);
 
     extern __shared__ uint8_t smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     uint8_t *tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + S * C::STAGE_BYTES);
-    uint64_t *full = bars, *empty = bars + S, *acc_full = bars + 2 * S;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * S + 1);
+    uint64_t *full = bars, *empty = bars + S, *acc_full = bars + 2 * S, *acc_empty = bars + 2 * S + AB;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * S + 2 * AB);
+    uint8_t *epi_stage = tiles + S * C::STAGE_BYTES + 256;       // 256 bytes of barriers in front, 16-byte aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * TILE_ROWS;          // first weight row of the tile
-    const int t0 = blockIdx.y * TN;                 // first token of the tile
     const int nstages = p.K / C::STAGE_K;           // K is a multiple of 256
+    const int w_tiles = (p.N + TILE_ROWS - 1) / TILE_ROWS;
+    const int n_tiles = w_tiles * ((p.M + TN - 1) / TN);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
-            mbar_init(&full[s], DEQ_WARPS + 1);     // 8 dequant warps + the TMA thread (with its bytes)
+            mbar_init(&full[s], DEQ_WARPS / 2 + 1); // the 4 warps of one dequant group + the TMA thread (with its bytes)
             mbar_init(&empty[s], 1);                // tcgen05.commit
         }
-        mbar_init(acc_full, 1);
+        for (int a = 0; a < AB; a++) {
+            mbar_init(&acc_full[a], 1);             // tcgen05.commit after the tile's last MMA
+            mbar_init(&acc_empty[a], EPI_WARPS);    // epilogue warps, once they have read it out
+        }
         mbar_init_fence();
     }
     if (warp == DEQ_WARPS + 1) {                    // the MMA warp owns TMEM
@@ -387,93 +430,66 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp < DEQ_WARPS) {
-        // ---------------- dequantise the weight tile, stage by stage ----------------
-        const int r = threadIdx.x & 127, sel = threadIdx.x >> 7;
-        const int row = min(n0 + r, p.N - 1);
-        const uint8_t *row_ptr = p.W + (size_t)row * p.row_stride;
+        // ---------------- dequantise weight tiles: group g produces the stages of parity g ----------------
+        const int r = threadIdx.x & 127, g = threadIdx.x >> 7;
         const int nb = p.K / QK_K;
-        bool ok = true;
         // TMEM address of this warp's lane quarter, first weight column
         const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + C::A_BASE_COL;
-        // one stage = K steps 2*hb and 2*hb+1 of the block: wait, store 64 f16 weights, hand over
-        auto stage = [&](auto hbc, const typename RawOf<QT>::type &raw, const ScalesQ4 &sq, int st) {
-            constexpr int HB = decltype(hbc)::value;
-            const int s = st % S;
-            if (st >= S && !mbar_wait(&empty[s], ((st / S) - 1) & 1)) {
-                report_error(p.err, KERR_EMPTY_WAIT);
-                ok = false;
-                return;
-            }
-            const uint32_t a_taddr = lane_base + (uint32_t)s * C::A_STAGE_COLS;
-            if constexpr (QT == 0) {
-                dequant_q4k_step<2 * HB>(raw, sq, sel, a_taddr);
-                dequant_q4k_step<2 * HB + 1>(raw, sq, sel, a_taddr + 32);
-            } else {
-                dequant_q6k_step<2 * HB>(raw, sel, a_taddr);
-                dequant_q6k_step<2 * HB + 1>(raw, sel, a_taddr + 32);
-            }
-            tmem_st_wait();                      // this warp's tensor-memory stores have landed
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full[s]);
-        };
-        typename RawOf<QT>::type cur = load_raw<QT>(row_ptr, nb, 0, sel);
-        for (int b = 0; b < nb && ok; b++) {
-            typename RawOf<QT>::type nxt = cur;
-            if (b + 1 < nb) nxt = load_raw<QT>(row_ptr, nb, b + 1, sel);     // in flight during this block
-            ScalesQ4 sq{};
-            if constexpr (QT == 0) sq = unpack_scales_q4k(cur.hdr);
-            stage(std::integral_constant<int, 0>{}, cur, sq, 2 * b);
-            if (ok) stage(std::integral_constant<int, 1>{}, cur, sq, 2 * b + 1);
-            cur = nxt;
-        }
-        // ---------------- epilogue: TMEM -> registers -> global ----------------
-        if (ok && !mbar_wait(acc_full, 0)) {
-            report_error(p.err, KERR_MMA_WAIT);
-            ok = false;
-        }
-        if (ok) {
-            tc_fence_after();
-            const int quarter = warp & 3;                       // TMEM lanes this warp may read
-            const int out_row = n0 + 32 * quarter + lane;
-            constexpr int COLS_PER_GROUP = TN / 2;              // warps 0-3: first half, 4-7: second half
-            const int col_base = (warp >> 2) * COLS_PER_GROUP;
-#pragma unroll 1
-            for (int c0 = 0; c0 < COLS_PER_GROUP; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(col_base + c0), v);
-                tmem_ld_wait();
-                if (out_row < p.N) {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const int tok = t0 + col_base + c0 + j;
-                        if (tok < p.M) {
-                            const size_t idx = (size_t)tok * p.N + out_row;
-                            const float val = __uint_as_float(v[j]) * __ldg(p.tok_scale + tok);
-                            if (p.out_bf16) ((__nv_bfloat16 *)p.Out)[idx] = __float2bfloat16_rn(val);
-                            else ((float *)p.Out)[idx] = val;
-                        }
-                    }
+        bool ok = true;
+        uint32_t tile_it = 0;                       // stages of the tiles before this one
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, tile_it += (uint32_t)nstages) {
+            const int n0 = (tile % w_tiles) * TILE_ROWS;
+            const int row = min(n0 + r, p.N - 1);
+            const uint8_t *row_ptr = p.W + (size_t)row * p.row_stride;
+            typename RawOf<QT>::type cur = load_raw<QT>(row_ptr, nb, 0, g);
+            for (int b = 0; b < nb; b++) {
+                typename RawOf<QT>::type nxt = cur;
+                if (b + 1 < nb) nxt = load_raw<QT>(row_ptr, nb, b + 1, g);     // in flight during this block
+                const uint32_t it = tile_it + 2u * (uint32_t)b + (uint32_t)g;   // stage number over all tiles
+                const uint32_t s = it % S;
+                if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1)) {
+                    report_error(p.err, KERR_EMPTY_WAIT);
+                    ok = false;
+                    break;
                 }
+                const uint32_t a_taddr = lane_base + s * C::A_STAGE_COLS;
+                if constexpr (QT == 0) {
+                    const ScalesQ4 sq = unpack_scales_q4k(cur.hdr);
+                    if (g == 0) dequant_q4k_half<0>(cur, sq, a_taddr);
+                    else dequant_q4k_half<1>(cur, sq, a_taddr);
+                } else {
+                    dequant_q6k_half(cur, a_taddr);
+                }
+                tmem_st_wait();                      // this warp's tensor-memory stores have landed
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full[s]);
+                cur = nxt;
             }
         }
     } else if (warp == DEQ_WARPS) {
         // ---------------- TMA producer of the activation tiles ----------------
         if (lane == 0) {
-            for (int st = 0; st < nstages; st++) {
-                const int s = st % S;
-                if (st >= S && !mbar_wait(&empty[s], ((st / S) - 1) & 1)) {
-                    report_error(p.err, KERR_EMPTY_WAIT);
-                    break;
-                }
-                mbar_arrive_expect_tx(&full[s], C::STAGE_BYTES);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int t0 = (tile / w_tiles) * TN;
+                for (int st = 0; st < nstages; st++, it++) {
+                    const uint32_t s = it % S;
+                    if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1)) {
+                        report_error(p.err, KERR_EMPTY_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&full[s], C::STAGE_BYTES);
 #pragma unroll
-                for (int u = 0; u < C::KSUB; u++)
-                    tma_load_2d(tiles + s * C::STAGE_BYTES + u * C::SUBTILE_BYTES, &tmap_x,
-                                st * C::STAGE_K + u * BK, t0, &full[s]);
+                    for (int u = 0; u < C::KSUB; u++)
+                        tma_load_2d(tiles + s * C::STAGE_BYTES + u * C::SUBTILE_BYTES, &tmap_x,
+                                    st * C::STAGE_K + u * BK, t0, &full[s]);
+                }
             }
         }
-    } else {
+    } else if (warp == DEQ_WARPS + 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             // Shared-memory descriptors differ only in their start-address field, so the loop adds to
@@ -483,29 +499,122 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
             const uint32_t desc_lo0 = (uint32_t)desc0;
             const uint32_t a_col0 = tmem_base + C::A_BASE_COL;
             bool ok = true;
-            for (int st = 0; st < nstages && ok; st++) {
-                const int s = st % S;
-                if (!mbar_wait(&full[s], (st / S) & 1)) {
-                    report_error(p.err, KERR_FULL_WAIT);
-                    ok = false;
+            uint32_t it = 0, tcount = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, tcount++) {
+                const uint32_t ab = tcount % AB;
+                // the epilogue must have read this accumulator out (tile tcount - AB) before it is overwritten
+                if (tcount >= (uint32_t)AB && !mbar_wait(&acc_empty[ab], ((tcount / AB) - 1) & 1)) {
+                    report_error(p.err, KERR_MMA_WAIT);
                     break;
                 }
                 tc_fence_after();
-                const uint32_t lo_s = desc_lo0 + (uint32_t)((s * C::STAGE_BYTES) >> 4);
-                const uint32_t a_s = a_col0 + (uint32_t)s * C::A_STAGE_COLS;
-#pragma unroll
-                for (int u = 0; u < C::KSUB; u++)
-#pragma unroll
-                    for (int kk = 0; kk < BK / UMMA_K; kk++) {
-                        // 16 K elements further: 8 TMEM columns of A, 32 bytes inside B's swizzled row
-                        const uint32_t lo = lo_s + (uint32_t)((u * C::SUBTILE_BYTES + kk * 32) >> 4);
-                        const uint64_t b_desc = ((uint64_t)desc_hi << 32) | lo;
-                        umma_f16_ts(tmem_base, a_s + (uint32_t)(u * 32 + kk * 8), b_desc, IDESC,
-                                    (st | u | kk) ? 1u : 0u);
+                const uint32_t d_tmem = tmem_base + ab * TN;
+                for (int st = 0; st < nstages; st++, it++) {
+                    const uint32_t s = it % S;
+                    if (!mbar_wait(&full[s], (it / S) & 1)) {
+                        report_error(p.err, KERR_FULL_WAIT);
+                        ok = false;
+                        break;
                     }
-                umma_commit(&empty[s]);            // stage free once these MMAs have read it
+                    tc_fence_after();
+                    const uint32_t lo_s = desc_lo0 + ((s * C::STAGE_BYTES) >> 4);
+                    const uint32_t a_s = a_col0 + s * C::A_STAGE_COLS;
+#pragma unroll
+                    for (int u = 0; u < C::KSUB; u++)
+#pragma unroll
+                        for (int kk = 0; kk < BK / UMMA_K; kk++) {
+                            // 16 K elements further: 8 TMEM columns of A, 32 bytes inside B's swizzled row
+                            const uint32_t lo = lo_s + (uint32_t)((u * C::SUBTILE_BYTES + kk * 32) >> 4);
+                            const uint64_t b_desc = ((uint64_t)desc_hi << 32) | lo;
+                            umma_f16_ts(d_tmem, a_s + (uint32_t)(u * 32 + kk * 8), b_desc, IDESC,
+                                        (st | u | kk) ? 1u : 0u);
+                        }
+                    umma_commit(&empty[s]);        // stage free once these MMAs have read it
+                }
+                if (ok) umma_commit(&acc_full[ab]);   // accumulator of this tile complete
             }
-            if (ok) umma_commit(acc_full);         // accumulator complete
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> shared staging -> global ----------------
+        // A thread owns one weight row (its TMEM lane) and sees that row's tokens, but the output is
+        // token-major: element (token, row) at token*N + row.  Each warp therefore transposes its
+        // 32 rows x 64 tokens through a private staging block in shared memory and writes 16-byte
+        // vectors (8 bf16 / 4 fp32 consecutive rows of one token); only __syncwarp is needed.
+        const int quarter = warp & 3;                           // TMEM lanes this warp may read
+        const int ew = warp - (DEQ_WARPS + 2);
+        const int esz = p.out_bf16 ? 2 : 4;                     // output element size
+        uint8_t *stg = epi_stage + (size_t)ew * (EPI_TOK * 32 * 4);       // [EPI_TOK tokens][32 rows]
+        float *scale_s = reinterpret_cast<float *>(epi_stage + EPI_WARPS * (EPI_TOK * 32 * 4)) + ew * TN_PAD;
+        const bool vec_ok = (p.N % (16 / esz)) == 0;            // 16-byte stores need N*esz % 16 == 0
+        uint32_t tcount = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, tcount++) {
+            const uint32_t ab = tcount % AB;
+            const int n0 = (tile % w_tiles) * TILE_ROWS, t0 = (tile / w_tiles) * TN;
+            // this tile's token factors (per warp copy, so no cross-warp barrier)
+            for (int c = lane; c < TN; c += 32) scale_s[c] = (t0 + c < p.M) ? __ldg(p.tok_scale + t0 + c) : 0.0f;
+            __syncwarp();
+            if (!mbar_wait(&acc_full[ab], (tcount / AB) & 1)) {
+                report_error(p.err, KERR_MMA_WAIT);
+                break;
+            }
+            tc_fence_after();
+            const int row0 = n0 + 32 * quarter;                 // first output row of this warp
+            const uint32_t acc = tmem_base + ab * TN + ((uint32_t)(32 * quarter) << 16);
+#pragma unroll 1
+            for (int g0 = 0; g0 < TN; g0 += EPI_TOK) {
+                constexpr int GT = TN < EPI_TOK ? TN : EPI_TOK;  // tokens in this group
+                // ---- TMEM -> registers (all loads of the group, one wait) -> scaled -> staging ----
+                uint32_t v[GT / 16][16];
+#pragma unroll
+                for (int c = 0; c < GT / 16; c++) tmem_ld16(acc + (uint32_t)(g0 + 16 * c), v[c]);
+                tmem_ld_wait();
+                if (g0 + GT >= TN) {                             // last read of this accumulator: hand it back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[ab]);
+                }
+#pragma unroll
+                for (int c = 0; c < GT / 16; c++) {
+#pragma unroll
+                    for (int j4 = 0; j4 < 4; j4++) {
+                        const float4 sc = *reinterpret_cast<const float4 *>(scale_s + g0 + 16 * c + 4 * j4);
+                        const float f[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const int tl = 16 * c + 4 * j4 + j;                  // token within the group
+                            const float val = __uint_as_float(v[c][4 * j4 + j]) * f[j];
+                            if (p.out_bf16) reinterpret_cast<__nv_bfloat16 *>(stg)[tl * 32 + lane] = __float2bfloat16_rn(val);
+                            else reinterpret_cast<float *>(stg)[tl * 32 + lane] = val;
+                        }
+                    }
+                }
+                __syncwarp();
+                // ---- staging -> global ----
+#ifdef LLMRS_DBG_NO_STORE
+                if (p.M < 0)
+#endif
+                if (vec_ok) {
+                    const int vec_per_tok = 32 * esz / 16;       // 4 (bf16) or 8 (fp32) vectors per token
+                    const int rows_per_vec = 16 / esz;
+                    for (int i = lane; i < GT * vec_per_tok; i += 32) {
+                        const int tl = i / vec_per_tok, vv = i % vec_per_tok;
+                        const int tok = t0 + g0 + tl, row = row0 + vv * rows_per_vec;
+                        if (tok < p.M && row < p.N) {
+                            const uint4 d = *reinterpret_cast<const uint4 *>(stg + (size_t)tl * 32 * esz + vv * 16);
+                            *reinterpret_cast<uint4 *>((uint8_t *)p.Out + ((size_t)tok * p.N + row) * esz) = d;
+                        }
+                    }
+                } else {
+                    for (int tl = 0; tl < GT; tl++) {
+                        const int tok = t0 + g0 + tl, row = row0 + lane;
+                        if (tok < p.M && row < p.N) {
+                            if (p.out_bf16) ((uint16_t *)p.Out)[(size_t)tok * p.N + row] = reinterpret_cast<const uint16_t *>(stg)[tl * 32 + lane];
+                            else ((float *)p.Out)[(size_t)tok * p.N + row] = reinterpret_cast<const float *>(stg)[tl * 32 + lane];
+                        }
+                    }
+                }
+                __syncwarp();                                    // staging is reused by the next group
+            }
         }
     }
 
@@ -612,7 +721,8 @@ cudaError_t launch_tn(const GemmParams &p, const void *x_f16, cudaStream_t s) {
     auto kern = gemm_kernel<QT, TN>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    dim3 grid((unsigned)((p.N + TILE_ROWS - 1) / TILE_ROWS), (unsigned)((p.M + TN - 1) / TN));
+    const int n_tiles = ((p.N + TILE_ROWS - 1) / TILE_ROWS) * ((p.M + TN - 1) / TN);
+    const int grid = n_tiles < p.sm_count ? n_tiles : p.sm_count;
     kern<<<grid, GEMM_THREADS, smem, s>>>(tmap, p);
     return cudaGetLastError();
 }
@@ -645,6 +755,10 @@ cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype
     GemmParams p{};
     p.W = w; p.Out = out; p.err = err_word; p.K = K; p.N = N; p.M = M; p.out_bf16 = out_dtype == DT_BF16;
     p.tok_scale = tok_scale;
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&p.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
     if (wdtype == DT_Q4K) {
         p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
         e = launch_qt<0>(p, x_f16, s);

@@ -21,10 +21,11 @@ constexpr int DT_F32 = 0, DT_Q4K = 12, DT_Q6K = 14, DT_BF16 = 30;
 //                           of block b (h = 0,1 half of the block, c = 0,1)
 //   [nbc * 16 B]            the int8 scales of block b at 16b
 //   [nbc * 2 B]             the f16 d of block b at 2b
-// Chunk ci of a row starts at byte 3360*ci of the row; rows are round_up(210*nb, 16) bytes apart.
+// Chunk ci of a row starts at byte 3360*ci of the row; rows are round_up(210*nb, 32) bytes apart,
+// so that the 96 bytes of a block half (slices (h,0) and (h,1)) are three aligned 32-byte sectors.
 inline size_t q6k_row_stride(int K) {
     size_t nb = (size_t)K / QK_K;
-    return (nb * Q6K_BLOCK_BYTES + 15) / 16 * 16;
+    return (nb * Q6K_BLOCK_BYTES + 31) / 32 * 32;
 }
 
 // Device bytes a [K, N] weight occupies in the layout the kernels read (+16 so a bulk copy of
