@@ -31,21 +31,25 @@ namespace llmrs {
 
 namespace {
 
-constexpr int CHUNK_BLOCKS = 16;                       // blocks of a row per pipeline stage
-constexpr int SLICES_PER_CHUNK = CHUNK_BLOCKS * 4;     // a slice is the 64 weights one lane handles
+// A pipeline stage holds CHUNK_BLOCKS = 16 consecutive blocks of each row of the tile; a slice is
+// the 64 weights one lane handles, four per block.  (8-block stages were measured: twice the
+// barrier rounds cost more than the deeper ring gains, 82 us against 59 us for Q4_K 4096x128256.)
 constexpr int MAX_STAGES = 8;
 constexpr int XBATCH = 8;                              // activation loads in flight per lane while staging
 
 // Activations become integers of 8*PLANES bits (two's complement, one byte plane each; the top
 // plane is signed).  |X| <= 2^XBITS keeps the integer dot product of a group inside int32.
-template <int PLANES> struct XFmt {
-    static constexpr int XBITS = PLANES == 3 ? 20 : 15;
-    static constexpr int XMAX = PLANES == 3 ? (1 << 20) : 32767;
+// (Q4_K takes its high nibbles in place, as 16*q <= 240, so its integers are two bits shorter:
+// 32 * 240 * 2^18 < 2^31.)
+template <int PLANES, int QT = 1> struct XFmt {
+    static constexpr int XBITS = PLANES == 3 ? (QT == 0 ? 18 : 20) : 15;
+    static constexpr int XMAX = PLANES == 3 ? (1 << XBITS) : 32767;
 };
 
 template <int QT, int PLANES> struct Fmt;
 template <int PLANES> struct Fmt<0, PLANES> {          // Q4_K, raw GGUF blocks
     static constexpr int BLOCK = Q4K_BLOCK_BYTES;
+    static constexpr int CHUNK_BLOCKS = 16;
     static constexpr int CHUNK_MAX = CHUNK_BLOCKS * Q4K_BLOCK_BYTES;   // 2304
     static constexpr int GROUP_BYTES = PLANES * 32;    // one sub-block: PLANES planes of 32 bytes
     static constexpr int META = 2 * GROUP_BYTES;       // float inv_lo, inv_hi, xsum_lo, xsum_hi
@@ -54,6 +58,7 @@ template <int PLANES> struct Fmt<0, PLANES> {          // Q4_K, raw GGUF blocks
 };
 template <int PLANES> struct Fmt<1, PLANES> {          // Q6_K, slice-major chunks (see kernels.h)
     static constexpr int BLOCK = Q6K_BLOCK_BYTES;
+    static constexpr int CHUNK_BLOCKS = 16;
     static constexpr int CHUNK_MAX = CHUNK_BLOCKS * Q6K_BLOCK_BYTES;   // 3360
     static constexpr int GROUP_BYTES = PLANES * 16;    // one scale group: PLANES planes of 16 bytes
     static constexpr int META = 4 * GROUP_BYTES;       // float inv[4], float xsum[4]
@@ -97,17 +102,17 @@ __device__ __forceinline__ float small_uint_to_float(uint32_t v) {
 
 // Power-of-two scale for a group whose largest magnitude is amax: returns e with
 // amax * 2^e < 2^X_BITS (clamped so that 2^e and 2^-e are normal floats).
-template <int PLANES>
+template <int PLANES, int QT>
 __device__ __forceinline__ int group_exponent(float amax) {
     const int eb = (int)((__float_as_uint(amax) >> 23) & 0xFFu);      // amax < 2^(eb-126)
-    int e = XFmt<PLANES>::XBITS + 126 - eb;
+    int e = XFmt<PLANES, QT>::XBITS + 126 - eb;
     return max(-126, min(126, e));
 }
 
 // One activation -> byte planes of its integer, written to plane l at planes[l*plane_stride + pos].
-template <int PLANES>
+template <int PLANES, int QT>
 __device__ __forceinline__ int quantise_store(float x, float scale, uint8_t *planes, int plane_stride, int pos) {
-    const int X = min(__float2int_rn(x * scale), XFmt<PLANES>::XMAX);
+    const int X = min(__float2int_rn(x * scale), XFmt<PLANES, QT>::XMAX);
 #pragma unroll
     for (int l = 0; l < PLANES; l++) planes[l * plane_stride + pos] = (uint8_t)((X >> (8 * l)) & 0xFF);
     return X;
@@ -144,9 +149,9 @@ __device__ void stage_activations(uint8_t *xarea, size_t xtok_bytes, const GemvP
                     float amax = fabsf(x);
 #pragma unroll
                     for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                    const int e = group_exponent<PLANES>(amax);
+                    const int e = group_exponent<PLANES, 0>(amax);
                     uint8_t *sl = xt + (size_t)(sb >> 1) * Fmt<0, PLANES>::XSTRIDE;
-                    int X = quantise_store<PLANES>(x, exp2i(e), sl + (sb & 1) * Fmt<0, PLANES>::GROUP_BYTES, 32, lane);
+                    int X = quantise_store<PLANES, 0>(x, exp2i(e), sl + (sb & 1) * Fmt<0, PLANES>::GROUP_BYTES, 32, lane);
 #pragma unroll
                     for (int o = 16; o; o >>= 1) X += __shfl_xor_sync(0xffffffffu, X, o);
                     if (lane == 0) {
@@ -179,9 +184,9 @@ __device__ void stage_activations(uint8_t *xarea, size_t xtok_bytes, const GemvP
                     float amax = fabsf(x);
 #pragma unroll
                     for (int o = 8; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                    const int e = group_exponent<PLANES>(amax);
+                    const int e = group_exponent<PLANES, 1>(amax);
                     uint8_t *sl = xt + (size_t)(4 * b + 2 * h + c) * Fmt<1, PLANES>::XSTRIDE;
-                    int X = quantise_store<PLANES>(x, exp2i(e), sl + g * Fmt<1, PLANES>::GROUP_BYTES, 16, i);
+                    int X = quantise_store<PLANES, 1>(x, exp2i(e), sl + g * Fmt<1, PLANES>::GROUP_BYTES, 16, i);
 #pragma unroll
                     for (int o = 8; o; o >>= 1) X += __shfl_xor_sync(0xffffffffu, X, o);
                     if (i == 0) {
@@ -206,8 +211,12 @@ template <int MT, int R, int PLANES>
 __device__ __forceinline__ void slice_q4k(const uint8_t *const (&row)[R], int sl, const uint8_t *xsl, size_t xtok_bytes,
                                           float (&total)[R][MT]) {
     const int b = sl >> 2, p = sl & 3;
-    const int sel = (p & 1) * 16;
+    // Lane constants for the 6-bit scale unpack (tests/ops.rs:29-39).  Pair p uses scale bytes
+    // (2p', 2p'+1), p' = p & 1, of the three scale words; pairs 2 and 3 use the split 4+2 bit form.
+    const uint32_t pick = (p & 1) ? 0x4432u : 0x4410u;          // byte_perm selector: bytes (2p', 2p'+1), zero above
     const bool upper = p >= 2;
+    const uint32_t mask_main = upper ? 0x0F0Fu : 0x3F3Fu;
+    const uint32_t mask_top = upper ? 0x3030u : 0u;
     uint32_t lo[R][8], hi[R][8];
     float s_lo[R], s_hi[R], m_lo[R], m_hi[R];
 #pragma unroll
@@ -220,20 +229,20 @@ __device__ __forceinline__ void slice_q4k(const uint8_t *const (&row)[R], int sl
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             lo[r][i] = w[i] & 0x0F0F0F0Fu;
-            hi[r][i] = (w[i] >> 4) & 0x0F0F0F0Fu;
+            hi[r][i] = w[i] & 0xF0F0F0F0u;        // 16*q, used in place; the 1/16 goes into the scale
         }
-        // 6-bit scales and mins of the two sub-blocks (tests/ops.rs:29-39)
         const float d = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu));
         const float dmin = f16_bits_to_f32((uint16_t)(hdr.x >> 16));
-        const uint32_t A = (hdr.y >> sel) & 0xFFFFu;
-        const uint32_t B = (hdr.z >> sel) & 0xFFFFu;
-        const uint32_t C = (hdr.w >> sel) & 0xFFFFu;
-        const uint32_t scp = upper ? ((C & 0x0F0Fu) | ((A >> 2) & 0x3030u)) : (A & 0x3F3Fu);
-        const uint32_t mnp = upper ? (((C >> 4) & 0x0F0Fu) | ((B >> 2) & 0x3030u)) : (B & 0x3F3Fu);
-        s_lo[r] = d * small_uint_to_float(scp & 0xFFu);
-        s_hi[r] = d * small_uint_to_float(scp >> 8);
-        m_lo[r] = dmin * small_uint_to_float(mnp & 0xFFu);
-        m_hi[r] = dmin * small_uint_to_float(mnp >> 8);
+        const uint32_t A = __byte_perm(hdr.y, 0, pick);          // scales[2p'], scales[2p'+1]
+        const uint32_t B = __byte_perm(hdr.z, 0, pick);          // scales[4+2p'], ...
+        const uint32_t C = __byte_perm(hdr.w, 0, pick);          // scales[8+2p'], ...
+        const uint32_t scp = ((upper ? C : A) & mask_main) | ((A >> 2) & mask_top);
+        const uint32_t mnp = ((upper ? (C >> 4) : B) & mask_main) | ((B >> 2) & mask_top);
+        // byte -> float through the mantissa of 2^23 (one byte permute each, no conversion)
+        s_lo[r] = d * (__uint_as_float(__byte_perm(scp, 0x4B000000u, 0x7440u)) - 8388608.0f);
+        s_hi[r] = d * 0.0625f * (__uint_as_float(__byte_perm(scp, 0x4B000000u, 0x7441u)) - 8388608.0f);
+        m_lo[r] = dmin * (__uint_as_float(__byte_perm(mnp, 0x4B000000u, 0x7440u)) - 8388608.0f);
+        m_hi[r] = dmin * (__uint_as_float(__byte_perm(mnp, 0x4B000000u, 0x7441u)) - 8388608.0f);
     }
 #pragma unroll
     for (int t = 0; t < MT; t++) {
@@ -262,7 +271,7 @@ __device__ __forceinline__ void slice_q4k(const uint8_t *const (&row)[R], int sl
                     if (PLANES == 3) s1 = dp4a_uu(q, pl[1][i], s1);
                     st = dp4a_us(q, pl[PLANES - 1][i], st);
                 }
-                // exact in int32: |S| <= 32*15*2^20
+                // exact in int32: |S| <= 32*240*2^18
                 const int S = PLANES == 3 ? (st * 256 + (int)s1) * 256 + (int)s0 : st * 256 + (int)s0;
                 val[r][hf] = (float)S * (hf ? meta.y : meta.x);
             }
@@ -388,7 +397,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                     report_error(p.err, KERR_EMPTY_WAIT);
                     return;
                 }
-                const int nbc = min(CHUNK_BLOCKS, nb - c * CHUNK_BLOCKS);
+                const int nbc = min(F::CHUNK_BLOCKS, nb - c * F::CHUNK_BLOCKS);
                 const uint32_t bytes = (uint32_t)((nbc * F::BLOCK + 15) / 16 * 16);
                 if (lane == 0) mbar_arrive_expect_tx(&full[s], bytes * RT);
                 __syncwarp();
@@ -420,12 +429,12 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                 report_error(p.err, KERR_FULL_WAIT);
                 return;
             }
-            const int nbc = min(CHUNK_BLOCKS, nb - c * CHUNK_BLOCKS);
+            const int nbc = min(F::CHUNK_BLOCKS, nb - c * F::CHUNK_BLOCKS);
             const uint8_t *row[R];
 #pragma unroll
             for (int r = 0; r < R; r++) row[r] = stages + s * stage_bytes + (size_t)(warp * R + r) * F::CHUNK_MAX;
             for (int sl = lane; sl < 4 * nbc; sl += 32) {
-                const uint8_t *xsl = xarea + (size_t)(c * SLICES_PER_CHUNK + sl) * F::XSTRIDE;
+                const uint8_t *xsl = xarea + (size_t)(c * F::CHUNK_BLOCKS * 4 + sl) * F::XSTRIDE;
                 if (QT == 0) slice_q4k<MT, R, PLANES>(row, sl, xsl, xtok_bytes, total);
                 else slice_q6k<MT, R, PLANES>(row, sl, nbc, xsl, xtok_bytes, total);
             }
@@ -476,7 +485,7 @@ cudaError_t launch_cfg(const GemvParams &p0, int sm_count, int want_stages, cuda
     constexpr int RT = R * NCW;
     static_assert(RT <= 32, "one producer lane per row of the tile");
     p.n_row_tiles = (p.N + RT - 1) / RT;
-    p.n_chunks = (p.K / QK_K + CHUNK_BLOCKS - 1) / CHUNK_BLOCKS;
+    p.n_chunks = (p.K / QK_K + Fmt<QT, PLANES>::CHUNK_BLOCKS - 1) / Fmt<QT, PLANES>::CHUNK_BLOCKS;
     p.stages = ring_stages<QT, MT, R, NCW, PLANES>(p.K, want_stages);
     if (p.stages < 2) return cudaErrorInvalidConfiguration;
     const size_t smem = smem_fixed<QT, MT, R, NCW, PLANES>(p.K) + (size_t)p.stages * RT * Fmt<QT, PLANES>::CHUNK_MAX;
