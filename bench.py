@@ -200,6 +200,22 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         obuf = be.wrap(local.data_ptr(), [n_local] if M == 1 else [n_local, M], DType.F32, keepalive=local)
         out_pinned = torch.empty(M, N_OUT, dtype=torch.float32).pin_memory()
 
+        # With more than one GPU and a decode batch the all-gather is fused into the kernel (peer stores
+        # over NVLink, llm_rs_b200/shard.py: FusedGatherMatmul); NCCL remains the fallback.
+        fused = None
+        exchange = "none"
+        if world > 1:
+            exchange = "NCCL all-gather of output slices"
+            if M <= 4 and not args.nccl:
+                try:
+                    from llm_rs_b200.shard import FusedGatherMatmul
+                    fused = [FusedGatherMatmul(be, wb, N_OUT, M) for wb in weights]
+                    full = None
+                    exchange = "all-gather fused into the kernel (peer stores over NVLink)"
+                except Exception as e:  # noqa: BLE001
+                    print(f"[bench] fused all-gather unavailable ({e!r}); using NCCL", file=sys.stderr)
+                    fused = None
+
         def gather():
             if world == 1:
                 return
@@ -209,15 +225,19 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 dist.all_gather_into_tensor(gathered.view(-1), local.reshape(-1))
                 full.view(M, world, -1).copy_(gathered.permute(1, 0, 2))
 
+        last = {"out": full}
+
         def step(i):
-            be.matmul(obuf, weights[i % copies], xbuf)
-            gather()
+            if fused is not None:
+                last["out"] = fused[i % copies](xbuf)
+            else:
+                be.matmul(obuf, weights[i % copies], xbuf)
+                gather()
 
         def step_e2e(i):
             be.write(xbuf, x_pinned.numpy())                       # H2D of this step's activations
-            be.matmul(obuf, weights[i % copies], xbuf)
-            gather()
-            out_pinned.copy_(full, non_blocking=True)              # D2H of the step's result
+            step(i)
+            out_pinned.copy_(last["out"], non_blocking=True)       # D2H of the step's result
             stream.synchronize()
 
         def barrier():
@@ -263,7 +283,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
         # correctness guard: a sample of rows against the CPU checker would import the oracle,
         # which only the cpu_baseline leg may do; here just make sure the output is live.
-        assert bool(torch.isfinite(full).all()) and float(full.abs().sum()) > 0.0
+        final = last["out"]
+        assert bool(torch.isfinite(final).all()) and float(final.abs().sum()) > 0.0
 
     alg = algorithmic_bytes(Q6K, K_IN, N_OUT, M)
     alg_local = algorithmic_bytes(Q6K, K_IN, n_local, M)
@@ -288,7 +309,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "vs_baseline": None, "dtype": "int32+f32",
         "data": "synthetic",
         "config": {"workload": f"configs[1]: Q6_K GEMV K={K_IN} N={N_OUT} M={M} (Llama-3-8B output projection)",
-                   "parallelism": f"N-split x{world}" + (" + NCCL all-gather of output slices" if world > 1 else ""),
+                   "parallelism": f"N-split x{world}" + (f" + {exchange}" if world > 1 else ""),
                    "rows_per_gpu": n_local,
                    "l2": (f"inputs larger than L2: the {shard_bytes / 1e6:.0f} MB weight shard is streamed every step "
                           f"(L2 is 126 MB)" if copies == 1 else
@@ -431,6 +452,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true",
                     help="skip the other parts of the metric (other GEMV shapes, prefill GEMM TFLOP/s, decode stack)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--nccl", action="store_true", help="N>1: use the NCCL all-gather instead of the fused one")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))

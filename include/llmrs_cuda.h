@@ -124,6 +124,23 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
 int llmrs_cuda_matmul_static_scratch(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight,
                                      const llmrs_buf *input);
 
+/* Multi-GPU decode matmul: this rank's rows of an N-sharded weight, with the all-gather of the
+ * output slices fused into the kernel.  The reference is single-GPU and has no counterpart; the
+ * sharding follows from every output row reading only its own weight row (shaders/ops.metal:249-289).
+ * Rank `rank` of `world` holds rows [rank*N_local, (rank+1)*N_local) (weight_shard, created by
+ * upload_tensor from those rows).  peer_out[d] is rank d's output buffer [M][n_total] of out_dtype
+ * and peer_flags[d] is slot `rank` of rank d's flag array (uint32 [world], zero before the first
+ * call), both as pointers this device can store through (peer-mapped / symmetric memory);
+ * my_flags is this rank's own flag array.  `step` must grow by one per call, on every rank alike.
+ * The kernel stores its slice into every rank's buffer with plain peer stores, publishes `step`,
+ * and returns only when all ranks' slices have arrived in its own buffer (bounded wait: a peer
+ * that never arrives yields LLMRS_ERR_KERNEL at the next sync).  M <= 4 (the decode kernel); all
+ * ranks must make the call for every step. */
+int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, const llmrs_buf *weight_shard, const llmrs_buf *input,
+                                uint32_t out_dtype, uint32_t n_total, uint32_t rank, uint32_t world,
+                                void *const *peer_out, uint32_t *const *peer_flags, uint32_t *my_flags,
+                                uint32_t step);
+
 /* Dequantises a Q4_K/Q6_K weight to float32 [N, K] in device memory `dev_out`
  * (N*K floats).  The reference has no such op; it exposes, for testing, the
  * values its kernels form in registers (tests/ops.rs:41-59, shaders/ops.metal:322-334). */

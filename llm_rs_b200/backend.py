@@ -84,6 +84,8 @@ ABI = {
     "llmrs_cuda_free": (C.c_int, [_VP, _BUFP]),
     "llmrs_cuda_matmul": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_matmul_static_scratch": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
+    "llmrs_cuda_matmul_allgather": (C.c_int, [_VP, _BUFP, _BUFP, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                              C.POINTER(_VP), C.POINTER(_VP), _VP, C.c_uint32]),
     "llmrs_cuda_dequantize": (C.c_int, [_VP, _BUFP, _VP]),
     "llmrs_cuda_write": (C.c_int, [_VP, _BUFP, _VP, C.c_size_t]),
     "llmrs_cuda_read_f32": (C.c_int, [_VP, _BUFP, C.POINTER(C.c_float), C.c_size_t]),
@@ -253,6 +255,19 @@ class CudaBackend:
         on the shared array."""
         self._check(self._lib.llmrs_cuda_matmul_static_scratch(self._ctx, C.byref(out._raw), C.byref(weight._raw),
                                                                C.byref(input._raw)))
+
+    def matmul_allgather(self, weight_shard: CudaBuffer, input: CudaBuffer, out_dtype: DType, n_total: int,
+                         rank: int, world: int, peer_out: Sequence[int], peer_flags: Sequence[int],
+                         my_flags: int, step: int) -> None:
+        """Decode matmul of this rank's weight rows with the all-gather fused into the kernel: the
+        slice is stored into every rank's [M, n_total] buffer (`peer_out`, device pointers this GPU
+        can store through) and the call's kernel finishes when all slices have arrived locally.
+        peer_flags[d] = address of slot `rank` in rank d's uint32 flag array; M <= 4."""
+        po = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_out])
+        pf = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_flags])
+        self._check(self._lib.llmrs_cuda_matmul_allgather(self._ctx, C.byref(weight_shard._raw), C.byref(input._raw),
+                                                          int(out_dtype), n_total, rank, world, po, pf,
+                                                          C.c_void_p(int(my_flags)), step & 0xFFFFFFFF))
 
     def launch_count(self) -> int:
         v = C.c_uint64()

@@ -35,7 +35,7 @@ struct llmrs_ctx {
     int gemv_max_m = 4;              // M <= this: exact decode kernel (1e-4 class); above: tensor-core GEMM (2e-3 class)
     void *scratch = nullptr;         // f16 copy of the activations for the tensor-core path
     size_t scratch_bytes = 0;
-    uint32_t *dev_error = nullptr;   // device word: first KernelError reported by a kernel
+    uint32_t *dev_error = nullptr;   // device word: first KernelError reported by a kernel; next word: CTA counter
     std::string error;
 
     int fail(int code, const char *fmt, ...) {
@@ -185,8 +185,8 @@ int llmrs_cuda_create(int device, void *stream, llmrs_ctx **out) {
     }
     e = cudaEventCreate(&ctx->ev_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_end);
-    if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->dev_error, sizeof(uint32_t));
-    if (e == cudaSuccess) e = cudaMemset(ctx->dev_error, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->dev_error, 2 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(ctx->dev_error, 0, 2 * sizeof(uint32_t));
     if (e != cudaSuccess) {
         g_create_error = cudaGetErrorString(e);
         llmrs_cuda_destroy(ctx);
@@ -398,6 +398,41 @@ int llmrs_cuda_matmul_static_scratch(llmrs_ctx *ctx, llmrs_buf *out, const llmrs
                                    out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, ctx->device, ctx->dev_error,
                                    ctx->stream, &ctx->launches);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_static_scratch: launch");
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, const llmrs_buf *weight_shard, const llmrs_buf *input,
+                                uint32_t out_dtype, uint32_t n_total, uint32_t rank, uint32_t world,
+                                void *const *peer_out, uint32_t *const *peer_flags, uint32_t *my_flags,
+                                uint32_t step) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!weight_shard || !input || !weight_shard->dptr || !input->dptr || !peer_out || !peer_flags || !my_flags)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul_allgather: null pointer");
+    const uint32_t K = weight_shard->dim0, N = weight_shard->dim1 ? weight_shard->dim1 : 1;
+    const uint32_t M = input->dim1 ? input->dim1 : 1;
+    if (weight_shard->dtype != LLMRS_Q4K && weight_shard->dtype != LLMRS_Q6K)
+        return ctx->fail(LLMRS_ERR_DTYPE, "matmul_allgather: weight dtype %u is not Q4_K/Q6_K", weight_shard->dtype);
+    if (!dense_elem_bytes(input->dtype) || !dense_elem_bytes(out_dtype))
+        return ctx->fail(LLMRS_ERR_DTYPE, "matmul_allgather: activations must be F32 or BF16");
+    if (world < 1 || world > 8 || rank >= world)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul_allgather: rank %u of %u (at most 8 ranks)", rank, world);
+    if (input->dim0 != K || K % QK_K || K > gemv_max_k())
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_allgather: input has %u features, weight expects %u", input->dim0, K);
+    if ((uint64_t)N * world != n_total)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_allgather: %u ranks x %u rows != %u rows", world, N, n_total);
+    if (M > 4)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_allgather: %u tokens; the fused kernel serves M <= 4 "
+                                          "(use matmul + a collective above that)", M);
+    for (uint32_t d = 0; d < world; d++)
+        if (!peer_out[d] || !peer_flags[d]) return ctx->fail(LLMRS_ERR_ARG, "matmul_allgather: null peer pointer");
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: event");
+    e = launch_gemv_allgather((int)weight_shard->dtype, (const uint8_t *)weight_shard->dptr, input->dptr,
+                              (int)input->dtype, (int)out_dtype, (int)K, (int)N, (int)M, (int)n_total, (int)rank,
+                              (int)world, peer_out, peer_flags, my_flags, ctx->dev_error + 1, step, ctx->sm_count,
+                              ctx->dev_error, ctx->stream, &ctx->launches);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: launch");
     return LLMRS_OK;
 }
 

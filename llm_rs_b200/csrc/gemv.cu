@@ -35,6 +35,7 @@ namespace {
 // the 64 weights one lane handles, four per block.  (8-block stages were measured: twice the
 // barrier rounds cost more than the deeper ring gains, 82 us against 59 us for Q4_K 4096x128256.)
 constexpr int MAX_STAGES = 8;
+constexpr uint32_t GATHER_WAIT_LIMIT = 1u << 25;       // polls (64 ns apart) before a peer is given up on
 constexpr int XBATCH = 8;                              // activation loads in flight per lane while staging
 
 // Activations become integers of 8*PLANES bits (two's complement, one byte plane each; the top
@@ -65,7 +66,25 @@ template <int PLANES> struct Fmt<1, PLANES> {          // Q6_K, slice-major chun
     static constexpr int XSTRIDE = META + 32 + 16;     // 240 / 176: odd number of 16-byte units
 };
 
+// Fused all-gather of the output slices of an N-sharded matmul (world == 0: not used).
+// Rank r owns rows [row_offset, row_offset + N) of an n_total-row output.  Every rank's kernel
+// stores its slice straight into every rank's output buffer through peer-mapped pointers
+// (plain stores over NVLink, no TMA, no multicast); the last CTA to finish publishes `step` in
+// slot `rank` of every rank's flag array and then waits, with a bound, until its own flag array
+// shows `step` from every rank.  When the kernel has completed on a rank, that rank's buffer
+// holds all slices, so stream order is all a consumer needs.
+constexpr int MAX_GATHER_RANKS = 8;
+struct GatherParams {
+    void *peer_out[MAX_GATHER_RANKS];         // output buffer [M][n_total] of each rank
+    uint32_t *peer_flag[MAX_GATHER_RANKS];    // slot `rank` of each rank's flag array
+    uint32_t *my_flags;                       // this rank's flag array [world]
+    uint32_t *done_counter;                   // local word: CTAs of this launch that have finished
+    int world, rank, n_total, row_offset;
+    uint32_t step;
+};
+
 struct GemvParams {
+    GatherParams g;
     const uint8_t *W;
     const void *X;
     void *Out;
@@ -416,7 +435,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
     named_barrier_sync(1, NCW * 32);
 
     uint32_t it = 0;
-    for (int rt = blockIdx.x; rt < p.n_row_tiles; rt += gridDim.x) {
+    bool ok = true;
+    for (int rt = blockIdx.x; rt < p.n_row_tiles && ok; rt += gridDim.x) {
         float total[R][MT];
 #pragma unroll
         for (int r = 0; r < R; r++)
@@ -427,7 +447,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
             const int s = it % S;
             if (!mbar_wait(&full[s], (it / S) & 1)) {
                 report_error(p.err, KERR_FULL_WAIT);
-                return;
+                ok = false;
+                break;
             }
             const int nbc = min(F::CHUNK_BLOCKS, nb - c * F::CHUNK_BLOCKS);
             const uint8_t *row[R];
@@ -450,9 +471,40 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
 #pragma unroll
                 for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
                 const int out_row = rt * RT + warp * R + r;
-                if (lane == 0 && out_row < p.N && t < p.m_valid)
-                    store_out(p.Out, (size_t)t * p.N + out_row, v, p.out_bf16);
+                if (ok && out_row < p.N && t < p.m_valid) {
+                    if (p.g.world == 0) {
+                        if (lane == 0) store_out(p.Out, (size_t)t * p.N + out_row, v, p.out_bf16);
+                    } else if (lane < p.g.world) {        // lane d stores into rank d's buffer
+                        store_out(p.g.peer_out[lane], (size_t)t * p.g.n_total + p.g.row_offset + out_row, v,
+                                  p.out_bf16);
+                    }
+                }
             }
+    }
+
+    if (p.g.world > 0) {
+        // ---- publish this rank's slice and wait for the others ----
+        __threadfence_system();                          // this thread's peer stores are visible system-wide
+        named_barrier_sync(1, NCW * 32);
+        if (threadIdx.x == 0) {
+            const uint32_t ticket = atomicAdd(p.g.done_counter, 1u);
+            if (ticket == gridDim.x - 1) {               // every CTA of this launch has stored and fenced
+                *p.g.done_counter = 0;                   // ready for the next launch
+                __threadfence_system();
+                for (int d = 0; d < p.g.world; d++)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.g.peer_flag[d]), "r"(p.g.step) : "memory");
+                for (int src = 0; src < p.g.world; src++) {
+                    bool seen = false;
+                    for (uint32_t i = 0; i < GATHER_WAIT_LIMIT && !seen; i++) {
+                        uint32_t f;
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(p.g.my_flags + src) : "memory");
+                        seen = (int32_t)(f - p.g.step) >= 0;
+                        if (!seen) __nanosleep(64);
+                    }
+                    if (!seen) report_error(p.err, KERR_GATHER_WAIT);
+                }
+            }
+        }
     }
 }
 
@@ -567,6 +619,41 @@ cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype
         return launch_fmt<1>(p, M, xe, oe, sm_count, s, launches);
     }
     return cudaErrorInvalidValue;
+}
+
+// N-sharded decode matmul with the all-gather of the output slices fused into the kernel (see
+// GatherParams).  One launch, so M <= 4 and the activations must fit the shared-memory staging.
+cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, int x_dtype, int out_dtype, int K,
+                                  int N_local, int M, int n_total, int rank, int world, void *const *peer_out,
+                                  uint32_t *const *peer_flags, uint32_t *my_flags, uint32_t *done_counter,
+                                  uint32_t step, int sm_count, uint32_t *err_word, cudaStream_t s,
+                                  uint64_t *launches) {
+    if (K <= 0 || N_local <= 0 || M <= 0 || M > 4 || world < 1 || world > MAX_GATHER_RANKS) return cudaErrorInvalidValue;
+    GemvParams p{};
+    p.W = w; p.X = x; p.Out = peer_out[rank]; p.err = err_word;
+    p.K = K; p.N = N_local;
+    p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;
+    p.g.world = world; p.g.rank = rank; p.g.n_total = n_total; p.g.row_offset = rank * N_local;
+    p.g.my_flags = my_flags; p.g.done_counter = done_counter; p.g.step = step;
+    for (int d = 0; d < world; d++) {
+        p.g.peer_out[d] = peer_out[d];
+        p.g.peer_flag[d] = peer_flags[d];
+    }
+    const int xe = x_dtype == DT_BF16 ? 2 : 4, oe = out_dtype == DT_BF16 ? 2 : 4;
+    uint64_t n = 0;
+    cudaError_t e;
+    if (wdtype == DT_Q4K) {
+        p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
+        e = launch_fmt<0>(p, M, xe, oe, sm_count, s, &n);
+    } else if (wdtype == DT_Q6K) {
+        p.row_stride = q6k_row_stride(K);
+        e = launch_fmt<1>(p, M, xe, oe, sm_count, s, &n);
+    } else {
+        return cudaErrorInvalidValue;
+    }
+    if (e == cudaSuccess && n != 1) e = cudaErrorInvalidConfiguration;   // token passes would each signal
+    if (launches) *launches += n;
+    return e;
 }
 
 #ifdef LLMRS_TUNING

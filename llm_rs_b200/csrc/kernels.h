@@ -49,6 +49,17 @@ cudaError_t launch_dequant(int wdtype, const uint8_t *w, int K, int N, float *ou
 cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                         int K, int N, int M, int sm_count, uint32_t *err_word, cudaStream_t s, uint64_t *launches);
 
+// The decode matmul of one rank's weight rows with the all-gather fused in: every rank's kernel
+// stores its [M, N_local] slice into all ranks' [M, n_total] buffers (peer-mapped pointers) and
+// returns once all slices have arrived in its own.  peer_out[d]: rank d's buffer; peer_flags[d]:
+// slot `rank` of rank d's flag array; my_flags: this rank's flag array [world]; step: a value
+// that grows by one per call on every rank.  M <= 4.
+cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, int x_dtype, int out_dtype, int K,
+                                  int N_local, int M, int n_total, int rank, int world, void *const *peer_out,
+                                  uint32_t *const *peer_flags, uint32_t *my_flags, uint32_t *done_counter,
+                                  uint32_t step, int sm_count, uint32_t *err_word, cudaStream_t s,
+                                  uint64_t *launches);
+
 // Largest in_features the decode kernel can stage in shared memory.
 size_t gemv_max_k();
 

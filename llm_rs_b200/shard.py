@@ -72,3 +72,47 @@ class ShardedMatmul:
         dist.all_gather_into_tensor(gathered.view(-1), local.reshape(-1), group=self.group)
         full.view(M, self.world, -1).copy_(gathered.permute(1, 0, 2))
         return full
+
+
+class FusedGatherMatmul:
+    """Decode matmul (M <= 4) of an N-sharded weight whose all-gather runs inside the kernel.
+
+    Output buffers and flag arrays live in symmetric memory (torch.distributed._symmetric_memory),
+    so every rank can hand the kernel device pointers to every other rank's buffer.  The kernel
+    (llmrs_cuda_matmul_allgather) stores its slice into all buffers over NVLink with plain stores,
+    publishes a step number in the peers' flag arrays and returns when all slices have arrived in
+    its own buffer.  No NCCL call per step.  `out` is this rank's [M, N] tensor, complete once the
+    call's kernel has finished (stream order).
+    """
+
+    def __init__(self, backend, weight_shard, N: int, M: int, out_dtype=torch.float32,
+                 group: dist.ProcessGroup | None = None):
+        import torch.distributed._symmetric_memory as symm
+        from .backend import DType
+        if M > 4:
+            raise ValueError("the fused all-gather serves the decode kernel only (M <= 4)")
+        self.be, self.w = backend, weight_shard
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.N, self.M = N, M
+        row_range(N, self.rank, self.world)                       # checks divisibility
+        dev = torch.device("cuda", backend.device)
+        self.out = symm.empty((M, N), dtype=out_dtype, device=dev)
+        self.flags = symm.empty((self.world,), dtype=torch.int32, device=dev)
+        self.out.zero_()
+        self.flags.zero_()
+        torch.cuda.synchronize(dev)
+        oh = symm.rendezvous(self.out, self.group)
+        fh = symm.rendezvous(self.flags, self.group)
+        self.peer_out = [int(p) for p in oh.buffer_ptrs]
+        self.peer_flags = [int(p) + 4 * self.rank for p in fh.buffer_ptrs]   # my slot in everyone's array
+        self.my_flags = int(fh.buffer_ptrs[self.rank])
+        self.out_dtype = DType.F32 if out_dtype == torch.float32 else DType.BF16
+        self.step = 0
+        dist.barrier(self.group)                                   # all flag arrays are zeroed before any step
+
+    def __call__(self, input_buf) -> torch.Tensor:
+        self.step += 1
+        self.be.matmul_allgather(self.w, input_buf, self.out_dtype, self.N, self.rank, self.world,
+                                 self.peer_out, self.peer_flags, self.my_flags, self.step)
+        return self.out
