@@ -35,6 +35,8 @@ struct llmrs_ctx {
     int gemv_max_m = 4;              // M <= this: exact decode kernel (1e-4 class); above: tensor-core GEMM (2e-3 class)
     void *scratch = nullptr;         // f16 copy of the activations for the tensor-core path
     size_t scratch_bytes = 0;
+    int gemm_split = -1;             // LLMRS_GEMM_SPLIT at creation: 0 never, 1 always, otherwise the estimate decides
+    void *split_ws = nullptr;        // workspace of the tensor-core path's split of the last wave (zero between launches)
     uint32_t *dev_error = nullptr;   // device word: first KernelError reported by a kernel; next word: CTA counter
     std::string error;
 
@@ -56,7 +58,8 @@ struct llmrs_ctx {
         cudaError_t e = cudaMemcpy(&code, dev_error, sizeof code, cudaMemcpyDeviceToHost);
         if (e != cudaSuccess) return cuda_fail(e, what);
         if (code == 0) return LLMRS_OK;
-        cudaMemset(dev_error, 0, sizeof code);
+        cudaMemset(dev_error, 0, 2 * sizeof code);
+        if (split_ws) cudaMemset(split_ws, 0, gemm_split_counter_bytes());     // an abandoned launch may have left counters behind
         return fail(LLMRS_ERR_KERNEL, "%s: a kernel gave up a bounded wait (code %u); results are incomplete", what, code);
     }
     // Grows the scratch buffer (synchronises; never called while the stream is being captured).
@@ -183,10 +186,13 @@ int llmrs_cuda_create(int device, void *stream, llmrs_ctx **out) {
         int v = atoi(env);
         if (v >= 0) ctx->gemv_max_m = v;
     }
+    if (const char *env = getenv("LLMRS_GEMM_SPLIT")) ctx->gemm_split = atoi(env) ? 1 : 0;
     e = cudaEventCreate(&ctx->ev_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_end);
     if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->dev_error, 2 * sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->dev_error, 0, 2 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->split_ws, gemm_split_workspace_bytes(ctx->sm_count));
+    if (e == cudaSuccess) e = cudaMemset(ctx->split_ws, 0, gemm_split_counter_bytes());
     if (e != cudaSuccess) {
         g_create_error = cudaGetErrorString(e);
         llmrs_cuda_destroy(ctx);
@@ -205,6 +211,7 @@ int llmrs_cuda_destroy(llmrs_ctx *ctx) {
     if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     if (ctx->dev_error) cudaFree(ctx->dev_error);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->split_ws) cudaFree(ctx->split_ws);
     delete ctx;
     return LLMRS_OK;
 }
@@ -354,7 +361,8 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
         e = ctx->reserve_scratch(gemm_scratch_bytes((int)K, (int)M));
         if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: scratch (grow it with one call outside graph capture)");
         e = launch_gemm((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
-                        (int)out->dtype, (int)K, (int)N, (int)M, ctx->scratch, ctx->dev_error, ctx->stream,
+                        (int)out->dtype, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->dev_error,
+                        ctx->stream,
                         &ctx->launches);
     }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: launch");

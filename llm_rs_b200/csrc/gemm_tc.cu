@@ -63,6 +63,73 @@ struct GemmParams {
     int sm_count;
     size_t row_stride;
     const float *tok_scale;   // per token: factor that undoes the power-of-two scaling of its f16 activations
+    // Split of the last, partial wave of tiles along K (kernel: 0 = off; host: -1 = estimate decides), see Sched below.
+    int split;
+    uint32_t *ws_counters;    // [2 * sm_count] zero between launches: arrivals / deposits per tail tile
+    float *ws_slots;          // [2 * sm_count] partial tiles of TILE_ROWS x TN floats, token-major
+};
+
+// ---- work schedule -----------------------------------------------------------------------------
+// A unit is a tile (128 weight rows x TN tokens) and a range of its 256-weight K blocks.  Without
+// the split, CTA c owns the whole tiles c, c + G, ...  (G = grid size).  With it, every CTA owns
+// n_tiles / G whole tiles, and the K blocks of the remaining R = n_tiles % G tiles -- the wave
+// that would leave most SMs idle -- form one sequence of T = R * nb blocks that is cut into G
+// equal contiguous ranges ("stream-K").  A range that covers only part of a tile yields a partial
+// accumulator: every CTA but the last to arrive deposits its partial in a workspace slot, the
+// last one adds the deposits to its own accumulator and writes the output.  The last arriver
+// waits only for CTAs that have already taken a ticket, i.e. are running their epilogue, so the
+// wait can not deadlock whatever else shares the GPU; it is bounded all the same.
+struct Sched {
+    int nb, w_tiles, n_tiles;
+    int full_per_cta, n_full;       // whole tiles of this CTA; tiles [0, n_full) are done whole
+    int T, gt;                      // tail: T blocks over the first gt CTAs
+    int tail_a, tail_b;             // this CTA's range of tail blocks
+};
+struct Unit {
+    int tile, b0, b1;
+};
+__device__ __forceinline__ int tail_start(const Sched &sc, int c) {      // first tail block of CTA c (c <= gt)
+    return (int)(((unsigned)sc.T * (unsigned)c) / (unsigned)sc.gt);
+}
+__device__ __forceinline__ Sched make_sched(const GemmParams &p, int TN) {
+    Sched sc;
+    const int G = gridDim.x, c = blockIdx.x;
+    sc.nb = p.K / QK_K;
+    sc.w_tiles = (p.N + TILE_ROWS - 1) / TILE_ROWS;
+    sc.n_tiles = sc.w_tiles * ((p.M + TN - 1) / TN);
+    if (!p.split) {
+        sc.n_full = sc.n_tiles;
+        sc.full_per_cta = c < sc.n_tiles ? (sc.n_tiles - c + G - 1) / G : 0;
+        sc.T = 0; sc.gt = 1; sc.tail_a = sc.tail_b = 0;
+    } else {
+        sc.full_per_cta = sc.n_tiles / G;
+        sc.n_full = sc.full_per_cta * G;
+        sc.T = (sc.n_tiles - sc.n_full) * sc.nb;
+        sc.gt = max(1, min(G, sc.T));
+        sc.tail_a = c < sc.gt ? tail_start(sc, c) : 0;
+        sc.tail_b = c < sc.gt ? tail_start(sc, c + 1) : 0;
+    }
+    return sc;
+}
+struct UnitIter {
+    int i = 0, pos = -1;
+    __device__ __forceinline__ bool next(const Sched &sc, Unit &u) {
+        if (i < sc.full_per_cta) {
+            u.tile = blockIdx.x + i * gridDim.x;
+            u.b0 = 0;
+            u.b1 = sc.nb;
+            i++;
+            return true;
+        }
+        if (pos < 0) pos = sc.tail_a;
+        if (pos >= sc.tail_b) return false;
+        const int t = pos / sc.nb;
+        u.tile = sc.n_full + t;
+        u.b0 = pos - t * sc.nb;
+        u.b1 = min(sc.nb, u.b0 + (sc.tail_b - pos));
+        pos += u.b1 - u.b0;
+        return true;
+    }
 };
 
 // ---- tcgen05 / TMA wrappers ------------------------------------------------------------------
@@ -405,9 +472,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     uint8_t *epi_stage = tiles + S * C::STAGE_BYTES + 256;       // 256 bytes of barriers in front, 16-byte aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nstages = p.K / C::STAGE_K;           // K is a multiple of 256
-    const int w_tiles = (p.N + TILE_ROWS - 1) / TILE_ROWS;
-    const int n_tiles = w_tiles * ((p.M + TN - 1) / TN);
+    const Sched sc = make_sched(p, TN);
+    const int w_tiles = sc.w_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
@@ -436,16 +502,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
         // TMEM address of this warp's lane quarter, first weight column
         const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + C::A_BASE_COL;
         bool ok = true;
-        uint32_t tile_it = 0;                       // stages of the tiles before this one
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, tile_it += (uint32_t)nstages) {
-            const int n0 = (tile % w_tiles) * TILE_ROWS;
+        uint32_t unit_it = 0;                       // stages of the units before this one
+        UnitIter ui;
+        Unit u;
+        typename RawOf<QT>::type cur;
+        bool have_cur = false;                      // `cur` already holds this unit's first block
+        while (ok && ui.next(sc, u)) {
+            const int n0 = (u.tile % w_tiles) * TILE_ROWS;
             const int row = min(n0 + r, p.N - 1);
             const uint8_t *row_ptr = p.W + (size_t)row * p.row_stride;
-            typename RawOf<QT>::type cur = load_raw<QT>(row_ptr, nb, 0, g);
-            for (int b = 0; b < nb; b++) {
+            if (!have_cur) cur = load_raw<QT>(row_ptr, nb, u.b0, g);
+            // the next unit's row, so that the register prefetch runs across the unit boundary
+            UnitIter peek = ui;
+            Unit un = u;
+            const bool has_next = peek.next(sc, un);
+            const uint8_t *next_row_ptr =
+                p.W + (size_t)min((un.tile % w_tiles) * TILE_ROWS + r, p.N - 1) * p.row_stride;
+            // (prefetch.global.L2 of the blocks further ahead was measured: 5-10 % slower on every
+            // shape -- each of these row-per-lane accesses costs 32 L1 wavefronts, prefetch or not)
+            for (int b = u.b0; b < u.b1; b++) {
                 typename RawOf<QT>::type nxt = cur;
-                if (b + 1 < nb) nxt = load_raw<QT>(row_ptr, nb, b + 1, g);     // in flight during this block
-                const uint32_t it = tile_it + 2u * (uint32_t)b + (uint32_t)g;   // stage number over all tiles
+                if (b + 1 < u.b1) nxt = load_raw<QT>(row_ptr, nb, b + 1, g);   // in flight during this block
+                else if (has_next) nxt = load_raw<QT>(next_row_ptr, nb, un.b0, g);
+                const uint32_t it = unit_it + 2u * (uint32_t)(b - u.b0) + (uint32_t)g;   // stage number over all units
                 const uint32_t s = it % S;
                 if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1)) {
                     report_error(p.err, KERR_EMPTY_WAIT);
@@ -466,15 +545,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                 if (lane == 0) mbar_arrive(&full[s]);
                 cur = nxt;
             }
+            unit_it += 2u * (uint32_t)(u.b1 - u.b0);
+            have_cur = has_next;
         }
     } else if (warp == DEQ_WARPS) {
         // ---------------- TMA producer of the activation tiles ----------------
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const int t0 = (tile / w_tiles) * TN;
-                for (int st = 0; st < nstages; st++, it++) {
+            UnitIter ui;
+            Unit u;
+            while (ok && ui.next(sc, u)) {
+                const int t0 = (u.tile / w_tiles) * TN;
+                for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
                     const uint32_t s = it % S;
                     if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1)) {
                         report_error(p.err, KERR_EMPTY_WAIT);
@@ -483,9 +566,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                     }
                     mbar_arrive_expect_tx(&full[s], C::STAGE_BYTES);
 #pragma unroll
-                    for (int u = 0; u < C::KSUB; u++)
-                        tma_load_2d(tiles + s * C::STAGE_BYTES + u * C::SUBTILE_BYTES, &tmap_x,
-                                    st * C::STAGE_K + u * BK, t0, &full[s]);
+                    for (int us = 0; us < C::KSUB; us++)
+                        tma_load_2d(tiles + s * C::STAGE_BYTES + us * C::SUBTILE_BYTES, &tmap_x,
+                                    st * C::STAGE_K + us * BK, t0, &full[s]);
                 }
             }
         }
@@ -500,16 +583,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
             const uint32_t a_col0 = tmem_base + C::A_BASE_COL;
             bool ok = true;
             uint32_t it = 0, tcount = 0;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, tcount++) {
+            UnitIter ui;
+            Unit u;
+            for (; ok && ui.next(sc, u); tcount++) {
                 const uint32_t ab = tcount % AB;
-                // the epilogue must have read this accumulator out (tile tcount - AB) before it is overwritten
+                // the epilogue must have read this accumulator out (unit tcount - AB) before it is overwritten
                 if (tcount >= (uint32_t)AB && !mbar_wait(&acc_empty[ab], ((tcount / AB) - 1) & 1)) {
                     report_error(p.err, KERR_MMA_WAIT);
                     break;
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ab * TN;
-                for (int st = 0; st < nstages; st++, it++) {
+                for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
                     const uint32_t s = it % S;
                     if (!mbar_wait(&full[s], (it / S) & 1)) {
                         report_error(p.err, KERR_FULL_WAIT);
@@ -520,48 +605,101 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                     const uint32_t lo_s = desc_lo0 + ((s * C::STAGE_BYTES) >> 4);
                     const uint32_t a_s = a_col0 + s * C::A_STAGE_COLS;
 #pragma unroll
-                    for (int u = 0; u < C::KSUB; u++)
+                    for (int us = 0; us < C::KSUB; us++)
 #pragma unroll
                         for (int kk = 0; kk < BK / UMMA_K; kk++) {
                             // 16 K elements further: 8 TMEM columns of A, 32 bytes inside B's swizzled row
-                            const uint32_t lo = lo_s + (uint32_t)((u * C::SUBTILE_BYTES + kk * 32) >> 4);
+                            const uint32_t lo = lo_s + (uint32_t)((us * C::SUBTILE_BYTES + kk * 32) >> 4);
                             const uint64_t b_desc = ((uint64_t)desc_hi << 32) | lo;
-                            umma_f16_ts(d_tmem, a_s + (uint32_t)(u * 32 + kk * 8), b_desc, IDESC,
-                                        (st | u | kk) ? 1u : 0u);
+                            umma_f16_ts(d_tmem, a_s + (uint32_t)(us * 32 + kk * 8), b_desc, IDESC,
+                                        ((st - 2 * u.b0) | us | kk) ? 1u : 0u);
                         }
                     umma_commit(&empty[s]);        // stage free once these MMAs have read it
                 }
-                if (ok) umma_commit(&acc_full[ab]);   // accumulator of this tile complete
+                if (ok) umma_commit(&acc_full[ab]);   // accumulator of this unit complete
             }
         }
     } else {
         // ---------------- epilogue: TMEM -> registers -> shared staging -> global ----------------
         // A thread owns one weight row (its TMEM lane) and sees that row's tokens, but the output is
         // token-major: element (token, row) at token*N + row.  Each warp therefore transposes its
-        // 32 rows x 64 tokens through a private staging block in shared memory and writes 16-byte
-        // vectors (8 bf16 / 4 fp32 consecutive rows of one token); only __syncwarp is needed.
+        // 32 rows x 16 tokens at a time through a private staging block in shared memory and writes
+        // 16-byte vectors (8 bf16 / 4 fp32 consecutive rows of one token); only __syncwarp is needed.
+        // A partial unit (split of the last wave) either deposits its raw fp32 accumulator in a
+        // workspace slot, laid out like a tile-sized output, or adds the others' deposits to its own.
         const int quarter = warp & 3;                           // TMEM lanes this warp may read
         const int ew = warp - (DEQ_WARPS + 2);
-        const int esz = p.out_bf16 ? 2 : 4;                     // output element size
         uint8_t *stg = epi_stage + (size_t)ew * (EPI_TOK * 32 * 4);       // [EPI_TOK tokens][32 rows]
         float *scale_s = reinterpret_cast<float *>(epi_stage + EPI_WARPS * (EPI_TOK * 32 * 4)) + ew * TN_PAD;
-        const bool vec_ok = (p.N % (16 / esz)) == 0;            // 16-byte stores need N*esz % 16 == 0
+        uint32_t *ticket_s = tmem_slot + 2;
+        constexpr int EPI_THREADS = EPI_WARPS * 32;
         uint32_t tcount = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, tcount++) {
+        bool dead = false;                                      // a wait gave up: no more memory traffic, barriers only
+        UnitIter ui;
+        Unit u;
+        for (; !dead && ui.next(sc, u); tcount++) {
             const uint32_t ab = tcount % AB;
-            const int n0 = (tile % w_tiles) * TILE_ROWS, t0 = (tile / w_tiles) * TN;
+            const int n0 = (u.tile % w_tiles) * TILE_ROWS, t0 = (u.tile / w_tiles) * TN;
+            const bool partial = u.b1 - u.b0 < sc.nb;
             // this tile's token factors (per warp copy, so no cross-warp barrier)
             for (int c = lane; c < TN; c += 32) scale_s[c] = (t0 + c < p.M) ? __ldg(p.tok_scale + t0 + c) : 0.0f;
             __syncwarp();
             if (!mbar_wait(&acc_full[ab], (tcount / AB) & 1)) {
                 report_error(p.err, KERR_MMA_WAIT);
-                break;
+                dead = true;
             }
             tc_fence_after();
-            const int row0 = n0 + 32 * quarter;                 // first output row of this warp
+
+            // ---- partial unit: who else works on this tile, and is this CTA the last to arrive? ----
+            bool deposit = false, combine = false;
+            int c_first = 0, c_last = -1, tt = 0, tb = 0;
+            if (partial) {
+                tt = u.tile - sc.n_full;
+                tb = tt * sc.nb;
+                const int te = tb + sc.nb;
+                // c_first: the CTA whose range holds block tb; c_last: the one that holds block te - 1
+                int c = min(sc.gt - 1, (int)(((unsigned)tb * (unsigned)sc.gt) / (unsigned)sc.T));
+                while (c + 1 < sc.gt && tail_start(sc, c + 1) <= tb) c++;
+                while (c > 0 && tail_start(sc, c) > tb) c--;
+                c_first = c;
+                while (c + 1 < sc.gt && tail_start(sc, c + 1) < te) c++;
+                c_last = c;
+                const uint32_t pieces = (uint32_t)(c_last - c_first + 1);
+                if (ew == 0 && lane == 0) *ticket_s = atomicAdd(p.ws_counters + 2 * tt, 1u);
+                named_barrier_sync(2, EPI_THREADS);
+                deposit = *ticket_s + 1 < pieces;
+                combine = !deposit;
+                if (combine) {
+                    if (ew == 0 && lane == 0) {                  // every other piece has a ticket: wait for their deposits
+                        bool seen = false;
+                        for (uint32_t i = 0; i < WAIT_LIMIT && !seen; i++) {
+                            uint32_t n;
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(n) : "l"(p.ws_counters + 2 * tt + 1) : "memory");
+                            seen = n + 1 >= pieces;
+                            if (!seen) __nanosleep(32);
+                        }
+                        if (!seen) report_error(p.err, KERR_SPLIT_WAIT);
+                    }
+                    named_barrier_sync(2, EPI_THREADS);
+                }
+            }
+
+            // ---- where this unit's values go ----
+            const bool o_bf16 = deposit ? false : (p.out_bf16 != 0);
+            const int esz = o_bf16 ? 2 : 4;
+            uint8_t *o_ptr = (uint8_t *)p.Out;
+            size_t o_stride = (size_t)p.N;                      // elements between tokens
+            int tok_base = t0, row_base = n0 + 32 * quarter, tok_lim = p.M, row_lim = p.N;
+            if (deposit) {
+                const int k = sc.tail_a >= tb ? 0 : 1;          // first or last piece of this CTA's range
+                o_ptr = (uint8_t *)(p.ws_slots + (size_t)(2 * blockIdx.x + k) * (TILE_ROWS * TN));
+                o_stride = TILE_ROWS;
+                tok_base = 0; row_base = 32 * quarter; tok_lim = TN; row_lim = TILE_ROWS;
+            }
+            const bool vec_ok = (o_stride % (size_t)(16 / esz)) == 0;     // 16-byte stores need whole vectors per token
             const uint32_t acc = tmem_base + ab * TN + ((uint32_t)(32 * quarter) << 16);
 #pragma unroll 1
-            for (int g0 = 0; g0 < TN; g0 += EPI_TOK) {
+            for (int g0 = 0; g0 < TN && !dead; g0 += EPI_TOK) {
                 constexpr int GT = TN < EPI_TOK ? TN : EPI_TOK;  // tokens in this group
                 // ---- TMEM -> registers (all loads of the group, one wait) -> scaled -> staging ----
                 uint32_t v[GT / 16][16];
@@ -573,47 +711,72 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[ab]);
                 }
+                if (combine) {
+                    for (int c = c_first; c <= c_last; c++) {
+                        if (c == (int)blockIdx.x) continue;
+                        const int k = tail_start(sc, c) >= tb ? 0 : 1;
+                        const float *sl = p.ws_slots + (size_t)(2 * c + k) * (TILE_ROWS * TN) + (size_t)g0 * TILE_ROWS +
+                                          32 * quarter + lane;
+                        float add[GT];
+#pragma unroll
+                        for (int j = 0; j < GT; j++) add[j] = __ldcg(sl + j * TILE_ROWS);
+#pragma unroll
+                        for (int j = 0; j < GT; j++)
+                            v[j / 16][j % 16] = __float_as_uint(__uint_as_float(v[j / 16][j % 16]) + add[j]);
+                    }
+                }
 #pragma unroll
                 for (int c = 0; c < GT / 16; c++) {
 #pragma unroll
                     for (int j4 = 0; j4 < 4; j4++) {
-                        const float4 sc = *reinterpret_cast<const float4 *>(scale_s + g0 + 16 * c + 4 * j4);
-                        const float f[4] = {sc.x, sc.y, sc.z, sc.w};
+                        const float4 sc4 = *reinterpret_cast<const float4 *>(scale_s + g0 + 16 * c + 4 * j4);
+                        const float f[4] = {sc4.x, sc4.y, sc4.z, sc4.w};
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
                             const int tl = 16 * c + 4 * j4 + j;                  // token within the group
-                            const float val = __uint_as_float(v[c][4 * j4 + j]) * f[j];
-                            if (p.out_bf16) reinterpret_cast<__nv_bfloat16 *>(stg)[tl * 32 + lane] = __float2bfloat16_rn(val);
+                            const float raw = __uint_as_float(v[c][4 * j4 + j]);
+                            const float val = deposit ? raw : raw * f[j];
+                            if (o_bf16) reinterpret_cast<__nv_bfloat16 *>(stg)[tl * 32 + lane] = __float2bfloat16_rn(val);
                             else reinterpret_cast<float *>(stg)[tl * 32 + lane] = val;
                         }
                     }
                 }
                 __syncwarp();
                 // ---- staging -> global ----
-#ifdef LLMRS_DBG_NO_STORE
-                if (p.M < 0)
-#endif
                 if (vec_ok) {
                     const int vec_per_tok = 32 * esz / 16;       // 4 (bf16) or 8 (fp32) vectors per token
                     const int rows_per_vec = 16 / esz;
                     for (int i = lane; i < GT * vec_per_tok; i += 32) {
                         const int tl = i / vec_per_tok, vv = i % vec_per_tok;
-                        const int tok = t0 + g0 + tl, row = row0 + vv * rows_per_vec;
-                        if (tok < p.M && row < p.N) {
+                        const int tok = tok_base + g0 + tl, row = row_base + vv * rows_per_vec;
+                        if (tok < tok_lim && row < row_lim) {
                             const uint4 d = *reinterpret_cast<const uint4 *>(stg + (size_t)tl * 32 * esz + vv * 16);
-                            *reinterpret_cast<uint4 *>((uint8_t *)p.Out + ((size_t)tok * p.N + row) * esz) = d;
+                            *reinterpret_cast<uint4 *>(o_ptr + ((size_t)tok * o_stride + row) * esz) = d;
                         }
                     }
                 } else {
                     for (int tl = 0; tl < GT; tl++) {
-                        const int tok = t0 + g0 + tl, row = row0 + lane;
-                        if (tok < p.M && row < p.N) {
-                            if (p.out_bf16) ((uint16_t *)p.Out)[(size_t)tok * p.N + row] = reinterpret_cast<const uint16_t *>(stg)[tl * 32 + lane];
-                            else ((float *)p.Out)[(size_t)tok * p.N + row] = reinterpret_cast<const float *>(stg)[tl * 32 + lane];
+                        const int tok = tok_base + g0 + tl, row = row_base + lane;
+                        if (tok < tok_lim && row < row_lim) {
+                            if (o_bf16) ((uint16_t *)o_ptr)[(size_t)tok * o_stride + row] = reinterpret_cast<const uint16_t *>(stg)[tl * 32 + lane];
+                            else ((float *)o_ptr)[(size_t)tok * o_stride + row] = reinterpret_cast<const float *>(stg)[tl * 32 + lane];
                         }
                     }
                 }
                 __syncwarp();                                    // staging is reused by the next group
+            }
+            if (partial) {
+                if (deposit) {
+                    __threadfence();                             // this thread's deposit is visible device-wide
+                    named_barrier_sync(2, EPI_THREADS);
+                    if (ew == 0 && lane == 0) atomicAdd(p.ws_counters + 2 * tt + 1, 1u);
+                } else {
+                    named_barrier_sync(2, EPI_THREADS);          // all deposits have been read
+                    if (ew == 0 && lane == 0) {                  // leave the counters at zero for the next launch
+                        p.ws_counters[2 * tt] = 0;
+                        p.ws_counters[2 * tt + 1] = 0;
+                    }
+                }
             }
         }
     }
@@ -704,6 +867,20 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// Does cutting the last, partial wave of tiles along K pay?  The exchange is not free: a deposit
+// is a tile-sized fp32 store, and the last arriver reads every deposit back group by group, one
+// L2 round trip each.  Measured on a B200 (split / no split): K=14336, N=4096 (32 tiles) 0.52 at
+// 16 tokens, 0.61 at 64, 0.80 at 128; K=4096 shapes 0.92 .. 1.46; 256-token tiles 1.0 .. 1.8.  So
+// the split is used where at least half of the SMs would otherwise idle through a long K loop
+// and the tiles (hence the deposits) are small.
+// `forced` = 0 / 1 overrides the rule (measurements and tests), -1 leaves it alone.
+bool split_pays(int n_tiles, int nb, int TN, int sms, int forced) {
+    const int rest = n_tiles % sms;
+    if (rest == 0 || nb < 2) return false;
+    if (forced >= 0) return forced != 0;
+    return n_tiles <= sms / 2 && nb >= 32 && TN <= 128;
+}
+
 template <int QT, int TN>
 cudaError_t launch_tn(const GemmParams &p, const void *x_f16, cudaStream_t s) {
     EncodeTiledFn enc = encode_tiled_fn();
@@ -722,8 +899,15 @@ cudaError_t launch_tn(const GemmParams &p, const void *x_f16, cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = ((p.N + TILE_ROWS - 1) / TILE_ROWS) * ((p.M + TN - 1) / TN);
-    const int grid = n_tiles < p.sm_count ? n_tiles : p.sm_count;
-    kern<<<grid, GEMM_THREADS, smem, s>>>(tmap, p);
+    int grid = n_tiles < p.sm_count ? n_tiles : p.sm_count;
+    GemmParams q = p;
+    q.split = 0;
+    if (p.ws_slots && split_pays(n_tiles, p.K / QK_K, TN, p.sm_count, p.split)) {
+        q.split = 1;
+        const int tail_blocks = (n_tiles % p.sm_count) * (p.K / QK_K);
+        if (n_tiles < p.sm_count) grid = tail_blocks < p.sm_count ? tail_blocks : p.sm_count;
+    }
+    kern<<<grid, GEMM_THREADS, smem, s>>>(tmap, q);
     return cudaGetLastError();
 }
 
@@ -742,8 +926,15 @@ static size_t scratch_x_bytes(int K, int M) { return ((size_t)K * M * 2 + 255) /
 
 size_t gemm_scratch_bytes(int K, int M) { return scratch_x_bytes(K, M) + (size_t)M * sizeof(float); }
 
+// Split workspace: [2 * sms counters in 4 KiB][2 * sms slots of 128 x 256 floats].
+size_t gemm_split_counter_bytes() { return 4096; }
+size_t gemm_split_workspace_bytes(int sms) {
+    return gemm_split_counter_bytes() + (size_t)2 * sms * TILE_ROWS * 256 * sizeof(float);
+}
+
 cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                        int K, int N, int M, void *scratch, uint32_t *err_word, cudaStream_t s, uint64_t *launches) {
+                        int K, int N, int M, void *scratch, void *split_ws, int split_mode, uint32_t *err_word,
+                        cudaStream_t s, uint64_t *launches) {
     if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
     if (!scratch) return cudaErrorInvalidValue;
     __half *x_f16 = (__half *)scratch;
@@ -755,10 +946,15 @@ cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype
     GemmParams p{};
     p.W = w; p.Out = out; p.err = err_word; p.K = K; p.N = N; p.M = M; p.out_bf16 = out_dtype == DT_BF16;
     p.tok_scale = tok_scale;
+    p.split = split_mode;          // launch_tn turns the mode into the decision
     int dev = 0;
     e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&p.sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
+    if (split_ws && 2 * p.sm_count * sizeof(uint32_t) <= gemm_split_counter_bytes()) {
+        p.ws_counters = (uint32_t *)split_ws;
+        p.ws_slots = (float *)((uint8_t *)split_ws + gemm_split_counter_bytes());
+    }
     if (wdtype == DT_Q4K) {
         p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
         e = launch_qt<0>(p, x_f16, s);
@@ -811,7 +1007,7 @@ cudaError_t launch_gemm_static_scratch(int wdtype, const uint8_t *w, const void 
     if (e != cudaSuccess) return e;
     // Nothing in the scratch has to start at zero: the conversion kernel rewrites every f16
     // activation and every token scale the GEMM of this call reads.
-    return launch_gemm(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, scratch, err_word, s, launches);
+    return launch_gemm(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, scratch, nullptr, 0, err_word, s, launches);
 }
 
 }  // namespace llmrs

@@ -66,9 +66,16 @@ size_t gemv_max_k();
 // Prefill matmul on the tensor cores (tcgen05, f16 operands, fp32 accumulate in TMEM); M >= 1.
 // The activations are first converted to per-token-scaled f16 in `scratch`
 // (gemm_scratch_bytes() bytes of device memory owned by the caller).
+// `split_ws` (optional): gemm_split_workspace_bytes() bytes of device memory, zeroed once by the
+// caller and left zeroed by every launch; with it the kernel may cut the tiles of the last,
+// partial wave along K so that every SM works until the end (split_mode: -1 = a cost estimate
+// decides, 0 = never, 1 = whenever there is a partial wave).  One launch at a time per workspace.
 size_t gemm_scratch_bytes(int K, int M);
+size_t gemm_split_workspace_bytes(int sms);
+size_t gemm_split_counter_bytes();      // the leading bytes of the workspace that must be zero
 cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                        int K, int N, int M, void *scratch, uint32_t *err_word, cudaStream_t s, uint64_t *launches);
+                        int K, int N, int M, void *scratch, void *split_ws, int split_mode, uint32_t *err_word,
+                        cudaStream_t s, uint64_t *launches);
 
 // The same GEMM with its scratch in a fixed 8 MiB device array that is part of the library image:
 // no allocation on this path.  `device` must be the current device; the first call on a device

@@ -17,7 +17,8 @@ enum KernelError : uint32_t {
     KERR_EMPTY_WAIT = 2,   // the producer gave up waiting for a stage to be released
     KERR_MMA_WAIT = 3,     // a wait on tensor-core completion gave up
     KERR_TMEM_ALLOC = 4,
-    KERR_GATHER_WAIT = 5   // the fused all-gather gave up waiting for a peer's slice
+    KERR_GATHER_WAIT = 5,  // the fused all-gather gave up waiting for a peer's slice
+    KERR_SPLIT_WAIT = 6    // a split-K tile gave up waiting for the other CTAs' partial sums
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {

@@ -74,6 +74,16 @@ class ShardedMatmul:
         return full
 
 
+def gather_pointers(out_ptrs, flag_ptrs, rank: int, M: int, N: int, elt: int):
+    """Device addresses the fused all-gather kernel needs, from the per-rank base addresses of the
+    symmetric [2, M, N] output and the [world] uint32 flag array: (peer_out[2][world],
+    peer_flags[world], my_flags).  Rank r publishes its step in slot r of every rank's flag array."""
+    half = M * N * elt
+    peer_out = [[int(p) + b * half for p in out_ptrs] for b in (0, 1)]
+    peer_flags = [int(p) + 4 * rank for p in flag_ptrs]
+    return peer_out, peer_flags, int(flag_ptrs[rank])
+
+
 class FusedGatherMatmul:
     """Decode matmul (M <= 4) of an N-sharded weight whose all-gather runs inside the kernel.
 
@@ -81,8 +91,15 @@ class FusedGatherMatmul:
     so every rank can hand the kernel device pointers to every other rank's buffer.  The kernel
     (llmrs_cuda_matmul_allgather) stores its slice into all buffers over NVLink with plain stores,
     publishes a step number in the peers' flag arrays and returns when all slices have arrived in
-    its own buffer.  No NCCL call per step.  `out` is this rank's [M, N] tensor, complete once the
-    call's kernel has finished (stream order).
+    its own buffer.  No NCCL call per step.  The call returns this rank's [M, N] tensor, complete
+    once the call's kernel has finished (stream order).
+
+    Two output buffers alternate by step.  A peer can start step s+1 as soon as its own step s is
+    complete, and would then store into the buffer this rank may still be reading; with two
+    buffers the one returned by step s is not written again before step s+2, which no peer can
+    reach until this rank's step s+1 kernel has run -- and that kernel is ordered, on this rank's
+    stream, after whatever consumed step s.  Consumers on other streams must order themselves
+    against the next-but-one call.
     """
 
     def __init__(self, backend, weight_shard, N: int, M: int, out_dtype=torch.float32,
@@ -97,22 +114,22 @@ class FusedGatherMatmul:
         self.N, self.M = N, M
         row_range(N, self.rank, self.world)                       # checks divisibility
         dev = torch.device("cuda", backend.device)
-        self.out = symm.empty((M, N), dtype=out_dtype, device=dev)
+        self.out = symm.empty((2, M, N), dtype=out_dtype, device=dev)
         self.flags = symm.empty((self.world,), dtype=torch.int32, device=dev)
         self.out.zero_()
         self.flags.zero_()
         torch.cuda.synchronize(dev)
         oh = symm.rendezvous(self.out, self.group)
         fh = symm.rendezvous(self.flags, self.group)
-        self.peer_out = [int(p) for p in oh.buffer_ptrs]
-        self.peer_flags = [int(p) + 4 * self.rank for p in fh.buffer_ptrs]   # my slot in everyone's array
-        self.my_flags = int(fh.buffer_ptrs[self.rank])
+        self.peer_out, self.peer_flags, self.my_flags = gather_pointers(
+            oh.buffer_ptrs, fh.buffer_ptrs, self.rank, M, N, self.out.element_size())
         self.out_dtype = DType.F32 if out_dtype == torch.float32 else DType.BF16
         self.step = 0
         dist.barrier(self.group)                                   # all flag arrays are zeroed before any step
 
     def __call__(self, input_buf) -> torch.Tensor:
         self.step += 1
+        b = self.step & 1
         self.be.matmul_allgather(self.w, input_buf, self.out_dtype, self.N, self.rank, self.world,
-                                 self.peer_out, self.peer_flags, self.my_flags, self.step)
-        return self.out
+                                 self.peer_out[b], self.peer_flags, self.my_flags, self.step)
+        return self.out[b]

@@ -316,6 +316,44 @@ def test_gemm_token_scaling(backend):
             assert O.rel_l2(got[t], truth[t]) <= GEMM_TOL, t
 
 
+@pytest.fixture(scope="module")
+def backend_split(cuda_lib):
+    """A context whose tensor-core path always cuts the last, partial wave of tiles along K."""
+    import os
+    from llm_rs_b200 import CudaBackend
+    os.environ["LLMRS_GEMM_SPLIT"] = "1"
+    try:
+        be = CudaBackend(0)
+    finally:
+        del os.environ["LLMRS_GEMM_SPLIT"]
+    yield be
+    be.close()
+
+
+@pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
+@pytest.mark.parametrize("K,N,M,out_bf16", [
+    (14336, 4096, 128, False),    # 32 tiles, all of them split over the SMs
+    (4096, 2049, 40, False),      # 17 tiles of 64 tokens, ragged last weight tile
+    (768, 130, 257, True),        # 4 tiles x 3 blocks: fewer blocks than SMs
+    (1024, 19000, 300, False),    # 298 tiles: two whole per SM, two split
+    (512, 128, 5, False),         # one tile cut in two
+    (256, 128, 9, False),         # a single K block: nothing to cut
+])
+def test_gemm_split_last_wave(backend_split, dt, K, N, M, out_bf16):
+    """Partial sums travel through the workspace and the last CTA to arrive adds them up: same
+    tolerance as the unsplit kernel, twice in a row (the counters return to zero by themselves)."""
+    w = synth.weight(dt, K, N, tid=13 * K + N + M)
+    x = synth.activations(M, K, tid=3100 + M)
+    wb = upload_weight(backend_split, dt, w, K, N)
+    rows = (0, N) if N * M * K < 3e10 else (N - 256, N)
+    truth = O.matmul(dt, w, K, N, x, acc="f64", rows=rows)
+    tol = GEMM_TOL + (2.0 ** -8 if out_bf16 else 0.0)
+    for _ in range(2):
+        got = run_matmul(backend_split, wb, x, K, N, M, False, out_bf16)
+        assert O.rel_l2(got[:, rows[0]:rows[1]], truth[:, rows[0]:rows[1]]) <= tol
+        assert np.isfinite(got).all()
+
+
 @pytest.mark.parametrize("in_f,out_f,seq", [(256, 8, 80), (1024, 64, 100), (4096, 1024, 128)])
 def test_check_matmul_q4k_prefill_lengths(backend, in_f, out_f, seq):
     """The reference's check (its generator, bf16 in/out, its tolerance) at prefill lengths its own
