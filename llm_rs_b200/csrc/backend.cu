@@ -35,6 +35,7 @@ struct llmrs_ctx {
     int gemv_max_m = 4;              // M <= this: exact decode kernel (1e-4 class); above: tensor-core GEMM (2e-3 class)
     void *scratch = nullptr;         // f16 copy of the activations for the tensor-core path
     size_t scratch_bytes = 0;
+    bool pdl = true;                 // decode kernels overlap their prologue with the previous kernel's tail (LLMRS_NO_PDL=1: off)
     int gemm_split = -1;             // LLMRS_GEMM_SPLIT at creation: 0 never, 1 always, otherwise the estimate decides
     void *split_ws = nullptr;        // workspace of the tensor-core path's split of the last wave (zero between launches)
     uint32_t *dev_error = nullptr;   // device word: first KernelError reported by a kernel; next word: CTA counter
@@ -186,6 +187,7 @@ int llmrs_cuda_create(int device, void *stream, llmrs_ctx **out) {
         int v = atoi(env);
         if (v >= 0) ctx->gemv_max_m = v;
     }
+    if (const char *env = getenv("LLMRS_NO_PDL")) ctx->pdl = atoi(env) == 0;
     if (const char *env = getenv("LLMRS_GEMM_SPLIT")) ctx->gemm_split = atoi(env) ? 1 : 0;
     e = cudaEventCreate(&ctx->ev_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_end);
@@ -354,7 +356,7 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: event");
     if (decode) {
         e = launch_gemv((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
-                        (int)out->dtype, (int)K, (int)N, (int)M, ctx->sm_count, ctx->dev_error, ctx->stream,
+                        (int)out->dtype, (int)K, (int)N, (int)M, ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream,
                         &ctx->launches);
     } else {
         // The reference switches to its tiled GEMM kernels by seq_len too (metal/mod.rs:542-633).
@@ -439,7 +441,7 @@ int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, const llmrs_buf *weight_shard, c
     e = launch_gemv_allgather((int)weight_shard->dtype, (const uint8_t *)weight_shard->dptr, input->dptr,
                               (int)input->dtype, (int)out_dtype, (int)K, (int)N, (int)M, (int)n_total, (int)rank,
                               (int)world, peer_out, peer_flags, my_flags, ctx->dev_error + 1, step, ctx->sm_count,
-                              ctx->dev_error, ctx->stream, &ctx->launches);
+                              ctx->pdl, ctx->dev_error, ctx->stream, &ctx->launches);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: launch");
     return LLMRS_OK;
 }

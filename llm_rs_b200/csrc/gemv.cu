@@ -32,11 +32,13 @@ namespace llmrs {
 namespace {
 
 // A pipeline stage holds CHUNK_BLOCKS = 16 consecutive blocks of each row of the tile; a slice is
-// the 64 weights one lane handles, four per block.  (8-block stages were measured: twice the
-// barrier rounds cost more than the deeper ring gains, 82 us against 59 us for Q4_K 4096x128256.)
+// the 64 weights one lane handles, four per block.  Shorter chunks were measured and are slower,
+// because every bulk copy costs the copy engine about 80 clocks whatever its size: with 8-block
+// chunks Q4_K 4096x128256 took 82 us against 59 us, with 4-block chunks 145 us, and even a
+// one-tile matrix (4096x4096), where arithmetic could start on the first quarter of K, took
+// 7.1 us against 4.6 us.
 constexpr int MAX_STAGES = 8;
 constexpr uint32_t GATHER_WAIT_LIMIT = 1u << 25;       // polls (64 ns apart) before a peer is given up on
-constexpr int XBATCH = 8;                              // activation loads in flight per lane while staging
 
 // Activations become integers of 8*PLANES bits (two's complement, one byte plane each; the top
 // plane is signed).  |X| <= 2^XBITS keeps the integer dot product of a group inside int32.
@@ -94,7 +96,24 @@ struct GemvParams {
     size_t row_stride;      // bytes between weight rows
     int n_row_tiles, n_chunks;
     int stages;             // depth of the weight ring (<= MAX_STAGES)
+    int pdl;                // host: launch with programmatic stream serialization (see the kernel)
+#ifdef LLMRS_TUNING
+    unsigned long long *trace;   // [grid][4] nanosecond stamps: start, activations staged, first chunk landed, end
+#endif
 };
+
+#ifdef LLMRS_TUNING
+__device__ __forceinline__ void trace_stamp(const GemvParams &p, int slot) {
+    if (p.trace) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.trace[4 * blockIdx.x + slot] = t;
+    }
+}
+#define LLMRS_TRACE(slot) trace_stamp(p, slot)
+#else
+#define LLMRS_TRACE(slot)
+#endif
 
 __device__ __forceinline__ float load_x(const void *x, size_t idx, int is_bf16) {
     return is_bf16 ? bf16_bits_to_f32(__ldg((const uint16_t *)x + idx)) : __ldg((const float *)x + idx);
@@ -128,94 +147,120 @@ __device__ __forceinline__ int group_exponent(float amax) {
     return max(-126, min(126, e));
 }
 
-// One activation -> byte planes of its integer, written to plane l at planes[l*plane_stride + pos].
-template <int PLANES, int QT>
-__device__ __forceinline__ int quantise_store(float x, float scale, uint8_t *planes, int plane_stride, int pos) {
-    const int X = min(__float2int_rn(x * scale), XFmt<PLANES, QT>::XMAX);
-#pragma unroll
-    for (int l = 0; l < PLANES; l++) planes[l * plane_stride + pos] = (uint8_t)((X >> (8 * l)) & 0xFF);
-    return X;
-}
-
 // ---------------------------------------------------------------------------------------------
-// Staging of the activations (all consumer warps, once per CTA).
+// Staging of the activations (all consumer threads, once per CTA).
 // Q4_K slice (208 B): sub-block lo: plane0[32] plane1[32] plane2[32]; sub-block hi: same;
 //                     then float inv_scale_lo, inv_scale_hi, xsum_lo, xsum_hi.
 // Q6_K slice (240 B): group g = 0..3: plane0[16] plane1[16] plane2[16]; then float inv_scale[4],
 //                     float xsum[4]; 16 B unused (keeps consecutive lanes on distinct banks).
 // xsum is the sum of the rounded activations, so both terms of the formulas above see the same x.
+// One thread converts one whole scale group (32 or 16 consecutive activations): maximum,
+// exponent, rounding, byte planes and sum all stay in its registers, all loads of the group are
+// in flight together (one trip to L2), and there are no shuffles.  Measured alternatives, on the
+// 225-matmul decode stack at one token: a warp per group with five-step shuffle reductions,
+// 1.88 ms per step; four activations per thread with coalesced loads and two- or three-step
+// shuffles, 1.87 ms (5.07 ms at four tokens); this one 1.64 ms (3.96 ms).
 // ---------------------------------------------------------------------------------------------
-template <int QT, int PLANES>
-__device__ void stage_activations(uint8_t *xarea, size_t xtok_bytes, const GemvParams &p, int warp, int lane,
-                                  int n_warps) {
-    const int K = p.K;
-    for (int t = 0; t < p.m_valid; t++) {
-        uint8_t *xt = xarea + (size_t)t * xtok_bytes;
-        if (QT == 0) {
-            // a batch of loads is issued before any is used: one memory latency per batch
-            for (int sb0 = warp; sb0 < K / 32; sb0 += n_warps * XBATCH) {
-                float xv[XBATCH];
+template <int GROUP>
+__device__ __forceinline__ void load_group(const void *x, size_t idx, int is_bf16, float (&v)[GROUP]) {
+    if (is_bf16) {
+        const uint16_t *src = (const uint16_t *)x + idx;
+        if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
 #pragma unroll
-                for (int u = 0; u < XBATCH; u++) {
-                    const int sb = sb0 + u * n_warps;
-                    xv[u] = sb < K / 32 ? load_x(p.X, (size_t)t * K + 32 * sb + lane, p.x_bf16) : 0.0f;
+            for (int j = 0; j < GROUP / 8; j++) {
+                const uint4 u = __ldg(reinterpret_cast<const uint4 *>(src) + j);
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    v[8 * j + 2 * i] = __uint_as_float(w[i] << 16);
+                    v[8 * j + 2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
                 }
+            }
+        } else {                                          // a view that is not 16-byte aligned
 #pragma unroll
-                for (int u = 0; u < XBATCH; u++) {
-                    const int sb = sb0 + u * n_warps;
-                    if (sb >= K / 32) break;
-                    const float x = xv[u];
-                    float amax = fabsf(x);
+            for (int i = 0; i < GROUP; i++) v[i] = bf16_bits_to_f32(__ldg(src + i));
+        }
+    } else {
+        const float *src = (const float *)x + idx;
+        if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
 #pragma unroll
-                    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                    const int e = group_exponent<PLANES, 0>(amax);
-                    uint8_t *sl = xt + (size_t)(sb >> 1) * Fmt<0, PLANES>::XSTRIDE;
-                    int X = quantise_store<PLANES, 0>(x, exp2i(e), sl + (sb & 1) * Fmt<0, PLANES>::GROUP_BYTES, 32, lane);
-#pragma unroll
-                    for (int o = 16; o; o >>= 1) X += __shfl_xor_sync(0xffffffffu, X, o);
-                    if (lane == 0) {
-                        const float inv = isfinite(amax) ? exp2i(-e) : __uint_as_float(0x7FC00000u);
-                        float *f = reinterpret_cast<float *>(sl + Fmt<0, PLANES>::META);
-                        f[sb & 1] = inv;
-                        f[2 + (sb & 1)] = (float)X * inv;
-                    }
-                }
+            for (int j = 0; j < GROUP / 4; j++) {
+                const float4 f = __ldg(reinterpret_cast<const float4 *>(src) + j);
+                v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
             }
         } else {
-            // two 16-value groups per warp pass: lanes 0-15 take c = 0, lanes 16-31 take c = 1
-            for (int pr0 = warp; pr0 < K / 32; pr0 += n_warps * XBATCH) {
-                const int c = lane >> 4, i = lane & 15;
-                float xv[XBATCH];
 #pragma unroll
-                for (int u = 0; u < XBATCH; u++) {
-                    const int pr = pr0 + u * n_warps;
-                    const int b = pr >> 3, h = (pr >> 2) & 1, g = pr & 3;
-                    xv[u] = pr < K / 32
-                                ? load_x(p.X, (size_t)t * K + 256 * b + 128 * h + 32 * g + 16 * c + i, p.x_bf16)
-                                : 0.0f;
-                }
+            for (int i = 0; i < GROUP; i++) v[i] = __ldg(src + i);
+        }
+    }
+}
+
+// One group -> integers of XBITS bits, their byte planes at dst + l * GROUP; returns (1/scale, sum/scale).
+template <int GROUP, int PLANES, int QT>
+__device__ __forceinline__ float2 quantise_group(const float (&v)[GROUP], uint8_t *dst) {
+    float amax = 0.0f;
 #pragma unroll
-                for (int u = 0; u < XBATCH; u++) {
-                    const int pr = pr0 + u * n_warps;
-                    if (pr >= K / 32) break;
-                    const int b = pr >> 3, h = (pr >> 2) & 1, g = pr & 3;
-                    const float x = xv[u];
-                    float amax = fabsf(x);
+    for (int i = 0; i < GROUP; i++) amax = fmaxf(amax, fabsf(v[i]));
+    const int e = group_exponent<PLANES, QT>(amax);
+    const float scale = exp2i(e);
+    int X[GROUP];
+    int sum = 0;
 #pragma unroll
-                    for (int o = 8; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                    const int e = group_exponent<PLANES, 1>(amax);
-                    uint8_t *sl = xt + (size_t)(4 * b + 2 * h + c) * Fmt<1, PLANES>::XSTRIDE;
-                    int X = quantise_store<PLANES, 1>(x, exp2i(e), sl + g * Fmt<1, PLANES>::GROUP_BYTES, 16, i);
+    for (int i = 0; i < GROUP; i++) {
+        X[i] = min(__float2int_rn(v[i] * scale), XFmt<PLANES, QT>::XMAX);
+        sum += X[i];
+    }
 #pragma unroll
-                    for (int o = 8; o; o >>= 1) X += __shfl_xor_sync(0xffffffffu, X, o);
-                    if (i == 0) {
-                        const float inv = isfinite(amax) ? exp2i(-e) : __uint_as_float(0x7FC00000u);
-                        float *f = reinterpret_cast<float *>(sl + Fmt<1, PLANES>::META);
-                        f[g] = inv;
-                        f[4 + g] = (float)X * inv;
-                    }
-                }
-            }
+    for (int l = 0; l < PLANES; l++) {
+        uint32_t w[GROUP / 4];
+#pragma unroll
+        for (int j = 0; j < GROUP / 4; j++) {
+            // byte l of four consecutive integers -> one word
+            const uint32_t sel = (uint32_t)l | ((uint32_t)(4 + l) << 4);
+            const uint32_t lo = __byte_perm((uint32_t)X[4 * j], (uint32_t)X[4 * j + 1], sel);
+            const uint32_t hi = __byte_perm((uint32_t)X[4 * j + 2], (uint32_t)X[4 * j + 3], sel);
+            w[j] = __byte_perm(lo, hi, 0x5410u);
+        }
+#pragma unroll
+        for (int j = 0; j < GROUP / 16; j++)
+            *reinterpret_cast<uint4 *>(dst + l * GROUP + 16 * j) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    }
+    // an infinity or a NaN anywhere in the group makes its results NaN (fmaxf alone would drop a NaN)
+    float probe = 0.0f;
+#pragma unroll
+    for (int i = 0; i < GROUP; i++) probe += v[i] * 0.0f;
+    const float inv = probe == 0.0f ? exp2i(-e) : __uint_as_float(0x7FC00000u);
+    return make_float2(inv, (float)sum * inv);
+}
+
+template <int QT, int PLANES>
+__device__ void stage_activations(uint8_t *xarea, size_t xtok_bytes, const GemvParams &p, int tid, int n_threads) {
+    const int K = p.K;
+    if (QT == 0) {
+        const int groups = K / 32;                       // group sb = sub-block sb of the row
+        for (int gi = tid; gi < groups * p.m_valid; gi += n_threads) {
+            const int t = gi / groups, sb = gi - t * groups;
+            float v[32];
+            load_group<32>(p.X, (size_t)t * K + 32 * (size_t)sb, p.x_bf16, v);
+            uint8_t *sl = xarea + (size_t)t * xtok_bytes + (size_t)(sb >> 1) * Fmt<0, PLANES>::XSTRIDE;
+            const float2 m = quantise_group<32, PLANES, 0>(v, sl + (sb & 1) * Fmt<0, PLANES>::GROUP_BYTES);
+            float *f = reinterpret_cast<float *>(sl + Fmt<0, PLANES>::META);
+            f[sb & 1] = m.x;
+            f[2 + (sb & 1)] = m.y;
+        }
+    } else {
+        // group q = 16b + 8h + 2g + c covers activations 16 q .. 16 q + 15: group g of slice 4b + 2h + c
+        const int groups = K / 16;
+        for (int gi = tid; gi < groups * p.m_valid; gi += n_threads) {
+            const int t = gi / groups, q = gi - t * groups;
+            const int g = (q >> 1) & 3, slice = ((q >> 3) << 1) | (q & 1);
+            float v[16];
+            load_group<16>(p.X, (size_t)t * K + 16 * (size_t)q, p.x_bf16, v);
+            uint8_t *sl = xarea + (size_t)t * xtok_bytes + (size_t)slice * Fmt<1, PLANES>::XSTRIDE;
+            const float2 m = quantise_group<16, PLANES, 1>(v, sl + g * Fmt<1, PLANES>::GROUP_BYTES);
+            float *f = reinterpret_cast<float *>(sl + Fmt<1, PLANES>::META);
+            f[g] = m.x;
+            f[4 + g] = m.y;
         }
     }
 }
@@ -397,6 +442,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) {
+        LLMRS_TRACE(0);
         for (int s = 0; s < S; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], NCW);
@@ -405,6 +451,13 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
     }
     __syncthreads();
 
+    // Programmatic dependent launch.  The kernel that follows this one in the stream may start
+    // right away (its CTAs take SMs as ours leave them), and this kernel may have started before
+    // its predecessor finished.  Weights are never written by a kernel that is still in flight
+    // (upload_tensor synchronises), so the producer warp starts fetching them at once; everything
+    // that reads activations or writes results comes after griddepcontrol.wait, which returns when
+    // the predecessor has completed and its writes are visible.  Both are no-ops in a plain launch.
+    asm volatile("griddepcontrol.launch_dependents;");
     const int nb = p.K / QK_K;
     if (warp == NCW) {
         // ---------------- producer ----------------
@@ -431,8 +484,10 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
     }
 
     // ---------------- consumers ----------------
-    stage_activations<QT, PLANES>(xarea, xtok_bytes, p, warp, lane, NCW);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    stage_activations<QT, PLANES>(xarea, xtok_bytes, p, threadIdx.x, NCW * 32);
     named_barrier_sync(1, NCW * 32);
+    if (threadIdx.x == 0) LLMRS_TRACE(1);
 
     uint32_t it = 0;
     bool ok = true;
@@ -450,6 +505,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                 ok = false;
                 break;
             }
+            if (threadIdx.x == 0 && it == 0) LLMRS_TRACE(2);
             const int nbc = min(F::CHUNK_BLOCKS, nb - c * F::CHUNK_BLOCKS);
             const uint8_t *row[R];
 #pragma unroll
@@ -482,6 +538,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
             }
     }
 
+    if (threadIdx.x == 0) LLMRS_TRACE(3);
     if (p.g.world > 0) {
         // ---- publish this rank's slice and wait for the others ----
         __threadfence_system();                          // this thread's peer stores are visible system-wide
@@ -540,13 +597,27 @@ cudaError_t launch_cfg(const GemvParams &p0, int sm_count, int want_stages, cuda
     p.n_chunks = (p.K / QK_K + Fmt<QT, PLANES>::CHUNK_BLOCKS - 1) / Fmt<QT, PLANES>::CHUNK_BLOCKS;
     p.stages = ring_stages<QT, MT, R, NCW, PLANES>(p.K, want_stages);
     if (p.stages < 2) return cudaErrorInvalidConfiguration;
+    {   // no more stages than the busiest CTA has chunks to fetch (less shared memory to carve out)
+        const int grid0 = p.n_row_tiles < sm_count ? p.n_row_tiles : sm_count;
+        const int chunks_per_cta = (p.n_row_tiles + grid0 - 1) / grid0 * p.n_chunks;
+        if (chunks_per_cta < p.stages) p.stages = chunks_per_cta;
+    }
     const size_t smem = smem_fixed<QT, MT, R, NCW, PLANES>(p.K) + (size_t)p.stages * RT * Fmt<QT, PLANES>::CHUNK_MAX;
     auto kern = gemv_kernel<QT, MT, R, NCW, PLANES>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int grid = p.n_row_tiles < sm_count ? p.n_row_tiles : sm_count;
-    kern<<<grid, (NCW + 1) * 32, smem, s>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((NCW + 1) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 // Rows per warp: two rows share the staged activations in registers (measured best at every
@@ -603,9 +674,11 @@ size_t gemv_max_k() {
 }
 
 cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                        int K, int N, int M, int sm_count, uint32_t *err_word, cudaStream_t s, uint64_t *launches) {
+                        int K, int N, int M, int sm_count, bool pdl, uint32_t *err_word, cudaStream_t s,
+                        uint64_t *launches) {
     if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
     GemvParams p{};
+    p.pdl = pdl;
     p.W = w; p.X = x; p.Out = out; p.err = err_word;
     p.K = K; p.N = N;
     p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;
@@ -626,10 +699,11 @@ cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype
 cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, int x_dtype, int out_dtype, int K,
                                   int N_local, int M, int n_total, int rank, int world, void *const *peer_out,
                                   uint32_t *const *peer_flags, uint32_t *my_flags, uint32_t *done_counter,
-                                  uint32_t step, int sm_count, uint32_t *err_word, cudaStream_t s,
+                                  uint32_t step, int sm_count, bool pdl, uint32_t *err_word, cudaStream_t s,
                                   uint64_t *launches) {
     if (K <= 0 || N_local <= 0 || M <= 0 || M > 4 || world < 1 || world > MAX_GATHER_RANKS) return cudaErrorInvalidValue;
     GemvParams p{};
+    p.pdl = pdl;
     p.W = w; p.X = x; p.Out = peer_out[rank]; p.err = err_word;
     p.K = K; p.N = N_local;
     p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;
@@ -667,13 +741,16 @@ cudaError_t tune_dispatch(const GemvParams &p, int sm, int R, int ncw, int plane
     LLMRS_TRY(1, 16, 3) LLMRS_TRY(2, 16, 3) LLMRS_TRY(1, 16, 2) LLMRS_TRY(2, 16, 2)
     LLMRS_TRY(1, 12, 3) LLMRS_TRY(2, 12, 3) LLMRS_TRY(1, 12, 2) LLMRS_TRY(2, 12, 2)
 #undef LLMRS_TRY
+
     return cudaErrorInvalidValue;
 }
 }  // namespace
 cudaError_t tune_gemv(int wdtype, const uint8_t *w, const void *x, void *out, int K, int N, int M, int sm_count,
-                      uint32_t *err, int R, int ncw, int planes, int stages, cudaStream_t s) {
+                      uint32_t *err, int R, int ncw, int planes, int stages, cudaStream_t s,
+                      unsigned long long *trace) {
     GemvParams p{};
     p.W = w; p.X = x; p.Out = out; p.err = err; p.K = K; p.N = N; p.m_valid = M;
+    p.trace = trace;
     if (wdtype == DT_Q4K) {
         p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
         return M == 1 ? tune_dispatch<0, 1>(p, sm_count, R, ncw, planes, stages, s)

@@ -45,9 +45,12 @@ cudaError_t launch_dequant(int wdtype, const uint8_t *w, int K, int N, float *ou
 // Decode matmul: integer dot products per scale group, float32 across groups; any M (tokens are
 // processed in passes of <= 4).  x_dtype / out_dtype are DT_F32 or DT_BF16.  err_word is a device
 // word that receives a KernelError if a bounded wait inside the kernel gives up.  *launches is
-// incremented per kernel launched.
+// incremented per kernel launched.  pdl: launch with programmatic stream serialization, so that
+// the kernel's prologue and weight fetch overlap the tail of the kernel before it in the stream
+// (requires that no kernel still in flight writes the weights).
 cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                        int K, int N, int M, int sm_count, uint32_t *err_word, cudaStream_t s, uint64_t *launches);
+                        int K, int N, int M, int sm_count, bool pdl, uint32_t *err_word, cudaStream_t s,
+                        uint64_t *launches);
 
 // The decode matmul of one rank's weight rows with the all-gather fused in: every rank's kernel
 // stores its [M, N_local] slice into all ranks' [M, n_total] buffers (peer-mapped pointers) and
@@ -57,7 +60,7 @@ cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype
 cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, int x_dtype, int out_dtype, int K,
                                   int N_local, int M, int n_total, int rank, int world, void *const *peer_out,
                                   uint32_t *const *peer_flags, uint32_t *my_flags, uint32_t *done_counter,
-                                  uint32_t step, int sm_count, uint32_t *err_word, cudaStream_t s,
+                                  uint32_t step, int sm_count, bool pdl, uint32_t *err_word, cudaStream_t s,
                                   uint64_t *launches);
 
 // Largest in_features the decode kernel can stage in shared memory.
