@@ -201,15 +201,15 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         out_pinned = torch.empty(M, N_OUT, dtype=torch.float32).pin_memory()
 
         # With more than one GPU and a decode batch the all-gather is fused into the kernel (peer stores
-        # over NVLink, llm_rs_b200/shard.py: FusedGatherMatmul); NCCL remains the fallback.
+        # over NVLink, llm_rs_b200/shard.py: FusedGather); NCCL remains the fallback.
         fused = None
         exchange = "none"
         if world > 1:
             exchange = "NCCL all-gather of output slices"
             if M <= 4 and not args.nccl:
                 try:
-                    from llm_rs_b200.shard import FusedGatherMatmul
-                    fused = [FusedGatherMatmul(be, wb, N_OUT, M) for wb in weights]
+                    from llm_rs_b200.shard import FusedGather
+                    fused = FusedGather(be, N_OUT, M)
                     full = None
                     exchange = "all-gather fused into the kernel (peer stores over NVLink)"
                 except Exception as e:  # noqa: BLE001
@@ -229,7 +229,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
         def step(i):
             if fused is not None:
-                last["out"] = fused[i % copies](xbuf)
+                last["out"] = fused(weights[i % copies], xbuf)
             else:
                 be.matmul(obuf, weights[i % copies], xbuf)
                 gather()
@@ -286,6 +286,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         final = last["out"]
         assert bool(torch.isfinite(final).all()) and float(final.abs().sum()) > 0.0
 
+        multi = None
+        if world > 1 and not args.no_extra:
+            for b in weights:
+                b.free()
+            multi = multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs)
+
     alg = algorithmic_bytes(Q6K, K_IN, N_OUT, M)
     alg_local = algorithmic_bytes(Q6K, K_IN, n_local, M)
     value = alg / (ms_step * 1e-3) / 1e9
@@ -328,10 +334,134 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if world == 1 and not args.no_cpu_baseline:
         gbs, per_s, info = cpu_baseline(Q6K, K_IN, N_OUT, M, budget_s=10.0)
         line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", **info}
+    if multi is not None:
+        line["extra"] = multi
     if world == 1 and not args.no_extra:
         line["extra"] = extra_measurements(be_factory=lambda: CudaBackend(local_rank, stream=stream.cuda_stream),
                                            stream=stream, peak_gbs=peak_gbs)
     print(json.dumps(line), flush=True)
+
+
+def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
+    """Configs 4 and 5 on `world` GPUs: the linear stack of one decode / prefill step of an 8B- and a
+    70B-shaped model, every weight N-sharded (rank g keeps rows [g N/G, (g+1) N/G)), activations
+    replicated, each matmul followed by the all-gather of its output slices -- fused into the decode
+    kernel up to 4 tokens, NCCL above.  One CUDA graph per step where capture works.  All ranks run
+    this; the caller prints rank 0's result.  Times are CUDA events on the stream, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from llm_rs_b200 import DType, TensorView, synth
+    from llm_rs_b200.shard import FusedGather, row_range
+    tf_peak = 1658.7
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            tf_peak = float(json.load(f).get("bf16_tflops", tf_peak))
+    except Exception:  # noqa: BLE001
+        pass
+    models = {
+        "config4_llama8b": dict(hidden=4096, kv=1024, ffn=14336, vocab=128256, layers=32, Ms=(1, 4, 16, 64)),
+        "config5_llama70b": dict(hidden=8192, kv=1024, ffn=28672, vocab=128256, layers=80, Ms=(1, 64, 512, 4096)),
+    }
+    out = {"n_gpus": world, "note": ("linear stack only (7 matmuls per layer + output projection, bf16 activations); "
+                                      "weights N-sharded, activations replicated, all-gather of every output: fused "
+                                      "into the decode kernel for M <= 4, NCCL above; no_exchange = the same matmuls "
+                                      "without the all-gather")}
+    for name, cfg in models.items():
+        H, KV, F, V, L = cfg["hidden"], cfg["kv"], cfg["ffn"], cfg["vocab"], cfg["layers"]
+        layer = [(Q4K, H, H), (Q4K, H, KV), (Q4K, H, KV), (Q4K, H, H), (Q4K, H, F), (Q4K, H, F), (Q6K, F, H)]
+        per_gpu = sum((N // world) * (K // 256) * BLOCK_BYTES[dt] for dt, K, N in layer)
+        n_sets = int(min(8, max(2, np.ceil(4 * L2_BYTES / per_gpu))))        # rotated so weights come from HBM
+        host = []
+        for i, (dt, K, N) in enumerate(layer):
+            a, b = row_range(N, rank, world)
+            host.append(synth.weight(dt, K, N, tid=400 + i, rows=(a, b)))
+        sets = [[be.upload_tensor(TensorView("w", DType(dt), [K, N // world], h)) for (dt, K, N), h in zip(layer, host)]
+                for _ in range(n_sets)]
+        a, b = row_range(V, rank, world)
+        wout = be.upload_tensor(TensorView("w", DType.Q6K, [H, V // world], synth.weight(Q6K, H, V, tid=450, rows=(a, b))))
+        del host
+        weight_bytes = L * sum(N * (K // 256) * BLOCK_BYTES[dt] for dt, K, N in layer) + V * (H // 256) * 210
+        flops_per_token = 2.0 * (L * sum(K * N for _, K, N in layer) + H * V)
+        res = {}
+        for M in cfg["Ms"]:
+            shp = (lambda d: [d] if M == 1 else [d, M])
+            xs = {K: be.upload_tensor(TensorView("x", DType.BF16, shp(K), synth.bf16_bits(synth.activations(M, K, tid=K))))
+                  for K in (H, F)}
+            dims = sorted({N for _, _, N in layer} | {V})
+            locals_ = {N: torch.empty(M, N // world, device=dev, dtype=torch.bfloat16) for N in dims}
+            lbufs = {N: be.wrap(t.data_ptr(), shp(N // world), DType.BF16, keepalive=t) for N, t in locals_.items()}
+            # the fused exchange where one launch holds all tokens' staged activations, NCCL elsewhere
+            kinds = {(dt, K) for dt, K, _ in layer + [(Q6K, H, V)]}
+            fits = {(dt, K) for dt, K in kinds if be.allgather_max_tokens(DType(dt), K) >= M}
+            fused = {N: FusedGather(be, N, M, out_dtype=torch.bfloat16) for N in dims} if fits else None
+            fulls = {N: torch.empty(world, M, N // world, device=dev, dtype=torch.bfloat16) for N in dims}
+
+            def step(exchange=True):
+                for l in range(L):
+                    for (dt, K, N), w in zip(layer, sets[l % n_sets]):
+                        run_one(w, dt, K, N, exchange)
+                run_one(wout, Q6K, H, V, exchange)
+
+            def run_one(w, dt, K, N, exchange):
+                if exchange and (dt, K) in fits:
+                    fused[N](w, xs[K])
+                else:
+                    be.matmul(lbufs[N], w, xs[K])
+                    if exchange:
+                        dist.all_gather_into_tensor(fulls[N].view(-1), locals_[N].view(-1))
+
+            def timed(exchange, reps):
+                step(exchange)
+                stream.synchronize()
+                runner = lambda: step(exchange)
+                graph = None
+                try:
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=stream):
+                        step(exchange)
+                    runner = graph.replay
+                except Exception as e:  # noqa: BLE001
+                    graph = None
+                    if rank == 0:
+                        print(f"[bench] no CUDA graph for {name} M={M} ({e!r}); timing eager launches", file=sys.stderr)
+                    torch.cuda.synchronize(dev)
+                runner()
+                dist.barrier()
+                torch.cuda.synchronize(dev)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(reps):
+                    runner()
+                e1.record(stream)
+                e1.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                return float(t.item()) * 1e-3, graph is not None
+
+            reps = 10 if M <= 64 else (3 if M <= 512 else 2)
+            t, graphed = timed(True, reps)
+            t0, _ = timed(False, reps)
+            res[f"m{M}"] = {"ms_per_step": round(t * 1e3, 4), "ms_no_exchange": round(t0 * 1e3, 4),
+                            "tok_per_s": round(M / t, 1),
+                            "weight_GBps": round(weight_bytes / t / 1e9, 1),
+                            "frac_of_hbm_peak_x_gpus": round(weight_bytes / t / 1e9 / (peak_gbs * world), 4),
+                            "TFLOPs": round(flops_per_token * M / t / 1e12, 1),
+                            "frac_of_tensor_peak_x_gpus": round(flops_per_token * M / t / 1e12 / (tf_peak * world), 4),
+                            "exchange": ("fused peer stores" if fits == kinds else
+                                         "fused peer stores where one launch fits, NCCL all-gather elsewhere" if fits
+                                         else "NCCL all-gather"),
+                            "cuda_graph": graphed}
+            for bfr in list(xs.values()) + list(lbufs.values()):
+                bfr.free()
+            del fused, fulls, locals_
+            torch.cuda.synchronize(dev)
+        for st in sets:
+            for bfr in st:
+                bfr.free()
+        wout.free()
+        out[name] = res
+    return out
 
 
 def extra_measurements(be_factory, stream, peak_gbs):

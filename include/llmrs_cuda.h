@@ -128,18 +128,32 @@ int llmrs_cuda_matmul_static_scratch(llmrs_ctx *ctx, llmrs_buf *out, const llmrs
  * output slices fused into the kernel.  The reference is single-GPU and has no counterpart; the
  * sharding follows from every output row reading only its own weight row (shaders/ops.metal:249-289).
  * Rank `rank` of `world` holds rows [rank*N_local, (rank+1)*N_local) (weight_shard, created by
- * upload_tensor from those rows).  peer_out[d] is rank d's output buffer [M][n_total] of out_dtype
- * and peer_flags[d] is slot `rank` of rank d's flag array (uint32 [world], zero before the first
- * call), both as pointers this device can store through (peer-mapped / symmetric memory);
- * my_flags is this rank's own flag array.  `step` must grow by one per call, on every rank alike.
- * The kernel stores its slice into every rank's buffer with plain peer stores, publishes `step`,
- * and returns only when all ranks' slices have arrived in its own buffer (bounded wait: a peer
- * that never arrives yields LLMRS_ERR_KERNEL at the next sync).  M <= 4 (the decode kernel); all
- * ranks must make the call for every step. */
-int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, const llmrs_buf *weight_shard, const llmrs_buf *input,
-                                uint32_t out_dtype, uint32_t n_total, uint32_t rank, uint32_t world,
-                                void *const *peer_out, uint32_t *const *peer_flags, uint32_t *my_flags,
-                                uint32_t step);
+ * upload_tensor from those rows); `out` is this rank's full result, [N_local*world] or
+ * [N_local*world, M], in ordinary device memory.  peer_mailbox[d] is rank d's mailbox --
+ * llmrs_cuda_allgather_mailbox_bytes() bytes, zero before the first call, 8-byte aligned -- as a
+ * pointer this device can store through (peer-mapped / symmetric memory; entry `rank` is this
+ * rank's own).  step_word is a word of this device's memory, zero before the first call, in
+ * which the kernel counts the calls.
+ * Each result is written to `out` here and posted to every other rank as one 8-byte store
+ * {value, call number} into that rank's mailbox; before it finishes, the kernel copies the words
+ * the other ranks posted into `out`, waiting (with a bound: a peer that never posts yields
+ * LLMRS_ERR_KERNEL at the next sync) for each to carry this call's number.  When the call's
+ * kernel has completed, `out` is complete: stream order is all a consumer needs.  The mailbox
+ * has two halves used in turn, because a peer may be one call ahead.  All ranks must make the
+ * same sequence of calls on one mailbox (same N_local and M every time).  No argument changes
+ * from call to call, so a captured CUDA graph of the call can be replayed.
+ * M <= llmrs_cuda_matmul_allgather_max_tokens(). */
+int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight_shard,
+                                const llmrs_buf *input, uint32_t rank, uint32_t world, void *const *peer_mailbox,
+                                uint32_t *step_word);
+
+/* Bytes of one rank's mailbox for outputs of n_total rows and `tokens` tokens. */
+size_t llmrs_cuda_allgather_mailbox_bytes(uint32_t n_total, uint32_t tokens);
+
+/* Largest number of tokens (0..4) llmrs_cuda_matmul_allgather accepts for a weight of this dtype
+ * with this many input features: all tokens' staged activations must fit one launch (4 up to
+ * 8192 features, fewer above).  No counterpart in the reference. */
+int llmrs_cuda_matmul_allgather_max_tokens(uint32_t weight_dtype, uint32_t in_features);
 
 /* Dequantises a Q4_K/Q6_K weight to float32 [N, K] in device memory `dev_out`
  * (N*K floats).  The reference has no such op; it exposes, for testing, the

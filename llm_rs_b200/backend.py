@@ -84,8 +84,9 @@ ABI = {
     "llmrs_cuda_free": (C.c_int, [_VP, _BUFP]),
     "llmrs_cuda_matmul": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_matmul_static_scratch": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
-    "llmrs_cuda_matmul_allgather": (C.c_int, [_VP, _BUFP, _BUFP, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
-                                              C.POINTER(_VP), C.POINTER(_VP), _VP, C.c_uint32]),
+    "llmrs_cuda_matmul_allgather": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_uint32, C.c_uint32, C.POINTER(_VP), _VP]),
+    "llmrs_cuda_allgather_mailbox_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32]),
+    "llmrs_cuda_matmul_allgather_max_tokens": (C.c_int, [C.c_uint32, C.c_uint32]),
     "llmrs_cuda_dequantize": (C.c_int, [_VP, _BUFP, _VP]),
     "llmrs_cuda_write": (C.c_int, [_VP, _BUFP, _VP, C.c_size_t]),
     "llmrs_cuda_read_f32": (C.c_int, [_VP, _BUFP, C.POINTER(C.c_float), C.c_size_t]),
@@ -256,18 +257,24 @@ class CudaBackend:
         self._check(self._lib.llmrs_cuda_matmul_static_scratch(self._ctx, C.byref(out._raw), C.byref(weight._raw),
                                                                C.byref(input._raw)))
 
-    def matmul_allgather(self, weight_shard: CudaBuffer, input: CudaBuffer, out_dtype: DType, n_total: int,
-                         rank: int, world: int, peer_out: Sequence[int], peer_flags: Sequence[int],
-                         my_flags: int, step: int) -> None:
-        """Decode matmul of this rank's weight rows with the all-gather fused into the kernel: the
-        slice is stored into every rank's [M, n_total] buffer (`peer_out`, device pointers this GPU
-        can store through) and the call's kernel finishes when all slices have arrived locally.
-        peer_flags[d] = address of slot `rank` in rank d's uint32 flag array; M <= 4."""
-        po = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_out])
-        pf = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_flags])
-        self._check(self._lib.llmrs_cuda_matmul_allgather(self._ctx, C.byref(weight_shard._raw), C.byref(input._raw),
-                                                          int(out_dtype), n_total, rank, world, po, pf,
-                                                          C.c_void_p(int(my_flags)), step & 0xFFFFFFFF))
+    def matmul_allgather(self, out: CudaBuffer, weight_shard: CudaBuffer, input: CudaBuffer, rank: int, world: int,
+                         peer_mailbox: Sequence[int], step_word: int) -> None:
+        """Decode matmul of this rank's weight rows with the all-gather fused into the kernel: every
+        result goes into `out` ([N_local * world] or [N_local * world, M], local memory) and, as one
+        8-byte {value, call number} store, into the other ranks' mailboxes (`peer_mailbox`, device
+        pointers this GPU can store through); the kernel finishes when it has copied what the
+        others posted into `out`.  step_word = address of a local uint32 the kernel counts calls in."""
+        pm = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_mailbox])
+        self._check(self._lib.llmrs_cuda_matmul_allgather(self._ctx, C.byref(out._raw), C.byref(weight_shard._raw),
+                                                          C.byref(input._raw), rank, world, pm,
+                                                          C.c_void_p(int(step_word))))
+
+    def allgather_mailbox_bytes(self, n_total: int, tokens: int) -> int:
+        return int(self._lib.llmrs_cuda_allgather_mailbox_bytes(n_total, tokens))
+
+    def allgather_max_tokens(self, weight_dtype: DType, in_features: int) -> int:
+        """Largest token count matmul_allgather accepts for this weight type and in_features."""
+        return int(self._lib.llmrs_cuda_matmul_allgather_max_tokens(int(weight_dtype), in_features))
 
     def launch_count(self) -> int:
         v = C.c_uint64()

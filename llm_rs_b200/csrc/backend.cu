@@ -411,39 +411,51 @@ int llmrs_cuda_matmul_static_scratch(llmrs_ctx *ctx, llmrs_buf *out, const llmrs
     return LLMRS_OK;
 }
 
-int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, const llmrs_buf *weight_shard, const llmrs_buf *input,
-                                uint32_t out_dtype, uint32_t n_total, uint32_t rank, uint32_t world,
-                                void *const *peer_out, uint32_t *const *peer_flags, uint32_t *my_flags,
-                                uint32_t step) {
+int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight_shard,
+                                const llmrs_buf *input, uint32_t rank, uint32_t world, void *const *peer_mailbox,
+                                uint32_t *step_word) {
     if (!ctx) return LLMRS_ERR_ARG;
-    if (!weight_shard || !input || !weight_shard->dptr || !input->dptr || !peer_out || !peer_flags || !my_flags)
+    if (!out || !weight_shard || !input || !out->dptr || !weight_shard->dptr || !input->dptr || !peer_mailbox ||
+        !step_word)
         return ctx->fail(LLMRS_ERR_ARG, "matmul_allgather: null pointer");
     const uint32_t K = weight_shard->dim0, N = weight_shard->dim1 ? weight_shard->dim1 : 1;
     const uint32_t M = input->dim1 ? input->dim1 : 1;
     if (weight_shard->dtype != LLMRS_Q4K && weight_shard->dtype != LLMRS_Q6K)
         return ctx->fail(LLMRS_ERR_DTYPE, "matmul_allgather: weight dtype %u is not Q4_K/Q6_K", weight_shard->dtype);
-    if (!dense_elem_bytes(input->dtype) || !dense_elem_bytes(out_dtype))
+    if (weight_shard->dtype == LLMRS_Q6K && weight_shard->layout != LLMRS_LAYOUT_Q6K_SLICES)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul_allgather: weight was not created by upload_tensor");
+    if (!dense_elem_bytes(input->dtype) || !dense_elem_bytes(out->dtype))
         return ctx->fail(LLMRS_ERR_DTYPE, "matmul_allgather: activations must be F32 or BF16");
     if (world < 1 || world > 8 || rank >= world)
         return ctx->fail(LLMRS_ERR_ARG, "matmul_allgather: rank %u of %u (at most 8 ranks)", rank, world);
     if (input->dim0 != K || K % QK_K || K > gemv_max_k())
         return ctx->fail(LLMRS_ERR_SHAPE, "matmul_allgather: input has %u features, weight expects %u", input->dim0, K);
-    if ((uint64_t)N * world != n_total)
-        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_allgather: %u ranks x %u rows != %u rows", world, N, n_total);
-    if (M > 4)
-        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_allgather: %u tokens; the fused kernel serves M <= 4 "
-                                          "(use matmul + a collective above that)", M);
+    if ((uint64_t)N * world != out->dim0 || (out->dim1 ? out->dim1 : 1) != M)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_allgather: output is [%u, %u], expected [%u ranks x %u rows, %u]",
+                         out->dim0, out->dim1, world, N, M);
+    const int max_m = gemv_single_launch_max_tokens((int)weight_shard->dtype, (int)K);
+    if ((int)M > max_m)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_allgather: %u tokens; with %u input features the fused kernel "
+                                          "serves at most %d (use matmul + a collective above that)", M, K, max_m);
     for (uint32_t d = 0; d < world; d++)
-        if (!peer_out[d] || !peer_flags[d]) return ctx->fail(LLMRS_ERR_ARG, "matmul_allgather: null peer pointer");
+        if (!peer_mailbox[d]) return ctx->fail(LLMRS_ERR_ARG, "matmul_allgather: null mailbox pointer");
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: event");
     e = launch_gemv_allgather((int)weight_shard->dtype, (const uint8_t *)weight_shard->dptr, input->dptr,
-                              (int)input->dtype, (int)out_dtype, (int)K, (int)N, (int)M, (int)n_total, (int)rank,
-                              (int)world, peer_out, peer_flags, my_flags, ctx->dev_error + 1, step, ctx->sm_count,
-                              ctx->pdl, ctx->dev_error, ctx->stream, &ctx->launches);
+                              (int)input->dtype, out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, (int)rank,
+                              (int)world, peer_mailbox, ctx->dev_error + 1, step_word, ctx->sm_count, ctx->pdl,
+                              ctx->dev_error, ctx->stream, &ctx->launches);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: launch");
     return LLMRS_OK;
+}
+
+size_t llmrs_cuda_allgather_mailbox_bytes(uint32_t n_total, uint32_t tokens) {
+    return gemv_allgather_mailbox_bytes((int)n_total, (int)tokens);
+}
+
+int llmrs_cuda_matmul_allgather_max_tokens(uint32_t weight_dtype, uint32_t in_features) {
+    return gemv_single_launch_max_tokens((int)weight_dtype, (int)in_features);
 }
 
 int llmrs_cuda_dequantize(llmrs_ctx *ctx, const llmrs_buf *weight, float *dev_out) {

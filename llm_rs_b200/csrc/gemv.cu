@@ -29,6 +29,10 @@
 
 namespace llmrs {
 
+#ifdef LLMRS_TUNING
+unsigned long long *g_gather_trace = nullptr;   // tuning builds: where the exchange stamps go
+#endif
+
 namespace {
 
 // A pipeline stage holds CHUNK_BLOCKS = 16 consecutive blocks of each row of the tile; a slice is
@@ -69,20 +73,27 @@ template <int PLANES> struct Fmt<1, PLANES> {          // Q6_K, slice-major chun
 };
 
 // Fused all-gather of the output slices of an N-sharded matmul (world == 0: not used).
-// Rank r owns rows [row_offset, row_offset + N) of an n_total-row output.  Every rank's kernel
-// stores its slice straight into every rank's output buffer through peer-mapped pointers
-// (plain stores over NVLink, no TMA, no multicast); the last CTA to finish publishes `step` in
-// slot `rank` of every rank's flag array and then waits, with a bound, until its own flag array
-// shows `step` from every rank.  When the kernel has completed on a rank, that rank's buffer
-// holds all slices, so stream order is all a consumer needs.
+// Rank r owns rows [row_offset, row_offset + N) of an n_total-row output.  A result travels to
+// the other ranks as ONE 8-byte store {value as float bits, call number} into a mailbox in the
+// peer's memory (plain peer stores over NVLink, no TMA, no multicast).  An 8-byte aligned store
+// arrives whole, so the call number doubles as the "this value has landed" flag and no fence is
+// needed anywhere: a system-scope fence was measured at 5-7 us on this machine, two of them
+// per matmul in an earlier store-then-flag version of this exchange.  When a CTA has finished
+// its rows, its threads take a share of the mailbox words addressed to this rank, poll each until
+// it carries this call's number (bounded) and write the value into the local output.  The kernel
+// therefore completes on a rank only when that rank's output holds every slice, and stream order
+// is all a consumer needs.
+// The mailbox has two halves used in turn (call number & 1): a peer may be one call ahead, never
+// two, because its next call cannot complete without this rank's values of that call.  The call
+// number lives in device memory (*step_word) and the kernel advances it itself, so a captured
+// CUDA graph can be replayed: nothing that changes from call to call is a launch parameter.
 constexpr int MAX_GATHER_RANKS = 8;
 struct GatherParams {
-    void *peer_out[MAX_GATHER_RANKS];         // output buffer [M][n_total] of each rank
-    uint32_t *peer_flag[MAX_GATHER_RANKS];    // slot `rank` of each rank's flag array
-    uint32_t *my_flags;                       // this rank's flag array [world]
+    uint2 *peer_box[MAX_GATHER_RANKS];        // mailbox of each rank: [2][world senders][M][N] words
     uint32_t *done_counter;                   // local word: CTAs of this launch that have finished
+    uint32_t *step_word;                      // local word: calls completed so far
+    size_t half_words;                        // words in one half of a mailbox: world * M * N
     int world, rank, n_total, row_offset;
-    uint32_t step;
 };
 
 struct GemvParams {
@@ -111,7 +122,10 @@ __device__ __forceinline__ void trace_stamp(const GemvParams &p, int slot) {
     }
 }
 #define LLMRS_TRACE(slot) trace_stamp(p, slot)
+// stamps of the CTA that runs the exchange: behind the per-CTA slots of up to 148 CTAs
+#define LLMRS_GTRACE(k) do { if (p.trace) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.trace[4 * 148 + (k)] = t_; } } while (0)
 #else
+#define LLMRS_GTRACE(k)
 #define LLMRS_TRACE(slot)
 #endif
 
@@ -485,6 +499,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
 
     // ---------------- consumers ----------------
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // this call's step; the word is only advanced by the last CTA of a launch, after every CTA has read it
+    const uint32_t gather_step = p.g.world > 0 ? *reinterpret_cast<volatile uint32_t *>(p.g.step_word) + 1u : 0u;
     stage_activations<QT, PLANES>(xarea, xtok_bytes, p, threadIdx.x, NCW * 32);
     named_barrier_sync(1, NCW * 32);
     if (threadIdx.x == 0) LLMRS_TRACE(1);
@@ -530,36 +546,53 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                 if (ok && out_row < p.N && t < p.m_valid) {
                     if (p.g.world == 0) {
                         if (lane == 0) store_out(p.Out, (size_t)t * p.N + out_row, v, p.out_bf16);
-                    } else if (lane < p.g.world) {        // lane d stores into rank d's buffer
-                        store_out(p.g.peer_out[lane], (size_t)t * p.g.n_total + p.g.row_offset + out_row, v,
-                                  p.out_bf16);
+                    } else if (lane == p.g.rank) {        // this rank's own copy: straight into the output
+                        store_out(p.Out, (size_t)t * p.g.n_total + p.g.row_offset + out_row, v, p.out_bf16);
+                    } else if (lane < p.g.world) {        // lane d posts the value to rank d's mailbox
+                        uint2 *box = p.g.peer_box[lane] + (gather_step & 1u) * p.g.half_words +
+                                     ((size_t)p.g.rank * p.m_valid + t) * p.N + out_row;
+                        asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(box), "r"(__float_as_uint(v)), "r"(gather_step) : "memory");
                     }
                 }
             }
     }
 
     if (threadIdx.x == 0) LLMRS_TRACE(3);
+    if (p.g.world > 1) {
+        // ---- collect the other ranks' slices from this rank's mailbox ----
+        if (threadIdx.x == 0) LLMRS_GTRACE(0);
+        const uint2 *box = p.g.peer_box[p.g.rank] + (gather_step & 1u) * p.g.half_words;
+        const int per_src = p.m_valid * p.N;                             // words one sender posts
+        const int remote = (p.g.world - 1) * per_src;
+        bool late = false;
+        for (int i = blockIdx.x * (NCW * 32) + threadIdx.x; i < remote && !late; i += gridDim.x * (NCW * 32)) {
+            const int q = i / per_src, rem = i - q * per_src;
+            const int src = q < p.g.rank ? q : q + 1;
+            const int t = rem / p.N, row = rem - t * p.N;
+            const uint2 *w = box + (size_t)src * per_src + rem;
+            uint32_t val = 0, tag = 0;
+            for (uint32_t spin = 0; spin < GATHER_WAIT_LIMIT; spin++) {
+                asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(val), "=r"(tag) : "l"(w) : "memory");
+                if (tag == gather_step) break;
+                __nanosleep(32);
+            }
+            if (tag != gather_step) {
+                report_error(p.err, KERR_GATHER_WAIT);
+                late = true;
+            } else {
+                store_out(p.Out, (size_t)t * p.g.n_total + (size_t)src * p.N + row, __uint_as_float(val), p.out_bf16);
+            }
+        }
+        if (threadIdx.x == 0) LLMRS_GTRACE(1);
+    }
     if (p.g.world > 0) {
-        // ---- publish this rank's slice and wait for the others ----
-        __threadfence_system();                          // this thread's peer stores are visible system-wide
+        // the last CTA to get here advances the call number for the next launch; every CTA read it long ago
         named_barrier_sync(1, NCW * 32);
         if (threadIdx.x == 0) {
             const uint32_t ticket = atomicAdd(p.g.done_counter, 1u);
-            if (ticket == gridDim.x - 1) {               // every CTA of this launch has stored and fenced
-                *p.g.done_counter = 0;                   // ready for the next launch
-                __threadfence_system();
-                for (int d = 0; d < p.g.world; d++)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.g.peer_flag[d]), "r"(p.g.step) : "memory");
-                for (int src = 0; src < p.g.world; src++) {
-                    bool seen = false;
-                    for (uint32_t i = 0; i < GATHER_WAIT_LIMIT && !seen; i++) {
-                        uint32_t f;
-                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(p.g.my_flags + src) : "memory");
-                        seen = (int32_t)(f - p.g.step) >= 0;
-                        if (!seen) __nanosleep(64);
-                    }
-                    if (!seen) report_error(p.err, KERR_GATHER_WAIT);
-                }
+            if (ticket == gridDim.x - 1) {
+                *p.g.done_counter = 0;
+                *p.g.step_word = gather_step;
             }
         }
     }
@@ -694,38 +727,61 @@ cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype
     return cudaErrorInvalidValue;
 }
 
+// Largest token count (<= 4) whose staged activations fit one launch of the decode kernel.
+namespace {
+template <int QT, int MT>
+bool one_pass_fits(int K) {
+    return ring_stages<QT, MT, 2, NCW_DEFAULT, PLANES_DEFAULT>(K, 4) >= 2 ||
+           ring_stages<QT, MT, 1, NCW_DEFAULT, PLANES_DEFAULT>(K, 4) >= 2;
+}
+template <int QT>
+int max_tokens_qt(int K) {
+    if (one_pass_fits<QT, 4>(K)) return 4;
+    if (one_pass_fits<QT, 3>(K)) return 3;
+    if (one_pass_fits<QT, 2>(K)) return 2;
+    return one_pass_fits<QT, 1>(K) ? 1 : 0;
+}
+}  // namespace
+int gemv_single_launch_max_tokens(int wdtype, int K) {
+    if (K <= 0 || K % QK_K) return 0;
+    return wdtype == DT_Q4K ? max_tokens_qt<0>(K) : wdtype == DT_Q6K ? max_tokens_qt<1>(K) : 0;
+}
+
 // N-sharded decode matmul with the all-gather of the output slices fused into the kernel (see
 // GatherParams).  One launch, so M <= 4 and the activations must fit the shared-memory staging.
-cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, int x_dtype, int out_dtype, int K,
-                                  int N_local, int M, int n_total, int rank, int world, void *const *peer_out,
-                                  uint32_t *const *peer_flags, uint32_t *my_flags, uint32_t *done_counter,
-                                  uint32_t step, int sm_count, bool pdl, uint32_t *err_word, cudaStream_t s,
-                                  uint64_t *launches) {
+size_t gemv_allgather_mailbox_bytes(int n_total, int M) { return (size_t)2 * M * n_total * sizeof(uint2); }
+
+cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
+                                  int K, int N_local, int M, int rank, int world, void *const *peer_mailbox,
+                                  uint32_t *done_counter, uint32_t *step_word, int sm_count, bool pdl,
+                                  uint32_t *err_word, cudaStream_t s, uint64_t *launches) {
     if (K <= 0 || N_local <= 0 || M <= 0 || M > 4 || world < 1 || world > MAX_GATHER_RANKS) return cudaErrorInvalidValue;
+    if (M > gemv_single_launch_max_tokens(wdtype, K)) return cudaErrorInvalidValue;   // token passes would each post
     GemvParams p{};
     p.pdl = pdl;
-    p.W = w; p.X = x; p.Out = peer_out[rank]; p.err = err_word;
+    p.W = w; p.X = x; p.Out = out; p.err = err_word;
     p.K = K; p.N = N_local;
     p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;
-    p.g.world = world; p.g.rank = rank; p.g.n_total = n_total; p.g.row_offset = rank * N_local;
-    p.g.my_flags = my_flags; p.g.done_counter = done_counter; p.g.step = step;
-    for (int d = 0; d < world; d++) {
-        p.g.peer_out[d] = peer_out[d];
-        p.g.peer_flag[d] = peer_flags[d];
-    }
-    const int xe = x_dtype == DT_BF16 ? 2 : 4, oe = out_dtype == DT_BF16 ? 2 : 4;
+    p.g.world = world; p.g.rank = rank; p.g.n_total = N_local * world; p.g.row_offset = rank * N_local;
+    p.g.done_counter = done_counter; p.g.step_word = step_word;
+    p.g.half_words = (size_t)world * M * N_local;
+#ifdef LLMRS_TUNING
+    p.trace = g_gather_trace;
+#endif
+    for (int d = 0; d < world; d++) p.g.peer_box[d] = (uint2 *)peer_mailbox[d];
     uint64_t n = 0;
     cudaError_t e;
+    // x_elem / out_elem are only used to step through token passes, of which there is one
     if (wdtype == DT_Q4K) {
         p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
-        e = launch_fmt<0>(p, M, xe, oe, sm_count, s, &n);
+        e = launch_fmt<0>(p, M, 0, 0, sm_count, s, &n);
     } else if (wdtype == DT_Q6K) {
         p.row_stride = q6k_row_stride(K);
-        e = launch_fmt<1>(p, M, xe, oe, sm_count, s, &n);
+        e = launch_fmt<1>(p, M, 0, 0, sm_count, s, &n);
     } else {
         return cudaErrorInvalidValue;
     }
-    if (e == cudaSuccess && n != 1) e = cudaErrorInvalidConfiguration;   // token passes would each signal
+    if (e == cudaSuccess && n != 1) e = cudaErrorInvalidConfiguration;
     if (launches) *launches += n;
     return e;
 }

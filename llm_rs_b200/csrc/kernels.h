@@ -52,19 +52,23 @@ cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype
                         int K, int N, int M, int sm_count, bool pdl, uint32_t *err_word, cudaStream_t s,
                         uint64_t *launches);
 
-// The decode matmul of one rank's weight rows with the all-gather fused in: every rank's kernel
-// stores its [M, N_local] slice into all ranks' [M, n_total] buffers (peer-mapped pointers) and
-// returns once all slices have arrived in its own.  peer_out[d]: rank d's buffer; peer_flags[d]:
-// slot `rank` of rank d's flag array; my_flags: this rank's flag array [world]; step: a value
-// that grows by one per call on every rank.  M <= 4.
-cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, int x_dtype, int out_dtype, int K,
-                                  int N_local, int M, int n_total, int rank, int world, void *const *peer_out,
-                                  uint32_t *const *peer_flags, uint32_t *my_flags, uint32_t *done_counter,
-                                  uint32_t step, int sm_count, bool pdl, uint32_t *err_word, cudaStream_t s,
-                                  uint64_t *launches);
+// The decode matmul of one rank's weight rows with the all-gather fused in.  `out` is this rank's
+// [M, N_local * world] result.  peer_mailbox[d] is rank d's mailbox (gemv_allgather_mailbox_bytes()
+// bytes, zero before the first call) as a pointer this device can store through; each result is
+// posted to the other ranks as one 8-byte {value, call number} store and the kernel copies what
+// the others posted into `out` before it finishes.  step_word: a local device word, zero before
+// the first call, in which the kernel counts the calls.  M <= gemv_single_launch_max_tokens().
+size_t gemv_allgather_mailbox_bytes(int n_total, int M);
+cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
+                                  int K, int N_local, int M, int rank, int world, void *const *peer_mailbox,
+                                  uint32_t *done_counter, uint32_t *step_word, int sm_count, bool pdl,
+                                  uint32_t *err_word, cudaStream_t s, uint64_t *launches);
 
 // Largest in_features the decode kernel can stage in shared memory.
 size_t gemv_max_k();
+// Largest number of tokens (0..4) the decode kernel serves in ONE launch for this weight type and
+// in_features (the staged activations of all tokens must fit beside two ring stages).
+int gemv_single_launch_max_tokens(int wdtype, int K);
 
 // Prefill matmul on the tensor cores (tcgen05, f16 operands, fp32 accumulate in TMEM); M >= 1.
 // The activations are first converted to per-token-scaled f16 in `scratch`

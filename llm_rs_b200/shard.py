@@ -74,62 +74,41 @@ class ShardedMatmul:
         return full
 
 
-def gather_pointers(out_ptrs, flag_ptrs, rank: int, M: int, N: int, elt: int):
-    """Device addresses the fused all-gather kernel needs, from the per-rank base addresses of the
-    symmetric [2, M, N] output and the [world] uint32 flag array: (peer_out[2][world],
-    peer_flags[world], my_flags).  Rank r publishes its step in slot r of every rank's flag array."""
-    half = M * N * elt
-    peer_out = [[int(p) + b * half for p in out_ptrs] for b in (0, 1)]
-    peer_flags = [int(p) + 4 * rank for p in flag_ptrs]
-    return peer_out, peer_flags, int(flag_ptrs[rank])
+class FusedGather:
+    """Decode matmuls (M <= 4) of N-sharded weights whose all-gather runs inside the kernel.
 
-
-class FusedGatherMatmul:
-    """Decode matmul (M <= 4) of an N-sharded weight whose all-gather runs inside the kernel.
-
-    Output buffers and flag arrays live in symmetric memory (torch.distributed._symmetric_memory),
-    so every rank can hand the kernel device pointers to every other rank's buffer.  The kernel
-    (llmrs_cuda_matmul_allgather) stores its slice into all buffers over NVLink with plain stores,
-    publishes a step number in the peers' flag arrays and returns when all slices have arrived in
-    its own buffer.  No NCCL call per step.  The call returns this rank's [M, N] tensor, complete
-    once the call's kernel has finished (stream order).
-
-    Two output buffers alternate by step.  A peer can start step s+1 as soon as its own step s is
-    complete, and would then store into the buffer this rank may still be reading; with two
-    buffers the one returned by step s is not written again before step s+2, which no peer can
-    reach until this rank's step s+1 kernel has run -- and that kernel is ordered, on this rank's
-    stream, after whatever consumed step s.  Consumers on other streams must order themselves
-    against the next-but-one call.
+    One object serves every weight with the same total N and token count.  It owns this rank's
+    [M, N] output (ordinary device memory), its mailbox in symmetric memory
+    (torch.distributed._symmetric_memory), so that every rank can hand the kernel device pointers
+    to every other rank's mailbox, and a device word in which the kernel counts the calls.  The
+    kernel (llmrs_cuda_matmul_allgather) posts each result to the other ranks as one 8-byte
+    {value, call number} store over NVLink and copies what the others posted into `out` before
+    it finishes: no NCCL call, no fence, no separate flag.  Nothing that changes per call is a
+    launch argument, so a step captured in a CUDA graph can be replayed.  `out` is complete when
+    the call's kernel has finished (stream order).
     """
 
-    def __init__(self, backend, weight_shard, N: int, M: int, out_dtype=torch.float32,
-                 group: dist.ProcessGroup | None = None):
+    def __init__(self, backend, N: int, M: int, out_dtype=torch.float32, group: dist.ProcessGroup | None = None):
         import torch.distributed._symmetric_memory as symm
         from .backend import DType
-        if M > 4:
-            raise ValueError("the fused all-gather serves the decode kernel only (M <= 4)")
-        self.be, self.w = backend, weight_shard
+        self.be = backend
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         self.N, self.M = N, M
         row_range(N, self.rank, self.world)                       # checks divisibility
         dev = torch.device("cuda", backend.device)
-        self.out = symm.empty((2, M, N), dtype=out_dtype, device=dev)
-        self.flags = symm.empty((self.world,), dtype=torch.int32, device=dev)
-        self.out.zero_()
-        self.flags.zero_()
+        self.out = torch.zeros(M, N, dtype=out_dtype, device=dev)
+        self.out_buf = backend.wrap(self.out.data_ptr(), [N] if M == 1 else [N, M],
+                                    DType.F32 if out_dtype == torch.float32 else DType.BF16, keepalive=self.out)
+        self.mailbox = symm.empty((backend.allgather_mailbox_bytes(N, M) // 8,), dtype=torch.int64, device=dev)
+        self.step_word = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.mailbox.zero_()
         torch.cuda.synchronize(dev)
-        oh = symm.rendezvous(self.out, self.group)
-        fh = symm.rendezvous(self.flags, self.group)
-        self.peer_out, self.peer_flags, self.my_flags = gather_pointers(
-            oh.buffer_ptrs, fh.buffer_ptrs, self.rank, M, N, self.out.element_size())
-        self.out_dtype = DType.F32 if out_dtype == torch.float32 else DType.BF16
-        self.step = 0
-        dist.barrier(self.group)                                   # all flag arrays are zeroed before any step
+        handle = symm.rendezvous(self.mailbox, self.group)
+        self.peer_mailbox = [int(p) for p in handle.buffer_ptrs]
+        dist.barrier(self.group)                                   # every mailbox is zeroed before any call
 
-    def __call__(self, input_buf) -> torch.Tensor:
-        self.step += 1
-        b = self.step & 1
-        self.be.matmul_allgather(self.w, input_buf, self.out_dtype, self.N, self.rank, self.world,
-                                 self.peer_out[b], self.peer_flags, self.my_flags, self.step)
-        return self.out[b]
+    def __call__(self, weight_shard, input_buf) -> torch.Tensor:
+        self.be.matmul_allgather(self.out_buf, weight_shard, input_buf, self.rank, self.world, self.peer_mailbox,
+                                 self.step_word.data_ptr())
+        return self.out

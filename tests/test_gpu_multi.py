@@ -15,7 +15,7 @@ def _worker(rank, world, port, q):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     from llm_rs_b200 import CudaBackend, DType, TensorView, synth
-    from llm_rs_b200.shard import FusedGatherMatmul, row_range
+    from llm_rs_b200.shard import FusedGather, row_range
     from oracle import oracle as O
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -31,17 +31,35 @@ def _worker(rank, world, port, q):
                 w_full = synth.weight(dt, K, N, tid=dt)
                 w_loc = synth.weight(dt, K, N, tid=dt, rows=(a, b))
                 wbuf = be.upload_tensor(TensorView("w", DType(dt), [K, b - a], w_loc))
-                fused = FusedGatherMatmul(be, wbuf, N, M)
+                fused = FusedGather(be, N, M)
                 for call in range(3):                      # flags and buffers are reused across steps
                     x = synth.activations(M, K, tid=50 + call)
                     xbuf = be.upload_tensor(TensorView("x", DType.F32, [K] if M == 1 else [K, M], x))
-                    out = fused(xbuf)
+                    out = fused(wbuf, xbuf)
                     be.sync()
                     got = out.cpu().numpy()
                     err = O.rel_l2(got, O.matmul(dt, w_full, K, N, x, acc="f64"))
                     if not err <= 1e-4:
                         ok, msg = False, f"dtype {dt} call {call}: rel_l2 {err}"
                     dist.barrier()
+                # the same call captured once in a CUDA graph and replayed: the kernel keeps its own count
+                x = synth.activations(M, K, tid=60)
+                xbuf = be.upload_tensor(TensorView("x", DType.F32, [K] if M == 1 else [K, M], x))
+                fused(wbuf, xbuf)                          # warm call outside capture
+                be.sync()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    fused(wbuf, xbuf)
+                truth = O.matmul(dt, w_full, K, N, x, acc="f64")
+                for _ in range(3):
+                    fused.out.zero_()
+                    g.replay()
+                    stream.synchronize()
+                    got = fused.out.cpu().numpy()
+                    err = O.rel_l2(got, truth)
+                    if not err <= 1e-4:
+                        ok, msg = False, f"dtype {dt} graph replay: rel_l2 {err}"
+                dist.barrier()
             be.close()
     except Exception as e:  # noqa: BLE001
         ok, msg = False, repr(e)

@@ -62,11 +62,3 @@ def test_sharded_matmul_two_gloo_ranks():
     for p in procs:
         p.join(60)
     assert res == [(0, True), (1, True)]
-
-
-def test_gather_pointers():
-    from llm_rs_b200.shard import gather_pointers
-    outs, flags = [0x1000, 0x9000, 0x11000], [0x100, 0x200, 0x300]
-    po, pf, mine = gather_pointers(outs, flags, rank=1, M=2, N=96, elt=4)
-    assert po[0] == outs and po[1] == [p + 2 * 96 * 4 for p in outs]
-    assert pf == [0x104, 0x204, 0x304] and mine == 0x200
