@@ -40,6 +40,7 @@
 #include "kernels.h"
 #include "llmrs_common.cuh"
 #include "pipeline.cuh"
+#include "tensor_map.h"
 
 namespace llmrs {
 
@@ -196,13 +197,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *tmap, int c0, int c1, uint64_t *bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
-        : "memory");
-}
 
 // Shared-memory matrix descriptor of a K-major, 128-byte-swizzled 16-bit tile whose rows are 128
 // bytes: start address, leading byte offset 1 (unused with swizzle), stride byte offset 1024
@@ -851,22 +845,6 @@ activations_to_f16_kernel(const void *__restrict__ x, int x_is_bf16, int K, __ha
 
 // ---- host side ---------------------------------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *sym = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-    return fn;
-}
-
 // Does cutting the last, partial wave of tiles along K pay?  The exchange is not free: a deposit
 // is a tile-sized fp32 store, and the last arriver reads every deposit back group by group, one
 // L2 round trip each.  Measured on a B200 (split / no split): K=14336, N=4096 (32 tiles) 0.52 at
@@ -883,20 +861,13 @@ bool split_pays(int n_tiles, int nb, int TN, int sms, int forced) {
 
 template <int QT, int TN>
 cudaError_t launch_tn(const GemmParams &p, const void *x_f16, cudaStream_t s) {
-    EncodeTiledFn enc = encode_tiled_fn();
-    if (!enc) return cudaErrorNotSupported;
     CUtensorMap tmap;
-    const cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
-    const cuuint64_t strides[1] = {(cuuint64_t)p.K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)TN};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x_f16), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    cudaError_t e = encode_2d(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x_f16, (uint64_t)p.K, (uint64_t)p.M,
+                              (uint64_t)p.K * 2, BK, TN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (e != cudaSuccess) return e;
     constexpr size_t smem = GemmCfg<TN>::SMEM;
     auto kern = gemm_kernel<QT, TN>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = ((p.N + TILE_ROWS - 1) / TILE_ROWS) * ((p.M + TN - 1) / TN);
     int grid = n_tiles < p.sm_count ? n_tiles : p.sm_count;

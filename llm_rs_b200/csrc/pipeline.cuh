@@ -70,6 +70,16 @@ __device__ __forceinline__ void bulk_copy_g2s(void *dst_smem, const void *src_gm
                  : "memory");
 }
 
+// Tiled (tensor-map) copy of one 2-D box global -> shared, completion reported to `bar` in bytes.
+// c0 (innermost coordinate) times the element size must be a multiple of 16 bytes; the destination
+// must be 128-byte aligned.  Parts of the box outside the tensor are filled with zeros and still count.
+__device__ __forceinline__ void tma_load_2d(void *dst_smem, const void *tmap, int c0, int c1, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
+}
+
 // Barrier over a subset of the CTA's warps (id 1..15; 0 is __syncthreads).
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
