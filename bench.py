@@ -519,6 +519,58 @@ def extra_measurements(be_factory, stream, peak_gbs):
                 fl = 2.0 * M * K * N
                 out["gemm"][f"{name}_m{M}"] = {"us": round(t * 1e6, 1), "TFLOPs": round(fl / t / 1e12, 1),
                                                "frac_of_tensor_peak": round(fl / t / 1e12 / tf_peak, 4)}
+        # next rows: the feed-forward front as one call, and the embedding lookup
+        out["ffn_front"], out["embed"] = {}, {}
+        wg = [be.upload_tensor(TensorView("w", DType.Q4K, [4096, 14336], synth.weight(Q4K, 4096, 14336, tid=60 + i)))
+              for i in range(8)]                      # 4 gate/up pairs, 264 MB: rotated, so they come from HBM
+        for M in (1, 4):
+            x = be.upload_tensor(TensorView("x", DType.BF16, [4096] if M == 1 else [4096, M],
+                                            synth.bf16_bits(synth.activations(M, 4096))))
+            o = be.alloc([14336] if M == 1 else [14336, M], DType.BF16)
+            g = be.alloc([14336] if M == 1 else [14336, M], DType.BF16)
+            for fused in (True, False):
+                def run(i):
+                    a, b = wg[2 * (i % 4)], wg[2 * (i % 4) + 1]
+                    if fused:
+                        be.matmul_gate_up(o, a, b, x)
+                    else:                             # the two matmuls alone: silu and mul would come on top
+                        be.matmul(g, a, x)
+                        be.matmul(o, b, x)
+                for i in range(5):
+                    run(i)
+                be.sync()
+                be.reset_gpu_secs()
+                for i in range(100):
+                    run(i)
+                be.sync()
+                t = be.gpu_secs_total() / 100
+                wbytes = 2 * 14336 * 16 * 144
+                out["ffn_front"][f"q4k_4096x14336_m{M}_{'one_call' if fused else 'two_matmuls'}"] = {
+                    "us": round(t * 1e6, 2), "weight_GBps": round(wbytes / t / 1e9, 1),
+                    "frac_of_hbm_peak": round(wbytes / t / 1e9 / peak_gbs, 4)}
+            for b in (x, o, g):
+                b.free()
+        for b in wg:
+            b.free()
+        rng = np.random.default_rng(5)
+        for name, dt, bb in (("q4k", Q4K, 144), ("q6k", Q6K, 210)):
+            vocab, dim, ntok = 128256, 4096, 2048
+            table = be.upload_tensor(TensorView("t", DType(dt), [dim, vocab], synth.weight(dt, dim, vocab, tid=70)))
+            toks = rng.integers(0, vocab, ntok).astype(np.uint32)
+            o = be.alloc([dim, ntok], DType.BF16)
+            for _ in range(3):
+                be.embed(o, table, toks)
+            be.sync()
+            be.reset_gpu_secs()
+            for _ in range(20):
+                be.embed(o, table, toks)
+            be.sync()
+            t = be.gpu_secs_total() / 20
+            nbytes = ntok * (dim // 256) * bb + ntok * dim * 2
+            out["embed"][f"{name}_dim4096_tokens2048"] = {"us": round(t * 1e6, 2), "GBps": round(nbytes / t / 1e9, 1),
+                                                          "frac_of_hbm_peak": round(nbytes / t / 1e9 / peak_gbs, 4)}
+            table.free()
+            o.free()
         # config 4: the 225 matmuls of one Llama-3-8B decode step (32 x {wq, wk, wv, wo, gate, up: Q4_K;
         # down: Q6_K} + output: Q6_K), back to back; norms, rope and attention are outside this path.
         layer = [(Q4K, 4096, 4096), (Q4K, 4096, 1024), (Q4K, 4096, 1024), (Q4K, 4096, 4096),

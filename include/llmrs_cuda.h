@@ -124,6 +124,28 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
 int llmrs_cuda_matmul_static_scratch(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight,
                                      const llmrs_buf *input);
 
+/* The front of the feed-forward block in one call: out = silu(gate) * up with gate = matmul(w_gate,
+ * input) and up = matmul(w_up, input), i.e. the four calls matmul, matmul, silu, mul of
+ * src/arch/llama.rs:165-168 (kernels shaders/ops.metal:762-793).  Both weights [K, N] of one type;
+ * out [N] or [N, M].  Up to 4 tokens (and where the activations fit) the decode kernel forms both
+ * dot products of an output row in one warp and writes silu(g) * u directly: one launch, nothing
+ * intermediate in memory.  Otherwise two matmuls into float32 scratch and one element-wise kernel.
+ * gate and up stay float32 until the single rounding of the output (the reference rounds each
+ * to bf16 in between). */
+int llmrs_cuda_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w_gate, const llmrs_buf *w_up,
+                              const llmrs_buf *input);
+
+/* Replaces Backend::embed (src/backend/mod.rs:25-27; metal/mod.rs:841-878, kernels
+ * shaders/ops.metal:917-965) for Q4_K / Q6_K tables: row tokens[s] of `table` ([dim, vocab], as
+ * uploaded by upload_tensor) is dequantised into column s of `out` ([dim] for one token, else
+ * [dim, n_tokens]; F32 or BF16).  `tokens` is host memory, as in the trait (tokens: &[u32]); ids
+ * are checked against the table before anything is enqueued.  The values are the float32
+ * dequantisation (the same numbers llmrs_cuda_dequantize writes), rounded once for a BF16 output.
+ * (The reference's Metal kernel for Q4_K reads its repacked blocks, whose d*sc and dmin*m were
+ * rounded to f16 at upload; this one keeps them exact.)  At most 65535 tokens per call. */
+int llmrs_cuda_embed(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *table, const uint32_t *tokens,
+                     uint32_t n_tokens);
+
 /* Multi-GPU decode matmul: this rank's rows of an N-sharded weight, with the all-gather of the
  * output slices fused into the kernel.  The reference is single-GPU and has no counterpart; the
  * sharding follows from every output row reading only its own weight row (shaders/ops.metal:249-289).

@@ -84,6 +84,8 @@ ABI = {
     "llmrs_cuda_free": (C.c_int, [_VP, _BUFP]),
     "llmrs_cuda_matmul": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_matmul_static_scratch": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
+    "llmrs_cuda_matmul_gate_up": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, _BUFP]),
+    "llmrs_cuda_embed": (C.c_int, [_VP, _BUFP, _BUFP, C.POINTER(C.c_uint32), C.c_uint32]),
     "llmrs_cuda_matmul_allgather": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_uint32, C.c_uint32, C.POINTER(_VP), _VP]),
     "llmrs_cuda_allgather_mailbox_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32]),
     "llmrs_cuda_matmul_allgather_max_tokens": (C.c_int, [C.c_uint32, C.c_uint32]),
@@ -257,6 +259,19 @@ class CudaBackend:
         self._check(self._lib.llmrs_cuda_matmul_static_scratch(self._ctx, C.byref(out._raw), C.byref(weight._raw),
                                                                C.byref(input._raw)))
 
+    def matmul_gate_up(self, out: CudaBuffer, w_gate: CudaBuffer, w_up: CudaBuffer, input: CudaBuffer) -> None:
+        """out = silu(matmul(w_gate, input)) * matmul(w_up, input): the calls matmul, matmul, silu, mul
+        of the reference's feed-forward block (src/arch/llama.rs:165-168) as one."""
+        self._check(self._lib.llmrs_cuda_matmul_gate_up(self._ctx, C.byref(out._raw), C.byref(w_gate._raw),
+                                                        C.byref(w_up._raw), C.byref(input._raw)))
+
+    def embed(self, out: CudaBuffer, table: CudaBuffer, tokens: Sequence[int]) -> None:
+        """Backend::embed (src/backend/mod.rs:25-27): out[:, i] = dequantised row tokens[i] of the
+        Q4_K / Q6_K table; `out` is [dim] for one token, else [dim, len(tokens)]."""
+        ids = np.ascontiguousarray(tokens, dtype=np.uint32).reshape(-1)
+        self._check(self._lib.llmrs_cuda_embed(self._ctx, C.byref(out._raw), C.byref(table._raw),
+                                               ids.ctypes.data_as(C.POINTER(C.c_uint32)), ids.size))
+
     def matmul_allgather(self, out: CudaBuffer, weight_shard: CudaBuffer, input: CudaBuffer, rank: int, world: int,
                          peer_mailbox: Sequence[int], step_word: int) -> None:
         """Decode matmul of this rank's weight rows with the all-gather fused into the kernel: every
@@ -285,5 +300,5 @@ class CudaBackend:
     def _unimplemented(self, *_a, **_k):
         raise NotImplementedError("only the matmul path of the Backend trait is implemented by the CUDA backend")
 
-    argmax = embed = rms_norm = rms_norm_heads = rope = attention = scatter_kv = gather = _unimplemented
+    argmax = rms_norm = rms_norm_heads = rope = attention = scatter_kv = gather = _unimplemented
     upload_u32 = silu = mul = add = _unimplemented

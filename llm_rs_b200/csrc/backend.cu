@@ -37,6 +37,8 @@ struct llmrs_ctx {
     size_t scratch_bytes = 0;
     bool pdl = true;                 // decode kernels overlap their prologue with the previous kernel's tail (LLMRS_NO_PDL=1: off)
     int gemm_split = -1;             // LLMRS_GEMM_SPLIT at creation: 0 never, 1 always, otherwise the estimate decides
+    uint32_t *tokens = nullptr;      // device copy of embed's token ids
+    size_t tokens_cap = 0;
     void *split_ws = nullptr;        // workspace of the tensor-core path's split of the last wave (zero between launches)
     uint32_t *dev_error = nullptr;   // device word: first KernelError reported by a kernel; next word: CTA counter
     std::string error;
@@ -61,6 +63,7 @@ struct llmrs_ctx {
         if (code == 0) return LLMRS_OK;
         cudaMemset(dev_error, 0, 2 * sizeof code);
         if (split_ws) cudaMemset(split_ws, 0, gemm_split_counter_bytes());     // an abandoned launch may have left counters behind
+        if (code == 7) return fail(LLMRS_ERR_ARG, "%s: embed was given a token id beyond the table", what);
         return fail(LLMRS_ERR_KERNEL, "%s: a kernel gave up a bounded wait (code %u); results are incomplete", what, code);
     }
     // Grows the scratch buffer (synchronises; never called while the stream is being captured).
@@ -214,6 +217,7 @@ int llmrs_cuda_destroy(llmrs_ctx *ctx) {
     if (ctx->dev_error) cudaFree(ctx->dev_error);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->split_ws) cudaFree(ctx->split_ws);
+    if (ctx->tokens) cudaFree(ctx->tokens);
     delete ctx;
     return LLMRS_OK;
 }
@@ -368,6 +372,120 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
                         &ctx->launches);
     }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: launch");
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w_gate, const llmrs_buf *w_up,
+                              const llmrs_buf *input) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!out || !w_gate || !w_up || !input || !out->dptr || !w_gate->dptr || !w_up->dptr || !input->dptr)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul_gate_up: null buffer");
+    const uint32_t K = w_gate->dim0, N = w_gate->dim1 ? w_gate->dim1 : 1, M = input->dim1 ? input->dim1 : 1;
+    if (w_gate->dtype != LLMRS_Q4K && w_gate->dtype != LLMRS_Q6K)
+        return ctx->fail(LLMRS_ERR_DTYPE, "matmul_gate_up: weight dtype %u is not Q4_K/Q6_K", w_gate->dtype);
+    if (w_up->dtype != w_gate->dtype || w_up->dim0 != K || (w_up->dim1 ? w_up->dim1 : 1) != N)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_gate_up: gate and up weights differ in type or shape");
+    const uint32_t want_layout = w_gate->dtype == LLMRS_Q6K ? LLMRS_LAYOUT_Q6K_SLICES : LLMRS_LAYOUT_RAW;
+    if (w_gate->layout != want_layout || w_up->layout != want_layout)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul_gate_up: weights were not created by upload_tensor");
+    if (!dense_elem_bytes(input->dtype) || !dense_elem_bytes(out->dtype))
+        return ctx->fail(LLMRS_ERR_DTYPE, "matmul_gate_up: activations must be F32 or BF16");
+    if (K % QK_K) return ctx->fail(LLMRS_ERR_SHAPE, "matmul_gate_up: in_features %u is not a multiple of 256", K);
+    if (input->dim0 != K)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_gate_up: input has %u features, weights expect %u", input->dim0, K);
+    if (out->dim0 != N || (out->dim1 ? out->dim1 : 1) != M)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_gate_up: output is [%u, %u], expected [%u, %u]", out->dim0, out->dim1, N, M);
+    if (w_gate->device != (uint32_t)ctx->device || w_up->device != (uint32_t)ctx->device ||
+        input->device != (uint32_t)ctx->device || out->device != (uint32_t)ctx->device)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul_gate_up: buffers belong to another device");
+    const bool decode = (int)M <= ctx->gemv_max_m;
+    if (decode && K > gemv_max_k())
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_gate_up: in_features %u exceeds the supported maximum %zu", K, gemv_max_k());
+    DeviceGuard guard(ctx->device);
+    cudaError_t e;
+    if (decode && gemv_gate_up_fits((int)w_gate->dtype, (int)K, (int)M)) {
+        e = ctx->begin_work();
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_gate_up: event");
+        e = launch_gemv_gate_up((int)w_gate->dtype, (const uint8_t *)w_gate->dptr, (const uint8_t *)w_up->dptr,
+                                input->dptr, (int)input->dtype, out->dptr, (int)out->dtype, (int)K, (int)N, (int)M,
+                                ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream, &ctx->launches);
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_gate_up: launch");
+        return LLMRS_OK;
+    }
+    // Two matmuls into float32 scratch behind the GEMM's own scratch, then the element-wise tail.
+    const size_t gemm_bytes = decode ? 0 : (gemm_scratch_bytes((int)K, (int)M) + 255) / 256 * 256;
+    const size_t half = ((size_t)M * N * sizeof(float) + 255) / 256 * 256;
+    e = ctx->reserve_scratch(gemm_bytes + 2 * half);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_gate_up: scratch (grow it with one call outside graph capture)");
+    float *g = (float *)((uint8_t *)ctx->scratch + gemm_bytes), *u = (float *)((uint8_t *)g + half);
+    e = ctx->begin_work();
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_gate_up: event");
+    const llmrs_buf *ws[2] = {w_gate, w_up};
+    float *dst[2] = {g, u};
+    for (int i = 0; i < 2 && e == cudaSuccess; i++) {
+        if (decode)
+            e = launch_gemv((int)ws[i]->dtype, (const uint8_t *)ws[i]->dptr, input->dptr, (int)input->dtype, dst[i],
+                            DT_F32, (int)K, (int)N, (int)M, ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream,
+                            &ctx->launches);
+        else
+            e = launch_gemm((int)ws[i]->dtype, (const uint8_t *)ws[i]->dptr, input->dptr, (int)input->dtype, dst[i],
+                            DT_F32, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws, ctx->gemm_split,
+                            ctx->dev_error, ctx->stream, &ctx->launches);
+    }
+    if (e == cudaSuccess) {
+        e = launch_silu_mul(g, u, out->dptr, (int)out->dtype, (size_t)M * N, ctx->stream);
+        ctx->launches++;
+    }
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_gate_up: launch");
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_embed(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *table, const uint32_t *tokens,
+                     uint32_t n_tokens) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!out || !table || !out->dptr || !table->dptr || (!tokens && n_tokens))
+        return ctx->fail(LLMRS_ERR_ARG, "embed: null pointer");
+    if (table->dtype != LLMRS_Q4K && table->dtype != LLMRS_Q6K)
+        return ctx->fail(LLMRS_ERR_DTYPE, "embed: table dtype %u is not Q4_K/Q6_K", table->dtype);
+    if (table->dtype == LLMRS_Q6K && table->layout != LLMRS_LAYOUT_Q6K_SLICES)
+        return ctx->fail(LLMRS_ERR_ARG, "embed: table was not created by upload_tensor");
+    if (!dense_elem_bytes(out->dtype)) return ctx->fail(LLMRS_ERR_DTYPE, "embed: output must be F32 or BF16");
+    const uint32_t K = table->dim0, vocab = table->dim1 ? table->dim1 : 1;
+    if (K % QK_K) return ctx->fail(LLMRS_ERR_SHAPE, "embed: dim %u is not a multiple of 256", K);
+    if (out->dim0 != K || (out->dim1 ? out->dim1 : 1) != (n_tokens ? n_tokens : 1))
+        return ctx->fail(LLMRS_ERR_SHAPE, "embed: output is [%u, %u], expected [%u, %u]", out->dim0, out->dim1, K, n_tokens);
+    if (n_tokens > 65535) return ctx->fail(LLMRS_ERR_SHAPE, "embed: %u tokens in one call (at most 65535)", n_tokens);
+    if (reinterpret_cast<uintptr_t>(out->dptr) & 15) return ctx->fail(LLMRS_ERR_ARG, "embed: output must be 16-byte aligned");
+    if (table->device != (uint32_t)ctx->device || out->device != (uint32_t)ctx->device)
+        return ctx->fail(LLMRS_ERR_ARG, "embed: buffers belong to another device");
+    if (n_tokens == 0) return LLMRS_OK;
+    for (uint32_t i = 0; i < n_tokens; i++)
+        if (tokens[i] >= vocab)
+            return ctx->fail(LLMRS_ERR_ARG, "embed: token %u is %u, the table has %u rows", i, tokens[i], vocab);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaSuccess;
+    if (n_tokens > ctx->tokens_cap) {            // grows outside stream capture only, like the scratch
+        cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(ctx->stream, &st);
+        if (st != cudaStreamCaptureStatusNone)
+            return ctx->fail(LLMRS_ERR_CUDA, "embed: token buffer must grow (make one call outside graph capture)");
+        e = cudaStreamSynchronize(ctx->stream);
+        if (e == cudaSuccess && ctx->tokens) e = cudaFree(ctx->tokens);
+        ctx->tokens = nullptr;
+        ctx->tokens_cap = 0;
+        const size_t cap = n_tokens < 256 ? 256 : n_tokens;
+        if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->tokens, cap * sizeof(uint32_t));
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "embed: token buffer");
+        ctx->tokens_cap = cap;
+    }
+    e = ctx->begin_work();
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "embed: event");
+    e = cudaMemcpyAsync(ctx->tokens, tokens, (size_t)n_tokens * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess)
+        e = launch_embed((int)table->dtype, (const uint8_t *)table->dptr, (int)K, vocab, ctx->tokens, (int)n_tokens,
+                         out->dptr, (int)out->dtype, ctx->dev_error, ctx->stream);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "embed: launch");
+    ctx->launches++;
     return LLMRS_OK;
 }
 

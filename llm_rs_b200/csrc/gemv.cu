@@ -25,6 +25,8 @@
 // evaluation of the reference formula the result is within ~1e-6 relative L2.
 #include "kernels.h"
 #include "llmrs_common.cuh"
+#include <type_traits>
+
 #include "pipeline.cuh"
 
 namespace llmrs {
@@ -101,6 +103,10 @@ struct GatherParams {
 
 struct GemvParams {
     GatherParams g;
+    // Fused feed-forward front (W2 != nullptr; two rows per warp only): the rows of a tile alternate
+    // between W (gate) and W2 (up), a warp owns gate row j and up row j, and writes
+    // silu(gate . x) * (up . x) as output row j (src/arch/llama.rs:165-168; shaders/ops.metal:762-793).
+    const uint8_t *W2;
     const uint8_t *W;
     const void *X;
     void *Out;
@@ -491,9 +497,11 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                 if (lane == 0) mbar_arrive_expect_tx(&full[s], bytes * RT);
                 __syncwarp();
                 if (lane < RT) {
-                    const int row = min(rt * RT + lane, p.N - 1);
+                    const bool pair = R == 2 && p.W2 != nullptr;
+                    const int row = pair ? min(rt * (RT / 2) + (lane >> 1), p.N - 1) : min(rt * RT + lane, p.N - 1);
+                    const uint8_t *src = pair && (lane & 1) ? p.W2 : p.W;
                     bulk_copy_g2s(stages + s * stage_bytes + (size_t)lane * F::CHUNK_MAX,
-                                  p.W + (size_t)row * p.row_stride + (size_t)c * F::CHUNK_MAX, bytes, &full[s]);
+                                  src + (size_t)row * p.row_stride + (size_t)c * F::CHUNK_MAX, bytes, &full[s]);
                 }
             }
         }
@@ -538,6 +546,22 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
             if (lane == 0) mbar_arrive(&empty[s]);
         }
 
+        if (R == 2 && p.W2 != nullptr) {
+            // ---- fused feed-forward front: silu(gate) * up, one output row per warp ----
+#pragma unroll
+            for (int t = 0; t < MT; t++) {
+                float g = total[0][t], u = total[R - 1][t];
+#pragma unroll
+                for (int o = 16; o; o >>= 1) {
+                    g += __shfl_xor_sync(0xffffffffu, g, o);
+                    u += __shfl_xor_sync(0xffffffffu, u, o);
+                }
+                const int out_row = rt * (RT / 2) + warp;
+                if (ok && lane == 0 && out_row < p.N && t < p.m_valid)
+                    store_out(p.Out, (size_t)t * p.N + out_row, g / (1.0f + expf(-g)) * u, p.out_bf16);
+            }
+            continue;
+        }
 #pragma unroll
         for (int r = 0; r < R; r++)
 #pragma unroll
@@ -629,7 +653,9 @@ cudaError_t launch_cfg(const GemvParams &p0, int sm_count, int want_stages, cuda
     GemvParams p = p0;
     constexpr int RT = R * NCW;
     static_assert(RT <= 32, "one producer lane per row of the tile");
-    p.n_row_tiles = (p.N + RT - 1) / RT;
+    const int out_rows_per_tile = p.W2 ? RT / 2 : RT;          // fused feed-forward front: gate and up rows alternate
+    if (p.W2 && R != 2) return cudaErrorInvalidConfiguration;
+    p.n_row_tiles = (p.N + out_rows_per_tile - 1) / out_rows_per_tile;
     p.n_chunks = (p.K / QK_K + Fmt<QT, PLANES>::CHUNK_BLOCKS - 1) / Fmt<QT, PLANES>::CHUNK_BLOCKS;
     p.stages = ring_stages<QT, MT, R, NCW, PLANES>(p.K, want_stages);
     if (p.stages < 2) return cudaErrorInvalidConfiguration;
@@ -663,7 +689,7 @@ cudaError_t launch_mt(const GemvParams &p, int sm_count, cudaStream_t s, bool *f
     constexpr int W = NCW_DEFAULT, P = PLANES_DEFAULT;
     *fits = true;
     if (ring_stages<QT, MT, 2, W, P>(p.K, 4) >= 2) return launch_cfg<QT, MT, 2, W, P>(p, sm_count, 4, s);
-    if (ring_stages<QT, MT, 1, W, P>(p.K, 4) >= 2) return launch_cfg<QT, MT, 1, W, P>(p, sm_count, 4, s);
+    if (!p.W2 && ring_stages<QT, MT, 1, W, P>(p.K, 4) >= 2) return launch_cfg<QT, MT, 1, W, P>(p, sm_count, 4, s);
     *fits = false;
     return cudaSuccess;
 }
@@ -728,6 +754,48 @@ cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype
         return launch_fmt<1>(p, M, xe, oe, sm_count, s, launches);
     }
     return cudaErrorInvalidValue;
+}
+
+// Fused feed-forward front: out[M, N] = silu(X . Wgate^T) * (X . Wup^T), both weights [K, N] of
+// one type; one launch.  Returns cudaErrorInvalidConfiguration when the two-rows-per-warp
+// configuration does not fit (large K with several tokens): the caller then runs two matmuls.
+bool gemv_gate_up_fits(int wdtype, int K, int M) {
+    if (M < 1 || M > 4 || K <= 0 || K % QK_K) return false;
+    auto fits = [&](auto qt) {
+        constexpr int QT = decltype(qt)::value;
+        switch (M) {
+            case 1: return ring_stages<QT, 1, 2, NCW_DEFAULT, PLANES_DEFAULT>(K, 4) >= 2;
+            case 2: return ring_stages<QT, 2, 2, NCW_DEFAULT, PLANES_DEFAULT>(K, 4) >= 2;
+            case 3: return ring_stages<QT, 3, 2, NCW_DEFAULT, PLANES_DEFAULT>(K, 4) >= 2;
+            default: return ring_stages<QT, 4, 2, NCW_DEFAULT, PLANES_DEFAULT>(K, 4) >= 2;
+        }
+    };
+    if (wdtype == DT_Q4K) return fits(std::integral_constant<int, 0>{});
+    if (wdtype == DT_Q6K) return fits(std::integral_constant<int, 1>{});
+    return false;
+}
+
+cudaError_t launch_gemv_gate_up(int wdtype, const uint8_t *w_gate, const uint8_t *w_up, const void *x, int x_dtype,
+                                void *out, int out_dtype, int K, int N, int M, int sm_count, bool pdl,
+                                uint32_t *err_word, cudaStream_t s, uint64_t *launches) {
+    if (!gemv_gate_up_fits(wdtype, K, M)) return cudaErrorInvalidConfiguration;
+    GemvParams p{};
+    p.pdl = pdl;
+    p.W = w_gate; p.W2 = w_up; p.X = x; p.Out = out; p.err = err_word;
+    p.K = K; p.N = N;
+    p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;
+    uint64_t n = 0;
+    cudaError_t e;
+    if (wdtype == DT_Q4K) {
+        p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
+        e = launch_fmt<0>(p, M, 0, 0, sm_count, s, &n);
+    } else {
+        p.row_stride = q6k_row_stride(K);
+        e = launch_fmt<1>(p, M, 0, 0, sm_count, s, &n);
+    }
+    if (e == cudaSuccess && n != 1) e = cudaErrorInvalidConfiguration;
+    if (launches) *launches += n;
+    return e;
 }
 
 // Largest token count (<= 4) whose staged activations fit one launch of the decode kernel.

@@ -42,6 +42,11 @@ cudaError_t launch_q6k_repack(const uint8_t *raw, uint8_t *dev, int K, int N, cu
 // Weight -> float32 [N, K], bit-exact with the reference's CPU dequantisation.
 cudaError_t launch_dequant(int wdtype, const uint8_t *w, int K, int N, float *out, cudaStream_t s);
 
+// Embedding lookup: column s of out [K, n_tokens] = dequantised row dev_tokens[s] of the table
+// ([K, vocab], as uploaded); out_dtype DT_F32 or DT_BF16.  grid.y = n_tokens <= 65535.
+cudaError_t launch_embed(int wdtype, const uint8_t *table, int K, uint32_t vocab, const uint32_t *dev_tokens,
+                         int n_tokens, void *out, int out_dtype, uint32_t *err_word, cudaStream_t s);
+
 // Decode matmul: integer dot products per scale group, float32 across groups; any M (tokens are
 // processed in passes of <= 4).  x_dtype / out_dtype are DT_F32 or DT_BF16.  err_word is a device
 // word that receives a KernelError if a bounded wait inside the kernel gives up.  *launches is
@@ -63,6 +68,16 @@ cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, i
                                   int K, int N_local, int M, int rank, int world, void *const *peer_mailbox,
                                   uint32_t *done_counter, uint32_t *step_word, int sm_count, bool pdl,
                                   uint32_t *err_word, cudaStream_t s, uint64_t *launches);
+
+// Fused feed-forward front on the decode kernel: out[M, N] = silu(X . Wgate^T) * (X . Wup^T) in one
+// launch (both weights [K, N], same type, as uploaded).  gemv_gate_up_fits() says whether the shape
+// can run that way (M <= 4 and the two-rows-per-warp ring fits beside the staged activations).
+bool gemv_gate_up_fits(int wdtype, int K, int M);
+cudaError_t launch_gemv_gate_up(int wdtype, const uint8_t *w_gate, const uint8_t *w_up, const void *x, int x_dtype,
+                                void *out, int out_dtype, int K, int N, int M, int sm_count, bool pdl,
+                                uint32_t *err_word, cudaStream_t s, uint64_t *launches);
+// out[i] = silu(gate[i]) * up[i] over n float32 values, written as out_dtype (the unfused tail).
+cudaError_t launch_silu_mul(const float *gate, const float *up, void *out, int out_dtype, size_t n, cudaStream_t s);
 
 // Largest in_features the decode kernel can stage in shared memory.
 size_t gemv_max_k();

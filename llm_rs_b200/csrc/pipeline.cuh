@@ -18,7 +18,8 @@ enum KernelError : uint32_t {
     KERR_MMA_WAIT = 3,     // a wait on tensor-core completion gave up
     KERR_TMEM_ALLOC = 4,
     KERR_GATHER_WAIT = 5,  // the fused all-gather gave up waiting for a peer's slice
-    KERR_SPLIT_WAIT = 6    // a split-K tile gave up waiting for the other CTAs' partial sums
+    KERR_SPLIT_WAIT = 6,   // a split-K tile gave up waiting for the other CTAs' partial sums
+    KERR_TOKEN_RANGE = 7   // embed: a token id beyond the table (row 0 was read instead)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {

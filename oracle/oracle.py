@@ -144,6 +144,22 @@ def dequant(dtype: int, w: np.ndarray, K: int, N: int, threads: int | None = Non
     return out
 
 
+def embed(dtype: int, w: np.ndarray, K: int, N: int, tokens, *, bf16: bool = False) -> np.ndarray:
+    """Embedding lookup (src/backend/mod.rs:25-27; shaders/ops.metal:917-965): float32
+    [len(tokens), K], row i = dequantised row tokens[i] of the [K, N] table -- the float32 values
+    of the reference's CPU dequantisation (tests/ops.rs:41-59), rounded to bf16 (round to nearest
+    even, as half::bf16::from_f32) and widened again when bf16=True."""
+    w = _check_weight(dtype, w, K, N)
+    row_bytes = (K // 256) * BLOCK_BYTES[dtype]
+    rows = np.stack([w[int(t) * row_bytes:(int(t) + 1) * row_bytes] for t in tokens]) if len(tokens) else \
+        np.empty((0, row_bytes), dtype=np.uint8)
+    out = dequant(dtype, np.ascontiguousarray(rows).reshape(-1), K, len(tokens)) if len(tokens) else \
+        np.empty((0, K), dtype=np.float32)
+    if bf16:
+        out = bf16_bits_to_f32(f32_to_bf16_bits(out)).reshape(out.shape)
+    return out
+
+
 def matmul(dtype: int, w: np.ndarray, K: int, N: int, x: np.ndarray, *, acc: str = "f64",
            rows: tuple[int, int] | None = None, threads: int | None = None, fast: bool = False) -> np.ndarray:
     """Out[M, N] = X[M, K] . W[N, K]^T.  acc="f32": the reference's sequential float

@@ -266,6 +266,85 @@ def test_wrap_torch_memory(backend):
     assert O.rel_l2(ot.cpu().numpy(), O.matmul(O.Q6K, w, K, N, x, acc="f64")) <= GEMV_TOL
 
 
+# ---------- feed-forward front: silu(gate) * up ----------
+
+def silu_mul_truth(dt, wg, wu, K, N, x):
+    g = O.matmul(dt, wg, K, N, x, acc="f64").astype(np.float64)
+    u = O.matmul(dt, wu, K, N, x, acc="f64").astype(np.float64)
+    return g / (1.0 + np.exp(-g)) * u
+
+
+@pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
+@pytest.mark.parametrize("K,N,M", [(256, 5, 1), (4096, 1000, 1), (4096, 14336, 1), (2048, 77, 3), (4096, 512, 4),
+                                   (14336, 96, 2), (14336, 64, 4), (1024, 300, 7), (4096, 256, 130)])
+def test_matmul_gate_up(backend, dt, K, N, M):
+    """One call for matmul, matmul, silu, mul (src/arch/llama.rs:165-168): fused in the decode kernel
+    up to 4 tokens, two matmuls and an element-wise kernel otherwise; same tolerance as the matmul
+    that serves that M."""
+    wg = synth.weight(dt, K, N, tid=17 * K + N)
+    wu = synth.weight(dt, K, N, tid=19 * K + N)
+    x = synth.activations(M, K, tid=4000 + M) * np.float32(0.05)        # keep gate in silu's curved range
+    out = backend.alloc([N] if M == 1 else [N, M], DType.F32)
+    backend.matmul_gate_up(out, upload_weight(backend, dt, wg, K, N), upload_weight(backend, dt, wu, K, N),
+                           upload_x(backend, x, M, K))
+    backend.sync()
+    got = backend.read_to_vec_f32(out).reshape(M, N)
+    # silu' <= 1.1 and the product rule: relative errors of gate and up add
+    assert O.rel_l2(got, silu_mul_truth(dt, wg, wu, K, N, x)) <= 2.5 * tol_for(M)
+
+
+def test_matmul_gate_up_bf16_and_errors(backend):
+    from llm_rs_b200.backend import BackendError
+    K, N = 1024, 64
+    wg, wu = synth.weight(O.Q4K, K, N, tid=1), synth.weight(O.Q4K, K, N, tid=2)
+    x = synth.activations(1, K, tid=3) * np.float32(0.05)
+    g, u = upload_weight(backend, O.Q4K, wg, K, N), upload_weight(backend, O.Q4K, wu, K, N)
+    out = backend.alloc([N], DType.BF16)
+    backend.matmul_gate_up(out, g, u, upload_x(backend, x, 1, K, True))
+    backend.sync()
+    xe = O.bf16_bits_to_f32(synth.bf16_bits(x)).reshape(1, K)
+    assert O.rel_l2(backend.read_to_vec_f32(out).reshape(1, N), silu_mul_truth(O.Q4K, wg, wu, K, N, xe)) <= 2.0 ** -8
+    other = upload_weight(backend, O.Q4K, synth.weight(O.Q4K, K, 32, tid=4), K, 32)
+    with pytest.raises(BackendError):
+        backend.matmul_gate_up(out, g, other, upload_x(backend, x, 1, K))
+
+
+# ---------- embedding lookup (Backend::embed) ----------
+
+@pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
+@pytest.mark.parametrize("K,N,toks", [
+    (256, 3, [2]), (512, 40, [7, 0, 39, 7, 13]), (4096, 1000, list(range(0, 1000, 37))),
+    (14336, 64, [63, 1, 1, 0]),
+])
+@pytest.mark.parametrize("out_bf16", [False, True])
+def test_embed_bit_exact(backend, dt, K, N, toks, out_bf16):
+    """Column s of out = dequantised row tokens[s]: the float32 values bit for bit, one
+    round-to-nearest-even for a bf16 output."""
+    w = synth.weight(dt, K, N, tid=5 * K + N)
+    table = upload_weight(backend, dt, w, K, N)
+    out = backend.alloc([K] if len(toks) == 1 else [K, len(toks)], DType.BF16 if out_bf16 else DType.F32)
+    backend.embed(out, table, toks)
+    backend.sync()
+    got = backend.read_to_vec_f32(out).reshape(len(toks), K)
+    want = O.embed(dt, w, K, N, toks, bf16=out_bf16)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_embed_errors(backend):
+    from llm_rs_b200.backend import BackendError
+    w = synth.weight(O.Q4K, 256, 4, tid=1)
+    table = upload_weight(backend, O.Q4K, w, 256, 4)
+    out = backend.alloc([256, 2], DType.F32)
+    with pytest.raises(BackendError):
+        backend.embed(out, table, [0, 4])                 # id beyond the table
+    with pytest.raises(BackendError):
+        backend.embed(out, table, [0, 1, 2])              # output holds two columns
+    backend.embed(out, table, [3, 3])                     # and the context still works
+    backend.sync()
+    got = backend.read_to_vec_f32(out).reshape(2, 256)
+    assert np.array_equal(got[0], got[1]) and np.array_equal(got[0], O.embed(O.Q4K, w, 256, 4, [3])[0])
+
+
 # ---------- GEMM on the tensor cores (M >= 5) ----------
 # Tolerance stated for this path: relative L2 <= 2e-3 against the float64 oracle.
 GEMM_TOL = 2e-3

@@ -252,3 +252,18 @@ def test_matmul_f32_is_sequential_sum():
         for i in range(256):
             acc = np.float32(acc + np.float32(W[r, i] * x[0, i]))
         assert got[0, r] == acc
+
+
+def test_embed_is_row_lookup_of_dequant():
+    """embed = rows of the dequantised table, in token order (src/backend/mod.rs:25-27)."""
+    from llm_rs_b200 import synth
+    for dt in (O.Q4K, O.Q6K):
+        K, N = 512, 40
+        w = synth.weight(dt, K, N, tid=91)
+        full = O.dequant(dt, w, K, N)
+        toks = [7, 0, 39, 7, 13]
+        got = O.embed(dt, w, K, N, toks)
+        assert got.shape == (5, K) and np.array_equal(got.view(np.uint32), full[toks].view(np.uint32))
+        gb = O.embed(dt, w, K, N, toks, bf16=True)
+        assert np.array_equal(O.f32_to_bf16_bits(gb), O.f32_to_bf16_bits(full[toks]))     # idempotent rounding
+        assert O.embed(dt, w, K, N, []).shape == (0, K)
