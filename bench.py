@@ -33,6 +33,7 @@ K_IN, N_OUT = 4096, 128256
 Q6K, Q4K = 14, 12
 BLOCK_BYTES = {Q4K: 144, Q6K: 210}
 L2_BYTES = 126e6
+FUSED_GATHER_MAX_WORDS = 1 << 18      # values one rank posts per peer and matmul, above which NCCL moves them
 
 
 def algorithmic_bytes(dtype: int, K: int, N: int, M: int, in_bytes: int = 4, out_bytes: int = 4) -> int:
@@ -365,8 +366,9 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
     }
     out = {"n_gpus": world, "note": ("linear stack only (7 matmuls per layer + output projection, bf16 activations); "
                                       "weights N-sharded, activations replicated, all-gather of every output: fused "
-                                      "into the decode kernel for M <= 4, NCCL above; no_exchange = the same matmuls "
-                                      "without the all-gather")}
+                                      "into the kernel (peer mailboxes) where a rank posts <= 256 K values per peer "
+                                      "and M <= 128, NCCL elsewhere; no_exchange = the same matmuls without the "
+                                      "all-gather")}
     for name, cfg in models.items():
         H, KV, F, V, L = cfg["hidden"], cfg["kv"], cfg["ffn"], cfg["vocab"], cfg["layers"]
         layer = [(Q4K, H, H), (Q4K, H, KV), (Q4K, H, KV), (Q4K, H, H), (Q4K, H, F), (Q4K, H, F), (Q6K, F, H)]
@@ -392,8 +394,10 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
             locals_ = {N: torch.empty(M, N // world, device=dev, dtype=torch.bfloat16) for N in dims}
             lbufs = {N: be.wrap(t.data_ptr(), shp(N // world), DType.BF16, keepalive=t) for N, t in locals_.items()}
             # the fused exchange where one launch holds all tokens' staged activations, NCCL elsewhere
-            kinds = {(dt, K) for dt, K, _ in layer + [(Q6K, H, V)]}
-            fits = {(dt, K) for dt, K in kinds if be.allgather_max_tokens(DType(dt), K) >= M}
+            # fused where the exchange is latency (few words per peer), NCCL where it is volume
+            kinds = {(dt, K, N) for dt, K, N in layer + [(Q6K, H, V)]}
+            fits = {(dt, K, N) for dt, K, N in kinds
+                    if be.allgather_max_tokens(DType(dt), K) >= M and M * (N // world) <= FUSED_GATHER_MAX_WORDS}
             fused = {N: FusedGather(be, N, M, out_dtype=torch.bfloat16) for N in dims} if fits else None
             fulls = {N: torch.empty(world, M, N // world, device=dev, dtype=torch.bfloat16) for N in dims}
 
@@ -404,7 +408,7 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
                 run_one(wout, Q6K, H, V, exchange)
 
             def run_one(w, dt, K, N, exchange):
-                if exchange and (dt, K) in fits:
+                if exchange and (dt, K, N) in fits:
                     fused[N](w, xs[K])
                 else:
                     be.matmul(lbufs[N], w, xs[K])
@@ -449,7 +453,7 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
                             "TFLOPs": round(flops_per_token * M / t / 1e12, 1),
                             "frac_of_tensor_peak_x_gpus": round(flops_per_token * M / t / 1e12 / (tf_peak * world), 4),
                             "exchange": ("fused peer stores" if fits == kinds else
-                                         "fused peer stores where one launch fits, NCCL all-gather elsewhere" if fits
+                                         "fused peer stores where a rank posts <= 256 K values per peer, NCCL all-gather elsewhere" if fits
                                          else "NCCL all-gather"),
                             "cuda_graph": graphed}
             for bfr in list(xs.values()) + list(lbufs.values()):

@@ -164,7 +164,9 @@ int llmrs_cuda_embed(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *table, con
  * has two halves used in turn, because a peer may be one call ahead.  All ranks must make the
  * same sequence of calls on one mailbox (same N_local and M every time).  No argument changes
  * from call to call, so a captured CUDA graph of the call can be replayed.
- * M <= llmrs_cuda_matmul_allgather_max_tokens(). */
+ * M <= llmrs_cuda_matmul_allgather_max_tokens().  Which kernel runs follows llmrs_cuda_matmul: the
+ * exact decode kernel up to LLMRS_GEMV_MAX_M tokens where one launch holds their staged
+ * activations, the tensor-core kernel otherwise (there N_local must be a multiple of 8). */
 int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight_shard,
                                 const llmrs_buf *input, uint32_t rank, uint32_t world, void *const *peer_mailbox,
                                 uint32_t *step_word);
@@ -172,9 +174,11 @@ int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf 
 /* Bytes of one rank's mailbox for outputs of n_total rows and `tokens` tokens. */
 size_t llmrs_cuda_allgather_mailbox_bytes(uint32_t n_total, uint32_t tokens);
 
-/* Largest number of tokens (0..4) llmrs_cuda_matmul_allgather accepts for a weight of this dtype
- * with this many input features: all tokens' staged activations must fit one launch (4 up to
- * 8192 features, fewer above).  No counterpart in the reference. */
+/* Largest number of tokens llmrs_cuda_matmul_allgather accepts for a weight of this dtype with
+ * this many input features (0 if the pair is not supported).  Above it the exchange would move
+ * more bytes than it saves in latency: run llmrs_cuda_matmul and a collective.  No counterpart in
+ * the reference. */
+#define LLMRS_ALLGATHER_MAX_TOKENS 128
 int llmrs_cuda_matmul_allgather_max_tokens(uint32_t weight_dtype, uint32_t in_features);
 
 /* Dequantises a Q4_K/Q6_K weight to float32 [N, K] in device memory `dev_out`

@@ -551,19 +551,32 @@ int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf 
     if ((uint64_t)N * world != out->dim0 || (out->dim1 ? out->dim1 : 1) != M)
         return ctx->fail(LLMRS_ERR_SHAPE, "matmul_allgather: output is [%u, %u], expected [%u ranks x %u rows, %u]",
                          out->dim0, out->dim1, world, N, M);
-    const int max_m = gemv_single_launch_max_tokens((int)weight_shard->dtype, (int)K);
-    if ((int)M > max_m)
-        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_allgather: %u tokens; with %u input features the fused kernel "
-                                          "serves at most %d (use matmul + a collective above that)", M, K, max_m);
+    // up to gemv_max_m tokens, where one launch of the decode kernel holds them: exact kernel;
+    // otherwise the tensor-core kernel, whose epilogue runs the same mailbox exchange
+    const bool decode = (int)M <= ctx->gemv_max_m && (int)M <= gemv_single_launch_max_tokens((int)weight_shard->dtype, (int)K);
+    if (!decode && M > LLMRS_ALLGATHER_MAX_TOKENS)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_allgather: %u tokens; the fused exchange serves at most %d "
+                                          "(use matmul + a collective above that)", M, LLMRS_ALLGATHER_MAX_TOKENS);
+    if (!decode && N % 8)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_allgather: %u rows per rank; the tensor-core path needs a multiple of 8", N);
     for (uint32_t d = 0; d < world; d++)
         if (!peer_mailbox[d]) return ctx->fail(LLMRS_ERR_ARG, "matmul_allgather: null mailbox pointer");
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: event");
-    e = launch_gemv_allgather((int)weight_shard->dtype, (const uint8_t *)weight_shard->dptr, input->dptr,
-                              (int)input->dtype, out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, (int)rank,
-                              (int)world, peer_mailbox, ctx->dev_error + 1, step_word, ctx->sm_count, ctx->pdl,
-                              ctx->dev_error, ctx->stream, &ctx->launches);
+    if (decode) {
+        e = launch_gemv_allgather((int)weight_shard->dtype, (const uint8_t *)weight_shard->dptr, input->dptr,
+                                  (int)input->dtype, out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, (int)rank,
+                                  (int)world, peer_mailbox, ctx->dev_error + 1, step_word, ctx->sm_count, ctx->pdl,
+                                  ctx->dev_error, ctx->stream, &ctx->launches);
+    } else {
+        e = ctx->reserve_scratch(gemm_scratch_bytes((int)K, (int)M));
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: scratch (grow it with one call outside graph capture)");
+        const GemmGather gg{(int)world, (int)rank, peer_mailbox, ctx->dev_error + 1, step_word};
+        e = launch_gemm((int)weight_shard->dtype, (const uint8_t *)weight_shard->dptr, input->dptr, (int)input->dtype,
+                        out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws,
+                        ctx->gemm_split, ctx->dev_error, ctx->stream, &ctx->launches, &gg);
+    }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: launch");
     return LLMRS_OK;
 }
@@ -573,7 +586,8 @@ size_t llmrs_cuda_allgather_mailbox_bytes(uint32_t n_total, uint32_t tokens) {
 }
 
 int llmrs_cuda_matmul_allgather_max_tokens(uint32_t weight_dtype, uint32_t in_features) {
-    return gemv_single_launch_max_tokens((int)weight_dtype, (int)in_features);
+    if ((weight_dtype != LLMRS_Q4K && weight_dtype != LLMRS_Q6K) || in_features == 0 || in_features % QK_K) return 0;
+    return LLMRS_ALLGATHER_MAX_TOKENS;
 }
 
 int llmrs_cuda_dequantize(llmrs_ctx *ctx, const llmrs_buf *weight, float *dev_out) {

@@ -68,6 +68,16 @@ struct GemmParams {
     int split;
     uint32_t *ws_counters;    // [2 * sm_count] zero between launches: arrivals / deposits per tail tile
     float *ws_slots;          // [2 * sm_count] partial tiles of TILE_ROWS x TN floats, token-major
+    // Fused all-gather of an N-sharded matmul (world > 1), the protocol of the decode kernel: this
+    // rank's rows are rows [row_offset, row_offset + N) of an n_total-row output; every result is
+    // stored locally and posted to each peer as one 8-byte word {value as float bits, call number}
+    // in that peer's mailbox ([2 halves][world senders][M][N] words); before the kernel ends its
+    // epilogue warps copy the words addressed to this rank into the local output, polling (bounded)
+    // until each carries this call's number.  No fences, no flags.
+    uint2 *peer_box[8];
+    uint32_t *done_counter, *step_word;
+    size_t half_words;
+    int world, rank, n_total, row_offset;
 };
 
 // ---- work schedule -----------------------------------------------------------------------------
@@ -629,6 +639,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
         constexpr int EPI_THREADS = EPI_WARPS * 32;
         uint32_t tcount = 0;
         bool dead = false;                                      // a wait gave up: no more memory traffic, barriers only
+        const bool gather = p.world > 1;
+        const uint32_t gather_step = gather ? *reinterpret_cast<volatile uint32_t *>(p.step_word) + 1u : 0u;
         UnitIter ui;
         Unit u;
         for (; !dead && ui.next(sc, u); tcount++) {
@@ -682,8 +694,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
             const bool o_bf16 = deposit ? false : (p.out_bf16 != 0);
             const int esz = o_bf16 ? 2 : 4;
             uint8_t *o_ptr = (uint8_t *)p.Out;
-            size_t o_stride = (size_t)p.N;                      // elements between tokens
-            int tok_base = t0, row_base = n0 + 32 * quarter, tok_lim = p.M, row_lim = p.N;
+            size_t o_stride = (size_t)p.n_total;                // elements between tokens (n_total = N unless sharded)
+            int tok_base = t0, row_base = p.row_offset + n0 + 32 * quarter, tok_lim = p.M, row_lim = p.row_offset + p.N;
             if (deposit) {
                 const int k = sc.tail_a >= tb ? 0 : 1;          // first or last piece of this CTA's range
                 o_ptr = (uint8_t *)(p.ws_slots + (size_t)(2 * blockIdx.x + k) * (TILE_ROWS * TN));
@@ -746,14 +758,56 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                         if (tok < tok_lim && row < row_lim) {
                             const uint4 d = *reinterpret_cast<const uint4 *>(stg + (size_t)tl * 32 * esz + vv * 16);
                             *reinterpret_cast<uint4 *>(o_ptr + ((size_t)tok * o_stride + row) * esz) = d;
+                            if (gather && !deposit) {            // the same values, as words, to every peer's mailbox
+                                float f[8];
+                                const uint32_t w4[4] = {d.x, d.y, d.z, d.w};
+                                int nv;
+                                if (o_bf16) {
+                                    nv = 8;
+#pragma unroll
+                                    for (int j = 0; j < 4; j++) {
+                                        f[2 * j] = __uint_as_float(w4[j] << 16);
+                                        f[2 * j + 1] = __uint_as_float(w4[j] & 0xFFFF0000u);
+                                    }
+                                } else {
+                                    nv = 4;
+#pragma unroll
+                                    for (int j = 0; j < 4; j++) f[j] = __uint_as_float(w4[j]);
+                                }
+                                const size_t word = (gather_step & 1u) * p.half_words +
+                                                    ((size_t)p.rank * p.M + tok) * p.N + (row - p.row_offset);
+                                for (int dd = 0; dd < p.world; dd++) {
+                                    if (dd == p.rank) continue;
+                                    uint2 *box = p.peer_box[dd] + word;
+                                    for (int j = 0; j < nv; j += 2)
+                                        asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(box + j),
+                                                     "r"(__float_as_uint(f[j])), "r"(gather_step),
+                                                     "r"(__float_as_uint(f[j + 1])), "r"(gather_step) : "memory");
+                                }
+                            }
                         }
                     }
                 } else {
                     for (int tl = 0; tl < GT; tl++) {
                         const int tok = tok_base + g0 + tl, row = row_base + lane;
                         if (tok < tok_lim && row < row_lim) {
-                            if (o_bf16) ((uint16_t *)o_ptr)[(size_t)tok * o_stride + row] = reinterpret_cast<const uint16_t *>(stg)[tl * 32 + lane];
-                            else ((float *)o_ptr)[(size_t)tok * o_stride + row] = reinterpret_cast<const float *>(stg)[tl * 32 + lane];
+                            float fv;
+                            if (o_bf16) {
+                                const uint16_t hb = reinterpret_cast<const uint16_t *>(stg)[tl * 32 + lane];
+                                ((uint16_t *)o_ptr)[(size_t)tok * o_stride + row] = hb;
+                                fv = __uint_as_float((uint32_t)hb << 16);
+                            } else {
+                                fv = reinterpret_cast<const float *>(stg)[tl * 32 + lane];
+                                ((float *)o_ptr)[(size_t)tok * o_stride + row] = fv;
+                            }
+                            if (gather && !deposit) {
+                                const size_t word = (gather_step & 1u) * p.half_words +
+                                                    ((size_t)p.rank * p.M + tok) * p.N + (row - p.row_offset);
+                                for (int dd = 0; dd < p.world; dd++)
+                                    if (dd != p.rank)
+                                        asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(p.peer_box[dd] + word),
+                                                     "r"(__float_as_uint(fv)), "r"(gather_step) : "memory");
+                            }
                         }
                     }
                 }
@@ -770,6 +824,56 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                         p.ws_counters[2 * tt] = 0;
                         p.ws_counters[2 * tt + 1] = 0;
                     }
+                }
+            }
+        }
+        if (gather) {
+            // ---- collect the other ranks' slices from this rank's mailbox ----
+            const uint2 *box = p.peer_box[p.rank] + (gather_step & 1u) * p.half_words;
+            const size_t per_src = (size_t)p.M * p.N;                    // words one sender posts
+            const size_t remote = (size_t)(p.world - 1) * per_src;
+            const int et = ew * 32 + lane;
+            // UNPACK words in flight per thread: a batch costs one trip to L2; only words that had not
+            // landed yet are polled again.
+            constexpr int UNPACK = 8;
+            const size_t stride = (size_t)gridDim.x * EPI_THREADS;
+            bool late = dead;
+            for (size_t i0 = (size_t)blockIdx.x * EPI_THREADS + et; i0 < remote && !late; i0 += UNPACK * stride) {
+                uint2 got[UNPACK];
+#pragma unroll
+                for (int b = 0; b < UNPACK; b++) {
+                    const size_t i = i0 + b * stride;
+                    if (i < remote) {
+                        const int q = (int)(i / per_src);
+                        got[b] = mailbox_load(box + (size_t)(q < p.rank ? q : q + 1) * per_src + (i - (size_t)q * per_src));
+                    }
+                }
+#pragma unroll
+                for (int b = 0; b < UNPACK; b++) {
+                    const size_t i = i0 + b * stride;
+                    if (i >= remote || late) continue;
+                    const int q = (int)(i / per_src);
+                    const size_t rem = i - (size_t)q * per_src;
+                    const int src = q < p.rank ? q : q + 1;
+                    const int tok = (int)(rem / p.N), row = (int)(rem - (size_t)tok * p.N);
+                    if (got[b].y != gather_step &&
+                        !mailbox_wait(box + (size_t)src * per_src + rem, gather_step, 1u << 25, got[b])) {
+                        report_error(p.err, KERR_GATHER_WAIT);
+                        late = true;
+                        continue;
+                    }
+                    const size_t o = (size_t)tok * p.n_total + (size_t)src * p.N + row;
+                    if (p.out_bf16) ((__nv_bfloat16 *)p.Out)[o] = __float2bfloat16_rn(__uint_as_float(got[b].x));
+                    else ((float *)p.Out)[o] = __uint_as_float(got[b].x);
+                }
+            }
+            // the last CTA to get here advances the call number for the next launch
+            named_barrier_sync(2, EPI_THREADS);
+            if (ew == 0 && lane == 0) {
+                const uint32_t ticket = atomicAdd(p.done_counter, 1u);
+                if (ticket == gridDim.x - 1) {
+                    *p.done_counter = 0;
+                    *p.step_word = gather_step;
                 }
             }
         }
@@ -878,6 +982,7 @@ cudaError_t launch_tn(const GemmParams &p, const void *x_f16, cudaStream_t s) {
         const int tail_blocks = (n_tiles % p.sm_count) * (p.K / QK_K);
         if (n_tiles < p.sm_count) grid = tail_blocks < p.sm_count ? tail_blocks : p.sm_count;
     }
+    if (q.world > 1) grid = p.sm_count;      // CTAs without a tile still take their share of the mailbox
     kern<<<grid, GEMM_THREADS, smem, s>>>(tmap, q);
     return cudaGetLastError();
 }
@@ -905,7 +1010,7 @@ size_t gemm_split_workspace_bytes(int sms) {
 
 cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                         int K, int N, int M, void *scratch, void *split_ws, int split_mode, uint32_t *err_word,
-                        cudaStream_t s, uint64_t *launches) {
+                        cudaStream_t s, uint64_t *launches, const GemmGather *gather) {
     if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
     if (!scratch) return cudaErrorInvalidValue;
     __half *x_f16 = (__half *)scratch;
@@ -918,6 +1023,13 @@ cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype
     p.W = w; p.Out = out; p.err = err_word; p.K = K; p.N = N; p.M = M; p.out_bf16 = out_dtype == DT_BF16;
     p.tok_scale = tok_scale;
     p.split = split_mode;          // launch_tn turns the mode into the decision
+    p.n_total = N;
+    if (gather && gather->world > 1) {
+        p.world = gather->world; p.rank = gather->rank; p.n_total = N * gather->world; p.row_offset = gather->rank * N;
+        p.done_counter = gather->done_counter; p.step_word = gather->step_word;
+        p.half_words = (size_t)gather->world * M * N;
+        for (int d = 0; d < gather->world; d++) p.peer_box[d] = (uint2 *)gather->peer_mailbox[d];
+    }
     int dev = 0;
     e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&p.sm_count, cudaDevAttrMultiProcessorCount, dev);
@@ -978,7 +1090,7 @@ cudaError_t launch_gemm_static_scratch(int wdtype, const uint8_t *w, const void 
     if (e != cudaSuccess) return e;
     // Nothing in the scratch has to start at zero: the conversion kernel rewrites every f16
     // activation and every token scale the GEMM of this call reads.
-    return launch_gemm(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, scratch, nullptr, 0, err_word, s, launches);
+    return launch_gemm(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, scratch, nullptr, 0, err_word, s, launches, nullptr);
 }
 
 }  // namespace llmrs

@@ -591,23 +591,35 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
         const uint2 *box = p.g.peer_box[p.g.rank] + (gather_step & 1u) * p.g.half_words;
         const int per_src = p.m_valid * p.N;                             // words one sender posts
         const int remote = (p.g.world - 1) * per_src;
+        // A thread takes words i, i + stride, ...; it has UNPACK of them in flight at a time, so a
+        // batch costs one trip to L2, and polls again only the words that had not landed yet.
+        constexpr int UNPACK = 8;
+        const int stride = gridDim.x * (NCW * 32);
         bool late = false;
-        for (int i = blockIdx.x * (NCW * 32) + threadIdx.x; i < remote && !late; i += gridDim.x * (NCW * 32)) {
-            const int q = i / per_src, rem = i - q * per_src;
-            const int src = q < p.g.rank ? q : q + 1;
-            const int t = rem / p.N, row = rem - t * p.N;
-            const uint2 *w = box + (size_t)src * per_src + rem;
-            uint32_t val = 0, tag = 0;
-            for (uint32_t spin = 0; spin < GATHER_WAIT_LIMIT; spin++) {
-                asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(val), "=r"(tag) : "l"(w) : "memory");
-                if (tag == gather_step) break;
-                __nanosleep(32);
+        for (int i0 = blockIdx.x * (NCW * 32) + threadIdx.x; i0 < remote && !late; i0 += UNPACK * stride) {
+            uint2 got[UNPACK];
+#pragma unroll
+            for (int b = 0; b < UNPACK; b++) {
+                const int i = i0 + b * stride;
+                if (i < remote) {
+                    const int q = i / per_src, rem = i - q * per_src;
+                    got[b] = mailbox_load(box + (size_t)(q < p.g.rank ? q : q + 1) * per_src + rem);
+                }
             }
-            if (tag != gather_step) {
-                report_error(p.err, KERR_GATHER_WAIT);
-                late = true;
-            } else {
-                store_out(p.Out, (size_t)t * p.g.n_total + (size_t)src * p.N + row, __uint_as_float(val), p.out_bf16);
+#pragma unroll
+            for (int b = 0; b < UNPACK; b++) {
+                const int i = i0 + b * stride;
+                if (i >= remote || late) continue;
+                const int q = i / per_src, rem = i - q * per_src;
+                const int src = q < p.g.rank ? q : q + 1;
+                const int t = rem / p.N, row = rem - t * p.N;
+                if (got[b].y != gather_step &&
+                    !mailbox_wait(box + (size_t)src * per_src + rem, gather_step, GATHER_WAIT_LIMIT, got[b])) {
+                    report_error(p.err, KERR_GATHER_WAIT);
+                    late = true;
+                    continue;
+                }
+                store_out(p.Out, (size_t)t * p.g.n_total + (size_t)src * p.N + row, __uint_as_float(got[b].x), p.out_bf16);
             }
         }
         if (threadIdx.x == 0) LLMRS_GTRACE(1);

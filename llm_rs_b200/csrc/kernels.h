@@ -92,12 +92,20 @@ int gemv_single_launch_max_tokens(int wdtype, int K);
 // caller and left zeroed by every launch; with it the kernel may cut the tiles of the last,
 // partial wave along K so that every SM works until the end (split_mode: -1 = a cost estimate
 // decides, 0 = never, 1 = whenever there is a partial wave).  One launch at a time per workspace.
+// `gather` (optional, world > 1): this call computes one rank's rows of an N-sharded matmul; `out` is
+// then the rank's full [M, N * world] result and the all-gather runs inside the kernel through the
+// peers' mailboxes, exactly as in launch_gemv_allgather (same mailbox size and layout).
+struct GemmGather {
+    int world, rank;
+    void *const *peer_mailbox;
+    uint32_t *done_counter, *step_word;
+};
 size_t gemm_scratch_bytes(int K, int M);
 size_t gemm_split_workspace_bytes(int sms);
 size_t gemm_split_counter_bytes();      // the leading bytes of the workspace that must be zero
 cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                         int K, int N, int M, void *scratch, void *split_ws, int split_mode, uint32_t *err_word,
-                        cudaStream_t s, uint64_t *launches);
+                        cudaStream_t s, uint64_t *launches, const GemmGather *gather = nullptr);
 
 // The same GEMM with its scratch in a fixed 8 MiB device array that is part of the library image:
 // no allocation on this path.  `device` must be the current device; the first call on a device

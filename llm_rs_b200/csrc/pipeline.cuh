@@ -90,4 +90,21 @@ __device__ __forceinline__ void report_error(uint32_t *err_word, uint32_t code) 
     if (err_word) atomicCAS(err_word, 0u, code);
 }
 
+// Mailbox word {value, tag} of the fused all-gather: one relaxed system-scope 8-byte load (the
+// writer is another GPU; an aligned 8-byte store arrives whole).
+__device__ __forceinline__ uint2 mailbox_load(const uint2 *w) {
+    uint2 r;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(w) : "memory");
+    return r;
+}
+// Polls until the word carries `tag`; false after `limit` polls 32 ns apart.
+__device__ __forceinline__ bool mailbox_wait(const uint2 *w, uint32_t tag, uint32_t limit, uint2 &out) {
+    for (uint32_t spin = 0; spin < limit; spin++) {
+        out = mailbox_load(w);
+        if (out.y == tag) return true;
+        __nanosleep(32);
+    }
+    return false;
+}
+
 }  // namespace llmrs
