@@ -125,6 +125,41 @@ def cpu_baseline(dtype: int, K: int, N: int, M: int, budget_s: float, rows: int 
                                 f"dequantise-then-dot over all rows, OpenMP over rows, -O2 -march=native"}
 
 
+def cpu_baselines_other_configs():
+    """The same CPU path on config 1 (the case the reference's own CPU code runs: Q4_K 4096 x 4096, one
+    token; once as its test computes it -- one thread, dequantise the row, sequential float sum,
+    tests/ops.rs:116-136 -- and once on all cores) and on the smallest case of config 3 (Q4_K
+    4096 -> 14336 at 128 tokens, a sample of 1024 output rows, scaled linearly to all rows)."""
+    from llm_rs_b200 import synth
+    from oracle import oracle as O
+    threads = len(os.sched_getaffinity(0))
+    out = {}
+    K, N = 4096, 4096
+    w, x = synth.weight(Q4K, K, N, tid=2), synth.activations(1, K, tid=3)
+
+    def time_it(fn, budget):
+        fn()
+        t0, reps = time.perf_counter(), 0
+        while time.perf_counter() - t0 < budget and reps < 500:
+            fn()
+            reps += 1
+        return (time.perf_counter() - t0) / reps
+
+    t = time_it(lambda: O.matmul(Q4K, w, K, N, x, acc="f32", threads=1), 1.5)
+    out["config1_q4k_4096x4096_m1_one_thread_as_the_reference_test"] = {
+        "ms": round(t * 1e3, 3), "GBps": round(algorithmic_bytes(Q4K, K, N, 1) / t / 1e9, 3), "cores": 1}
+    t = time_it(lambda: O.matmul(Q4K, w, K, N, x, fast=True, threads=threads), 1.5)
+    out["config1_q4k_4096x4096_m1_all_cores"] = {
+        "ms": round(t * 1e3, 3), "GBps": round(algorithmic_bytes(Q4K, K, N, 1) / t / 1e9, 3), "cores": threads}
+    K, N, M, rows = 4096, 14336, 128, 1024
+    w, x = synth.weight(Q4K, K, rows, tid=4), synth.activations(M, K, tid=5)
+    t = time_it(lambda: O.matmul(Q4K, w, K, rows, x, fast=True, threads=threads), 2.0) * (N / rows)
+    out["config3_q4k_4096x14336_m128_all_cores"] = {
+        "ms": round(t * 1e3, 2), "TFLOPs": round(2.0 * M * K * N / t / 1e12, 4), "cores": threads,
+        "sample": f"{rows} of {N} rows, scaled linearly"}
+    return out
+
+
 def run_reference(args, rank: int, world: int):
     """--impl reference: the reference's CPU implementation of the op (its Rust test code, restated in
     C: oracle/llmrs_oracle.c; the Rust/Metal original cannot be built on this box) on the host cores."""
@@ -335,6 +370,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if world == 1 and not args.no_cpu_baseline:
         gbs, per_s, info = cpu_baseline(Q6K, K_IN, N_OUT, M, budget_s=10.0)
         line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", **info}
+        line["cpu_baseline"]["other_configs"] = cpu_baselines_other_configs()
     if multi is not None:
         line["extra"] = multi
     if world == 1 and not args.no_extra:

@@ -15,7 +15,7 @@
 //              measured 42 % busy.
 //   warp  8    one lane issues the TMA tensor copy of the step's tokens x 64 f16 activation tile
 //              (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill past the last token).
-//   warp  9    allocates TMEM; one lane issues tcgen05.mma (kind::f16, f16 x bf16 -> fp32,
+//   warp  9    allocates TMEM; one lane issues tcgen05.mma (kind::f16, f16 x f16 -> fp32,
 //              M=128, N=tokens, K=16, four per step) with the accumulator in TMEM, and
 //              tcgen05.commit to hand shared-memory stages back and to publish the accumulator.
 //   warps 10-13 epilogue: tcgen05.ld -> token scale -> global, overlapping the next tile's K loop
@@ -159,16 +159,8 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// D[tmem] (+)= A[smem desc] * B[smem desc]; accumulate = 0 overwrites D.
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Same with the A operand in tensor memory (lane = row, each 32-bit column = two K-consecutive f16).
+// D[tmem] (+)= A * B; accumulate = 0 overwrites D.  The A operand lives in tensor memory
+// (lane = row, each 32-bit column = two K-consecutive f16), B in shared memory.
 __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                             uint32_t accumulate) {
     asm volatile(
@@ -227,12 +219,6 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 // M >> 4 at bit 24.
 __host__ __device__ constexpr uint32_t umma_idesc_f16(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
 }
 
 // Two floats -> packed f16x2 (round to nearest even, clamped to +-65504), first value in the low half.
