@@ -628,34 +628,45 @@ def extra_measurements(be_factory, stream, peak_gbs):
                   14336: be.upload_tensor(TensorView("x", DType.BF16, shp(14336), synth.bf16_bits(synth.activations(M, 14336))))}
             outs = {n: be.alloc(shp(n), DType.BF16) for n in (4096, 1024, 14336, 128256)}
 
-            def step():
+            def step(one_call_ffn=False):
                 for l in range(32):
                     ws = sets[l % n_layer_sets]
-                    for (dt, K, N), wb in zip(layer, ws):
-                        be.matmul(outs[N], wb, xs[K])
+                    for i, ((dt, K, N), wb) in enumerate(zip(layer, ws)):
+                        if one_call_ffn and i == 4:          # gate and up (and silu, mul) as one call
+                            be.matmul_gate_up(outs[N], ws[4], ws[5], xs[K])
+                        elif not (one_call_ffn and i == 5):
+                            be.matmul(outs[N], wb, xs[K])
                 be.matmul(outs[128256], wout, xs[4096])
-            for _ in range(2):
-                step()
-            be.sync()
-            # the 225 launches are captured once in a CUDA graph and replayed (matmul only enqueues)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                step()
-            graph.replay()
-            stream.synchronize()
-            reps = 10
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for _ in range(reps):
+
+            def timed_graph(fn):
+                for _ in range(2):
+                    fn()
+                be.sync()
+                # the launches are captured once in a CUDA graph and replayed (matmul only enqueues)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    fn()
                 graph.replay()
-            e1.record(stream)
-            stream.synchronize()
-            t = e0.elapsed_time(e1) * 1e-3 / reps
-            del graph
+                stream.synchronize()
+                reps = 10
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(reps):
+                    graph.replay()
+                e1.record(stream)
+                stream.synchronize()
+                return e0.elapsed_time(e1) * 1e-3 / reps
+
+            t = timed_graph(step)
+            t_ffn = timed_graph(lambda: step(True))
             out["decode_stack"][f"m{M}"] = {"ms_per_step": round(t * 1e3, 4), "tok_per_s": round(M / t, 1),
                                             "weight_GBps": round(weight_bytes / t / 1e9, 1),
                                             "frac_of_hbm_peak": round(weight_bytes / t / 1e9 / peak_gbs, 4),
-                                            "matmuls_per_step": 225}
+                                            "matmuls_per_step": 225,
+                                            "with_gate_up_as_one_call": {
+                                                "ms_per_step": round(t_ffn * 1e3, 4), "tok_per_s": round(M / t_ffn, 1),
+                                                "frac_of_hbm_peak": round(weight_bytes / t_ffn / 1e9 / peak_gbs, 4),
+                                                "calls_per_step": 193}}
             for b in list(xs.values()) + list(outs.values()):
                 b.free()
         out["decode_stack"]["note"] = ("linear stack only (225 matmuls, bf16 activations), one CUDA graph per step; "

@@ -124,6 +124,24 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
 int llmrs_cuda_matmul_static_scratch(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight,
                                      const llmrs_buf *input);
 
+/* Replace Backend::silu / mul / add (src/backend/mod.rs:76-78; shaders/ops.metal:762-793):
+ * silu in place, out = a * b, out = a + b over buffers of equal element count (F32 or BF16 each);
+ * float32 arithmetic, one rounding to the output type. */
+int llmrs_cuda_silu(llmrs_ctx *ctx, llmrs_buf *x);
+int llmrs_cuda_mul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *a, const llmrs_buf *b);
+int llmrs_cuda_add(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *a, const llmrs_buf *b);
+
+/* Replaces Backend::rms_norm (src/backend/mod.rs:36-38; shaders/ops.metal:970-1003): every column
+ * of input [dim] / [dim, seq_len] is scaled by rsqrt(mean(v^2) + eps) and by the float32 weight[dim]:
+ * out = (v * inv_rms) * weight. */
+int llmrs_cuda_rms_norm(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *input, const llmrs_buf *weight, float eps);
+
+/* Replaces Backend::argmax (src/backend/mod.rs:21-23; shaders/ops.metal:803-835): index of the
+ * largest logit, computed on the device; the call completes the stream, like the reference's
+ * (metal/mod.rs:836).  On ties the smallest index wins (the reference's tree reduction leaves
+ * the choice among equal maxima to its thread layout). */
+int llmrs_cuda_argmax(llmrs_ctx *ctx, const llmrs_buf *logits, uint32_t *index);
+
 /* The front of the feed-forward block in one call: out = silu(gate) * up with gate = matmul(w_gate,
  * input) and up = matmul(w_up, input), i.e. the four calls matmul, matmul, silu, mul of
  * src/arch/llama.rs:165-168 (kernels shaders/ops.metal:762-793).  Both weights [K, N] of one type;

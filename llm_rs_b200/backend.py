@@ -84,6 +84,11 @@ ABI = {
     "llmrs_cuda_free": (C.c_int, [_VP, _BUFP]),
     "llmrs_cuda_matmul": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_matmul_static_scratch": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
+    "llmrs_cuda_silu": (C.c_int, [_VP, _BUFP]),
+    "llmrs_cuda_mul": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
+    "llmrs_cuda_add": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
+    "llmrs_cuda_rms_norm": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_float]),
+    "llmrs_cuda_argmax": (C.c_int, [_VP, _BUFP, C.POINTER(C.c_uint32)]),
     "llmrs_cuda_matmul_gate_up": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_embed": (C.c_int, [_VP, _BUFP, _BUFP, C.POINTER(C.c_uint32), C.c_uint32]),
     "llmrs_cuda_matmul_allgather": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_uint32, C.c_uint32, C.POINTER(_VP), _VP]),
@@ -259,6 +264,27 @@ class CudaBackend:
         self._check(self._lib.llmrs_cuda_matmul_static_scratch(self._ctx, C.byref(out._raw), C.byref(weight._raw),
                                                                C.byref(input._raw)))
 
+    def silu(self, x: CudaBuffer) -> None:
+        """Backend::silu (src/backend/mod.rs:76): in place."""
+        self._check(self._lib.llmrs_cuda_silu(self._ctx, C.byref(x._raw)))
+
+    def mul(self, out: CudaBuffer, a: CudaBuffer, b: CudaBuffer) -> None:
+        self._check(self._lib.llmrs_cuda_mul(self._ctx, C.byref(out._raw), C.byref(a._raw), C.byref(b._raw)))
+
+    def add(self, out: CudaBuffer, a: CudaBuffer, b: CudaBuffer) -> None:
+        self._check(self._lib.llmrs_cuda_add(self._ctx, C.byref(out._raw), C.byref(a._raw), C.byref(b._raw)))
+
+    def rms_norm(self, out: CudaBuffer, input: CudaBuffer, weight: CudaBuffer, eps: float) -> None:
+        """Backend::rms_norm (src/backend/mod.rs:36-38); `weight` is an F32 buffer of dim values."""
+        self._check(self._lib.llmrs_cuda_rms_norm(self._ctx, C.byref(out._raw), C.byref(input._raw),
+                                                  C.byref(weight._raw), float(eps)))
+
+    def argmax(self, logits: CudaBuffer) -> int:
+        """Backend::argmax (src/backend/mod.rs:21-23): computed on the device, four bytes come back."""
+        v = C.c_uint32()
+        self._check(self._lib.llmrs_cuda_argmax(self._ctx, C.byref(logits._raw), C.byref(v)))
+        return int(v.value)
+
     def matmul_gate_up(self, out: CudaBuffer, w_gate: CudaBuffer, w_up: CudaBuffer, input: CudaBuffer) -> None:
         """out = silu(matmul(w_gate, input)) * matmul(w_up, input): the calls matmul, matmul, silu, mul
         of the reference's feed-forward block (src/arch/llama.rs:165-168) as one."""
@@ -300,5 +326,5 @@ class CudaBackend:
     def _unimplemented(self, *_a, **_k):
         raise NotImplementedError("only the matmul path of the Backend trait is implemented by the CUDA backend")
 
-    argmax = rms_norm = rms_norm_heads = rope = attention = scatter_kv = gather = _unimplemented
-    upload_u32 = silu = mul = add = _unimplemented
+    rms_norm_heads = rope = attention = scatter_kv = gather = _unimplemented
+    upload_u32 = _unimplemented

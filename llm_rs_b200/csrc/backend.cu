@@ -37,6 +37,7 @@ struct llmrs_ctx {
     size_t scratch_bytes = 0;
     bool pdl = true;                 // decode kernels overlap their prologue with the previous kernel's tail (LLMRS_NO_PDL=1: off)
     int gemm_split = -1;             // LLMRS_GEMM_SPLIT at creation: 0 never, 1 always, otherwise the estimate decides
+    uint32_t *argmax_out = nullptr;  // device word argmax writes its result to
     uint32_t *tokens = nullptr;      // device copy of embed's token ids
     size_t tokens_cap = 0;
     void *split_ws = nullptr;        // workspace of the tensor-core path's split of the last wave (zero between launches)
@@ -196,6 +197,7 @@ int llmrs_cuda_create(int device, void *stream, llmrs_ctx **out) {
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_end);
     if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->dev_error, 2 * sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->dev_error, 0, 2 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->argmax_out, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->split_ws, gemm_split_workspace_bytes(ctx->sm_count));
     if (e == cudaSuccess) e = cudaMemset(ctx->split_ws, 0, gemm_split_counter_bytes());
     if (e != cudaSuccess) {
@@ -218,6 +220,7 @@ int llmrs_cuda_destroy(llmrs_ctx *ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->split_ws) cudaFree(ctx->split_ws);
     if (ctx->tokens) cudaFree(ctx->tokens);
+    if (ctx->argmax_out) cudaFree(ctx->argmax_out);
     delete ctx;
     return LLMRS_OK;
 }
@@ -372,6 +375,71 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
                         &ctx->launches);
     }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: launch");
+    return LLMRS_OK;
+}
+
+static size_t buf_elems(const llmrs_buf *b) { return (size_t)b->dim0 * (b->dim1 ? b->dim1 : 1); }
+
+static int elementwise(llmrs_ctx *ctx, const char *name, int op, llmrs_buf *out, const llmrs_buf *a, const llmrs_buf *b) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!out || !a || !out->dptr || !a->dptr || (op && (!b || !b->dptr))) return ctx->fail(LLMRS_ERR_ARG, "%s: null buffer", name);
+    if (!dense_elem_bytes(out->dtype) || !dense_elem_bytes(a->dtype) || (op && !dense_elem_bytes(b->dtype)))
+        return ctx->fail(LLMRS_ERR_DTYPE, "%s: buffers must be F32 or BF16", name);
+    const size_t n = buf_elems(out);
+    if (buf_elems(a) != n || (op && buf_elems(b) != n)) return ctx->fail(LLMRS_ERR_SHAPE, "%s: buffers differ in size", name);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e == cudaSuccess)
+        e = launch_elementwise(op, a->dptr, (int)a->dtype, op ? b->dptr : nullptr, op ? (int)b->dtype : DT_F32, out->dptr,
+                               (int)out->dtype, n, ctx->stream);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, name);
+    ctx->launches++;
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_silu(llmrs_ctx *ctx, llmrs_buf *x) { return elementwise(ctx, "silu", 0, x, x, nullptr); }
+int llmrs_cuda_mul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *a, const llmrs_buf *b) {
+    return elementwise(ctx, "mul", 1, out, a, b);
+}
+int llmrs_cuda_add(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *a, const llmrs_buf *b) {
+    return elementwise(ctx, "add", 2, out, a, b);
+}
+
+int llmrs_cuda_rms_norm(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *input, const llmrs_buf *weight, float eps) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!out || !input || !weight || !out->dptr || !input->dptr || !weight->dptr)
+        return ctx->fail(LLMRS_ERR_ARG, "rms_norm: null buffer");
+    if (!dense_elem_bytes(out->dtype) || !dense_elem_bytes(input->dtype) || weight->dtype != LLMRS_F32)
+        return ctx->fail(LLMRS_ERR_DTYPE, "rms_norm: activations F32 or BF16, weight F32");
+    const uint32_t dim = input->dim0, rows = input->dim1 ? input->dim1 : 1;
+    if (weight->dim0 != dim || out->dim0 != dim || (out->dim1 ? out->dim1 : 1) != rows)
+        return ctx->fail(LLMRS_ERR_SHAPE, "rms_norm: input [%u, %u], weight [%u], output [%u, %u]", dim, rows, weight->dim0,
+                         out->dim0, out->dim1);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e == cudaSuccess)
+        e = launch_rms_norm(input->dptr, (int)input->dtype, (const float *)weight->dptr, out->dptr, (int)out->dtype,
+                            (int)dim, (int)rows, eps, ctx->stream);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "rms_norm");
+    ctx->launches++;
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_argmax(llmrs_ctx *ctx, const llmrs_buf *logits, uint32_t *index) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!logits || !logits->dptr || !index) return ctx->fail(LLMRS_ERR_ARG, "argmax: null pointer");
+    if (!dense_elem_bytes(logits->dtype)) return ctx->fail(LLMRS_ERR_DTYPE, "argmax: logits must be F32 or BF16");
+    const size_t n = buf_elems(logits);
+    if (n == 0 || n > 0xFFFFFFFFull) return ctx->fail(LLMRS_ERR_SHAPE, "argmax: %zu values", n);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e == cudaSuccess) e = launch_argmax(logits->dptr, (int)logits->dtype, (uint32_t)n, ctx->argmax_out, ctx->stream);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "argmax");
+    ctx->launches++;
+    int rc = llmrs_cuda_sync(ctx);                       // the trait returns the index: the call completes the stream
+    if (rc != LLMRS_OK) return rc;
+    e = cudaMemcpy(index, ctx->argmax_out, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "argmax: read");
     return LLMRS_OK;
 }
 

@@ -704,17 +704,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                     if (lane == 0) mbar_arrive(&acc_empty[ab]);
                 }
                 if (combine) {
-                    for (int c = c_first; c <= c_last; c++) {
-                        if (c == (int)blockIdx.x) continue;
+                    // the deposits of two other CTAs are loaded together: one trip to L2 per pair
+                    auto slot_of = [&](int c) {
                         const int k = tail_start(sc, c) >= tb ? 0 : 1;
-                        const float *sl = p.ws_slots + (size_t)(2 * c + k) * (TILE_ROWS * TN) + (size_t)g0 * TILE_ROWS +
-                                          32 * quarter + lane;
-                        float add[GT];
+                        return p.ws_slots + (size_t)(2 * c + k) * (TILE_ROWS * TN) + (size_t)g0 * TILE_ROWS + 32 * quarter + lane;
+                    };
+                    int c = c_first;
+                    while (c <= c_last) {
+                        if (c == (int)blockIdx.x) { c++; continue; }
+                        const float *sa = slot_of(c++);
+                        if (c <= c_last && c == (int)blockIdx.x) c++;
+                        const bool two = c <= c_last;
+                        const float *sb = two ? slot_of(c++) : sa;
+                        float add_a[GT], add_b[GT];
 #pragma unroll
-                        for (int j = 0; j < GT; j++) add[j] = __ldcg(sl + j * TILE_ROWS);
+                        for (int j = 0; j < GT; j++) add_a[j] = __ldcg(sa + j * TILE_ROWS);
+                        if (two) {
+#pragma unroll
+                            for (int j = 0; j < GT; j++) add_b[j] = __ldcg(sb + j * TILE_ROWS);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < GT; j++) add_b[j] = 0.0f;
+                        }
 #pragma unroll
                         for (int j = 0; j < GT; j++)
-                            v[j / 16][j % 16] = __float_as_uint(__uint_as_float(v[j / 16][j % 16]) + add[j]);
+                            v[j / 16][j % 16] = __float_as_uint(__uint_as_float(v[j / 16][j % 16]) + add_a[j] + add_b[j]);
                     }
                 }
 #pragma unroll

@@ -47,6 +47,14 @@ cudaError_t launch_dequant(int wdtype, const uint8_t *w, int K, int N, float *ou
 cudaError_t launch_embed(int wdtype, const uint8_t *table, int K, uint32_t vocab, const uint32_t *dev_tokens,
                          int n_tokens, void *out, int out_dtype, uint32_t *err_word, cudaStream_t s);
 
+// Element-wise ops on n values (op 0: out = silu(a); 1: out = a * b; 2: out = a + b), per-row RMS norm
+// ([rows] rows of dim values, float32 weight[dim]) and argmax of n values into *dev_out.
+cudaError_t launch_elementwise(int op, const void *a, int a_dtype, const void *b, int b_dtype, void *out,
+                               int out_dtype, size_t n, cudaStream_t s);
+cudaError_t launch_rms_norm(const void *in, int in_dtype, const float *weight, void *out, int out_dtype, int dim,
+                            int rows, float eps, cudaStream_t s);
+cudaError_t launch_argmax(const void *x, int dtype, uint32_t n, uint32_t *dev_out, cudaStream_t s);
+
 // Decode matmul: integer dot products per scale group, float32 across groups; any M (tokens are
 // processed in passes of <= 4).  x_dtype / out_dtype are DT_F32 or DT_BF16.  err_word is a device
 // word that receives a KernelError if a bounded wait inside the kernel gives up.  *launches is

@@ -160,6 +160,43 @@ def embed(dtype: int, w: np.ndarray, K: int, N: int, tokens, *, bf16: bool = Fal
     return out
 
 
+def _round_io(v: np.ndarray, bf16: bool) -> np.ndarray:
+    v = np.asarray(v, dtype=np.float32)
+    return bf16_bits_to_f32(f32_to_bf16_bits(v)).reshape(v.shape) if bf16 else v
+
+
+def silu(x: np.ndarray, *, bf16: bool = False) -> np.ndarray:
+    """shaders/ops.metal:762-771: v / (1 + exp(-v)) in float32 (exp evaluated in double here), then the
+    output rounding."""
+    v = np.asarray(x, dtype=np.float32).astype(np.float64)
+    return _round_io((v / (1.0 + np.exp(-v))).astype(np.float32), bf16)
+
+
+def mul(a: np.ndarray, b: np.ndarray, *, bf16: bool = False) -> np.ndarray:
+    """shaders/ops.metal:785-793: float(a) * float(b), one rounding."""
+    return _round_io(np.asarray(a, np.float32) * np.asarray(b, np.float32), bf16)
+
+
+def add(a: np.ndarray, b: np.ndarray, *, bf16: bool = False) -> np.ndarray:
+    """shaders/ops.metal:775-783."""
+    return _round_io(np.asarray(a, np.float32) + np.asarray(b, np.float32), bf16)
+
+
+def rms_norm(x: np.ndarray, weight: np.ndarray, eps: float, *, bf16: bool = False) -> np.ndarray:
+    """shaders/ops.metal:970-1003 per row of x [rows, dim]: inv = rsqrt(sum(v^2) / dim + eps);
+    out = (v * inv) * weight.  The sum of squares is taken in double (the shader's own order of
+    float additions depends on its thread count); inv and the products are float32."""
+    v = np.asarray(x, dtype=np.float32)
+    ss = (v.astype(np.float64) ** 2).sum(axis=-1, keepdims=True)
+    inv = (1.0 / np.sqrt(ss / v.shape[-1] + np.float64(np.float32(eps)))).astype(np.float32)
+    return _round_io((v * inv) * np.asarray(weight, np.float32), bf16)
+
+
+def argmax(x: np.ndarray) -> int:
+    """shaders/ops.metal:803-835 for distinct maxima; the smallest index among equal maxima."""
+    return int(np.argmax(np.asarray(x, dtype=np.float32)))
+
+
 def matmul(dtype: int, w: np.ndarray, K: int, N: int, x: np.ndarray, *, acc: str = "f64",
            rows: tuple[int, int] | None = None, threads: int | None = None, fast: bool = False) -> np.ndarray:
     """Out[M, N] = X[M, K] . W[N, K]^T.  acc="f32": the reference's sequential float

@@ -309,6 +309,68 @@ def test_matmul_gate_up_bf16_and_errors(backend):
         backend.matmul_gate_up(out, g, other, upload_x(backend, x, 1, K))
 
 
+# ---------- the small ops between the matmuls: silu, mul, add, rms_norm, argmax ----------
+
+def _upload_dense(be, v, bf16):
+    shape = [v.shape[-1]] if v.ndim == 1 or v.shape[0] == 1 else [v.shape[-1], v.shape[0]]
+    if bf16:
+        return be.upload_tensor(TensorView("v", DType.BF16, shape, synth.bf16_bits(v)))
+    return be.upload_tensor(TensorView("v", DType.F32, shape, np.ascontiguousarray(v, np.float32)))
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("n", [1, 255, 14336, 4 * 4096])
+def test_silu_mul_add(backend, n, bf16):
+    """Element-wise ops in float32 with one rounding of the result: mul and add bit for bit, silu within
+    one unit in the last place of the output type (expf against exp)."""
+    a = synth.activations(1, n, tid=70).reshape(-1) * np.float32(3.0)
+    b = synth.activations(1, n, tid=71).reshape(-1)
+    if bf16:
+        a, b = (O.bf16_bits_to_f32(synth.bf16_bits(v)).reshape(-1) for v in (a, b))
+    ab, bb = _upload_dense(backend, a, bf16), _upload_dense(backend, b, bf16)
+    out = backend.alloc([n], DType.BF16 if bf16 else DType.F32)
+    backend.mul(out, ab, bb)
+    backend.sync()
+    assert np.array_equal(backend.read_to_vec_f32(out), O.mul(a, b, bf16=bf16))
+    backend.add(out, ab, bb)
+    backend.sync()
+    assert np.array_equal(backend.read_to_vec_f32(out), O.add(a, b, bf16=bf16))
+    backend.silu(ab)
+    backend.sync()
+    got, want = backend.read_to_vec_f32(ab), O.silu(a, bf16=bf16)
+    ulp = 2.0 ** -7 if bf16 else 2.0 ** -22
+    assert np.all(np.abs(got - want) <= ulp * np.maximum(np.abs(want), 1e-30))
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("dim,rows", [(256, 1), (4096, 1), (4096, 7), (14336, 3), (100, 5)])
+def test_rms_norm(backend, dim, rows, bf16):
+    x = synth.activations(rows, dim, tid=80) * np.float32(2.5)
+    if bf16:
+        x = O.bf16_bits_to_f32(synth.bf16_bits(x)).reshape(rows, dim)
+    w = (synth.activations(1, dim, tid=81).reshape(-1) * np.float32(0.1) + np.float32(1.0)).astype(np.float32)
+    xb = _upload_dense(backend, x, bf16)
+    wb = backend.upload_tensor(TensorView("w", DType.F32, [dim], w))
+    out = backend.alloc([dim] if rows == 1 else [dim, rows], DType.BF16 if bf16 else DType.F32)
+    backend.rms_norm(out, xb, wb, 1e-5)
+    backend.sync()
+    got = backend.read_to_vec_f32(out).reshape(rows, dim)
+    want = O.rms_norm(x, w, 1e-5, bf16=bf16)
+    ulp = 2.0 ** -7 if bf16 else 2.0 ** -21              # the sum of squares is rounded in a different order
+    assert np.all(np.abs(got - want) <= ulp * np.maximum(np.abs(want), 1e-30))
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("n", [1, 1000, 128256])
+def test_argmax(backend, n, bf16):
+    x = synth.activations(1, n, tid=90).reshape(-1)
+    if bf16:
+        x = O.bf16_bits_to_f32(synth.bf16_bits(x)).reshape(-1)
+    assert backend.argmax(_upload_dense(backend, x, bf16)) == O.argmax(x)
+    x[n // 2] = x[n - 1] = np.float32(100.0)              # a tie: the smaller index
+    assert backend.argmax(_upload_dense(backend, x, bf16)) == n // 2 if n > 1 else 0
+
+
 # ---------- embedding lookup (Backend::embed) ----------
 
 @pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])

@@ -267,3 +267,16 @@ def test_embed_is_row_lookup_of_dequant():
         gb = O.embed(dt, w, K, N, toks, bf16=True)
         assert np.array_equal(O.f32_to_bf16_bits(gb), O.f32_to_bf16_bits(full[toks]))     # idempotent rounding
         assert O.embed(dt, w, K, N, []).shape == (0, K)
+
+
+def test_small_ops_known_values():
+    """silu, mul, add, rms_norm, argmax against values worked out by hand."""
+    assert np.allclose(O.silu(np.array([0.0, 1.0, -1.0], np.float32)), [0.0, 0.7310586, -0.26894143], atol=1e-7)
+    assert np.array_equal(O.mul(np.array([1.5, -2.0], np.float32), np.array([2.0, 0.25], np.float32)), [3.0, -0.5])
+    assert np.array_equal(O.add(np.array([1.5, -2.0], np.float32), np.array([2.0, 0.25], np.float32)), [3.5, -1.75])
+    x = np.array([[3.0, 4.0, 0.0, 0.0]], np.float32)                  # mean square 6.25
+    got = O.rms_norm(x, np.array([1.0, 2.0, 1.0, 1.0], np.float32), 0.0)
+    assert np.allclose(got, [[1.2, 3.2, 0.0, 0.0]], rtol=1e-6)
+    assert O.argmax(np.array([1.0, 5.0, 5.0, -2.0], np.float32)) == 1
+    # bf16 output is a single round-to-nearest-even of the float32 result
+    assert O.add(np.array([1.0], np.float32), np.array([2.0 ** -9], np.float32), bf16=True)[0] == 1.0
