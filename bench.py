@@ -33,6 +33,7 @@ K_IN, N_OUT = 4096, 128256
 Q6K, Q4K = 14, 12
 BLOCK_BYTES = {Q4K: 144, Q6K: 210}
 L2_BYTES = 126e6
+NCU_DRAM_BYTES_PER_LAUNCH = 435114240   # Q6_K 4096 -> 128256, one token: 431.03 MB read + 4.08 MB written
 FUSED_GATHER_MAX_WORDS = 1 << 18      # values one rank posts per peer and matmul, above which NCCL moves them
 
 
@@ -334,13 +335,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     e2e_value = alg / (ms_e2e * 1e-3) / 1e9
     achieved = alg_local / (ms_kernel * 1e-3) / 1e9
 
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tpath):
-        with open(tpath) as f:
-            t = json.load(f).get("q6k_gemv_k4096_n128256_m1")
-        if t and M == 1:
-            traffic = int(t["dram_bytes_per_launch"] * n_local / N_OUT)
+    # DRAM bytes of one launch of the headline kernel (dram__bytes_read.sum + dram__bytes_write.sum of
+    # the ncu capture summarised under profiles/), scaled by the rows this GPU holds
+    traffic = int(NCU_DRAM_BYTES_PER_LAUNCH * n_local / N_OUT) if M == 1 else None
 
     if rank != 0:
         return

@@ -950,17 +950,17 @@ activations_to_f16_kernel(const void *__restrict__ x, int x_is_bf16, int K, __ha
 // ---- host side ---------------------------------------------------------------------------------
 
 // Does cutting the last, partial wave of tiles along K pay?  The exchange is not free: a deposit
-// is a tile-sized fp32 store, and the last arriver reads every deposit back group by group, one
-// L2 round trip each.  Measured on a B200 (split / no split): K=14336, N=4096 (32 tiles) 0.52 at
-// 16 tokens, 0.61 at 64, 0.80 at 128; K=4096 shapes 0.92 .. 1.46; 256-token tiles 1.0 .. 1.8.  So
-// the split is used where at least half of the SMs would otherwise idle through a long K loop
-// and the tiles (hence the deposits) are small.
+// is a tile-sized fp32 store, and the last arriver reads the deposits back group by group, one
+// L2 round trip per two deposits.  Measured on a B200 (split / no split): K=14336, N=4096
+// (32 tiles up to 128 tokens, 64 at 512) 0.52 at 16 tokens, 0.61 at 64, 0.73 at 128, 0.94 at 512;
+// K=4096 shapes 0.92 .. 1.46; more than half a wave of 256-token tiles 1.04 .. 1.8.  So the split
+// is used where at least half of the SMs would otherwise idle through a long K loop.
 // `forced` = 0 / 1 overrides the rule (measurements and tests), -1 leaves it alone.
-bool split_pays(int n_tiles, int nb, int TN, int sms, int forced) {
+bool split_pays(int n_tiles, int nb, int sms, int forced) {
     const int rest = n_tiles % sms;
     if (rest == 0 || nb < 2) return false;
     if (forced >= 0) return forced != 0;
-    return n_tiles <= sms / 2 && nb >= 32 && TN <= 128;
+    return n_tiles <= sms / 2 && nb >= 32;
 }
 
 template <int QT, int TN>
@@ -977,7 +977,7 @@ cudaError_t launch_tn(const GemmParams &p, const void *x_f16, cudaStream_t s) {
     int grid = n_tiles < p.sm_count ? n_tiles : p.sm_count;
     GemmParams q = p;
     q.split = 0;
-    if (p.ws_slots && split_pays(n_tiles, p.K / QK_K, TN, p.sm_count, p.split)) {
+    if (p.ws_slots && split_pays(n_tiles, p.K / QK_K, p.sm_count, p.split)) {
         q.split = 1;
         const int tail_blocks = (n_tiles % p.sm_count) * (p.K / QK_K);
         if (n_tiles < p.sm_count) grid = tail_blocks < p.sm_count ? tail_blocks : p.sm_count;

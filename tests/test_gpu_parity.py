@@ -368,7 +368,7 @@ def test_argmax(backend, n, bf16):
         x = O.bf16_bits_to_f32(synth.bf16_bits(x)).reshape(-1)
     assert backend.argmax(_upload_dense(backend, x, bf16)) == O.argmax(x)
     x[n // 2] = x[n - 1] = np.float32(100.0)              # a tie: the smaller index
-    assert backend.argmax(_upload_dense(backend, x, bf16)) == n // 2 if n > 1 else 0
+    assert backend.argmax(_upload_dense(backend, x, bf16)) == n // 2
 
 
 # ---------- embedding lookup (Backend::embed) ----------
