@@ -35,6 +35,7 @@ enum llmrs_dtype {
     LLMRS_F32 = 0,
     LLMRS_Q4K = 12,
     LLMRS_Q6K = 14,
+    LLMRS_I32 = 26,     /* index buffers (positions, slot mapping, page tables), as upload_u32 makes them */
     LLMRS_BF16 = 30
 };
 
@@ -141,6 +142,39 @@ int llmrs_cuda_rms_norm(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *input, 
  * (metal/mod.rs:836).  On ties the smallest index wins (the reference's tree reduction leaves
  * the choice among equal maxima to its thread layout). */
 int llmrs_cuda_argmax(llmrs_ctx *ctx, const llmrs_buf *logits, uint32_t *index);
+
+/* Replaces Backend::rms_norm_heads (src/backend/mod.rs:40-43; metal/mod.rs:719-742): every
+ * consecutive chunk of weight.dim0 values of x is normalised in place like a row of rms_norm. */
+int llmrs_cuda_rms_norm_heads(llmrs_ctx *ctx, llmrs_buf *x, const llmrs_buf *weight, float eps);
+
+/* Replaces Backend::rope (src/backend/mod.rs:45-47; metal/mod.rs:744-785; shaders/ops.metal:1011-1042):
+ * rotary embedding of q and k in place; positions is an I32 buffer with one absolute position per
+ * column; split_half = 0 rotates pairs (2i, 2i+1) of each head (RopeLayout::Interleaved), 1 rotates
+ * (i, i + head_dim/2) (RopeLayout::SplitHalf). */
+int llmrs_cuda_rope(llmrs_ctx *ctx, llmrs_buf *q, llmrs_buf *k, const llmrs_buf *positions, uint32_t head_dim,
+                    float rope_theta, uint32_t split_half);
+
+/* Replaces Backend::scatter_kv (src/backend/mod.rs:68-69; shaders/ops.metal:841-853):
+ * pool[slot_mapping[t] * kv_dim + d] = src[t * kv_dim + d] for t < num_tokens. */
+int llmrs_cuda_scatter_kv(llmrs_ctx *ctx, llmrs_buf *pool, const llmrs_buf *src, const llmrs_buf *slot_mapping,
+                          uint32_t kv_dim, uint32_t num_tokens);
+
+/* Replaces Backend::gather (src/backend/mod.rs:71-72; shaders/ops.metal:859-873):
+ * column c of out = column indices[c] of src ([dim, seq_len]) for c < num_indices. */
+int llmrs_cuda_gather(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *src, const llmrs_buf *indices,
+                      uint32_t num_indices);
+
+/* Replaces Backend::attention (src/backend/mod.rs:49-66; metal/mod.rs:880-928; shaders/ops.metal:636-758):
+ * paged, variable-length, grouped-query attention with a causal mask.  q and out are
+ * [n_heads * head_dim, total_query_tokens]; the pools hold pages of block_size positions of
+ * n_kv_heads * head_dim values; request r owns query tokens query_starts[r] .. query_starts[r+1]
+ * (query_starts has num_requests + 1 entries), has seq_lens[r] positions in total, and its page p is
+ * block_table[r * max_blocks_per_seq + p].  Query token i of a request with c query tokens sees
+ * positions 0 .. seq_len - c + i.  head_dim a multiple of 32, at most 256. */
+int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, const llmrs_buf *k_pool,
+                         const llmrs_buf *v_pool, const llmrs_buf *block_table, const llmrs_buf *query_starts,
+                         const llmrs_buf *seq_lens, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                         uint32_t block_size, uint32_t max_blocks_per_seq);
 
 /* The front of the feed-forward block in one call: out = silu(gate) * up with gate = matmul(w_gate,
  * input) and up = matmul(w_up, input), i.e. the four calls matmul, matmul, silu, mul of

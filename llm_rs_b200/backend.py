@@ -6,8 +6,8 @@ same here: `upload_tensor`, `alloc`, `matmul`, `read_to_vec_f32`, `sync`,
 `gpu_secs_total`, `reset_gpu_secs`.  Every call goes through the C ABI of
 include/llmrs_cuda.h (ctypes); there is no CPU path, and importing the library
 on a machine without the built .so, or creating a backend without a B200,
-raises.  Trait methods outside the matmul path raise NotImplementedError, as
-the reference does with `unimplemented!` for what a backend lacks
+raises.  Every method of the trait is present; dtypes a method does not handle are
+refused with an error, as the reference does with `unimplemented!` for what a backend lacks
 (src/backend/metal/mod.rs:511).
 """
 from __future__ import annotations
@@ -29,13 +29,14 @@ class DType(enum.IntEnum):
     F32 = 0
     Q4K = 12
     Q6K = 14
+    I32 = 26
     BF16 = 30
 
     def block_elems(self) -> int:                     # src/tensor/mod.rs:37-50
         return 256 if self in (DType.Q4K, DType.Q6K) else 1
 
     def block_size_bytes(self) -> int:                # src/tensor/mod.rs:52-86
-        return {DType.F32: 4, DType.BF16: 2, DType.Q4K: 144, DType.Q6K: 210}[self]
+        return {DType.F32: 4, DType.I32: 4, DType.BF16: 2, DType.Q4K: 144, DType.Q6K: 210}[self]
 
     def storage_size(self, n_elements: int) -> int:   # src/tensor/mod.rs:89-93
         be = self.block_elems()
@@ -89,6 +90,11 @@ ABI = {
     "llmrs_cuda_add": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_rms_norm": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_float]),
     "llmrs_cuda_argmax": (C.c_int, [_VP, _BUFP, C.POINTER(C.c_uint32)]),
+    "llmrs_cuda_rms_norm_heads": (C.c_int, [_VP, _BUFP, _BUFP, C.c_float]),
+    "llmrs_cuda_rope": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_uint32, C.c_float, C.c_uint32]),
+    "llmrs_cuda_scatter_kv": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_uint32, C.c_uint32]),
+    "llmrs_cuda_gather": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_uint32]),
+    "llmrs_cuda_attention": (C.c_int, [_VP] + [_BUFP] * 7 + [C.c_uint32] * 5),
     "llmrs_cuda_matmul_gate_up": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_embed": (C.c_int, [_VP, _BUFP, _BUFP, C.POINTER(C.c_uint32), C.c_uint32]),
     "llmrs_cuda_matmul_allgather": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_uint32, C.c_uint32, C.POINTER(_VP), _VP]),
@@ -285,6 +291,38 @@ class CudaBackend:
         self._check(self._lib.llmrs_cuda_argmax(self._ctx, C.byref(logits._raw), C.byref(v)))
         return int(v.value)
 
+    def rms_norm_heads(self, x: CudaBuffer, weight: CudaBuffer, eps: float) -> None:
+        """Backend::rms_norm_heads (src/backend/mod.rs:40-43): in place, per chunk of weight.dim0 values."""
+        self._check(self._lib.llmrs_cuda_rms_norm_heads(self._ctx, C.byref(x._raw), C.byref(weight._raw), float(eps)))
+
+    def upload_u32(self, data: Sequence[int]) -> CudaBuffer:
+        """Backend::upload_u32 (src/backend/mod.rs:74-75): a small index array as an I32 buffer."""
+        arr = np.ascontiguousarray(data, dtype=np.uint32).reshape(-1)
+        return self.upload_tensor(TensorView("u32", DType.I32, [max(arr.size, 1)], arr if arr.size else np.zeros(1, np.uint32)))
+
+    def rope(self, q: CudaBuffer, k: CudaBuffer, positions: CudaBuffer, head_dim: int, rope_theta: float,
+             split_half: bool = False) -> None:
+        """Backend::rope (src/backend/mod.rs:45-47); split_half=False is RopeLayout::Interleaved."""
+        self._check(self._lib.llmrs_cuda_rope(self._ctx, C.byref(q._raw), C.byref(k._raw), C.byref(positions._raw),
+                                              head_dim, float(rope_theta), 1 if split_half else 0))
+
+    def scatter_kv(self, pool: CudaBuffer, src: CudaBuffer, slot_mapping: CudaBuffer, kv_dim: int, num_tokens: int) -> None:
+        self._check(self._lib.llmrs_cuda_scatter_kv(self._ctx, C.byref(pool._raw), C.byref(src._raw),
+                                                    C.byref(slot_mapping._raw), kv_dim, num_tokens))
+
+    def gather(self, out: CudaBuffer, src: CudaBuffer, indices: CudaBuffer, num_indices: int) -> None:
+        self._check(self._lib.llmrs_cuda_gather(self._ctx, C.byref(out._raw), C.byref(src._raw), C.byref(indices._raw),
+                                                num_indices))
+
+    def attention(self, out: CudaBuffer, q: CudaBuffer, k_pool: CudaBuffer, v_pool: CudaBuffer, block_table: CudaBuffer,
+                  query_starts: CudaBuffer, seq_lens: CudaBuffer, n_heads: int, n_kv_heads: int, head_dim: int,
+                  block_size: int, max_blocks_per_seq: int) -> None:
+        """Backend::attention (src/backend/mod.rs:49-66): paged varlen causal grouped-query attention."""
+        self._check(self._lib.llmrs_cuda_attention(self._ctx, C.byref(out._raw), C.byref(q._raw), C.byref(k_pool._raw),
+                                                   C.byref(v_pool._raw), C.byref(block_table._raw),
+                                                   C.byref(query_starts._raw), C.byref(seq_lens._raw), n_heads,
+                                                   n_kv_heads, head_dim, block_size, max_blocks_per_seq))
+
     def matmul_gate_up(self, out: CudaBuffer, w_gate: CudaBuffer, w_up: CudaBuffer, input: CudaBuffer) -> None:
         """out = silu(matmul(w_gate, input)) * matmul(w_up, input): the calls matmul, matmul, silu, mul
         of the reference's feed-forward block (src/arch/llama.rs:165-168) as one."""
@@ -322,9 +360,3 @@ class CudaBackend:
         self._check(self._lib.llmrs_cuda_launch_count(self._ctx, C.byref(v)))
         return int(v.value)
 
-    # -- rest of the trait: outside the matmul path --
-    def _unimplemented(self, *_a, **_k):
-        raise NotImplementedError("only the matmul path of the Backend trait is implemented by the CUDA backend")
-
-    rms_norm_heads = rope = attention = scatter_kv = gather = _unimplemented
-    upload_u32 = _unimplemented

@@ -124,7 +124,7 @@ bool storage_size(uint32_t dtype, uint64_t n_elems, size_t *out) {
         *out = (size_t)(n_elems / QK_K) * (dtype == LLMRS_Q4K ? Q4K_BLOCK_BYTES : Q6K_BLOCK_BYTES);
         return true;
     }
-    size_t eb = dense_elem_bytes(dtype);
+    size_t eb = dtype == LLMRS_I32 ? 4 : dense_elem_bytes(dtype);
     if (!eb) return false;
     *out = (size_t)n_elems * eb;
     return true;
@@ -234,8 +234,8 @@ int llmrs_cuda_alloc(llmrs_ctx *ctx, uint32_t dtype, const uint64_t *shape, int 
     if (!out) return ctx->fail(LLMRS_ERR_ARG, "alloc: out is null");
     uint32_t d0, d1;
     if (!shape_dims(shape, ndims, &d0, &d1)) return ctx->fail(LLMRS_ERR_SHAPE, "alloc: bad shape");
-    size_t eb = dense_elem_bytes(dtype);
-    if (!eb) return ctx->fail(LLMRS_ERR_DTYPE, "alloc: dtype %u is not F32/BF16", dtype);
+    size_t eb = dtype == LLMRS_I32 ? 4 : dense_elem_bytes(dtype);
+    if (!eb) return ctx->fail(LLMRS_ERR_DTYPE, "alloc: dtype %u is not F32/BF16/I32", dtype);
     size_t nbytes = (size_t)d0 * (d1 ? d1 : 1) * eb;
     DeviceGuard guard(ctx->device);
     void *p = nullptr;
@@ -250,8 +250,8 @@ int llmrs_cuda_wrap(llmrs_ctx *ctx, void *dptr, uint32_t dtype, const uint64_t *
     if (!out || !dptr) return ctx->fail(LLMRS_ERR_ARG, "wrap: null pointer");
     uint32_t d0, d1;
     if (!shape_dims(shape, ndims, &d0, &d1)) return ctx->fail(LLMRS_ERR_SHAPE, "wrap: bad shape");
-    size_t eb = dense_elem_bytes(dtype);
-    if (!eb) return ctx->fail(LLMRS_ERR_DTYPE, "wrap: dtype %u is not F32/BF16", dtype);
+    size_t eb = dtype == LLMRS_I32 ? 4 : dense_elem_bytes(dtype);
+    if (!eb) return ctx->fail(LLMRS_ERR_DTYPE, "wrap: dtype %u is not F32/BF16/I32", dtype);
     if ((uintptr_t)dptr % 16) return ctx->fail(LLMRS_ERR_ARG, "wrap: pointer must be 16-byte aligned");
     *out = llmrs_buf{dptr, (size_t)d0 * (d1 ? d1 : 1) * eb, dtype, d0, d1, LLMRS_LAYOUT_RAW, 0u,
                      (uint32_t)ctx->device};
@@ -284,7 +284,7 @@ int llmrs_cuda_upload_tensor(llmrs_ctx *ctx, uint32_t dtype, const uint64_t *sha
     if (quant && d0 % QK_K)
         return ctx->fail(LLMRS_ERR_SHAPE, "upload_tensor: in_features %u is not a multiple of 256", d0);
     if (!storage_size(dtype, n_elems, &want))
-        return ctx->fail(LLMRS_ERR_DTYPE, "upload_tensor: dtype %u is not supported (F32, BF16, Q4_K, Q6_K)", dtype);
+        return ctx->fail(LLMRS_ERR_DTYPE, "upload_tensor: dtype %u is not supported (F32, BF16, I32, Q4_K, Q6_K)", dtype);
     if (want != nbytes)
         return ctx->fail(LLMRS_ERR_SHAPE, "upload_tensor: %zu bytes given, shape needs %zu", nbytes, want);
     DeviceGuard guard(ctx->device);
@@ -440,6 +440,121 @@ int llmrs_cuda_argmax(llmrs_ctx *ctx, const llmrs_buf *logits, uint32_t *index) 
     if (rc != LLMRS_OK) return rc;
     e = cudaMemcpy(index, ctx->argmax_out, sizeof(uint32_t), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "argmax: read");
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_rms_norm_heads(llmrs_ctx *ctx, llmrs_buf *x, const llmrs_buf *weight, float eps) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!x || !weight || !x->dptr || !weight->dptr) return ctx->fail(LLMRS_ERR_ARG, "rms_norm_heads: null buffer");
+    if (!dense_elem_bytes(x->dtype) || weight->dtype != LLMRS_F32)
+        return ctx->fail(LLMRS_ERR_DTYPE, "rms_norm_heads: activations F32 or BF16, weight F32");
+    const size_t dim = buf_elems(weight), n = buf_elems(x);
+    if (dim == 0 || n % dim) return ctx->fail(LLMRS_ERR_SHAPE, "rms_norm_heads: %zu values are not chunks of %zu", n, dim);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e == cudaSuccess)
+        e = launch_rms_norm(x->dptr, (int)x->dtype, (const float *)weight->dptr, x->dptr, (int)x->dtype, (int)dim,
+                            (int)(n / dim), eps, ctx->stream);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "rms_norm_heads");
+    ctx->launches++;
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_rope(llmrs_ctx *ctx, llmrs_buf *q, llmrs_buf *k, const llmrs_buf *positions, uint32_t head_dim,
+                    float rope_theta, uint32_t split_half) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!q || !k || !positions || !q->dptr || !k->dptr || !positions->dptr) return ctx->fail(LLMRS_ERR_ARG, "rope: null buffer");
+    if (!dense_elem_bytes(q->dtype) || !dense_elem_bytes(k->dtype) || positions->dtype != LLMRS_I32)
+        return ctx->fail(LLMRS_ERR_DTYPE, "rope: q and k F32 or BF16, positions I32");
+    const uint32_t seq = q->dim1 ? q->dim1 : 1;
+    if (head_dim == 0 || head_dim % 2 || q->dim0 % head_dim || k->dim0 % head_dim || (k->dim1 ? k->dim1 : 1) != seq ||
+        buf_elems(positions) < seq)
+        return ctx->fail(LLMRS_ERR_SHAPE, "rope: q [%u, %u], k [%u, %u], head_dim %u, %zu positions", q->dim0, q->dim1,
+                         k->dim0, k->dim1, head_dim, buf_elems(positions));
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    llmrs_buf *both[2] = {q, k};
+    for (int i = 0; i < 2 && e == cudaSuccess; i++) {
+        e = launch_rope(both[i]->dptr, (int)both[i]->dtype, (const uint32_t *)positions->dptr, (int)head_dim, rope_theta,
+                        (int)both[i]->dim0, (int)seq, split_half != 0, ctx->stream);
+        ctx->launches++;
+    }
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "rope");
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_scatter_kv(llmrs_ctx *ctx, llmrs_buf *pool, const llmrs_buf *src, const llmrs_buf *slot_mapping,
+                          uint32_t kv_dim, uint32_t num_tokens) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!pool || !src || !slot_mapping || !pool->dptr || !src->dptr || !slot_mapping->dptr)
+        return ctx->fail(LLMRS_ERR_ARG, "scatter_kv: null buffer");
+    if (!dense_elem_bytes(pool->dtype) || pool->dtype != src->dtype || slot_mapping->dtype != LLMRS_I32)
+        return ctx->fail(LLMRS_ERR_DTYPE, "scatter_kv: pool and src of one type (F32 or BF16), slot_mapping I32");
+    if ((size_t)kv_dim * num_tokens > buf_elems(src) || buf_elems(slot_mapping) < num_tokens || kv_dim == 0 ||
+        buf_elems(pool) % kv_dim)
+        return ctx->fail(LLMRS_ERR_SHAPE, "scatter_kv: %u tokens of %u values from %zu, %zu slots", num_tokens, kv_dim,
+                         buf_elems(src), buf_elems(slot_mapping));
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e == cudaSuccess)
+        e = launch_move_rows(pool->dptr, src->dptr, (const uint32_t *)slot_mapping->dptr, 1,
+                             (size_t)kv_dim * dense_elem_bytes(src->dtype), (int)num_tokens, ctx->stream);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "scatter_kv");
+    ctx->launches++;
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_gather(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *src, const llmrs_buf *indices,
+                      uint32_t num_indices) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!out || !src || !indices || !out->dptr || !src->dptr || !indices->dptr)
+        return ctx->fail(LLMRS_ERR_ARG, "gather: null buffer");
+    if (!dense_elem_bytes(out->dtype) || out->dtype != src->dtype || indices->dtype != LLMRS_I32)
+        return ctx->fail(LLMRS_ERR_DTYPE, "gather: out and src of one type (F32 or BF16), indices I32");
+    const uint32_t dim = src->dim0;
+    if (out->dim0 != dim || (size_t)dim * num_indices > buf_elems(out) || buf_elems(indices) < num_indices)
+        return ctx->fail(LLMRS_ERR_SHAPE, "gather: %u columns of %u values into [%u, %u]", num_indices, dim, out->dim0, out->dim1);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e == cudaSuccess)
+        e = launch_move_rows(out->dptr, src->dptr, (const uint32_t *)indices->dptr, 0,
+                             (size_t)dim * dense_elem_bytes(src->dtype), (int)num_indices, ctx->stream);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "gather");
+    ctx->launches++;
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, const llmrs_buf *k_pool,
+                         const llmrs_buf *v_pool, const llmrs_buf *block_table, const llmrs_buf *query_starts,
+                         const llmrs_buf *seq_lens, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                         uint32_t block_size, uint32_t max_blocks_per_seq) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    const llmrs_buf *all[7] = {out, q, k_pool, v_pool, block_table, query_starts, seq_lens};
+    for (const llmrs_buf *b : all)
+        if (!b || !b->dptr) return ctx->fail(LLMRS_ERR_ARG, "attention: null buffer");
+    if (!dense_elem_bytes(q->dtype) || out->dtype != q->dtype || k_pool->dtype != q->dtype || v_pool->dtype != q->dtype)
+        return ctx->fail(LLMRS_ERR_DTYPE, "attention: q, out and the pools of one type (F32 or BF16)");
+    if (block_table->dtype != LLMRS_I32 || query_starts->dtype != LLMRS_I32 || seq_lens->dtype != LLMRS_I32)
+        return ctx->fail(LLMRS_ERR_DTYPE, "attention: block_table, query_starts and seq_lens are I32");
+    if (n_heads == 0 || n_kv_heads == 0 || n_heads % n_kv_heads || head_dim == 0 || head_dim % 32 || head_dim > 256 ||
+        block_size == 0 || max_blocks_per_seq == 0)
+        return ctx->fail(LLMRS_ERR_SHAPE, "attention: %u heads, %u kv heads, head_dim %u, pages of %u", n_heads, n_kv_heads,
+                         head_dim, block_size);
+    const size_t row = (size_t)n_heads * head_dim;
+    const size_t total_q = buf_elems(q) / row, num_req = buf_elems(seq_lens);
+    if (buf_elems(q) % row || buf_elems(out) != buf_elems(q) || buf_elems(query_starts) < num_req + 1 ||
+        buf_elems(block_table) < num_req * max_blocks_per_seq)
+        return ctx->fail(LLMRS_ERR_SHAPE, "attention: q of %zu values, %zu requests, %zu query_starts, %zu page entries",
+                         buf_elems(q), num_req, buf_elems(query_starts), buf_elems(block_table));
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e == cudaSuccess)
+        e = launch_attention(q->dptr, k_pool->dptr, v_pool->dptr, out->dptr, (int)q->dtype,
+                             (const uint32_t *)block_table->dptr, (const uint32_t *)query_starts->dptr,
+                             (const uint32_t *)seq_lens->dptr, (int)total_q, (int)num_req, (int)n_heads, (int)n_kv_heads,
+                             (int)head_dim, (int)block_size, (int)max_blocks_per_seq, ctx->stream);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "attention");
+    ctx->launches++;
     return LLMRS_OK;
 }
 

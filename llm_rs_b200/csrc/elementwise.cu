@@ -1,5 +1,7 @@
-// The small operations that sit between the matmuls of a decode step: silu, mul, add
-// (shaders/ops.metal:762-793), rms_norm (ops.metal:970-1003) and argmax (ops.metal:803-835).
+// The operations of a decode step other than matmul and embed: silu, mul, add
+// (shaders/ops.metal:762-793), rms_norm (ops.metal:970-1003), argmax (ops.metal:803-835), rope
+// (ops.metal:1011-1042), scatter_kv and gather (ops.metal:841-873) and paged attention
+// (ops.metal:636-758).
 // Buffers are F32 or BF16; arithmetic is float32 as in the reference's kernels, with one rounding
 // to the output type.
 #include "kernels.h"
@@ -88,7 +90,182 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const void *x, int bf16, u
     }
 }
 
+// Rotary embedding in place (shaders/ops.metal:1011-1042): x is [row_stride, seq_len] made of heads of
+// head_dim; pair i of a head is (2i, 2i+1) ("interleaved") or (i, i + head_dim/2) ("split half");
+// angle = position * theta^(-2i / head_dim).  One thread per pair.
+__global__ void rope_kernel(void *x, int bf16, const uint32_t *__restrict__ positions, int head_dim, float theta,
+                            int pairs_per_row, int row_stride, int split_half) {
+    const int pair = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
+    if (pair >= pairs_per_row) return;
+    const int half = head_dim / 2, head = pair / half, i = pair % half;
+    const size_t base = (size_t)s * row_stride + (size_t)head * head_dim;
+    const size_t a = split_half ? base + i : base + 2 * i;
+    const size_t b = split_half ? base + i + half : base + 2 * i + 1;
+    const float freq = 1.0f / powf(theta, 2.0f * (float)i / (float)head_dim);
+    const float angle = (float)positions[s] * freq;
+    float sn, cs;
+    sincosf(angle, &sn, &cs);
+    const float x0 = load_f(x, a, bf16), x1 = load_f(x, b, bf16);
+    store_f(x, a, x0 * cs - x1 * sn, bf16);
+    store_f(x, b, x0 * sn + x1 * cs, bf16);
+}
+
+// pool[slot_mapping[t] * kv_dim + d] = src[t * kv_dim + d]  (ops.metal:841-853), and
+// out[c * dim + d] = src[indices[c] * dim + d]              (ops.metal:859-873): rows of `width`
+// elements of `esz` bytes moved by index; one of the two index sides is the identity.
+__global__ void move_rows_kernel(uint8_t *dst, const uint8_t *src, const uint32_t *__restrict__ index, int scatter,
+                                 size_t row_bytes, int rows) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;      // one 2-byte unit each
+    const size_t units = row_bytes / 2;
+    if (i >= units * rows) return;
+    const size_t r = i / units, u = i - r * units;
+    const size_t from = scatter ? r : index[r], to = scatter ? index[r] : r;
+    ((uint16_t *)dst)[to * units + u] = ((const uint16_t *)src)[from * units + u];
+}
+
+// Paged, variable-length, grouped-query attention with a causal mask (shaders/ops.metal:636-758).
+// One CTA per (query token, head).  Keys are taken ATT_TILE positions at a time: thread j forms
+// q . k_j (the key row read as 16-byte vectors, q from shared memory), the tile maximum and sum
+// go through warp shuffles, and thread d accumulates sum_j p_j v_j[d] with the online-softmax
+// rescaling.  A tile never crosses a page when block_size is a multiple of ATT_TILE; otherwise
+// the page is looked up per position.
+constexpr int ATT_TILE = 128;
+constexpr int ATT_THREADS = 128;
+__global__ void __launch_bounds__(ATT_THREADS)
+attention_kernel(const void *q, const void *k_pool, const void *v_pool, void *out, int bf16,
+                 const uint32_t *__restrict__ block_table, const uint32_t *__restrict__ query_starts,
+                 const uint32_t *__restrict__ seq_lens, int n_heads, int n_kv_heads, int head_dim, int block_size,
+                 int max_blocks_per_seq, int num_requests) {
+    extern __shared__ float att_smem[];
+    float *qs = att_smem;                   // [head_dim]
+    float *scores = qs + head_dim;          // [ATT_TILE]
+    __shared__ float red[ATT_THREADS / 32];
+    __shared__ float bcast;
+    const int head = blockIdx.x % n_heads, gq = blockIdx.x / n_heads;
+    int req = 0;
+    while (req + 1 < num_requests && (uint32_t)gq >= query_starts[req + 1]) req++;
+    const int local_q = gq - (int)query_starts[req];
+    const int q_count = (int)query_starts[req + 1] - (int)query_starts[req];
+    const int kv_head = head / (n_heads / n_kv_heads), kv_dim = n_kv_heads * head_dim, kv_off = kv_head * head_dim;
+    const float scale = rsqrtf((float)head_dim);
+    const int causal_len = (int)seq_lens[req] - q_count + local_q + 1;
+    const size_t q_off = (size_t)gq * n_heads * head_dim + (size_t)head * head_dim;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < head_dim; i += ATT_THREADS) qs[i] = load_f(q, q_off + i, bf16);
+    __syncthreads();
+
+    auto block_max = [&](float v) {
+#pragma unroll
+        for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+        if (lane == 0) red[warp] = v;
+        __syncthreads();
+        if (tid == 0) {
+            float m = red[0];
+            for (int w = 1; w < ATT_THREADS / 32; w++) m = fmaxf(m, red[w]);
+            bcast = m;
+        }
+        __syncthreads();
+        return bcast;
+    };
+    auto block_sum = [&](float v) {
+#pragma unroll
+        for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        __syncthreads();                         // `red` and `bcast` of the maximum have been read
+        if (lane == 0) red[warp] = v;
+        __syncthreads();
+        if (tid == 0) {
+            float t = 0.0f;
+            for (int w = 0; w < ATT_THREADS / 32; w++) t += red[w];
+            bcast = t;
+        }
+        __syncthreads();
+        return bcast;
+    };
+    auto kv_row = [&](int t) {                   // element offset of position t of this request in the pools
+        const uint32_t page = block_table[(size_t)req * max_blocks_per_seq + t / block_size];
+        return ((size_t)page * block_size + (size_t)(t % block_size)) * kv_dim + kv_off;
+    };
+
+    float acc[2] = {0.0f, 0.0f};                 // output dims tid and tid + 128 (head_dim <= 256)
+    float m_i = -INFINITY, l_i = 0.0f;
+    for (int t0 = 0; t0 < causal_len; t0 += ATT_TILE) {
+        const int tile_len = min(ATT_TILE, causal_len - t0);
+        float sc = -INFINITY;
+        if (tid < tile_len) {
+            const size_t row = kv_row(t0 + tid);
+            float dot = 0.0f;
+            if (bf16 && (head_dim % 8) == 0 && (row % 8) == 0) {
+                const uint4 *kr = reinterpret_cast<const uint4 *>((const uint16_t *)k_pool + row);
+                for (int i = 0; i < head_dim / 8; i++) {
+                    const uint4 u = __ldg(kr + i);
+                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        dot = fmaf(qs[8 * i + 2 * j], __uint_as_float(w[j] << 16), dot);
+                        dot = fmaf(qs[8 * i + 2 * j + 1], __uint_as_float(w[j] & 0xFFFF0000u), dot);
+                    }
+                }
+            } else {
+                for (int i = 0; i < head_dim; i++) dot = fmaf(qs[i], load_f(k_pool, row + i, bf16), dot);
+            }
+            sc = dot * scale;
+        }
+        const float m_new = fmaxf(m_i, block_max(sc));
+        const float rescale = __expf(m_i - m_new);       // exp(-inf) = 0 on the first tile
+        const float e = tid < tile_len ? __expf(sc - m_new) : 0.0f;
+        scores[tid] = e;
+        const float tile_sum = block_sum(e);             // its barriers also publish scores[]
+        l_i = l_i * rescale + tile_sum;
+        m_i = m_new;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int d = tid + h * ATT_THREADS;
+            if (d < head_dim) {
+                float a = acc[h] * rescale;
+                for (int j = 0; j < tile_len; j++) a = fmaf(scores[j], load_f(v_pool, kv_row(t0 + j) + d, bf16), a);
+                acc[h] = a;
+            }
+        }
+        __syncthreads();                                 // scores[] is rewritten by the next tile
+    }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int d = tid + h * ATT_THREADS;
+        if (d < head_dim) store_f(out, q_off + d, acc[h] / l_i, bf16);
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_rope(void *x, int dtype, const uint32_t *positions, int head_dim, float theta, int row_stride,
+                        int seq_len, int split_half, cudaStream_t s) {
+    const int pairs = row_stride / 2;
+    if (pairs <= 0 || seq_len <= 0) return cudaSuccess;
+    rope_kernel<<<dim3((unsigned)((pairs + 255) / 256), (unsigned)seq_len), 256, 0, s>>>(
+        x, dtype == DT_BF16, positions, head_dim, theta, pairs, row_stride, split_half);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_move_rows(void *dst, const void *src, const uint32_t *index, int scatter, size_t row_bytes,
+                             int rows, cudaStream_t s) {
+    const size_t n = row_bytes / 2 * (size_t)rows;
+    if (n == 0) return cudaSuccess;
+    move_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>((uint8_t *)dst, (const uint8_t *)src, index, scatter,
+                                                               row_bytes, rows);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_attention(const void *q, const void *k_pool, const void *v_pool, void *out, int dtype,
+                             const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
+                             int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
+                             int block_size, int max_blocks_per_seq, cudaStream_t s) {
+    if (total_query_tokens <= 0) return cudaSuccess;
+    const size_t smem = (size_t)(head_dim + ATT_TILE) * sizeof(float);
+    attention_kernel<<<(unsigned)(total_query_tokens * n_heads), ATT_THREADS, smem, s>>>(
+        q, k_pool, v_pool, out, dtype == DT_BF16, block_table, query_starts, seq_lens, n_heads, n_kv_heads, head_dim,
+        block_size, max_blocks_per_seq, num_requests);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_elementwise(int op, const void *a, int a_dtype, const void *b, int b_dtype, void *out,
                                int out_dtype, size_t n, cudaStream_t s) {

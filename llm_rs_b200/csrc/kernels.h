@@ -54,6 +54,16 @@ cudaError_t launch_elementwise(int op, const void *a, int a_dtype, const void *b
 cudaError_t launch_rms_norm(const void *in, int in_dtype, const float *weight, void *out, int out_dtype, int dim,
                             int rows, float eps, cudaStream_t s);
 cudaError_t launch_argmax(const void *x, int dtype, uint32_t n, uint32_t *dev_out, cudaStream_t s);
+// Rotary embedding in place on x [row_stride, seq_len]; scatter (dst[index[r]] = src[r]) or gather
+// (dst[r] = src[index[r]]) of `rows` rows of row_bytes bytes; paged causal grouped-query attention.
+cudaError_t launch_rope(void *x, int dtype, const uint32_t *positions, int head_dim, float theta, int row_stride,
+                        int seq_len, int split_half, cudaStream_t s);
+cudaError_t launch_move_rows(void *dst, const void *src, const uint32_t *index, int scatter, size_t row_bytes,
+                             int rows, cudaStream_t s);
+cudaError_t launch_attention(const void *q, const void *k_pool, const void *v_pool, void *out, int dtype,
+                             const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
+                             int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
+                             int block_size, int max_blocks_per_seq, cudaStream_t s);
 
 // Decode matmul: integer dot products per scale group, float32 across groups; any M (tokens are
 // processed in passes of <= 4).  x_dtype / out_dtype are DT_F32 or DT_BF16.  err_word is a device

@@ -197,6 +197,75 @@ def argmax(x: np.ndarray) -> int:
     return int(np.argmax(np.asarray(x, dtype=np.float32)))
 
 
+def rope(x: np.ndarray, positions, head_dim: int, theta: float, *, split_half: bool = False,
+         bf16: bool = False) -> np.ndarray:
+    """shaders/ops.metal:1011-1042 on x [seq_len, row_stride] (rows of heads of head_dim): pair i of a
+    head is (2i, 2i+1), or (i, i + head_dim/2) when split_half; angle = position * theta^(-2i/head_dim);
+    (x0, x1) -> (x0 cos - x1 sin, x0 sin + x1 cos).  Frequency and angle are float32 values as in the
+    shader (the angle's rounding, position * 2^-24 radians, is part of the reference's result); cosine,
+    sine and the rotation are taken in double."""
+    v = np.asarray(x, dtype=np.float32).astype(np.float64)
+    seq, stride = v.shape
+    half = head_dim // 2
+    i = np.arange(half, dtype=np.float32)
+    freq = (np.float32(1.0) / np.power(np.float32(theta), np.float32(2.0) * i / np.float32(head_dim))).astype(np.float32)
+    out = v.copy()
+    for s in range(seq):
+        ang = (np.float32(int(positions[s])) * freq).astype(np.float32).astype(np.float64)
+        c, sn = np.cos(ang), np.sin(ang)
+        for h in range(stride // head_dim):
+            base = h * head_dim
+            ia = base + (np.arange(half) if split_half else 2 * np.arange(half))
+            ib = ia + half if split_half else ia + 1
+            x0, x1 = v[s, ia], v[s, ib]
+            out[s, ia] = x0 * c - x1 * sn
+            out[s, ib] = x0 * sn + x1 * c
+    return _round_io(out.astype(np.float32), bf16)
+
+
+def scatter_kv(pool: np.ndarray, src: np.ndarray, slot_mapping, kv_dim: int, num_tokens: int) -> np.ndarray:
+    """shaders/ops.metal:841-853: pool[slot_mapping[t] * kv_dim + d] = src[t * kv_dim + d]."""
+    out = np.array(pool, copy=True).reshape(-1, kv_dim)
+    s = np.asarray(src).reshape(-1)[:num_tokens * kv_dim].reshape(num_tokens, kv_dim)
+    for t in range(num_tokens):
+        out[int(slot_mapping[t])] = s[t]
+    return out.reshape(np.asarray(pool).shape)
+
+
+def gather(src: np.ndarray, indices, num_indices: int) -> np.ndarray:
+    """shaders/ops.metal:859-873 on src [seq_len, dim]: row c of the result = row indices[c]."""
+    return np.asarray(src)[[int(i) for i in indices[:num_indices]]]
+
+
+def attention(q: np.ndarray, k_pool: np.ndarray, v_pool: np.ndarray, block_table, query_starts, seq_lens,
+              n_heads: int, n_kv_heads: int, head_dim: int, block_size: int, max_blocks_per_seq: int,
+              *, bf16: bool = False) -> np.ndarray:
+    """shaders/ops.metal:636-758: q [total_query_tokens, n_heads * head_dim]; pools [slots, n_kv_heads *
+    head_dim] with slot = page * block_size + offset; request r owns query tokens query_starts[r] ..
+    query_starts[r+1], has seq_lens[r] positions, page p = block_table[r * max_blocks_per_seq + p];
+    query token i of c sees positions 0 .. seq_len - c + i; softmax(q.k / sqrt(head_dim)) v per head,
+    head h reading kv head h / (n_heads / n_kv_heads).  In double."""
+    qf = np.asarray(q, dtype=np.float32).astype(np.float64)
+    kf = np.asarray(k_pool, dtype=np.float32).astype(np.float64).reshape(-1, n_kv_heads * head_dim)
+    vf = np.asarray(v_pool, dtype=np.float32).astype(np.float64).reshape(-1, n_kv_heads * head_dim)
+    out = np.zeros_like(qf)
+    group = n_heads // n_kv_heads
+    for r in range(len(seq_lens)):
+        q0, q1 = int(query_starts[r]), int(query_starts[r + 1])
+        count = q1 - q0
+        for li in range(count):
+            n_pos = int(seq_lens[r]) - count + li + 1
+            slots = [int(block_table[r * max_blocks_per_seq + t // block_size]) * block_size + t % block_size
+                     for t in range(n_pos)]
+            for h in range(n_heads):
+                kv = (h // group) * head_dim
+                qq = qf[q0 + li, h * head_dim:(h + 1) * head_dim]
+                sc = kf[slots, kv:kv + head_dim] @ qq / np.sqrt(np.float64(head_dim))
+                p = np.exp(sc - sc.max())
+                out[q0 + li, h * head_dim:(h + 1) * head_dim] = (p / p.sum()) @ vf[slots, kv:kv + head_dim]
+    return _round_io(out.astype(np.float32), bf16)
+
+
 def matmul(dtype: int, w: np.ndarray, K: int, N: int, x: np.ndarray, *, acc: str = "f64",
            rows: tuple[int, int] | None = None, threads: int | None = None, fast: bool = False) -> np.ndarray:
     """Out[M, N] = X[M, K] . W[N, K]^T.  acc="f32": the reference's sequential float

@@ -371,6 +371,94 @@ def test_argmax(backend, n, bf16):
     assert backend.argmax(_upload_dense(backend, x, bf16)) == n // 2
 
 
+# ---------- rest of the trait: rms_norm_heads, rope, scatter_kv, gather, attention ----------
+
+def _dense(be, v, bf16):
+    """numpy [cols, dim] (or [dim]) -> buffer [dim, cols] of F32 or BF16, plus the values it holds."""
+    v = np.ascontiguousarray(v, np.float32)
+    held = O.bf16_bits_to_f32(synth.bf16_bits(v)).reshape(v.shape) if bf16 else v
+    shape = [v.shape[-1]] if v.ndim == 1 else [v.shape[-1], v.shape[0]]
+    data = synth.bf16_bits(v) if bf16 else v
+    return be.upload_tensor(TensorView("v", DType.BF16 if bf16 else DType.F32, shape, data)), held
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_rms_norm_heads(backend, bf16):
+    hd, heads, seq = 128, 6, 3
+    xb, x = _dense(backend, synth.activations(seq, heads * hd, tid=101) * np.float32(1.7), bf16)
+    w = (synth.activations(1, hd, tid=102).reshape(-1) * np.float32(0.1) + np.float32(1.0)).astype(np.float32)
+    backend.rms_norm_heads(xb, backend.upload_tensor(TensorView("w", DType.F32, [hd], w)), 1e-6)
+    backend.sync()
+    got = backend.read_to_vec_f32(xb).reshape(seq * heads, hd)
+    want = O.rms_norm(x.reshape(seq * heads, hd), w, 1e-6, bf16=bf16)
+    ulp = 2.0 ** -7 if bf16 else 2.0 ** -21
+    assert np.all(np.abs(got - want) <= ulp * np.maximum(np.abs(want), 1e-30))
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("split_half", [False, True])
+def test_rope(backend, split_half, bf16):
+    hd, seq = 128, 5
+    positions = [0, 1, 17, 4095, 100000]
+    qb, q = _dense(backend, synth.activations(seq, 4 * hd, tid=111), bf16)
+    kb, k = _dense(backend, synth.activations(seq, 2 * hd, tid=112), bf16)
+    backend.rope(qb, kb, backend.upload_u32(positions), hd, 500000.0, split_half)
+    backend.sync()
+    for buf, src in ((qb, q), (kb, k)):
+        got = backend.read_to_vec_f32(buf).reshape(src.shape)
+        want = O.rope(src, positions, hd, 500000.0, split_half=split_half, bf16=bf16)
+        # the angle is a float32 product of the position and a float32 power: a few units in its last
+        # place (position * 2^-22 radians) separate one powf from another, and the output moves with it
+        tol = np.abs(src).max() * ((2.0 ** -7 if bf16 else 2e-6) + np.array(positions, np.float64)[:, None] * 2.0 ** -21)
+        assert np.all(np.abs(got - want) <= tol)
+
+
+def test_scatter_kv_and_gather(backend):
+    kv_dim, slots, tokens = 256, 64, 5
+    pool = np.zeros((slots, kv_dim), np.float32)
+    src = synth.activations(tokens, kv_dim, tid=121)
+    mapping = [63, 0, 17, 18, 5]
+    pb, _ = _dense(backend, pool, True)
+    sb, held = _dense(backend, src, True)
+    backend.scatter_kv(pb, sb, backend.upload_u32(mapping), kv_dim, tokens)
+    backend.sync()
+    got = backend.read_to_vec_f32(pb).reshape(slots, kv_dim)
+    assert np.array_equal(got, O.scatter_kv(pool, held, mapping, kv_dim, tokens))
+    out = backend.alloc([kv_dim, 3], DType.BF16)
+    backend.gather(out, pb, backend.upload_u32([17, 63, 17]), 3)
+    backend.sync()
+    assert np.array_equal(backend.read_to_vec_f32(out).reshape(3, kv_dim), O.gather(got, [17, 63, 17], 3))
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("n_heads,n_kv,hd,block", [(4, 2, 128, 16), (8, 8, 64, 32), (2, 1, 256, 8)])
+def test_attention(backend, n_heads, n_kv, hd, block, bf16):
+    """Three requests in one call: a decode step deep into its pages, a prefill of 37 tokens (causal), a
+    decode step at position 0; pages scattered through the pool."""
+    seq_lens, q_counts = [300, 37, 1], [1, 37, 1]
+    max_blocks = (max(seq_lens) + block - 1) // block
+    n_pages = 3 * max_blocks + 5
+    rng = np.random.default_rng(7)
+    pages = rng.permutation(n_pages)
+    table = np.zeros((3, max_blocks), np.uint32)
+    for r in range(3):
+        table[r] = pages[r * max_blocks:(r + 1) * max_blocks]
+    starts = [0, 1, 38, 39]
+    total_q = 39
+    kvd = n_kv * hd
+    qb, q = _dense(backend, synth.activations(total_q, n_heads * hd, tid=131), bf16)
+    kb, k = _dense(backend, synth.activations(n_pages * block, kvd, tid=132), bf16)
+    vb, v = _dense(backend, synth.activations(n_pages * block, kvd, tid=133), bf16)
+    out = backend.alloc([n_heads * hd, total_q], DType.BF16 if bf16 else DType.F32)
+    backend.attention(out, qb, kb, vb, backend.upload_u32(table.reshape(-1)), backend.upload_u32(starts),
+                      backend.upload_u32(seq_lens), n_heads, n_kv, hd, block, max_blocks)
+    backend.sync()
+    got = backend.read_to_vec_f32(out).reshape(total_q, n_heads * hd)
+    want = O.attention(q, k, v, table.reshape(-1), starts, seq_lens, n_heads, n_kv, hd, block, max_blocks, bf16=bf16)
+    assert O.rel_l2(got, want) <= (4e-3 if bf16 else 2e-5)
+    assert np.abs(got - want).max() <= (2e-2 if bf16 else 1e-4)
+
+
 # ---------- embedding lookup (Backend::embed) ----------
 
 @pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])

@@ -280,3 +280,26 @@ def test_small_ops_known_values():
     assert O.argmax(np.array([1.0, 5.0, 5.0, -2.0], np.float32)) == 1
     # bf16 output is a single round-to-nearest-even of the float32 result
     assert O.add(np.array([1.0], np.float32), np.array([2.0 ** -9], np.float32), bf16=True)[0] == 1.0
+
+
+def test_rope_scatter_gather_attention_known_values():
+    # rope: position 0 leaves x alone; a quarter turn of pair 0 (angle = position * 1) maps (1, 0) to (cos, sin)
+    x = np.array([[1.0, 0.0, 2.0, 3.0]], np.float32)
+    assert np.array_equal(O.rope(x, [0], 4, 10000.0), x)
+    got = O.rope(x, [1], 4, 10000.0)
+    assert np.allclose(got[0, :2], [np.cos(1.0), np.sin(1.0)], atol=1e-7)
+    a = 1.0 / 10000.0 ** 0.5                                            # pair 1: theta^(-2/4)
+    assert np.allclose(got[0, 2:], [2 * np.cos(a) - 3 * np.sin(a), 2 * np.sin(a) + 3 * np.cos(a)], atol=1e-6)
+    sp = O.rope(x, [1], 4, 10000.0, split_half=True)                    # pairs (0, 2) and (1, 3)
+    assert np.allclose(sp[0, [0, 2]], [np.cos(1.0) - 2 * np.sin(1.0), np.sin(1.0) + 2 * np.cos(1.0)], atol=1e-6)
+    # scatter / gather
+    pool = np.zeros((4, 2), np.float32)
+    out = O.scatter_kv(pool, np.array([[1, 2], [3, 4]], np.float32), [3, 0], 2, 2)
+    assert np.array_equal(out, [[3, 4], [0, 0], [0, 0], [1, 2]])
+    assert np.array_equal(O.gather(out, [3, 3, 0], 3), [[1, 2], [1, 2], [3, 4]])
+    # attention: one head, two positions with equal keys -> the mean of the values; causal for the first query token
+    k = np.zeros((4, 32), np.float32); v = np.zeros((4, 32), np.float32)
+    v[2], v[3] = 1.0, 3.0                                               # page 1 (block_size 2) holds positions 0, 1
+    q = np.ones((2, 32), np.float32)
+    o = O.attention(q, k, v, [1], [0, 2], [2], 1, 1, 32, 2, 1)
+    assert np.allclose(o[0], 1.0) and np.allclose(o[1], 2.0)
