@@ -608,6 +608,47 @@ def extra_measurements(be_factory, stream, peak_gbs):
                                                           "frac_of_hbm_peak": round(nbytes / t / 1e9 / peak_gbs, 4)}
             table.free()
             o.free()
+        # the other ops of a decode step (8B shapes): time per call, and attention's KV bytes per second
+        out["other_ops"] = {}
+
+        def time_call(fn, iters=50):
+            for _ in range(3):
+                fn()
+            be.sync()
+            be.reset_gpu_secs()
+            for _ in range(iters):
+                fn()
+            be.sync()
+            return be.gpu_secs_total() / iters
+
+        hd, nh, nkv, blk = 128, 32, 8, 256
+        xa = be.upload_tensor(TensorView("x", DType.BF16, [4096], synth.bf16_bits(synth.activations(1, 4096, tid=9))))
+        xo = be.alloc([4096], DType.BF16)
+        nw = be.upload_tensor(TensorView("w", DType.F32, [4096], np.ones(4096, np.float32)))
+        out["other_ops"]["rms_norm_4096_us"] = round(time_call(lambda: be.rms_norm(xo, xa, nw, 1e-5)) * 1e6, 2)
+        out["other_ops"]["add_4096_us"] = round(time_call(lambda: be.add(xo, xa, xa)) * 1e6, 2)
+        kx = be.upload_tensor(TensorView("k", DType.BF16, [1024], synth.bf16_bits(synth.activations(1, 1024, tid=8))))
+        pos = be.upload_u32([4095])
+        out["other_ops"]["rope_q4096_k1024_us"] = round(time_call(lambda: be.rope(xa, kx, pos, hd, 500000.0)) * 1e6, 2)
+        for name, n_req, ctx_len, q_per in (("decode_8x4096", 8, 4096, 1), ("prefill_1x512", 1, 512, 512)):
+            pages_per = (ctx_len + blk - 1) // blk
+            n_slots = n_req * pages_per * blk
+            kp = be.upload_tensor(TensorView("k", DType.BF16, [nkv * hd, n_slots],
+                                             synth.bf16_bits(synth.activations(n_slots, nkv * hd, tid=11))))
+            vp = be.upload_tensor(TensorView("v", DType.BF16, [nkv * hd, n_slots],
+                                             synth.bf16_bits(synth.activations(n_slots, nkv * hd, tid=12))))
+            tq = n_req * q_per
+            qb = be.upload_tensor(TensorView("q", DType.BF16, [nh * hd] if tq == 1 else [nh * hd, tq],
+                                             synth.bf16_bits(synth.activations(tq, nh * hd, tid=13))))
+            ob = be.alloc([nh * hd] if tq == 1 else [nh * hd, tq], DType.BF16)
+            bt = be.upload_u32(np.arange(n_req * pages_per, dtype=np.uint32))
+            qs = be.upload_u32([i * q_per for i in range(n_req + 1)])
+            sl = be.upload_u32([ctx_len] * n_req)
+            t = time_call(lambda: be.attention(ob, qb, kp, vp, bt, qs, sl, nh, nkv, hd, blk, pages_per), 10)
+            kv_bytes = 2 * n_req * ctx_len * nkv * hd * 2
+            out["other_ops"][f"attention_{name}"] = {"us": round(t * 1e6, 1), "kv_GBps": round(kv_bytes / t / 1e9, 1)}
+            for b in (kp, vp, qb, ob, bt, qs, sl):
+                b.free()
         # config 4: the 225 matmuls of one Llama-3-8B decode step (32 x {wq, wk, wv, wo, gate, up: Q4_K;
         # down: Q6_K} + output: Q6_K), back to back; norms, rope and attention are outside this path.
         layer = [(Q4K, 4096, 4096), (Q4K, 4096, 1024), (Q4K, 4096, 1024), (Q4K, 4096, 4096),
