@@ -37,6 +37,8 @@ struct llmrs_ctx {
     size_t scratch_bytes = 0;
     bool pdl = true;                 // decode kernels overlap their prologue with the previous kernel's tail (LLMRS_NO_PDL=1: off)
     int gemm_split = -1;             // LLMRS_GEMM_SPLIT at creation: 0 never, 1 always, otherwise the estimate decides
+    float *att_ws = nullptr;         // partial results of attention over split sequences
+    size_t att_ws_bytes = 0;
     uint32_t *argmax_out = nullptr;  // device word argmax writes its result to
     uint32_t *tokens = nullptr;      // device copy of embed's token ids
     size_t tokens_cap = 0;
@@ -221,6 +223,7 @@ int llmrs_cuda_destroy(llmrs_ctx *ctx) {
     if (ctx->split_ws) cudaFree(ctx->split_ws);
     if (ctx->tokens) cudaFree(ctx->tokens);
     if (ctx->argmax_out) cudaFree(ctx->argmax_out);
+    if (ctx->att_ws) cudaFree(ctx->att_ws);
     delete ctx;
     return LLMRS_OK;
 }
@@ -547,7 +550,36 @@ int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, con
         return ctx->fail(LLMRS_ERR_SHAPE, "attention: q of %zu values, %zu requests, %zu query_starts, %zu page entries",
                          buf_elems(q), num_req, buf_elems(query_starts), buf_elems(block_table));
     DeviceGuard guard(ctx->device);
-    cudaError_t e = ctx->begin_work();
+    cudaError_t e;
+    if (attention_gqa_supported((int)q->dtype, (int)n_heads, (int)n_kv_heads, (int)head_dim)) {
+        // sequence lengths live on the device: the page table's capacity bounds them for the split count
+        const int splits = attention_splits((int)total_q, (int)n_kv_heads, (int)(block_size * max_blocks_per_seq), ctx->sm_count);
+        const size_t need = attention_workspace_bytes((int)total_q, (int)n_heads, (int)head_dim, splits);
+        if (need > ctx->att_ws_bytes) {              // grows outside stream capture only, like the scratch
+            cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+            cudaStreamIsCapturing(ctx->stream, &st);
+            if (st != cudaStreamCaptureStatusNone)
+                return ctx->fail(LLMRS_ERR_CUDA, "attention: workspace must grow (make one call outside graph capture)");
+            e = cudaStreamSynchronize(ctx->stream);
+            if (e == cudaSuccess && ctx->att_ws) e = cudaFree(ctx->att_ws);
+            ctx->att_ws = nullptr;
+            ctx->att_ws_bytes = 0;
+            if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->att_ws, need);
+            if (e != cudaSuccess) return ctx->cuda_fail(e, "attention: workspace");
+            ctx->att_ws_bytes = need;
+        }
+        e = ctx->begin_work();
+        if (e == cudaSuccess)
+            e = launch_attention_gqa(q->dptr, k_pool->dptr, v_pool->dptr, out->dptr, ctx->att_ws,
+                                     (const uint32_t *)block_table->dptr, (const uint32_t *)query_starts->dptr,
+                                     (const uint32_t *)seq_lens->dptr, (int)total_q, (int)num_req, (int)n_heads,
+                                     (int)n_kv_heads, (int)head_dim, (int)block_size, (int)max_blocks_per_seq, splits,
+                                     ctx->stream);
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "attention");
+        ctx->launches += splits > 1 ? 2 : 1;
+        return LLMRS_OK;
+    }
+    e = ctx->begin_work();
     if (e == cudaSuccess)
         e = launch_attention(q->dptr, k_pool->dptr, v_pool->dptr, out->dptr, (int)q->dtype,
                              (const uint32_t *)block_table->dptr, (const uint32_t *)query_starts->dptr,

@@ -235,7 +235,222 @@ attention_kernel(const void *q, const void *k_pool, const void *v_pool, void *ou
     }
 }
 
+// The same attention for bf16 buffers, organised around the memory traffic.  One CTA per (query
+// token, KV head, split of the sequence): the `GROUP` query heads that share a KV head are served
+// from ONE pass over its keys and values, which come into shared memory 64 positions at a time with
+// coalesced 16-byte loads (16 consecutive threads per 256-byte row).  Thread (position, half of the
+// heads) forms the scores from shared memory, a warp per head does the online-softmax bookkeeping,
+// thread d accumulates the values for all heads of the group.  A long sequence with few query
+// tokens (decode) is cut into `splits` ranges so that all SMs work; the partial (accumulator,
+// maximum, sum) triples are merged by attention_merge_kernel.
+constexpr int AT2_TILE = 64;
+constexpr int AT2_THREADS = 128;
+template <int HD, int GROUP>
+__global__ void __launch_bounds__(AT2_THREADS)
+attention_gqa_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k_pool,
+                     const uint16_t *__restrict__ v_pool, uint16_t *__restrict__ out, float *__restrict__ partial,
+                     const uint32_t *__restrict__ block_table, const uint32_t *__restrict__ query_starts,
+                     const uint32_t *__restrict__ seq_lens, int n_heads, int n_kv_heads, int block_size,
+                     int max_blocks_per_seq, int num_requests, int splits) {
+    constexpr int KROW = HD + 8;                         // padded key row (bf16): 16-byte reads of 8 rows hit 32 banks
+    __shared__ __align__(16) uint16_t k_s[AT2_TILE * KROW];
+    __shared__ __align__(16) uint16_t v_s[AT2_TILE * HD];
+    __shared__ __align__(16) float q_s[GROUP * HD];
+    __shared__ __align__(16) float p_s[AT2_TILE * GROUP];          // [position][head]
+    __shared__ float m_s[GROUP], l_s[GROUP], r_s[GROUP];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kvh = blockIdx.x % n_kv_heads, gq = blockIdx.x / n_kv_heads, split = blockIdx.y;
+    int req = 0;
+    while (req + 1 < num_requests && (uint32_t)gq >= query_starts[req + 1]) req++;
+    const int local_q = gq - (int)query_starts[req];
+    const int q_count = (int)query_starts[req + 1] - (int)query_starts[req];
+    const int causal_len = (int)seq_lens[req] - q_count + local_q + 1;
+    const int kv_dim = n_kv_heads * HD, kv_off = kvh * HD;
+    const float scale = rsqrtf((float)HD);
+    const size_t q_off = (size_t)gq * n_heads * HD + (size_t)kvh * GROUP * HD;       // the group's heads are adjacent
+    // this split's range of positions, whole tiles
+    const int tiles = (causal_len + AT2_TILE - 1) / AT2_TILE;
+    const int per = (tiles + splits - 1) / splits;
+    const int t_begin = min(split * per, tiles) * AT2_TILE, t_end = min(min((split + 1) * per, tiles) * AT2_TILE, causal_len);
+
+    for (int i = tid; i < GROUP * HD; i += AT2_THREADS) q_s[i] = bf16_bits_to_f32(q[q_off + i]) * scale;
+    if (tid < GROUP) { m_s[tid] = -INFINITY; l_s[tid] = 0.0f; }
+    float acc[GROUP];
+#pragma unroll
+    for (int h = 0; h < GROUP; h++) acc[h] = 0.0f;
+    __syncthreads();
+
+    constexpr int CH = HD / 8;                           // 16-byte chunks per row
+    for (int t0 = t_begin; t0 < t_end; t0 += AT2_TILE) {
+        const int tile_len = min(AT2_TILE, t_end - t0);
+        // ---- keys and values of the tile -> shared memory ----
+        for (int c = tid; c < AT2_TILE * CH; c += AT2_THREADS) {
+            const int j = c / CH, ch = c % CH;
+            uint4 kk = make_uint4(0, 0, 0, 0), vv = kk;
+            if (j < tile_len) {
+                const int t = t0 + j;
+                const uint32_t page = block_table[(size_t)req * max_blocks_per_seq + t / block_size];
+                const size_t row = ((size_t)page * block_size + (size_t)(t % block_size)) * kv_dim + kv_off;
+                kk = __ldg(reinterpret_cast<const uint4 *>(k_pool + row) + ch);
+                vv = __ldg(reinterpret_cast<const uint4 *>(v_pool + row) + ch);
+            }
+            *reinterpret_cast<uint4 *>(k_s + j * KROW + 8 * ch) = kk;
+            *reinterpret_cast<uint4 *>(v_s + j * HD + 8 * ch) = vv;
+        }
+        __syncthreads();
+        // ---- scores: thread (position j, half of the heads) ----
+        {
+            constexpr int HH = GROUP >= 2 ? GROUP / 2 : 1;          // heads per thread
+            const int j = tid % AT2_TILE, h0 = (tid / AT2_TILE) * HH;
+            if (GROUP >= 2 || tid < AT2_TILE) {
+                float dot[HH];
+#pragma unroll
+                for (int h = 0; h < HH; h++) dot[h] = 0.0f;
+#pragma unroll 4
+                for (int ch = 0; ch < CH; ch++) {
+                    const uint4 u = *reinterpret_cast<const uint4 *>(k_s + j * KROW + 8 * ch);
+                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+                    float kf[8];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        kf[2 * e] = __uint_as_float(w[e] << 16);
+                        kf[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+                    }
+#pragma unroll
+                    for (int h = 0; h < HH; h++) {
+                        const float4 qa = *reinterpret_cast<const float4 *>(q_s + (h0 + h) * HD + 8 * ch);
+                        const float4 qb = *reinterpret_cast<const float4 *>(q_s + (h0 + h) * HD + 8 * ch + 4);
+                        dot[h] = fmaf(qa.x, kf[0], fmaf(qa.y, kf[1], fmaf(qa.z, kf[2], fmaf(qa.w, kf[3], dot[h]))));
+                        dot[h] = fmaf(qb.x, kf[4], fmaf(qb.y, kf[5], fmaf(qb.z, kf[6], fmaf(qb.w, kf[7], dot[h]))));
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < HH; h++) p_s[j * GROUP + h0 + h] = j < tile_len ? dot[h] : -INFINITY;
+            }
+        }
+        __syncthreads();
+        // ---- online softmax: warp w keeps the books of heads w, w + 4 ----
+        for (int h = warp; h < GROUP; h += AT2_THREADS / 32) {
+            const float s0 = p_s[lane * GROUP + h], s1 = p_s[(lane + 32) * GROUP + h];
+            float mx = fmaxf(s0, s1);
+#pragma unroll
+            for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float m_old = m_s[h], m_new = fmaxf(m_old, mx);
+            const float e0 = __expf(s0 - m_new), e1 = __expf(s1 - m_new);
+            p_s[lane * GROUP + h] = e0;
+            p_s[(lane + 32) * GROUP + h] = e1;
+            float sum = e0 + e1;
+#pragma unroll
+            for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) {
+                const float r = __expf(m_old - m_new);
+                r_s[h] = r;
+                l_s[h] = l_s[h] * r + sum;
+                m_s[h] = m_new;
+            }
+        }
+        __syncthreads();
+        // ---- values: thread d, all heads of the group ----
+        for (int d = tid; d < HD; d += AT2_THREADS) {
+#pragma unroll
+            for (int h = 0; h < GROUP; h++) acc[h] *= r_s[h];
+            for (int j = 0; j < tile_len; j++) {
+                const float v = bf16_bits_to_f32(v_s[j * HD + d]);
+#pragma unroll
+                for (int h = 0; h < GROUP; h++) acc[h] = fmaf(p_s[j * GROUP + h], v, acc[h]);
+            }
+        }
+        __syncthreads();
+    }
+    for (int d = tid; d < HD; d += AT2_THREADS) {
+#pragma unroll
+        for (int h = 0; h < GROUP; h++) {
+            const int head = kvh * GROUP + h;
+            if (splits == 1) {
+                out[(size_t)gq * n_heads * HD + (size_t)head * HD + d] =
+                    __bfloat16_as_ushort(__float2bfloat16_rn(acc[h] / l_s[h]));
+            } else {
+                float *pr = partial + (((size_t)gq * n_heads + head) * splits + split) * (HD + 2);
+                pr[d] = acc[h];
+                if (d == 0) { pr[HD] = m_s[h]; pr[HD + 1] = l_s[h]; }
+            }
+        }
+    }
+}
+
+// out = sum_s acc_s e^(m_s - m) / sum_s l_s e^(m_s - m): one CTA of HD threads per (query token, head).
+__global__ void attention_merge_kernel(const float *__restrict__ partial, uint16_t *__restrict__ out, int hd, int splits) {
+    const size_t th = blockIdx.x;                        // token * n_heads + head
+    const float *pr = partial + th * splits * (hd + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < splits; s++) m = fmaxf(m, pr[s * (hd + 2) + hd]);
+    float l = 0.0f, a = 0.0f;
+    const int d = threadIdx.x;
+    for (int s = 0; s < splits; s++) {
+        const float ms = pr[s * (hd + 2) + hd];
+        const float w = ms == -INFINITY ? 0.0f : __expf(ms - m);
+        l = fmaf(pr[s * (hd + 2) + hd + 1], w, l);
+        a = fmaf(pr[s * (hd + 2) + d], w, a);
+    }
+    out[th * hd + d] = __bfloat16_as_ushort(__float2bfloat16_rn(a / l));
+}
+
 }  // namespace
+
+size_t attention_workspace_bytes(int total_query_tokens, int n_heads, int head_dim, int splits) {
+    return splits <= 1 ? 0 : (size_t)total_query_tokens * n_heads * splits * (head_dim + 2) * sizeof(float);
+}
+
+// How many ranges to cut the sequences into: enough CTAs for two per SM, ranges of at least four tiles.
+int attention_splits(int total_query_tokens, int n_kv_heads, int max_seq_len, int sm_count) {
+    const int ctas = total_query_tokens * n_kv_heads;
+    const int want = (2 * sm_count + ctas - 1) / ctas;
+    const int most = (max_seq_len + 4 * AT2_TILE - 1) / (4 * AT2_TILE);
+    const int s = want < most ? want : most;
+    return s < 1 ? 1 : (s > 32 ? 32 : s);
+}
+
+template <int HD>
+static cudaError_t launch_gqa_hd(int group, dim3 grid, cudaStream_t s, const uint16_t *q, const uint16_t *k,
+                                 const uint16_t *v, uint16_t *out, float *partial, const uint32_t *bt,
+                                 const uint32_t *qs, const uint32_t *sl, int n_heads, int n_kv, int block_size,
+                                 int max_blocks, int n_req, int splits) {
+#define LLMRS_GQA(G) attention_gqa_kernel<HD, G><<<grid, AT2_THREADS, 0, s>>>(q, k, v, out, partial, bt, qs, sl, n_heads, n_kv, block_size, max_blocks, n_req, splits)
+    switch (group) {
+        case 1: LLMRS_GQA(1); break;
+        case 2: LLMRS_GQA(2); break;
+        case 4: LLMRS_GQA(4); break;
+        case 8: LLMRS_GQA(8); break;
+        default: return cudaErrorInvalidValue;
+    }
+#undef LLMRS_GQA
+    return cudaGetLastError();
+}
+
+bool attention_gqa_supported(int dtype, int n_heads, int n_kv_heads, int head_dim) {
+    const int group = n_kv_heads ? n_heads / n_kv_heads : 0;
+    return dtype == DT_BF16 && (head_dim == 64 || head_dim == 128) && (group == 1 || group == 2 || group == 4 || group == 8);
+}
+
+cudaError_t launch_attention_gqa(const void *q, const void *k_pool, const void *v_pool, void *out, float *workspace,
+                                 const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
+                                 int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
+                                 int block_size, int max_blocks_per_seq, int splits, cudaStream_t s) {
+    if (total_query_tokens <= 0) return cudaSuccess;
+    const dim3 grid((unsigned)(total_query_tokens * n_kv_heads), (unsigned)splits);
+    const int group = n_heads / n_kv_heads;
+    cudaError_t e = head_dim == 128
+        ? launch_gqa_hd<128>(group, grid, s, (const uint16_t *)q, (const uint16_t *)k_pool, (const uint16_t *)v_pool,
+                             (uint16_t *)out, workspace, block_table, query_starts, seq_lens, n_heads, n_kv_heads,
+                             block_size, max_blocks_per_seq, num_requests, splits)
+        : launch_gqa_hd<64>(group, grid, s, (const uint16_t *)q, (const uint16_t *)k_pool, (const uint16_t *)v_pool,
+                            (uint16_t *)out, workspace, block_table, query_starts, seq_lens, n_heads, n_kv_heads,
+                            block_size, max_blocks_per_seq, num_requests, splits);
+    if (e != cudaSuccess || splits == 1) return e;
+    attention_merge_kernel<<<(unsigned)(total_query_tokens * n_heads), head_dim, 0, s>>>(workspace, (uint16_t *)out,
+                                                                                        head_dim, splits);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_rope(void *x, int dtype, const uint32_t *positions, int head_dim, float theta, int row_stride,
                         int seq_len, int split_half, cudaStream_t s) {

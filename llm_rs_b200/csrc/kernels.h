@@ -60,6 +60,17 @@ cudaError_t launch_rope(void *x, int dtype, const uint32_t *positions, int head_
                         int seq_len, int split_half, cudaStream_t s);
 cudaError_t launch_move_rows(void *dst, const void *src, const uint32_t *index, int scatter, size_t row_bytes,
                              int rows, cudaStream_t s);
+// The bf16 attention organised around its memory traffic (head_dim 64 or 128, 1/2/4/8 query heads per
+// KV head): one pass over a KV head's keys and values serves its whole group, long sequences are
+// cut into `splits` ranges (attention_splits) whose partial results go through `workspace`
+// (attention_workspace_bytes) and a merge kernel.
+bool attention_gqa_supported(int dtype, int n_heads, int n_kv_heads, int head_dim);
+int attention_splits(int total_query_tokens, int n_kv_heads, int max_seq_len, int sm_count);
+size_t attention_workspace_bytes(int total_query_tokens, int n_heads, int head_dim, int splits);
+cudaError_t launch_attention_gqa(const void *q, const void *k_pool, const void *v_pool, void *out, float *workspace,
+                                 const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
+                                 int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
+                                 int block_size, int max_blocks_per_seq, int splits, cudaStream_t s);
 cudaError_t launch_attention(const void *q, const void *k_pool, const void *v_pool, void *out, int dtype,
                              const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
                              int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,

@@ -413,6 +413,27 @@ def test_rope(backend, split_half, bf16):
         assert np.all(np.abs(got - want) <= tol)
 
 
+def test_attention_long_decode_splits(backend):
+    """Two decode requests deep into long sequences: the bf16 kernel cuts them into ranges whose partial
+    results are merged; one request ends in the middle of a tile."""
+    n_heads, n_kv, hd, block = 32, 8, 128, 256
+    seq_lens, max_blocks = [5000, 777], 20
+    rng = np.random.default_rng(9)
+    pages = rng.permutation(2 * max_blocks + 3)
+    table = np.stack([pages[:max_blocks], pages[max_blocks:2 * max_blocks]]).astype(np.uint32)
+    n_slots = (2 * max_blocks + 3) * block
+    qb, q = _dense(backend, synth.activations(2, n_heads * hd, tid=141), True)
+    kb, k = _dense(backend, synth.activations(n_slots, n_kv * hd, tid=142), True)
+    vb, v = _dense(backend, synth.activations(n_slots, n_kv * hd, tid=143), True)
+    out = backend.alloc([n_heads * hd, 2], DType.BF16)
+    backend.attention(out, qb, kb, vb, backend.upload_u32(table.reshape(-1)), backend.upload_u32([0, 1, 2]),
+                      backend.upload_u32(seq_lens), n_heads, n_kv, hd, block, max_blocks)
+    backend.sync()
+    got = backend.read_to_vec_f32(out).reshape(2, n_heads * hd)
+    want = O.attention(q, k, v, table.reshape(-1), [0, 1, 2], seq_lens, n_heads, n_kv, hd, block, max_blocks, bf16=True)
+    assert O.rel_l2(got, want) <= 4e-3 and np.abs(got - want).max() <= 2e-2
+
+
 def test_scatter_kv_and_gather(backend):
     kv_dim, slots, tokens = 256, 64, 5
     pool = np.zeros((slots, kv_dim), np.float32)
@@ -431,7 +452,8 @@ def test_scatter_kv_and_gather(backend):
 
 
 @pytest.mark.parametrize("bf16", [False, True])
-@pytest.mark.parametrize("n_heads,n_kv,hd,block", [(4, 2, 128, 16), (8, 8, 64, 32), (2, 1, 256, 8)])
+@pytest.mark.parametrize("n_heads,n_kv,hd,block", [(4, 2, 128, 16), (8, 8, 64, 32), (2, 1, 256, 8), (8, 1, 64, 16),
+                                                   (8, 2, 128, 256), (3, 1, 128, 16)])
 def test_attention(backend, n_heads, n_kv, hd, block, bf16):
     """Three requests in one call: a decode step deep into its pages, a prefill of 37 tokens (causal), a
     decode step at position 0; pages scattered through the pool."""
