@@ -707,6 +707,72 @@ def extra_measurements(be_factory, stream, peak_gbs):
                                                 "calls_per_step": 193}}
             for b in list(xs.values()) + list(outs.values()):
                 b.free()
+        # A whole decode step of the 8B shape through the trait: per layer rms_norm, q/k/v matmuls, rope,
+        # scatter_kv, paged attention, wo matmul, add, rms_norm, gate/up + silu * mul as one call, down
+        # matmul, add; then the final norm and the output projection.  One CUDA graph; the embedding
+        # lookup before it and the argmax after it move host data and are timed as they are.
+        out["decode_step_full"] = {}
+        hd, nh, nkv, blk, ctx_len = 128, 32, 8, 256, 1024
+        ones = be.upload_tensor(TensorView("n", DType.F32, [4096], np.ones(4096, np.float32)))
+        emb = be.upload_tensor(TensorView("e", DType.Q4K, [4096, 32000], synth.weight(Q4K, 4096, 32000, tid=500)))
+        for M in (1, 8):
+            shp = (lambda d: [d] if M == 1 else [d, M])
+            pages_per = (ctx_len + blk) // blk + 1
+            n_slots = M * pages_per * blk
+            pools = [(be.alloc([nkv * hd, n_slots], DType.BF16), be.alloc([nkv * hd, n_slots], DType.BF16)) for _ in range(32)]
+            kv_init = synth.bf16_bits(synth.activations(n_slots, nkv * hd, tid=501) * np.float32(0.3))
+            for kp, vp in pools:
+                be.write(kp, kv_init)
+                be.write(vp, kv_init)
+            bt = be.upload_u32(np.arange(M * pages_per, dtype=np.uint32))
+            qs = be.upload_u32(list(range(M + 1)))
+            sl = be.upload_u32([ctx_len + 1] * M)
+            pos = be.upload_u32([ctx_len] * M)
+            slots = be.upload_u32([r * pages_per * blk + ctx_len for r in range(M)])
+            x, x2, xn = (be.alloc(shp(4096), DType.BF16) for _ in range(3))
+            qb, ao, wo_o, ffn_o = (be.alloc(shp(4096), DType.BF16) for _ in range(4))
+            kb, vb = be.alloc(shp(1024), DType.BF16), be.alloc(shp(1024), DType.BF16)
+            gu = be.alloc(shp(14336), DType.BF16)
+            logits = be.alloc(shp(128256), DType.BF16)
+            toks = np.arange(M, dtype=np.uint32) + 17
+
+            def layers():
+                for l in range(32):
+                    wq, wk, wv, wo, w1, w3, w2 = sets[l % n_layer_sets]
+                    kp, vp = pools[l]
+                    be.rms_norm(xn, x, ones, 1e-5)
+                    be.matmul(qb, wq, xn)
+                    be.matmul(kb, wk, xn)
+                    be.matmul(vb, wv, xn)
+                    be.rope(qb, kb, pos, hd, 500000.0)
+                    be.scatter_kv(kp, kb, slots, nkv * hd, M)
+                    be.scatter_kv(vp, vb, slots, nkv * hd, M)
+                    be.attention(ao, qb, kp, vp, bt, qs, sl, nh, nkv, hd, blk, pages_per)
+                    be.matmul(wo_o, wo, ao)
+                    be.add(x2, x, wo_o)
+                    be.rms_norm(xn, x2, ones, 1e-5)
+                    be.matmul_gate_up(gu, w1, w3, xn)
+                    be.matmul(ffn_o, w2, gu)
+                    be.add(x, x2, ffn_o)
+                be.rms_norm(xn, x, ones, 1e-5)
+                be.matmul(logits, wout, xn)
+
+            be.embed(x, emb, toks)
+            t_graph = timed_graph(layers)
+            be.embed(x, emb, toks)                       # fresh activations: 32 random layers blow the scale up
+            be.sync()
+            t0 = time.perf_counter()
+            for _ in range(5):
+                be.embed(x, emb, toks)
+                be.argmax(logits) if M == 1 else be.sync()
+            t_edges = (time.perf_counter() - t0) / 5
+            out["decode_step_full"][f"m{M}_ctx{ctx_len}"] = {
+                "ms_graph": round(t_graph * 1e3, 4), "ms_embed_and_argmax_host_timed": round(t_edges * 1e3, 4),
+                "tok_per_s": round(M / (t_graph + t_edges), 1), "kernels_per_step": 32 * 15 + 2}
+            for b in [bt, qs, sl, pos, slots, x, x2, xn, qb, ao, wo_o, ffn_o, kb, vb, gu, logits] + [p for kv in pools for p in kv]:
+                b.free()
+        out["decode_step_full"]["note"] = ("random weights: the numbers in the activations are meaningless, the work is that "
+                                           "of a Llama-3-8B decode step at the stated context; argmax only at one token")
         out["decode_stack"]["note"] = ("linear stack only (225 matmuls, bf16 activations), one CUDA graph per step; "
                                        "weight bytes per step 4 841 250 816")
         be.close()

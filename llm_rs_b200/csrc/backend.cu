@@ -394,7 +394,7 @@ static int elementwise(llmrs_ctx *ctx, const char *name, int op, llmrs_buf *out,
     cudaError_t e = ctx->begin_work();
     if (e == cudaSuccess)
         e = launch_elementwise(op, a->dptr, (int)a->dtype, op ? b->dptr : nullptr, op ? (int)b->dtype : DT_F32, out->dptr,
-                               (int)out->dtype, n, ctx->stream);
+                               (int)out->dtype, n, ctx->stream, ctx->pdl);
     if (e != cudaSuccess) return ctx->cuda_fail(e, name);
     ctx->launches++;
     return LLMRS_OK;
@@ -422,7 +422,7 @@ int llmrs_cuda_rms_norm(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *input, 
     cudaError_t e = ctx->begin_work();
     if (e == cudaSuccess)
         e = launch_rms_norm(input->dptr, (int)input->dtype, (const float *)weight->dptr, out->dptr, (int)out->dtype,
-                            (int)dim, (int)rows, eps, ctx->stream);
+                            (int)dim, (int)rows, eps, ctx->stream, ctx->pdl);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "rms_norm");
     ctx->launches++;
     return LLMRS_OK;
@@ -457,7 +457,7 @@ int llmrs_cuda_rms_norm_heads(llmrs_ctx *ctx, llmrs_buf *x, const llmrs_buf *wei
     cudaError_t e = ctx->begin_work();
     if (e == cudaSuccess)
         e = launch_rms_norm(x->dptr, (int)x->dtype, (const float *)weight->dptr, x->dptr, (int)x->dtype, (int)dim,
-                            (int)(n / dim), eps, ctx->stream);
+                            (int)(n / dim), eps, ctx->stream, ctx->pdl);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "rms_norm_heads");
     ctx->launches++;
     return LLMRS_OK;
@@ -479,7 +479,7 @@ int llmrs_cuda_rope(llmrs_ctx *ctx, llmrs_buf *q, llmrs_buf *k, const llmrs_buf 
     llmrs_buf *both[2] = {q, k};
     for (int i = 0; i < 2 && e == cudaSuccess; i++) {
         e = launch_rope(both[i]->dptr, (int)both[i]->dtype, (const uint32_t *)positions->dptr, (int)head_dim, rope_theta,
-                        (int)both[i]->dim0, (int)seq, split_half != 0, ctx->stream);
+                        (int)both[i]->dim0, (int)seq, split_half != 0, ctx->stream, ctx->pdl);
         ctx->launches++;
     }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "rope");
@@ -501,7 +501,7 @@ int llmrs_cuda_scatter_kv(llmrs_ctx *ctx, llmrs_buf *pool, const llmrs_buf *src,
     cudaError_t e = ctx->begin_work();
     if (e == cudaSuccess)
         e = launch_move_rows(pool->dptr, src->dptr, (const uint32_t *)slot_mapping->dptr, 1,
-                             (size_t)kv_dim * dense_elem_bytes(src->dtype), (int)num_tokens, ctx->stream);
+                             (size_t)kv_dim * dense_elem_bytes(src->dtype), (int)num_tokens, ctx->stream, ctx->pdl);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "scatter_kv");
     ctx->launches++;
     return LLMRS_OK;
@@ -521,7 +521,7 @@ int llmrs_cuda_gather(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *src, cons
     cudaError_t e = ctx->begin_work();
     if (e == cudaSuccess)
         e = launch_move_rows(out->dptr, src->dptr, (const uint32_t *)indices->dptr, 0,
-                             (size_t)dim * dense_elem_bytes(src->dtype), (int)num_indices, ctx->stream);
+                             (size_t)dim * dense_elem_bytes(src->dtype), (int)num_indices, ctx->stream, ctx->pdl);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "gather");
     ctx->launches++;
     return LLMRS_OK;
@@ -574,7 +574,7 @@ int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, con
                                      (const uint32_t *)block_table->dptr, (const uint32_t *)query_starts->dptr,
                                      (const uint32_t *)seq_lens->dptr, (int)total_q, (int)num_req, (int)n_heads,
                                      (int)n_kv_heads, (int)head_dim, (int)block_size, (int)max_blocks_per_seq, splits,
-                                     ctx->stream);
+                                     ctx->stream, ctx->pdl);
         if (e != cudaSuccess) return ctx->cuda_fail(e, "attention");
         ctx->launches += splits > 1 ? 2 : 1;
         return LLMRS_OK;
@@ -584,7 +584,7 @@ int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, con
         e = launch_attention(q->dptr, k_pool->dptr, v_pool->dptr, out->dptr, (int)q->dtype,
                              (const uint32_t *)block_table->dptr, (const uint32_t *)query_starts->dptr,
                              (const uint32_t *)seq_lens->dptr, (int)total_q, (int)num_req, (int)n_heads, (int)n_kv_heads,
-                             (int)head_dim, (int)block_size, (int)max_blocks_per_seq, ctx->stream);
+                             (int)head_dim, (int)block_size, (int)max_blocks_per_seq, ctx->stream, ctx->pdl);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "attention");
     ctx->launches++;
     return LLMRS_OK;

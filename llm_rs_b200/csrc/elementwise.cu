@@ -6,6 +6,7 @@
 // to the output type.
 #include "kernels.h"
 #include "llmrs_common.cuh"
+#include "pipeline.cuh"
 
 namespace llmrs {
 
@@ -22,6 +23,7 @@ __device__ __forceinline__ void store_f(void *p, size_t i, float v, int bf16) {
 // op 0: out = silu(a); 1: out = a * b; 2: out = a + b
 __global__ void binary_kernel(int op, const void *a, int a_bf16, const void *b, int b_bf16, void *out, int out_bf16,
                               size_t n) {
+    pdl_prologue();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float x = load_f(a, i, a_bf16);
@@ -35,6 +37,7 @@ __global__ void binary_kernel(int op, const void *a, int a_bf16, const void *b, 
 // One CTA per token row: inv = rsqrt(mean(v^2) + eps); out = v * inv * weight.
 __global__ void __launch_bounds__(256)
 rms_norm_kernel(const void *in, int in_bf16, const float *__restrict__ weight, void *out, int out_bf16, int dim, float eps) {
+    pdl_prologue();
     __shared__ float red[8];
     __shared__ float inv_s;
     const size_t off = (size_t)blockIdx.x * dim;
@@ -60,6 +63,7 @@ rms_norm_kernel(const void *in, int in_bf16, const float *__restrict__ weight, v
 
 // Index of the largest value (the smallest such index on ties; NaNs never win), one CTA.
 __global__ void __launch_bounds__(1024) argmax_kernel(const void *x, int bf16, uint32_t n, uint32_t *out) {
+    pdl_prologue();
     __shared__ float sv[32];
     __shared__ uint32_t si[32];
     float best = -INFINITY;
@@ -95,6 +99,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const void *x, int bf16, u
 // angle = position * theta^(-2i / head_dim).  One thread per pair.
 __global__ void rope_kernel(void *x, int bf16, const uint32_t *__restrict__ positions, int head_dim, float theta,
                             int pairs_per_row, int row_stride, int split_half) {
+    pdl_prologue();
     const int pair = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
     if (pair >= pairs_per_row) return;
     const int half = head_dim / 2, head = pair / half, i = pair % half;
@@ -115,6 +120,7 @@ __global__ void rope_kernel(void *x, int bf16, const uint32_t *__restrict__ posi
 // elements of `esz` bytes moved by index; one of the two index sides is the identity.
 __global__ void move_rows_kernel(uint8_t *dst, const uint8_t *src, const uint32_t *__restrict__ index, int scatter,
                                  size_t row_bytes, int rows) {
+    pdl_prologue();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;      // one 2-byte unit each
     const size_t units = row_bytes / 2;
     if (i >= units * rows) return;
@@ -136,6 +142,7 @@ attention_kernel(const void *q, const void *k_pool, const void *v_pool, void *ou
                  const uint32_t *__restrict__ block_table, const uint32_t *__restrict__ query_starts,
                  const uint32_t *__restrict__ seq_lens, int n_heads, int n_kv_heads, int head_dim, int block_size,
                  int max_blocks_per_seq, int num_requests) {
+    pdl_prologue();
     extern __shared__ float att_smem[];
     float *qs = att_smem;                   // [head_dim]
     float *scores = qs + head_dim;          // [ATT_TILE]
@@ -252,6 +259,7 @@ attention_gqa_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict_
                      const uint32_t *__restrict__ block_table, const uint32_t *__restrict__ query_starts,
                      const uint32_t *__restrict__ seq_lens, int n_heads, int n_kv_heads, int block_size,
                      int max_blocks_per_seq, int num_requests, int splits) {
+    pdl_prologue();
     constexpr int KROW = HD + 8;                         // padded key row (bf16): 16-byte reads of 8 rows hit 32 banks
     __shared__ __align__(16) uint16_t k_s[AT2_TILE * KROW];
     __shared__ __align__(16) uint16_t v_s[AT2_TILE * HD];
@@ -380,6 +388,7 @@ attention_gqa_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict_
 
 // out = sum_s acc_s e^(m_s - m) / sum_s l_s e^(m_s - m): one CTA of HD threads per (query token, head).
 __global__ void attention_merge_kernel(const float *__restrict__ partial, uint16_t *__restrict__ out, int hd, int splits) {
+    pdl_prologue();
     const size_t th = blockIdx.x;                        // token * n_heads + head
     const float *pr = partial + th * splits * (hd + 2);
     float m = -INFINITY;
@@ -414,17 +423,16 @@ template <int HD>
 static cudaError_t launch_gqa_hd(int group, dim3 grid, cudaStream_t s, const uint16_t *q, const uint16_t *k,
                                  const uint16_t *v, uint16_t *out, float *partial, const uint32_t *bt,
                                  const uint32_t *qs, const uint32_t *sl, int n_heads, int n_kv, int block_size,
-                                 int max_blocks, int n_req, int splits) {
-#define LLMRS_GQA(G) attention_gqa_kernel<HD, G><<<grid, AT2_THREADS, 0, s>>>(q, k, v, out, partial, bt, qs, sl, n_heads, n_kv, block_size, max_blocks, n_req, splits)
+                                 int max_blocks, int n_req, int splits, bool pdl) {
+#define LLMRS_GQA(G) return launch_dependent(attention_gqa_kernel<HD, G>, grid, dim3(AT2_THREADS), 0, s, pdl, q, k, v, out, partial, bt, qs, sl, n_heads, n_kv, block_size, max_blocks, n_req, splits)
     switch (group) {
-        case 1: LLMRS_GQA(1); break;
-        case 2: LLMRS_GQA(2); break;
-        case 4: LLMRS_GQA(4); break;
-        case 8: LLMRS_GQA(8); break;
+        case 1: LLMRS_GQA(1);
+        case 2: LLMRS_GQA(2);
+        case 4: LLMRS_GQA(4);
+        case 8: LLMRS_GQA(8);
         default: return cudaErrorInvalidValue;
     }
 #undef LLMRS_GQA
-    return cudaGetLastError();
 }
 
 bool attention_gqa_supported(int dtype, int n_heads, int n_kv_heads, int head_dim) {
@@ -435,66 +443,61 @@ bool attention_gqa_supported(int dtype, int n_heads, int n_kv_heads, int head_di
 cudaError_t launch_attention_gqa(const void *q, const void *k_pool, const void *v_pool, void *out, float *workspace,
                                  const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
                                  int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
-                                 int block_size, int max_blocks_per_seq, int splits, cudaStream_t s) {
+                                 int block_size, int max_blocks_per_seq, int splits, cudaStream_t s, bool pdl) {
     if (total_query_tokens <= 0) return cudaSuccess;
     const dim3 grid((unsigned)(total_query_tokens * n_kv_heads), (unsigned)splits);
     const int group = n_heads / n_kv_heads;
     cudaError_t e = head_dim == 128
         ? launch_gqa_hd<128>(group, grid, s, (const uint16_t *)q, (const uint16_t *)k_pool, (const uint16_t *)v_pool,
                              (uint16_t *)out, workspace, block_table, query_starts, seq_lens, n_heads, n_kv_heads,
-                             block_size, max_blocks_per_seq, num_requests, splits)
+                             block_size, max_blocks_per_seq, num_requests, splits, pdl)
         : launch_gqa_hd<64>(group, grid, s, (const uint16_t *)q, (const uint16_t *)k_pool, (const uint16_t *)v_pool,
                             (uint16_t *)out, workspace, block_table, query_starts, seq_lens, n_heads, n_kv_heads,
-                            block_size, max_blocks_per_seq, num_requests, splits);
+                            block_size, max_blocks_per_seq, num_requests, splits, pdl);
     if (e != cudaSuccess || splits == 1) return e;
-    attention_merge_kernel<<<(unsigned)(total_query_tokens * n_heads), head_dim, 0, s>>>(workspace, (uint16_t *)out,
-                                                                                        head_dim, splits);
-    return cudaGetLastError();
+    return launch_dependent(attention_merge_kernel, dim3((unsigned)(total_query_tokens * n_heads)), dim3(head_dim), 0, s,
+                            pdl, (const float *)workspace, (uint16_t *)out, head_dim, splits);
 }
 
 cudaError_t launch_rope(void *x, int dtype, const uint32_t *positions, int head_dim, float theta, int row_stride,
-                        int seq_len, int split_half, cudaStream_t s) {
+                        int seq_len, int split_half, cudaStream_t s, bool pdl) {
     const int pairs = row_stride / 2;
     if (pairs <= 0 || seq_len <= 0) return cudaSuccess;
-    rope_kernel<<<dim3((unsigned)((pairs + 255) / 256), (unsigned)seq_len), 256, 0, s>>>(
-        x, dtype == DT_BF16, positions, head_dim, theta, pairs, row_stride, split_half);
-    return cudaGetLastError();
+    return launch_dependent(rope_kernel, dim3((unsigned)((pairs + 255) / 256), (unsigned)seq_len), dim3(256), 0, s, pdl, x,
+                            (int)(dtype == DT_BF16), positions, head_dim, theta, pairs, row_stride, split_half);
 }
 
 cudaError_t launch_move_rows(void *dst, const void *src, const uint32_t *index, int scatter, size_t row_bytes,
-                             int rows, cudaStream_t s) {
+                             int rows, cudaStream_t s, bool pdl) {
     const size_t n = row_bytes / 2 * (size_t)rows;
     if (n == 0) return cudaSuccess;
-    move_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>((uint8_t *)dst, (const uint8_t *)src, index, scatter,
-                                                               row_bytes, rows);
-    return cudaGetLastError();
+    return launch_dependent(move_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, pdl, (uint8_t *)dst,
+                            (const uint8_t *)src, index, scatter, row_bytes, rows);
 }
 
 cudaError_t launch_attention(const void *q, const void *k_pool, const void *v_pool, void *out, int dtype,
                              const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
                              int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
-                             int block_size, int max_blocks_per_seq, cudaStream_t s) {
+                             int block_size, int max_blocks_per_seq, cudaStream_t s, bool pdl) {
     if (total_query_tokens <= 0) return cudaSuccess;
     const size_t smem = (size_t)(head_dim + ATT_TILE) * sizeof(float);
-    attention_kernel<<<(unsigned)(total_query_tokens * n_heads), ATT_THREADS, smem, s>>>(
-        q, k_pool, v_pool, out, dtype == DT_BF16, block_table, query_starts, seq_lens, n_heads, n_kv_heads, head_dim,
-        block_size, max_blocks_per_seq, num_requests);
-    return cudaGetLastError();
+    return launch_dependent(attention_kernel, dim3((unsigned)(total_query_tokens * n_heads)), dim3(ATT_THREADS), smem, s,
+                            pdl, q, k_pool, v_pool, out, (int)(dtype == DT_BF16), block_table, query_starts, seq_lens,
+                            n_heads, n_kv_heads, head_dim, block_size, max_blocks_per_seq, num_requests);
 }
 
 cudaError_t launch_elementwise(int op, const void *a, int a_dtype, const void *b, int b_dtype, void *out,
-                               int out_dtype, size_t n, cudaStream_t s) {
+                               int out_dtype, size_t n, cudaStream_t s, bool pdl) {
     if (n == 0) return cudaSuccess;
-    binary_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(op, a, a_dtype == DT_BF16, b, b_dtype == DT_BF16, out,
-                                                             out_dtype == DT_BF16, n);
-    return cudaGetLastError();
+    return launch_dependent(binary_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, pdl, op, a,
+                            (int)(a_dtype == DT_BF16), b, (int)(b_dtype == DT_BF16), out, (int)(out_dtype == DT_BF16), n);
 }
 
 cudaError_t launch_rms_norm(const void *in, int in_dtype, const float *weight, void *out, int out_dtype, int dim,
-                            int rows, float eps, cudaStream_t s) {
+                            int rows, float eps, cudaStream_t s, bool pdl) {
     if (dim <= 0 || rows <= 0) return cudaSuccess;
-    rms_norm_kernel<<<(unsigned)rows, 256, 0, s>>>(in, in_dtype == DT_BF16, weight, out, out_dtype == DT_BF16, dim, eps);
-    return cudaGetLastError();
+    return launch_dependent(rms_norm_kernel, dim3((unsigned)rows), dim3(256), 0, s, pdl, in, (int)(in_dtype == DT_BF16),
+                            weight, out, (int)(out_dtype == DT_BF16), dim, eps);
 }
 
 cudaError_t launch_argmax(const void *x, int dtype, uint32_t n, uint32_t *dev_out, cudaStream_t s) {

@@ -47,19 +47,21 @@ cudaError_t launch_dequant(int wdtype, const uint8_t *w, int K, int N, float *ou
 cudaError_t launch_embed(int wdtype, const uint8_t *table, int K, uint32_t vocab, const uint32_t *dev_tokens,
                          int n_tokens, void *out, int out_dtype, uint32_t *err_word, cudaStream_t s);
 
+// (pdl, here and below: launch with programmatic stream serialization; the kernels wait for their
+// predecessor before touching memory, so only the launch latency between dependent kernels goes.)
 // Element-wise ops on n values (op 0: out = silu(a); 1: out = a * b; 2: out = a + b), per-row RMS norm
 // ([rows] rows of dim values, float32 weight[dim]) and argmax of n values into *dev_out.
 cudaError_t launch_elementwise(int op, const void *a, int a_dtype, const void *b, int b_dtype, void *out,
-                               int out_dtype, size_t n, cudaStream_t s);
+                               int out_dtype, size_t n, cudaStream_t s, bool pdl);
 cudaError_t launch_rms_norm(const void *in, int in_dtype, const float *weight, void *out, int out_dtype, int dim,
-                            int rows, float eps, cudaStream_t s);
+                            int rows, float eps, cudaStream_t s, bool pdl);
 cudaError_t launch_argmax(const void *x, int dtype, uint32_t n, uint32_t *dev_out, cudaStream_t s);
 // Rotary embedding in place on x [row_stride, seq_len]; scatter (dst[index[r]] = src[r]) or gather
 // (dst[r] = src[index[r]]) of `rows` rows of row_bytes bytes; paged causal grouped-query attention.
 cudaError_t launch_rope(void *x, int dtype, const uint32_t *positions, int head_dim, float theta, int row_stride,
-                        int seq_len, int split_half, cudaStream_t s);
+                        int seq_len, int split_half, cudaStream_t s, bool pdl);
 cudaError_t launch_move_rows(void *dst, const void *src, const uint32_t *index, int scatter, size_t row_bytes,
-                             int rows, cudaStream_t s);
+                             int rows, cudaStream_t s, bool pdl);
 // The bf16 attention organised around its memory traffic (head_dim 64 or 128, 1/2/4/8 query heads per
 // KV head): one pass over a KV head's keys and values serves its whole group, long sequences are
 // cut into `splits` ranges (attention_splits) whose partial results go through `workspace`
@@ -70,11 +72,11 @@ size_t attention_workspace_bytes(int total_query_tokens, int n_heads, int head_d
 cudaError_t launch_attention_gqa(const void *q, const void *k_pool, const void *v_pool, void *out, float *workspace,
                                  const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
                                  int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
-                                 int block_size, int max_blocks_per_seq, int splits, cudaStream_t s);
+                                 int block_size, int max_blocks_per_seq, int splits, cudaStream_t s, bool pdl);
 cudaError_t launch_attention(const void *q, const void *k_pool, const void *v_pool, void *out, int dtype,
                              const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
                              int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
-                             int block_size, int max_blocks_per_seq, cudaStream_t s);
+                             int block_size, int max_blocks_per_seq, cudaStream_t s, bool pdl);
 
 // Decode matmul: integer dot products per scale group, float32 across groups; any M (tokens are
 // processed in passes of <= 4).  x_dtype / out_dtype are DT_F32 or DT_BF16.  err_word is a device

@@ -2,6 +2,7 @@
 // WAIT_LIMIT polls it gives up, the caller records an error code and leaves the kernel, so a
 // logic error can not spin a shared GPU forever.
 #pragma once
+#include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace llmrs {
@@ -105,6 +106,33 @@ __device__ __forceinline__ bool mailbox_wait(const uint2 *w, uint32_t tag, uint3
         __nanosleep(32);
     }
     return false;
+}
+
+// Programmatic dependent launch for the short kernels of a decode step.  Launched with programmatic
+// stream serialization, a kernel's CTAs may become resident while its predecessor in the stream is
+// still running; pdl_prologue() at the top of the kernel first lets the NEXT kernel do the same and
+// then waits until the predecessor has completed and its writes are visible.  Nothing is read or
+// written before that, so the semantics are those of a plain launch; what is saved is the launch
+// latency between dependent kernels (2-3 us each, several hundred kernels per decode step).
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                    bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 }  // namespace llmrs
