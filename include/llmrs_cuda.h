@@ -154,6 +154,13 @@ int llmrs_cuda_rms_norm_heads(llmrs_ctx *ctx, llmrs_buf *x, const llmrs_buf *wei
 int llmrs_cuda_rope(llmrs_ctx *ctx, llmrs_buf *q, llmrs_buf *k, const llmrs_buf *positions, uint32_t head_dim,
                     float rope_theta, uint32_t split_half);
 
+/* rope(q, k) and the two scatter_kv calls that follow it in a layer (src/arch/llama.rs:156-158) as one
+ * call and one launch: q and k are rotated in place, the rotated k and v are written to the slots
+ * slot_mapping[t] of k_pool and v_pool (kv_dim = k.dim0).  All five of one element type. */
+int llmrs_cuda_rope_scatter_kv(llmrs_ctx *ctx, llmrs_buf *q, llmrs_buf *k, const llmrs_buf *v, const llmrs_buf *positions,
+                               uint32_t head_dim, float rope_theta, uint32_t split_half, llmrs_buf *k_pool,
+                               llmrs_buf *v_pool, const llmrs_buf *slot_mapping);
+
 /* Replaces Backend::scatter_kv (src/backend/mod.rs:68-69; shaders/ops.metal:841-853):
  * pool[slot_mapping[t] * kv_dim + d] = src[t * kv_dim + d] for t < num_tokens. */
 int llmrs_cuda_scatter_kv(llmrs_ctx *ctx, llmrs_buf *pool, const llmrs_buf *src, const llmrs_buf *slot_mapping,
@@ -175,6 +182,24 @@ int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, con
                          const llmrs_buf *v_pool, const llmrs_buf *block_table, const llmrs_buf *query_starts,
                          const llmrs_buf *seq_lens, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
                          uint32_t block_size, uint32_t max_blocks_per_seq);
+
+/* out = residual + matmul(weight, input): the pairs matmul, add of src/arch/llama.rs:162-163 and
+ * 168-169 as one call.  Up to LLMRS_GEMV_MAX_M tokens the decode kernel adds the residual as it
+ * writes its results (no second kernel, no second pass over the output); above that the matmul is
+ * followed by the add kernel.  residual has the shape of out, F32 or BF16, and may be `out` itself. */
+int llmrs_cuda_matmul_add(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input,
+                          const llmrs_buf *residual);
+
+/* rms_norm followed by matmul (src/arch/llama.rs:152-155), and rms_norm followed by the feed-forward
+ * front (llama.rs:164-168), as one call each: out = matmul(weight, rms_norm(input, norm_weight, eps)).
+ * Up to LLMRS_GEMV_MAX_M tokens the decode kernel normalises the activations while it stages them
+ * (every CTA forms the row's sum of squares itself: 4096 values), so the norm costs no launch and no
+ * pass over memory, and the normalised activations are never rounded to bf16 in between.  Otherwise
+ * the norm runs into a temporary first.  norm_weight is F32 [in_features]. */
+int llmrs_cuda_rms_norm_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input,
+                               const llmrs_buf *norm_weight, float eps);
+int llmrs_cuda_rms_norm_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w_gate, const llmrs_buf *w_up,
+                                       const llmrs_buf *input, const llmrs_buf *norm_weight, float eps);
 
 /* The front of the feed-forward block in one call: out = silu(gate) * up with gate = matmul(w_gate,
  * input) and up = matmul(w_up, input), i.e. the four calls matmul, matmul, silu, mul of

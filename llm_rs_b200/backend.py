@@ -92,9 +92,14 @@ ABI = {
     "llmrs_cuda_argmax": (C.c_int, [_VP, _BUFP, C.POINTER(C.c_uint32)]),
     "llmrs_cuda_rms_norm_heads": (C.c_int, [_VP, _BUFP, _BUFP, C.c_float]),
     "llmrs_cuda_rope": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_uint32, C.c_float, C.c_uint32]),
+    "llmrs_cuda_rope_scatter_kv": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, _BUFP, C.c_uint32, C.c_float, C.c_uint32,
+                                             _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_scatter_kv": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_uint32, C.c_uint32]),
     "llmrs_cuda_gather": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_uint32]),
     "llmrs_cuda_attention": (C.c_int, [_VP] + [_BUFP] * 7 + [C.c_uint32] * 5),
+    "llmrs_cuda_rms_norm_matmul": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, _BUFP, C.c_float]),
+    "llmrs_cuda_rms_norm_matmul_gate_up": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, _BUFP, _BUFP, C.c_float]),
+    "llmrs_cuda_matmul_add": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_matmul_gate_up": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_embed": (C.c_int, [_VP, _BUFP, _BUFP, C.POINTER(C.c_uint32), C.c_uint32]),
     "llmrs_cuda_matmul_allgather": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, C.c_uint32, C.c_uint32, C.POINTER(_VP), _VP]),
@@ -306,6 +311,15 @@ class CudaBackend:
         self._check(self._lib.llmrs_cuda_rope(self._ctx, C.byref(q._raw), C.byref(k._raw), C.byref(positions._raw),
                                               head_dim, float(rope_theta), 1 if split_half else 0))
 
+    def rope_scatter_kv(self, q: CudaBuffer, k: CudaBuffer, v: CudaBuffer, positions: CudaBuffer, head_dim: int,
+                        rope_theta: float, k_pool: CudaBuffer, v_pool: CudaBuffer, slot_mapping: CudaBuffer,
+                        split_half: bool = False) -> None:
+        """rope(q, k) + scatter_kv(k_pool, k) + scatter_kv(v_pool, v) (src/arch/llama.rs:156-158) as one call."""
+        self._check(self._lib.llmrs_cuda_rope_scatter_kv(self._ctx, C.byref(q._raw), C.byref(k._raw), C.byref(v._raw),
+                                                         C.byref(positions._raw), head_dim, float(rope_theta),
+                                                         1 if split_half else 0, C.byref(k_pool._raw),
+                                                         C.byref(v_pool._raw), C.byref(slot_mapping._raw)))
+
     def scatter_kv(self, pool: CudaBuffer, src: CudaBuffer, slot_mapping: CudaBuffer, kv_dim: int, num_tokens: int) -> None:
         self._check(self._lib.llmrs_cuda_scatter_kv(self._ctx, C.byref(pool._raw), C.byref(src._raw),
                                                     C.byref(slot_mapping._raw), kv_dim, num_tokens))
@@ -322,6 +336,24 @@ class CudaBackend:
                                                    C.byref(v_pool._raw), C.byref(block_table._raw),
                                                    C.byref(query_starts._raw), C.byref(seq_lens._raw), n_heads,
                                                    n_kv_heads, head_dim, block_size, max_blocks_per_seq))
+
+    def rms_norm_matmul(self, out: CudaBuffer, weight: CudaBuffer, input: CudaBuffer, norm_weight: CudaBuffer,
+                        eps: float) -> None:
+        """out = matmul(weight, rms_norm(input, norm_weight, eps)): rms_norm + matmul (src/arch/llama.rs:152-155)."""
+        self._check(self._lib.llmrs_cuda_rms_norm_matmul(self._ctx, C.byref(out._raw), C.byref(weight._raw),
+                                                         C.byref(input._raw), C.byref(norm_weight._raw), float(eps)))
+
+    def rms_norm_matmul_gate_up(self, out: CudaBuffer, w_gate: CudaBuffer, w_up: CudaBuffer, input: CudaBuffer,
+                                norm_weight: CudaBuffer, eps: float) -> None:
+        """rms_norm + matmul, matmul, silu, mul (src/arch/llama.rs:164-168) as one call."""
+        self._check(self._lib.llmrs_cuda_rms_norm_matmul_gate_up(self._ctx, C.byref(out._raw), C.byref(w_gate._raw),
+                                                                 C.byref(w_up._raw), C.byref(input._raw),
+                                                                 C.byref(norm_weight._raw), float(eps)))
+
+    def matmul_add(self, out: CudaBuffer, weight: CudaBuffer, input: CudaBuffer, residual: CudaBuffer) -> None:
+        """out = residual + matmul(weight, input): matmul followed by add (src/arch/llama.rs:162-163) as one call."""
+        self._check(self._lib.llmrs_cuda_matmul_add(self._ctx, C.byref(out._raw), C.byref(weight._raw),
+                                                    C.byref(input._raw), C.byref(residual._raw)))
 
     def matmul_gate_up(self, out: CudaBuffer, w_gate: CudaBuffer, w_up: CudaBuffer, input: CudaBuffer) -> None:
         """out = silu(matmul(w_gate, input)) * matmul(w_up, input): the calls matmul, matmul, silu, mul

@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <functional>
 #include <string>
 #include <vector>
 
@@ -37,6 +38,11 @@ struct llmrs_ctx {
     size_t scratch_bytes = 0;
     bool pdl = true;                 // decode kernels overlap their prologue with the previous kernel's tail (LLMRS_NO_PDL=1: off)
     int gemm_split = -1;             // LLMRS_GEMM_SPLIT at creation: 0 never, 1 always, otherwise the estimate decides
+    const llmrs_buf *residual = nullptr;   // set by matmul_add around its call of matmul
+    void *norm_tmp = nullptr;              // normalised activations where the norm is not fused into the matmul
+    size_t norm_tmp_bytes = 0;
+    const float *norm_w = nullptr;         // set by the rms_norm_matmul calls around theirs
+    float norm_eps = 0.0f;
     float *att_ws = nullptr;         // partial results of attention over split sequences
     size_t att_ws_bytes = 0;
     uint32_t *argmax_out = nullptr;  // device word argmax writes its result to
@@ -224,6 +230,7 @@ int llmrs_cuda_destroy(llmrs_ctx *ctx) {
     if (ctx->tokens) cudaFree(ctx->tokens);
     if (ctx->argmax_out) cudaFree(ctx->argmax_out);
     if (ctx->att_ws) cudaFree(ctx->att_ws);
+    if (ctx->norm_tmp) cudaFree(ctx->norm_tmp);
     delete ctx;
     return LLMRS_OK;
 }
@@ -367,7 +374,8 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
     if (decode) {
         e = launch_gemv((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
                         (int)out->dtype, (int)K, (int)N, (int)M, ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream,
-                        &ctx->launches);
+                        &ctx->launches, ctx->residual ? ctx->residual->dptr : nullptr,
+                        ctx->residual ? (int)ctx->residual->dtype : DT_F32, ctx->norm_w, ctx->norm_eps);
     } else {
         // The reference switches to its tiled GEMM kernels by seq_len too (metal/mod.rs:542-633).
         e = ctx->reserve_scratch(gemm_scratch_bytes((int)K, (int)M));
@@ -476,13 +484,39 @@ int llmrs_cuda_rope(llmrs_ctx *ctx, llmrs_buf *q, llmrs_buf *k, const llmrs_buf 
                          k->dim0, k->dim1, head_dim, buf_elems(positions));
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
-    llmrs_buf *both[2] = {q, k};
-    for (int i = 0; i < 2 && e == cudaSuccess; i++) {
-        e = launch_rope(both[i]->dptr, (int)both[i]->dtype, (const uint32_t *)positions->dptr, (int)head_dim, rope_theta,
-                        (int)both[i]->dim0, (int)seq, split_half != 0, ctx->stream, ctx->pdl);
-        ctx->launches++;
-    }
+    if (e == cudaSuccess)
+        e = launch_rope(q->dptr, (int)q->dtype, (int)q->dim0, k->dptr, (int)k->dtype, (int)k->dim0,
+                        (const uint32_t *)positions->dptr, (int)head_dim, rope_theta, (int)seq, split_half != 0,
+                        ctx->stream, ctx->pdl);
+    ctx->launches++;
     if (e != cudaSuccess) return ctx->cuda_fail(e, "rope");
+    return LLMRS_OK;
+}
+
+int llmrs_cuda_rope_scatter_kv(llmrs_ctx *ctx, llmrs_buf *q, llmrs_buf *k, const llmrs_buf *v, const llmrs_buf *positions,
+                               uint32_t head_dim, float rope_theta, uint32_t split_half, llmrs_buf *k_pool,
+                               llmrs_buf *v_pool, const llmrs_buf *slot_mapping) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    const llmrs_buf *all[7] = {q, k, v, positions, k_pool, v_pool, slot_mapping};
+    for (const llmrs_buf *b : all)
+        if (!b || !b->dptr) return ctx->fail(LLMRS_ERR_ARG, "rope_scatter_kv: null buffer");
+    if (!dense_elem_bytes(q->dtype) || k->dtype != q->dtype || v->dtype != q->dtype || k_pool->dtype != q->dtype ||
+        v_pool->dtype != q->dtype || positions->dtype != LLMRS_I32 || slot_mapping->dtype != LLMRS_I32)
+        return ctx->fail(LLMRS_ERR_DTYPE, "rope_scatter_kv: q, k, v and the pools of one type (F32 or BF16), indices I32");
+    const uint32_t seq = q->dim1 ? q->dim1 : 1;
+    if (head_dim == 0 || head_dim % 2 || q->dim0 % head_dim || k->dim0 % head_dim || v->dim0 != k->dim0 ||
+        (k->dim1 ? k->dim1 : 1) != seq || (v->dim1 ? v->dim1 : 1) != seq || buf_elems(positions) < seq ||
+        buf_elems(slot_mapping) < seq || buf_elems(k_pool) % k->dim0 || buf_elems(v_pool) % k->dim0)
+        return ctx->fail(LLMRS_ERR_SHAPE, "rope_scatter_kv: q [%u, %u], k [%u, %u], v [%u, %u], head_dim %u", q->dim0, q->dim1,
+                         k->dim0, k->dim1, v->dim0, v->dim1, head_dim);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e == cudaSuccess)
+        e = launch_rope_scatter(q->dptr, (int)q->dim0, k->dptr, v->dptr, (int)k->dim0, (int)q->dtype,
+                                (const uint32_t *)positions->dptr, (const uint32_t *)slot_mapping->dptr, k_pool->dptr,
+                                v_pool->dptr, (int)head_dim, rope_theta, (int)seq, split_half != 0, ctx->stream, ctx->pdl);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "rope_scatter_kv");
+    ctx->launches++;
     return LLMRS_OK;
 }
 
@@ -590,6 +624,85 @@ int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, con
     return LLMRS_OK;
 }
 
+int llmrs_cuda_matmul_add(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input,
+                          const llmrs_buf *residual) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!residual || !residual->dptr || !out) return ctx->fail(LLMRS_ERR_ARG, "matmul_add: null buffer");
+    if (!dense_elem_bytes(residual->dtype)) return ctx->fail(LLMRS_ERR_DTYPE, "matmul_add: residual must be F32 or BF16");
+    if (residual->dim0 != out->dim0 || (residual->dim1 ? residual->dim1 : 1) != (out->dim1 ? out->dim1 : 1))
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul_add: residual is [%u, %u], output [%u, %u]", residual->dim0, residual->dim1,
+                         out->dim0, out->dim1);
+    const uint32_t M = input && input->dim1 ? input->dim1 : 1;
+    const bool decode = input && weight && (int)M <= ctx->gemv_max_m;
+    if (!decode) {                                   // tensor-core path: the matmul, then the add as its own kernel
+        int rc = llmrs_cuda_matmul(ctx, out, weight, input);
+        return rc != LLMRS_OK ? rc : llmrs_cuda_add(ctx, out, out, residual);
+    }
+    ctx->residual = residual;                        // picked up by llmrs_cuda_matmul's decode branch
+    int rc = llmrs_cuda_matmul(ctx, out, weight, input);
+    ctx->residual = nullptr;
+    return rc;
+}
+
+// rms_norm fused into the staging of the decode kernel where that kernel serves the call in one launch;
+// otherwise rms_norm into a temporary, then the plain call.
+static int with_norm(llmrs_ctx *ctx, const char *name, const llmrs_buf *input, const llmrs_buf *norm_weight, float eps,
+                     bool fused_ok, const std::function<int(const llmrs_buf *)> &call) {
+    if (!norm_weight || !norm_weight->dptr || !input || !input->dptr) return ctx->fail(LLMRS_ERR_ARG, "%s: null buffer", name);
+    if (norm_weight->dtype != LLMRS_F32 || norm_weight->dim0 != input->dim0)
+        return ctx->fail(LLMRS_ERR_SHAPE, "%s: norm weight must be F32 [%u]", name, input->dim0);
+    if (fused_ok) {
+        ctx->norm_w = (const float *)norm_weight->dptr;
+        ctx->norm_eps = eps;
+        int rc = call(input);
+        ctx->norm_w = nullptr;
+        return rc;
+    }
+    // the normalised activations go to a buffer of the context (grown outside stream capture only)
+    const size_t need = (size_t)input->dim0 * (input->dim1 ? input->dim1 : 1) * dense_elem_bytes(input->dtype);
+    if (!need) return ctx->fail(LLMRS_ERR_DTYPE, "%s: activations must be F32 or BF16", name);
+    if (need > ctx->norm_tmp_bytes) {
+        cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(ctx->stream, &st);
+        if (st != cudaStreamCaptureStatusNone)
+            return ctx->fail(LLMRS_ERR_CUDA, "%s: temporary must grow (make one call outside graph capture)", name);
+        DeviceGuard guard(ctx->device);
+        cudaError_t e = cudaStreamSynchronize(ctx->stream);
+        if (e == cudaSuccess && ctx->norm_tmp) e = cudaFree(ctx->norm_tmp);
+        ctx->norm_tmp = nullptr;
+        ctx->norm_tmp_bytes = 0;
+        if (e == cudaSuccess) e = cudaMalloc(&ctx->norm_tmp, need);
+        if (e != cudaSuccess) return ctx->cuda_fail(e, name);
+        ctx->norm_tmp_bytes = need;
+    }
+    llmrs_buf tmp = *input;
+    tmp.dptr = ctx->norm_tmp;
+    tmp.nbytes = need;
+    tmp.owned = 0;
+    int rc = llmrs_cuda_rms_norm(ctx, &tmp, input, norm_weight, eps);
+    return rc == LLMRS_OK ? call(&tmp) : rc;
+}
+
+int llmrs_cuda_rms_norm_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input,
+                               const llmrs_buf *norm_weight, float eps) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    const uint32_t M = input && input->dim1 ? input->dim1 : 1;
+    const bool fused = weight && input && (int)M <= ctx->gemv_max_m &&
+                       (int)M <= gemv_single_launch_max_tokens((int)weight->dtype, (int)weight->dim0);
+    return with_norm(ctx, "rms_norm_matmul", input, norm_weight, eps, fused,
+                     [&](const llmrs_buf *x) { return llmrs_cuda_matmul(ctx, out, weight, x); });
+}
+
+int llmrs_cuda_rms_norm_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w_gate, const llmrs_buf *w_up,
+                                       const llmrs_buf *input, const llmrs_buf *norm_weight, float eps) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    const uint32_t M = input && input->dim1 ? input->dim1 : 1;
+    const bool fused = w_gate && input && (int)M <= ctx->gemv_max_m &&
+                       gemv_gate_up_fits((int)w_gate->dtype, (int)w_gate->dim0, (int)M);
+    return with_norm(ctx, "rms_norm_matmul_gate_up", input, norm_weight, eps, fused,
+                     [&](const llmrs_buf *x) { return llmrs_cuda_matmul_gate_up(ctx, out, w_gate, w_up, x); });
+}
+
 int llmrs_cuda_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w_gate, const llmrs_buf *w_up,
                               const llmrs_buf *input) {
     if (!ctx) return LLMRS_ERR_ARG;
@@ -623,10 +736,12 @@ int llmrs_cuda_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w
         if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_gate_up: event");
         e = launch_gemv_gate_up((int)w_gate->dtype, (const uint8_t *)w_gate->dptr, (const uint8_t *)w_up->dptr,
                                 input->dptr, (int)input->dtype, out->dptr, (int)out->dtype, (int)K, (int)N, (int)M,
-                                ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream, &ctx->launches);
+                                ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream, &ctx->launches, ctx->norm_w,
+                                ctx->norm_eps);
         if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_gate_up: launch");
         return LLMRS_OK;
     }
+    if (ctx->norm_w) return ctx->fail(LLMRS_ERR_SHAPE, "matmul_gate_up: the fused norm needs the one-launch path");
     // Two matmuls into float32 scratch behind the GEMM's own scratch, then the element-wise tail.
     const size_t gemm_bytes = decode ? 0 : (gemm_scratch_bytes((int)K, (int)M) + 255) / 256 * 256;
     const size_t half = ((size_t)M * N * sizeof(float) + 255) / 256 * 256;

@@ -97,9 +97,13 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const void *x, int bf16, u
 // Rotary embedding in place (shaders/ops.metal:1011-1042): x is [row_stride, seq_len] made of heads of
 // head_dim; pair i of a head is (2i, 2i+1) ("interleaved") or (i, i + head_dim/2) ("split half");
 // angle = position * theta^(-2i / head_dim).  One thread per pair.
-__global__ void rope_kernel(void *x, int bf16, const uint32_t *__restrict__ positions, int head_dim, float theta,
-                            int pairs_per_row, int row_stride, int split_half) {
+// q and k go through one launch: blockIdx.z picks the buffer.
+__global__ void rope_kernel(void *xq, int q_bf16, int q_stride, void *xk, int k_bf16, int k_stride,
+                            const uint32_t *__restrict__ positions, int head_dim, float theta, int split_half) {
     pdl_prologue();
+    void *x = blockIdx.z ? xk : xq;
+    const int bf16 = blockIdx.z ? k_bf16 : q_bf16, row_stride = blockIdx.z ? k_stride : q_stride;
+    const int pairs_per_row = row_stride / 2;
     const int pair = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
     if (pair >= pairs_per_row) return;
     const int half = head_dim / 2, head = pair / half, i = pair % half;
@@ -113,6 +117,43 @@ __global__ void rope_kernel(void *x, int bf16, const uint32_t *__restrict__ posi
     const float x0 = load_f(x, a, bf16), x1 = load_f(x, b, bf16);
     store_f(x, a, x0 * cs - x1 * sn, bf16);
     store_f(x, b, x0 * sn + x1 * cs, bf16);
+}
+
+// rope of q and k and the two scatter_kv calls that follow it in a layer (src/arch/llama.rs:156-158) in one
+// launch: blockIdx.z = 0 rotates q in place, 1 rotates k in place and writes the rotated pair into the
+// key pool, 2 copies v into the value pool.  Pools and k, v share one element type.
+__global__ void rope_scatter_kernel(void *q, int q_stride, void *k, const void *v, int kv_stride, int bf16,
+                                    const uint32_t *__restrict__ positions, const uint32_t *__restrict__ slots,
+                                    void *k_pool, void *v_pool, int head_dim, float theta, int split_half) {
+    pdl_prologue();
+    const int which = blockIdx.z, s = blockIdx.y;
+    const int row_stride = which == 0 ? q_stride : kv_stride;
+    const int pair = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pair >= row_stride / 2) return;
+    if (which == 2) {                                    // two values of v per thread
+        const size_t src = (size_t)s * kv_stride + 2 * pair, dst = (size_t)slots[s] * kv_stride + 2 * pair;
+        store_f(v_pool, dst, load_f(v, src, bf16), bf16);
+        store_f(v_pool, dst + 1, load_f(v, src + 1, bf16), bf16);
+        return;
+    }
+    void *x = which == 0 ? q : k;
+    const int half = head_dim / 2, head = pair / half, i = pair % half;
+    const size_t in_row = (size_t)head * head_dim + (split_half ? i : 2 * i);
+    const size_t step = split_half ? half : 1;
+    const size_t a = (size_t)s * row_stride + in_row, b = a + step;
+    const float freq = 1.0f / powf(theta, 2.0f * (float)i / (float)head_dim);
+    const float angle = (float)positions[s] * freq;
+    float sn, cs;
+    sincosf(angle, &sn, &cs);
+    const float x0 = load_f(x, a, bf16), x1 = load_f(x, b, bf16);
+    const float y0 = x0 * cs - x1 * sn, y1 = x0 * sn + x1 * cs;
+    store_f(x, a, y0, bf16);
+    store_f(x, b, y1, bf16);
+    if (which == 1) {
+        const size_t pa = (size_t)slots[s] * kv_stride + in_row;
+        store_f(k_pool, pa, y0, bf16);
+        store_f(k_pool, pa + step, y1, bf16);
+    }
 }
 
 // pool[slot_mapping[t] * kv_dim + d] = src[t * kv_dim + d]  (ops.metal:841-853), and
@@ -410,11 +451,12 @@ size_t attention_workspace_bytes(int total_query_tokens, int n_heads, int head_d
     return splits <= 1 ? 0 : (size_t)total_query_tokens * n_heads * splits * (head_dim + 2) * sizeof(float);
 }
 
-// How many ranges to cut the sequences into: enough CTAs for two per SM, ranges of at least four tiles.
+// How many ranges to cut the sequences into: enough CTAs for two per SM, ranges of at least one tile
+// (a single decode request is a chain of dependent tiles: the shorter the chain, the sooner it ends).
 int attention_splits(int total_query_tokens, int n_kv_heads, int max_seq_len, int sm_count) {
     const int ctas = total_query_tokens * n_kv_heads;
     const int want = (2 * sm_count + ctas - 1) / ctas;
-    const int most = (max_seq_len + 4 * AT2_TILE - 1) / (4 * AT2_TILE);
+    const int most = (max_seq_len + AT2_TILE - 1) / AT2_TILE;
     const int s = want < most ? want : most;
     return s < 1 ? 1 : (s > 32 ? 32 : s);
 }
@@ -459,12 +501,23 @@ cudaError_t launch_attention_gqa(const void *q, const void *k_pool, const void *
                             pdl, (const float *)workspace, (uint16_t *)out, head_dim, splits);
 }
 
-cudaError_t launch_rope(void *x, int dtype, const uint32_t *positions, int head_dim, float theta, int row_stride,
-                        int seq_len, int split_half, cudaStream_t s, bool pdl) {
-    const int pairs = row_stride / 2;
+cudaError_t launch_rope(void *q, int q_dtype, int q_stride, void *k, int k_dtype, int k_stride, const uint32_t *positions,
+                        int head_dim, float theta, int seq_len, int split_half, cudaStream_t s, bool pdl) {
+    const int pairs = (q_stride > k_stride ? q_stride : k_stride) / 2;
     if (pairs <= 0 || seq_len <= 0) return cudaSuccess;
-    return launch_dependent(rope_kernel, dim3((unsigned)((pairs + 255) / 256), (unsigned)seq_len), dim3(256), 0, s, pdl, x,
-                            (int)(dtype == DT_BF16), positions, head_dim, theta, pairs, row_stride, split_half);
+    return launch_dependent(rope_kernel, dim3((unsigned)((pairs + 255) / 256), (unsigned)seq_len, 2), dim3(256), 0, s, pdl,
+                            q, (int)(q_dtype == DT_BF16), q_stride, k, (int)(k_dtype == DT_BF16), k_stride, positions,
+                            head_dim, theta, split_half);
+}
+
+cudaError_t launch_rope_scatter(void *q, int q_stride, void *k, const void *v, int kv_stride, int dtype,
+                                const uint32_t *positions, const uint32_t *slots, void *k_pool, void *v_pool,
+                                int head_dim, float theta, int seq_len, int split_half, cudaStream_t s, bool pdl) {
+    const int pairs = (q_stride > kv_stride ? q_stride : kv_stride) / 2;
+    if (pairs <= 0 || seq_len <= 0) return cudaSuccess;
+    return launch_dependent(rope_scatter_kernel, dim3((unsigned)((pairs + 255) / 256), (unsigned)seq_len, 3), dim3(256), 0, s,
+                            pdl, q, q_stride, k, v, kv_stride, (int)(dtype == DT_BF16), positions, slots, k_pool, v_pool,
+                            head_dim, theta, split_half);
 }
 
 cudaError_t launch_move_rows(void *dst, const void *src, const uint32_t *index, int scatter, size_t row_bytes,

@@ -107,6 +107,15 @@ struct GemvParams {
     // between W (gate) and W2 (up), a warp owns gate row j and up row j, and writes
     // silu(gate . x) * (up . x) as output row j (src/arch/llama.rs:165-168; shaders/ops.metal:762-793).
     const uint8_t *W2;
+    // Residual-add epilogue (Residual != nullptr): out = Residual + X . W^T, the residual read in its
+    // own type (src/arch/llama.rs:163,169: matmul followed by add).
+    const void *Residual;
+    int res_bf16;
+    // RMS norm of the activations while they are staged (NormW != nullptr): every token row is scaled by
+    // rsqrt(mean(x^2) + eps) and by NormW[k] before it is rounded to its block fixed point
+    // (src/arch/llama.rs:152-153,164-165: rms_norm followed by matmul; shaders/ops.metal:970-1003).
+    const float *NormW;
+    float norm_eps;
     const uint8_t *W;
     const void *X;
     void *Out;
@@ -256,15 +265,65 @@ __device__ __forceinline__ float2 quantise_group(const float (&v)[GROUP], uint8_
     return make_float2(inv, (float)sum * inv);
 }
 
+// Sum of squares of every token row over the whole CTA (tokens <= 4): each thread adds up the groups it
+// will stage, warps reduce by shuffle, `red` ([warps][4] floats of shared memory) carries the rest.
+template <int GROUP>
+__device__ void row_inverse_rms(const GemvParams &p, int tid, int n_threads, float (*red)[4], float (&inv)[4]) {
+    const int K = p.K, groups = K / GROUP;
+    float ss[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int gi = tid; gi < groups * p.m_valid; gi += n_threads) {
+        const int t = gi / groups, g = gi - t * groups;
+        float v[GROUP];
+        load_group<GROUP>(p.X, (size_t)t * K + (size_t)GROUP * g, p.x_bf16, v);
+        float a = 0.0f;
+#pragma unroll
+        for (int i = 0; i < GROUP; i++) a = fmaf(v[i], v[i], a);
+#pragma unroll
+        for (int tt = 0; tt < 4; tt++) ss[tt] += tt == t ? a : 0.0f;
+    }
+#pragma unroll
+    for (int tt = 0; tt < 4; tt++) {
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss[tt] += __shfl_xor_sync(0xffffffffu, ss[tt], o);
+    }
+    if ((tid & 31) == 0) {
+#pragma unroll
+        for (int tt = 0; tt < 4; tt++) red[tid >> 5][tt] = ss[tt];
+    }
+    named_barrier_sync(1, n_threads);
+#pragma unroll
+    for (int tt = 0; tt < 4; tt++) {
+        float t = 0.0f;
+        for (int w = 0; w < n_threads / 32; w++) t += red[w][tt];
+        inv[tt] = rsqrtf(t / (float)K + p.norm_eps);
+    }
+}
+
+template <int GROUP>
+__device__ __forceinline__ void scale_group(const GemvParams &p, float (&v)[GROUP], int k0, float inv) {
+#pragma unroll
+    for (int j = 0; j < GROUP / 4; j++) {
+        const float4 w = __ldg(reinterpret_cast<const float4 *>(p.NormW + k0) + j);
+        v[4 * j] = v[4 * j] * inv * w.x;
+        v[4 * j + 1] = v[4 * j + 1] * inv * w.y;
+        v[4 * j + 2] = v[4 * j + 2] * inv * w.z;
+        v[4 * j + 3] = v[4 * j + 3] * inv * w.w;
+    }
+}
+
 template <int QT, int PLANES>
-__device__ void stage_activations(uint8_t *xarea, size_t xtok_bytes, const GemvParams &p, int tid, int n_threads) {
+__device__ void stage_activations(uint8_t *xarea, size_t xtok_bytes, const GemvParams &p, int tid, int n_threads,
+                                  float (*red)[4]) {
     const int K = p.K;
+    float inv_rms[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+    if (p.NormW) row_inverse_rms<QT == 0 ? 32 : 16>(p, tid, n_threads, red, inv_rms);
     if (QT == 0) {
         const int groups = K / 32;                       // group sb = sub-block sb of the row
         for (int gi = tid; gi < groups * p.m_valid; gi += n_threads) {
             const int t = gi / groups, sb = gi - t * groups;
             float v[32];
             load_group<32>(p.X, (size_t)t * K + 32 * (size_t)sb, p.x_bf16, v);
+            if (p.NormW) scale_group<32>(p, v, 32 * sb, t == 0 ? inv_rms[0] : t == 1 ? inv_rms[1] : t == 2 ? inv_rms[2] : inv_rms[3]);
             uint8_t *sl = xarea + (size_t)t * xtok_bytes + (size_t)(sb >> 1) * Fmt<0, PLANES>::XSTRIDE;
             const float2 m = quantise_group<32, PLANES, 0>(v, sl + (sb & 1) * Fmt<0, PLANES>::GROUP_BYTES);
             float *f = reinterpret_cast<float *>(sl + Fmt<0, PLANES>::META);
@@ -279,6 +338,7 @@ __device__ void stage_activations(uint8_t *xarea, size_t xtok_bytes, const GemvP
             const int g = (q >> 1) & 3, slice = ((q >> 3) << 1) | (q & 1);
             float v[16];
             load_group<16>(p.X, (size_t)t * K + 16 * (size_t)q, p.x_bf16, v);
+            if (p.NormW) scale_group<16>(p, v, 16 * q, t == 0 ? inv_rms[0] : t == 1 ? inv_rms[1] : t == 2 ? inv_rms[2] : inv_rms[3]);
             uint8_t *sl = xarea + (size_t)t * xtok_bytes + (size_t)slice * Fmt<1, PLANES>::XSTRIDE;
             const float2 m = quantise_group<16, PLANES, 1>(v, sl + g * Fmt<1, PLANES>::GROUP_BYTES);
             float *f = reinterpret_cast<float *>(sl + Fmt<1, PLANES>::META);
@@ -453,6 +513,7 @@ template <int QT, int MT, int R, int NCW, int PLANES>
 __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParams p) {
     using F = Fmt<QT, PLANES>;
     constexpr int RT = R * NCW;
+    __shared__ float norm_red[NCW][4];
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + MAX_STAGES;
@@ -512,7 +573,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // this call's step; the word is only advanced by the last CTA of a launch, after every CTA has read it
     const uint32_t gather_step = p.g.world > 0 ? *reinterpret_cast<volatile uint32_t *>(p.g.step_word) + 1u : 0u;
-    stage_activations<QT, PLANES>(xarea, xtok_bytes, p, threadIdx.x, NCW * 32);
+    stage_activations<QT, PLANES>(xarea, xtok_bytes, p, threadIdx.x, NCW * 32, norm_red);
     named_barrier_sync(1, NCW * 32);
     if (threadIdx.x == 0) LLMRS_TRACE(1);
 
@@ -584,7 +645,11 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                 const int out_row = rt * RT + warp * R + r;
                 if (ok && out_row < p.N && t < p.m_valid) {
                     if (p.g.world == 0) {
-                        if (lane == 0) store_out(p.Out, (size_t)t * p.N + out_row, v, p.out_bf16);
+                        if (lane == 0) {
+                            const size_t o = (size_t)t * p.N + out_row;
+                            if (p.Residual) v += load_x(p.Residual, o, p.res_bf16);
+                            store_out(p.Out, o, v, p.out_bf16);
+                        }
                     } else if (lane == p.g.rank) {        // this rank's own copy: straight into the output
                         store_out(p.Out, (size_t)t * p.g.n_total + p.g.row_offset + out_row, v, p.out_bf16);
                     } else if (lane < p.g.world) {        // lane d posts the value to rank d's mailbox
@@ -654,7 +719,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
 // ---------------------------------------------------------------------------------------------
 constexpr int NCW_DEFAULT = 16;
 constexpr int PLANES_DEFAULT = 3;
-constexpr size_t SMEM_LIMIT = 227 * 1024;
+constexpr size_t SMEM_LIMIT = 226 * 1024;       // 227 KB per CTA less the kernel's static shared memory
 
 template <int QT, int MT, int R, int NCW, int PLANES>
 size_t smem_fixed(int K) {
@@ -723,12 +788,14 @@ cudaError_t launch_fmt(GemvParams p, int M, int x_elem, int out_elem, int sm_cou
                        uint64_t *launches) {
     const uint8_t *X = (const uint8_t *)p.X;
     uint8_t *Out = (uint8_t *)p.Out;
+    const uint8_t *Res = (const uint8_t *)p.Residual;
     int t0 = 0;
     int mt = M >= 4 ? 4 : M;
     while (t0 < M) {
         int m = M - t0 < mt ? M - t0 : mt;
         p.X = X + (size_t)t0 * p.K * x_elem;
         p.Out = Out + (size_t)t0 * p.N * out_elem;
+        if (Res) p.Residual = Res + (size_t)t0 * p.N * (p.res_bf16 ? 2 : 4);
         p.m_valid = m;
         bool fits = false;
         cudaError_t e = cudaSuccess;
@@ -761,10 +828,15 @@ size_t gemv_max_k() {
 
 cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                         int K, int N, int M, int sm_count, bool pdl, uint32_t *err_word, cudaStream_t s,
-                        uint64_t *launches) {
+                        uint64_t *launches, const void *residual, int residual_dtype, const float *norm_weight,
+                        float norm_eps) {
     if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
     GemvParams p{};
     p.pdl = pdl;
+    p.NormW = norm_weight;
+    p.norm_eps = norm_eps;
+    p.Residual = residual;
+    p.res_bf16 = residual_dtype == DT_BF16;
     p.W = w; p.X = x; p.Out = out; p.err = err_word;
     p.K = K; p.N = N;
     p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;
@@ -801,10 +873,13 @@ bool gemv_gate_up_fits(int wdtype, int K, int M) {
 
 cudaError_t launch_gemv_gate_up(int wdtype, const uint8_t *w_gate, const uint8_t *w_up, const void *x, int x_dtype,
                                 void *out, int out_dtype, int K, int N, int M, int sm_count, bool pdl,
-                                uint32_t *err_word, cudaStream_t s, uint64_t *launches) {
+                                uint32_t *err_word, cudaStream_t s, uint64_t *launches, const float *norm_weight,
+                                float norm_eps) {
     if (!gemv_gate_up_fits(wdtype, K, M)) return cudaErrorInvalidConfiguration;
     GemvParams p{};
     p.pdl = pdl;
+    p.NormW = norm_weight;
+    p.norm_eps = norm_eps;
     p.W = w_gate; p.W2 = w_up; p.X = x; p.Out = out; p.err = err_word;
     p.K = K; p.N = N;
     p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;

@@ -56,10 +56,14 @@ cudaError_t launch_elementwise(int op, const void *a, int a_dtype, const void *b
 cudaError_t launch_rms_norm(const void *in, int in_dtype, const float *weight, void *out, int out_dtype, int dim,
                             int rows, float eps, cudaStream_t s, bool pdl);
 cudaError_t launch_argmax(const void *x, int dtype, uint32_t n, uint32_t *dev_out, cudaStream_t s);
-// Rotary embedding in place on x [row_stride, seq_len]; scatter (dst[index[r]] = src[r]) or gather
+// Rotary embedding in place on q [q_stride, seq_len] and k [k_stride, seq_len] in one launch; scatter (dst[index[r]] = src[r]) or gather
 // (dst[r] = src[index[r]]) of `rows` rows of row_bytes bytes; paged causal grouped-query attention.
-cudaError_t launch_rope(void *x, int dtype, const uint32_t *positions, int head_dim, float theta, int row_stride,
-                        int seq_len, int split_half, cudaStream_t s, bool pdl);
+cudaError_t launch_rope(void *q, int q_dtype, int q_stride, void *k, int k_dtype, int k_stride, const uint32_t *positions,
+                        int head_dim, float theta, int seq_len, int split_half, cudaStream_t s, bool pdl);
+// rope of q and k plus the scatter of the rotated k and of v into their pools, one launch (one element type).
+cudaError_t launch_rope_scatter(void *q, int q_stride, void *k, const void *v, int kv_stride, int dtype,
+                                const uint32_t *positions, const uint32_t *slots, void *k_pool, void *v_pool,
+                                int head_dim, float theta, int seq_len, int split_half, cudaStream_t s, bool pdl);
 cudaError_t launch_move_rows(void *dst, const void *src, const uint32_t *index, int scatter, size_t row_bytes,
                              int rows, cudaStream_t s, bool pdl);
 // The bf16 attention organised around its memory traffic (head_dim 64 or 128, 1/2/4/8 query heads per
@@ -83,10 +87,14 @@ cudaError_t launch_attention(const void *q, const void *k_pool, const void *v_po
 // word that receives a KernelError if a bounded wait inside the kernel gives up.  *launches is
 // incremented per kernel launched.  pdl: launch with programmatic stream serialization, so that
 // the kernel's prologue and weight fetch overlap the tail of the kernel before it in the stream
-// (requires that no kernel still in flight writes the weights).
+// (requires that no kernel still in flight writes the weights).  residual (optional, [M, N] of
+// residual_dtype): out = residual + matmul, added in the epilogue; with more than four tokens the
+// token passes each add their part.  norm_weight (optional, float32 [K]): the activations are RMS-normalised
+// (rsqrt(mean(x^2) + norm_eps) * norm_weight) as they are staged, so rms_norm + matmul is one kernel.
 cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                         int K, int N, int M, int sm_count, bool pdl, uint32_t *err_word, cudaStream_t s,
-                        uint64_t *launches);
+                        uint64_t *launches, const void *residual = nullptr, int residual_dtype = DT_F32,
+                        const float *norm_weight = nullptr, float norm_eps = 0.0f);
 
 // The decode matmul of one rank's weight rows with the all-gather fused in.  `out` is this rank's
 // [M, N_local * world] result.  peer_mailbox[d] is rank d's mailbox (gemv_allgather_mailbox_bytes()
@@ -106,7 +114,8 @@ cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, i
 bool gemv_gate_up_fits(int wdtype, int K, int M);
 cudaError_t launch_gemv_gate_up(int wdtype, const uint8_t *w_gate, const uint8_t *w_up, const void *x, int x_dtype,
                                 void *out, int out_dtype, int K, int N, int M, int sm_count, bool pdl,
-                                uint32_t *err_word, cudaStream_t s, uint64_t *launches);
+                                uint32_t *err_word, cudaStream_t s, uint64_t *launches,
+                                const float *norm_weight = nullptr, float norm_eps = 0.0f);
 // out[i] = silu(gate[i]) * up[i] over n float32 values, written as out_dtype (the unfused tail).
 cudaError_t launch_silu_mul(const float *gate, const float *up, void *out, int out_dtype, size_t n, cudaStream_t s);
 

@@ -293,6 +293,61 @@ def test_matmul_gate_up(backend, dt, K, N, M):
     assert O.rel_l2(got, silu_mul_truth(dt, wg, wu, K, N, x)) <= 2.5 * tol_for(M)
 
 
+@pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
+@pytest.mark.parametrize("K,N,M,bf16", [(4096, 1000, 1, False), (14336, 4096, 1, True), (2048, 77, 4, False), (1024, 256, 9, True)])
+def test_matmul_add(backend, dt, K, N, M, bf16):
+    """out = residual + matmul: the residual is added where the decode kernel writes its results (up to 4
+    tokens), by the add kernel after the tensor-core matmul otherwise."""
+    w = synth.weight(dt, K, N, tid=23 * K + N)
+    x = synth.activations(M, K, tid=4100 + M)
+    res = synth.activations(M, N, tid=4200 + M) * np.float32(50.0)
+    if bf16:
+        x = O.bf16_bits_to_f32(synth.bf16_bits(x)).reshape(M, K)
+        res = O.bf16_bits_to_f32(synth.bf16_bits(res)).reshape(M, N)
+    rb = upload_x(backend, res, M, N, bf16)
+    out = backend.alloc([N] if M == 1 else [N, M], DType.BF16 if bf16 else DType.F32)
+    backend.matmul_add(out, upload_weight(backend, dt, w, K, N), upload_x(backend, x, M, K, bf16), rb)
+    backend.sync()
+    got = backend.read_to_vec_f32(out).reshape(M, N)
+    truth = O.matmul(dt, w, K, N, x, acc="f64").astype(np.float64) + res
+    assert O.rel_l2(got, truth) <= tol_for(M) + (2.0 ** -8 if bf16 else 0.0)
+
+
+@pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
+@pytest.mark.parametrize("K,N,M", [(4096, 512, 1), (14336, 256, 1), (2048, 300, 3), (4096, 128, 4), (1024, 256, 9)])
+def test_rms_norm_matmul(backend, dt, K, N, M):
+    """rms_norm folded into the decode kernel's staging (up to 4 tokens) or run ahead of the tensor-core
+    matmul: against the float64 chain norm -> matmul, nothing rounded in between."""
+    w = synth.weight(dt, K, N, tid=29 * K + N)
+    x = synth.activations(M, K, tid=4300 + M) * np.float32(3.0)
+    nw = (synth.activations(1, K, tid=4400).reshape(-1) * np.float32(0.2) + np.float32(1.0)).astype(np.float32)
+    nb = backend.upload_tensor(TensorView("nw", DType.F32, [K], nw))
+    out = backend.alloc([N] if M == 1 else [N, M], DType.F32)
+    backend.rms_norm_matmul(out, upload_weight(backend, dt, w, K, N), upload_x(backend, x, M, K), nb, 1e-5)
+    backend.sync()
+    got = backend.read_to_vec_f32(out).reshape(M, N)
+    x64 = x.astype(np.float64)
+    xn = x64 / np.sqrt((x64 ** 2).mean(axis=1, keepdims=True) + 1e-5) * nw
+    truth = O.matmul(dt, w, K, N, xn.astype(np.float32), acc="f64")       # normalised rows differ from float32 by 6e-8
+    assert O.rel_l2(got, truth) <= tol_for(M)
+
+
+@pytest.mark.parametrize("M", [1, 4])
+def test_rms_norm_matmul_gate_up(backend, M):
+    K, N = 4096, 640
+    wg, wu = synth.weight(O.Q4K, K, N, tid=31), synth.weight(O.Q4K, K, N, tid=32)
+    x = synth.activations(M, K, tid=4500 + M) * np.float32(7.0)
+    nw = np.full(K, 0.05, np.float32)
+    out = backend.alloc([N] if M == 1 else [N, M], DType.F32)
+    backend.rms_norm_matmul_gate_up(out, upload_weight(backend, O.Q4K, wg, K, N), upload_weight(backend, O.Q4K, wu, K, N),
+                                    upload_x(backend, x, M, K), backend.upload_tensor(TensorView("nw", DType.F32, [K], nw)),
+                                    1e-5)
+    backend.sync()
+    x64 = x.astype(np.float64)
+    xn = (x64 / np.sqrt((x64 ** 2).mean(axis=1, keepdims=True) + 1e-5) * nw).astype(np.float32)
+    assert O.rel_l2(backend.read_to_vec_f32(out).reshape(M, N), silu_mul_truth(O.Q4K, wg, wu, K, N, xn)) <= 2.5e-4
+
+
 def test_matmul_gate_up_bf16_and_errors(backend):
     from llm_rs_b200.backend import BackendError
     K, N = 1024, 64
@@ -432,6 +487,35 @@ def test_attention_long_decode_splits(backend):
     got = backend.read_to_vec_f32(out).reshape(2, n_heads * hd)
     want = O.attention(q, k, v, table.reshape(-1), [0, 1, 2], seq_lens, n_heads, n_kv, hd, block, max_blocks, bf16=True)
     assert O.rel_l2(got, want) <= 4e-3 and np.abs(got - want).max() <= 2e-2
+
+
+@pytest.mark.parametrize("split_half", [False, True])
+def test_rope_scatter_kv_equals_the_three_calls(backend, split_half):
+    """One launch for rope(q, k), scatter_kv(k), scatter_kv(v): bit for bit what the three calls give."""
+    hd, seq, nq, nkv, slots_n = 128, 4, 4, 2, 40
+    positions, slots = [0, 5, 300, 7], [39, 0, 17, 3]
+    q0 = synth.activations(seq, nq * hd, tid=151)
+    k0 = synth.activations(seq, nkv * hd, tid=152)
+    v0 = synth.activations(seq, nkv * hd, tid=153)
+    res = []
+    for fused in (False, True):
+        qb, _ = _dense(backend, q0, True)
+        kb, _ = _dense(backend, k0, True)
+        vb, _ = _dense(backend, v0, True)
+        kp, _ = _dense(backend, np.zeros((slots_n, nkv * hd), np.float32), True)
+        vp, _ = _dense(backend, np.zeros((slots_n, nkv * hd), np.float32), True)
+        pb, sb = backend.upload_u32(positions), backend.upload_u32(slots)
+        if fused:
+            backend.rope_scatter_kv(qb, kb, vb, pb, hd, 10000.0, kp, vp, sb, split_half)
+        else:
+            backend.rope(qb, kb, pb, hd, 10000.0, split_half)
+            backend.scatter_kv(kp, kb, sb, nkv * hd, seq)
+            backend.scatter_kv(vp, vb, sb, nkv * hd, seq)
+        backend.sync()
+        res.append([backend.read_to_vec_f32(b) for b in (qb, kb, kp, vp)])
+    for a, b in zip(*res):
+        assert np.array_equal(a, b)
+    assert res[1][2].any() and res[1][3].any()
 
 
 def test_scatter_kv_and_gather(backend):
