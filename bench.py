@@ -548,7 +548,21 @@ def extra_measurements(be_factory, stream, peak_gbs):
                 alg = algorithmic_bytes(dt, K, N, M)
                 out["gemv"][f"{name}_m{M}"] = {"us": round(t * 1e6, 2), "GBps": round(alg / t / 1e9, 1),
                                                "frac_of_hbm_peak": round(alg / t / 1e9 / peak_gbs, 4),
-                                               "kernel": "exact" if M <= 4 else "tensor-core f16"}
+                                               "kernel": "exact" if M <= 4 else "tensor-core f16, two terms (1e-4 class)"}
+        # the same output projection on the one-term tensor-core kernel (2e-3 class; LLMRS_TC_TWO_TERM=0)
+        os.environ["LLMRS_TC_TWO_TERM"] = "0"
+        try:
+            be_two, be = be, be_factory()
+        finally:
+            del os.environ["LLMRS_TC_TWO_TERM"]
+        for M in (8, 32, 64):
+            t = time_matmul(Q6K, 4096, 128256, M, DType.F32, DType.F32, 50)
+            alg = algorithmic_bytes(Q6K, 4096, 128256, M)
+            out["gemv"][f"q6k_4096x128256_m{M}_one_term"] = {
+                "us": round(t * 1e6, 2), "GBps": round(alg / t / 1e9, 1),
+                "frac_of_hbm_peak": round(alg / t / 1e9 / peak_gbs, 4), "kernel": "tensor-core f16, one term (2e-3 class)"}
+        be.close()
+        be = be_two
         # config 3: Q4_K 4096 -> 14336 then Q6_K 14336 -> 4096, bf16 activations in and out
         for M in (128, 512, 2048):
             for name, dt, K, N in (("q4k_4096x14336", Q4K, 4096, 14336), ("q6k_14336x4096", Q6K, 14336, 4096)):

@@ -4,6 +4,7 @@
 // the extern "C" surface declared in include/llmrs_cuda.h.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -33,7 +34,11 @@ struct llmrs_ctx {
     double gpu_secs = 0.0;
     uint64_t launches = 0;
     int sm_count = 0;
-    int gemv_max_m = 4;              // M <= this: exact decode kernel (1e-4 class); above: tensor-core GEMM (2e-3 class)
+    int gemv_max_m = 4;              // M <= this: exact decode kernel (1e-4 class); above: tensor-core GEMM
+    bool cost_rule = true;           // up to 64 tokens the decode kernel also runs where it is the cheaper one;
+                                     // an explicit LLMRS_GEMV_MAX_M makes the boundary hard
+    bool two_term = true;            // tensor-core GEMM up to 64 tokens carries hi + lo f16 terms (1e-4 class);
+                                     // LLMRS_TC_TWO_TERM=0: one term (2e-3 class, about half the time)
     void *scratch = nullptr;         // f16 copy of the activations for the tensor-core path
     size_t scratch_bytes = 0;
     bool pdl = true;                 // decode kernels overlap their prologue with the previous kernel's tail (LLMRS_NO_PDL=1: off)
@@ -197,9 +202,10 @@ int llmrs_cuda_create(int device, void *stream, llmrs_ctx **out) {
     ctx->sm_count = prop.multiProcessorCount;
     if (const char *env = getenv("LLMRS_GEMV_MAX_M")) {
         int v = atoi(env);
-        if (v >= 0) ctx->gemv_max_m = v;
+        if (v >= 0) { ctx->gemv_max_m = v; ctx->cost_rule = false; }
     }
     if (const char *env = getenv("LLMRS_NO_PDL")) ctx->pdl = atoi(env) == 0;
+    if (const char *env = getenv("LLMRS_TC_TWO_TERM")) ctx->two_term = atoi(env) != 0;
     if (const char *env = getenv("LLMRS_GEMM_SPLIT")) ctx->gemm_split = atoi(env) ? 1 : 0;
     e = cudaEventCreate(&ctx->ev_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_end);
@@ -342,6 +348,27 @@ int llmrs_cuda_write(llmrs_ctx *ctx, llmrs_buf *dst, const void *host, size_t nb
     return LLMRS_OK;
 }
 
+// Between the decode kernel's token limit and 64 tokens both kernels meet the decode tolerance, so
+// the cheaper one runs.  The decode kernel streams the weights once per pass of up to four tokens
+// (fewer where the staged activations of four do not fit): about 2 us + 0.2 us per MB and token,
+// at least 4.5 us per pass.  The tensor-core kernel has a floor of a few tens of microseconds (its
+// pipeline fill and the activation conversion) and streams the weights once: two-term
+// 45 us + 0.55 us/MB, one-term 24 us + 0.27 us/MB.  Fitted on a B200 to 4096x4096 .. 4096x128256
+// weights at 5 .. 64 tokens.
+static bool decode_kernel_cheaper(const llmrs_ctx *ctx, const llmrs_buf *weight, uint32_t M, uint32_t K) {
+    if (!ctx->cost_rule || M > (uint32_t)GEMM_TWO_TERM_MAX_TOKENS || K > gemv_max_k()) return false;
+    const int per_pass = std::min(4, gemv_single_launch_max_tokens((int)weight->dtype, (int)K));
+    if (per_pass <= 0) return false;
+    const double mb = (double)weight->nbytes * 1e-6;
+    // weights of up to half a wave of tiles and K >= 4096 are cut along K over all SMs: floor 27 us
+    const bool cut = ctx->split_ws && ctx->gemm_split != 0 && K >= 4096 && (weight->dim1 + 127) / 128 <= (uint32_t)ctx->sm_count / 2;
+    const double tc = ctx->two_term ? (cut ? 27.0 : 45.0) + 0.55 * mb : 24.0 + 0.27 * mb;
+    double decode = 0.0;
+    for (uint32_t done = 0; done < M; done += (uint32_t)per_pass)
+        decode += std::max(4.5, 2.0 + 0.2 * mb * std::min<uint32_t>((uint32_t)per_pass, M - done));
+    return decode < tc;
+}
+
 int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input) {
     if (!ctx) return LLMRS_ERR_ARG;
     if (!out || !weight || !input || !out->dptr || !weight->dptr || !input->dptr)
@@ -357,7 +384,7 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
         return ctx->fail(LLMRS_ERR_DTYPE, "matmul: activations must be F32 or BF16 (got %u -> %u)", input->dtype,
                          out->dtype);
     if (K % QK_K) return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u is not a multiple of 256", K);
-    const bool decode = (int)M <= ctx->gemv_max_m;
+    const bool decode = (int)M <= ctx->gemv_max_m || decode_kernel_cheaper(ctx, weight, M, K);
     if (decode && K > gemv_max_k())
         return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u exceeds the supported maximum %zu", K, gemv_max_k());
     if (input->dim0 != K)
@@ -382,8 +409,7 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
         if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: scratch (grow it with one call outside graph capture)");
         e = launch_gemm((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
                         (int)out->dtype, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->dev_error,
-                        ctx->stream,
-                        &ctx->launches);
+                        ctx->stream, &ctx->launches, nullptr, ctx->two_term);
     }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: launch");
     return LLMRS_OK;
@@ -760,7 +786,7 @@ int llmrs_cuda_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w
         else
             e = launch_gemm((int)ws[i]->dtype, (const uint8_t *)ws[i]->dptr, input->dptr, (int)input->dtype, dst[i],
                             DT_F32, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws, ctx->gemm_split,
-                            ctx->dev_error, ctx->stream, &ctx->launches);
+                            ctx->dev_error, ctx->stream, &ctx->launches, nullptr, ctx->two_term);
     }
     if (e == cudaSuccess) {
         e = launch_silu_mul(g, u, out->dptr, (int)out->dtype, (size_t)M * N, ctx->stream);
@@ -854,7 +880,7 @@ int llmrs_cuda_matmul_static_scratch(llmrs_ctx *ctx, llmrs_buf *out, const llmrs
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_static_scratch: event");
     e = launch_gemm_static_scratch((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype,
                                    out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, ctx->device, ctx->dev_error,
-                                   ctx->stream, &ctx->launches);
+                                   ctx->stream, &ctx->launches, ctx->two_term);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_static_scratch: launch");
     return LLMRS_OK;
 }
@@ -905,7 +931,7 @@ int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf 
         const GemmGather gg{(int)world, (int)rank, peer_mailbox, ctx->dev_error + 1, step_word};
         e = launch_gemm((int)weight_shard->dtype, (const uint8_t *)weight_shard->dptr, input->dptr, (int)input->dtype,
                         out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws,
-                        ctx->gemm_split, ctx->dev_error, ctx->stream, &ctx->launches, &gg);
+                        ctx->gemm_split, ctx->dev_error, ctx->stream, &ctx->launches, &gg, ctx->two_term);
     }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: launch");
     return LLMRS_OK;

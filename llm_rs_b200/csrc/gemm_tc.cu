@@ -404,6 +404,77 @@ __device__ __forceinline__ void dequant_q6k_half(const RawQ6 &raw, uint32_t a_ta
     for (int g = 0; g < 4; g++) tmem_st16(a_taddr + 16 * g, o[g]);
 }
 
+// ---- two-term dequantisation: exact float32 weight -> (hi, lo) f16 pair ---------------------------
+// The float32 value is the one llmrs_cuda_dequantize writes (d*sc*q - dmin*m and d*sc*(q-32): exact
+// products, one rounding); hi = RN_f16(w), lo = RN_f16(w - hi) (the difference is exact in float32).
+__device__ __forceinline__ void split_pair(float w0, float w1, uint32_t &hi, uint32_t &lo) {
+    hi = pack_w(w0, w1);
+    const float2 back = __half22float2(*reinterpret_cast<const __half2 *>(&hi));
+    lo = pack_w(w0 - back.x, w1 - back.y);
+}
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t bits) { return __half2float(__ushort_as_half(bits)); }
+// (small unsigned integer < 2^23) -> float without a conversion instruction.
+__device__ __forceinline__ float u_to_f(uint32_t v) { return __uint_as_float(0x4B000000u | v) - 8388608.0f; }
+
+// Q4_K half-block G of a row -> 64 hi columns at a_taddr and 64 lo columns at a_taddr + 64.
+template <int G>
+__device__ __forceinline__ void dequant_q4k_half_split(const RawQ4 &raw, uint32_t a_taddr) {
+    const uint4 &hdr = raw.hdr;
+    const float d = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu)), dmin = f16_bits_to_f32((uint16_t)(hdr.x >> 16));
+    // the eight 6-bit scales and mins as bytes (tests/ops.rs:29-39)
+    const uint32_t sc_w = G == 0 ? (hdr.y & 0x3F3F3F3Fu) : ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u));
+    const uint32_t mn_w = G == 0 ? (hdr.z & 0x3F3F3F3Fu) : (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u));
+#pragma unroll
+    for (int sl = 0; sl < 4; sl++) {                     // sub-block 4G + sl: pair sl / 2, low nibbles for even sl
+        const float ds = d * u_to_f((sc_w >> (8 * sl)) & 0xFFu), dm = dmin * u_to_f((mn_w >> (8 * sl)) & 0xFFu);
+        const uint4 qa = raw.q[2 * (sl >> 1)], qb = raw.q[2 * (sl >> 1) + 1];
+        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+        uint32_t hi[16], lo[16];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint32_t nib = (sl & 1) ? ((w[j] >> 4) & 0x0F0F0F0Fu) : (w[j] & 0x0F0F0F0Fu);
+            float f[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) f[e] = fmaf(ds, u_to_f((nib >> (8 * e)) & 0xFFu), -dm);
+            split_pair(f[0], f[1], hi[2 * j], lo[2 * j]);
+            split_pair(f[2], f[3], hi[2 * j + 1], lo[2 * j + 1]);
+        }
+        tmem_st16(a_taddr + 16 * sl, hi);
+        tmem_st16(a_taddr + 64 + 16 * sl, lo);
+    }
+}
+
+// Q6_K half-block (slice-major layout, see dequant_q6k_half) -> 64 hi columns and 64 lo columns.
+__device__ __forceinline__ void dequant_q6k_half_split(const RawQ6 &raw, uint32_t a_taddr) {
+    const float d = f16_bits_to_f32((uint16_t)raw.d);
+#pragma unroll
+    for (int g = 0; g < 4; g++) {                        // K-local 32g + 16c + i -> column 16g + 8c + i/2
+        uint32_t hi[16], lo[16];
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+            const uint32_t sw = g < 2 ? raw.sc.x : raw.sc.y;
+            const int sc = (int)(int8_t)((sw >> (8 * (2 * (g & 1) + c))) & 0xFFu);     // scales[8h + 2g + c]
+            const float dsc = d * (float)sc;
+            const uint4 q0 = raw.ql[c][0], q1 = raw.ql[c][1], qh = raw.qh[c];
+            const uint32_t l0[4] = {q0.x, q0.y, q0.z, q0.w}, l1[4] = {q1.x, q1.y, q1.z, q1.w};
+            const uint32_t hw[4] = {qh.x, qh.y, qh.z, qh.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t lw = (g & 1) ? l1[i] : l0[i];
+                const uint32_t low = g < 2 ? (lw & 0x0F0F0F0Fu) : ((lw >> 4) & 0x0F0F0F0Fu);
+                const uint32_t v = low | (((hw[i] >> (2 * g)) & 0x03030303u) << 4);      // four 6-bit quants
+                float f[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) f[e] = dsc * (u_to_f((v >> (8 * e)) & 0xFFu) - 32.0f);
+                split_pair(f[0], f[1], hi[8 * c + 2 * i], lo[8 * c + 2 * i]);
+                split_pair(f[2], f[3], hi[8 * c + 2 * i + 1], lo[8 * c + 2 * i + 1]);
+            }
+        }
+        tmem_st16(a_taddr + 16 * g, hi);
+        tmem_st16(a_taddr + 64 + 16 * g, lo);
+    }
+}
+
 template <int QT> struct RawOf;
 template <> struct RawOf<0> { using type = RawQ4; };
 template <> struct RawOf<1> { using type = RawQ6; };
@@ -415,15 +486,24 @@ __device__ __forceinline__ typename RawOf<QT>::type load_raw(const uint8_t *row_
 }
 // ---- the kernel --------------------------------------------------------------------------------
 
-template <int TN> struct GemmCfg {
+// SPLIT: the two-term variant for small token counts that must meet the decode tolerance (1e-4).
+// Weights and activations are each kept as hi + lo f16 pairs (w = w_hi + w_lo to 2^-22, likewise x)
+// and a stage issues three products, w_hi x_hi + w_lo x_hi + w_hi x_lo, into the same fp32
+// accumulator; w_lo x_lo (2^-22 of the result) is dropped.  A weight stage is then 128 TMEM
+// columns (hi in the first 64, lo behind them) and an activation stage holds the hi sub-tiles
+// followed by the lo sub-tiles.
+template <int TN, bool SPLIT = false> struct GemmCfg {
     // A stage is 128 K elements: two 64-wide swizzled activation sub-tiles in shared memory and
     // 64 TMEM columns of weights.  One barrier round per stage keeps the single MMA-issuing
     // thread (which runs at a few cycles per instruction) ahead of the tensor core.
     static constexpr int KSUB = 2;
     static constexpr int STAGE_K = BK * KSUB;
     static constexpr int SUBTILE_BYTES = TN * BK * 2;
-    static constexpr int STAGE_BYTES = SUBTILE_BYTES * KSUB;
-    static constexpr uint32_t A_STAGE_COLS = STAGE_K / 2;            // 64 TMEM columns per weight stage
+    static constexpr int HALF_STAGE_BYTES = SUBTILE_BYTES * KSUB;      // the hi (or only) sub-tiles of a stage
+    static constexpr int STAGE_BYTES = HALF_STAGE_BYTES * (SPLIT ? 2 : 1);
+    static constexpr uint32_t A_HALF_COLS = STAGE_K / 2;             // 64 TMEM columns per weight stage and term
+    static constexpr uint32_t A_STAGE_COLS = A_HALF_COLS * (SPLIT ? 2 : 1);
+    static_assert(!SPLIT || TN <= 64, "the two-term variant serves up to 64 tokens");
     // Tensor memory (512 columns): accumulators first, weight stages behind them.  Up to 128
     // tokens the accumulator is double-buffered, so the epilogue of one tile overlaps the K loop
     // of the next; a 256-token accumulator leaves room for one.
@@ -445,10 +525,10 @@ template <int TN> struct GemmCfg {
 
 // Persistent: one CTA per SM walks tiles (weight tile fastest, so the CTAs of a wave share one
 // activation tile through L2).  14 warps: 0-7 dequantise, 8 TMA, 9 MMA + TMEM owner, 10-13 epilogue.
-template <int QT, int TN>
+template <int QT, int TN, bool SPLIT = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
-    using C = GemmCfg<TN>;
+    using C = GemmCfg<TN, SPLIT>;
     constexpr int S = C::STAGES;
     constexpr int AB = C::ACC_BUFS;
     constexpr uint32_t IDESC = umma_idesc_f16(TN);
@@ -522,7 +602,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                     break;
                 }
                 const uint32_t a_taddr = lane_base + s * C::A_STAGE_COLS;
-                if constexpr (QT == 0) {
+                if constexpr (SPLIT) {
+                    if constexpr (QT == 0) {
+                        if (g == 0) dequant_q4k_half_split<0>(cur, a_taddr);
+                        else dequant_q4k_half_split<1>(cur, a_taddr);
+                    } else {
+                        dequant_q6k_half_split(cur, a_taddr);
+                    }
+                } else if constexpr (QT == 0) {
                     const ScalesQ4 sq = unpack_scales_q4k(cur.hdr);
                     if (g == 0) dequant_q4k_half<0>(cur, sq, a_taddr);
                     else dequant_q4k_half<1>(cur, sq, a_taddr);
@@ -559,6 +646,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                     for (int us = 0; us < C::KSUB; us++)
                         tma_load_2d(tiles + s * C::STAGE_BYTES + us * C::SUBTILE_BYTES, &tmap_x,
                                     st * C::STAGE_K + us * BK, t0, &full[s]);
+                    if constexpr (SPLIT) {               // the lo terms are rows M .. 2M-1 of the same tensor
+#pragma unroll
+                        for (int us = 0; us < C::KSUB; us++)
+                            tma_load_2d(tiles + s * C::STAGE_BYTES + C::HALF_STAGE_BYTES + us * C::SUBTILE_BYTES, &tmap_x,
+                                        st * C::STAGE_K + us * BK, p.M + t0, &full[s]);
+                    }
                 }
             }
         }
@@ -603,6 +696,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                             const uint64_t b_desc = ((uint64_t)desc_hi << 32) | lo;
                             umma_f16_ts(d_tmem, a_s + (uint32_t)(us * 32 + kk * 8), b_desc, IDESC,
                                         ((st - 2 * u.b0) | us | kk) ? 1u : 0u);
+                            if constexpr (SPLIT) {       // + w_lo x_hi + w_hi x_lo
+                                const uint64_t b_lo = ((uint64_t)desc_hi << 32) | (lo + (uint32_t)(C::HALF_STAGE_BYTES >> 4));
+                                umma_f16_ts(d_tmem, a_s + C::A_HALF_COLS + (uint32_t)(us * 32 + kk * 8), b_desc, IDESC, 1u);
+                                umma_f16_ts(d_tmem, a_s + (uint32_t)(us * 32 + kk * 8), b_lo, IDESC, 1u);
+                            }
                         }
                     umma_commit(&empty[s]);        // stage free once these MMAs have read it
                 }
@@ -894,7 +992,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
 // and is applied to the token's outputs in the GEMM epilogue (exact: powers of two).
 __global__ void __launch_bounds__(256)
 activations_to_f16_kernel(const void *__restrict__ x, int x_is_bf16, int K, __half *__restrict__ out,
-                          float *__restrict__ tok_scale) {
+                          __half *__restrict__ out_lo, float *__restrict__ tok_scale) {
     __shared__ float red[8];
     const int tok = blockIdx.x;
     const size_t base = (size_t)tok * K;
@@ -943,6 +1041,16 @@ activations_to_f16_kernel(const void *__restrict__ x, int x_is_bf16, int K, __ha
         o.z = pack_w(v[4] * sc, v[5] * sc);
         o.w = pack_w(v[6] * sc, v[7] * sc);
         *reinterpret_cast<uint4 *>(out + base + k) = o;
+        if (out_lo) {                                    // two-term variant: what the f16 value left behind
+            const uint32_t h[4] = {o.x, o.y, o.z, o.w};
+            uint32_t l[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 back = __half22float2(*reinterpret_cast<const __half2 *>(&h[i]));
+                l[i] = pack_w(v[2 * i] * sc - back.x, v[2 * i + 1] * sc - back.y);
+            }
+            *reinterpret_cast<uint4 *>(out_lo + base + k) = make_uint4(l[0], l[1], l[2], l[3]);
+        }
     }
     if (threadIdx.x == 0) tok_scale[tok] = exp2i(-e);
 }
@@ -955,29 +1063,33 @@ activations_to_f16_kernel(const void *__restrict__ x, int x_is_bf16, int K, __ha
 // (32 tiles up to 128 tokens, 64 at 512) 0.52 at 16 tokens, 0.61 at 64, 0.73 at 128, 0.94 at 512;
 // K=4096 shapes 0.92 .. 1.46; more than half a wave of 256-token tiles 1.04 .. 1.8.  So the split
 // is used where at least half of the SMs would otherwise idle through a long K loop.
+// The two-term kernel spends about twice as long on a K block, the exchange costs the same, so there
+// the split already pays at K=4096 (split / no split with up to 32 tiles: 0.57 .. 0.80 at 8 .. 64
+// tokens; K=14336: 0.36 .. 0.40; 112 tiles: 1.12).
 // `forced` = 0 / 1 overrides the rule (measurements and tests), -1 leaves it alone.
-bool split_pays(int n_tiles, int nb, int sms, int forced) {
+bool split_pays(int n_tiles, int nb, int sms, int forced, bool two_term) {
     const int rest = n_tiles % sms;
     if (rest == 0 || nb < 2) return false;
     if (forced >= 0) return forced != 0;
-    return n_tiles <= sms / 2 && nb >= 32;
+    return n_tiles <= sms / 2 && nb >= (two_term ? 16 : 32);
 }
 
-template <int QT, int TN>
+template <int QT, int TN, bool SPLIT = false>
 cudaError_t launch_tn(const GemmParams &p, const void *x_f16, cudaStream_t s) {
     CUtensorMap tmap;
-    cudaError_t e = encode_2d(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x_f16, (uint64_t)p.K, (uint64_t)p.M,
-                              (uint64_t)p.K * 2, BK, TN, CU_TENSOR_MAP_SWIZZLE_128B);
+    // two-term variant: rows M .. 2M-1 of the converted activations hold the lo terms
+    cudaError_t e = encode_2d(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x_f16, (uint64_t)p.K,
+                              (uint64_t)p.M * (SPLIT ? 2 : 1), (uint64_t)p.K * 2, BK, TN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (e != cudaSuccess) return e;
-    constexpr size_t smem = GemmCfg<TN>::SMEM;
-    auto kern = gemm_kernel<QT, TN>;
+    constexpr size_t smem = GemmCfg<TN, SPLIT>::SMEM;
+    auto kern = gemm_kernel<QT, TN, SPLIT>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = ((p.N + TILE_ROWS - 1) / TILE_ROWS) * ((p.M + TN - 1) / TN);
     int grid = n_tiles < p.sm_count ? n_tiles : p.sm_count;
     GemmParams q = p;
     q.split = 0;
-    if (p.ws_slots && split_pays(n_tiles, p.K / QK_K, p.sm_count, p.split)) {
+    if (p.ws_slots && split_pays(n_tiles, p.K / QK_K, p.sm_count, p.split, SPLIT)) {
         q.split = 1;
         const int tail_blocks = (n_tiles % p.sm_count) * (p.K / QK_K);
         if (n_tiles < p.sm_count) grid = tail_blocks < p.sm_count ? tail_blocks : p.sm_count;
@@ -988,7 +1100,8 @@ cudaError_t launch_tn(const GemmParams &p, const void *x_f16, cudaStream_t s) {
 }
 
 template <int QT>
-cudaError_t launch_qt(const GemmParams &p, const void *x_f16, cudaStream_t s) {
+cudaError_t launch_qt(const GemmParams &p, const void *x_f16, bool two_term, cudaStream_t s) {
+    if (two_term) return p.M <= 32 ? launch_tn<QT, 32, true>(p, x_f16, s) : launch_tn<QT, 64, true>(p, x_f16, s);
     if (p.M <= 32) return launch_tn<QT, 32>(p, x_f16, s);
     if (p.M <= 64) return launch_tn<QT, 64>(p, x_f16, s);
     if (p.M <= 128) return launch_tn<QT, 128>(p, x_f16, s);
@@ -997,8 +1110,12 @@ cudaError_t launch_qt(const GemmParams &p, const void *x_f16, cudaStream_t s) {
 
 }  // namespace
 
-// Scratch layout: [M*K f16 activations, rounded up to 256 bytes][M float token scales].
-static size_t scratch_x_bytes(int K, int M) { return ((size_t)K * M * 2 + 255) / 256 * 256; }
+// Scratch layout: [M*K f16 activations (and M*K lo terms behind them where the two-term variant
+// can run), rounded up to 256 bytes][M float token scales].
+static size_t scratch_x_bytes(int K, int M) {
+    const size_t rows = M <= GEMM_TWO_TERM_MAX_TOKENS ? 2 * (size_t)M : (size_t)M;
+    return (rows * K * 2 + 255) / 256 * 256;
+}
 
 size_t gemm_scratch_bytes(int K, int M) { return scratch_x_bytes(K, M) + (size_t)M * sizeof(float); }
 
@@ -1010,12 +1127,14 @@ size_t gemm_split_workspace_bytes(int sms) {
 
 cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                         int K, int N, int M, void *scratch, void *split_ws, int split_mode, uint32_t *err_word,
-                        cudaStream_t s, uint64_t *launches, const GemmGather *gather) {
+                        cudaStream_t s, uint64_t *launches, const GemmGather *gather, bool two_term) {
     if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
     if (!scratch) return cudaErrorInvalidValue;
+    two_term = two_term && M <= GEMM_TWO_TERM_MAX_TOKENS;
     __half *x_f16 = (__half *)scratch;
     float *tok_scale = (float *)((uint8_t *)scratch + scratch_x_bytes(K, M));
-    activations_to_f16_kernel<<<(unsigned)M, 256, 0, s>>>(x, x_dtype == DT_BF16, K, x_f16, tok_scale);
+    activations_to_f16_kernel<<<(unsigned)M, 256, 0, s>>>(x, x_dtype == DT_BF16, K, x_f16,
+                                                          two_term ? x_f16 + (size_t)M * K : nullptr, tok_scale);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (launches) (*launches)++;
@@ -1040,10 +1159,10 @@ cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype
     }
     if (wdtype == DT_Q4K) {
         p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
-        e = launch_qt<0>(p, x_f16, s);
+        e = launch_qt<0>(p, x_f16, two_term, s);
     } else if (wdtype == DT_Q6K) {
         p.row_stride = q6k_row_stride(K);
-        e = launch_qt<1>(p, x_f16, s);
+        e = launch_qt<1>(p, x_f16, two_term, s);
     } else {
         return cudaErrorInvalidValue;
     }
@@ -1083,14 +1202,14 @@ static cudaError_t static_scratch_address(int device, void **out) {
 
 cudaError_t launch_gemm_static_scratch(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out,
                                        int out_dtype, int K, int N, int M, int device, uint32_t *err_word,
-                                       cudaStream_t s, uint64_t *launches) {
+                                       cudaStream_t s, uint64_t *launches, bool two_term) {
     if (gemm_scratch_bytes(K, M) > STATIC_SCRATCH_BYTES) return cudaErrorInvalidValue;
     void *scratch = nullptr;
     cudaError_t e = static_scratch_address(device, &scratch);
     if (e != cudaSuccess) return e;
     // Nothing in the scratch has to start at zero: the conversion kernel rewrites every f16
     // activation and every token scale the GEMM of this call reads.
-    return launch_gemm(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, scratch, nullptr, 0, err_word, s, launches, nullptr);
+    return launch_gemm(wdtype, w, x, x_dtype, out, out_dtype, K, N, M, scratch, nullptr, 0, err_word, s, launches, nullptr, two_term);
 }
 
 }  // namespace llmrs

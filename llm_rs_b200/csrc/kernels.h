@@ -135,6 +135,11 @@ int gemv_single_launch_max_tokens(int wdtype, int K);
 // `gather` (optional, world > 1): this call computes one rank's rows of an N-sharded matmul; `out` is
 // then the rank's full [M, N * world] result and the all-gather runs inside the kernel through the
 // peers' mailboxes, exactly as in launch_gemv_allgather (same mailbox size and layout).
+// `two_term` (up to GEMM_TWO_TERM_MAX_TOKENS tokens; ignored above): weights and activations are
+// each carried as a hi + lo pair of f16 values and three products are accumulated per K step, which
+// brings the result to the decode kernel's tolerance class (1e-4 relative L2 against float32) at
+// roughly twice the time of the one-term kernel.
+constexpr int GEMM_TWO_TERM_MAX_TOKENS = 64;
 struct GemmGather {
     int world, rank;
     void *const *peer_mailbox;
@@ -145,7 +150,7 @@ size_t gemm_split_workspace_bytes(int sms);
 size_t gemm_split_counter_bytes();      // the leading bytes of the workspace that must be zero
 cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                         int K, int N, int M, void *scratch, void *split_ws, int split_mode, uint32_t *err_word,
-                        cudaStream_t s, uint64_t *launches, const GemmGather *gather = nullptr);
+                        cudaStream_t s, uint64_t *launches, const GemmGather *gather = nullptr, bool two_term = false);
 
 // The same GEMM with its scratch in a fixed 8 MiB device array that is part of the library image:
 // no allocation on this path.  `device` must be the current device; the first call on a device
@@ -154,6 +159,6 @@ cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype
 size_t gemm_static_scratch_capacity();
 cudaError_t launch_gemm_static_scratch(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out,
                                        int out_dtype, int K, int N, int M, int device, uint32_t *err_word,
-                                       cudaStream_t s, uint64_t *launches);
+                                       cudaStream_t s, uint64_t *launches, bool two_term = false);
 
 }  // namespace llmrs

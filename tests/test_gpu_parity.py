@@ -19,8 +19,23 @@ GEMV_TOL = 1e-4      # exact decode kernel (M <= 4 by default)
 TC_TOL = 2e-3        # tensor-core kernel (M >= 5): f16 operands, fp32 accumulate
 
 
+@pytest.fixture(scope="module")
+def backend_tc(cuda_lib):
+    """A context with a hard boundary: five tokens and more always run on the tensor cores."""
+    import os
+    from llm_rs_b200 import CudaBackend
+    os.environ["LLMRS_GEMV_MAX_M"] = "4"
+    try:
+        be = CudaBackend(0)
+    finally:
+        del os.environ["LLMRS_GEMV_MAX_M"]
+    yield be
+    be.close()
+
+
 def tol_for(M):
-    return GEMV_TOL if M <= 4 else TC_TOL
+    """Up to 4 tokens the decode kernel, up to 64 the two-term tensor-core kernel: both 1e-4."""
+    return GEMV_TOL if M <= 64 else TC_TOL
 
 
 def upload_weight(be, dt, w, K, N):
@@ -114,7 +129,10 @@ def test_check_matmul_q4k(backend, in_f, out_f, seq):
     (4096, 2049, 5), (4096, 512, 8), (4096, 300, 9), (14336, 256, 1), (14336, 64, 4), (28672, 32, 1),
     (28672, 40, 2), (4096, 129, 32), (4096, 96, 64), (18432, 16, 1),
 ])
-def test_matmul_f32_parity(backend, dt, K, N, M):
+@pytest.mark.parametrize("ctx", ["backend", "backend_tc"])
+def test_matmul_f32_parity(request, ctx, dt, K, N, M):
+    """`backend` picks the cheaper kernel between 5 and 64 tokens, `backend_tc` always the tensor cores."""
+    backend = request.getfixturevalue(ctx)
     w = synth.weight(dt, K, N, tid=7 * K + N + M)
     x = synth.activations(M, K, tid=2000 + M)
     got = run_matmul(backend, upload_weight(backend, dt, w, K, N), x, K, N, M)
@@ -652,15 +670,72 @@ def test_gemm_token_scaling(backend):
 
 
 @pytest.fixture(scope="module")
+def backend_one_term(cuda_lib):
+    """A context whose tensor-core path keeps single f16 operands at every token count."""
+    import os
+    from llm_rs_b200 import CudaBackend
+    os.environ["LLMRS_TC_TWO_TERM"] = "0"
+    os.environ["LLMRS_GEMV_MAX_M"] = "4"
+    try:
+        be = CudaBackend(0)
+    finally:
+        del os.environ["LLMRS_TC_TWO_TERM"], os.environ["LLMRS_GEMV_MAX_M"]
+    yield be
+    be.close()
+
+
+@pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
+@pytest.mark.parametrize("K,N,M", [(4096, 2049, 5), (4096, 300, 9), (4096, 129, 32), (1024, 96, 64), (14336, 40, 17)])
+def test_one_term_kernel_below_65_tokens(backend_one_term, dt, K, N, M):
+    """LLMRS_TC_TWO_TERM=0: the faster single-f16 kernel, held to the prefill tolerance."""
+    w = synth.weight(dt, K, N, tid=7 * K + N + M)
+    x = synth.activations(M, K, tid=2000 + M)
+    got = run_matmul(backend_one_term, upload_weight(backend_one_term, dt, w, K, N), x, K, N, M)
+    err = O.rel_l2(got, O.matmul(dt, w, K, N, x, acc="f64"))
+    assert err <= GEMM_TOL
+    assert err > GEMV_TOL / 4, "the one-term kernel is expected to sit near 4e-4: was the two-term kernel launched?"
+
+
+@pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
+@pytest.mark.parametrize("in_bf16,out_bf16", [(True, False), (False, True), (True, True)])
+def test_two_term_bf16_io(backend_tc, dt, in_bf16, out_bf16):
+    backend = backend_tc
+    K, N, M = 2048, 300, 24
+    w = synth.weight(dt, K, N, tid=61)
+    x = synth.activations(M, K, tid=62)
+    xe = O.bf16_bits_to_f32(synth.bf16_bits(x)).reshape(M, K) if in_bf16 else x
+    got = run_matmul(backend, upload_weight(backend, dt, w, K, N), x, K, N, M, in_bf16, out_bf16)
+    truth = O.matmul(dt, w, K, N, xe, acc="f64")
+    assert O.rel_l2(got, truth) <= GEMV_TOL + (2.0 ** -8 if out_bf16 else 0.0)
+
+
+def test_two_term_token_scaling(backend_tc):
+    """Token rows 40 decades apart, an all-zero row: every row of the two-term kernel stays at 1e-4."""
+    backend = backend_tc
+    K, N, M = 1024, 128, 40
+    w = synth.weight(O.Q6K, K, N, tid=71)
+    x = synth.activations(M, K, tid=72)
+    x = x * (np.float32(10.0) ** np.linspace(-20, 20, M).astype(np.float32))[:, None]
+    x[5] = 0.0
+    got = run_matmul(backend, upload_weight(backend, O.Q6K, w, K, N), x, K, N, M)
+    truth = O.matmul(O.Q6K, w, K, N, x, acc="f64")
+    assert np.isfinite(got).all() and not got[5].any()
+    for t in range(M):
+        if t != 5:
+            assert O.rel_l2(got[t], truth[t]) <= GEMV_TOL, t
+
+
+@pytest.fixture(scope="module")
 def backend_split(cuda_lib):
     """A context whose tensor-core path always cuts the last, partial wave of tiles along K."""
     import os
     from llm_rs_b200 import CudaBackend
     os.environ["LLMRS_GEMM_SPLIT"] = "1"
+    os.environ["LLMRS_GEMV_MAX_M"] = "4"
     try:
         be = CudaBackend(0)
     finally:
-        del os.environ["LLMRS_GEMM_SPLIT"]
+        del os.environ["LLMRS_GEMM_SPLIT"], os.environ["LLMRS_GEMV_MAX_M"]
     yield be
     be.close()
 
@@ -682,7 +757,7 @@ def test_gemm_split_last_wave(backend_split, dt, K, N, M, out_bf16):
     wb = upload_weight(backend_split, dt, w, K, N)
     rows = (0, N) if N * M * K < 3e10 else (N - 256, N)
     truth = O.matmul(dt, w, K, N, x, acc="f64", rows=rows)
-    tol = GEMM_TOL + (2.0 ** -8 if out_bf16 else 0.0)
+    tol = tol_for(M) + (2.0 ** -8 if out_bf16 else 0.0)
     for _ in range(2):
         got = run_matmul(backend_split, wb, x, K, N, M, False, out_bf16)
         assert O.rel_l2(got[:, rows[0]:rows[1]], truth[:, rows[0]:rows[1]]) <= tol
