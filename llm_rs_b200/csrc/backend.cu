@@ -351,18 +351,18 @@ int llmrs_cuda_write(llmrs_ctx *ctx, llmrs_buf *dst, const void *host, size_t nb
 // Between the decode kernel's token limit and 64 tokens both kernels meet the decode tolerance, so
 // the cheaper one runs.  The decode kernel streams the weights once per pass of up to four tokens
 // (fewer where the staged activations of four do not fit): about 2 us + 0.2 us per MB and token,
-// at least 4.5 us per pass.  The tensor-core kernel has a floor of a few tens of microseconds (its
-// pipeline fill and the activation conversion) and streams the weights once: two-term
-// 45 us + 0.55 us/MB, one-term 24 us + 0.27 us/MB.  Fitted on a B200 to 4096x4096 .. 4096x128256
-// weights at 5 .. 64 tokens.
+// at least 4.5 us per pass.  The tensor-core kernel streams the weights once behind a floor (pipeline
+// fill, activation conversion): two-term max(47 us, 0.61 us/MB), or 27 us + 0.6 us/MB where its tiles
+// are cut along K over all SMs; one-term max(25 us, 0.31 us/MB).  Fitted on a B200 to 4096x1024 ..
+// 4096x128256 weights at 5 .. 64 tokens.
 static bool decode_kernel_cheaper(const llmrs_ctx *ctx, const llmrs_buf *weight, uint32_t M, uint32_t K) {
     if (!ctx->cost_rule || M > (uint32_t)GEMM_TWO_TERM_MAX_TOKENS || K > gemv_max_k()) return false;
     const int per_pass = std::min(4, gemv_single_launch_max_tokens((int)weight->dtype, (int)K));
     if (per_pass <= 0) return false;
     const double mb = (double)weight->nbytes * 1e-6;
-    // weights of up to half a wave of tiles and K >= 4096 are cut along K over all SMs: floor 27 us
+    // two-term: weights of up to half a wave of tiles and K >= 4096 are cut along K over all SMs
     const bool cut = ctx->split_ws && ctx->gemm_split != 0 && K >= 4096 && (weight->dim1 + 127) / 128 <= (uint32_t)ctx->sm_count / 2;
-    const double tc = ctx->two_term ? (cut ? 27.0 : 45.0) + 0.55 * mb : 24.0 + 0.27 * mb;
+    const double tc = !ctx->two_term ? std::max(25.0, 0.31 * mb) : cut ? 27.0 + 0.6 * mb : std::max(47.0, 0.61 * mb);
     double decode = 0.0;
     for (uint32_t done = 0; done < M; done += (uint32_t)per_pass)
         decode += std::max(4.5, 2.0 + 0.2 * mb * std::min<uint32_t>((uint32_t)per_pass, M - done));

@@ -435,7 +435,7 @@ __device__ __forceinline__ void dequant_q4k_half_split(const RawQ4 &raw, uint32_
             const uint32_t nib = (sl & 1) ? ((w[j] >> 4) & 0x0F0F0F0Fu) : (w[j] & 0x0F0F0F0Fu);
             float f[4];
 #pragma unroll
-            for (int e = 0; e < 4; e++) f[e] = fmaf(ds, u_to_f((nib >> (8 * e)) & 0xFFu), -dm);
+            for (int e = 0; e < 4; e++) f[e] = fmaf(ds, byte_to_float(nib, e), -dm);
             split_pair(f[0], f[1], hi[2 * j], lo[2 * j]);
             split_pair(f[2], f[3], hi[2 * j + 1], lo[2 * j + 1]);
         }
@@ -465,7 +465,8 @@ __device__ __forceinline__ void dequant_q6k_half_split(const RawQ6 &raw, uint32_
                 const uint32_t v = low | (((hw[i] >> (2 * g)) & 0x03030303u) << 4);      // four 6-bit quants
                 float f[4];
 #pragma unroll
-                for (int e = 0; e < 4; e++) f[e] = dsc * (u_to_f((v >> (8 * e)) & 0xFFu) - 32.0f);
+                for (int e = 0; e < 4; e++)                   // one permute drops the byte into 2^23's mantissa
+                    f[e] = dsc * (__uint_as_float(__byte_perm(v, 0x4B000000u, 0x7440u + (uint32_t)e)) - 8388640.0f);
                 split_pair(f[0], f[1], hi[8 * c + 2 * i], lo[8 * c + 2 * i]);
                 split_pair(f[2], f[3], hi[8 * c + 2 * i + 1], lo[8 * c + 2 * i + 1]);
             }
@@ -489,9 +490,12 @@ __device__ __forceinline__ typename RawOf<QT>::type load_raw(const uint8_t *row_
 // SPLIT: the two-term variant for small token counts that must meet the decode tolerance (1e-4).
 // Weights and activations are each kept as hi + lo f16 pairs (w = w_hi + w_lo to 2^-22, likewise x)
 // and a stage issues three products, w_hi x_hi + w_lo x_hi + w_hi x_lo, into the same fp32
-// accumulator; w_lo x_lo (2^-22 of the result) is dropped.  A weight stage is then 128 TMEM
+// accumulators; w_lo x_lo (2^-22 of the result) is dropped.  A weight stage is then 128 TMEM
 // columns (hi in the first 64, lo behind them) and an activation stage holds the hi sub-tiles
-// followed by the lo sub-tiles.
+// followed by the lo sub-tiles.  The two small products go to an accumulator of their own, which the
+// epilogue adds: the tensor core's fp32 accumulation does not round to nearest, every product added
+// to the large sum costs about 2^-25 of it (measured: 1.4e-5 relative after the 768 additions of
+// K=4096 with one accumulator), so the large sum takes only the one product per K step it must.
 template <int TN, bool SPLIT = false> struct GemmCfg {
     // A stage is 128 K elements: two 64-wide swizzled activation sub-tiles in shared memory and
     // 64 TMEM columns of weights.  One barrier round per stage keeps the single MMA-issuing
@@ -507,8 +511,10 @@ template <int TN, bool SPLIT = false> struct GemmCfg {
     // Tensor memory (512 columns): accumulators first, weight stages behind them.  Up to 128
     // tokens the accumulator is double-buffered, so the epilogue of one tile overlaps the K loop
     // of the next; a 256-token accumulator leaves room for one.
-    static constexpr int ACC_BUFS = TN <= 128 ? 2 : 1;
-    static constexpr uint32_t A_BASE_COL = ACC_BUFS * TN;
+    // (the two-term variant has one buffer of two accumulators: main and small products)
+    static constexpr int ACC_BUFS = SPLIT ? 1 : (TN <= 128 ? 2 : 1);
+    static constexpr uint32_t ACC_COLS = SPLIT ? 2 * TN : TN;
+    static constexpr uint32_t A_BASE_COL = ACC_BUFS * ACC_COLS;
     static constexpr int TMEM_STAGES = (512 - (int)A_BASE_COL) / (int)A_STAGE_COLS;
     static constexpr int SMEM_STAGES = (227 * 1024 - 1280 - (EPI_WARPS * (EPI_TOK * 32 * 4) + EPI_WARPS * TN_PAD * 4)) / STAGE_BYTES;
     static constexpr int STAGES = TMEM_STAGES < SMEM_STAGES ? (TMEM_STAGES < 4 ? TMEM_STAGES : 4)
@@ -676,7 +682,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                     break;
                 }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + ab * TN;
+                const uint32_t d_tmem = tmem_base + ab * C::ACC_COLS;
                 for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
                     const uint32_t s = it % S;
                     if (!mbar_wait(&full[s], (it / S) & 1)) {
@@ -696,10 +702,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                             const uint64_t b_desc = ((uint64_t)desc_hi << 32) | lo;
                             umma_f16_ts(d_tmem, a_s + (uint32_t)(us * 32 + kk * 8), b_desc, IDESC,
                                         ((st - 2 * u.b0) | us | kk) ? 1u : 0u);
-                            if constexpr (SPLIT) {       // + w_lo x_hi + w_hi x_lo
+                            if constexpr (SPLIT) {       // w_lo x_hi + w_hi x_lo, into the accumulator behind the main one
                                 const uint64_t b_lo = ((uint64_t)desc_hi << 32) | (lo + (uint32_t)(C::HALF_STAGE_BYTES >> 4));
-                                umma_f16_ts(d_tmem, a_s + C::A_HALF_COLS + (uint32_t)(us * 32 + kk * 8), b_desc, IDESC, 1u);
-                                umma_f16_ts(d_tmem, a_s + (uint32_t)(us * 32 + kk * 8), b_lo, IDESC, 1u);
+                                umma_f16_ts(d_tmem + TN, a_s + C::A_HALF_COLS + (uint32_t)(us * 32 + kk * 8), b_desc, IDESC,
+                                            ((st - 2 * u.b0) | us | kk) ? 1u : 0u);
+                                umma_f16_ts(d_tmem + TN, a_s + (uint32_t)(us * 32 + kk * 8), b_lo, IDESC, 1u);
                             }
                         }
                     umma_commit(&empty[s]);        // stage free once these MMAs have read it
@@ -787,7 +794,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                 tok_base = 0; row_base = 32 * quarter; tok_lim = TN; row_lim = TILE_ROWS;
             }
             const bool vec_ok = (o_stride % (size_t)(16 / esz)) == 0;     // 16-byte stores need whole vectors per token
-            const uint32_t acc = tmem_base + ab * TN + ((uint32_t)(32 * quarter) << 16);
+            const uint32_t acc = tmem_base + ab * C::ACC_COLS + ((uint32_t)(32 * quarter) << 16);
 #pragma unroll 1
             for (int g0 = 0; g0 < TN && !dead; g0 += EPI_TOK) {
                 constexpr int GT = TN < EPI_TOK ? TN : EPI_TOK;  // tokens in this group
@@ -795,6 +802,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                 uint32_t v[GT / 16][16];
 #pragma unroll
                 for (int c = 0; c < GT / 16; c++) tmem_ld16(acc + (uint32_t)(g0 + 16 * c), v[c]);
+                if constexpr (SPLIT) {                           // plus the accumulator of the small products
+                    uint32_t sm[GT / 16][16];
+#pragma unroll
+                    for (int c = 0; c < GT / 16; c++) tmem_ld16(acc + (uint32_t)(TN + g0 + 16 * c), sm[c]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < GT / 16; c++)
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            v[c][j] = __float_as_uint(__uint_as_float(v[c][j]) + __uint_as_float(sm[c][j]));
+                }
                 tmem_ld_wait();
                 if (g0 + GT >= TN) {                             // last read of this accumulator: hand it back
                     tc_fence_before();

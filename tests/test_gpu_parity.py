@@ -127,7 +127,7 @@ def test_check_matmul_q4k(backend, in_f, out_f, seq):
 @pytest.mark.parametrize("K,N,M", [
     (256, 1, 1), (256, 7, 1), (256, 33, 2), (512, 65, 3), (768, 100, 4), (4096, 4096, 1), (4096, 1024, 2),
     (4096, 2049, 5), (4096, 512, 8), (4096, 300, 9), (14336, 256, 1), (14336, 64, 4), (28672, 32, 1),
-    (28672, 40, 2), (4096, 129, 32), (4096, 96, 64), (18432, 16, 1),
+    (28672, 40, 2), (4096, 129, 32), (4096, 96, 64), (18432, 16, 1), (14336, 40, 17), (28672, 130, 9), (28672, 24, 64),
 ])
 @pytest.mark.parametrize("ctx", ["backend", "backend_tc"])
 def test_matmul_f32_parity(request, ctx, dt, K, N, M):
