@@ -59,7 +59,11 @@ enum llmrs_status {
     LLMRS_ERR_DTYPE = -3,        /* dtype not supported on this path */
     LLMRS_ERR_ARG = -4,          /* null pointer, bad size, wrong context */
     LLMRS_ERR_NO_DEVICE = -5,    /* no CUDA device / not an sm_100 device */
-    LLMRS_ERR_KERNEL = -6        /* a kernel abandoned a bounded wait; reported at the next sync/read */
+    LLMRS_ERR_KERNEL = -6,       /* a kernel abandoned a bounded wait; reported at the next sync/read */
+    LLMRS_ERR_IO = -7,           /* a file could not be opened or read (GgufError::Io) */
+    LLMRS_ERR_FORMAT = -8,       /* not a GGUF v2/v3 file, or its directory is malformed (GgufError::InvalidMagic,
+                                    UnsupportedVersion, UnknownDType, UnknownMetadataType, InvalidUtf8) */
+    LLMRS_ERR_NOT_FOUND = -9     /* no tensor / metadata key of that name (GgufError::TensorNotFound) */
 };
 
 typedef struct llmrs_ctx llmrs_ctx;
@@ -285,6 +289,80 @@ int llmrs_cuda_launch_count(llmrs_ctx *ctx, uint64_t *count);
 
 /* Message of the last failure on `ctx` (or of the last failed create when ctx is NULL). */
 const char *llmrs_cuda_last_error(llmrs_ctx *ctx);
+
+/* ---- GGUF files: the on-disk step in front of upload_tensor --------------------------------------
+ * Replaces GgufFile (src/gguf/mod.rs:80-86).  The reference reads the whole file into one page-aligned
+ * host copy that its unified-memory GPU then addresses in place (:167-175, :307-342; metal/mod.rs:463-484).
+ * Here only the directory (metadata and tensor table) stays on the host; a tensor's bytes travel
+ * file -> pinned staging -> device when it is uploaded.  A handle is independent of any context and
+ * may be shared by the contexts of several GPUs (each uploads its own tensors or slices). */
+typedef struct llmrs_gguf llmrs_gguf;
+
+/* One entry of the tensor table (TensorInfo, src/gguf/mod.rs:14-24; what tensor_view returns, :242-254,
+ * without the bytes).  `name` stays valid until llmrs_gguf_close.  shape[0] is the contiguous
+ * dimension, as stored in the file. */
+typedef struct llmrs_gguf_tensor {
+    const char *name;
+    uint32_t dtype;      /* GGUF type id, 0..30 (src/tensor/mod.rs:96-130); not limited to llmrs_dtype */
+    uint32_t n_dims;     /* at most 4 */
+    uint64_t shape[4];
+    uint64_t offset;     /* from the start of the data section (llmrs_gguf_data_offset) */
+    uint64_t nbytes;     /* DType::storage_size of the shape (src/tensor/mod.rs:89-93) */
+} llmrs_gguf_tensor;
+
+/* Metadata value types (src/gguf/mod.rs:256-273). */
+enum llmrs_gguf_type {
+    LLMRS_GGUF_U8 = 0, LLMRS_GGUF_I8 = 1, LLMRS_GGUF_U16 = 2, LLMRS_GGUF_I16 = 3, LLMRS_GGUF_U32 = 4,
+    LLMRS_GGUF_I32 = 5, LLMRS_GGUF_F32 = 6, LLMRS_GGUF_BOOL = 7, LLMRS_GGUF_STRING = 8, LLMRS_GGUF_ARRAY = 9,
+    LLMRS_GGUF_U64 = 10, LLMRS_GGUF_I64 = 11, LLMRS_GGUF_F64 = 12
+};
+
+/* Replaces GgufFile::open (src/gguf/mod.rs:167-218): magic, version 2 or 3, key/value section, tensor
+ * table, data section at the next multiple of 32.  A truncated or malformed directory is an error
+ * (the reference panics on an out-of-range slice).  Failures: LLMRS_ERR_IO / LLMRS_ERR_FORMAT with
+ * the text in llmrs_gguf_last_error(). */
+int llmrs_gguf_open(const char *path, llmrs_gguf **out);
+void llmrs_gguf_close(llmrs_gguf *g);
+/* Message of the last failed llmrs_gguf_* call on this thread. */
+const char *llmrs_gguf_last_error(void);
+
+uint32_t llmrs_gguf_version(const llmrs_gguf *g);
+uint64_t llmrs_gguf_file_size(const llmrs_gguf *g);        /* GgufFile::file_size (:224-226) */
+uint64_t llmrs_gguf_data_offset(const llmrs_gguf *g);
+uint64_t llmrs_gguf_tensor_count(const llmrs_gguf *g);
+uint64_t llmrs_gguf_metadata_count(const llmrs_gguf *g);
+
+/* Tensor table by position (GgufFile::tensors) and by name (the lookup of tensor_view, :243-244). */
+int llmrs_gguf_tensor_at(const llmrs_gguf *g, uint64_t index, llmrs_gguf_tensor *out);
+int llmrs_gguf_find_tensor(const llmrs_gguf *g, const char *name, llmrs_gguf_tensor *out);
+/* The bytes tensor_view exposes as TensorView.data (:246-253), copied to `host` (nbytes must equal the
+ * tensor's).  Eight concurrent positional reads, as read_file_fast (:307-342). */
+int llmrs_gguf_read_tensor(const llmrs_gguf *g, const char *name, void *host, size_t nbytes);
+
+/* Key/value section by position: key, type, and for arrays element type and length (any may be NULL). */
+int llmrs_gguf_metadata_at(const llmrs_gguf *g, uint64_t index, const char **key, uint32_t *type,
+                           uint32_t *elem_type, uint64_t *count);
+/* Values by key (of two equal keys the later one, as the reference's map keeps it).
+ * get_u32: MetadataValue::as_u32, U32/I32/U64/I64 truncated (src/gguf/metadata.rs:38-46);
+ * get_u64: any integer or bool, sign-extended; get_f64: as_f32's F32/F64 (:48-54), not narrowed;
+ * get_str: as_str (:31-36), not NUL-terminated, valid until close;
+ * get_array: element type, length and, for numeric arrays, the packed little-endian elements;
+ * get_array_str: element `index` of an array of strings (as_string_array, :56-61). */
+int llmrs_gguf_get_u32(const llmrs_gguf *g, const char *key, uint32_t *out);
+int llmrs_gguf_get_u64(const llmrs_gguf *g, const char *key, uint64_t *out);
+int llmrs_gguf_get_f64(const llmrs_gguf *g, const char *key, double *out);
+int llmrs_gguf_get_str(const llmrs_gguf *g, const char *key, const char **out, uint64_t *len);
+int llmrs_gguf_get_array(const llmrs_gguf *g, const char *key, uint32_t *elem_type, uint64_t *count, const void **data);
+int llmrs_gguf_get_array_str(const llmrs_gguf *g, const char *key, uint64_t index, const char **out, uint64_t *len);
+
+/* Replaces Loader::opt (src/arch/mod.rs:52-57): tensor_view(name) + upload_tensor in one call, without a
+ * host copy of the tensor.  The bytes are read in pieces of whole rows into two pinned staging buffers
+ * (eight concurrent positional reads per piece) and copied to the device piece by piece, the read of one
+ * piece overlapping the copy (and, for Q6_K, the re-layout kernel) of the one before.  Shapes: 1-D or 2-D
+ * as upload_tensor takes them (trailing dimensions of 1 are dropped); dtypes as upload_tensor.
+ * LLMRS_ERR_NOT_FOUND when the file has no such tensor (Loader::opt's None).  Returns when the tensor is
+ * complete in device memory. */
+int llmrs_cuda_upload_gguf_tensor(llmrs_ctx *ctx, const llmrs_gguf *g, const char *name, llmrs_buf *out);
 
 #ifdef __cplusplus
 }

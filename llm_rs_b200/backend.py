@@ -68,6 +68,12 @@ class BackendError(RuntimeError):
         self.code = code
 
 
+class _GgufTensor(C.Structure):
+    """llmrs_gguf_tensor: one entry of a GGUF file's tensor table."""
+    _fields_ = [("name", C.c_char_p), ("dtype", C.c_uint32), ("n_dims", C.c_uint32), ("shape", C.c_uint64 * 4),
+                ("offset", C.c_uint64), ("nbytes", C.c_uint64)]
+
+
 class _Buf(C.Structure):
     _fields_ = [("dptr", C.c_void_p), ("nbytes", C.c_uint64), ("dtype", C.c_uint32), ("dim0", C.c_uint32),
                 ("dim1", C.c_uint32), ("layout", C.c_uint32), ("owned", C.c_uint32), ("device", C.c_uint32)]
@@ -113,6 +119,26 @@ ABI = {
     "llmrs_cuda_reset_gpu_secs": (C.c_int, [_VP]),
     "llmrs_cuda_launch_count": (C.c_int, [_VP, _U64P]),
     "llmrs_cuda_last_error": (C.c_char_p, [_VP]),
+    "llmrs_cuda_upload_gguf_tensor": (C.c_int, [_VP, _VP, C.c_char_p, _BUFP]),
+    "llmrs_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(_VP)]),
+    "llmrs_gguf_close": (None, [_VP]),
+    "llmrs_gguf_last_error": (C.c_char_p, []),
+    "llmrs_gguf_version": (C.c_uint32, [_VP]),
+    "llmrs_gguf_file_size": (C.c_uint64, [_VP]),
+    "llmrs_gguf_data_offset": (C.c_uint64, [_VP]),
+    "llmrs_gguf_tensor_count": (C.c_uint64, [_VP]),
+    "llmrs_gguf_metadata_count": (C.c_uint64, [_VP]),
+    "llmrs_gguf_tensor_at": (C.c_int, [_VP, C.c_uint64, C.POINTER(_GgufTensor)]),
+    "llmrs_gguf_find_tensor": (C.c_int, [_VP, C.c_char_p, C.POINTER(_GgufTensor)]),
+    "llmrs_gguf_read_tensor": (C.c_int, [_VP, C.c_char_p, _VP, C.c_size_t]),
+    "llmrs_gguf_metadata_at": (C.c_int, [_VP, C.c_uint64, C.POINTER(C.c_char_p), C.POINTER(C.c_uint32),
+                                         C.POINTER(C.c_uint32), _U64P]),
+    "llmrs_gguf_get_u32": (C.c_int, [_VP, C.c_char_p, C.POINTER(C.c_uint32)]),
+    "llmrs_gguf_get_u64": (C.c_int, [_VP, C.c_char_p, _U64P]),
+    "llmrs_gguf_get_f64": (C.c_int, [_VP, C.c_char_p, C.POINTER(C.c_double)]),
+    "llmrs_gguf_get_str": (C.c_int, [_VP, C.c_char_p, C.POINTER(_VP), _U64P]),
+    "llmrs_gguf_get_array": (C.c_int, [_VP, C.c_char_p, C.POINTER(C.c_uint32), _U64P, C.POINTER(_VP)]),
+    "llmrs_gguf_get_array_str": (C.c_int, [_VP, C.c_char_p, C.c_uint64, C.POINTER(_VP), _U64P]),
 }
 
 _lib = None

@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "../../include/llmrs_cuda.h"
+#include "gguf.h"
 #include "kernels.h"
 
 using namespace llmrs;
@@ -52,6 +53,10 @@ struct llmrs_ctx {
     size_t att_ws_bytes = 0;
     uint32_t *argmax_out = nullptr;  // device word argmax writes its result to
     uint32_t *tokens = nullptr;      // device copy of embed's token ids
+    // GGUF uploads: two pinned host pieces, two device pieces (raw Q6_K before its re-layout), one event each
+    uint8_t *stage_host[2] = {nullptr, nullptr};
+    uint8_t *stage_dev[2] = {nullptr, nullptr};
+    cudaEvent_t stage_done[2] = {nullptr, nullptr};
     size_t tokens_cap = 0;
     void *split_ws = nullptr;        // workspace of the tensor-core path's split of the last wave (zero between launches)
     uint32_t *dev_error = nullptr;   // device word: first KernelError reported by a kernel; next word: CTA counter
@@ -237,6 +242,11 @@ int llmrs_cuda_destroy(llmrs_ctx *ctx) {
     if (ctx->argmax_out) cudaFree(ctx->argmax_out);
     if (ctx->att_ws) cudaFree(ctx->att_ws);
     if (ctx->norm_tmp) cudaFree(ctx->norm_tmp);
+    for (int i = 0; i < 2; i++) {
+        if (ctx->stage_host[i]) cudaFreeHost(ctx->stage_host[i]);
+        if (ctx->stage_dev[i]) cudaFree(ctx->stage_dev[i]);
+        if (ctx->stage_done[i]) cudaEventDestroy(ctx->stage_done[i]);
+    }
     delete ctx;
     return LLMRS_OK;
 }
@@ -332,6 +342,84 @@ int llmrs_cuda_upload_tensor(llmrs_ctx *ctx, uint32_t dtype, const uint64_t *sha
         return ctx->cuda_fail(e, "upload_tensor: copy");
     }
     *out = llmrs_buf{p, dev_bytes, dtype, d0, d1, layout, 1u, (uint32_t)ctx->device};
+    return LLMRS_OK;
+}
+
+// Piece size of a streamed upload: large enough that eight readers each get the 4 MiB requests the
+// reference issues (src/gguf/mod.rs:311-312) and that a copy runs at the link's rate, small enough that
+// two pinned pieces cost little host memory.
+static constexpr size_t UPLOAD_PIECE_BYTES = 32u << 20;
+static constexpr int UPLOAD_READERS = 8;
+
+int llmrs_cuda_upload_gguf_tensor(llmrs_ctx *ctx, const llmrs_gguf *gf, const char *name, llmrs_buf *out) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    if (!gf || !name || !out) return ctx->fail(LLMRS_ERR_ARG, "upload_gguf_tensor: null pointer");
+    const llmrs::GgufFile *g = reinterpret_cast<const llmrs::GgufFile *>(gf);
+    const llmrs::GgufTensor *t = g->find_tensor(name);
+    if (!t) return ctx->fail(LLMRS_ERR_NOT_FOUND, "tensor not found: %s", name);
+    int ndims = (int)t->n_dims;
+    while (ndims > 2 && t->shape[ndims - 1] == 1) ndims--;          // [K, N, 1, 1] is the 2-D tensor [K, N]
+    uint32_t d0, d1;
+    if (!shape_dims(t->shape, ndims, &d0, &d1))
+        return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s has a shape this backend does not hold (1-D or 2-D)", name);
+    const uint32_t dtype = t->dtype;
+    const bool quant = dtype == LLMRS_Q4K || dtype == LLMRS_Q6K;
+    if (quant && d0 % QK_K)
+        return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s: in_features %u is not a multiple of 256", name, d0);
+    size_t want = 0;
+    if (!storage_size(dtype, (uint64_t)d0 * (d1 ? d1 : 1), &want))
+        return ctx->fail(LLMRS_ERR_DTYPE, "upload_gguf_tensor: %s: dtype %u is not supported (F32, BF16, I32, Q4_K, Q6_K)", name, dtype);
+    if (want != t->nbytes) return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s: directory and shape disagree on the size", name);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaSuccess;
+    for (int i = 0; i < 2 && e == cudaSuccess; i++) {
+        if (!ctx->stage_host[i]) e = cudaHostAlloc((void **)&ctx->stage_host[i], UPLOAD_PIECE_BYTES, cudaHostAllocDefault);
+        if (e == cudaSuccess && !ctx->stage_done[i]) e = cudaEventCreateWithFlags(&ctx->stage_done[i], cudaEventDisableTiming);
+        if (e == cudaSuccess && dtype == LLMRS_Q6K && !ctx->stage_dev[i]) e = cudaMalloc((void **)&ctx->stage_dev[i], UPLOAD_PIECE_BYTES);
+    }
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "upload_gguf_tensor: staging buffers");
+    const int K = (int)d0, N = (int)(d1 ? d1 : 1);
+    const size_t dev_bytes = quant ? weight_device_bytes((int)dtype, K, N) : want;
+    uint8_t *p = nullptr;
+    e = cudaMalloc((void **)&p, dev_bytes);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "upload_gguf_tensor: cudaMalloc");
+    // pieces of whole rows, so that the Q6_K re-layout can run piece by piece
+    const size_t row_bytes = want / (size_t)N;
+    if (row_bytes > UPLOAD_PIECE_BYTES) {
+        cudaFree(p);
+        return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s: one row is %zu bytes, more than a staging piece", name, row_bytes);
+    }
+    const size_t rows_per_piece = UPLOAD_PIECE_BYTES / row_bytes;
+    const uint64_t file_pos = g->data_offset + t->offset;
+    bool io_ok = true;
+    int piece = 0;
+    for (size_t row = 0; row < (size_t)N && e == cudaSuccess && io_ok; row += rows_per_piece, piece++) {
+        const int sb = piece & 1;
+        const size_t rows = std::min(rows_per_piece, (size_t)N - row), bytes = rows * row_bytes;
+        if (piece >= 2) e = cudaEventSynchronize(ctx->stage_done[sb]);      // the copy out of this piece, two pieces ago
+        if (e != cudaSuccess) break;
+        io_ok = llmrs::gguf_pread_parallel(g->fd, ctx->stage_host[sb], file_pos + row * row_bytes, bytes, UPLOAD_READERS);
+        if (!io_ok) break;
+        if (dtype == LLMRS_Q6K) {
+            e = cudaMemcpyAsync(ctx->stage_dev[sb], ctx->stage_host[sb], bytes, cudaMemcpyHostToDevice, ctx->stream);
+            if (e == cudaSuccess) {
+                e = launch_q6k_repack(ctx->stage_dev[sb], p + row * q6k_row_stride(K), K, (int)rows, ctx->stream);
+                ctx->launches++;
+            }
+        } else {
+            e = cudaMemcpyAsync(p + row * row_bytes, ctx->stage_host[sb], bytes, cudaMemcpyHostToDevice, ctx->stream);
+        }
+        if (e == cudaSuccess) e = cudaEventRecord(ctx->stage_done[sb], ctx->stream);
+    }
+    const cudaError_t e2 = cudaStreamSynchronize(ctx->stream);    // also on failure: nothing may still read the pieces
+    if (e == cudaSuccess) e = e2;
+    if (!io_ok || e != cudaSuccess) {
+        cudaFree(p);
+        if (!io_ok) return ctx->fail(LLMRS_ERR_IO, "IO error: reading tensor %s", name);
+        return ctx->cuda_fail(e, "upload_gguf_tensor: copy");
+    }
+    *out = llmrs_buf{p, dev_bytes, dtype, d0, d1, dtype == LLMRS_Q6K ? (uint32_t)LLMRS_LAYOUT_Q6K_SLICES : (uint32_t)LLMRS_LAYOUT_RAW,
+                     1u, (uint32_t)ctx->device};
     return LLMRS_OK;
 }
 

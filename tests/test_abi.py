@@ -12,7 +12,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def declared_symbols():
     text = open(os.path.join(ROOT, "include", "llmrs_cuda.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(llmrs_cuda_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(llmrs_(?:cuda|gguf)_\w+)\s*\(", text)))
 
 
 def test_header_and_binding_agree():
