@@ -57,6 +57,8 @@ struct llmrs_ctx {
     uint8_t *stage_host[2] = {nullptr, nullptr};
     uint8_t *stage_dev[2] = {nullptr, nullptr};
     cudaEvent_t stage_done[2] = {nullptr, nullptr};
+    size_t upload_piece = 32u << 20;  // LLMRS_UPLOAD_PIECE_MB (1..1024)
+    int upload_readers = 8;           // LLMRS_UPLOAD_READERS (1..64)
     size_t tokens_cap = 0;
     void *split_ws = nullptr;        // workspace of the tensor-core path's split of the last wave (zero between launches)
     uint32_t *dev_error = nullptr;   // device word: first KernelError reported by a kernel; next word: CTA counter
@@ -211,6 +213,14 @@ int llmrs_cuda_create(int device, void *stream, llmrs_ctx **out) {
     }
     if (const char *env = getenv("LLMRS_NO_PDL")) ctx->pdl = atoi(env) == 0;
     if (const char *env = getenv("LLMRS_TC_TWO_TERM")) ctx->two_term = atoi(env) != 0;
+    if (const char *env = getenv("LLMRS_UPLOAD_PIECE_MB")) {
+        const int v = atoi(env);
+        if (v >= 1 && v <= 1024) ctx->upload_piece = (size_t)v << 20;
+    }
+    if (const char *env = getenv("LLMRS_UPLOAD_READERS")) {
+        const int v = atoi(env);
+        if (v >= 1 && v <= 64) ctx->upload_readers = v;
+    }
     if (const char *env = getenv("LLMRS_GEMM_SPLIT")) ctx->gemm_split = atoi(env) ? 1 : 0;
     e = cudaEventCreate(&ctx->ev_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_end);
@@ -345,11 +355,9 @@ int llmrs_cuda_upload_tensor(llmrs_ctx *ctx, uint32_t dtype, const uint64_t *sha
     return LLMRS_OK;
 }
 
-// Piece size of a streamed upload: large enough that eight readers each get the 4 MiB requests the
-// reference issues (src/gguf/mod.rs:311-312) and that a copy runs at the link's rate, small enough that
-// two pinned pieces cost little host memory.
-static constexpr size_t UPLOAD_PIECE_BYTES = 32u << 20;
-static constexpr int UPLOAD_READERS = 8;
+// Piece size of a streamed upload (default 32 MiB): large enough that eight readers each get the 4 MiB
+// requests the reference issues (src/gguf/mod.rs:311-312) and that a copy runs at the link's rate, small
+// enough that two pinned pieces cost little host memory.
 
 int llmrs_cuda_upload_gguf_tensor(llmrs_ctx *ctx, const llmrs_gguf *gf, const char *name, llmrs_buf *out) {
     if (!ctx) return LLMRS_ERR_ARG;
@@ -373,9 +381,9 @@ int llmrs_cuda_upload_gguf_tensor(llmrs_ctx *ctx, const llmrs_gguf *gf, const ch
     DeviceGuard guard(ctx->device);
     cudaError_t e = cudaSuccess;
     for (int i = 0; i < 2 && e == cudaSuccess; i++) {
-        if (!ctx->stage_host[i]) e = cudaHostAlloc((void **)&ctx->stage_host[i], UPLOAD_PIECE_BYTES, cudaHostAllocDefault);
+        if (!ctx->stage_host[i]) e = cudaHostAlloc((void **)&ctx->stage_host[i], ctx->upload_piece, cudaHostAllocDefault);
         if (e == cudaSuccess && !ctx->stage_done[i]) e = cudaEventCreateWithFlags(&ctx->stage_done[i], cudaEventDisableTiming);
-        if (e == cudaSuccess && dtype == LLMRS_Q6K && !ctx->stage_dev[i]) e = cudaMalloc((void **)&ctx->stage_dev[i], UPLOAD_PIECE_BYTES);
+        if (e == cudaSuccess && dtype == LLMRS_Q6K && !ctx->stage_dev[i]) e = cudaMalloc((void **)&ctx->stage_dev[i], ctx->upload_piece);
     }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "upload_gguf_tensor: staging buffers");
     const int K = (int)d0, N = (int)(d1 ? d1 : 1);
@@ -385,11 +393,11 @@ int llmrs_cuda_upload_gguf_tensor(llmrs_ctx *ctx, const llmrs_gguf *gf, const ch
     if (e != cudaSuccess) return ctx->cuda_fail(e, "upload_gguf_tensor: cudaMalloc");
     // pieces of whole rows, so that the Q6_K re-layout can run piece by piece
     const size_t row_bytes = want / (size_t)N;
-    if (row_bytes > UPLOAD_PIECE_BYTES) {
+    if (row_bytes > ctx->upload_piece) {
         cudaFree(p);
         return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s: one row is %zu bytes, more than a staging piece", name, row_bytes);
     }
-    const size_t rows_per_piece = UPLOAD_PIECE_BYTES / row_bytes;
+    const size_t rows_per_piece = ctx->upload_piece / row_bytes;
     const uint64_t file_pos = g->data_offset + t->offset;
     bool io_ok = true;
     int piece = 0;
@@ -398,7 +406,7 @@ int llmrs_cuda_upload_gguf_tensor(llmrs_ctx *ctx, const llmrs_gguf *gf, const ch
         const size_t rows = std::min(rows_per_piece, (size_t)N - row), bytes = rows * row_bytes;
         if (piece >= 2) e = cudaEventSynchronize(ctx->stage_done[sb]);      // the copy out of this piece, two pieces ago
         if (e != cudaSuccess) break;
-        io_ok = llmrs::gguf_pread_parallel(g->fd, ctx->stage_host[sb], file_pos + row * row_bytes, bytes, UPLOAD_READERS);
+        io_ok = llmrs::gguf_pread_parallel(g->fd, ctx->stage_host[sb], file_pos + row * row_bytes, bytes, ctx->upload_readers);
         if (!io_ok) break;
         if (dtype == LLMRS_Q6K) {
             e = cudaMemcpyAsync(ctx->stage_dev[sb], ctx->stage_host[sb], bytes, cudaMemcpyHostToDevice, ctx->stream);
