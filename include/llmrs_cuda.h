@@ -364,6 +364,13 @@ int llmrs_gguf_get_array_str(const llmrs_gguf *g, const char *key, uint64_t inde
  * complete in device memory. */
 int llmrs_cuda_upload_gguf_tensor(llmrs_ctx *ctx, const llmrs_gguf *g, const char *name, llmrs_buf *out);
 
+/* The same for rows [first_row, first_row + n_rows) of a 2-D tensor's outer dimension (output features of
+ * a weight, token rows of an embedding table): what one rank of an N-sharded matmul holds.  Only that
+ * slice is read from the file.  The buffer's dim1 is n_rows.  No counterpart in the reference, which runs
+ * on one GPU. */
+int llmrs_cuda_upload_gguf_tensor_rows(llmrs_ctx *ctx, const llmrs_gguf *g, const char *name, uint64_t first_row,
+                                       uint64_t n_rows, llmrs_buf *out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -120,6 +120,7 @@ ABI = {
     "llmrs_cuda_launch_count": (C.c_int, [_VP, _U64P]),
     "llmrs_cuda_last_error": (C.c_char_p, [_VP]),
     "llmrs_cuda_upload_gguf_tensor": (C.c_int, [_VP, _VP, C.c_char_p, _BUFP]),
+    "llmrs_cuda_upload_gguf_tensor_rows": (C.c_int, [_VP, _VP, C.c_char_p, C.c_uint64, C.c_uint64, _BUFP]),
     "llmrs_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(_VP)]),
     "llmrs_gguf_close": (None, [_VP]),
     "llmrs_gguf_last_error": (C.c_char_p, []),

@@ -360,6 +360,11 @@ int llmrs_cuda_upload_tensor(llmrs_ctx *ctx, uint32_t dtype, const uint64_t *sha
 // enough that two pinned pieces cost little host memory.
 
 int llmrs_cuda_upload_gguf_tensor(llmrs_ctx *ctx, const llmrs_gguf *gf, const char *name, llmrs_buf *out) {
+    return llmrs_cuda_upload_gguf_tensor_rows(ctx, gf, name, 0, UINT64_MAX, out);
+}
+
+int llmrs_cuda_upload_gguf_tensor_rows(llmrs_ctx *ctx, const llmrs_gguf *gf, const char *name, uint64_t first_row,
+                                       uint64_t n_rows, llmrs_buf *out) {
     if (!ctx) return LLMRS_ERR_ARG;
     if (!gf || !name || !out) return ctx->fail(LLMRS_ERR_ARG, "upload_gguf_tensor: null pointer");
     const llmrs::GgufFile *g = reinterpret_cast<const llmrs::GgufFile *>(gf);
@@ -374,10 +379,20 @@ int llmrs_cuda_upload_gguf_tensor(llmrs_ctx *ctx, const llmrs_gguf *gf, const ch
     const bool quant = dtype == LLMRS_Q4K || dtype == LLMRS_Q6K;
     if (quant && d0 % QK_K)
         return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s: in_features %u is not a multiple of 256", name, d0);
-    size_t want = 0;
-    if (!storage_size(dtype, (uint64_t)d0 * (d1 ? d1 : 1), &want))
+    size_t whole = 0;
+    if (!storage_size(dtype, (uint64_t)d0 * (d1 ? d1 : 1), &whole))
         return ctx->fail(LLMRS_ERR_DTYPE, "upload_gguf_tensor: %s: dtype %u is not supported (F32, BF16, I32, Q4_K, Q6_K)", name, dtype);
-    if (want != t->nbytes) return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s: directory and shape disagree on the size", name);
+    if (whole != t->nbytes) return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s: directory and shape disagree on the size", name);
+    // a slice of the rows: rows [first_row, first_row + n_rows) of the outer dimension
+    const uint64_t all_rows = d1 ? d1 : 1;
+    if (n_rows == UINT64_MAX && first_row == 0) n_rows = all_rows;
+    if (n_rows == 0 || first_row >= all_rows || n_rows > all_rows - first_row)
+        return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s: rows [%llu, +%llu) of %llu", name, (unsigned long long)first_row,
+                         (unsigned long long)n_rows, (unsigned long long)all_rows);
+    if (n_rows != all_rows && !d1) return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s is 1-D: it has no rows to slice", name);
+    const size_t src_row_bytes = whole / (size_t)all_rows;
+    const size_t want = src_row_bytes * (size_t)n_rows;
+    if (d1) d1 = (uint32_t)n_rows;
     DeviceGuard guard(ctx->device);
     cudaError_t e = cudaSuccess;
     for (int i = 0; i < 2 && e == cudaSuccess; i++) {
@@ -398,7 +413,7 @@ int llmrs_cuda_upload_gguf_tensor(llmrs_ctx *ctx, const llmrs_gguf *gf, const ch
         return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s: one row is %zu bytes, more than a staging piece", name, row_bytes);
     }
     const size_t rows_per_piece = ctx->upload_piece / row_bytes;
-    const uint64_t file_pos = g->data_offset + t->offset;
+    const uint64_t file_pos = g->data_offset + t->offset + first_row * src_row_bytes;
     bool io_ok = true;
     int piece = 0;
     for (size_t row = 0; row < (size_t)N && e == cudaSuccess && io_ok; row += rows_per_piece, piece++) {

@@ -293,6 +293,15 @@ attention_kernel(const void *q, const void *k_pool, const void *v_pool, void *ou
 // maximum, sum) triples are merged by attention_merge_kernel.
 constexpr int AT2_TILE = 64;
 constexpr int AT2_THREADS = 128;
+
+// 16 bytes global -> shared without a register in between (both addresses 16-byte aligned).
+__device__ __forceinline__ void async_copy16(void *smem_dst, const void *gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
+                 : "memory");
+}
+__device__ __forceinline__ void async_copy_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
 template <int HD, int GROUP>
 __global__ void __launch_bounds__(AT2_THREADS)
 attention_gqa_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k_pool,
@@ -333,19 +342,23 @@ attention_gqa_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict_
     for (int t0 = t_begin; t0 < t_end; t0 += AT2_TILE) {
         const int tile_len = min(AT2_TILE, t_end - t0);
         // ---- keys and values of the tile -> shared memory ----
+        // Asynchronous 16-byte copies, all of a thread's chunks in flight at once: with loads through
+        // registers the loop ran one memory round trip per iteration, eight in a row per tile.
         for (int c = tid; c < AT2_TILE * CH; c += AT2_THREADS) {
             const int j = c / CH, ch = c % CH;
-            uint4 kk = make_uint4(0, 0, 0, 0), vv = kk;
+            uint16_t *kd = k_s + j * KROW + 8 * ch, *vd = v_s + j * HD + 8 * ch;
             if (j < tile_len) {
                 const int t = t0 + j;
                 const uint32_t page = block_table[(size_t)req * max_blocks_per_seq + t / block_size];
                 const size_t row = ((size_t)page * block_size + (size_t)(t % block_size)) * kv_dim + kv_off;
-                kk = __ldg(reinterpret_cast<const uint4 *>(k_pool + row) + ch);
-                vv = __ldg(reinterpret_cast<const uint4 *>(v_pool + row) + ch);
+                async_copy16(kd, k_pool + row + 8 * ch);
+                async_copy16(vd, v_pool + row + 8 * ch);
+            } else {
+                *reinterpret_cast<uint4 *>(kd) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4 *>(vd) = make_uint4(0, 0, 0, 0);
             }
-            *reinterpret_cast<uint4 *>(k_s + j * KROW + 8 * ch) = kk;
-            *reinterpret_cast<uint4 *>(v_s + j * HD + 8 * ch) = vv;
         }
+        async_copy_wait_all();
         __syncthreads();
         // ---- scores: thread (position j, half of the heads) ----
         {
@@ -403,10 +416,22 @@ attention_gqa_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict_
         for (int d = tid; d < HD; d += AT2_THREADS) {
 #pragma unroll
             for (int h = 0; h < GROUP; h++) acc[h] *= r_s[h];
+#pragma unroll 4
             for (int j = 0; j < tile_len; j++) {
                 const float v = bf16_bits_to_f32(v_s[j * HD + d]);
+                float pj[GROUP];                         // the position's weights for all heads: one or two 16-byte reads
+                if constexpr (GROUP % 4 == 0) {
 #pragma unroll
-                for (int h = 0; h < GROUP; h++) acc[h] = fmaf(p_s[j * GROUP + h], v, acc[h]);
+                    for (int h4 = 0; h4 < GROUP / 4; h4++) {
+                        const float4 t = *reinterpret_cast<const float4 *>(p_s + j * GROUP + 4 * h4);
+                        pj[4 * h4] = t.x; pj[4 * h4 + 1] = t.y; pj[4 * h4 + 2] = t.z; pj[4 * h4 + 3] = t.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int h = 0; h < GROUP; h++) pj[h] = p_s[j * GROUP + h];
+                }
+#pragma unroll
+                for (int h = 0; h < GROUP; h++) acc[h] = fmaf(pj[h], v, acc[h]);
             }
         }
         __syncthreads();
@@ -428,21 +453,42 @@ attention_gqa_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict_
 }
 
 // out = sum_s acc_s e^(m_s - m) / sum_s l_s e^(m_s - m): one CTA of HD threads per (query token, head).
+// The ranges' maxima and sums are fetched by one thread each and combined with shuffles, and the
+// accumulators are read eight ranges at a time: two memory round trips, where a loop over the ranges
+// that used each value at once made one round trip per range (8 of the 13 us of a decode call).
 __global__ void attention_merge_kernel(const float *__restrict__ partial, uint16_t *__restrict__ out, int hd, int splits) {
     pdl_prologue();
+    __shared__ float w_s[32];
+    __shared__ float l_total;
     const size_t th = blockIdx.x;                        // token * n_heads + head
     const float *pr = partial + th * splits * (hd + 2);
-    float m = -INFINITY;
-    for (int s = 0; s < splits; s++) m = fmaxf(m, pr[s * (hd + 2) + hd]);
-    float l = 0.0f, a = 0.0f;
     const int d = threadIdx.x;
-    for (int s = 0; s < splits; s++) {
-        const float ms = pr[s * (hd + 2) + hd];
+    if (d < 32) {                                        // splits <= 32
+        const float ms = d < splits ? pr[d * (hd + 2) + hd] : -INFINITY;
+        const float ls = d < splits ? pr[d * (hd + 2) + hd + 1] : 0.0f;
+        float m = ms;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         const float w = ms == -INFINITY ? 0.0f : __expf(ms - m);
-        l = fmaf(pr[s * (hd + 2) + hd + 1], w, l);
-        a = fmaf(pr[s * (hd + 2) + d], w, a);
+        float l = ls * w;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        w_s[d] = w;
+        if (d == 0) l_total = l;
     }
-    out[th * hd + d] = __bfloat16_as_ushort(__float2bfloat16_rn(a / l));
+    float a = 0.0f;
+    int s = 0;
+    for (; s + 8 <= splits; s += 8) {                    // the eight loads go out before the first is used
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = pr[(s + i) * (hd + 2) + d];
+        if (s == 0) __syncthreads();                     // w_s is ready; the loads above did not need it
+#pragma unroll
+        for (int i = 0; i < 8; i++) a = fmaf(v[i], w_s[s + i], a);
+    }
+    if (s == 0) __syncthreads();
+    for (; s < splits; s++) a = fmaf(pr[s * (hd + 2) + d], w_s[s], a);
+    out[th * hd + d] = __bfloat16_as_ushort(__float2bfloat16_rn(a / l_total));
 }
 
 }  // namespace

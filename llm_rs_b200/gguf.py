@@ -177,20 +177,27 @@ class Loader:
         self.bytes = 0
         self.start = time.perf_counter()
 
-    def opt(self, name: str) -> Optional[CudaBuffer]:
-        """src/arch/mod.rs:52-57: None when the file has no such tensor."""
+    def opt(self, name: str, rows: Optional[Sequence[int]] = None) -> Optional[CudaBuffer]:
+        """src/arch/mod.rs:52-57: None when the file has no such tensor.  `rows=(first, end)` uploads only
+        that slice of the outer dimension (one rank's part of an N-sharded weight, see shard.row_range)."""
         raw = _Buf()
         be = self.backend
-        rc = be._lib.llmrs_cuda_upload_gguf_tensor(be._ctx, self.gguf._h, name.encode(), C.byref(raw))
+        if rows is None:
+            rc = be._lib.llmrs_cuda_upload_gguf_tensor(be._ctx, self.gguf._h, name.encode(), C.byref(raw))
+        else:
+            rc = be._lib.llmrs_cuda_upload_gguf_tensor_rows(be._ctx, self.gguf._h, name.encode(), int(rows[0]),
+                                                            int(rows[1]) - int(rows[0]), C.byref(raw))
         if rc == -9:
             return None
         be._check(rc)
-        self.bytes += self.gguf.tensor_info(name).nbytes
+        info = self.gguf.tensor_info(name)
+        outer = int(info.shape[1]) if len(info.shape) > 1 else 1
+        self.bytes += info.nbytes if rows is None else info.nbytes // outer * (int(rows[1]) - int(rows[0]))
         return CudaBuffer(be, raw)
 
-    def req(self, name: str) -> CudaBuffer:
+    def req(self, name: str, rows: Optional[Sequence[int]] = None) -> CudaBuffer:
         """src/arch/mod.rs:59-61 (a panic there)."""
-        buf = self.opt(name)
+        buf = self.opt(name, rows)
         if buf is None:
             raise KeyError(f"missing tensor: {name}")
         return buf

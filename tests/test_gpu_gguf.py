@@ -78,3 +78,33 @@ def test_streamed_upload_equals_upload_tensor(backend, G, tmp_path, dt, K, N):
         want = O.dequant(dt, np.ascontiguousarray(w).reshape(N, -1)[rows].reshape(-1), K, len(rows))
         assert np.array_equal(da[rows].view(np.uint32), want.view(np.uint32))
         assert ld.bytes == w.nbytes
+
+
+@pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
+def test_row_slices_for_sharded_weights(backend, G, tmp_path, dt):
+    """Each rank of an N-sharded matmul uploads its rows only (shard.row_range): the slices dequantise to the
+    rows of the whole tensor, in every split, and bad ranges are refused before anything is read."""
+    from llm_rs_b200 import BackendError
+    from llm_rs_b200.shard import row_range
+    K, N = 768, 1008
+    w = synth.weight(dt, K, N, tid=88)
+    path = str(tmp_path / "shard.gguf")
+    with open(path, "wb") as f:
+        f.write(OG.build([], [("w", [K, N], dt, np.ascontiguousarray(w).tobytes()), ("v", [K], 0, bytes(4 * K))]))
+    want = O.dequant(dt, w, K, N)
+    with G.GgufFile(path) as g:
+        ld = G.Loader(g, backend)
+        for world in (2, 3, 8):
+            for rank in range(world):
+                a, b = row_range(N, rank, world)
+                part = ld.req("w", rows=(a, b))
+                assert (part.dim0, part.dim1) == (K, b - a)
+                assert np.array_equal(backend.dequantize(part).view(np.uint32), want[a:b].view(np.uint32)), (world, rank)
+        for bad in ((0, 0), (5, 4), (1007, 1009), (1008, 1009)):
+            with pytest.raises(BackendError) as e:
+                ld.req("w", rows=bad)
+            assert e.value.code == -2
+        assert ld.req("v", rows=(0, 1)).dim1 == 0          # a 1-D tensor is one row: only the whole of it
+        with pytest.raises(BackendError):
+            ld.req("v", rows=(0, 2))
+        assert ld.opt("nope", rows=(0, 1)) is None
