@@ -194,6 +194,16 @@ int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, con
 int llmrs_cuda_matmul_add(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input,
                           const llmrs_buf *residual);
 
+/* rms_norm followed by the three projections of one input, src/arch/llama.rs:152-155, as one call:
+ * out_q = matmul(wq, xn), out_k = matmul(wk, xn), out_v = matmul(wv, xn) with xn = rms_norm(input).
+ * Up to LLMRS_GEMV_MAX_M tokens the weights that share a format run in ONE launch of the decode kernel
+ * (a Q4_K_M file keeps wq, wk in Q4_K and wv in Q4_K or Q6_K: one or two launches instead of three, each
+ * normalising the activations as it stages them); otherwise the three llmrs_cuda_rms_norm_matmul calls.
+ * Same results as those calls. */
+int llmrs_cuda_rms_norm_matmul_qkv(llmrs_ctx *ctx, llmrs_buf *out_q, llmrs_buf *out_k, llmrs_buf *out_v,
+                                   const llmrs_buf *wq, const llmrs_buf *wk, const llmrs_buf *wv,
+                                   const llmrs_buf *input, const llmrs_buf *norm_weight, float eps);
+
 /* rms_norm followed by matmul (src/arch/llama.rs:152-155), and rms_norm followed by the feed-forward
  * front (llama.rs:164-168), as one call each: out = matmul(weight, rms_norm(input, norm_weight, eps)).
  * Up to LLMRS_GEMV_MAX_M tokens the decode kernel normalises the activations while it stages them

@@ -105,6 +105,7 @@ ABI = {
     "llmrs_cuda_attention": (C.c_int, [_VP] + [_BUFP] * 7 + [C.c_uint32] * 5),
     "llmrs_cuda_rms_norm_matmul": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, _BUFP, C.c_float]),
     "llmrs_cuda_rms_norm_matmul_gate_up": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, _BUFP, _BUFP, C.c_float]),
+    "llmrs_cuda_rms_norm_matmul_qkv": (C.c_int, [_VP] + [_BUFP] * 8 + [C.c_float]),
     "llmrs_cuda_matmul_add": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_matmul_gate_up": (C.c_int, [_VP, _BUFP, _BUFP, _BUFP, _BUFP]),
     "llmrs_cuda_embed": (C.c_int, [_VP, _BUFP, _BUFP, C.POINTER(C.c_uint32), C.c_uint32]),
@@ -376,6 +377,13 @@ class CudaBackend:
         self._check(self._lib.llmrs_cuda_rms_norm_matmul_gate_up(self._ctx, C.byref(out._raw), C.byref(w_gate._raw),
                                                                  C.byref(w_up._raw), C.byref(input._raw),
                                                                  C.byref(norm_weight._raw), float(eps)))
+
+    def rms_norm_matmul_qkv(self, out_q: CudaBuffer, out_k: CudaBuffer, out_v: CudaBuffer, wq: CudaBuffer, wk: CudaBuffer,
+                            wv: CudaBuffer, input: CudaBuffer, norm_weight: CudaBuffer, eps: float) -> None:
+        """rms_norm + the q, k and v projections (src/arch/llama.rs:152-155) as one call."""
+        self._check(self._lib.llmrs_cuda_rms_norm_matmul_qkv(
+            self._ctx, C.byref(out_q._raw), C.byref(out_k._raw), C.byref(out_v._raw), C.byref(wq._raw), C.byref(wk._raw),
+            C.byref(wv._raw), C.byref(input._raw), C.byref(norm_weight._raw), float(eps)))
 
     def matmul_add(self, out: CudaBuffer, weight: CudaBuffer, input: CudaBuffer, residual: CudaBuffer) -> None:
         """out = residual + matmul(weight, input): matmul followed by add (src/arch/llama.rs:162-163) as one call."""

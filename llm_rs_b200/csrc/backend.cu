@@ -830,6 +830,61 @@ int llmrs_cuda_rms_norm_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *
                      [&](const llmrs_buf *x) { return llmrs_cuda_matmul(ctx, out, weight, x); });
 }
 
+int llmrs_cuda_rms_norm_matmul_qkv(llmrs_ctx *ctx, llmrs_buf *out_q, llmrs_buf *out_k, llmrs_buf *out_v,
+                                   const llmrs_buf *wq, const llmrs_buf *wk, const llmrs_buf *wv, const llmrs_buf *input,
+                                   const llmrs_buf *norm_weight, float eps) {
+    if (!ctx) return LLMRS_ERR_ARG;
+    llmrs_buf *outs[3] = {out_q, out_k, out_v};
+    const llmrs_buf *ws[3] = {wq, wk, wv};
+    for (int i = 0; i < 3; i++)
+        if (!outs[i] || !ws[i] || !outs[i]->dptr || !ws[i]->dptr) return ctx->fail(LLMRS_ERR_ARG, "rms_norm_matmul_qkv: null buffer");
+    if (!input || !input->dptr || !norm_weight || !norm_weight->dptr) return ctx->fail(LLMRS_ERR_ARG, "rms_norm_matmul_qkv: null buffer");
+    const uint32_t K = input->dim0, M = input->dim1 ? input->dim1 : 1;
+    // One launch serves weights of one format whose call the decode kernel would take in one pass; anything
+    // else (more tokens, odd shapes, an argument error to report) goes through the single calls.
+    bool one_pass = (int)M <= ctx->gemv_max_m && M <= 4 && dense_elem_bytes(input->dtype) && norm_weight->dtype == LLMRS_F32 &&
+                    norm_weight->dim0 == K && K % QK_K == 0 && K <= gemv_max_k() && input->device == (uint32_t)ctx->device;
+    for (int i = 0; i < 3 && one_pass; i++) {
+        const llmrs_buf *w = ws[i], *o = outs[i];
+        const uint32_t want_layout = w->dtype == LLMRS_Q6K ? LLMRS_LAYOUT_Q6K_SLICES : LLMRS_LAYOUT_RAW;
+        const uint32_t n = w->dim1 ? w->dim1 : 1;
+        one_pass = (w->dtype == LLMRS_Q4K || w->dtype == LLMRS_Q6K) && w->layout == want_layout && w->dim0 == K &&
+                   (int)M <= gemv_single_launch_max_tokens((int)w->dtype, (int)K) && o->dtype == outs[0]->dtype &&
+                   dense_elem_bytes(o->dtype) && o->dim0 == n && (o->dim1 ? o->dim1 : 1) == M &&
+                   w->device == (uint32_t)ctx->device && o->device == (uint32_t)ctx->device;
+    }
+    if (!one_pass) {
+        int rc = LLMRS_OK;
+        for (int i = 0; i < 3 && rc == LLMRS_OK; i++) rc = llmrs_cuda_rms_norm_matmul(ctx, outs[i], ws[i], input, norm_weight, eps);
+        return rc;
+    }
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = ctx->begin_work();
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "rms_norm_matmul_qkv: event");
+    for (uint32_t dt : {(uint32_t)LLMRS_Q4K, (uint32_t)LLMRS_Q6K}) {
+        const uint8_t *gw[3];
+        void *go[3];
+        int gn[3], n = 0;
+        for (int i = 0; i < 3; i++)
+            if (ws[i]->dtype == dt) {
+                gw[n] = (const uint8_t *)ws[i]->dptr;
+                go[n] = outs[i]->dptr;
+                gn[n++] = (int)(ws[i]->dim1 ? ws[i]->dim1 : 1);
+            }
+        if (n == 0) continue;
+        if (n == 1)
+            e = launch_gemv((int)dt, gw[0], input->dptr, (int)input->dtype, go[0], (int)outs[0]->dtype, (int)K, gn[0], (int)M,
+                            ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream, &ctx->launches, nullptr, DT_F32,
+                            (const float *)norm_weight->dptr, eps);
+        else
+            e = launch_gemv_multi((int)dt, n, gw, gn, go, input->dptr, (int)input->dtype, (int)outs[0]->dtype, (int)K, (int)M,
+                                  ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream, &ctx->launches,
+                                  (const float *)norm_weight->dptr, eps);
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "rms_norm_matmul_qkv: launch");
+    }
+    return LLMRS_OK;
+}
+
 int llmrs_cuda_rms_norm_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w_gate, const llmrs_buf *w_up,
                                        const llmrs_buf *input, const llmrs_buf *norm_weight, float eps) {
     if (!ctx) return LLMRS_ERR_ARG;

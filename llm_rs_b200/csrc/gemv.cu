@@ -116,6 +116,13 @@ struct GemvParams {
     // (src/arch/llama.rs:152-153,164-165: rms_norm followed by matmul; shaders/ops.metal:970-1003).
     const float *NormW;
     float norm_eps;
+    // Several weights of one format and K behind one input (n_segs >= 2: the q, k and v projections,
+    // src/arch/llama.rs:153-155): rows [seg_first[i], seg_first[i + 1]) of the launch are the rows of
+    // seg_W[i] and go to seg_out[i], a [tokens, rows of segment i] buffer.  N is the sum of the rows.
+    int n_segs;
+    int seg_first[4];
+    const uint8_t *seg_W[3];
+    void *seg_out[3];
     const uint8_t *W;
     const void *X;
     void *Out;
@@ -265,49 +272,28 @@ __device__ __forceinline__ float2 quantise_group(const float (&v)[GROUP], uint8_
     return make_float2(inv, (float)sum * inv);
 }
 
-// Sum of squares of every token row over the whole CTA (tokens <= 4): each thread adds up the groups it
-// will stage, warps reduce by shuffle, `red` ([warps][4] floats of shared memory) carries the rest.
+// RMS norm folded into the matmul: out = rsqrt(mean(x^2) + eps) * (W . (x * g)).  The row's factor is a
+// scalar, so it is applied to the finished dot products and the staging needs one pass only: a group is
+// loaded once, its squares are added up on the side (norm_squares), it is multiplied by the norm weight
+// and rounded to its block fixed point (whose exponent follows the group's own magnitude).  The sums of
+// squares meet in `red` ([warps][4] floats of shared memory) behind the barrier that ends the staging.
 template <int GROUP>
-__device__ void row_inverse_rms(const GemvParams &p, int tid, int n_threads, float (*red)[4], float (&inv)[4]) {
-    const int K = p.K, groups = K / GROUP;
-    float ss[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int gi = tid; gi < groups * p.m_valid; gi += n_threads) {
-        const int t = gi / groups, g = gi - t * groups;
-        float v[GROUP];
-        load_group<GROUP>(p.X, (size_t)t * K + (size_t)GROUP * g, p.x_bf16, v);
-        float a = 0.0f;
+__device__ __forceinline__ float norm_squares(const float (&v)[GROUP]) {
+    float a = 0.0f;
 #pragma unroll
-        for (int i = 0; i < GROUP; i++) a = fmaf(v[i], v[i], a);
-#pragma unroll
-        for (int tt = 0; tt < 4; tt++) ss[tt] += tt == t ? a : 0.0f;
-    }
-#pragma unroll
-    for (int tt = 0; tt < 4; tt++) {
-#pragma unroll
-        for (int o = 16; o; o >>= 1) ss[tt] += __shfl_xor_sync(0xffffffffu, ss[tt], o);
-    }
-    if ((tid & 31) == 0) {
-#pragma unroll
-        for (int tt = 0; tt < 4; tt++) red[tid >> 5][tt] = ss[tt];
-    }
-    named_barrier_sync(1, n_threads);
-#pragma unroll
-    for (int tt = 0; tt < 4; tt++) {
-        float t = 0.0f;
-        for (int w = 0; w < n_threads / 32; w++) t += red[w][tt];
-        inv[tt] = rsqrtf(t / (float)K + p.norm_eps);
-    }
+    for (int i = 0; i < GROUP; i++) a = fmaf(v[i], v[i], a);
+    return a;
 }
 
 template <int GROUP>
-__device__ __forceinline__ void scale_group(const GemvParams &p, float (&v)[GROUP], int k0, float inv) {
+__device__ __forceinline__ void scale_group(const GemvParams &p, float (&v)[GROUP], int k0) {
 #pragma unroll
     for (int j = 0; j < GROUP / 4; j++) {
         const float4 w = __ldg(reinterpret_cast<const float4 *>(p.NormW + k0) + j);
-        v[4 * j] = v[4 * j] * inv * w.x;
-        v[4 * j + 1] = v[4 * j + 1] * inv * w.y;
-        v[4 * j + 2] = v[4 * j + 2] * inv * w.z;
-        v[4 * j + 3] = v[4 * j + 3] * inv * w.w;
+        v[4 * j] *= w.x;
+        v[4 * j + 1] *= w.y;
+        v[4 * j + 2] *= w.z;
+        v[4 * j + 3] *= w.w;
     }
 }
 
@@ -315,15 +301,19 @@ template <int QT, int PLANES>
 __device__ void stage_activations(uint8_t *xarea, size_t xtok_bytes, const GemvParams &p, int tid, int n_threads,
                                   float (*red)[4]) {
     const int K = p.K;
-    float inv_rms[4] = {1.0f, 1.0f, 1.0f, 1.0f};
-    if (p.NormW) row_inverse_rms<QT == 0 ? 32 : 16>(p, tid, n_threads, red, inv_rms);
+    float ss[4] = {0.0f, 0.0f, 0.0f, 0.0f};              // this thread's share of every token's sum of squares
     if (QT == 0) {
         const int groups = K / 32;                       // group sb = sub-block sb of the row
         for (int gi = tid; gi < groups * p.m_valid; gi += n_threads) {
             const int t = gi / groups, sb = gi - t * groups;
             float v[32];
             load_group<32>(p.X, (size_t)t * K + 32 * (size_t)sb, p.x_bf16, v);
-            if (p.NormW) scale_group<32>(p, v, 32 * sb, t == 0 ? inv_rms[0] : t == 1 ? inv_rms[1] : t == 2 ? inv_rms[2] : inv_rms[3]);
+            if (p.NormW) {
+                const float a = norm_squares<32>(v);
+#pragma unroll
+                for (int tt = 0; tt < 4; tt++) ss[tt] += tt == t ? a : 0.0f;
+                scale_group<32>(p, v, 32 * sb);
+            }
             uint8_t *sl = xarea + (size_t)t * xtok_bytes + (size_t)(sb >> 1) * Fmt<0, PLANES>::XSTRIDE;
             const float2 m = quantise_group<32, PLANES, 0>(v, sl + (sb & 1) * Fmt<0, PLANES>::GROUP_BYTES);
             float *f = reinterpret_cast<float *>(sl + Fmt<0, PLANES>::META);
@@ -338,12 +328,28 @@ __device__ void stage_activations(uint8_t *xarea, size_t xtok_bytes, const GemvP
             const int g = (q >> 1) & 3, slice = ((q >> 3) << 1) | (q & 1);
             float v[16];
             load_group<16>(p.X, (size_t)t * K + 16 * (size_t)q, p.x_bf16, v);
-            if (p.NormW) scale_group<16>(p, v, 16 * q, t == 0 ? inv_rms[0] : t == 1 ? inv_rms[1] : t == 2 ? inv_rms[2] : inv_rms[3]);
+            if (p.NormW) {
+                const float a = norm_squares<16>(v);
+#pragma unroll
+                for (int tt = 0; tt < 4; tt++) ss[tt] += tt == t ? a : 0.0f;
+                scale_group<16>(p, v, 16 * q);
+            }
             uint8_t *sl = xarea + (size_t)t * xtok_bytes + (size_t)slice * Fmt<1, PLANES>::XSTRIDE;
             const float2 m = quantise_group<16, PLANES, 1>(v, sl + g * Fmt<1, PLANES>::GROUP_BYTES);
             float *f = reinterpret_cast<float *>(sl + Fmt<1, PLANES>::META);
             f[g] = m.x;
             f[4 + g] = m.y;
+        }
+    }
+    if (p.NormW) {
+#pragma unroll
+        for (int tt = 0; tt < 4; tt++) {
+#pragma unroll
+            for (int o = 16; o; o >>= 1) ss[tt] += __shfl_xor_sync(0xffffffffu, ss[tt], o);
+        }
+        if ((tid & 31) == 0) {
+#pragma unroll
+            for (int tt = 0; tt < 4; tt++) red[tid >> 5][tt] = ss[tt];
         }
     }
 }
@@ -559,8 +565,13 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                 __syncwarp();
                 if (lane < RT) {
                     const bool pair = R == 2 && p.W2 != nullptr;
-                    const int row = pair ? min(rt * (RT / 2) + (lane >> 1), p.N - 1) : min(rt * RT + lane, p.N - 1);
+                    int row = pair ? min(rt * (RT / 2) + (lane >> 1), p.N - 1) : min(rt * RT + lane, p.N - 1);
                     const uint8_t *src = pair && (lane & 1) ? p.W2 : p.W;
+                    if (p.n_segs) {                      // the weight this row belongs to
+                        const int sg = (row >= p.seg_first[1]) + (row >= p.seg_first[2]);
+                        src = p.seg_W[sg];
+                        row -= p.seg_first[sg];
+                    }
                     bulk_copy_g2s(stages + s * stage_bytes + (size_t)lane * F::CHUNK_MAX,
                                   src + (size_t)row * p.row_stride + (size_t)c * F::CHUNK_MAX, bytes, &full[s]);
                 }
@@ -576,6 +587,17 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
     stage_activations<QT, PLANES>(xarea, xtok_bytes, p, threadIdx.x, NCW * 32, norm_red);
     named_barrier_sync(1, NCW * 32);
     if (threadIdx.x == 0) LLMRS_TRACE(1);
+    float inv_rms[MT];                                   // the tokens' norm factors, applied to the finished sums
+#pragma unroll
+    for (int t = 0; t < MT; t++) {
+        inv_rms[t] = 1.0f;
+        if (p.NormW) {
+            float sq = 0.0f;
+#pragma unroll
+            for (int w = 0; w < NCW; w++) sq += norm_red[w][t];
+            inv_rms[t] = rsqrtf(sq / (float)p.K + p.norm_eps);
+        }
+    }
 
     uint32_t it = 0;
     bool ok = true;
@@ -629,6 +651,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                     g += __shfl_xor_sync(0xffffffffu, g, o);
                     u += __shfl_xor_sync(0xffffffffu, u, o);
                 }
+                g *= inv_rms[t];
+                u *= inv_rms[t];
                 const int out_row = rt * (RT / 2) + warp;
                 if (ok && lane == 0 && out_row < p.N && t < p.m_valid)
                     store_out(p.Out, (size_t)t * p.N + out_row, g / (1.0f + expf(-g)) * u, p.out_bf16);
@@ -642,9 +666,16 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                 float v = total[r][t];
 #pragma unroll
                 for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                v *= inv_rms[t];
                 const int out_row = rt * RT + warp * R + r;
                 if (ok && out_row < p.N && t < p.m_valid) {
-                    if (p.g.world == 0) {
+                    if (p.n_segs) {
+                        if (lane == 0) {
+                            const int sg = (out_row >= p.seg_first[1]) + (out_row >= p.seg_first[2]);
+                            const int n_sg = p.seg_first[sg + 1] - p.seg_first[sg];
+                            store_out(p.seg_out[sg], (size_t)t * n_sg + (out_row - p.seg_first[sg]), v, p.out_bf16);
+                        }
+                    } else if (p.g.world == 0) {
                         if (lane == 0) {
                             const size_t o = (size_t)t * p.N + out_row;
                             if (p.Residual) v += load_x(p.Residual, o, p.res_bf16);
@@ -848,6 +879,45 @@ cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype
     if (wdtype == DT_Q6K) {
         p.row_stride = q6k_row_stride(K);
         return launch_fmt<1>(p, M, xe, oe, sm_count, s, launches);
+    }
+    return cudaErrorInvalidValue;
+}
+
+// Two or three weights of one format and K behind the same (optionally normalised) input, one launch,
+// one token pass: M <= 4 and M <= gemv_single_launch_max_tokens.  out[i] is [M, n_rows[i]].
+cudaError_t launch_gemv_multi(int wdtype, int n, const uint8_t *const *ws, const int *n_rows, void *const *outs,
+                              const void *x, int x_dtype, int out_dtype, int K, int M, int sm_count, bool pdl,
+                              uint32_t *err_word, cudaStream_t s, uint64_t *launches, const float *norm_weight,
+                              float norm_eps) {
+    if (n < 2 || n > 3 || K <= 0 || M <= 0 || M > 4 || M > gemv_single_launch_max_tokens(wdtype, K)) return cudaErrorInvalidValue;
+    GemvParams p{};
+    p.pdl = pdl;
+    p.NormW = norm_weight;
+    p.norm_eps = norm_eps;
+    p.X = x; p.err = err_word; p.K = K;
+    p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;
+    p.n_segs = n;
+    int first = 0;
+    for (int i = 0; i < 3; i++) {
+        p.seg_first[i] = first;
+        if (i < n) {
+            if (n_rows[i] <= 0) return cudaErrorInvalidValue;
+            p.seg_W[i] = ws[i];
+            p.seg_out[i] = outs[i];
+            first += n_rows[i];
+        }
+    }
+    p.seg_first[3] = first;
+    for (int i = n; i < 3; i++) p.seg_first[i] = first;         // absent segments are empty
+    p.N = first;
+    p.W = ws[0]; p.Out = outs[0];
+    if (wdtype == DT_Q4K) {
+        p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
+        return launch_fmt<0>(p, M, 0, 0, sm_count, s, launches);
+    }
+    if (wdtype == DT_Q6K) {
+        p.row_stride = q6k_row_stride(K);
+        return launch_fmt<1>(p, M, 0, 0, sm_count, s, launches);
     }
     return cudaErrorInvalidValue;
 }

@@ -125,6 +125,14 @@ size_t gemv_max_k();
 // in_features (the staged activations of all tokens must fit beside two ring stages).
 int gemv_single_launch_max_tokens(int wdtype, int K);
 
+// Two or three weights of one format and in_features behind the same input in ONE launch of the decode
+// kernel (the q, k and v projections): outs[i] = X . ws[i]^T, [M, n_rows[i]].  M <= 4 and
+// M <= gemv_single_launch_max_tokens; norm_weight as in launch_gemv.
+cudaError_t launch_gemv_multi(int wdtype, int n, const uint8_t *const *ws, const int *n_rows, void *const *outs,
+                              const void *x, int x_dtype, int out_dtype, int K, int M, int sm_count, bool pdl,
+                              uint32_t *err_word, cudaStream_t s, uint64_t *launches, const float *norm_weight,
+                              float norm_eps);
+
 // Prefill matmul on the tensor cores (tcgen05, f16 operands, fp32 accumulate in TMEM); M >= 1.
 // The activations are first converted to per-token-scaled f16 in `scratch`
 // (gemm_scratch_bytes() bytes of device memory owned by the caller).

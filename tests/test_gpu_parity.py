@@ -366,6 +366,41 @@ def test_rms_norm_matmul_gate_up(backend, M):
     assert O.rel_l2(backend.read_to_vec_f32(out).reshape(M, N), silu_mul_truth(O.Q4K, wg, wu, K, N, xn)) <= 2.5e-4
 
 
+@pytest.mark.parametrize("dts", [(O.Q4K, O.Q4K, O.Q4K), (O.Q4K, O.Q4K, O.Q6K), (O.Q6K, O.Q4K, O.Q6K), (O.Q6K, O.Q6K, O.Q6K)])
+@pytest.mark.parametrize("K,Nq,Nkv,M,bf16", [(4096, 4096, 1024, 1, True), (1024, 200, 40, 3, False), (2048, 96, 33, 4, True),
+                                              (512, 64, 64, 6, False)])
+def test_rms_norm_matmul_qkv_equals_the_three_calls(backend, dts, K, Nq, Nkv, M, bf16):
+    """One call for rms_norm + q, k, v projections: bit-identical to three rms_norm_matmul calls (weights of one
+    format share a launch, rows of a tile may straddle two weights), and inside the decode tolerance; six
+    tokens take the unfused route."""
+    ws = [synth.weight(dt, K, n, tid=900 + i) for i, (dt, n) in enumerate(zip(dts, (Nq, Nkv, Nkv)))]
+    wb = [upload_weight(backend, dt, w, K, n) for dt, w, n in zip(dts, ws, (Nq, Nkv, Nkv))]
+    x = synth.activations(M, K, tid=910)
+    g = (1.0 + 0.1 * synth.activations(1, K, tid=911)[0]).astype(np.float32)
+    gb = backend.upload_tensor(TensorView("g", DType.F32, [K], g))
+    xb = upload_x(backend, x, M, K, bf16)
+    odt = DType.BF16 if bf16 else DType.F32
+    shp = lambda n: [n] if M == 1 else [n, M]
+    one = [backend.alloc(shp(n), odt) for n in (Nq, Nkv, Nkv)]
+    three = [backend.alloc(shp(n), odt) for n in (Nq, Nkv, Nkv)]
+    before = backend.launch_count()
+    backend.rms_norm_matmul_qkv(one[0], one[1], one[2], wb[0], wb[1], wb[2], xb, gb, 1e-5)
+    launches = backend.launch_count() - before
+    for o, w in zip(three, wb):
+        backend.rms_norm_matmul(o, w, xb, gb, 1e-5)
+    backend.sync()
+    if M <= 4:
+        assert launches == len(set(dts))                  # one launch per weight format
+    xe = O.bf16_bits_to_f32(synth.bf16_bits(x)).reshape(M, K) if bf16 else x
+    x64 = xe.astype(np.float64)
+    xn = (x64 / np.sqrt((x64 ** 2).mean(axis=1, keepdims=True) + 1e-5) * g).astype(np.float32)
+    for o1, o3, dt, w, n in zip(one, three, dts, ws, (Nq, Nkv, Nkv)):
+        a, b = backend.read_to_vec_f32(o1), backend.read_to_vec_f32(o3)
+        assert np.array_equal(a, b)
+        truth = O.matmul(dt, w, K, n, xn, acc="f64")
+        assert O.rel_l2(a.reshape(M, n), truth) <= GEMV_TOL + (2.0 ** -8 if bf16 else 0.0)
+
+
 def test_matmul_gate_up_bf16_and_errors(backend):
     from llm_rs_b200.backend import BackendError
     K, N = 1024, 64
