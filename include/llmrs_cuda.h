@@ -107,7 +107,12 @@ int llmrs_cuda_free(llmrs_ctx *ctx, llmrs_buf *buf);
 /* Replaces Backend::matmul (src/backend/mod.rs:29-34; metal/mod.rs:496-687):
  * out[s*N + r] = sum_k W[r,k] * in[s*K + k].  Weight dtype Q4_K or Q6_K; input
  * and output each F32 or BF16 (read from the buffers).  Enqueues only: no
- * synchronisation and no allocation, so it may be captured in a CUDA graph. */
+ * synchronisation and no allocation, so it may be captured in a CUDA graph.
+ * Accuracy against the float64 product, as relative L2 error: up to 64 tokens 1e-4 or better (1..4 tokens
+ * the decode kernel, exact integer dot products; 5..64 whichever of that kernel and the two-term
+ * tensor-core kernel is cheaper for the shape); from 65 tokens 2e-3 (one-term tensor-core kernel, f16
+ * operands, measured ~4e-4).  LLMRS_TC_TWO_TERM=0 at context creation extends the one-term kernel down
+ * to 5 tokens; LLMRS_GEMV_MAX_M=m makes "decode kernel up to m tokens, tensor cores above" the rule. */
 int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input);
 
 /* The same product as llmrs_cuda_matmul, computed by the tensor-core kernel for any M, with that
@@ -117,7 +122,8 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
  * they are running: a server that gave the whole GPU to its own memory pool, or a loop that cannot
  * take the device-wide synchronisation a cudaMalloc or cudaFree causes.  This call never allocates
  * or frees device memory.
- *   - Limit: gemm scratch = round_up(2*K*M, 256) + 4*M bytes must fit 8 MiB (for example 1023
+ *   - Limit: gemm scratch = round_up(2*K*R, 256) + 4*M bytes, R = 2*M up to 64 tokens (hi and lo terms of
+ *     the two-term kernel) and M above, must fit 8 MiB (for example 1023
  *     tokens at K=4096, 292 at K=14336); larger shapes fail with LLMRS_ERR_SHAPE and a message
  *     that names both sizes.
  *   - Every GPU that loads the library holds the 8 MiB until the process exits.

@@ -298,7 +298,7 @@ class CudaBackend:
     def matmul_static_scratch(self, out: CudaBuffer, weight: CudaBuffer, input: CudaBuffer) -> None:
         """`matmul` through the tensor-core kernel with its scratch in the 8 MiB device array built
         into the library: for hosts that must not allocate device memory while running.  Raises
-        BackendError (-2) when 2*K*M + 4*M bytes do not fit; calls that may overlap on the GPU race
+        BackendError (-2) when 2*K*M + 4*M bytes (twice the first term up to 64 tokens) do not fit; calls that may overlap on the GPU race
         on the shared array."""
         self._check(self._lib.llmrs_cuda_matmul_static_scratch(self._ctx, C.byref(out._raw), C.byref(weight._raw),
                                                                C.byref(input._raw)))

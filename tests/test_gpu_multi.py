@@ -1,5 +1,5 @@
 """Two-GPU test of the N-sharded decode matmul with the all-gather fused into the kernel.
-Needs two B200s on one node (run with `gpurun --gpus 2`); skipped on a single-GPU box."""
+Needs two B200s on one node; skipped on a single-GPU box."""
 import os
 import sys
 
