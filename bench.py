@@ -644,7 +644,8 @@ def extra_measurements(be_factory, stream, peak_gbs):
         kx = be.upload_tensor(TensorView("k", DType.BF16, [1024], synth.bf16_bits(synth.activations(1, 1024, tid=8))))
         pos = be.upload_u32([4095])
         out["other_ops"]["rope_q4096_k1024_us"] = round(time_call(lambda: be.rope(xa, kx, pos, hd, 500000.0)) * 1e6, 2)
-        for name, n_req, ctx_len, q_per in (("decode_8x4096", 8, 4096, 1), ("prefill_1x512", 1, 512, 512)):
+        for name, n_req, ctx_len, q_per in (("decode_8x4096", 8, 4096, 1), ("prefill_1x512", 1, 512, 512),
+                                             ("prefill_1x2048", 1, 2048, 2048)):
             pages_per = (ctx_len + blk - 1) // blk
             n_slots = n_req * pages_per * blk
             kp = be.upload_tensor(TensorView("k", DType.BF16, [nkv * hd, n_slots],
@@ -661,6 +662,9 @@ def extra_measurements(be_factory, stream, peak_gbs):
             t = time_call(lambda: be.attention(ob, qb, kp, vp, bt, qs, sl, nh, nkv, hd, blk, pages_per), 10)
             kv_bytes = 2 * n_req * ctx_len * nkv * hd * 2
             out["other_ops"][f"attention_{name}"] = {"us": round(t * 1e6, 1), "kv_GBps": round(kv_bytes / t / 1e9, 1)}
+            if q_per > 1:       # causal: query token i of the request sees ctx_len - q_per + i + 1 positions
+                pairs = n_req * (q_per * (ctx_len - q_per) + q_per * (q_per + 1) // 2)
+                out["other_ops"][f"attention_{name}"]["TFLOPs"] = round(4.0 * nh * hd * pairs / t / 1e12, 1)
             for b in (kp, vp, qb, ob, bt, qs, sl):
                 b.free()
         # config 4: the 225 matmuls of one Llama-3-8B decode step (32 x {wq, wk, wv, wo, gate, up: Q4_K;

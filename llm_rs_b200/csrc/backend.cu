@@ -722,6 +722,18 @@ int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, con
                          buf_elems(q), num_req, buf_elems(query_starts), buf_elems(block_table));
     DeviceGuard guard(ctx->device);
     cudaError_t e;
+    if (attention_gqa_supported((int)q->dtype, (int)n_heads, (int)n_kv_heads, (int)head_dim) && total_q >= 2 * num_req) {
+        // requests with several query tokens on average (prefill): the tensor-core kernel, chunks of query tokens
+        e = ctx->begin_work();
+        if (e == cudaSuccess)
+            e = launch_attention_prefill(q->dptr, k_pool->dptr, v_pool->dptr, out->dptr, (const uint32_t *)block_table->dptr,
+                                         (const uint32_t *)query_starts->dptr, (const uint32_t *)seq_lens->dptr, (int)total_q,
+                                         (int)num_req, (int)n_heads, (int)n_kv_heads, (int)head_dim, (int)block_size,
+                                         (int)max_blocks_per_seq, ctx->stream, ctx->pdl);
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "attention");
+        ctx->launches++;
+        return LLMRS_OK;
+    }
     if (attention_gqa_supported((int)q->dtype, (int)n_heads, (int)n_kv_heads, (int)head_dim)) {
         // sequence lengths live on the device: the page table's capacity bounds them for the split count
         const int splits = attention_splits((int)total_q, (int)n_kv_heads, (int)(block_size * max_blocks_per_seq), ctx->sm_count);

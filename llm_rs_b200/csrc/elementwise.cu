@@ -302,6 +302,11 @@ __device__ __forceinline__ void async_copy16(void *smem_dst, const void *gmem_sr
 __device__ __forceinline__ void async_copy_wait_all() {
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
+__device__ __forceinline__ void async_copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most `Pending` of this thread's committed groups are still in flight.
+template <int Pending> __device__ __forceinline__ void async_copy_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(Pending) : "memory");
+}
 template <int HD, int GROUP>
 __global__ void __launch_bounds__(AT2_THREADS)
 attention_gqa_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k_pool,
@@ -491,6 +496,213 @@ __global__ void attention_merge_kernel(const float *__restrict__ partial, uint16
     out[th * hd + d] = __bfloat16_as_ushort(__float2bfloat16_rn(a / l_total));
 }
 
+// ---- prefill attention on the tensor cores -------------------------------------------------------
+// Requests with several query tokens (prefill, chunked prefill): one CTA per (request, 64 / GROUP
+// consecutive query tokens, KV head).  The CTA's 64 rows are (token, head of the group) pairs, 16 per
+// warp, so one key / value tile serves every head of the group and every token of the chunk.  Per tile
+// of 64 positions: S = Q K^T and O += P V run as mma.sync m16n8k16 (bf16 in, fp32 out) with the
+// running maximum and sum of each row in registers (the score fragments of S are the A fragments of
+// P V as they stand).  Keys and values come into shared memory by asynchronous 16-byte copies; rows are
+// 8 elements longer than head_dim so that fragment reads fall on distinct banks.
+constexpr int FA_BN = 64;             // positions per tile
+constexpr int FA_THREADS = 128;       // four warps of 16 rows
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// (lo, hi) -> packed bf16x2, lo in the low half, round to nearest even
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// Four 8x8 b16 matrices from shared memory: lane i gives the address of row i % 8 of matrix i / 8 and
+// receives, of every matrix, elements (row lane / 4, columns 2 (lane % 4), +1); transposed: (rows
+// 2 (lane % 4), +1, column lane / 4).  These are the B fragments of mma.m16n8k16 as they stand.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *row_ptr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(row_ptr)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *row_ptr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(row_ptr)));
+}
+
+template <int HD, int GROUP>
+__global__ void __launch_bounds__(FA_THREADS)
+attention_prefill_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k_pool,
+                         const uint16_t *__restrict__ v_pool, uint16_t *__restrict__ out,
+                         const uint32_t *__restrict__ block_table, const uint32_t *__restrict__ query_starts,
+                         const uint32_t *__restrict__ seq_lens, int n_heads, int n_kv_heads, int block_size,
+                         int max_blocks_per_seq, int num_requests) {
+    pdl_prologue();
+    constexpr int TOK = 64 / GROUP;                      // query tokens per CTA
+    constexpr int STRIDE = HD + 8;                       // elements per shared-memory row
+    constexpr int KS = HD / 16, NT = HD / 8, CH = HD / 8;
+    constexpr int TILE = FA_BN * STRIDE;                 // elements of one key (or value) tile
+    extern __shared__ __align__(16) uint16_t fa_s[];     // [2 buffers][key tile | value tile]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int kvh = blockIdx.y;
+    // which request and which chunk of its query tokens: the grid holds a chunk count that no batch exceeds
+    int req = 0, chunk = blockIdx.x;
+    for (; req < num_requests; req++) {
+        const int cnt = (int)query_starts[req + 1] - (int)query_starts[req];
+        const int chunks = (cnt + TOK - 1) / TOK;
+        if (chunk < chunks) {
+            chunk = chunks - 1 - chunk;                  // late chunks see the most positions: they start first
+            break;
+        }
+        chunk -= chunks;
+    }
+    if (req >= num_requests) return;
+    const int q_begin = (int)query_starts[req], q_count = (int)query_starts[req + 1] - q_begin;
+    const int tok0 = chunk * TOK;
+    const int base_len = (int)seq_lens[req] - q_count;   // positions in front of the request's first query token
+    const int kv_dim = n_kv_heads * HD, kv_off = kvh * HD;
+    // this thread's two rows: r0 = 16 warp + g and r0 + 8; row -> (token tok0 + row / GROUP, head row % GROUP)
+    const int r0 = 16 * warp + g, r1 = r0 + 8;
+    const int tl0 = tok0 + r0 / GROUP, tl1 = tok0 + r1 / GROUP;
+    const bool ok0 = tl0 < q_count, ok1 = tl1 < q_count;
+    const int len0 = ok0 ? base_len + tl0 + 1 : 0, len1 = ok1 ? base_len + tl1 + 1 : 0;    // causal: visible positions
+    const size_t qo0 = ((size_t)(q_begin + tl0) * n_heads + (size_t)kvh * GROUP + r0 % GROUP) * HD;
+    const size_t qo1 = ((size_t)(q_begin + tl1) * n_heads + (size_t)kvh * GROUP + r1 % GROUP) * HD;
+    uint32_t qa[KS][4];                                  // the rows' queries as A fragments
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+        const int c = 16 * ks + 2 * t;
+        qa[ks][0] = ok0 ? *reinterpret_cast<const uint32_t *>(q + qo0 + c) : 0u;
+        qa[ks][1] = ok1 ? *reinterpret_cast<const uint32_t *>(q + qo1 + c) : 0u;
+        qa[ks][2] = ok0 ? *reinterpret_cast<const uint32_t *>(q + qo0 + c + 8) : 0u;
+        qa[ks][3] = ok1 ? *reinterpret_cast<const uint32_t *>(q + qo1 + c + 8) : 0u;
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    const float sc = rsqrtf((float)HD) * 1.4426950408889634f;      // scores in units of log2: exp2f below
+    const int kv_len = base_len + min(tok0 + TOK, q_count);         // what the chunk's last token sees
+
+    // the tile that starts at position p0 -> buffer `buf`, asynchronously (rows past the range: zeros, not
+    // stale bits, since 0 * NaN would poison P V)
+    auto fetch_tile = [&](int p0, int buf) {
+        uint16_t *kb = fa_s + buf * 2 * TILE, *vb = kb + TILE;
+        for (int c = tid; c < FA_BN * CH; c += FA_THREADS) {
+            const int j = c / CH, ch = c % CH;
+            uint16_t *kd = kb + j * STRIDE + 8 * ch, *vd = vb + j * STRIDE + 8 * ch;
+            const int pos = p0 + j;
+            if (pos < kv_len) {
+                const uint32_t page = block_table[(size_t)req * max_blocks_per_seq + pos / block_size];
+                const size_t row = ((size_t)page * block_size + (size_t)(pos % block_size)) * kv_dim + kv_off;
+                async_copy16(kd, k_pool + row + 8 * ch);
+                async_copy16(vd, v_pool + row + 8 * ch);
+            } else {
+                *reinterpret_cast<uint4 *>(kd) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4 *>(vd) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        async_copy_commit();
+    };
+    if (kv_len > 0) fetch_tile(0, 0);
+    int buf = 0;
+    for (int p0 = 0; p0 < kv_len; p0 += FA_BN, buf ^= 1) {
+        const uint16_t *k_s = fa_s + buf * 2 * TILE, *v_s = k_s + TILE;
+        // the other buffer was last read before the barrier that closed the previous iteration
+        if (p0 + FA_BN < kv_len) {
+            fetch_tile(p0 + FA_BN, buf ^ 1);             // travels while this tile is worked on
+            async_copy_wait<1>();
+        } else {
+            async_copy_wait<0>();
+        }
+        __syncthreads();
+        // ---- S = Q K^T: 16 rows x 64 positions per warp ----
+        float s[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+        const int lm = lane >> 3, lr = lane & 7;          // ldmatrix: this lane addresses row lr of matrix lm
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++)
+#pragma unroll
+            for (int nt = 0; nt < 8; nt += 2) {
+                // B fragments (k = dimension, n = position) of position tiles nt and nt + 1:
+                // matrices (nt, dims 0-7), (nt, dims 8-15), (nt + 1, dims 0-7), (nt + 1, dims 8-15) of the step
+                uint32_t b[4];
+                ldmatrix_x4(b, k_s + (8 * (nt + (lm >> 1)) + lr) * STRIDE + 16 * ks + 8 * (lm & 1));
+                mma_bf16(s[nt], qa[ks], b[0], b[1]);
+                mma_bf16(s[nt + 1], qa[ks], b[2], b[3]);
+            }
+        // ---- scale, causal mask, running maximum ----
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int pos = p0 + 8 * nt + 2 * t + e;
+                s[nt][e] = pos < len0 ? s[nt][e] * sc : -INFINITY;
+                s[nt][2 + e] = pos < len1 ? s[nt][2 + e] * sc : -INFINITY;
+                mx0 = fmaxf(mx0, s[nt][e]);
+                mx1 = fmaxf(mx1, s[nt][2 + e]);
+            }
+#pragma unroll
+        for (int sh = 1; sh <= 2; sh <<= 1) {            // the four lanes of a quad hold one row
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+        }
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float u0 = mn0 == -INFINITY ? 0.0f : mn0, u1 = mn1 == -INFINITY ? 0.0f : mn1;   // rows that see nothing yet
+        const float f0 = exp2f(m0 - u0), f1 = exp2f(m1 - u1);
+        m0 = mn0;
+        m1 = mn1;
+        float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                s[nt][e] = exp2f(s[nt][e] - u0);
+                s[nt][2 + e] = exp2f(s[nt][2 + e] - u1);
+                sum0 += s[nt][e];
+                sum1 += s[nt][2 + e];
+            }
+        l0 = l0 * f0 + sum0;                             // this lane's columns only; the quad adds up at the end
+        l1 = l1 * f1 + sum1;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            o[nt][0] *= f0; o[nt][1] *= f0;
+            o[nt][2] *= f1; o[nt][3] *= f1;
+        }
+        // ---- O += P V: the score fragments are the A fragments of this product ----
+#pragma unroll
+        for (int j = 0; j < FA_BN / 16; j++) {
+            const uint32_t pa[4] = {pack_bf16(s[2 * j][0], s[2 * j][1]), pack_bf16(s[2 * j][2], s[2 * j][3]),
+                                    pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]), pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3])};
+#pragma unroll
+            for (int nt = 0; nt < NT; nt += 2) {
+                // B fragments (k = position, n = dimension) of dimension tiles nt and nt + 1, transposed on the way:
+                // matrices (positions 0-7, nt), (positions 8-15, nt), (0-7, nt + 1), (8-15, nt + 1) of the step
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, v_s + (16 * j + 8 * (lm & 1) + lr) * STRIDE + 8 * (nt + (lm >> 1)));
+                mma_bf16(o[nt], pa, b[0], b[1]);
+                mma_bf16(o[nt + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncthreads();                                 // every warp is done with this buffer
+    }
+#pragma unroll
+    for (int sh = 1; sh <= 2; sh <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, sh);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, sh);
+    }
+    const float i0 = ok0 ? 1.0f / l0 : 0.0f, i1 = ok1 ? 1.0f / l1 : 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int c = 8 * nt + 2 * t;
+        if (ok0) *reinterpret_cast<uint32_t *>(out + qo0 + c) = pack_bf16(o[nt][0] * i0, o[nt][1] * i0);
+        if (ok1) *reinterpret_cast<uint32_t *>(out + qo1 + c) = pack_bf16(o[nt][2] * i1, o[nt][3] * i1);
+    }
+}
+
 }  // namespace
 
 size_t attention_workspace_bytes(int total_query_tokens, int n_heads, int head_dim, int splits) {
@@ -521,6 +733,41 @@ static cudaError_t launch_gqa_hd(int group, dim3 grid, cudaStream_t s, const uin
         default: return cudaErrorInvalidValue;
     }
 #undef LLMRS_GQA
+}
+
+// Chunks of query tokens the grid must hold: every request may end in a partial chunk.
+template <int HD>
+static cudaError_t launch_prefill_hd(int group, int total_q, int num_req, int n_kv, cudaStream_t s, bool pdl, const uint16_t *q,
+                                     const uint16_t *k, const uint16_t *v, uint16_t *out, const uint32_t *bt,
+                                     const uint32_t *qs, const uint32_t *sl, int n_heads, int block_size, int max_blocks) {
+    constexpr size_t smem = (size_t)2 * 2 * FA_BN * (HD + 8) * sizeof(uint16_t);      // two buffers of a key and a value tile
+#define LLMRS_FA(G) { const int tok = 64 / G; const dim3 grid((unsigned)((total_q + tok - 1) / tok + num_req), (unsigned)n_kv); \
+    cudaError_t ea = cudaFuncSetAttribute(attention_prefill_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (ea != cudaSuccess) return ea; \
+    return launch_dependent(attention_prefill_kernel<HD, G>, grid, dim3(FA_THREADS), smem, s, pdl, q, k, v, out, bt, qs, sl, n_heads, n_kv, block_size, max_blocks, num_req); }
+    switch (group) {
+        case 1: LLMRS_FA(1)
+        case 2: LLMRS_FA(2)
+        case 4: LLMRS_FA(4)
+        case 8: LLMRS_FA(8)
+        default: return cudaErrorInvalidValue;
+    }
+#undef LLMRS_FA
+}
+
+cudaError_t launch_attention_prefill(const void *q, const void *k_pool, const void *v_pool, void *out,
+                                     const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
+                                     int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
+                                     int block_size, int max_blocks_per_seq, cudaStream_t s, bool pdl) {
+    if (total_query_tokens <= 0) return cudaSuccess;
+    const int group = n_heads / n_kv_heads;
+    if (head_dim == 128)
+        return launch_prefill_hd<128>(group, total_query_tokens, num_requests, n_kv_heads, s, pdl, (const uint16_t *)q,
+                                      (const uint16_t *)k_pool, (const uint16_t *)v_pool, (uint16_t *)out, block_table,
+                                      query_starts, seq_lens, n_heads, block_size, max_blocks_per_seq);
+    return launch_prefill_hd<64>(group, total_query_tokens, num_requests, n_kv_heads, s, pdl, (const uint16_t *)q,
+                                 (const uint16_t *)k_pool, (const uint16_t *)v_pool, (uint16_t *)out, block_table,
+                                 query_starts, seq_lens, n_heads, block_size, max_blocks_per_seq);
 }
 
 bool attention_gqa_supported(int dtype, int n_heads, int n_kv_heads, int head_dim) {

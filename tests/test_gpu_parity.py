@@ -850,3 +850,33 @@ def test_config3_prefill_full_size(backend):
     backend.matmul(h1, wb1, xb)
     backend.sync()
     assert np.array_equal(backend.read_to_vec_f32(h2), np.float32(2.0) * backend.read_to_vec_f32(h1))
+
+
+@pytest.mark.parametrize("n_heads,n_kv,hd,block", [(32, 8, 128, 256), (8, 8, 64, 16), (8, 4, 128, 32), (16, 2, 64, 64)])
+def test_attention_prefill_chunks(backend, n_heads, n_kv, hd, block):
+    """Prefill on the tensor-core kernel: a fresh prompt of 150 tokens, a chunked prefill of 70 tokens behind
+    200 cached positions, a single token and a 17-token tail, in one call; chunks of 64 / group query tokens
+    with ragged ends, causal masks that cut through tiles."""
+    seq_lens, q_counts = [150, 270, 90, 17], [150, 70, 1, 17]
+    max_blocks = (max(seq_lens) + block - 1) // block
+    n_pages = 4 * max_blocks + 3
+    rng = np.random.default_rng(11)
+    pages = rng.permutation(n_pages)
+    table = np.stack([pages[r * max_blocks:(r + 1) * max_blocks] for r in range(4)]).astype(np.uint32)
+    starts = np.concatenate([[0], np.cumsum(q_counts)]).astype(np.uint32)
+    total_q = int(starts[-1])
+    kvd = n_kv * hd
+    qb, q = _dense(backend, synth.activations(total_q, n_heads * hd, tid=141), True)
+    kb, k = _dense(backend, synth.activations(n_pages * block, kvd, tid=142), True)
+    vb, v = _dense(backend, synth.activations(n_pages * block, kvd, tid=143), True)
+    out = backend.alloc([n_heads * hd, total_q], DType.BF16)
+    before = backend.launch_count()
+    backend.attention(out, qb, kb, vb, backend.upload_u32(table.reshape(-1)), backend.upload_u32(starts),
+                      backend.upload_u32(seq_lens), n_heads, n_kv, hd, block, max_blocks)
+    backend.sync()
+    assert backend.launch_count() - before == 1
+    got = backend.read_to_vec_f32(out).reshape(total_q, n_heads * hd)
+    want = O.attention(q, k, v, table.reshape(-1), list(starts), seq_lens, n_heads, n_kv, hd, block, max_blocks, bf16=True)
+    assert np.isfinite(got).all()
+    assert O.rel_l2(got, want) <= 4e-3
+    assert np.abs(got - want).max() <= 2e-2
