@@ -792,8 +792,8 @@ def extra_measurements(be_factory, stream, peak_gbs):
             be.embed(x, emb, toks)
             t_plain = timed_graph(lambda: layers(False))
             be.embed(x, emb, toks)                       # fresh activations: 32 random layers blow the scale up
-            # the one-call forms pay off where the decode kernel serves them (up to 4 tokens)
-            t_graph = timed_graph(layers) if M <= 4 else t_plain
+            # the one-call forms: inside the decode kernel up to 4 tokens, fewer launches (one norm, one rope + scatter) above
+            t_graph = timed_graph(layers)
             be.embed(x, emb, toks)
             be.sync()
             t0 = time.perf_counter()
@@ -803,13 +803,58 @@ def extra_measurements(be_factory, stream, peak_gbs):
             t_edges = (time.perf_counter() - t0) / 5
             out["decode_step_full"][f"m{M}_ctx{ctx_len}"] = {
                 "ms_graph": round(t_graph * 1e3, 4), "ms_embed_and_argmax_host_timed": round(t_edges * 1e3, 4),
-                "tok_per_s": round(M / (t_graph + t_edges), 1), "calls_per_layer": 6 if M <= 4 else 16,
+                "tok_per_s": round(M / (t_graph + t_edges), 1), "calls_per_layer": 6,
                 "call_for_call_as_the_reference": {"ms_graph": round(t_plain * 1e3, 4), "calls_per_layer": 16,
                                                    "tok_per_s": round(M / (t_plain + t_edges), 1)}}
             for b in [bt, qs, sl, pos, slots, x, x2, xn, qb, ao, wo_o, ffn_o, kb, vb, gu, gu2, logits] + [p for kv in pools for p in kv]:
                 b.free()
         out["decode_step_full"]["note"] = ("random weights: the numbers in the activations are meaningless, the work is that "
                                            "of a Llama-3-8B decode step at the stated context; argmax only at one token")
+        # a whole prefill pass through the trait: one request of T prompt tokens, call for call as
+        # src/arch/llama.rs:150-170 makes them (the logits of the last token only, as a server needs them)
+        out["prefill_step_full"] = {}
+        for T in (512, 2048):
+            pages_per = (T + blk - 1) // blk
+            n_slots = pages_per * blk
+            pools = [(be.alloc([nkv * hd, n_slots], DType.BF16), be.alloc([nkv * hd, n_slots], DType.BF16)) for _ in range(32)]
+            bt = be.upload_u32(np.arange(pages_per, dtype=np.uint32))
+            qs, sl = be.upload_u32([0, T]), be.upload_u32([T])
+            pos = be.upload_u32(np.arange(T, dtype=np.uint32))
+            x, x2, xn, qb, ao, wo_o, ffn_o = (be.alloc([4096, T], DType.BF16) for _ in range(7))
+            kb, vb = be.alloc([1024, T], DType.BF16), be.alloc([1024, T], DType.BF16)
+            gu, gu2 = be.alloc([14336, T], DType.BF16), be.alloc([14336, T], DType.BF16)
+            last, lastn = be.alloc([4096], DType.BF16), be.alloc([4096], DType.BF16)
+            last_idx = be.upload_u32([T - 1])
+            logits = be.alloc([128256], DType.BF16)
+            toks = (np.arange(T, dtype=np.uint32) * 7 + 3) % 32000
+
+            def prefill():
+                for l in range(32):
+                    wq, wk, wv, wo, w1, w3, w2 = sets[l % n_layer_sets]
+                    kp, vp = pools[l]
+                    be.rms_norm(xn, x, ones, 1e-5)
+                    be.matmul(qb, wq, xn)
+                    be.matmul(kb, wk, xn)
+                    be.matmul(vb, wv, xn)
+                    be.rope_scatter_kv(qb, kb, vb, pos, hd, 500000.0, kp, vp, pos)
+                    be.attention(ao, qb, kp, vp, bt, qs, sl, nh, nkv, hd, blk, pages_per)
+                    be.matmul(wo_o, wo, ao)
+                    be.add(x2, x, wo_o)
+                    be.rms_norm(xn, x2, ones, 1e-5)
+                    be.matmul_gate_up(gu, w1, w3, xn)
+                    be.matmul(ffn_o, w2, gu)
+                    be.add(x, x2, ffn_o)
+                be.gather(last, x, last_idx, 1)
+                be.rms_norm(lastn, last, ones, 1e-5)
+                be.matmul(logits, wout, lastn)
+
+            be.embed(x, emb, toks)
+            t = timed_graph(prefill)
+            out["prefill_step_full"][f"t{T}"] = {"ms_graph": round(t * 1e3, 3), "tok_per_s": round(T / t, 1)}
+            for b in [bt, qs, sl, pos, x, x2, xn, qb, ao, wo_o, ffn_o, kb, vb, gu, gu2, last, lastn, last_idx, logits] + [p for kv in pools for p in kv]:
+                b.free()
+        out["prefill_step_full"]["note"] = ("one request, 8B shapes, random weights, 32 layers in one CUDA graph: norms, q/k/v, "
+                                            "rope + KV scatter, causal attention, wo, residuals, gate/up, down; last token's logits")
         out["decode_stack"]["note"] = ("linear stack only (225 matmuls, bf16 activations), one CUDA graph per step; "
                                        "weight bytes per step 4 841 250 816")
         out["gguf_upload"] = gguf_upload_measurement(be)

@@ -866,6 +866,12 @@ int llmrs_cuda_rms_norm_matmul_qkv(llmrs_ctx *ctx, llmrs_buf *out_q, llmrs_buf *
                    w->device == (uint32_t)ctx->device && o->device == (uint32_t)ctx->device;
     }
     if (!one_pass) {
+        if ((int)M > ctx->gemv_max_m)                    // no kernel folds the norm in at this token count: normalise once
+            return with_norm(ctx, "rms_norm_matmul_qkv", input, norm_weight, eps, false, [&](const llmrs_buf *x) {
+                int rc = LLMRS_OK;
+                for (int i = 0; i < 3 && rc == LLMRS_OK; i++) rc = llmrs_cuda_matmul(ctx, outs[i], ws[i], x);
+                return rc;
+            });
         int rc = LLMRS_OK;
         for (int i = 0; i < 3 && rc == LLMRS_OK; i++) rc = llmrs_cuda_rms_norm_matmul(ctx, outs[i], ws[i], input, norm_weight, eps);
         return rc;
