@@ -722,21 +722,15 @@ int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, con
                          buf_elems(q), num_req, buf_elems(query_starts), buf_elems(block_table));
     DeviceGuard guard(ctx->device);
     cudaError_t e;
-    if (attention_gqa_supported((int)q->dtype, (int)n_heads, (int)n_kv_heads, (int)head_dim) && total_q >= 2 * num_req) {
-        // requests with several query tokens on average (prefill): the tensor-core kernel, chunks of query tokens
-        e = ctx->begin_work();
-        if (e == cudaSuccess)
-            e = launch_attention_prefill(q->dptr, k_pool->dptr, v_pool->dptr, out->dptr, (const uint32_t *)block_table->dptr,
-                                         (const uint32_t *)query_starts->dptr, (const uint32_t *)seq_lens->dptr, (int)total_q,
-                                         (int)num_req, (int)n_heads, (int)n_kv_heads, (int)head_dim, (int)block_size,
-                                         (int)max_blocks_per_seq, ctx->stream, ctx->pdl);
-        if (e != cudaSuccess) return ctx->cuda_fail(e, "attention");
-        ctx->launches++;
-        return LLMRS_OK;
-    }
     if (attention_gqa_supported((int)q->dtype, (int)n_heads, (int)n_kv_heads, (int)head_dim)) {
-        // sequence lengths live on the device: the page table's capacity bounds them for the split count
-        const int splits = attention_splits((int)total_q, (int)n_kv_heads, (int)(block_size * max_blocks_per_seq), ctx->sm_count);
+        // The request lengths live on the device; the host knows the totals.  As many query tokens as requests:
+        // a decode batch, split-sequence kernel.  One request: a prefill, tensor-core kernel.  Otherwise the batch
+        // may mix the two: the tensor-core kernel takes the requests with several query tokens, the split-sequence
+        // kernel, its grid over requests, those with one.
+        const bool decode_only = total_q == num_req, prefill_only = num_req == 1 && total_q > 1;
+        const int split_tokens = (int)num_req;            // single-token requests at most
+        const int splits = prefill_only ? 1 : attention_splits(split_tokens, (int)n_kv_heads, (int)(block_size * max_blocks_per_seq), ctx->sm_count);
+        // the workspace is indexed by query token
         const size_t need = attention_workspace_bytes((int)total_q, (int)n_heads, (int)head_dim, splits);
         if (need > ctx->att_ws_bytes) {              // grows outside stream capture only, like the scratch
             cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
@@ -752,14 +746,22 @@ int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, con
             ctx->att_ws_bytes = need;
         }
         e = ctx->begin_work();
-        if (e == cudaSuccess)
+        if (e == cudaSuccess && !decode_only) {
+            e = launch_attention_prefill(q->dptr, k_pool->dptr, v_pool->dptr, out->dptr, (const uint32_t *)block_table->dptr,
+                                         (const uint32_t *)query_starts->dptr, (const uint32_t *)seq_lens->dptr, (int)total_q,
+                                         (int)num_req, (int)n_heads, (int)n_kv_heads, (int)head_dim, (int)block_size,
+                                         (int)max_blocks_per_seq, !prefill_only, ctx->stream, ctx->pdl);
+            ctx->launches++;
+        }
+        if (e == cudaSuccess && !prefill_only) {
             e = launch_attention_gqa(q->dptr, k_pool->dptr, v_pool->dptr, out->dptr, ctx->att_ws,
                                      (const uint32_t *)block_table->dptr, (const uint32_t *)query_starts->dptr,
                                      (const uint32_t *)seq_lens->dptr, (int)total_q, (int)num_req, (int)n_heads,
                                      (int)n_kv_heads, (int)head_dim, (int)block_size, (int)max_blocks_per_seq, splits,
-                                     ctx->stream, ctx->pdl);
+                                     !decode_only, ctx->stream, ctx->pdl);
+            ctx->launches += splits > 1 ? 2 : 1;
+        }
         if (e != cudaSuccess) return ctx->cuda_fail(e, "attention");
-        ctx->launches += splits > 1 ? 2 : 1;
         return LLMRS_OK;
     }
     e = ctx->begin_work();

@@ -313,7 +313,7 @@ attention_gqa_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict_
                      const uint16_t *__restrict__ v_pool, uint16_t *__restrict__ out, float *__restrict__ partial,
                      const uint32_t *__restrict__ block_table, const uint32_t *__restrict__ query_starts,
                      const uint32_t *__restrict__ seq_lens, int n_heads, int n_kv_heads, int block_size,
-                     int max_blocks_per_seq, int num_requests, int splits) {
+                     int max_blocks_per_seq, int num_requests, int splits, int by_request) {
     pdl_prologue();
     constexpr int KROW = HD + 8;                         // padded key row (bf16): 16-byte reads of 8 rows hit 32 banks
     __shared__ __align__(16) uint16_t k_s[AT2_TILE * KROW];
@@ -322,9 +322,17 @@ attention_gqa_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict_
     __shared__ __align__(16) float p_s[AT2_TILE * GROUP];          // [position][head]
     __shared__ float m_s[GROUP], l_s[GROUP], r_s[GROUP];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int kvh = blockIdx.x % n_kv_heads, gq = blockIdx.x / n_kv_heads, split = blockIdx.y;
-    int req = 0;
-    while (req + 1 < num_requests && (uint32_t)gq >= query_starts[req + 1]) req++;
+    const int kvh = blockIdx.x % n_kv_heads, split = blockIdx.y;
+    int gq = blockIdx.x / n_kv_heads, req = 0;
+    if (by_request) {
+        // mixed batch: the grid runs over requests and serves those with ONE query token; requests with
+        // several go to attention_prefill_kernel, launched beside this one
+        req = gq;
+        if ((int)query_starts[req + 1] - (int)query_starts[req] != 1) return;
+        gq = (int)query_starts[req];
+    } else {
+        while (req + 1 < num_requests && (uint32_t)gq >= query_starts[req + 1]) req++;
+    }
     const int local_q = gq - (int)query_starts[req];
     const int q_count = (int)query_starts[req + 1] - (int)query_starts[req];
     const int causal_len = (int)seq_lens[req] - q_count + local_q + 1;
@@ -461,11 +469,17 @@ attention_gqa_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict_
 // The ranges' maxima and sums are fetched by one thread each and combined with shuffles, and the
 // accumulators are read eight ranges at a time: two memory round trips, where a loop over the ranges
 // that used each value at once made one round trip per range (8 of the 13 us of a decode call).
-__global__ void attention_merge_kernel(const float *__restrict__ partial, uint16_t *__restrict__ out, int hd, int splits) {
+__global__ void attention_merge_kernel(const float *__restrict__ partial, uint16_t *__restrict__ out, int hd, int splits,
+                                       const uint32_t *__restrict__ query_starts, int n_heads, int by_request) {
     pdl_prologue();
     __shared__ float w_s[32];
     __shared__ float l_total;
-    const size_t th = blockIdx.x;                        // token * n_heads + head
+    size_t th = blockIdx.x;                              // token * n_heads + head
+    if (by_request) {                                    // request * n_heads + head: single-token requests only
+        const int req = (int)(blockIdx.x / (unsigned)n_heads), head = (int)(blockIdx.x % (unsigned)n_heads);
+        if ((int)query_starts[req + 1] - (int)query_starts[req] != 1) return;
+        th = (size_t)query_starts[req] * n_heads + head;
+    }
     const float *pr = partial + th * splits * (hd + 2);
     const int d = threadIdx.x;
     if (d < 32) {                                        // splits <= 32
@@ -537,7 +551,7 @@ attention_prefill_kernel(const uint16_t *__restrict__ q, const uint16_t *__restr
                          const uint16_t *__restrict__ v_pool, uint16_t *__restrict__ out,
                          const uint32_t *__restrict__ block_table, const uint32_t *__restrict__ query_starts,
                          const uint32_t *__restrict__ seq_lens, int n_heads, int n_kv_heads, int block_size,
-                         int max_blocks_per_seq, int num_requests) {
+                         int max_blocks_per_seq, int num_requests, int skip_single) {
     pdl_prologue();
     constexpr int TOK = 64 / GROUP;                      // query tokens per CTA
     constexpr int STRIDE = HD + 8;                       // elements per shared-memory row
@@ -550,7 +564,8 @@ attention_prefill_kernel(const uint16_t *__restrict__ q, const uint16_t *__restr
     int req = 0, chunk = blockIdx.x;
     for (; req < num_requests; req++) {
         const int cnt = (int)query_starts[req + 1] - (int)query_starts[req];
-        const int chunks = (cnt + TOK - 1) / TOK;
+        // requests of one query token are the split-sequence kernel's when it runs beside this one
+        const int chunks = skip_single && cnt == 1 ? 0 : (cnt + TOK - 1) / TOK;
         if (chunk < chunks) {
             chunk = chunks - 1 - chunk;                  // late chunks see the most positions: they start first
             break;
@@ -723,8 +738,8 @@ template <int HD>
 static cudaError_t launch_gqa_hd(int group, dim3 grid, cudaStream_t s, const uint16_t *q, const uint16_t *k,
                                  const uint16_t *v, uint16_t *out, float *partial, const uint32_t *bt,
                                  const uint32_t *qs, const uint32_t *sl, int n_heads, int n_kv, int block_size,
-                                 int max_blocks, int n_req, int splits, bool pdl) {
-#define LLMRS_GQA(G) return launch_dependent(attention_gqa_kernel<HD, G>, grid, dim3(AT2_THREADS), 0, s, pdl, q, k, v, out, partial, bt, qs, sl, n_heads, n_kv, block_size, max_blocks, n_req, splits)
+                                 int max_blocks, int n_req, int splits, int by_request, bool pdl) {
+#define LLMRS_GQA(G) return launch_dependent(attention_gqa_kernel<HD, G>, grid, dim3(AT2_THREADS), 0, s, pdl, q, k, v, out, partial, bt, qs, sl, n_heads, n_kv, block_size, max_blocks, n_req, splits, by_request)
     switch (group) {
         case 1: LLMRS_GQA(1);
         case 2: LLMRS_GQA(2);
@@ -739,12 +754,13 @@ static cudaError_t launch_gqa_hd(int group, dim3 grid, cudaStream_t s, const uin
 template <int HD>
 static cudaError_t launch_prefill_hd(int group, int total_q, int num_req, int n_kv, cudaStream_t s, bool pdl, const uint16_t *q,
                                      const uint16_t *k, const uint16_t *v, uint16_t *out, const uint32_t *bt,
-                                     const uint32_t *qs, const uint32_t *sl, int n_heads, int block_size, int max_blocks) {
+                                     const uint32_t *qs, const uint32_t *sl, int n_heads, int block_size, int max_blocks,
+                                     int skip_single) {
     constexpr size_t smem = (size_t)2 * 2 * FA_BN * (HD + 8) * sizeof(uint16_t);      // two buffers of a key and a value tile
 #define LLMRS_FA(G) { const int tok = 64 / G; const dim3 grid((unsigned)((total_q + tok - 1) / tok + num_req), (unsigned)n_kv); \
     cudaError_t ea = cudaFuncSetAttribute(attention_prefill_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (ea != cudaSuccess) return ea; \
-    return launch_dependent(attention_prefill_kernel<HD, G>, grid, dim3(FA_THREADS), smem, s, pdl, q, k, v, out, bt, qs, sl, n_heads, n_kv, block_size, max_blocks, num_req); }
+    return launch_dependent(attention_prefill_kernel<HD, G>, grid, dim3(FA_THREADS), smem, s, pdl, q, k, v, out, bt, qs, sl, n_heads, n_kv, block_size, max_blocks, num_req, skip_single); }
     switch (group) {
         case 1: LLMRS_FA(1)
         case 2: LLMRS_FA(2)
@@ -758,16 +774,18 @@ static cudaError_t launch_prefill_hd(int group, int total_q, int num_req, int n_
 cudaError_t launch_attention_prefill(const void *q, const void *k_pool, const void *v_pool, void *out,
                                      const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
                                      int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
-                                     int block_size, int max_blocks_per_seq, cudaStream_t s, bool pdl) {
+                                     int block_size, int max_blocks_per_seq, bool skip_single_token_requests, cudaStream_t s,
+                                     bool pdl) {
     if (total_query_tokens <= 0) return cudaSuccess;
     const int group = n_heads / n_kv_heads;
+    const int skip_single = skip_single_token_requests ? 1 : 0;
     if (head_dim == 128)
         return launch_prefill_hd<128>(group, total_query_tokens, num_requests, n_kv_heads, s, pdl, (const uint16_t *)q,
                                       (const uint16_t *)k_pool, (const uint16_t *)v_pool, (uint16_t *)out, block_table,
-                                      query_starts, seq_lens, n_heads, block_size, max_blocks_per_seq);
+                                      query_starts, seq_lens, n_heads, block_size, max_blocks_per_seq, skip_single);
     return launch_prefill_hd<64>(group, total_query_tokens, num_requests, n_kv_heads, s, pdl, (const uint16_t *)q,
                                  (const uint16_t *)k_pool, (const uint16_t *)v_pool, (uint16_t *)out, block_table,
-                                 query_starts, seq_lens, n_heads, block_size, max_blocks_per_seq);
+                                 query_starts, seq_lens, n_heads, block_size, max_blocks_per_seq, skip_single);
 }
 
 bool attention_gqa_supported(int dtype, int n_heads, int n_kv_heads, int head_dim) {
@@ -778,20 +796,23 @@ bool attention_gqa_supported(int dtype, int n_heads, int n_kv_heads, int head_di
 cudaError_t launch_attention_gqa(const void *q, const void *k_pool, const void *v_pool, void *out, float *workspace,
                                  const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
                                  int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
-                                 int block_size, int max_blocks_per_seq, int splits, cudaStream_t s, bool pdl) {
+                                 int block_size, int max_blocks_per_seq, int splits, bool single_token_requests_only,
+                                 cudaStream_t s, bool pdl) {
     if (total_query_tokens <= 0) return cudaSuccess;
-    const dim3 grid((unsigned)(total_query_tokens * n_kv_heads), (unsigned)splits);
+    const int by_request = single_token_requests_only ? 1 : 0;
+    const int units = by_request ? num_requests : total_query_tokens;       // what the grid runs over
+    const dim3 grid((unsigned)(units * n_kv_heads), (unsigned)splits);
     const int group = n_heads / n_kv_heads;
     cudaError_t e = head_dim == 128
         ? launch_gqa_hd<128>(group, grid, s, (const uint16_t *)q, (const uint16_t *)k_pool, (const uint16_t *)v_pool,
                              (uint16_t *)out, workspace, block_table, query_starts, seq_lens, n_heads, n_kv_heads,
-                             block_size, max_blocks_per_seq, num_requests, splits, pdl)
+                             block_size, max_blocks_per_seq, num_requests, splits, by_request, pdl)
         : launch_gqa_hd<64>(group, grid, s, (const uint16_t *)q, (const uint16_t *)k_pool, (const uint16_t *)v_pool,
                             (uint16_t *)out, workspace, block_table, query_starts, seq_lens, n_heads, n_kv_heads,
-                            block_size, max_blocks_per_seq, num_requests, splits, pdl);
+                            block_size, max_blocks_per_seq, num_requests, splits, by_request, pdl);
     if (e != cudaSuccess || splits == 1) return e;
-    return launch_dependent(attention_merge_kernel, dim3((unsigned)(total_query_tokens * n_heads)), dim3(head_dim), 0, s,
-                            pdl, (const float *)workspace, (uint16_t *)out, head_dim, splits);
+    return launch_dependent(attention_merge_kernel, dim3((unsigned)(units * n_heads)), dim3(head_dim), 0, s,
+                            pdl, (const float *)workspace, (uint16_t *)out, head_dim, splits, query_starts, n_heads, by_request);
 }
 
 cudaError_t launch_rope(void *q, int q_dtype, int q_stride, void *k, int k_dtype, int k_stride, const uint32_t *positions,

@@ -76,14 +76,18 @@ size_t attention_workspace_bytes(int total_query_tokens, int n_heads, int head_d
 cudaError_t launch_attention_gqa(const void *q, const void *k_pool, const void *v_pool, void *out, float *workspace,
                                  const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
                                  int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
-                                 int block_size, int max_blocks_per_seq, int splits, cudaStream_t s, bool pdl);
+                                 int block_size, int max_blocks_per_seq, int splits, bool single_token_requests_only,
+                                 cudaStream_t s, bool pdl);
 // The same shapes and types where requests bring several query tokens (prefill): scores and weighted
 // values on the tensor cores (mma.sync, bf16), one CTA per (request, 64 / group consecutive query tokens,
-// KV head); no workspace.
+// KV head); no workspace.  In a mixed batch the two kernels run side by side: this one with
+// skip_single_token_requests, launch_attention_gqa with single_token_requests_only (its grid then runs over
+// requests, `splits` chosen for num_requests tokens).
 cudaError_t launch_attention_prefill(const void *q, const void *k_pool, const void *v_pool, void *out,
                                      const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
                                      int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
-                                     int block_size, int max_blocks_per_seq, cudaStream_t s, bool pdl);
+                                     int block_size, int max_blocks_per_seq, bool skip_single_token_requests, cudaStream_t s,
+                                     bool pdl);
 cudaError_t launch_attention(const void *q, const void *k_pool, const void *v_pool, void *out, int dtype,
                              const uint32_t *block_table, const uint32_t *query_starts, const uint32_t *seq_lens,
                              int total_query_tokens, int num_requests, int n_heads, int n_kv_heads, int head_dim,
