@@ -34,7 +34,7 @@ Q6K, Q4K = 14, 12
 BLOCK_BYTES = {Q4K: 144, Q6K: 210}
 L2_BYTES = 126e6
 NCU_DRAM_BYTES_PER_LAUNCH = 435114240   # Q6_K 4096 -> 128256, one token: 431.03 MB read + 4.08 MB written
-FUSED_GATHER_MAX_WORDS = 1 << 18      # values one rank posts per peer and matmul, above which NCCL moves them
+FUSED_GATHER_MAX_WORDS = 1 << 18      # values one rank receives from its peers per matmul, above which NCCL moves them
 
 
 def algorithmic_bytes(dtype: int, K: int, N: int, M: int, in_bytes: int = 4, out_bytes: int = 4) -> int:
@@ -399,7 +399,7 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
     }
     out = {"n_gpus": world, "note": ("linear stack only (7 matmuls per layer + output projection, bf16 activations); "
                                       "weights N-sharded, activations replicated, all-gather of every output: fused "
-                                      "into the kernel (peer mailboxes) where a rank posts <= 256 K values per peer "
+                                      "into the kernel (peer mailboxes) where a rank receives <= 256 K values per matmul "
                                       "and M <= 128, NCCL elsewhere; no_exchange = the same matmuls without the "
                                       "all-gather")}
     for name, cfg in models.items():
@@ -430,7 +430,7 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
             # fused where the exchange is latency (few words per peer), NCCL where it is volume
             kinds = {(dt, K, N) for dt, K, N in layer + [(Q6K, H, V)]}
             fits = {(dt, K, N) for dt, K, N in kinds
-                    if be.allgather_max_tokens(DType(dt), K) >= M and M * (N // world) <= FUSED_GATHER_MAX_WORDS}
+                    if be.allgather_max_tokens(DType(dt), K) >= M and (world - 1) * M * (N // world) <= FUSED_GATHER_MAX_WORDS}
             fused = {N: FusedGather(be, N, M, out_dtype=torch.bfloat16) for N in dims} if fits else None
             fulls = {N: torch.empty(world, M, N // world, device=dev, dtype=torch.bfloat16) for N in dims}
 
@@ -486,7 +486,7 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
                             "TFLOPs": round(flops_per_token * M / t / 1e12, 1),
                             "frac_of_tensor_peak_x_gpus": round(flops_per_token * M / t / 1e12 / (tf_peak * world), 4),
                             "exchange": ("fused peer stores" if fits == kinds else
-                                         "fused peer stores where a rank posts <= 256 K values per peer, NCCL all-gather elsewhere" if fits
+                                         "fused peer stores where a rank receives <= 256 K values per matmul, NCCL all-gather elsewhere" if fits
                                          else "NCCL all-gather"),
                             "cuda_graph": graphed}
             for bfr in list(xs.values()) + list(lbufs.values()):
