@@ -171,12 +171,7 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// registers -> 32 lanes x 8 (16) consecutive 32-bit TMEM columns
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
-                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
-}
+// registers -> 32 lanes x 16 consecutive 32-bit TMEM columns
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -236,8 +231,6 @@ __device__ __forceinline__ float byte_to_float(uint32_t word, int byte) {
     return __uint_as_float(bits) - 8388608.0f;
 }
 
-// 16-byte chunk `c` (0..7) of row `r` inside a 128-byte-swizzled tile.
-__device__ __forceinline__ uint32_t swz_off(int r, int c) { return (uint32_t)r * 128u + (uint32_t)((c ^ (r & 7)) << 4); }
 
 // ---- dequantisation of one thread's 32 weights of a K step ---------------------------------------
 // The raw bytes of a whole 256-weight block are fetched one block ahead into registers, so the
@@ -262,8 +255,6 @@ __device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
     asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
     return r;
 }
-// float -> f16 bits duplicated in both halves (clamped to the finite range).
-__device__ __forceinline__ uint32_t h2_dup(float v) { return pack_w(v, v); }
 
 // bytes (b0, b1) resp. (b2, b3) of `bytes4` -> f16x2 (1024 + b, 1024 + b'); bytes must be < 1024.
 __device__ __forceinline__ uint32_t magic_lo(uint32_t bytes4) { return __byte_perm(bytes4, 0x64646464u, 0x5140u); }
