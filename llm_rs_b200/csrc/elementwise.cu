@@ -283,186 +283,24 @@ attention_kernel(const void *q, const void *k_pool, const void *v_pool, void *ou
     }
 }
 
-// The same attention for bf16 buffers, organised around the memory traffic.  One CTA per (query
-// token, KV head, split of the sequence): the `GROUP` query heads that share a KV head are served
-// from ONE pass over its keys and values, which come into shared memory 64 positions at a time with
-// coalesced 16-byte loads (16 consecutive threads per 256-byte row).  Thread (position, half of the
-// heads) forms the scores from shared memory, a warp per head does the online-softmax bookkeeping,
-// thread d accumulates the values for all heads of the group.  A long sequence with few query
-// tokens (decode) is cut into `splits` ranges so that all SMs work; the partial (accumulator,
-// maximum, sum) triples are merged by attention_merge_kernel.
-constexpr int AT2_TILE = 64;
-constexpr int AT2_THREADS = 128;
+// Attention for bf16 buffers (head_dim 64 or 128, 1/2/4/8 query heads per KV head), organised around the
+// memory traffic: the query heads that share a KV head are served from ONE pass over its keys and values,
+// which come into shared memory 64 positions at a time by asynchronous 16-byte copies.  A long sequence
+// with few query tokens (decode) is cut into `splits` ranges so that all SMs work; the ranges' partial
+// (accumulator, maximum, sum) triples are merged by attention_merge_kernel.  The kernels follow further
+// down (attention_decode_mma_kernel, attention_prefill_kernel); a first version that formed scores and
+// weighted values on the CUDA cores took 74 us where the tensor-core one takes 40 (8 requests x 4096).
+constexpr int AT2_TILE = 64;          // positions per tile: what attention_splits counts in
 
 // 16 bytes global -> shared without a register in between (both addresses 16-byte aligned).
 __device__ __forceinline__ void async_copy16(void *smem_dst, const void *gmem_src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
                  : "memory");
 }
-__device__ __forceinline__ void async_copy_wait_all() {
-    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
-}
 __device__ __forceinline__ void async_copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 // Waits until at most `Pending` of this thread's committed groups are still in flight.
 template <int Pending> __device__ __forceinline__ void async_copy_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(Pending) : "memory");
-}
-template <int HD, int GROUP>
-__global__ void __launch_bounds__(AT2_THREADS)
-attention_gqa_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k_pool,
-                     const uint16_t *__restrict__ v_pool, uint16_t *__restrict__ out, float *__restrict__ partial,
-                     const uint32_t *__restrict__ block_table, const uint32_t *__restrict__ query_starts,
-                     const uint32_t *__restrict__ seq_lens, int n_heads, int n_kv_heads, int block_size,
-                     int max_blocks_per_seq, int num_requests, int splits, int by_request) {
-    pdl_prologue();
-    constexpr int KROW = HD + 8;                         // padded key row (bf16): 16-byte reads of 8 rows hit 32 banks
-    __shared__ __align__(16) uint16_t k_s[AT2_TILE * KROW];
-    __shared__ __align__(16) uint16_t v_s[AT2_TILE * HD];
-    __shared__ __align__(16) float q_s[GROUP * HD];
-    __shared__ __align__(16) float p_s[AT2_TILE * GROUP];          // [position][head]
-    __shared__ float m_s[GROUP], l_s[GROUP], r_s[GROUP];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int kvh = blockIdx.x % n_kv_heads, split = blockIdx.y;
-    int gq = blockIdx.x / n_kv_heads, req = 0;
-    if (by_request) {
-        // mixed batch: the grid runs over requests and serves those with ONE query token; requests with
-        // several go to attention_prefill_kernel, launched beside this one
-        req = gq;
-        if ((int)query_starts[req + 1] - (int)query_starts[req] != 1) return;
-        gq = (int)query_starts[req];
-    } else {
-        while (req + 1 < num_requests && (uint32_t)gq >= query_starts[req + 1]) req++;
-    }
-    const int local_q = gq - (int)query_starts[req];
-    const int q_count = (int)query_starts[req + 1] - (int)query_starts[req];
-    const int causal_len = (int)seq_lens[req] - q_count + local_q + 1;
-    const int kv_dim = n_kv_heads * HD, kv_off = kvh * HD;
-    const float scale = rsqrtf((float)HD);
-    const size_t q_off = (size_t)gq * n_heads * HD + (size_t)kvh * GROUP * HD;       // the group's heads are adjacent
-    // this split's range of positions, whole tiles
-    const int tiles = (causal_len + AT2_TILE - 1) / AT2_TILE;
-    const int per = (tiles + splits - 1) / splits;
-    const int t_begin = min(split * per, tiles) * AT2_TILE, t_end = min(min((split + 1) * per, tiles) * AT2_TILE, causal_len);
-
-    for (int i = tid; i < GROUP * HD; i += AT2_THREADS) q_s[i] = bf16_bits_to_f32(q[q_off + i]) * scale;
-    if (tid < GROUP) { m_s[tid] = -INFINITY; l_s[tid] = 0.0f; }
-    float acc[GROUP];
-#pragma unroll
-    for (int h = 0; h < GROUP; h++) acc[h] = 0.0f;
-    __syncthreads();
-
-    constexpr int CH = HD / 8;                           // 16-byte chunks per row
-    for (int t0 = t_begin; t0 < t_end; t0 += AT2_TILE) {
-        const int tile_len = min(AT2_TILE, t_end - t0);
-        // ---- keys and values of the tile -> shared memory ----
-        // Asynchronous 16-byte copies, all of a thread's chunks in flight at once: with loads through
-        // registers the loop ran one memory round trip per iteration, eight in a row per tile.
-        for (int c = tid; c < AT2_TILE * CH; c += AT2_THREADS) {
-            const int j = c / CH, ch = c % CH;
-            uint16_t *kd = k_s + j * KROW + 8 * ch, *vd = v_s + j * HD + 8 * ch;
-            if (j < tile_len) {
-                const int t = t0 + j;
-                const uint32_t page = block_table[(size_t)req * max_blocks_per_seq + t / block_size];
-                const size_t row = ((size_t)page * block_size + (size_t)(t % block_size)) * kv_dim + kv_off;
-                async_copy16(kd, k_pool + row + 8 * ch);
-                async_copy16(vd, v_pool + row + 8 * ch);
-            } else {
-                *reinterpret_cast<uint4 *>(kd) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4 *>(vd) = make_uint4(0, 0, 0, 0);
-            }
-        }
-        async_copy_wait_all();
-        __syncthreads();
-        // ---- scores: thread (position j, half of the heads) ----
-        {
-            constexpr int HH = GROUP >= 2 ? GROUP / 2 : 1;          // heads per thread
-            const int j = tid % AT2_TILE, h0 = (tid / AT2_TILE) * HH;
-            if (GROUP >= 2 || tid < AT2_TILE) {
-                float dot[HH];
-#pragma unroll
-                for (int h = 0; h < HH; h++) dot[h] = 0.0f;
-#pragma unroll 4
-                for (int ch = 0; ch < CH; ch++) {
-                    const uint4 u = *reinterpret_cast<const uint4 *>(k_s + j * KROW + 8 * ch);
-                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-                    float kf[8];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        kf[2 * e] = __uint_as_float(w[e] << 16);
-                        kf[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
-                    }
-#pragma unroll
-                    for (int h = 0; h < HH; h++) {
-                        const float4 qa = *reinterpret_cast<const float4 *>(q_s + (h0 + h) * HD + 8 * ch);
-                        const float4 qb = *reinterpret_cast<const float4 *>(q_s + (h0 + h) * HD + 8 * ch + 4);
-                        dot[h] = fmaf(qa.x, kf[0], fmaf(qa.y, kf[1], fmaf(qa.z, kf[2], fmaf(qa.w, kf[3], dot[h]))));
-                        dot[h] = fmaf(qb.x, kf[4], fmaf(qb.y, kf[5], fmaf(qb.z, kf[6], fmaf(qb.w, kf[7], dot[h]))));
-                    }
-                }
-#pragma unroll
-                for (int h = 0; h < HH; h++) p_s[j * GROUP + h0 + h] = j < tile_len ? dot[h] : -INFINITY;
-            }
-        }
-        __syncthreads();
-        // ---- online softmax: warp w keeps the books of heads w, w + 4 ----
-        for (int h = warp; h < GROUP; h += AT2_THREADS / 32) {
-            const float s0 = p_s[lane * GROUP + h], s1 = p_s[(lane + 32) * GROUP + h];
-            float mx = fmaxf(s0, s1);
-#pragma unroll
-            for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            const float m_old = m_s[h], m_new = fmaxf(m_old, mx);
-            const float e0 = __expf(s0 - m_new), e1 = __expf(s1 - m_new);
-            p_s[lane * GROUP + h] = e0;
-            p_s[(lane + 32) * GROUP + h] = e1;
-            float sum = e0 + e1;
-#pragma unroll
-            for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (lane == 0) {
-                const float r = __expf(m_old - m_new);
-                r_s[h] = r;
-                l_s[h] = l_s[h] * r + sum;
-                m_s[h] = m_new;
-            }
-        }
-        __syncthreads();
-        // ---- values: thread d, all heads of the group ----
-        for (int d = tid; d < HD; d += AT2_THREADS) {
-#pragma unroll
-            for (int h = 0; h < GROUP; h++) acc[h] *= r_s[h];
-#pragma unroll 4
-            for (int j = 0; j < tile_len; j++) {
-                const float v = bf16_bits_to_f32(v_s[j * HD + d]);
-                float pj[GROUP];                         // the position's weights for all heads: one or two 16-byte reads
-                if constexpr (GROUP % 4 == 0) {
-#pragma unroll
-                    for (int h4 = 0; h4 < GROUP / 4; h4++) {
-                        const float4 t = *reinterpret_cast<const float4 *>(p_s + j * GROUP + 4 * h4);
-                        pj[4 * h4] = t.x; pj[4 * h4 + 1] = t.y; pj[4 * h4 + 2] = t.z; pj[4 * h4 + 3] = t.w;
-                    }
-                } else {
-#pragma unroll
-                    for (int h = 0; h < GROUP; h++) pj[h] = p_s[j * GROUP + h];
-                }
-#pragma unroll
-                for (int h = 0; h < GROUP; h++) acc[h] = fmaf(pj[h], v, acc[h]);
-            }
-        }
-        __syncthreads();
-    }
-    for (int d = tid; d < HD; d += AT2_THREADS) {
-#pragma unroll
-        for (int h = 0; h < GROUP; h++) {
-            const int head = kvh * GROUP + h;
-            if (splits == 1) {
-                out[(size_t)gq * n_heads * HD + (size_t)head * HD + d] =
-                    __bfloat16_as_ushort(__float2bfloat16_rn(acc[h] / l_s[h]));
-            } else {
-                float *pr = partial + (((size_t)gq * n_heads + head) * splits + split) * (HD + 2);
-                pr[d] = acc[h];
-                if (d == 0) { pr[HD] = m_s[h]; pr[HD + 1] = l_s[h]; }
-            }
-        }
-    }
 }
 
 // out = sum_s acc_s e^(m_s - m) / sum_s l_s e^(m_s - m): one CTA of HD threads per (query token, head).
@@ -718,6 +556,173 @@ attention_prefill_kernel(const uint16_t *__restrict__ q, const uint16_t *__restr
     }
 }
 
+// ---- decode attention on the tensor cores --------------------------------------------------------
+// One CTA per (query token, KV head, range of the sequence); scores and weighted values are mma.sync m16n8k16: the group's heads are rows
+// 0 .. GROUP-1 of the 16-row A operand (the rest are zero), and the four warps split a tile's 64 positions,
+// 16 each, every warp keeping its own running maximum, sum and accumulator over the positions it sees;
+// the four meet in shared memory at the end.  Per tile a warp issues 2 x HD/16 + HD/8 MMAs where the
+// CUDA-core kernel spends ~1000 multiply-adds per thread.
+template <int HD, int GROUP>
+__global__ void __launch_bounds__(FA_THREADS)
+attention_decode_mma_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k_pool,
+                            const uint16_t *__restrict__ v_pool, uint16_t *__restrict__ out, float *__restrict__ partial,
+                            const uint32_t *__restrict__ block_table, const uint32_t *__restrict__ query_starts,
+                            const uint32_t *__restrict__ seq_lens, int n_heads, int n_kv_heads, int block_size,
+                            int max_blocks_per_seq, int num_requests, int splits, int by_request) {
+    pdl_prologue();
+    constexpr int STRIDE = HD + 8;
+    constexpr int KS = HD / 16, NT = HD / 8, CH = HD / 8;
+    constexpr int TILE = FA_BN * STRIDE;
+    static_assert(4 * GROUP * (HD + 2) * 4 <= 2 * TILE * 2, "the warps' results reuse the first tile buffer");
+    extern __shared__ __align__(16) uint16_t fa_s[];     // [2 buffers][key tile | value tile]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int kvh = blockIdx.x % n_kv_heads, split = blockIdx.y;
+    int gq = blockIdx.x / n_kv_heads, req = 0;
+    if (by_request) {                                    // mixed batch: requests with one query token only
+        req = gq;
+        if ((int)query_starts[req + 1] - (int)query_starts[req] != 1) return;
+        gq = (int)query_starts[req];
+    } else {
+        while (req + 1 < num_requests && (uint32_t)gq >= query_starts[req + 1]) req++;
+    }
+    const int local_q = gq - (int)query_starts[req];
+    const int q_count = (int)query_starts[req + 1] - (int)query_starts[req];
+    const int causal_len = (int)seq_lens[req] - q_count + local_q + 1;
+    const int kv_dim = n_kv_heads * HD, kv_off = kvh * HD;
+    const int tiles = (causal_len + FA_BN - 1) / FA_BN;
+    const int per = (tiles + splits - 1) / splits;
+    const int t_begin = min(split * per, tiles) * FA_BN, t_end = min(min((split + 1) * per, tiles) * FA_BN, causal_len);
+    const size_t q_off = (size_t)gq * n_heads * HD + (size_t)kvh * GROUP * HD;
+    const bool row_ok = g < GROUP;                       // row g of the A operand is head g of the group
+    uint32_t qa[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+        const int c = 16 * ks + 2 * t;
+        qa[ks][0] = row_ok ? *reinterpret_cast<const uint32_t *>(q + q_off + (size_t)g * HD + c) : 0u;
+        qa[ks][2] = row_ok ? *reinterpret_cast<const uint32_t *>(q + q_off + (size_t)g * HD + c + 8) : 0u;
+        qa[ks][1] = qa[ks][3] = 0u;                      // rows 8 .. 15: no heads there
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;               // of row g, over this warp's positions
+    const float sc = rsqrtf((float)HD);
+
+    auto fetch_tile = [&](int p0, int buf) {
+        uint16_t *kb = fa_s + buf * 2 * TILE, *vb = kb + TILE;
+        for (int c = tid; c < FA_BN * CH; c += FA_THREADS) {
+            const int j = c / CH, ch = c % CH;
+            uint16_t *kd = kb + j * STRIDE + 8 * ch, *vd = vb + j * STRIDE + 8 * ch;
+            const int pos = p0 + j;
+            if (pos < t_end) {
+                const uint32_t page = block_table[(size_t)req * max_blocks_per_seq + pos / block_size];
+                const size_t row = ((size_t)page * block_size + (size_t)(pos % block_size)) * kv_dim + kv_off;
+                async_copy16(kd, k_pool + row + 8 * ch);
+                async_copy16(vd, v_pool + row + 8 * ch);
+            } else {
+                *reinterpret_cast<uint4 *>(kd) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4 *>(vd) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        async_copy_commit();
+    };
+    if (t_begin < t_end) fetch_tile(t_begin, 0);
+    int buf = 0;
+    const int lm = lane >> 3, lr = lane & 7;
+    for (int p0 = t_begin; p0 < t_end; p0 += FA_BN, buf ^= 1) {
+        const uint16_t *k_s = fa_s + buf * 2 * TILE, *v_s = k_s + TILE;
+        if (p0 + FA_BN < t_end) {
+            fetch_tile(p0 + FA_BN, buf ^ 1);
+            async_copy_wait<1>();
+        } else {
+            async_copy_wait<0>();
+        }
+        __syncthreads();
+        // ---- scores of this warp's 16 positions: two position tiles ----
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            uint32_t b[4];
+            ldmatrix_x4(b, k_s + (16 * warp + 8 * (lm >> 1) + lr) * STRIDE + 16 * ks + 8 * (lm & 1));
+            mma_bf16(s[0], qa[ks], b[0], b[1]);
+            mma_bf16(s[1], qa[ks], b[2], b[3]);
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int pos = p0 + 16 * warp + 8 * nt + 2 * t + e;
+                s[nt][e] = pos < t_end ? s[nt][e] * sc : -INFINITY;
+                mx = fmaxf(mx, s[nt][e]);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+        const float f = __expf(m_run - m_use);
+        m_run = m_new;
+        float sum = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                s[nt][e] = __expf(s[nt][e] - m_use);
+                sum += s[nt][e];
+            }
+        l_run = l_run * f + sum;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) { o[nt][0] *= f; o[nt][1] *= f; }
+        // ---- weighted values: one step of 16 positions ----
+        const uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), 0u, pack_bf16(s[1][0], s[1][1]), 0u};
+#pragma unroll
+        for (int nt = 0; nt < NT; nt += 2) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, v_s + (16 * warp + 8 * (lm & 1) + lr) * STRIDE + 8 * (nt + (lm >> 1)));
+            mma_bf16(o[nt], pa, b[0], b[1]);
+            mma_bf16(o[nt + 1], pa, b[2], b[3]);
+        }
+        __syncthreads();
+    }
+    // ---- the four warps' results meet in shared memory (the tile buffers are no longer read) ----
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    float *res = reinterpret_cast<float *>(fa_s);        // [warp][head][HD accumulator values, maximum, sum]
+    if (row_ok) {
+        float *r = res + (size_t)(warp * GROUP + g) * (HD + 2);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            r[8 * nt + 2 * t] = o[nt][0];
+            r[8 * nt + 2 * t + 1] = o[nt][1];
+        }
+        if (t == 0) { r[HD] = m_run; r[HD + 1] = l_run; }
+    }
+    __syncthreads();
+    for (int i = tid; i < GROUP * HD; i += FA_THREADS) {
+        const int h = i / HD, d = i % HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) m = fmaxf(m, res[(size_t)(w * GROUP + h) * (HD + 2) + HD]);
+        float acc = 0.0f, l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float *r = res + (size_t)(w * GROUP + h) * (HD + 2);
+            const float wt = r[HD] == -INFINITY ? 0.0f : __expf(r[HD] - m);
+            acc = fmaf(r[d], wt, acc);
+            l = fmaf(r[HD + 1], wt, l);
+        }
+        const int head = kvh * GROUP + h;
+        if (splits == 1) {
+            out[(size_t)gq * n_heads * HD + (size_t)head * HD + d] = __bfloat16_as_ushort(__float2bfloat16_rn(acc / l));
+        } else {
+            float *pr = partial + (((size_t)gq * n_heads + head) * splits + split) * (HD + 2);
+            pr[d] = acc;
+            if (d == 0) { pr[HD] = m; pr[HD + 1] = l; }
+        }
+    }
+}
+
 }  // namespace
 
 size_t attention_workspace_bytes(int total_query_tokens, int n_heads, int head_dim, int splits) {
@@ -739,12 +744,15 @@ static cudaError_t launch_gqa_hd(int group, dim3 grid, cudaStream_t s, const uin
                                  const uint16_t *v, uint16_t *out, float *partial, const uint32_t *bt,
                                  const uint32_t *qs, const uint32_t *sl, int n_heads, int n_kv, int block_size,
                                  int max_blocks, int n_req, int splits, int by_request, bool pdl) {
-#define LLMRS_GQA(G) return launch_dependent(attention_gqa_kernel<HD, G>, grid, dim3(AT2_THREADS), 0, s, pdl, q, k, v, out, partial, bt, qs, sl, n_heads, n_kv, block_size, max_blocks, n_req, splits, by_request)
+    constexpr size_t smem = (size_t)2 * 2 * FA_BN * (HD + 8) * sizeof(uint16_t);      // two buffers of a key and a value tile
+#define LLMRS_GQA(G) { cudaError_t ea = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (ea != cudaSuccess) return ea; \
+    return launch_dependent(attention_decode_mma_kernel<HD, G>, grid, dim3(FA_THREADS), smem, s, pdl, q, k, v, out, partial, bt, qs, sl, n_heads, n_kv, block_size, max_blocks, n_req, splits, by_request); }
     switch (group) {
-        case 1: LLMRS_GQA(1);
-        case 2: LLMRS_GQA(2);
-        case 4: LLMRS_GQA(4);
-        case 8: LLMRS_GQA(8);
+        case 1: LLMRS_GQA(1)
+        case 2: LLMRS_GQA(2)
+        case 4: LLMRS_GQA(4)
+        case 8: LLMRS_GQA(8)
         default: return cudaErrorInvalidValue;
     }
 #undef LLMRS_GQA
