@@ -33,13 +33,24 @@ K_IN, N_OUT = 4096, 128256
 Q6K, Q4K = 14, 12
 BLOCK_BYTES = {Q4K: 144, Q6K: 210}
 L2_BYTES = 126e6
-NCU_DRAM_BYTES_PER_LAUNCH = 435114240   # Q6_K 4096 -> 128256, one token: 431.03 MB read + 4.08 MB written
 FUSED_GATHER_MAX_WORDS = 1 << 18      # values one rank receives from its peers per matmul, above which NCCL moves them
 
 
 def algorithmic_bytes(dtype: int, K: int, N: int, M: int, in_bytes: int = 4, out_bytes: int = 4) -> int:
     """GGUF weight bytes + activations in + outputs out (the figure the roofline uses)."""
     return N * (K // 256) * BLOCK_BYTES[dtype] + M * K * in_bytes + M * N * out_bytes
+
+
+def ncu_dram_bytes_per_launch() -> tuple[int | None, str | None]:
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel (Q6_K 4096 ->
+    128256, one token), from the ncu capture recorded in profiles/traffic.json together with the commit
+    of the kernel it was taken on; None when the record is missing."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            rec = json.load(f)["q6k_gemv_k4096_n128256_m1"]
+        return int(rec["dram_bytes_read"]) + int(rec["dram_bytes_write"]), str(rec.get("kernel_commit"))
+    except Exception:  # noqa: BLE001
+        return None, None
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -198,6 +209,64 @@ def run_reference(args, rank: int, world: int):
 # ------------------------------------------------------------------------------------------------
 # Our arm
 # ------------------------------------------------------------------------------------------------
+def allgather_check(be, stream, dev, world, fused, weight, xbuf, N, M, out_torch_dtype):
+    """Product against product: the matmul with the all-gather fused into the kernel (FusedGather: one eager
+    call and one replay of a captured CUDA graph) beside the plain matmul of the same weight shard followed
+    by NCCL's all-gather, on the same inputs.  The caller passes activations that differ from those of the
+    calls before, so a mailbox word left over from an earlier call cannot pass for this call's.  Returns
+    the differences; `ok` is what the bench fails on."""
+    import torch
+    import torch.distributed as dist
+
+    from llm_rs_b200 import DType
+    per = N // world
+    ldt = DType.F32 if out_torch_dtype == torch.float32 else DType.BF16
+    local = torch.empty(M, per, device=dev, dtype=out_torch_dtype)
+    lbuf = be.wrap(local.data_ptr(), [per] if M == 1 else [per, M], ldt, keepalive=local)
+    gathered = torch.empty(world, M, per, device=dev, dtype=out_torch_dtype)
+    be.matmul(lbuf, weight, xbuf)
+    dist.all_gather_into_tensor(gathered.view(-1), local.view(-1))
+    stream.synchronize()
+    ref = gathered.permute(1, 0, 2).reshape(M, N).float()
+    fused.out.zero_()
+    stream.synchronize()
+    dist.barrier()
+    eager = fused(weight, xbuf).clone()
+    stream.synchronize()
+    dist.barrier()
+    res = {}
+    try:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fused(weight, xbuf)
+        fused.out.zero_()
+        stream.synchronize()
+        dist.barrier()
+        g.replay()
+        stream.synchronize()
+        replay = fused.out.clone()
+    except Exception as e:  # noqa: BLE001
+        replay = None
+        res["graph"] = f"not captured: {e!r}"
+    scale = float(ref.abs().max())
+    lim = 2.0 ** -7 if out_torch_dtype == torch.bfloat16 else (2e-4 if M <= 64 else 4e-3)
+    ok = True
+    for name, got in (("eager", eager), ("graph_replay", replay)):
+        if got is None:
+            continue
+        d = (got.float() - ref).abs()
+        res[name] = {"bit_equal": bool(torch.equal(got.float(), ref)), "max_diff_over_max": float(d.max()) / max(scale, 1e-30),
+                     "rel_l2": float(d.norm() / ref.norm().clamp_min(1e-30))}
+        ok = ok and res[name]["max_diff_over_max"] <= lim and bool(torch.isfinite(got.float()).all())
+    res["limit_max_diff_over_max"] = lim
+    res["ok"] = ok
+    t = torch.tensor([0.0 if ok else 1.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)                  # every rank checked its own copy
+    res["ok_all_ranks"] = float(t.item()) == 0.0
+    lbuf.free()
+    return res
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     import torch
     import torch.distributed as dist
@@ -319,9 +388,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         be.sync()
 
         # correctness guard: a sample of rows against the CPU checker would import the oracle,
-        # which only the cpu_baseline leg may do; here just make sure the output is live.
+        # which only the cpu_baseline leg may do; here make sure the output is live, and on several
+        # GPUs hold the fused exchange against matmul + NCCL all-gather on fresh activations.
         final = last["out"]
         assert bool(torch.isfinite(final).all()) and float(final.abs().sum()) > 0.0
+        gather_check = None
+        if fused is not None:
+            x_dev.copy_(torch.from_numpy(synth.activations(M, K_IN, tid=77)).to(dev))
+            gather_check = allgather_check(be, stream, dev, world, fused, weights[0], xbuf, N_OUT, M, torch.float32)
+            x_dev.copy_(torch.from_numpy(x_host).to(dev))
+            stream.synchronize()
 
         multi = None
         if world > 1 and not args.no_extra:
@@ -337,9 +413,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # DRAM bytes of one launch of the headline kernel (dram__bytes_read.sum + dram__bytes_write.sum of
     # the ncu capture summarised under profiles/), scaled by the rows this GPU holds
-    traffic = int(NCU_DRAM_BYTES_PER_LAUNCH * n_local / N_OUT) if M == 1 else None
+    ncu_bytes, ncu_commit = ncu_dram_bytes_per_launch()
+    traffic = int(ncu_bytes * n_local / N_OUT) if (M == 1 and ncu_bytes) else None
 
+    checks_ok = (gather_check is None or gather_check["ok_all_ranks"]) and (multi is None or multi.get("allgather_checks_ok", True))
     if rank != 0:
+        if not checks_ok:
+            sys.exit(3)
         return
     line = {
         "metric": "q6k_gemv_algorithmic_GBps", "value": round(value, 2), "unit": "GB/s",
@@ -358,7 +438,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak_gbs, "unit": "GB/s",
                      "frac": round(achieved / peak_gbs, 4), "traffic": traffic,
                      "kernel": "gemv_kernel (Q6_K, 1 token)", "ms_per_launch": round(ms_kernel, 5),
-                     "peak_kind": f"of {peak_kind}", "bytes_per_launch": alg_local},
+                     "peak_kind": f"of {peak_kind}", "bytes_per_launch": alg_local,
+                     "traffic_source": f"profiles/traffic.json (ncu capture of the kernel at commit {ncu_commit})" if traffic else None},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": int(x_host.nbytes),
                 "d2h_bytes_per_step": int(M * N_OUT * 4), "ms_per_step": round(ms_e2e, 5)},
         "gpu_launches": int(launches),
@@ -368,12 +449,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         gbs, per_s, info = cpu_baseline(Q6K, K_IN, N_OUT, M, budget_s=10.0)
         line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", **info}
         line["cpu_baseline"]["other_configs"] = cpu_baselines_other_configs()
+    if gather_check is not None:
+        line["allgather_check"] = gather_check
     if multi is not None:
         line["extra"] = multi
     if world == 1 and not args.no_extra:
         line["extra"] = extra_measurements(be_factory=lambda: CudaBackend(local_rank, stream=stream.cuda_stream),
                                            stream=stream, peak_gbs=peak_gbs)
     print(json.dumps(line), flush=True)
+    if not checks_ok:
+        print("[bench] the fused all-gather disagrees with matmul + NCCL all-gather: see allgather_check", file=sys.stderr)
+        sys.exit(3)
 
 
 def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
@@ -479,6 +565,18 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
             reps = 10 if M <= 64 else (3 if M <= 512 else 2)
             t, graphed = timed(True, reps)
             t0, _ = timed(False, reps)
+            # the fused exchange against matmul + NCCL all-gather, once per kind of matrix, on other activations
+            checks = {}
+            if fits:
+                xs2 = {K: be.upload_tensor(TensorView("x", DType.BF16, shp(K), synth.bf16_bits(synth.activations(M, K, tid=7000 + K))))
+                       for K in (H, F)}
+                for (dt, K, N) in sorted(fits):
+                    w = wout if N == V else sets[0][[i for i, k in enumerate(layer) if k == (dt, K, N)][0]]
+                    c = allgather_check(be, stream, dev, world, fused[N], w, xs2[K], N, M, torch.bfloat16)
+                    checks[f"{'q4k' if dt == Q4K else 'q6k'}_{K}x{N}"] = c
+                    out["allgather_checks_ok"] = out.get("allgather_checks_ok", True) and c["ok_all_ranks"]
+                for bfr in xs2.values():
+                    bfr.free()
             res[f"m{M}"] = {"ms_per_step": round(t * 1e3, 4), "ms_no_exchange": round(t0 * 1e3, 4),
                             "tok_per_s": round(M / t, 1),
                             "weight_GBps": round(weight_bytes / t / 1e9, 1),
@@ -488,7 +586,7 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
                             "exchange": ("fused peer stores" if fits == kinds else
                                          "fused peer stores where a rank receives <= 256 K values per matmul, NCCL all-gather elsewhere" if fits
                                          else "NCCL all-gather"),
-                            "cuda_graph": graphed}
+                            "cuda_graph": graphed, "allgather_check": checks}
             for bfr in list(xs.values()) + list(lbufs.values()):
                 bfr.free()
             del fused, fulls, locals_
@@ -539,6 +637,7 @@ def extra_measurements(be_factory, stream, peak_gbs):
             return t
 
         for name, dt, K, N, Ms in (("q4k_4096x4096", Q4K, 4096, 4096, (1,)),
+                                   ("q4k_4096x1024", Q4K, 4096, 1024, (1,)),
                                    ("q4k_4096x14336", Q4K, 4096, 14336, (1,)),
                                    ("q6k_14336x4096", Q6K, 14336, 4096, (1,)),
                                    ("q4k_4096x128256", Q4K, 4096, 128256, (1,)),

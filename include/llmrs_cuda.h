@@ -16,6 +16,11 @@
  *   output  shape [N] or [N, M]: element (token s, row r) at s*N + r
  *   1-D buffers carry dim1 = 0; M = max(input.dim1, 1).
  *
+ * Every wait inside a kernel is bounded: after a number of polls it gives up, the kernel finishes,
+ * and the next llmrs_cuda_sync / read_f32 returns LLMRS_ERR_KERNEL; the context stays usable.  The
+ * limits are seconds by default; LLMRS_WAIT_POLLS=n at llmrs_cuda_create sets both poll counts
+ * (16 .. 2^30), which is how the give-up path is tested.
+ *
  * A context owns one device and one stream.  It is not thread-safe (the
  * reference backend is `Send`, never `Sync`: metal/mod.rs:1005-1009); callers
  * serialise.  Operations are enqueued on the context's stream in call order.
@@ -106,8 +111,13 @@ int llmrs_cuda_free(llmrs_ctx *ctx, llmrs_buf *buf);
 
 /* Replaces Backend::matmul (src/backend/mod.rs:29-34; metal/mod.rs:496-687):
  * out[s*N + r] = sum_k W[r,k] * in[s*K + k].  Weight dtype Q4_K or Q6_K; input
- * and output each F32 or BF16 (read from the buffers).  Enqueues only: no
- * synchronisation and no allocation, so it may be captured in a CUDA graph.
+ * and output each F32 or BF16 (read from the buffers).  Enqueues only.  The tensor-core path keeps
+ * converted activations in a scratch buffer of the context, which grows (one cudaMalloc) the first
+ * time a call needs more than any call before it: so there is no allocation once a call of the same
+ * or larger M*K has been made, and a call that is to be captured in a CUDA graph must have been
+ * made once outside capture (inside capture a needed growth fails with LLMRS_ERR_CUDA).  An outgrown
+ * scratch buffer is kept until llmrs_cuda_destroy, so graphs captured earlier stay replayable.  The
+ * same holds for the temporaries of attention, embed and the rms_norm_* calls.
  * Accuracy against the float64 product, as relative L2 error: up to 64 tokens 1e-4 or better (1..4 tokens
  * the decode kernel, exact integer dot products; 5..64 whichever of that kernel and the two-term
  * tensor-core kernel is cheaper for the shape); from 65 tokens 2e-3 (one-term tensor-core kernel, f16
@@ -299,6 +309,16 @@ int llmrs_cuda_sync(llmrs_ctx *ctx);
  * stream, of the work enqueued between synchronisation points. */
 int llmrs_cuda_gpu_secs_total(llmrs_ctx *ctx, double *secs);
 int llmrs_cuda_reset_gpu_secs(llmrs_ctx *ctx);
+
+/* Per-kernel timing table, the counterpart of the reference's LLM_PERF output (metal/mod.rs:150-153,
+ * 323-400, 996-1002).  With LLMRS_PERF=1 in the environment at llmrs_cuda_create every operation is
+ * bracketed by an event pair, and each llmrs_cuda_sync prints one line per kind of operation since the
+ * previous sync to stderr: calls, device time, share, algorithmic GB/s and TFLOP/s, each also as a
+ * fraction of the peaks LLMRS_PEAK_HBM_GBS / LLMRS_PEAK_TFLOPS give (defaults: the nominal 8000 GB/s and
+ * 2250 TFLOP/s of a B200).  This call copies the table of the last sync into buf (NUL-terminated, at
+ * most cap bytes) and returns its full length; 0 when nothing was recorded.  Operations inside a stream
+ * capture are not timed. */
+size_t llmrs_cuda_perf_table(llmrs_ctx *ctx, char *buf, size_t cap);
 
 /* Number of kernels this library has launched on the context since creation. */
 int llmrs_cuda_launch_count(llmrs_ctx *ctx, uint64_t *count);

@@ -119,6 +119,7 @@ ABI = {
     "llmrs_cuda_gpu_secs_total": (C.c_int, [_VP, C.POINTER(C.c_double)]),
     "llmrs_cuda_reset_gpu_secs": (C.c_int, [_VP]),
     "llmrs_cuda_launch_count": (C.c_int, [_VP, _U64P]),
+    "llmrs_cuda_perf_table": (C.c_size_t, [_VP, C.c_char_p, C.c_size_t]),
     "llmrs_cuda_last_error": (C.c_char_p, [_VP]),
     "llmrs_cuda_upload_gguf_tensor": (C.c_int, [_VP, _VP, C.c_char_p, _BUFP]),
     "llmrs_cuda_upload_gguf_tensor_rows": (C.c_int, [_VP, _VP, C.c_char_p, C.c_uint64, C.c_uint64, _BUFP]),
@@ -427,3 +428,13 @@ class CudaBackend:
         self._check(self._lib.llmrs_cuda_launch_count(self._ctx, C.byref(v)))
         return int(v.value)
 
+
+    def perf_table(self) -> str:
+        """The per-kernel table of the last sync (LLMRS_PERF=1 at creation; the reference's LLM_PERF
+        output, src/backend/metal/mod.rs:323-400).  Empty when nothing was recorded."""
+        n = int(self._lib.llmrs_cuda_perf_table(self._ctx, None, 0))
+        if n == 0:
+            return ""
+        buf = C.create_string_buffer(n + 1)
+        self._lib.llmrs_cuda_perf_table(self._ctx, buf, n + 1)
+        return buf.value.decode()

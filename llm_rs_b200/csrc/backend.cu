@@ -62,7 +62,21 @@ struct llmrs_ctx {
     size_t tokens_cap = 0;
     void *split_ws = nullptr;        // workspace of the tensor-core path's split of the last wave (zero between launches)
     uint32_t *dev_error = nullptr;   // device word: first KernelError reported by a kernel; next word: CTA counter
+    uint32_t mbar_polls = DEFAULT_MBAR_POLLS;      // LLMRS_WAIT_POLLS at creation shortens both limits (tests of the
+    uint32_t gather_polls = DEFAULT_GATHER_POLLS;  // give-up path); see ErrSink
+    // Internal buffers that were outgrown.  They are kept until the context is destroyed, because a CUDA
+    // graph captured earlier has their addresses baked in and may still be replayed.
+    std::vector<void *> retired;
+    // LLMRS_PERF=1: one event pair per operation, a table per kernel at every sync (metal/mod.rs:323-400).
+    bool perf = false;
+    double peak_gbs = 8000.0, peak_tflops = 2250.0;   // LLMRS_PEAK_HBM_GBS / LLMRS_PEAK_TFLOPS override the nominal figures
+    struct PerfOp { std::string name; double bytes, flops; cudaEvent_t a, b; };
+    std::vector<PerfOp> perf_ops;
+    std::vector<cudaEvent_t> perf_free;
+    std::string perf_last;           // the table of the last sync
     std::string error;
+
+    ErrSink sink() const { return ErrSink(dev_error, mbar_polls, gather_polls); }
 
     int fail(int code, const char *fmt, ...) {
         char buf[512];
@@ -87,21 +101,32 @@ struct llmrs_ctx {
         if (code == 7) return fail(LLMRS_ERR_ARG, "%s: embed was given a token id beyond the table", what);
         return fail(LLMRS_ERR_KERNEL, "%s: a kernel gave up a bounded wait (code %u); results are incomplete", what, code);
     }
-    // Grows the scratch buffer (synchronises; never called while the stream is being captured).
-    cudaError_t reserve_scratch(size_t bytes) {
-        if (bytes <= scratch_bytes) return cudaSuccess;
+    // Grows one of the context's internal buffers.  Never while the stream is being captured (an
+    // allocation cannot be part of a graph); the outgrown buffer is parked in `retired`, not freed, so
+    // that graphs captured while it was current stay valid.  Sizes at least double, which bounds what
+    // the parked buffers can add up to.
+    cudaError_t grow(void **buf, size_t *have, size_t need) {
+        if (need <= *have) return cudaSuccess;
         cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
         cudaStreamIsCapturing(stream, &st);
         if (st != cudaStreamCaptureStatusNone) return cudaErrorStreamCaptureUnsupported;
-        cudaError_t e = cudaStreamSynchronize(stream);
+        const size_t want = std::max(need, 2 * *have);
+        void *fresh = nullptr;
+        cudaError_t e = cudaMalloc(&fresh, want);
+        if (e != cudaSuccess && want > need) {
+            (void)cudaGetLastError();
+            e = cudaMalloc(&fresh, need);
+            if (e == cudaSuccess) { if (*buf) retired.push_back(*buf); *buf = fresh; *have = need; return e; }
+        }
         if (e != cudaSuccess) return e;
-        if (scratch) cudaFree(scratch);
-        scratch = nullptr;
-        scratch_bytes = 0;
-        e = cudaMalloc(&scratch, bytes);
-        if (e == cudaSuccess) scratch_bytes = bytes;
-        return e;
+        if (*buf) {
+            try { retired.push_back(*buf); } catch (...) { cudaFree(fresh); return cudaErrorMemoryAllocation; }
+        }
+        *buf = fresh;
+        *have = want;
+        return cudaSuccess;
     }
+    cudaError_t reserve_scratch(size_t bytes) { return grow(&scratch, &scratch_bytes, bytes); }
     // Called before enqueueing: opens the timed span the way the reference opens a
     // command buffer lazily on the first dispatch (metal/mod.rs:287-319).
     cudaError_t begin_work() {
@@ -171,6 +196,95 @@ struct DeviceGuard {
     }
 };
 
+// LLMRS_PERF=1: brackets one operation with an event pair.  The reference's LLM_PERF does the same with
+// GPU timestamps per dispatch and prints a per-kernel table with bytes/s and flop/s against the
+// machine's speed of light (metal/mod.rs:150-153,323-400,996-1002).  Nothing is recorded while the
+// stream is being captured.  `bytes` and `flops` are the algorithmic figures of the call.
+struct PerfScope {
+    llmrs_ctx *ctx;
+    cudaEvent_t a = nullptr, b = nullptr;
+    const char *name;
+    double bytes, flops;
+    PerfScope(llmrs_ctx *c, const char *n, double by, double fl) : ctx(c), name(n), bytes(by), flops(fl) {
+        if (!ctx->perf) return;
+        cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(ctx->stream, &st);
+        if (st != cudaStreamCaptureStatusNone) return;
+        for (cudaEvent_t *ev : {&a, &b}) {
+            if (!ctx->perf_free.empty()) { *ev = ctx->perf_free.back(); ctx->perf_free.pop_back(); }
+            else if (cudaEventCreate(ev) != cudaSuccess) { *ev = nullptr; }
+        }
+        if (!a || !b || cudaEventRecord(a, ctx->stream) != cudaSuccess) {
+            if (a) ctx->perf_free.push_back(a);
+            if (b) ctx->perf_free.push_back(b);
+            a = b = nullptr;
+        }
+    }
+    ~PerfScope() {
+        if (!a) return;
+        cudaEventRecord(b, ctx->stream);
+        try { ctx->perf_ops.push_back({name, bytes, flops, a, b}); } catch (...) { cudaEventDestroy(a); cudaEventDestroy(b); }
+    }
+};
+
+const char *dtype_name(uint32_t dt) {
+    switch (dt) {
+        case LLMRS_F32: return "f32";
+        case LLMRS_Q4K: return "q4_k";
+        case LLMRS_Q6K: return "q6_k";
+        case LLMRS_BF16: return "bf16";
+        case LLMRS_I32: return "i32";
+        default: return "?";
+    }
+}
+
+// Algorithmic bytes of a matmul: the weight as stored on disk, the activations in, the results out.
+double matmul_bytes(const llmrs_buf *w, const llmrs_buf *in, const llmrs_buf *out) {
+    size_t wb = 0;
+    storage_size(w->dtype, (uint64_t)w->dim0 * (w->dim1 ? w->dim1 : 1), &wb);
+    return (double)wb + (double)in->dim0 * (in->dim1 ? in->dim1 : 1) * dense_elem_bytes(in->dtype) +
+           (double)out->dim0 * (out->dim1 ? out->dim1 : 1) * dense_elem_bytes(out->dtype);
+}
+double matmul_flops(const llmrs_buf *w, const llmrs_buf *in) {
+    return 2.0 * w->dim0 * (w->dim1 ? w->dim1 : 1) * (in->dim1 ? in->dim1 : 1);
+}
+
+// After a synchronisation point: the operations recorded since the last one, one line per kind, in
+// first-use order; printed to stderr and kept for llmrs_cuda_perf_table.
+void perf_flush(llmrs_ctx *ctx) {
+    if (ctx->perf_ops.empty()) return;
+    struct Row { std::string name; int calls; double ms, bytes, flops; };
+    std::vector<Row> rows;
+    for (auto &op : ctx->perf_ops) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, op.a, op.b) != cudaSuccess) { (void)cudaGetLastError(); ms = 0.f; }
+        ctx->perf_free.push_back(op.a);
+        ctx->perf_free.push_back(op.b);
+        auto it = std::find_if(rows.begin(), rows.end(), [&](const Row &r) { return r.name == op.name; });
+        if (it == rows.end()) rows.push_back({op.name, 1, ms, op.bytes, op.flops});
+        else { it->calls++; it->ms += ms; it->bytes += op.bytes; it->flops += op.flops; }
+    }
+    ctx->perf_ops.clear();
+    double total = 0.0;
+    for (auto &r : rows) total += r.ms;
+    char line[256];
+    std::string t;
+    snprintf(line, sizeof line, "%-34s %6s %10s %6s %9s %6s %9s %6s\n", "kernel", "calls", "us", "share", "GB/s", "of pk",
+             "TFLOP/s", "of pk");
+    t += line;
+    for (auto &r : rows) {
+        const double secs = r.ms * 1e-3, gbs = secs > 0 ? r.bytes / secs * 1e-9 : 0.0, tf = secs > 0 ? r.flops / secs * 1e-12 : 0.0;
+        snprintf(line, sizeof line, "%-34s %6d %10.1f %5.1f%% %9.1f %5.1f%% %9.2f %5.1f%%\n", r.name.c_str(), r.calls, r.ms * 1e3,
+                 total > 0 ? 100.0 * r.ms / total : 0.0, gbs, 100.0 * gbs / ctx->peak_gbs, tf, 100.0 * tf / ctx->peak_tflops);
+        t += line;
+    }
+    snprintf(line, sizeof line, "(peaks: %.0f GB/s, %.0f TFLOP/s; times are per operation, events around each)\n", ctx->peak_gbs,
+             ctx->peak_tflops);
+    t += line;
+    fputs(t.c_str(), stderr);
+    ctx->perf_last = t;
+}
+
 }  // namespace
 
 extern "C" {
@@ -222,6 +336,13 @@ int llmrs_cuda_create(int device, void *stream, llmrs_ctx **out) {
         if (v >= 1 && v <= 64) ctx->upload_readers = v;
     }
     if (const char *env = getenv("LLMRS_GEMM_SPLIT")) ctx->gemm_split = atoi(env) ? 1 : 0;
+    if (const char *env = getenv("LLMRS_WAIT_POLLS")) {
+        const long v = atol(env);
+        if (v >= 16 && v <= (1L << 30)) ctx->mbar_polls = ctx->gather_polls = (uint32_t)v;
+    }
+    if (const char *env = getenv("LLMRS_PERF")) ctx->perf = atoi(env) != 0;
+    if (const char *env = getenv("LLMRS_PEAK_HBM_GBS")) { const double v = atof(env); if (v > 0) ctx->peak_gbs = v; }
+    if (const char *env = getenv("LLMRS_PEAK_TFLOPS")) { const double v = atof(env); if (v > 0) ctx->peak_tflops = v; }
     e = cudaEventCreate(&ctx->ev_begin);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev_end);
     if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->dev_error, 2 * sizeof(uint32_t));
@@ -252,6 +373,9 @@ int llmrs_cuda_destroy(llmrs_ctx *ctx) {
     if (ctx->argmax_out) cudaFree(ctx->argmax_out);
     if (ctx->att_ws) cudaFree(ctx->att_ws);
     if (ctx->norm_tmp) cudaFree(ctx->norm_tmp);
+    for (void *old : ctx->retired) cudaFree(old);
+    for (auto &op : ctx->perf_ops) { cudaEventDestroy(op.a); cudaEventDestroy(op.b); }
+    for (cudaEvent_t ev : ctx->perf_free) cudaEventDestroy(ev);
     for (int i = 0; i < 2; i++) {
         if (ctx->stage_host[i]) cudaFreeHost(ctx->stage_host[i]);
         if (ctx->stage_dev[i]) cudaFree(ctx->stage_dev[i]);
@@ -480,6 +604,11 @@ static bool decode_kernel_cheaper(const llmrs_ctx *ctx, const llmrs_buf *weight,
     return decode < tc;
 }
 
+// The kernel llmrs_cuda_matmul picks for M tokens of this weight: the decode kernel or the tensor cores.
+static bool matmul_uses_decode_kernel(const llmrs_ctx *ctx, const llmrs_buf *weight, uint32_t M, uint32_t K) {
+    return (int)M <= ctx->gemv_max_m || decode_kernel_cheaper(ctx, weight, M, K);
+}
+
 int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input) {
     if (!ctx) return LLMRS_ERR_ARG;
     if (!out || !weight || !input || !out->dptr || !weight->dptr || !input->dptr)
@@ -495,7 +624,7 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
         return ctx->fail(LLMRS_ERR_DTYPE, "matmul: activations must be F32 or BF16 (got %u -> %u)", input->dtype,
                          out->dtype);
     if (K % QK_K) return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u is not a multiple of 256", K);
-    const bool decode = (int)M <= ctx->gemv_max_m || decode_kernel_cheaper(ctx, weight, M, K);
+    const bool decode = matmul_uses_decode_kernel(ctx, weight, M, K);
     if (decode && K > gemv_max_k())
         return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u exceeds the supported maximum %zu", K, gemv_max_k());
     if (input->dim0 != K)
@@ -509,9 +638,14 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: event");
+    char perf_name[48];
+    if (ctx->perf)
+        snprintf(perf_name, sizeof perf_name, "matmul %s %s", dtype_name(weight->dtype),
+                 decode ? "decode kernel" : (M <= (uint32_t)GEMM_TWO_TERM_MAX_TOKENS && ctx->two_term) ? "tensor cores, two-term" : "tensor cores");
+    PerfScope perf(ctx, perf_name, matmul_bytes(weight, input, out), matmul_flops(weight, input));
     if (decode) {
         e = launch_gemv((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
-                        (int)out->dtype, (int)K, (int)N, (int)M, ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream,
+                        (int)out->dtype, (int)K, (int)N, (int)M, ctx->sm_count, ctx->pdl, ctx->sink(), ctx->stream,
                         &ctx->launches, ctx->residual ? ctx->residual->dptr : nullptr,
                         ctx->residual ? (int)ctx->residual->dtype : DT_F32, ctx->norm_w, ctx->norm_eps);
     } else {
@@ -519,7 +653,7 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
         e = ctx->reserve_scratch(gemm_scratch_bytes((int)K, (int)M));
         if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: scratch (grow it with one call outside graph capture)");
         e = launch_gemm((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
-                        (int)out->dtype, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->dev_error,
+                        (int)out->dtype, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->sink(),
                         ctx->stream, &ctx->launches, nullptr, ctx->two_term);
     }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: launch");
@@ -537,6 +671,8 @@ static int elementwise(llmrs_ctx *ctx, const char *name, int op, llmrs_buf *out,
     if (buf_elems(a) != n || (op && buf_elems(b) != n)) return ctx->fail(LLMRS_ERR_SHAPE, "%s: buffers differ in size", name);
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
+    PerfScope perf(ctx, name, (double)n * (dense_elem_bytes(a->dtype) + (op ? dense_elem_bytes(b->dtype) : 0) + dense_elem_bytes(out->dtype)),
+                   (double)n);
     if (e == cudaSuccess)
         e = launch_elementwise(op, a->dptr, (int)a->dtype, op ? b->dptr : nullptr, op ? (int)b->dtype : DT_F32, out->dptr,
                                (int)out->dtype, n, ctx->stream, ctx->pdl);
@@ -565,6 +701,8 @@ int llmrs_cuda_rms_norm(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *input, 
                          out->dim0, out->dim1);
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
+    PerfScope perf(ctx, "rms_norm", (double)dim * rows * (dense_elem_bytes(input->dtype) + dense_elem_bytes(out->dtype)) + 4.0 * dim,
+                   3.0 * dim * rows);
     if (e == cudaSuccess)
         e = launch_rms_norm(input->dptr, (int)input->dtype, (const float *)weight->dptr, out->dptr, (int)out->dtype,
                             (int)dim, (int)rows, eps, ctx->stream, ctx->pdl);
@@ -581,7 +719,10 @@ int llmrs_cuda_argmax(llmrs_ctx *ctx, const llmrs_buf *logits, uint32_t *index) 
     if (n == 0 || n > 0xFFFFFFFFull) return ctx->fail(LLMRS_ERR_SHAPE, "argmax: %zu values", n);
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
-    if (e == cudaSuccess) e = launch_argmax(logits->dptr, (int)logits->dtype, (uint32_t)n, ctx->argmax_out, ctx->stream);
+    {
+        PerfScope perf(ctx, "argmax", (double)n * dense_elem_bytes(logits->dtype), 0.0);
+        if (e == cudaSuccess) e = launch_argmax(logits->dptr, (int)logits->dtype, (uint32_t)n, ctx->argmax_out, ctx->stream);
+    }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "argmax");
     ctx->launches++;
     int rc = llmrs_cuda_sync(ctx);                       // the trait returns the index: the call completes the stream
@@ -600,6 +741,7 @@ int llmrs_cuda_rms_norm_heads(llmrs_ctx *ctx, llmrs_buf *x, const llmrs_buf *wei
     if (dim == 0 || n % dim) return ctx->fail(LLMRS_ERR_SHAPE, "rms_norm_heads: %zu values are not chunks of %zu", n, dim);
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
+    PerfScope perf(ctx, "rms_norm_heads", 2.0 * n * dense_elem_bytes(x->dtype), 3.0 * n);
     if (e == cudaSuccess)
         e = launch_rms_norm(x->dptr, (int)x->dtype, (const float *)weight->dptr, x->dptr, (int)x->dtype, (int)dim,
                             (int)(n / dim), eps, ctx->stream, ctx->pdl);
@@ -621,6 +763,7 @@ int llmrs_cuda_rope(llmrs_ctx *ctx, llmrs_buf *q, llmrs_buf *k, const llmrs_buf 
                          k->dim0, k->dim1, head_dim, buf_elems(positions));
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
+    PerfScope perf(ctx, "rope", 2.0 * (buf_elems(q) * dense_elem_bytes(q->dtype) + buf_elems(k) * dense_elem_bytes(k->dtype)), 0.0);
     if (e == cudaSuccess)
         e = launch_rope(q->dptr, (int)q->dtype, (int)q->dim0, k->dptr, (int)k->dtype, (int)k->dim0,
                         (const uint32_t *)positions->dptr, (int)head_dim, rope_theta, (int)seq, split_half != 0,
@@ -648,6 +791,7 @@ int llmrs_cuda_rope_scatter_kv(llmrs_ctx *ctx, llmrs_buf *q, llmrs_buf *k, const
                          k->dim0, k->dim1, v->dim0, v->dim1, head_dim);
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
+    PerfScope perf(ctx, "rope_scatter_kv", dense_elem_bytes(q->dtype) * (2.0 * buf_elems(q) + 3.0 * buf_elems(k) + 2.0 * buf_elems(v)), 0.0);
     if (e == cudaSuccess)
         e = launch_rope_scatter(q->dptr, (int)q->dim0, k->dptr, v->dptr, (int)k->dim0, (int)q->dtype,
                                 (const uint32_t *)positions->dptr, (const uint32_t *)slot_mapping->dptr, k_pool->dptr,
@@ -670,6 +814,7 @@ int llmrs_cuda_scatter_kv(llmrs_ctx *ctx, llmrs_buf *pool, const llmrs_buf *src,
                          buf_elems(src), buf_elems(slot_mapping));
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
+    PerfScope perf(ctx, "scatter_kv", 2.0 * kv_dim * num_tokens * dense_elem_bytes(src->dtype), 0.0);
     if (e == cudaSuccess)
         e = launch_move_rows(pool->dptr, src->dptr, (const uint32_t *)slot_mapping->dptr, 1,
                              (size_t)kv_dim * dense_elem_bytes(src->dtype), (int)num_tokens, ctx->stream, ctx->pdl);
@@ -690,6 +835,7 @@ int llmrs_cuda_gather(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *src, cons
         return ctx->fail(LLMRS_ERR_SHAPE, "gather: %u columns of %u values into [%u, %u]", num_indices, dim, out->dim0, out->dim1);
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
+    PerfScope perf(ctx, "gather", 2.0 * dim * num_indices * dense_elem_bytes(src->dtype), 0.0);
     if (e == cudaSuccess)
         e = launch_move_rows(out->dptr, src->dptr, (const uint32_t *)indices->dptr, 0,
                              (size_t)dim * dense_elem_bytes(src->dtype), (int)num_indices, ctx->stream, ctx->pdl);
@@ -722,6 +868,7 @@ int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, con
                          buf_elems(q), num_req, buf_elems(query_starts), buf_elems(block_table));
     DeviceGuard guard(ctx->device);
     cudaError_t e;
+    PerfScope perf(ctx, "attention", 2.0 * buf_elems(q) * dense_elem_bytes(q->dtype), 0.0);   // bytes: q and out only (the KV read depends on the lengths, which live on the device)
     if (attention_gqa_supported((int)q->dtype, (int)n_heads, (int)n_kv_heads, (int)head_dim)) {
         // The request lengths live on the device; the host knows the totals.  As many query tokens as requests:
         // a decode batch, split-sequence kernel.  One request: a prefill, tensor-core kernel.  Otherwise the batch
@@ -733,17 +880,10 @@ int llmrs_cuda_attention(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *q, con
         // the workspace is indexed by query token
         const size_t need = attention_workspace_bytes((int)total_q, (int)n_heads, (int)head_dim, splits);
         if (need > ctx->att_ws_bytes) {              // grows outside stream capture only, like the scratch
-            cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
-            cudaStreamIsCapturing(ctx->stream, &st);
-            if (st != cudaStreamCaptureStatusNone)
+            e = ctx->grow((void **)&ctx->att_ws, &ctx->att_ws_bytes, need);
+            if (e == cudaErrorStreamCaptureUnsupported)
                 return ctx->fail(LLMRS_ERR_CUDA, "attention: workspace must grow (make one call outside graph capture)");
-            e = cudaStreamSynchronize(ctx->stream);
-            if (e == cudaSuccess && ctx->att_ws) e = cudaFree(ctx->att_ws);
-            ctx->att_ws = nullptr;
-            ctx->att_ws_bytes = 0;
-            if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->att_ws, need);
             if (e != cudaSuccess) return ctx->cuda_fail(e, "attention: workspace");
-            ctx->att_ws_bytes = need;
         }
         e = ctx->begin_work();
         if (e == cudaSuccess && !decode_only) {
@@ -784,10 +924,29 @@ int llmrs_cuda_matmul_add(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weigh
         return ctx->fail(LLMRS_ERR_SHAPE, "matmul_add: residual is [%u, %u], output [%u, %u]", residual->dim0, residual->dim1,
                          out->dim0, out->dim1);
     const uint32_t M = input && input->dim1 ? input->dim1 : 1;
-    const bool decode = input && weight && (int)M <= ctx->gemv_max_m;
+    const bool quant = weight && (weight->dtype == LLMRS_Q4K || weight->dtype == LLMRS_Q6K);
+    const bool decode = input && quant && matmul_uses_decode_kernel(ctx, weight, M, weight->dim0);
     if (!decode) {                                   // tensor-core path: the matmul, then the add as its own kernel
-        int rc = llmrs_cuda_matmul(ctx, out, weight, input);
-        return rc != LLMRS_OK ? rc : llmrs_cuda_add(ctx, out, out, residual);
+        const uint8_t *r0 = (const uint8_t *)residual->dptr, *o0 = (const uint8_t *)out->dptr;
+        const bool overlap = r0 < o0 + out->nbytes && o0 < r0 + residual->nbytes;
+        if (!overlap || !input || !quant || !out->dptr) {
+            int rc = llmrs_cuda_matmul(ctx, out, weight, input);
+            return rc != LLMRS_OK ? rc : llmrs_cuda_add(ctx, out, out, residual);
+        }
+        // The residual IS the output (x = x + matmul(w, h), the usual call): the product goes to float32
+        // scratch behind the GEMM's own scratch first, because the GEMM would overwrite the residual.
+        const uint32_t K = weight->dim0, N = weight->dim1 ? weight->dim1 : 1;
+        const size_t gemm_bytes = (gemm_scratch_bytes((int)K, (int)M) + 255) / 256 * 256;
+        DeviceGuard guard(ctx->device);
+        cudaError_t e = ctx->reserve_scratch(gemm_bytes + (size_t)M * N * sizeof(float));
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_add: scratch (grow it with one call outside graph capture)");
+        llmrs_buf tmp = *out;
+        tmp.dptr = (uint8_t *)ctx->scratch + gemm_bytes;
+        tmp.nbytes = (size_t)M * N * sizeof(float);
+        tmp.dtype = LLMRS_F32;
+        tmp.owned = 0;
+        int rc = llmrs_cuda_matmul(ctx, &tmp, weight, input);
+        return rc != LLMRS_OK ? rc : llmrs_cuda_add(ctx, out, &tmp, residual);
     }
     ctx->residual = residual;                        // picked up by llmrs_cuda_matmul's decode branch
     int rc = llmrs_cuda_matmul(ctx, out, weight, input);
@@ -813,18 +972,11 @@ static int with_norm(llmrs_ctx *ctx, const char *name, const llmrs_buf *input, c
     const size_t need = (size_t)input->dim0 * (input->dim1 ? input->dim1 : 1) * dense_elem_bytes(input->dtype);
     if (!need) return ctx->fail(LLMRS_ERR_DTYPE, "%s: activations must be F32 or BF16", name);
     if (need > ctx->norm_tmp_bytes) {
-        cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
-        cudaStreamIsCapturing(ctx->stream, &st);
-        if (st != cudaStreamCaptureStatusNone)
-            return ctx->fail(LLMRS_ERR_CUDA, "%s: temporary must grow (make one call outside graph capture)", name);
         DeviceGuard guard(ctx->device);
-        cudaError_t e = cudaStreamSynchronize(ctx->stream);
-        if (e == cudaSuccess && ctx->norm_tmp) e = cudaFree(ctx->norm_tmp);
-        ctx->norm_tmp = nullptr;
-        ctx->norm_tmp_bytes = 0;
-        if (e == cudaSuccess) e = cudaMalloc(&ctx->norm_tmp, need);
+        cudaError_t e = ctx->grow(&ctx->norm_tmp, &ctx->norm_tmp_bytes, need);
+        if (e == cudaErrorStreamCaptureUnsupported)
+            return ctx->fail(LLMRS_ERR_CUDA, "%s: temporary must grow (make one call outside graph capture)", name);
         if (e != cudaSuccess) return ctx->cuda_fail(e, name);
-        ctx->norm_tmp_bytes = need;
     }
     llmrs_buf tmp = *input;
     tmp.dptr = ctx->norm_tmp;
@@ -881,6 +1033,8 @@ int llmrs_cuda_rms_norm_matmul_qkv(llmrs_ctx *ctx, llmrs_buf *out_q, llmrs_buf *
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
     if (e != cudaSuccess) return ctx->cuda_fail(e, "rms_norm_matmul_qkv: event");
+    PerfScope perf(ctx, "rms_norm_matmul_qkv", matmul_bytes(wq, input, out_q) + matmul_bytes(wk, input, out_k) + matmul_bytes(wv, input, out_v) -
+                   2.0 * K * M * dense_elem_bytes(input->dtype), matmul_flops(wq, input) + matmul_flops(wk, input) + matmul_flops(wv, input));
     for (uint32_t dt : {(uint32_t)LLMRS_Q4K, (uint32_t)LLMRS_Q6K}) {
         const uint8_t *gw[3];
         void *go[3];
@@ -894,11 +1048,11 @@ int llmrs_cuda_rms_norm_matmul_qkv(llmrs_ctx *ctx, llmrs_buf *out_q, llmrs_buf *
         if (n == 0) continue;
         if (n == 1)
             e = launch_gemv((int)dt, gw[0], input->dptr, (int)input->dtype, go[0], (int)outs[0]->dtype, (int)K, gn[0], (int)M,
-                            ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream, &ctx->launches, nullptr, DT_F32,
+                            ctx->sm_count, ctx->pdl, ctx->sink(), ctx->stream, &ctx->launches, nullptr, DT_F32,
                             (const float *)norm_weight->dptr, eps);
         else
             e = launch_gemv_multi((int)dt, n, gw, gn, go, input->dptr, (int)input->dtype, (int)outs[0]->dtype, (int)K, (int)M,
-                                  ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream, &ctx->launches,
+                                  ctx->sm_count, ctx->pdl, ctx->sink(), ctx->stream, &ctx->launches,
                                   (const float *)norm_weight->dptr, eps);
         if (e != cudaSuccess) return ctx->cuda_fail(e, "rms_norm_matmul_qkv: launch");
     }
@@ -943,12 +1097,15 @@ int llmrs_cuda_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w
         return ctx->fail(LLMRS_ERR_SHAPE, "matmul_gate_up: in_features %u exceeds the supported maximum %zu", K, gemv_max_k());
     DeviceGuard guard(ctx->device);
     cudaError_t e;
+    PerfScope perf(ctx, w_gate->dtype == LLMRS_Q4K ? "matmul_gate_up q4_k" : "matmul_gate_up q6_k",
+                   2.0 * matmul_bytes(w_gate, input, out) - (double)K * M * dense_elem_bytes(input->dtype) - (double)N * M * dense_elem_bytes(out->dtype),
+                   2.0 * matmul_flops(w_gate, input));
     if (decode && gemv_gate_up_fits((int)w_gate->dtype, (int)K, (int)M)) {
         e = ctx->begin_work();
         if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_gate_up: event");
         e = launch_gemv_gate_up((int)w_gate->dtype, (const uint8_t *)w_gate->dptr, (const uint8_t *)w_up->dptr,
                                 input->dptr, (int)input->dtype, out->dptr, (int)out->dtype, (int)K, (int)N, (int)M,
-                                ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream, &ctx->launches, ctx->norm_w,
+                                ctx->sm_count, ctx->pdl, ctx->sink(), ctx->stream, &ctx->launches, ctx->norm_w,
                                 ctx->norm_eps);
         if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_gate_up: launch");
         return LLMRS_OK;
@@ -967,12 +1124,12 @@ int llmrs_cuda_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w
     for (int i = 0; i < 2 && e == cudaSuccess; i++) {
         if (decode)
             e = launch_gemv((int)ws[i]->dtype, (const uint8_t *)ws[i]->dptr, input->dptr, (int)input->dtype, dst[i],
-                            DT_F32, (int)K, (int)N, (int)M, ctx->sm_count, ctx->pdl, ctx->dev_error, ctx->stream,
+                            DT_F32, (int)K, (int)N, (int)M, ctx->sm_count, ctx->pdl, ctx->sink(), ctx->stream,
                             &ctx->launches);
         else
             e = launch_gemm((int)ws[i]->dtype, (const uint8_t *)ws[i]->dptr, input->dptr, (int)input->dtype, dst[i],
                             DT_F32, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws, ctx->gemm_split,
-                            ctx->dev_error, ctx->stream, &ctx->launches, nullptr, ctx->two_term);
+                            ctx->sink(), ctx->stream, &ctx->launches, nullptr, ctx->two_term);
     }
     if (e == cudaSuccess) {
         e = launch_silu_mul(g, u, out->dptr, (int)out->dtype, (size_t)M * N, ctx->stream);
@@ -1007,21 +1164,16 @@ int llmrs_cuda_embed(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *table, con
     DeviceGuard guard(ctx->device);
     cudaError_t e = cudaSuccess;
     if (n_tokens > ctx->tokens_cap) {            // grows outside stream capture only, like the scratch
-        cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
-        cudaStreamIsCapturing(ctx->stream, &st);
-        if (st != cudaStreamCaptureStatusNone)
+        size_t have = ctx->tokens_cap * sizeof(uint32_t);
+        e = ctx->grow((void **)&ctx->tokens, &have, (size_t)(n_tokens < 256 ? 256 : n_tokens) * sizeof(uint32_t));
+        if (e == cudaErrorStreamCaptureUnsupported)
             return ctx->fail(LLMRS_ERR_CUDA, "embed: token buffer must grow (make one call outside graph capture)");
-        e = cudaStreamSynchronize(ctx->stream);
-        if (e == cudaSuccess && ctx->tokens) e = cudaFree(ctx->tokens);
-        ctx->tokens = nullptr;
-        ctx->tokens_cap = 0;
-        const size_t cap = n_tokens < 256 ? 256 : n_tokens;
-        if (e == cudaSuccess) e = cudaMalloc((void **)&ctx->tokens, cap * sizeof(uint32_t));
         if (e != cudaSuccess) return ctx->cuda_fail(e, "embed: token buffer");
-        ctx->tokens_cap = cap;
+        ctx->tokens_cap = have / sizeof(uint32_t);
     }
     e = ctx->begin_work();
     if (e != cudaSuccess) return ctx->cuda_fail(e, "embed: event");
+    PerfScope perf(ctx, "embed", (double)n_tokens * K * ((table->dtype == LLMRS_Q4K ? 144.0 : 210.0) / 256.0 + dense_elem_bytes(out->dtype)), 0.0);
     e = cudaMemcpyAsync(ctx->tokens, tokens, (size_t)n_tokens * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream);
     if (e == cudaSuccess)
         e = launch_embed((int)table->dtype, (const uint8_t *)table->dptr, (int)K, vocab, ctx->tokens, (int)n_tokens,
@@ -1064,8 +1216,9 @@ int llmrs_cuda_matmul_static_scratch(llmrs_ctx *ctx, llmrs_buf *out, const llmrs
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_static_scratch: event");
+    PerfScope perf(ctx, "matmul_static_scratch", matmul_bytes(weight, input, out), matmul_flops(weight, input));
     e = launch_gemm_static_scratch((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype,
-                                   out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, ctx->device, ctx->dev_error,
+                                   out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, ctx->device, ctx->sink(),
                                    ctx->stream, &ctx->launches, ctx->two_term);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_static_scratch: launch");
     return LLMRS_OK;
@@ -1106,18 +1259,19 @@ int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf 
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: event");
+    PerfScope perf(ctx, "matmul_allgather", matmul_bytes(weight_shard, input, out), matmul_flops(weight_shard, input));
     if (decode) {
         e = launch_gemv_allgather((int)weight_shard->dtype, (const uint8_t *)weight_shard->dptr, input->dptr,
                                   (int)input->dtype, out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, (int)rank,
                                   (int)world, peer_mailbox, ctx->dev_error + 1, step_word, ctx->sm_count, ctx->pdl,
-                                  ctx->dev_error, ctx->stream, &ctx->launches);
+                                  ctx->sink(), ctx->stream, &ctx->launches);
     } else {
         e = ctx->reserve_scratch(gemm_scratch_bytes((int)K, (int)M));
         if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: scratch (grow it with one call outside graph capture)");
         const GemmGather gg{(int)world, (int)rank, peer_mailbox, ctx->dev_error + 1, step_word};
         e = launch_gemm((int)weight_shard->dtype, (const uint8_t *)weight_shard->dptr, input->dptr, (int)input->dtype,
                         out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws,
-                        ctx->gemm_split, ctx->dev_error, ctx->stream, &ctx->launches, &gg, ctx->two_term);
+                        ctx->gemm_split, ctx->sink(), ctx->stream, &ctx->launches, &gg, ctx->two_term);
     }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: launch");
     return LLMRS_OK;
@@ -1153,6 +1307,9 @@ int llmrs_cuda_sync(llmrs_ctx *ctx) {
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->finish_work();
     if (e != cudaSuccess) return ctx->cuda_fail(e, "sync");
+    if (ctx->perf) {
+        try { perf_flush(ctx); } catch (...) { ctx->perf_ops.clear(); }
+    }
     return ctx->check_kernel_error("sync");
 }
 
@@ -1192,6 +1349,17 @@ int llmrs_cuda_reset_gpu_secs(llmrs_ctx *ctx) {
     if (!ctx) return LLMRS_ERR_ARG;
     ctx->gpu_secs = 0.0;
     return LLMRS_OK;
+}
+
+size_t llmrs_cuda_perf_table(llmrs_ctx *ctx, char *buf, size_t cap) {
+    if (!ctx) return 0;
+    const size_t n = ctx->perf_last.size();
+    if (buf && cap) {
+        const size_t k = n < cap - 1 ? n : cap - 1;
+        memcpy(buf, ctx->perf_last.data(), k);
+        buf[k] = 0;
+    }
+    return n;
 }
 
 int llmrs_cuda_launch_count(llmrs_ctx *ctx, uint64_t *count) {

@@ -61,6 +61,7 @@ struct GemmParams {
     const uint8_t *W;
     void *Out;
     uint32_t *err;
+    uint32_t wait_limit, gather_limit;   // polls before an mbarrier (or partial-sum) wait / a mailbox wait is abandoned
     int K, N, M;
     int out_bf16;
     int sm_count;
@@ -615,7 +616,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                 else if (has_next) nxt = load_raw<QT>(next_row_ptr, nb, un.b0, g);
                 const uint32_t it = unit_it + 2u * (uint32_t)(b - u.b0) + (uint32_t)g;   // stage number over all units
                 const uint32_t s = it % S;
-                if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1)) {
+                if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
                     report_error(p.err, KERR_EMPTY_WAIT);
                     ok = false;
                     break;
@@ -655,7 +656,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                 const int t0 = (u.tile / w_tiles) * TN;
                 for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
                     const uint32_t s = it % S;
-                    if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1)) {
+                    if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
                         report_error(p.err, KERR_EMPTY_WAIT);
                         ok = false;
                         break;
@@ -690,7 +691,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
             for (; ok && ui.next(sc, u); tcount++) {
                 const uint32_t ab = tcount % AB;
                 // the epilogue must have read this accumulator out (unit tcount - AB) before it is overwritten
-                if (tcount >= (uint32_t)AB && !mbar_wait(&acc_empty[ab], ((tcount / AB) - 1) & 1)) {
+                if (tcount >= (uint32_t)AB && !mbar_wait(&acc_empty[ab], ((tcount / AB) - 1) & 1, p.wait_limit)) {
                     report_error(p.err, KERR_MMA_WAIT);
                     break;
                 }
@@ -698,7 +699,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                 const uint32_t d_tmem = tmem_base + ab * C::ACC_COLS;
                 for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
                     const uint32_t s = it % S;
-                    if (!mbar_wait(&full[s], (it / S) & 1)) {
+                    if (!mbar_wait(&full[s], (it / S) & 1, p.wait_limit)) {
                         report_error(p.err, KERR_FULL_WAIT);
                         ok = false;
                         break;
@@ -754,7 +755,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
             // this tile's token factors (per warp copy, so no cross-warp barrier)
             for (int c = lane; c < TN; c += 32) scale_s[c] = (t0 + c < p.M) ? __ldg(p.tok_scale + t0 + c) : 0.0f;
             __syncwarp();
-            if (!mbar_wait(&acc_full[ab], (tcount / AB) & 1)) {
+            if (!mbar_wait(&acc_full[ab], (tcount / AB) & 1, p.wait_limit)) {
                 report_error(p.err, KERR_MMA_WAIT);
                 dead = true;
             }
@@ -782,7 +783,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                 if (combine) {
                     if (ew == 0 && lane == 0) {                  // every other piece has a ticket: wait for their deposits
                         bool seen = false;
-                        for (uint32_t i = 0; i < WAIT_LIMIT && !seen; i++) {
+                        for (uint32_t i = 0; i < p.wait_limit && !seen; i++) {
                             uint32_t n;
                             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(n) : "l"(p.ws_counters + 2 * tt + 1) : "memory");
                             seen = n + 1 >= pieces;
@@ -908,10 +909,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                                 for (int dd = 0; dd < p.world; dd++) {
                                     if (dd == p.rank) continue;
                                     uint2 *box = p.peer_box[dd] + word;
-                                    for (int j = 0; j < nv; j += 2)
-                                        asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(box + j),
-                                                     "r"(__float_as_uint(f[j])), "r"(gather_step),
-                                                     "r"(__float_as_uint(f[j + 1])), "r"(gather_step) : "memory");
+                                    for (int j = 0; j < nv; j++) mailbox_store(box + j, __float_as_uint(f[j]), gather_step);
                                 }
                             }
                         }
@@ -934,8 +932,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                                                     ((size_t)p.rank * p.M + tok) * p.N + (row - p.row_offset);
                                 for (int dd = 0; dd < p.world; dd++)
                                     if (dd != p.rank)
-                                        asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(p.peer_box[dd] + word),
-                                                     "r"(__float_as_uint(fv)), "r"(gather_step) : "memory");
+                                        mailbox_store(p.peer_box[dd] + word, __float_as_uint(fv), gather_step);
                             }
                         }
                     }
@@ -986,7 +983,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                     const int src = q < p.rank ? q : q + 1;
                     const int tok = (int)(rem / p.N), row = (int)(rem - (size_t)tok * p.N);
                     if (got[b].y != gather_step &&
-                        !mailbox_wait(box + (size_t)src * per_src + rem, gather_step, 1u << 25, got[b])) {
+                        !mailbox_wait(box + (size_t)src * per_src + rem, gather_step, p.gather_limit, got[b])) {
                         report_error(p.err, KERR_GATHER_WAIT);
                         late = true;
                         continue;
@@ -1157,7 +1154,7 @@ size_t gemm_split_workspace_bytes(int sms) {
 }
 
 cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                        int K, int N, int M, void *scratch, void *split_ws, int split_mode, uint32_t *err_word,
+                        int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
                         cudaStream_t s, uint64_t *launches, const GemmGather *gather, bool two_term) {
     if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
     if (!scratch) return cudaErrorInvalidValue;
@@ -1170,7 +1167,7 @@ cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype
     if (e != cudaSuccess) return e;
     if (launches) (*launches)++;
     GemmParams p{};
-    p.W = w; p.Out = out; p.err = err_word; p.K = K; p.N = N; p.M = M; p.out_bf16 = out_dtype == DT_BF16;
+    p.W = w; p.Out = out; p.err = err_word.word; p.wait_limit = err_word.mbar_polls; p.gather_limit = err_word.gather_polls; p.K = K; p.N = N; p.M = M; p.out_bf16 = out_dtype == DT_BF16;
     p.tok_scale = tok_scale;
     p.split = split_mode;          // launch_tn turns the mode into the decision
     p.n_total = N;
@@ -1232,7 +1229,7 @@ static cudaError_t static_scratch_address(int device, void **out) {
 }
 
 cudaError_t launch_gemm_static_scratch(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out,
-                                       int out_dtype, int K, int N, int M, int device, uint32_t *err_word,
+                                       int out_dtype, int K, int N, int M, int device, ErrSink err_word,
                                        cudaStream_t s, uint64_t *launches, bool two_term) {
     if (gemm_scratch_bytes(K, M) > STATIC_SCRATCH_BYTES) return cudaErrorInvalidValue;
     void *scratch = nullptr;

@@ -31,10 +31,6 @@
 
 namespace llmrs {
 
-#ifdef LLMRS_TUNING
-unsigned long long *g_gather_trace = nullptr;   // tuning builds: where the exchange stamps go
-#endif
-
 namespace {
 
 // A pipeline stage holds CHUNK_BLOCKS = 16 consecutive blocks of each row of the tile; a slice is
@@ -47,7 +43,6 @@ namespace {
 // one-tile matrix (4096x4096), where arithmetic could start on the first quarter of K, took
 // 7.1 us against 4.6 us.
 constexpr int MAX_STAGES = 8;
-constexpr uint32_t GATHER_WAIT_LIMIT = 1u << 25;       // polls (64 ns apart) before a peer is given up on
 
 // Activations become integers of 8*PLANES bits (two's complement, one byte plane each; the top
 // plane is signed).  |X| <= 2^XBITS keeps the integer dot product of a group inside int32.
@@ -80,8 +75,9 @@ template <int PLANES> struct Fmt<1, PLANES> {          // Q6_K, slice-major chun
 // Fused all-gather of the output slices of an N-sharded matmul (world == 0: not used).
 // Rank r owns rows [row_offset, row_offset + N) of an n_total-row output.  A result travels to
 // the other ranks as ONE 8-byte store {value as float bits, call number} into a mailbox in the
-// peer's memory (plain peer stores over NVLink, no TMA, no multicast).  An 8-byte aligned store
-// arrives whole, so the call number doubles as the "this value has landed" flag and no fence is
+// peer's memory (plain peer stores over NVLink, no TMA, no multicast).  The word is written and read
+// as one 64-bit relaxed system-scope access (mailbox_store / mailbox_load), which is a single access in
+// the memory model, so the call number doubles as the "this value has landed" flag and no fence is
 // needed anywhere: a system-scope fence was measured at 5-7 us on this machine, two of them
 // per matmul in an earlier store-then-flag version of this exchange.  When a CTA has finished
 // its rows, its threads take a share of the mailbox words addressed to this rank, poll each until
@@ -127,32 +123,14 @@ struct GemvParams {
     const void *X;
     void *Out;
     uint32_t *err;
+    uint32_t wait_limit, gather_limit;   // polls before an mbarrier wait / a mailbox wait is abandoned
     int K, N, m_valid;
     int x_bf16, out_bf16;
     size_t row_stride;      // bytes between weight rows
     int n_row_tiles, n_chunks;
     int stages;             // depth of the weight ring (<= MAX_STAGES)
     int pdl;                // host: launch with programmatic stream serialization (see the kernel)
-#ifdef LLMRS_TUNING
-    unsigned long long *trace;   // [grid][4] nanosecond stamps: start, activations staged, first chunk landed, end
-#endif
 };
-
-#ifdef LLMRS_TUNING
-__device__ __forceinline__ void trace_stamp(const GemvParams &p, int slot) {
-    if (p.trace) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        p.trace[4 * blockIdx.x + slot] = t;
-    }
-}
-#define LLMRS_TRACE(slot) trace_stamp(p, slot)
-// stamps of the CTA that runs the exchange: behind the per-CTA slots of up to 148 CTAs
-#define LLMRS_GTRACE(k) do { if (p.trace) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.trace[4 * 148 + (k)] = t_; } } while (0)
-#else
-#define LLMRS_GTRACE(k)
-#define LLMRS_TRACE(slot)
-#endif
 
 __device__ __forceinline__ float load_x(const void *x, size_t idx, int is_bf16) {
     return is_bf16 ? bf16_bits_to_f32(__ldg((const uint16_t *)x + idx)) : __ldg((const float *)x + idx);
@@ -520,6 +498,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
     using F = Fmt<QT, PLANES>;
     constexpr int RT = R * NCW;
     __shared__ float norm_red[NCW][4];
+    __shared__ uint64_t consumers_done;                  // every consumer warp arrives here when it has finished
+    __shared__ int gave_up;                              // a bounded wait ran out somewhere in this CTA
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + MAX_STAGES;
@@ -532,11 +512,12 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) {
-        LLMRS_TRACE(0);
         for (int s = 0; s < S; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], NCW);
         }
+        mbar_init(&consumers_done, NCW);
+        gave_up = 0;
         mbar_init_fence();
     }
     __syncthreads();
@@ -552,12 +533,16 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
     if (warp == NCW) {
         // ---------------- producer ----------------
         uint32_t it = 0;
-        for (int rt = blockIdx.x; rt < p.n_row_tiles; rt += gridDim.x) {
+        bool stop = false;
+        for (int rt = blockIdx.x; rt < p.n_row_tiles && !stop; rt += gridDim.x) {
             for (int c = 0; c < p.n_chunks; c++, it++) {
                 const int s = it % S;
-                if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1)) {
+                if (*(volatile int *)&gave_up) { stop = true; break; }
+                if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
                     report_error(p.err, KERR_EMPTY_WAIT);
-                    return;
+                    *(volatile int *)&gave_up = 1;
+                    stop = true;
+                    break;
                 }
                 const int nbc = min(F::CHUNK_BLOCKS, nb - c * F::CHUNK_BLOCKS);
                 const uint32_t bytes = (uint32_t)((nbc * F::BLOCK + 15) / 16 * 16);
@@ -577,6 +562,15 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                 }
             }
         }
+        // The producer leaves last.  In the normal course every copy has been consumed by then.  After an
+        // abandoned wait, copies of up to S stages may still be in flight towards this CTA's shared
+        // memory; the CTA must not end (and hand the memory to another CTA) before they have landed, so
+        // the producer waits, again with a limit, for the full barrier of each stage it armed last.
+        mbar_wait(&consumers_done, 0, p.wait_limit);
+        if (*(volatile int *)&gave_up) {
+            const uint32_t first = it > (uint32_t)S ? it - (uint32_t)S : 0u;
+            for (uint32_t j = first; j < it; j++) mbar_wait(&full[j % S], (j / S) & 1, p.wait_limit);
+        }
         return;
     }
 
@@ -586,7 +580,6 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
     const uint32_t gather_step = p.g.world > 0 ? *reinterpret_cast<volatile uint32_t *>(p.g.step_word) + 1u : 0u;
     stage_activations<QT, PLANES>(xarea, xtok_bytes, p, threadIdx.x, NCW * 32, norm_red);
     named_barrier_sync(1, NCW * 32);
-    if (threadIdx.x == 0) LLMRS_TRACE(1);
     float inv_rms[MT];                                   // the tokens' norm factors, applied to the finished sums
 #pragma unroll
     for (int t = 0; t < MT; t++) {
@@ -610,12 +603,12 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
 
         for (int c = 0; c < p.n_chunks; c++, it++) {
             const int s = it % S;
-            if (!mbar_wait(&full[s], (it / S) & 1)) {
+            if (!mbar_wait(&full[s], (it / S) & 1, p.wait_limit)) {
                 report_error(p.err, KERR_FULL_WAIT);
+                *(volatile int *)&gave_up = 1;
                 ok = false;
                 break;
             }
-            if (threadIdx.x == 0 && it == 0) LLMRS_TRACE(2);
             const int nbc = min(F::CHUNK_BLOCKS, nb - c * F::CHUNK_BLOCKS);
             const uint8_t *row[R];
 #pragma unroll
@@ -686,16 +679,14 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                     } else if (lane < p.g.world) {        // lane d posts the value to rank d's mailbox
                         uint2 *box = p.g.peer_box[lane] + (gather_step & 1u) * p.g.half_words +
                                      ((size_t)p.g.rank * p.m_valid + t) * p.N + out_row;
-                        asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(box), "r"(__float_as_uint(v)), "r"(gather_step) : "memory");
+                        mailbox_store(box, __float_as_uint(v), gather_step);
                     }
                 }
             }
     }
 
-    if (threadIdx.x == 0) LLMRS_TRACE(3);
     if (p.g.world > 1) {
         // ---- collect the other ranks' slices from this rank's mailbox ----
-        if (threadIdx.x == 0) LLMRS_GTRACE(0);
         const uint2 *box = p.g.peer_box[p.g.rank] + (gather_step & 1u) * p.g.half_words;
         const int per_src = p.m_valid * p.N;                             // words one sender posts
         const int remote = (p.g.world - 1) * per_src;
@@ -722,7 +713,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                 const int src = q < p.g.rank ? q : q + 1;
                 const int t = rem / p.N, row = rem - t * p.N;
                 if (got[b].y != gather_step &&
-                    !mailbox_wait(box + (size_t)src * per_src + rem, gather_step, GATHER_WAIT_LIMIT, got[b])) {
+                    !mailbox_wait(box + (size_t)src * per_src + rem, gather_step, p.gather_limit, got[b])) {
                     report_error(p.err, KERR_GATHER_WAIT);
                     late = true;
                     continue;
@@ -730,7 +721,6 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                 store_out(p.Out, (size_t)t * p.g.n_total + (size_t)src * p.N + row, __uint_as_float(got[b].x), p.out_bf16);
             }
         }
-        if (threadIdx.x == 0) LLMRS_GTRACE(1);
     }
     if (p.g.world > 0) {
         // the last CTA to get here advances the call number for the next launch; every CTA read it long ago
@@ -743,6 +733,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
             }
         }
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&consumers_done);         // lets the producer warp, and with it the CTA, end
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -858,7 +850,7 @@ size_t gemv_max_k() {
 }
 
 cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                        int K, int N, int M, int sm_count, bool pdl, uint32_t *err_word, cudaStream_t s,
+                        int K, int N, int M, int sm_count, bool pdl, ErrSink err_word, cudaStream_t s,
                         uint64_t *launches, const void *residual, int residual_dtype, const float *norm_weight,
                         float norm_eps) {
     if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
@@ -868,7 +860,7 @@ cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype
     p.norm_eps = norm_eps;
     p.Residual = residual;
     p.res_bf16 = residual_dtype == DT_BF16;
-    p.W = w; p.X = x; p.Out = out; p.err = err_word;
+    p.W = w; p.X = x; p.Out = out; p.err = err_word.word; p.wait_limit = err_word.mbar_polls; p.gather_limit = err_word.gather_polls;
     p.K = K; p.N = N;
     p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;
     const int xe = x_dtype == DT_BF16 ? 2 : 4, oe = out_dtype == DT_BF16 ? 2 : 4;
@@ -887,14 +879,14 @@ cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype
 // one token pass: M <= 4 and M <= gemv_single_launch_max_tokens.  out[i] is [M, n_rows[i]].
 cudaError_t launch_gemv_multi(int wdtype, int n, const uint8_t *const *ws, const int *n_rows, void *const *outs,
                               const void *x, int x_dtype, int out_dtype, int K, int M, int sm_count, bool pdl,
-                              uint32_t *err_word, cudaStream_t s, uint64_t *launches, const float *norm_weight,
+                              ErrSink err_word, cudaStream_t s, uint64_t *launches, const float *norm_weight,
                               float norm_eps) {
     if (n < 2 || n > 3 || K <= 0 || M <= 0 || M > 4 || M > gemv_single_launch_max_tokens(wdtype, K)) return cudaErrorInvalidValue;
     GemvParams p{};
     p.pdl = pdl;
     p.NormW = norm_weight;
     p.norm_eps = norm_eps;
-    p.X = x; p.err = err_word; p.K = K;
+    p.X = x; p.err = err_word.word; p.wait_limit = err_word.mbar_polls; p.gather_limit = err_word.gather_polls; p.K = K;
     p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;
     p.n_segs = n;
     int first = 0;
@@ -943,14 +935,14 @@ bool gemv_gate_up_fits(int wdtype, int K, int M) {
 
 cudaError_t launch_gemv_gate_up(int wdtype, const uint8_t *w_gate, const uint8_t *w_up, const void *x, int x_dtype,
                                 void *out, int out_dtype, int K, int N, int M, int sm_count, bool pdl,
-                                uint32_t *err_word, cudaStream_t s, uint64_t *launches, const float *norm_weight,
+                                ErrSink err_word, cudaStream_t s, uint64_t *launches, const float *norm_weight,
                                 float norm_eps) {
     if (!gemv_gate_up_fits(wdtype, K, M)) return cudaErrorInvalidConfiguration;
     GemvParams p{};
     p.pdl = pdl;
     p.NormW = norm_weight;
     p.norm_eps = norm_eps;
-    p.W = w_gate; p.W2 = w_up; p.X = x; p.Out = out; p.err = err_word;
+    p.W = w_gate; p.W2 = w_up; p.X = x; p.Out = out; p.err = err_word.word; p.wait_limit = err_word.mbar_polls; p.gather_limit = err_word.gather_polls;
     p.K = K; p.N = N;
     p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;
     uint64_t n = 0;
@@ -994,20 +986,17 @@ size_t gemv_allgather_mailbox_bytes(int n_total, int M) { return (size_t)2 * M *
 cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                                   int K, int N_local, int M, int rank, int world, void *const *peer_mailbox,
                                   uint32_t *done_counter, uint32_t *step_word, int sm_count, bool pdl,
-                                  uint32_t *err_word, cudaStream_t s, uint64_t *launches) {
+                                  ErrSink err_word, cudaStream_t s, uint64_t *launches) {
     if (K <= 0 || N_local <= 0 || M <= 0 || M > 4 || world < 1 || world > MAX_GATHER_RANKS) return cudaErrorInvalidValue;
     if (M > gemv_single_launch_max_tokens(wdtype, K)) return cudaErrorInvalidValue;   // token passes would each post
     GemvParams p{};
     p.pdl = pdl;
-    p.W = w; p.X = x; p.Out = out; p.err = err_word;
+    p.W = w; p.X = x; p.Out = out; p.err = err_word.word; p.wait_limit = err_word.mbar_polls; p.gather_limit = err_word.gather_polls;
     p.K = K; p.N = N_local;
     p.x_bf16 = x_dtype == DT_BF16; p.out_bf16 = out_dtype == DT_BF16;
     p.g.world = world; p.g.rank = rank; p.g.n_total = N_local * world; p.g.row_offset = rank * N_local;
     p.g.done_counter = done_counter; p.g.step_word = step_word;
     p.g.half_words = (size_t)world * M * N_local;
-#ifdef LLMRS_TUNING
-    p.trace = g_gather_trace;
-#endif
     for (int d = 0; d < world; d++) p.g.peer_box[d] = (uint2 *)peer_mailbox[d];
     uint64_t n = 0;
     cudaError_t e;
@@ -1025,37 +1014,5 @@ cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, i
     if (launches) *launches += n;
     return e;
 }
-
-#ifdef LLMRS_TUNING
-// Tuning hook (only in builds made with -DLLMRS_TUNING): launch one explicit configuration.
-namespace {
-template <int QT, int MT>
-cudaError_t tune_dispatch(const GemvParams &p, int sm, int R, int ncw, int planes, int stages, cudaStream_t s) {
-#define LLMRS_TRY(RR, WW, PP) \
-    if (R == RR && ncw == WW && planes == PP) return launch_cfg<QT, MT, RR, WW, PP>(p, sm, stages, s);
-    LLMRS_TRY(1, 8, 3) LLMRS_TRY(2, 8, 3) LLMRS_TRY(4, 8, 3) LLMRS_TRY(1, 8, 2) LLMRS_TRY(2, 8, 2) LLMRS_TRY(4, 8, 2)
-    LLMRS_TRY(1, 16, 3) LLMRS_TRY(2, 16, 3) LLMRS_TRY(1, 16, 2) LLMRS_TRY(2, 16, 2)
-    LLMRS_TRY(1, 12, 3) LLMRS_TRY(2, 12, 3) LLMRS_TRY(1, 12, 2) LLMRS_TRY(2, 12, 2)
-#undef LLMRS_TRY
-
-    return cudaErrorInvalidValue;
-}
-}  // namespace
-cudaError_t tune_gemv(int wdtype, const uint8_t *w, const void *x, void *out, int K, int N, int M, int sm_count,
-                      uint32_t *err, int R, int ncw, int planes, int stages, cudaStream_t s,
-                      unsigned long long *trace) {
-    GemvParams p{};
-    p.W = w; p.X = x; p.Out = out; p.err = err; p.K = K; p.N = N; p.m_valid = M;
-    p.trace = trace;
-    if (wdtype == DT_Q4K) {
-        p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
-        return M == 1 ? tune_dispatch<0, 1>(p, sm_count, R, ncw, planes, stages, s)
-                      : tune_dispatch<0, 2>(p, sm_count, R, ncw, planes, stages, s);
-    }
-    p.row_stride = q6k_row_stride(K);
-    return M == 1 ? tune_dispatch<1, 1>(p, sm_count, R, ncw, planes, stages, s)
-                  : tune_dispatch<1, 2>(p, sm_count, R, ncw, planes, stages, s);
-}
-#endif
 
 }  // namespace llmrs

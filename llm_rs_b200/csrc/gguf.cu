@@ -12,6 +12,7 @@
 #include <cerrno>
 #include <cstdio>
 #include <cstring>
+#include <new>
 #include <thread>
 
 #include "../../include/llmrs_cuda.h"
@@ -22,6 +23,7 @@ namespace {
 constexpr uint32_t GGUF_MAGIC = 0x46554747u;      // "GGUF" read as a little-endian u32
 constexpr uint64_t GGUF_ALIGNMENT = 32;
 constexpr size_t PREAD_PIECE = 4u << 20;
+constexpr uint64_t MAX_DIRECTORY_BYTES = 1ull << 30;   // no honest directory is longer; bounds host memory on a corrupt file
 
 // Thrown by the cursor when the bytes read so far end inside the directory: the caller reads more.
 struct NeedMore {};
@@ -32,9 +34,11 @@ struct Cursor {
     const uint8_t *buf;
     size_t len, pos = 0;
     bool whole_file;                               // nothing more to read: running out is an error
+    uint64_t file_size;                            // a length that reaches beyond the file is a lie, not a short read
     void need(uint64_t n) const {
         if (n > len - pos) {
-            if (whole_file) throw ParseError{"file ends inside the GGUF directory"};
+            if (whole_file || n > file_size - std::min<uint64_t>(file_size, pos))
+                throw ParseError{"file ends inside the GGUF directory"};
             throw NeedMore{};
         }
     }
@@ -137,7 +141,7 @@ void read_value(Cursor &c, GgufValue &v) {
 
 // Parses buf[0, len) into g.  Throws NeedMore when the directory continues beyond len.
 void parse(GgufFile &g, const uint8_t *buf, size_t len, bool whole_file) {
-    Cursor c{buf, len, 0, whole_file};
+    Cursor c{buf, len, 0, whole_file, g.file_size};
     const uint32_t magic = c.get<uint32_t>();
     if (magic != GGUF_MAGIC) {
         char m[48];
@@ -223,13 +227,12 @@ const GgufTensor *GgufFile::find_tensor(const char *name) const {
     return nullptr;
 }
 
-GgufFile *gguf_open(const char *path, std::string *error) {
-    GgufFile *g = new GgufFile();
+// The file is untrusted input and this runs below a C ABI: nothing may be thrown out of it.
+static GgufFile *gguf_open_impl(const char *path, std::string *error, GgufFile *g) {
     g->fd = open(path, O_RDONLY | O_CLOEXEC);
     struct stat st;
     if (g->fd < 0 || fstat(g->fd, &st) != 0) {
         *error = std::string("IO error: ") + path + ": " + strerror(errno);
-        delete g;
         return nullptr;
     }
     g->file_size = (uint64_t)st.st_size;
@@ -241,17 +244,19 @@ GgufFile *gguf_open(const char *path, std::string *error) {
         g->header.resize(want);
         if (!pread_all(g->fd, g->header.data() + have, want - have, have)) {
             *error = std::string("IO error: reading ") + path + ": " + strerror(errno);
-            delete g;
             return nullptr;
         }
         try {
             parse(*g, g->header.data(), want, want == g->file_size);
             break;
         } catch (const NeedMore &) {
-            want = (size_t)std::min<uint64_t>(g->file_size, (uint64_t)want * 4);
+            if (want >= MAX_DIRECTORY_BYTES) {
+                *error = "GGUF directory longer than 1 GiB";
+                return nullptr;
+            }
+            want = (size_t)std::min<uint64_t>(std::min<uint64_t>(g->file_size, MAX_DIRECTORY_BYTES), (uint64_t)want * 4);
         } catch (const ParseError &e) {
             *error = e.what;
-            delete g;
             return nullptr;
         }
     }
@@ -260,10 +265,27 @@ GgufFile *gguf_open(const char *path, std::string *error) {
     for (const GgufTensor &t : g->tensors)
         if (t.offset > g->file_size || t.nbytes > g->file_size - t.offset || g->data_offset > g->file_size - t.offset - t.nbytes) {
             *error = "tensor " + t.name + " lies outside the file";
-            delete g;
             return nullptr;
         }
     return g;
+}
+
+GgufFile *gguf_open(const char *path, std::string *error) {
+    GgufFile *g = new (std::nothrow) GgufFile();
+    if (!g) {
+        *error = "IO error: out of host memory";
+        return nullptr;
+    }
+    GgufFile *ok = nullptr;
+    try {
+        ok = gguf_open_impl(path, error, g);
+    } catch (const std::bad_alloc &) {
+        try { *error = "IO error: out of host memory while reading the GGUF directory"; } catch (...) {}
+    } catch (...) {                                // length_error and the like: a directory no host can hold
+        try { *error = "malformed GGUF directory"; } catch (...) {}
+    }
+    if (!ok) delete g;
+    return ok;
 }
 
 bool gguf_pread_parallel(int fd, void *dst, uint64_t offset, size_t len, int threads) {
@@ -314,11 +336,15 @@ const char *llmrs_gguf_last_error(void) { return g_gguf_error.c_str(); }
 
 int llmrs_gguf_open(const char *path, llmrs_gguf **out) {
     if (!path || !out) return gguf_fail(LLMRS_ERR_ARG, "gguf_open: null pointer");
-    std::string err;
-    llmrs::GgufFile *g = llmrs::gguf_open(path, &err);
-    if (!g) return gguf_fail(err.rfind("IO error", 0) == 0 ? LLMRS_ERR_IO : LLMRS_ERR_FORMAT, err);
-    *out = static_cast<llmrs_gguf *>(g);
-    return LLMRS_OK;
+    try {
+        std::string err;
+        llmrs::GgufFile *g = llmrs::gguf_open(path, &err);
+        if (!g) return gguf_fail(err.rfind("IO error", 0) == 0 ? LLMRS_ERR_IO : LLMRS_ERR_FORMAT, err);
+        *out = static_cast<llmrs_gguf *>(g);
+        return LLMRS_OK;
+    } catch (...) {
+        return LLMRS_ERR_IO;
+    }
 }
 
 void llmrs_gguf_close(llmrs_gguf *g) { delete static_cast<llmrs::GgufFile *>(g); }

@@ -10,6 +10,21 @@ constexpr int QK_K = 256;            // weights per K-quant block (src/tensor/mo
 constexpr int Q4K_BLOCK_BYTES = 144; // src/tensor/mod.rs:71
 constexpr int Q6K_BLOCK_BYTES = 210; // src/tensor/mod.rs:73
 
+// Where a kernel reports an abandoned wait, and how long its waits may last.  Every wait inside a
+// kernel (on an mbarrier, on a peer's mailbox word, on another CTA's partial sums) gives up after a
+// number of polls, writes a KernelError to `word` (first error wins) and lets the kernel finish, so
+// that the context stays usable and the host learns of it at its next synchronisation point.  The
+// defaults are seconds; a context may shorten them (LLMRS_WAIT_POLLS), which is how the give-up path
+// is tested without hanging anything.
+constexpr uint32_t DEFAULT_MBAR_POLLS = 1u << 22;      // mbarrier.try_wait polls (each blocks ~1 us in hardware)
+constexpr uint32_t DEFAULT_GATHER_POLLS = 1u << 25;    // mailbox polls, 32 ns apart
+struct ErrSink {
+    uint32_t *word;
+    uint32_t mbar_polls, gather_polls;
+    ErrSink(uint32_t *w = nullptr, uint32_t m = DEFAULT_MBAR_POLLS, uint32_t g = DEFAULT_GATHER_POLLS)
+        : word(w), mbar_polls(m), gather_polls(g) {}
+};
+
 // GGUF dtype ids (src/tensor/mod.rs:3-33); same values as enum llmrs_dtype.
 constexpr int DT_F32 = 0, DT_Q4K = 12, DT_Q6K = 14, DT_BF16 = 30;
 
@@ -94,8 +109,8 @@ cudaError_t launch_attention(const void *q, const void *k_pool, const void *v_po
                              int block_size, int max_blocks_per_seq, cudaStream_t s, bool pdl);
 
 // Decode matmul: integer dot products per scale group, float32 across groups; any M (tokens are
-// processed in passes of <= 4).  x_dtype / out_dtype are DT_F32 or DT_BF16.  err_word is a device
-// word that receives a KernelError if a bounded wait inside the kernel gives up.  *launches is
+// processed in passes of <= 4).  x_dtype / out_dtype are DT_F32 or DT_BF16.  err_word names the device
+// word that receives a KernelError if a bounded wait inside the kernel gives up, and the poll limits.  *launches is
 // incremented per kernel launched.  pdl: launch with programmatic stream serialization, so that
 // the kernel's prologue and weight fetch overlap the tail of the kernel before it in the stream
 // (requires that no kernel still in flight writes the weights).  residual (optional, [M, N] of
@@ -103,7 +118,7 @@ cudaError_t launch_attention(const void *q, const void *k_pool, const void *v_po
 // token passes each add their part.  norm_weight (optional, float32 [K]): the activations are RMS-normalised
 // (rsqrt(mean(x^2) + norm_eps) * norm_weight) as they are staged, so rms_norm + matmul is one kernel.
 cudaError_t launch_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                        int K, int N, int M, int sm_count, bool pdl, uint32_t *err_word, cudaStream_t s,
+                        int K, int N, int M, int sm_count, bool pdl, ErrSink err_word, cudaStream_t s,
                         uint64_t *launches, const void *residual = nullptr, int residual_dtype = DT_F32,
                         const float *norm_weight = nullptr, float norm_eps = 0.0f);
 
@@ -117,7 +132,7 @@ size_t gemv_allgather_mailbox_bytes(int n_total, int M);
 cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                                   int K, int N_local, int M, int rank, int world, void *const *peer_mailbox,
                                   uint32_t *done_counter, uint32_t *step_word, int sm_count, bool pdl,
-                                  uint32_t *err_word, cudaStream_t s, uint64_t *launches);
+                                  ErrSink err_word, cudaStream_t s, uint64_t *launches);
 
 // Fused feed-forward front on the decode kernel: out[M, N] = silu(X . Wgate^T) * (X . Wup^T) in one
 // launch (both weights [K, N], same type, as uploaded).  gemv_gate_up_fits() says whether the shape
@@ -125,7 +140,7 @@ cudaError_t launch_gemv_allgather(int wdtype, const uint8_t *w, const void *x, i
 bool gemv_gate_up_fits(int wdtype, int K, int M);
 cudaError_t launch_gemv_gate_up(int wdtype, const uint8_t *w_gate, const uint8_t *w_up, const void *x, int x_dtype,
                                 void *out, int out_dtype, int K, int N, int M, int sm_count, bool pdl,
-                                uint32_t *err_word, cudaStream_t s, uint64_t *launches,
+                                ErrSink err_word, cudaStream_t s, uint64_t *launches,
                                 const float *norm_weight = nullptr, float norm_eps = 0.0f);
 // out[i] = silu(gate[i]) * up[i] over n float32 values, written as out_dtype (the unfused tail).
 cudaError_t launch_silu_mul(const float *gate, const float *up, void *out, int out_dtype, size_t n, cudaStream_t s);
@@ -141,7 +156,7 @@ int gemv_single_launch_max_tokens(int wdtype, int K);
 // M <= gemv_single_launch_max_tokens; norm_weight as in launch_gemv.
 cudaError_t launch_gemv_multi(int wdtype, int n, const uint8_t *const *ws, const int *n_rows, void *const *outs,
                               const void *x, int x_dtype, int out_dtype, int K, int M, int sm_count, bool pdl,
-                              uint32_t *err_word, cudaStream_t s, uint64_t *launches, const float *norm_weight,
+                              ErrSink err_word, cudaStream_t s, uint64_t *launches, const float *norm_weight,
                               float norm_eps);
 
 // Prefill matmul on the tensor cores (tcgen05, f16 operands, fp32 accumulate in TMEM); M >= 1.
@@ -168,7 +183,7 @@ size_t gemm_scratch_bytes(int K, int M);
 size_t gemm_split_workspace_bytes(int sms);
 size_t gemm_split_counter_bytes();      // the leading bytes of the workspace that must be zero
 cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                        int K, int N, int M, void *scratch, void *split_ws, int split_mode, uint32_t *err_word,
+                        int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
                         cudaStream_t s, uint64_t *launches, const GemmGather *gather = nullptr, bool two_term = false);
 
 // The same GEMM with its scratch in a fixed 8 MiB device array that is part of the library image:
@@ -177,7 +192,7 @@ cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype
 // exceeds gemm_static_scratch_capacity().
 size_t gemm_static_scratch_capacity();
 cudaError_t launch_gemm_static_scratch(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out,
-                                       int out_dtype, int K, int N, int M, int device, uint32_t *err_word,
+                                       int out_dtype, int K, int N, int M, int device, ErrSink err_word,
                                        cudaStream_t s, uint64_t *launches, bool two_term = false);
 
 }  // namespace llmrs

@@ -46,10 +46,10 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t by
                  : "memory");
 }
 
-// true when the phase with the given parity has completed; false after WAIT_LIMIT polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+// true when the phase with the given parity has completed; false after `limit` polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = WAIT_LIMIT) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+    for (uint32_t i = 0; i < limit; i++) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -91,12 +91,19 @@ __device__ __forceinline__ void report_error(uint32_t *err_word, uint32_t code) 
     if (err_word) atomicCAS(err_word, 0u, code);
 }
 
-// Mailbox word {value, tag} of the fused all-gather: one relaxed system-scope 8-byte load (the
-// writer is another GPU; an aligned 8-byte store arrives whole).
+// Mailbox word {value, tag} of the fused all-gather, written by one GPU and polled by another.  The
+// pair travels as ONE 64-bit scalar access on both sides (value in the low half, tag in the high
+// half): a relaxed system-scope 64-bit store and a relaxed system-scope 64-bit load are each single
+// accesses in the memory model, so a reader that sees the tag sees the value that was stored with
+// it.  (A vector store of two 32-bit words would be two accesses whose order is unspecified.)
+__device__ __forceinline__ void mailbox_store(uint2 *w, uint32_t value_bits, uint32_t tag) {
+    const unsigned long long word = ((unsigned long long)tag << 32) | (unsigned long long)value_bits;
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(w), "l"(word) : "memory");
+}
 __device__ __forceinline__ uint2 mailbox_load(const uint2 *w) {
-    uint2 r;
-    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(w) : "memory");
-    return r;
+    unsigned long long word;
+    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(word) : "l"(w) : "memory");
+    return make_uint2((uint32_t)word, (uint32_t)(word >> 32));
 }
 // Polls until the word carries `tag`; false after `limit` polls 32 ns apart.
 __device__ __forceinline__ bool mailbox_wait(const uint2 *w, uint32_t tag, uint32_t limit, uint2 &out) {

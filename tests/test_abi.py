@@ -53,3 +53,25 @@ def test_product_does_not_import_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in src.lower(), f"{f} mentions the oracle"
+
+
+def test_integration_rust_binding_is_consistent():
+    """The Rust text of INTEGRATION.md cannot be compiled here, so it is held to what can be checked by
+    reading: every llmrs_* function a Rust block calls is declared in an `extern "C"` block of the page
+    (in a code block or in the prose that says what to add), and every declared name exists in the header."""
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    blocks = re.findall(r"```rust\n(.*?)```", text, flags=re.S)
+    assert blocks, "no Rust blocks found"
+    declared = set(re.findall(r"\bfn\s+(llmrs_(?:cuda|gguf)_\w+)\s*\(", text))
+    called = set()
+    for b in blocks:
+        for name in re.findall(r"\b(llmrs_(?:cuda|gguf)_\w+)\s*\(", b):
+            called.add(name)
+    header = set(declared_symbols())
+    assert called <= declared, f"called in the Rust text but never declared extern: {sorted(called - declared)}"
+    assert declared <= header, f"declared extern in INTEGRATION.md but not in the header: {sorted(declared - header)}"
+    # the Rust struct derives only Clone and Copy: nothing may ask it for a Default
+    assert "LlmrsBuf::default()" not in text
+    # the build step compiles every kernel file of the package
+    csrc = os.path.join(ROOT, "llm_rs_b200", "csrc")
+    assert "read_dir(\"cuda/csrc\")" in text and all(f.endswith((".cu", ".cuh", ".h")) for f in os.listdir(csrc))

@@ -154,6 +154,7 @@ def test_directory_longer_than_the_first_read(G, tmp_path):
     ("mtype", -8, "unknown metadata type: 13"), ("atype", -8, "unknown metadata type: 9"), ("utf8", -8, "invalid UTF-8 in string"),
     ("truncated", -8, "file ends inside the GGUF directory"), ("outside", -8, "lies outside the file"),
     ("blocks", -8, "not divisible by block size 256"), ("missing", -7, "IO error"), ("empty", -8, "file ends inside"),
+    ("biglen", -8, "file ends inside the GGUF directory"), ("bigcount", -8, "file ends inside the GGUF directory"),
 ])
 def test_native_errors(G, tmp_path, case, code, text):
     good = OG.build([("k", 8, "v", None)], [("t", [256], 12, bytes(144))])
@@ -168,6 +169,10 @@ def test_native_errors(G, tmp_path, case, code, text):
         "utf8": head + struct.pack("<IQ", 8, 2) + b"\xff\xfe" + bytes(32),
         "truncated": good[:40], "outside": tinfo([256], 12, 0) + bytes(100), "blocks": tinfo([255], 12, 0) + bytes(256),
         "empty": b"",
+        # lengths that reach beyond the file, in a file longer than the first prefix read: an error at once,
+        # not a reason to read the rest of the file
+        "biglen": head + struct.pack("<IQ", 8, 1 << 40) + bytes(3 << 20),
+        "bigcount": head + struct.pack("<IIQ", 9, 4, 1 << 61) + bytes(3 << 20),
     }
     path = str(tmp_path / "nope.gguf") if case == "missing" else write(tmp_path, case + ".gguf", bufs[case])
     with pytest.raises(G.GgufError) as e:
