@@ -68,8 +68,10 @@ def test_config3_feed_forward_gemms_fewer_tokens(backend, M):
         x = synth.activations(M, K, tid=63 + M)
         y = _run(backend, wbuf, x, K, N, M)
         _check_sampled(y, dt, w, K, N, x, M, seed=80 + M, n_runs=32)               # 4096 rows x all tokens
+        # power-of-two token scaling: the same tensor-core products, so twice the result up to the order
+        # in which the K pieces of a split tile are added (which CTA arrives last differs run to run)
         y2 = _run(backend, wbuf, np.float32(2.0) * x, K, N, M)
-        assert np.array_equal(y2, np.float32(2.0) * y)           # power-of-two token scaling: exact
+        assert O.rel_l2(y2, 2.0 * y.astype(np.float64)) <= 1e-6
 
 
 @pytest.mark.parametrize("dt,K,N", [(O.Q4K, 8192, 1024), (O.Q4K, 8192, 8192), (O.Q6K, 28672, 8192), (O.Q4K, 8192, 28672)])
