@@ -38,6 +38,8 @@ struct llmrs_ctx {
     int gemv_max_m = 4;              // M <= this: exact decode kernel (1e-4 class); above: tensor-core GEMM
     bool cost_rule = true;           // up to 64 tokens the decode kernel also runs where it is the cheaper one;
                                      // an explicit LLMRS_GEMV_MAX_M makes the boundary hard
+    bool exact = true;               // up to 64 tokens the tensor-core path runs the exact-integer-operand kernel
+                                     // (gemm_exact.cu); LLMRS_TC_EXACT=0: the older two-term kernel of gemm_tc.cu
     bool two_term = true;            // tensor-core GEMM up to 64 tokens carries hi + lo f16 terms (1e-4 class);
                                      // LLMRS_TC_TWO_TERM=0: one term (2e-3 class, about half the time)
     void *scratch = nullptr;         // f16 copy of the activations for the tensor-core path
@@ -327,6 +329,7 @@ int llmrs_cuda_create(int device, void *stream, llmrs_ctx **out) {
     }
     if (const char *env = getenv("LLMRS_NO_PDL")) ctx->pdl = atoi(env) == 0;
     if (const char *env = getenv("LLMRS_TC_TWO_TERM")) ctx->two_term = atoi(env) != 0;
+    if (const char *env = getenv("LLMRS_TC_EXACT")) ctx->exact = atoi(env) != 0;
     if (const char *env = getenv("LLMRS_UPLOAD_PIECE_MB")) {
         const int v = atoi(env);
         if (v >= 1 && v <= 1024) ctx->upload_piece = (size_t)v << 20;
@@ -583,6 +586,23 @@ int llmrs_cuda_write(llmrs_ctx *ctx, llmrs_buf *dst, const void *host, size_t nb
     return LLMRS_OK;
 }
 
+// The tensor-core path: which kernel serves M tokens, how much scratch it needs, and its launch.
+static bool uses_exact_kernel(const llmrs_ctx *ctx, uint32_t M) {
+    return ctx->two_term && ctx->exact && M <= (uint32_t)GEMM_EXACT_MAX_TOKENS;
+}
+static size_t tc_scratch_bytes(const llmrs_ctx *ctx, uint32_t K, uint32_t M) {
+    return uses_exact_kernel(ctx, M) ? gemm_exact_scratch_bytes((int)K, (int)M) : gemm_scratch_bytes((int)K, (int)M);
+}
+static cudaError_t tc_matmul(llmrs_ctx *ctx, uint32_t wdtype, const void *w, const void *x, uint32_t x_dtype, void *out,
+                             uint32_t out_dtype, uint32_t K, uint32_t N, uint32_t M, const GemmGather *gather = nullptr) {
+    if (uses_exact_kernel(ctx, M))
+        return launch_gemm_exact((int)wdtype, (const uint8_t *)w, x, (int)x_dtype, out, (int)out_dtype, (int)K, (int)N, (int)M,
+                                 ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->sink(), ctx->stream, &ctx->launches, gather);
+    return launch_gemm((int)wdtype, (const uint8_t *)w, x, (int)x_dtype, out, (int)out_dtype, (int)K, (int)N, (int)M,
+                       ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->sink(), ctx->stream, &ctx->launches, gather,
+                       ctx->two_term);
+}
+
 // Between the decode kernel's token limit and 64 tokens both kernels meet the decode tolerance, so
 // the cheaper one runs.  The decode kernel streams the weights once per pass of up to four tokens
 // (fewer where the staged activations of four do not fit): about 2 us + 0.2 us per MB and token,
@@ -641,7 +661,8 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
     char perf_name[48];
     if (ctx->perf)
         snprintf(perf_name, sizeof perf_name, "matmul %s %s", dtype_name(weight->dtype),
-                 decode ? "decode kernel" : (M <= (uint32_t)GEMM_TWO_TERM_MAX_TOKENS && ctx->two_term) ? "tensor cores, two-term" : "tensor cores");
+                 decode ? "decode kernel" : uses_exact_kernel(ctx, M) ? "tensor cores, exact" :
+                 (M <= (uint32_t)GEMM_TWO_TERM_MAX_TOKENS && ctx->two_term) ? "tensor cores, two-term" : "tensor cores");
     PerfScope perf(ctx, perf_name, matmul_bytes(weight, input, out), matmul_flops(weight, input));
     if (decode) {
         e = launch_gemv((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
@@ -650,11 +671,9 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
                         ctx->residual ? (int)ctx->residual->dtype : DT_F32, ctx->norm_w, ctx->norm_eps);
     } else {
         // The reference switches to its tiled GEMM kernels by seq_len too (metal/mod.rs:542-633).
-        e = ctx->reserve_scratch(gemm_scratch_bytes((int)K, (int)M));
+        e = ctx->reserve_scratch(tc_scratch_bytes(ctx, K, M));
         if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: scratch (grow it with one call outside graph capture)");
-        e = launch_gemm((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
-                        (int)out->dtype, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->sink(),
-                        ctx->stream, &ctx->launches, nullptr, ctx->two_term);
+        e = tc_matmul(ctx, weight->dtype, weight->dptr, input->dptr, input->dtype, out->dptr, out->dtype, K, N, M);
     }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: launch");
     return LLMRS_OK;
@@ -936,7 +955,7 @@ int llmrs_cuda_matmul_add(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weigh
         // The residual IS the output (x = x + matmul(w, h), the usual call): the product goes to float32
         // scratch behind the GEMM's own scratch first, because the GEMM would overwrite the residual.
         const uint32_t K = weight->dim0, N = weight->dim1 ? weight->dim1 : 1;
-        const size_t gemm_bytes = (gemm_scratch_bytes((int)K, (int)M) + 255) / 256 * 256;
+        const size_t gemm_bytes = (tc_scratch_bytes(ctx, K, M) + 255) / 256 * 256;
         DeviceGuard guard(ctx->device);
         cudaError_t e = ctx->reserve_scratch(gemm_bytes + (size_t)M * N * sizeof(float));
         if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_add: scratch (grow it with one call outside graph capture)");
@@ -1112,7 +1131,7 @@ int llmrs_cuda_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w
     }
     if (ctx->norm_w) return ctx->fail(LLMRS_ERR_SHAPE, "matmul_gate_up: the fused norm needs the one-launch path");
     // Two matmuls into float32 scratch behind the GEMM's own scratch, then the element-wise tail.
-    const size_t gemm_bytes = decode ? 0 : (gemm_scratch_bytes((int)K, (int)M) + 255) / 256 * 256;
+    const size_t gemm_bytes = decode ? 0 : (tc_scratch_bytes(ctx, K, M) + 255) / 256 * 256;
     const size_t half = ((size_t)M * N * sizeof(float) + 255) / 256 * 256;
     e = ctx->reserve_scratch(gemm_bytes + 2 * half);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_gate_up: scratch (grow it with one call outside graph capture)");
@@ -1127,9 +1146,7 @@ int llmrs_cuda_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w
                             DT_F32, (int)K, (int)N, (int)M, ctx->sm_count, ctx->pdl, ctx->sink(), ctx->stream,
                             &ctx->launches);
         else
-            e = launch_gemm((int)ws[i]->dtype, (const uint8_t *)ws[i]->dptr, input->dptr, (int)input->dtype, dst[i],
-                            DT_F32, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws, ctx->gemm_split,
-                            ctx->sink(), ctx->stream, &ctx->launches, nullptr, ctx->two_term);
+            e = tc_matmul(ctx, ws[i]->dtype, ws[i]->dptr, input->dptr, input->dtype, dst[i], LLMRS_F32, K, N, M);
     }
     if (e == cudaSuccess) {
         e = launch_silu_mul(g, u, out->dptr, (int)out->dtype, (size_t)M * N, ctx->stream);
@@ -1207,7 +1224,7 @@ int llmrs_cuda_matmul_static_scratch(llmrs_ctx *ctx, llmrs_buf *out, const llmrs
     if (weight->device != (uint32_t)ctx->device || input->device != (uint32_t)ctx->device ||
         out->device != (uint32_t)ctx->device)
         return ctx->fail(LLMRS_ERR_ARG, "matmul_static_scratch: buffers belong to another device");
-    const size_t need = gemm_scratch_bytes((int)K, (int)M), have = gemm_static_scratch_capacity();
+    const size_t need = tc_scratch_bytes(ctx, K, M), have = gemm_static_scratch_capacity();
     if (need > have)
         return ctx->fail(LLMRS_ERR_SHAPE,
                          "matmul_static_scratch: %u tokens x %u features need %zu bytes of scratch, the built-in "
@@ -1219,7 +1236,7 @@ int llmrs_cuda_matmul_static_scratch(llmrs_ctx *ctx, llmrs_buf *out, const llmrs
     PerfScope perf(ctx, "matmul_static_scratch", matmul_bytes(weight, input, out), matmul_flops(weight, input));
     e = launch_gemm_static_scratch((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype,
                                    out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, ctx->device, ctx->sink(),
-                                   ctx->stream, &ctx->launches, ctx->two_term);
+                                   ctx->stream, &ctx->launches, ctx->two_term, uses_exact_kernel(ctx, M));
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_static_scratch: launch");
     return LLMRS_OK;
 }
@@ -1266,12 +1283,10 @@ int llmrs_cuda_matmul_allgather(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf 
                                   (int)world, peer_mailbox, ctx->dev_error + 1, step_word, ctx->sm_count, ctx->pdl,
                                   ctx->sink(), ctx->stream, &ctx->launches);
     } else {
-        e = ctx->reserve_scratch(gemm_scratch_bytes((int)K, (int)M));
+        e = ctx->reserve_scratch(tc_scratch_bytes(ctx, K, M));
         if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: scratch (grow it with one call outside graph capture)");
         const GemmGather gg{(int)world, (int)rank, peer_mailbox, ctx->dev_error + 1, step_word};
-        e = launch_gemm((int)weight_shard->dtype, (const uint8_t *)weight_shard->dptr, input->dptr, (int)input->dtype,
-                        out->dptr, (int)out->dtype, (int)K, (int)N, (int)M, ctx->scratch, ctx->split_ws,
-                        ctx->gemm_split, ctx->sink(), ctx->stream, &ctx->launches, &gg, ctx->two_term);
+        e = tc_matmul(ctx, weight_shard->dtype, weight_shard->dptr, input->dptr, input->dtype, out->dptr, out->dtype, K, N, M, &gg);
     }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_allgather: launch");
     return LLMRS_OK;

@@ -1,0 +1,985 @@
+// Small-batch matmul (5 .. 64 tokens) for Q4_K / Q6_K weights on the 5th-generation tensor cores of
+// sm_100a, to the tolerance of the decode kernel (1e-4 relative L2; measured ~1e-6).
+//
+//   Out[M, N] = X[M, K] . W[N, K]^T        (src/backend/mod.rs:29-34)
+//
+// Replaces gemm_q4k / gemm_q4k_pipe / gemm_q6k of the reference at these token counts
+// (shaders/ops.metal:357-424, 456-558, 560-621).  The idea: keep every factor that the block format
+// makes an INTEGER exact in f16, let the tensor core multiply and add those, and apply the one
+// factor that is a real number, the block's d, in float32 outside it.
+//
+//   Q4_K (tests/ops.rs:41-59):  w = d * (sc * q) - dmin * m         sc, m < 64, q < 16
+//        A operand = sc * q          (<= 945: exact in f16's 11-bit significand)
+//        per 256-weight block b:  acc_b[r, t] = sum_k (sc q)[r, k] * x[t, k]     (tensor core, fp32)
+//        out[r, t] = sum_b d[r, b] * acc_b[r, t]  -  sum_{b, sb} (dmin * m)[r, b, sb] * xsum[t, b, sb]
+//        The second sum is a small matmul of its own (K / 32 columns): dmin * m is split exactly into
+//        two f16 values and rides through the tensor core into a second accumulator.
+//   Q6_K (shaders/ops.metal:28-42, 322-334):  w = d * (sc * (q - 32))     sc int8, q < 64
+//        sc * (q - 32) has up to 13 bits: A_hi = RN_f16(sc (q - 32)), A_lo = the rounding error
+//        (-1, 0 or 1, exact); both go through the tensor core.
+//
+// Activations are x = x_hi + x_lo, two f16 values (to 2^-22 of the token's largest magnitude), so a
+// K step is two (Q4_K) or three (Q6_K: A_lo x_lo is below 2^-22) products.  Nothing is rounded to
+// f16 that is not exact there, except x itself at 2^-22.
+//
+// Pipeline of one CTA (persistent, one per SM, 15 warps):
+//   warp 14     one lane copies the raw blocks of 128 weight rows into a shared-memory ring with tiled
+//               TMA copies (cp.async.bulk.tensor.2d on the weight matrix seen as a 2-D byte tensor; no
+//               multicast): one 144-byte box per row for Q4_K (rows 144 bytes apart in shared memory,
+//               so the 16-byte reads of consecutive rows fall into distinct banks), boxes of 48 / 16
+//               bytes per row for the slices, scales and d of Q6_K's slice-major layout.
+//   warps 0-7   read their row's bytes from the ring (thread = weight row), build the f16 operand and
+//               store it into TENSOR MEMORY (tcgen05.st); two groups of four warps alternate the two
+//               128-weight halves of every block.
+//   warp 8      one lane issues the TMA copies of the stage's activation tiles (x_hi, x_lo and, for
+//               Q4_K, the per-sub-block sums), 128-byte swizzle.
+//   warp 9      allocates TMEM; one lane issues tcgen05.mma (kind::f16, A from TMEM, B from shared
+//               memory, fp32 accumulators in TMEM) and the commits.
+//   warps 10-13 read the block accumulator out of TMEM after every block (tcgen05.ld), multiply by
+//               d[r, b] and add into float32 registers; at the end of a unit they subtract the
+//               minimum term, scale by the token factor and write the results (transposed through
+//               shared memory: the output is token-major).
+// Work is cut as in the prefill kernel (umma.cuh: Sched): tiles of 128 rows x TN tokens; matrices with
+// fewer tiles than SMs are cut along K over all SMs, partial sums meeting in a workspace.
+// Every wait is bounded; a wait that gives up reports a KernelError and the CTA still releases its
+// TMEM before it exits.
+#include <cuda.h>
+
+#include "kernels.h"
+#include "llmrs_common.cuh"
+#include "pipeline.cuh"
+#include "tensor_map.h"
+#include "umma.cuh"
+
+namespace llmrs {
+
+namespace {
+
+constexpr int XQ_WARPS = DEQ_WARPS + 2 + EPI_WARPS + 1;      // 15
+constexpr int XQ_THREADS = XQ_WARPS * 32;
+constexpr int RAW_WARP = DEQ_WARPS + 2 + EPI_WARPS;          // 14
+constexpr int D_RING = 4;                                     // blocks whose d values are kept for the epilogue
+constexpr int XS_SLOTS = 64;                                  // f16 slots per block in the sub-block sum tensor
+
+template <int QT, int TN> struct ExactCfg {
+    static constexpr bool MIN = QT == 0;                      // Q4_K carries a minimum term
+    // Activation tiles of a stage (128 K elements), each TN tokens x 64 f16 with 128-byte swizzled rows.  The
+    // x_hi tile of a 64-wide K slice is followed directly by its x_lo tile, so that ONE tensor-core
+    // instruction with N = 2 TN columns forms both products of a K step: columns 0..TN-1 of the
+    // accumulator take A x_hi, columns TN..2TN-1 take A x_lo.  Q4_K: the sub-block sums (hi tile, lo tile)
+    // of the block come with its first stage.
+    static constexpr int SUBTILE_BYTES = TN * BK * 2;
+    static constexpr int STAGE_SUBTILES = MIN ? 6 : 4;
+    static constexpr int STAGE_BYTES = SUBTILE_BYTES * STAGE_SUBTILES;
+    static constexpr uint32_t A_TERM_COLS = 64;               // 128 K elements of one term (Q6_K: hi, then lo)
+    static constexpr uint32_t A_MAIN_COLS = QT == 0 ? 64 : 128;
+    static constexpr uint32_t A_MIN_COLS = MIN ? 8 : 0;       // 16 K slots of the minimum term
+    static constexpr uint32_t A_STAGE_COLS = A_MAIN_COLS + A_MIN_COLS;
+    static constexpr uint32_t ACC_BUF_COLS = 2 * TN;          // one block accumulator: A x_hi | A x_lo
+    static constexpr uint32_t ACC_COLS = 2 * ACC_BUF_COLS;    // two buffers
+    static constexpr uint32_t MACC_COLS = MIN ? TN : 0;       // minimum-term accumulator of the unit (one buffer)
+    static constexpr uint32_t A_BASE_COL = ACC_COLS + MACC_COLS;
+    static constexpr int TMEM_STAGES = (512 - (int)A_BASE_COL) / (int)A_STAGE_COLS;
+    static constexpr int STAGES = TMEM_STAGES < 4 ? TMEM_STAGES : 4;
+    static_assert(STAGES >= 2, "at least a double buffer");
+    // raw ring: one slot = the bytes of one 256-weight block of 128 rows
+    static constexpr int Q6_SLICE_BOX = TILE_ROWS * 48;       // one of the four 48-byte slices of a block, all rows
+    static constexpr int Q6_SMALL_BOX = TILE_ROWS * 16;       // scales of the block / the 16-byte window holding its d
+    static constexpr int RAW_SLOT_BYTES = QT == 0 ? TILE_ROWS * Q4K_BLOCK_BYTES : 4 * Q6_SLICE_BOX + 2 * Q6_SMALL_BOX;
+    static constexpr size_t EPI_BYTES = (size_t)EPI_WARPS * (EPI_TOK * 32 * 4) + (size_t)EPI_WARPS * TN_PAD * 4;
+    static constexpr size_t FIXED = 1024 /* alignment slack */ + (size_t)STAGES * STAGE_BYTES + 512 /* barriers */ +
+                                    (size_t)D_RING * TILE_ROWS * 4 + EPI_BYTES;
+    static constexpr int RAW_FIT = (int)((227 * 1024 - FIXED) / RAW_SLOT_BYTES);
+    static constexpr int RAW_SLOTS = RAW_FIT < 4 ? RAW_FIT : 4;
+    static_assert(RAW_SLOTS >= 2, "the raw ring needs two slots");
+    static constexpr size_t SMEM = FIXED + (size_t)RAW_SLOTS * RAW_SLOT_BYTES;
+    static constexpr uint32_t TMEM_COLS = 512;
+    static_assert(A_BASE_COL + STAGES * A_STAGE_COLS <= 512, "tensor memory budget");
+};
+
+struct ExactMaps {
+    CUtensorMap x;       // [2M rows][K] f16: x_hi rows 0..M-1, x_lo rows M..2M-1; box 64 x TN, 128-byte swizzle
+    CUtensorMap xs;      // Q4_K: [2M rows][nb * 64] f16 sub-block sums (hi rows, then lo rows); same box
+    CUtensorMap w_a;     // weights as bytes [N rows][row stride]: box 144 x 128 (Q4_K) / 48 x 128 (Q6_K)
+    CUtensorMap w_b;     // Q6_K: box 16 x 128
+};
+
+__device__ __forceinline__ uint4 lds128(const uint8_t *p) { return *reinterpret_cast<const uint4 *>(p); }
+
+// registers -> 32 lanes x 8 consecutive 32-bit TMEM columns
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
+constexpr uint32_t H2_M1024 = 0xE400E400u;    // (-1024.0, -1024.0)
+constexpr uint32_t H2_2M4 = 0x2C002C00u;      // (2^-4, 2^-4)
+constexpr uint32_t IDESC_NEG_A = 1u << 13;    // instruction descriptor: negate the A operand
+
+// ---- Q4_K: half-block G of one row -> 64 TMEM columns of sc * q (exact integers) ------------------
+// Pair 2G + pr holds sub-block 4G + 2 pr in its low nibbles and 4G + 2 pr + 1 in its high nibbles
+// (tests/ops.rs:41-59).  A quant byte is dropped into the mantissa of 1024.0 (1024 + q, exact) and one
+// fma takes it to sc * q: (1024 + q) * sc - 1024 * sc.  High nibbles stay in place (16 q) and their
+// scale carries the 1/16.  All operands and results are integers below 2048 (or multiples of powers
+// of two): nothing is rounded.
+template <int G>
+__device__ __forceinline__ void dequant_q4k_half_exact(const uint4 &hdr, const uint4 (&q)[4], uint32_t a_taddr) {
+    // the six-bit scales of sub-blocks 4G .. 4G+3 as bytes (tests/ops.rs:29-39)
+    const uint32_t sc_w = G == 0 ? (hdr.y & 0x3F3F3F3Fu) : ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u));
+#pragma unroll
+    for (int pr = 0; pr < 2; pr++) {
+        const uint32_t sc2 = h2_sub(magic_lo(sc_w >> (16 * pr)), H2_1024);       // (sc_even, sc_odd), exact
+        const uint32_t s_lo = h2_bcast_lo(sc2);
+        const uint32_t s_hi = h2_mul(h2_bcast_hi(sc2), H2_2M4);                  // sc / 16, exact
+        const uint32_t c_lo = h2_mul(s_lo, H2_M1024), c_hi = h2_mul(s_hi, H2_M1024);
+        const uint4 qa = q[2 * pr], qb = q[2 * pr + 1];
+        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+        uint32_t lo[16], hi[16];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint32_t l4 = w[j] & 0x0F0F0F0Fu, h4 = w[j] & 0xF0F0F0F0u;
+            lo[2 * j] = h2_fma(magic_lo(l4), s_lo, c_lo);
+            lo[2 * j + 1] = h2_fma(magic_hi(l4), s_lo, c_lo);
+            hi[2 * j] = h2_fma(magic_lo(h4), s_hi, c_hi);
+            hi[2 * j + 1] = h2_fma(magic_hi(h4), s_hi, c_hi);
+        }
+        tmem_st16(a_taddr + 32 * pr, lo);
+        tmem_st16(a_taddr + 32 * pr + 16, hi);
+    }
+}
+
+// The minimum term's operand of one block and row: 16 K slots = 8 TMEM columns.  p = dmin * m has 17
+// significant bits at most; p_hi = RN_f16(p) and p_lo = p - p_hi (the rounding error of a product, which
+// one fma yields exactly) are both f16 values.  Slots 0-7: p_hi of sub-blocks 0-7, slots 8-15: p_lo; the
+// sums' tile holds each sub-block's sum in slot sb and again in slot 8 + sb, so one K step of the tensor
+// core forms (p_hi + p_lo) * sum.
+// Range: |dmin| * 63 must stay below 65504, i.e. |dmin| < 1039 (weights of real models are below 1).
+__device__ __forceinline__ void min_operand_q4k(const uint4 &hdr, uint32_t a_taddr) {
+    const uint32_t mn[2] = {hdr.z & 0x3F3F3F3Fu, ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u)};
+    const uint32_t dmin2 = (hdr.x >> 16) * 0x00010001u;
+    uint32_t r[8];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t m2 = h2_sub(magic_lo(mn[i >> 1] >> (16 * (i & 1))), H2_1024);   // (m[2i], m[2i+1]), exact
+        const uint32_t hi = h2_mul(m2, dmin2);
+        r[i] = hi;
+        r[4 + i] = h2_fma(m2, dmin2, hi ^ 0x80008000u);
+    }
+    tmem_st8(a_taddr, r);
+}
+
+// ---- Q6_K: half h of a block of one row -> 64 hi columns and 64 lo columns -------------------------
+// Staged bytes (slice-major layout, kernels.h): slices (h, c = 0, 1), each ql[64h+16c..+16) |
+// ql[64h+32+16c..+16) | qh[32h+16c..+16); weight 128h + 32g + 16c + i has its low nibble in ql run
+// (g & 1), low half for g < 2 and high half for g >= 2, and bits 2g..2g+1 of qh; its group scale is
+// scales[8h + 2g + c] (shaders/ops.metal:28-42, 322-334).  K-local 32g + 16c + i -> column 16g + 8c + i/2.
+// Per pair of weights: q' = q - 32 (exact), hi = RN_f16(q' sc) (one multiply), and with -sc one fma gives
+// hi - q' sc = -lo exactly; the MMA that consumes the lo columns negates its A operand.
+struct RawQ6Half {
+    uint4 ql0[2], ql1[2], qh[2];   // [c]: the two ql runs and the qh run of slice (h, c)
+    uint2 sc;                      // int8 scales[8h .. 8h+8)
+};
+// Returns the OR of this row's lo terms: zero when sc (q - 32) was exact in f16 everywhere (always so
+// while |sc| <= 64), in which case the MMA warp skips the product of the lo columns for the stage.
+__device__ __forceinline__ uint32_t dequant_q6k_half_exact(const RawQ6Half &raw, uint32_t a_taddr) {
+    uint32_t any = 0u;
+    const uint2 scw = raw.sc;
+    // the eight int8 scales of this half as f16 pairs: (sc + 128) as a byte in the mantissa of 1024, minus 1152
+    const uint32_t s01 = scw.x ^ 0x80808080u, s23 = scw.y ^ 0x80808080u;
+    constexpr uint32_t H2_1152 = 0x64806480u;
+    const uint32_t sp[4] = {h2_sub(magic_lo(s01), H2_1152), h2_sub(magic_hi(s01), H2_1152),
+                            h2_sub(magic_lo(s23), H2_1152), h2_sub(magic_hi(s23), H2_1152)};   // (sc[2g], sc[2g+1])
+#pragma unroll
+    for (int c = 0; c < 2; c++) {
+        const uint4 q0 = raw.ql0[c], q1 = raw.ql1[c], qh = raw.qh[c];
+        const uint32_t l0[4] = {q0.x, q0.y, q0.z, q0.w}, l1[4] = {q1.x, q1.y, q1.z, q1.w};
+        const uint32_t hw[4] = {qh.x, qh.y, qh.z, qh.w};
+        uint32_t s2[4], ns2[4];
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            s2[g] = c ? h2_bcast_hi(sp[g]) : h2_bcast_lo(sp[g]);
+            ns2[g] = s2[g] ^ 0x80008000u;
+        }
+        uint32_t hi[4][8], lo[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            // four bytes of 6-bit quants for each of the four groups, 11 logic ops for 16 weights
+            const uint32_t qA = hw[i] & 0x33333333u;
+            const uint32_t qB = (hw[i] >> 2) & 0x33333333u;
+            const uint32_t v[4] = {(l0[i] & 0x0F0F0F0Fu) | ((qA << 4) & 0xF0F0F0F0u),
+                                   (l1[i] & 0x0F0F0F0Fu) | ((qB << 4) & 0xF0F0F0F0u),
+                                   ((l0[i] >> 4) & 0x0F0F0F0Fu) | (qA & 0xF0F0F0F0u),
+                                   ((l1[i] >> 4) & 0x0F0F0F0Fu) | (qB & 0xF0F0F0F0u)};
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const uint32_t q2 = h2_sub(e ? magic_hi(v[g]) : magic_lo(v[g]), H2_1056);   // (q - 32) pair
+                    const uint32_t h = h2_mul(q2, s2[g]);
+                    hi[g][2 * i + e] = h;
+                    lo[g][2 * i + e] = h2_fma(q2, ns2[g], h);                                 // hi - q' sc = -lo
+                    any |= lo[g][2 * i + e];
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            tmem_st8(a_taddr + 16 * g + 8 * c, hi[g]);
+            tmem_st8(a_taddr + 64 + 16 * g + 8 * c, lo[g]);
+        }
+    }
+    return any & 0x7FFF7FFFu;                          // a negative zero is a zero
+}
+
+// ---- the kernel --------------------------------------------------------------------------------
+template <int QT, int TN>
+__global__ void __launch_bounds__(XQ_THREADS, 1)
+gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
+    using C = ExactCfg<QT, TN>;
+    constexpr int S = C::STAGES;
+    constexpr int R = C::RAW_SLOTS;
+    constexpr bool MIN = C::MIN;
+    constexpr uint32_t IDESC = umma_idesc_f16(TN);
+
+    extern __shared__ uint8_t smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle
+    uint8_t *tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + S * C::STAGE_BYTES);
+    uint64_t *full = bars, *empty = full + S, *raw_full = empty + S, *raw_empty = raw_full + R;
+    uint64_t *acc_full = raw_empty + R, *acc_empty = acc_full + 2, *macc_full = acc_empty + 2, *macc_empty = macc_full + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(macc_empty + 1);          // [0] TMEM base, [2] split ticket
+    uint32_t *lo_flag = tmem_slot + 4;                                           // Q6_K: [stage][warp of the group]: any nonzero lo term
+    static_assert((2 * 4 + 2 * 4 + 6) * 8 + 16 + 4 * 4 * 4 <= 512, "barrier area");
+    float *d_ring = reinterpret_cast<float *>(tiles + S * C::STAGE_BYTES + 512);   // [D_RING][128]
+    uint8_t *epi_stage = reinterpret_cast<uint8_t *>(d_ring + D_RING * TILE_ROWS);
+    uint8_t *raw_ring = epi_stage + C::EPI_BYTES;                                // 128-byte aligned: all sizes above are
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const Sched sc = make_sched(p, TN);
+    const int w_tiles = sc.w_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(&full[s], DEQ_WARPS / 2 + 1);   // the 4 warps of one dequantising group + the TMA thread (with its bytes)
+            mbar_init(&empty[s], 1);                  // tcgen05.commit
+        }
+        for (int s = 0; s < R; s++) {
+            mbar_init(&raw_full[s], 1);               // the weight TMA thread (with its bytes)
+            mbar_init(&raw_empty[s], DEQ_WARPS);      // every dequantising warp, once its bytes are in registers
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&acc_full[a], 1);               // tcgen05.commit after a block's last MMA
+            mbar_init(&acc_empty[a], EPI_WARPS);
+        }
+        mbar_init(macc_full, 1);                      // tcgen05.commit after a unit's last MMA
+        mbar_init(macc_empty, EPI_WARPS);
+        mbar_init_fence();
+    }
+    if (warp == DEQ_WARPS + 1) {                      // the MMA warp owns TMEM
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int nb = p.K / QK_K;
+
+    if (warp < DEQ_WARPS) {
+        // ---------------- raw bytes (shared memory) -> f16 operand (tensor memory) ----------------
+        const int r = threadIdx.x & 127, g = threadIdx.x >> 7;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + C::A_BASE_COL;
+        bool ok = true;
+        uint32_t it0 = 0, blk = 0;                    // stages / blocks of the units before this one
+        UnitIter ui;
+        Unit u;
+        while (ok && ui.next(sc, u)) {
+            for (int b = u.b0; b < u.b1; b++, blk++) {
+                const uint32_t rs = blk % R;
+                if (!mbar_wait(&raw_full[rs], (blk / R) & 1, p.wait_limit)) {
+                    report_error(p.err, KERR_FULL_WAIT);
+                    ok = false;
+                    break;
+                }
+                const uint8_t *slot = raw_ring + (size_t)rs * C::RAW_SLOT_BYTES;
+                const uint32_t it = it0 + 2u * (uint32_t)(b - u.b0) + (uint32_t)g;
+                const uint32_t s = it % S;
+                const uint32_t a_taddr = lane_base + s * C::A_STAGE_COLS;
+                if constexpr (QT == 0) {
+                    const uint8_t *rowp = slot + (size_t)r * Q4K_BLOCK_BYTES;
+                    const uint4 hdr = lds128(rowp);
+                    uint4 q[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) q[i] = lds128(rowp + 16 + 64 * g + 16 * i);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&raw_empty[rs]);          // the slot may be refilled
+                    if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
+                        report_error(p.err, KERR_EMPTY_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    if (g == 0) {
+                        dequant_q4k_half_exact<0>(hdr, q, a_taddr);
+                        min_operand_q4k(hdr, a_taddr + C::A_MAIN_COLS);
+                        d_ring[(blk % D_RING) * TILE_ROWS + r] = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu));
+                    } else {
+                        dequant_q4k_half_exact<1>(hdr, q, a_taddr);
+                    }
+                } else {
+                    const int bl = b & 15;
+                    RawQ6Half raw;
+#pragma unroll
+                    for (int c = 0; c < 2; c++) {
+                        const uint8_t *sl = slot + (size_t)(2 * g + c) * C::Q6_SLICE_BOX + (size_t)r * 48;
+                        raw.ql0[c] = lds128(sl);
+                        raw.ql1[c] = lds128(sl + 16);
+                        raw.qh[c] = lds128(sl + 32);
+                    }
+                    raw.sc = *reinterpret_cast<const uint2 *>(slot + 4 * C::Q6_SLICE_BOX + (size_t)r * 16 + 8 * g);
+                    const uint16_t dbits = *reinterpret_cast<const uint16_t *>(slot + 4 * C::Q6_SLICE_BOX + C::Q6_SMALL_BOX +
+                                                                               (size_t)r * 16 + ((2 * bl) & 15));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&raw_empty[rs]);          // the slot may be refilled
+                    if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
+                        report_error(p.err, KERR_EMPTY_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const bool any_lo = __any_sync(0xffffffffu, dequant_q6k_half_exact(raw, a_taddr) != 0u);
+                    if (lane == 0) lo_flag[s * 4 + (warp & 3)] = any_lo ? 1u : 0u;
+                    if (g == 0) d_ring[(blk % D_RING) * TILE_ROWS + r] = f16_bits_to_f32(dbits);
+                }
+                tmem_st_wait();                      // this warp's tensor-memory stores have landed
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full[s]);
+            }
+            it0 += 2u * (uint32_t)(u.b1 - u.b0);
+        }
+    } else if (warp == DEQ_WARPS) {
+        // ---------------- TMA producer of the activation tiles ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            UnitIter ui;
+            Unit u;
+            while (ok && ui.next(sc, u)) {
+                const int t0 = (u.tile / w_tiles) * TN;
+                for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
+                    const uint32_t s = it % S;
+                    if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
+                        report_error(p.err, KERR_EMPTY_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    const bool with_sums = MIN && (st & 1) == 0;
+                    mbar_arrive_expect_tx(&full[s], (with_sums ? 6 : 4) * C::SUBTILE_BYTES);
+                    uint8_t *dst = tiles + s * C::STAGE_BYTES;
+#pragma unroll
+                    for (int us = 0; us < 2; us++) {     // x_hi tile, then x_lo tile, of each 64-wide K slice
+                        tma_load_2d(dst + (2 * us) * C::SUBTILE_BYTES, &maps.x, st * 128 + us * BK, t0, &full[s]);
+                        tma_load_2d(dst + (2 * us + 1) * C::SUBTILE_BYTES, &maps.x, st * 128 + us * BK, p.M + t0, &full[s]);
+                    }
+                    if (with_sums) {
+                        tma_load_2d(dst + 4 * C::SUBTILE_BYTES, &maps.xs, (st >> 1) * XS_SLOTS, t0, &full[s]);
+                        tma_load_2d(dst + 5 * C::SUBTILE_BYTES, &maps.xs, (st >> 1) * XS_SLOTS, p.M + t0, &full[s]);
+                    }
+                }
+            }
+        }
+    } else if (warp == RAW_WARP) {
+        // ---------------- TMA producer of the raw weight blocks ----------------
+        if (lane == 0) {
+            uint32_t blk = 0;
+            bool ok = true;
+            UnitIter ui;
+            Unit u;
+            while (ok && ui.next(sc, u)) {
+                const int n0 = (u.tile % w_tiles) * TILE_ROWS;
+                for (int b = u.b0; b < u.b1; b++, blk++) {
+                    const uint32_t rs = blk % R;
+                    if (blk >= (uint32_t)R && !mbar_wait(&raw_empty[rs], ((blk / R) - 1) & 1, p.wait_limit)) {
+                        report_error(p.err, KERR_EMPTY_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *slot = raw_ring + (size_t)rs * C::RAW_SLOT_BYTES;
+                    mbar_arrive_expect_tx(&raw_full[rs], C::RAW_SLOT_BYTES);
+                    if constexpr (QT == 0) {
+                        tma_load_2d(slot, &maps.w_a, b * Q4K_BLOCK_BYTES, n0, &raw_full[rs]);
+                    } else {
+                        const int ci = b >> 4, bl = b & 15;
+                        const int nbc = min(16, nb - 16 * ci);
+                        const int base = 3360 * ci;
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            tma_load_2d(slot + j * C::Q6_SLICE_BOX, &maps.w_a, base + 192 * bl + 48 * j, n0, &raw_full[rs]);
+                        tma_load_2d(slot + 4 * C::Q6_SLICE_BOX, &maps.w_b, base + 192 * nbc + 16 * bl, n0, &raw_full[rs]);
+                        tma_load_2d(slot + 4 * C::Q6_SLICE_BOX + C::Q6_SMALL_BOX, &maps.w_b,
+                                    base + 208 * nbc + ((2 * bl) & ~15), n0, &raw_full[rs]);
+                    }
+                }
+            }
+        }
+    } else if (warp == DEQ_WARPS + 1) {
+        // ---------------- MMA issuer ----------------
+        // The whole warp walks the schedule and waits on the barriers (warp-uniform control flow, so the
+        // descriptors and tensor-memory addresses are formed once per warp); the elected lane issues.
+        const bool leader = elect_one();
+        const uint64_t desc0 = umma_desc_sw128(smem_u32(tiles));
+        const uint32_t desc_hi = (uint32_t)(desc0 >> 32);
+        const uint32_t desc_lo0 = (uint32_t)desc0;
+        const uint32_t a_col0 = tmem_base + C::A_BASE_COL;
+        constexpr uint32_t IDESC2 = umma_idesc_f16(2 * TN);       // A x [x_hi | x_lo]
+        bool ok = true;
+        uint32_t it = 0, blk = 0, ucount = 0;
+        UnitIter ui;
+        Unit u;
+        for (; ok && ui.next(sc, u); ucount++) {
+            // the one minimum-term accumulator: the epilogue must have read the previous unit's out
+            if (MIN && ucount >= 1u && !mbar_wait(macc_empty, (ucount - 1) & 1, p.wait_limit)) {
+                report_error(p.err, KERR_MMA_WAIT);
+                break;
+            }
+            const uint32_t m_tmem = tmem_base + C::ACC_COLS;
+            for (int b = u.b0; b < u.b1 && ok; b++, blk++) {
+                const uint32_t ab = blk & 1u;
+                // the epilogue must have read this accumulator out (block blk - 2) before it is overwritten
+                if (blk >= 2u && !mbar_wait(&acc_empty[ab], ((blk >> 1) - 1) & 1, p.wait_limit)) {
+                    report_error(p.err, KERR_MMA_WAIT);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + ab * C::ACC_BUF_COLS;
+#pragma unroll
+                for (int half = 0; half < 2; half++, it++) {
+                    const uint32_t s = it % S;
+                    if (!mbar_wait(&full[s], (it / S) & 1, p.wait_limit)) {
+                        report_error(p.err, KERR_FULL_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t lo_s = desc_lo0 + ((s * C::STAGE_BYTES) >> 4);
+                    const uint32_t a_s = a_col0 + s * C::A_STAGE_COLS;
+                    bool need_lo = false;
+                    if constexpr (QT == 1)
+                        need_lo = (lo_flag[s * 4] | lo_flag[s * 4 + 1] | lo_flag[s * 4 + 2] | lo_flag[s * 4 + 3]) != 0u;
+                    if (leader) {
+#pragma unroll
+                        for (int us = 0; us < 2; us++)
+#pragma unroll
+                            for (int kk = 0; kk < BK / UMMA_K; kk++) {
+                                // 16 K elements further: 8 TMEM columns of A, 32 bytes inside B's swizzled rows
+                                const uint32_t lo = lo_s + (uint32_t)((2 * us * C::SUBTILE_BYTES + kk * 32) >> 4);
+                                const uint64_t b_desc = ((uint64_t)desc_hi << 32) | lo;
+                                const uint32_t a = a_s + (uint32_t)(us * 32 + kk * 8);
+                                umma_f16_ts(d_tmem, a, b_desc, IDESC2, (half | us | kk) ? 1u : 0u);
+                                if constexpr (QT == 1) {     // the lo columns hold -lo: negate A; x_hi rows only
+                                    if (need_lo) umma_f16_ts(d_tmem, a + C::A_TERM_COLS, b_desc, IDESC | IDESC_NEG_A, 1u);
+                                }
+                            }
+                        if (MIN && half == 0) {              // (p_hi + p_lo) x sums: hi rows, then lo rows
+                            const uint32_t lo = lo_s + (uint32_t)((4 * C::SUBTILE_BYTES) >> 4);
+                            umma_f16_ts(m_tmem, a_s + C::A_MAIN_COLS, ((uint64_t)desc_hi << 32) | lo, IDESC, b != u.b0 ? 1u : 0u);
+                            umma_f16_ts(m_tmem, a_s + C::A_MAIN_COLS,
+                                        ((uint64_t)desc_hi << 32) | (lo + (uint32_t)(C::SUBTILE_BYTES >> 4)), IDESC, 1u);
+                        }
+                        umma_commit(&empty[s]);            // stage free once these MMAs have read it
+                    }
+                    __syncwarp();
+                }
+                if (ok && leader) umma_commit(&acc_full[ab]);   // this block's accumulator is complete
+                __syncwarp();
+            }
+            if (MIN && ok && leader) umma_commit(macc_full);
+            __syncwarp();
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        // A thread owns one weight row (its TMEM lane).  After every block it reads the block's
+        // accumulator, multiplies by the row's d of that block and adds into its float32 totals; at
+        // the end of the unit the minimum term comes off and the totals go out like the prefill
+        // kernel's: scaled by the token factor, transposed through a per-warp staging block, written
+        // as 16-byte vectors (or deposited / combined when the unit is part of a tile cut along K).
+        const int quarter = warp & 3;                           // TMEM lanes this warp may read
+        const int ew = warp - (DEQ_WARPS + 2);
+        const int row_in_tile = 32 * quarter + lane;
+        uint8_t *stg = epi_stage + (size_t)ew * (EPI_TOK * 32 * 4);       // [EPI_TOK tokens][32 rows]
+        float *scale_s = reinterpret_cast<float *>(epi_stage + EPI_WARPS * (EPI_TOK * 32 * 4)) + ew * TN_PAD;
+        uint32_t *ticket_s = tmem_slot + 2;
+        constexpr int EPI_THREADS = EPI_WARPS * 32;
+        uint32_t blk = 0, ucount = 0;
+        bool dead = false;
+        const bool gather = p.world > 1;
+        const uint32_t gather_step = gather ? *reinterpret_cast<volatile uint32_t *>(p.step_word) + 1u : 0u;
+        const uint32_t lane_off = (uint32_t)(32 * quarter) << 16;
+        UnitIter ui;
+        Unit u;
+        for (; !dead && ui.next(sc, u); ucount++) {
+            const int n0 = (u.tile % w_tiles) * TILE_ROWS, t0 = (u.tile / w_tiles) * TN;
+            const bool partial = u.b1 - u.b0 < sc.nb;
+            for (int c = lane; c < TN; c += 32) scale_s[c] = (t0 + c < p.M) ? __ldg(p.tok_scale + t0 + c) : 0.0f;
+            __syncwarp();
+            float total[TN];
+#pragma unroll
+            for (int j = 0; j < TN; j++) total[j] = 0.0f;
+            for (int b = u.b0; b < u.b1 && !dead; b++, blk++) {
+                const uint32_t ab = blk & 1u;
+                if (!mbar_wait(&acc_full[ab], (blk >> 1) & 1, p.wait_limit)) {
+                    report_error(p.err, KERR_MMA_WAIT);
+                    dead = true;
+                    break;
+                }
+                tc_fence_after();
+                const float d = d_ring[(blk % D_RING) * TILE_ROWS + row_in_tile];
+                const uint32_t acc = tmem_base + ab * C::ACC_BUF_COLS + lane_off;
+#pragma unroll
+                for (int c = 0; c < TN / 16; c++) {
+                    uint32_t vh[16], vl[16];
+                    tmem_ld16(acc + 16 * c, vh);                  // A x_hi
+                    tmem_ld16(acc + TN + 16 * c, vl);             // A x_lo
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j++)
+                        total[16 * c + j] = fmaf(d, __uint_as_float(vh[j]) + __uint_as_float(vl[j]), total[16 * c + j]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[ab]);
+            }
+            if (MIN && !dead) {
+                if (!mbar_wait(macc_full, ucount & 1, p.wait_limit)) {
+                    report_error(p.err, KERR_MMA_WAIT);
+                    dead = true;
+                } else {
+                    tc_fence_after();
+                    const uint32_t macc = tmem_base + C::ACC_COLS + lane_off;
+#pragma unroll
+                    for (int c = 0; c < TN / 16; c++) {
+                        uint32_t v[16];
+                        tmem_ld16(macc + 16 * c, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; j++) total[16 * c + j] = fmaf(-32.0f, __uint_as_float(v[j]), total[16 * c + j]);
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(macc_empty);
+                }
+            }
+            if (dead) break;
+
+            // ---- partial unit: who else works on this tile, and is this CTA the last to arrive? ----
+            bool deposit = false, combine = false;
+            int c_first = 0, c_last = -1, tt = 0, tb = 0;
+            if (partial) {
+                tt = u.tile - sc.n_full;
+                tb = tt * sc.nb;
+                const int te = tb + sc.nb;
+                int c = min(sc.gt - 1, (int)(((unsigned)tb * (unsigned)sc.gt) / (unsigned)sc.T));
+                while (c + 1 < sc.gt && tail_start(sc, c + 1) <= tb) c++;
+                while (c > 0 && tail_start(sc, c) > tb) c--;
+                c_first = c;
+                while (c + 1 < sc.gt && tail_start(sc, c + 1) < te) c++;
+                c_last = c;
+                const uint32_t pieces = (uint32_t)(c_last - c_first + 1);
+                if (ew == 0 && lane == 0) *ticket_s = atomicAdd(p.ws_counters + 2 * tt, 1u);
+                named_barrier_sync(2, EPI_THREADS);
+                deposit = *ticket_s + 1 < pieces;
+                combine = !deposit;
+                if (combine) {
+                    if (ew == 0 && lane == 0) {                  // every other piece has a ticket: wait for their deposits
+                        bool seen = false;
+                        for (uint32_t i = 0; i < p.wait_limit && !seen; i++) {
+                            uint32_t n;
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(n) : "l"(p.ws_counters + 2 * tt + 1) : "memory");
+                            seen = n + 1 >= pieces;
+                            if (!seen) __nanosleep(32);
+                        }
+                        if (!seen) report_error(p.err, KERR_SPLIT_WAIT);
+                    }
+                    named_barrier_sync(2, EPI_THREADS);
+                }
+            }
+
+            // ---- where this unit's values go ----
+            const bool o_bf16 = deposit ? false : (p.out_bf16 != 0);
+            const int esz = o_bf16 ? 2 : 4;
+            uint8_t *o_ptr = (uint8_t *)p.Out;
+            size_t o_stride = (size_t)p.n_total;                // elements between tokens (n_total = N unless sharded)
+            int tok_base = t0, row_base = p.row_offset + n0 + 32 * quarter, tok_lim = p.M, row_lim = p.row_offset + p.N;
+            if (deposit) {
+                const int k = sc.tail_a >= tb ? 0 : 1;          // first or last piece of this CTA's range
+                o_ptr = (uint8_t *)(p.ws_slots + (size_t)(2 * blockIdx.x + k) * (TILE_ROWS * TN));
+                o_stride = TILE_ROWS;
+                tok_base = 0; row_base = 32 * quarter; tok_lim = TN; row_lim = TILE_ROWS;
+            }
+            const bool vec_ok = (o_stride % (size_t)(16 / esz)) == 0;
+#pragma unroll
+            for (int g0 = 0; g0 < TN; g0 += EPI_TOK) {
+                if (combine) {
+                    // the deposits of the other CTAs, token by token (coalesced over the rows of the warp)
+                    for (int c = c_first; c <= c_last; c++) {
+                        if (c == (int)blockIdx.x) continue;
+                        const int k = tail_start(sc, c) >= tb ? 0 : 1;
+                        const float *sa = p.ws_slots + (size_t)(2 * c + k) * (TILE_ROWS * TN) + (size_t)g0 * TILE_ROWS + row_in_tile;
+                        float add[EPI_TOK];
+#pragma unroll
+                        for (int j = 0; j < EPI_TOK; j++) add[j] = __ldcg(sa + j * TILE_ROWS);
+#pragma unroll
+                        for (int j = 0; j < EPI_TOK; j++) total[g0 + j] += add[j];
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < EPI_TOK; j++) {
+                    const float val = deposit ? total[g0 + j] : total[g0 + j] * scale_s[g0 + j];
+                    if (o_bf16) reinterpret_cast<__nv_bfloat16 *>(stg)[j * 32 + lane] = __float2bfloat16_rn(val);
+                    else reinterpret_cast<float *>(stg)[j * 32 + lane] = val;
+                }
+                __syncwarp();
+                // ---- staging -> global ----
+                if (vec_ok) {
+                    const int vec_per_tok = 32 * esz / 16;       // 4 (bf16) or 8 (fp32) vectors per token
+                    const int rows_per_vec = 16 / esz;
+                    for (int i = lane; i < EPI_TOK * vec_per_tok; i += 32) {
+                        const int tl = i / vec_per_tok, vv = i % vec_per_tok;
+                        const int tok = tok_base + g0 + tl, row = row_base + vv * rows_per_vec;
+                        if (tok < tok_lim && row < row_lim) {
+                            const uint4 dv = *reinterpret_cast<const uint4 *>(stg + (size_t)tl * 32 * esz + vv * 16);
+                            *reinterpret_cast<uint4 *>(o_ptr + ((size_t)tok * o_stride + row) * esz) = dv;
+                            if (gather && !deposit) {            // the same values, as words, to every peer's mailbox
+                                float f[8];
+                                const uint32_t w4[4] = {dv.x, dv.y, dv.z, dv.w};
+                                int nv;
+                                if (o_bf16) {
+                                    nv = 8;
+#pragma unroll
+                                    for (int j = 0; j < 4; j++) {
+                                        f[2 * j] = __uint_as_float(w4[j] << 16);
+                                        f[2 * j + 1] = __uint_as_float(w4[j] & 0xFFFF0000u);
+                                    }
+                                } else {
+                                    nv = 4;
+#pragma unroll
+                                    for (int j = 0; j < 4; j++) f[j] = __uint_as_float(w4[j]);
+                                }
+                                const size_t word = (gather_step & 1u) * p.half_words +
+                                                    ((size_t)p.rank * p.M + tok) * p.N + (row - p.row_offset);
+                                for (int dd = 0; dd < p.world; dd++) {
+                                    if (dd == p.rank) continue;
+                                    uint2 *box = p.peer_box[dd] + word;
+                                    for (int j = 0; j < nv; j++) mailbox_store(box + j, __float_as_uint(f[j]), gather_step);
+                                }
+                            }
+                        }
+                    }
+                } else {
+                    for (int tl = 0; tl < EPI_TOK; tl++) {
+                        const int tok = tok_base + g0 + tl, row = row_base + lane;
+                        if (tok < tok_lim && row < row_lim) {
+                            float fv;
+                            if (o_bf16) {
+                                const uint16_t hb = reinterpret_cast<const uint16_t *>(stg)[tl * 32 + lane];
+                                ((uint16_t *)o_ptr)[(size_t)tok * o_stride + row] = hb;
+                                fv = __uint_as_float((uint32_t)hb << 16);
+                            } else {
+                                fv = reinterpret_cast<const float *>(stg)[tl * 32 + lane];
+                                ((float *)o_ptr)[(size_t)tok * o_stride + row] = fv;
+                            }
+                            if (gather && !deposit) {
+                                const size_t word = (gather_step & 1u) * p.half_words +
+                                                    ((size_t)p.rank * p.M + tok) * p.N + (row - p.row_offset);
+                                for (int dd = 0; dd < p.world; dd++)
+                                    if (dd != p.rank) mailbox_store(p.peer_box[dd] + word, __float_as_uint(fv), gather_step);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();                                    // staging is reused by the next group
+            }
+            if (partial) {
+                if (deposit) {
+                    __threadfence();                             // this thread's deposit is visible device-wide
+                    named_barrier_sync(2, EPI_THREADS);
+                    if (ew == 0 && lane == 0) atomicAdd(p.ws_counters + 2 * tt + 1, 1u);
+                } else {
+                    named_barrier_sync(2, EPI_THREADS);          // all deposits have been read
+                    if (ew == 0 && lane == 0) {                  // leave the counters at zero for the next launch
+                        p.ws_counters[2 * tt] = 0;
+                        p.ws_counters[2 * tt + 1] = 0;
+                    }
+                }
+            }
+        }
+        if (gather) {
+            // ---- collect the other ranks' slices from this rank's mailbox ----
+            const uint2 *box = p.peer_box[p.rank] + (gather_step & 1u) * p.half_words;
+            const size_t per_src = (size_t)p.M * p.N;                    // words one sender posts
+            const size_t remote = (size_t)(p.world - 1) * per_src;
+            const int et = ew * 32 + lane;
+            constexpr int UNPACK = 8;
+            const size_t stride = (size_t)gridDim.x * EPI_THREADS;
+            bool late = dead;
+            for (size_t i0 = (size_t)blockIdx.x * EPI_THREADS + et; i0 < remote && !late; i0 += UNPACK * stride) {
+                uint2 got[UNPACK];
+#pragma unroll
+                for (int b = 0; b < UNPACK; b++) {
+                    const size_t i = i0 + b * stride;
+                    if (i < remote) {
+                        const int q = (int)(i / per_src);
+                        got[b] = mailbox_load(box + (size_t)(q < p.rank ? q : q + 1) * per_src + (i - (size_t)q * per_src));
+                    }
+                }
+#pragma unroll
+                for (int b = 0; b < UNPACK; b++) {
+                    const size_t i = i0 + b * stride;
+                    if (i >= remote || late) continue;
+                    const int q = (int)(i / per_src);
+                    const size_t rem = i - (size_t)q * per_src;
+                    const int src = q < p.rank ? q : q + 1;
+                    const int tok = (int)(rem / p.N), row = (int)(rem - (size_t)tok * p.N);
+                    if (got[b].y != gather_step &&
+                        !mailbox_wait(box + (size_t)src * per_src + rem, gather_step, p.gather_limit, got[b])) {
+                        report_error(p.err, KERR_GATHER_WAIT);
+                        late = true;
+                        continue;
+                    }
+                    const size_t o = (size_t)tok * p.n_total + (size_t)src * p.N + row;
+                    if (p.out_bf16) ((__nv_bfloat16 *)p.Out)[o] = __float2bfloat16_rn(__uint_as_float(got[b].x));
+                    else ((float *)p.Out)[o] = __uint_as_float(got[b].x);
+                }
+            }
+            named_barrier_sync(2, EPI_THREADS);
+            if (ew == 0 && lane == 0) {
+                const uint32_t ticket = atomicAdd(p.done_counter, 1u);
+                if (ticket == gridDim.x - 1) {
+                    *p.done_counter = 0;
+                    *p.step_word = gather_step;
+                }
+            }
+        }
+    }
+
+    // teardown: everyone meets here, also after an abandoned wait, so TMEM is always released
+    tc_fence_before();
+    __syncthreads();
+    if (warp == DEQ_WARPS + 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---- activations -> (x_hi, x_lo) f16 pairs, token factors and sub-block sums ---------------------
+// One CTA per token.  The token row is multiplied by a power of two that brings its largest magnitude
+// to [2^13, 2^14); x_hi = RN_f16(x * 2^e), x_lo = RN_f16(x * 2^e - x_hi); the inverse factor goes to
+// tok_scale[token].  For Q4_K the sums of every 32 consecutive scaled values (what the block's
+// minimum multiplies), divided by 32 so that they stay below 2^14, are written as hi + lo f16 pairs
+// into `xs` ([2M rows]: hi parts in row token, lo parts in row M + token), 64 slots per 256-weight
+// block in the order the minimum operand expects (see min_operand_q4k): the sum of sub-block sb in
+// slot sb and again in slot 8 + sb, the rest zero.
+__global__ void __launch_bounds__(256)
+activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M, __half *__restrict__ out,
+                         __half *__restrict__ xs, float *__restrict__ tok_scale) {
+    __shared__ float red[8];
+    const int tok = blockIdx.x;
+    const size_t base = (size_t)tok * K;
+    auto load8 = [&](int k, float (&v)[8]) {
+        if (x_is_bf16) {
+            const uint4 u = __ldg(reinterpret_cast<const uint4 *>((const uint16_t *)x + base + k));
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+        } else {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>((const float *)x + base + k));
+            const float4 b = __ldg(reinterpret_cast<const float4 *>((const float *)x + base + k + 4));
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        }
+    };
+    float amax = 0.0f;
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+        float v[8];
+        load8(k, v);
+#pragma unroll
+        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) amax = fmaxf(amax, red[i]);
+    const int eb = (int)((__float_as_uint(amax) >> 23) & 0xFFu);
+    int e = 140 - eb;                                    // amax < 2^(eb-126): the scaled row stays below 2^14
+    e = max(-126, min(126, e));
+    if (amax == 0.0f || eb == 255) e = 0;                // all-zero row, or inf/nan: leave as is
+    const float sc = exp2i(e);
+    const int nb = K / QK_K;
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {   // second read comes from L1/L2
+        float v[8];
+        load8(k, v);
+        uint32_t h[4], l[4];
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float a = v[2 * i] * sc, b = v[2 * i + 1] * sc;
+            h[i] = pack_w(a, b);
+            const float2 back = __half22float2(*reinterpret_cast<const __half2 *>(&h[i]));
+            l[i] = pack_w(a - back.x, b - back.y);
+            const float2 lowf = __half22float2(*reinterpret_cast<const __half2 *>(&l[i]));
+            sum += (back.x + lowf.x) + (back.y + lowf.y);          // what the tensor core will see
+        }
+        *reinterpret_cast<uint4 *>(out + base + k) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4 *>(out + (size_t)M * K + base + k) = make_uint4(l[0], l[1], l[2], l[3]);
+        if (xs) {
+            // four consecutive threads hold one sub-block of 32 values
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            const int sb = k >> 5, blk = sb >> 3, j = sb & 7;
+            __half *row_hi = xs + ((size_t)tok * nb + blk) * XS_SLOTS;
+            __half *row_lo = xs + ((size_t)(M + tok) * nb + blk) * XS_SLOTS;
+            if ((threadIdx.x & 3) == 0) {
+                const float s32 = sum * 0.03125f;
+                const __half hi = __float2half_rn(s32);
+                const __half lo = __float2half_rn(s32 - __half2float(hi));
+                row_hi[j] = hi;
+                row_hi[8 + j] = hi;
+                row_lo[j] = lo;
+                row_lo[8 + j] = lo;
+            }
+            // the 32 threads of a block zero its unused slots 16..63
+            const int tb = (k >> 3) & 31;
+            const __half zero = __float2half_rn(0.0f);
+            row_hi[16 + tb] = zero;
+            row_lo[16 + tb] = zero;
+            if (tb < 16) {
+                row_hi[48 + tb] = zero;
+                row_lo[48 + tb] = zero;
+            }
+        }
+    }
+    if (threadIdx.x == 0) tok_scale[tok] = exp2i(-e);
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+size_t exact_x_bytes(int K, int M) { return ((size_t)2 * M * K * 2 + 255) / 256 * 256; }
+size_t exact_xs_bytes(int K, int M) { return ((size_t)2 * M * (K / QK_K) * XS_SLOTS * 2 + 255) / 256 * 256; }
+
+template <int QT, int TN>
+cudaError_t launch_exact_tn(const GemmParams &p, const uint8_t *scratch, int split_mode, cudaStream_t s) {
+    using C = ExactCfg<QT, TN>;
+    ExactMaps maps;
+    const __half *x_f16 = (const __half *)scratch;
+    const __half *xs = (const __half *)(scratch + exact_x_bytes(p.K, p.M));
+    cudaError_t e = encode_2d(&maps.x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x_f16, (uint64_t)p.K, (uint64_t)p.M * 2,
+                              (uint64_t)p.K * 2, BK, TN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (e != cudaSuccess) return e;
+    const int nb = p.K / QK_K;
+    if (QT == 0) {
+        e = encode_2d(&maps.xs, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, xs, (uint64_t)nb * XS_SLOTS, (uint64_t)p.M * 2,
+                      (uint64_t)nb * XS_SLOTS * 2, BK, TN, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (e != cudaSuccess) return e;
+        e = encode_2d(&maps.w_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.W, (uint64_t)p.row_stride, (uint64_t)p.N,
+                      (uint64_t)p.row_stride, Q4K_BLOCK_BYTES, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (e != cudaSuccess) return e;
+        maps.w_b = maps.w_a;
+    } else {
+        maps.xs = maps.x;
+        e = encode_2d(&maps.w_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.W, (uint64_t)p.row_stride, (uint64_t)p.N,
+                      (uint64_t)p.row_stride, 48, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (e != cudaSuccess) return e;
+        e = encode_2d(&maps.w_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.W, (uint64_t)p.row_stride, (uint64_t)p.N,
+                      (uint64_t)p.row_stride, 16, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (e != cudaSuccess) return e;
+    }
+    auto kern = gemm_exact_kernel<QT, TN>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+    if (e != cudaSuccess) return e;
+    const int n_tiles = ((p.N + TILE_ROWS - 1) / TILE_ROWS) * ((p.M + TN - 1) / TN);
+    int grid = n_tiles < p.sm_count ? n_tiles : p.sm_count;
+    GemmParams q = p;
+    q.split = 0;
+    // Cutting the last, partial wave of tiles along K: every SM then streams its share of the weights
+    // (a whole small matrix, or the tail of a large one).  The exchange is one tile-sized float32 deposit
+    // per piece, at most 32 KB at these token counts, so it is used whenever there is a partial wave and
+    // there are K blocks to share out.
+    const int rest = n_tiles % p.sm_count;
+    const bool want = split_mode > 0 || (split_mode < 0 && rest != 0 && nb >= 4);
+    if (p.ws_slots && want && rest != 0 && nb >= 2) {
+        q.split = 1;
+        const int tail_blocks = rest * nb;
+        if (n_tiles < p.sm_count) grid = tail_blocks < p.sm_count ? tail_blocks : p.sm_count;
+    }
+    if (q.world > 1) grid = p.sm_count;      // CTAs without a tile still take their share of the mailbox
+    kern<<<grid, XQ_THREADS, C::SMEM, s>>>(maps, q);
+    return cudaGetLastError();
+}
+
+template <int QT>
+cudaError_t launch_exact_qt(const GemmParams &p, const uint8_t *scratch, int split_mode, cudaStream_t s) {
+    if (p.M <= 16) return launch_exact_tn<QT, 16>(p, scratch, split_mode, s);
+    if (p.M <= 32) return launch_exact_tn<QT, 32>(p, scratch, split_mode, s);
+    return launch_exact_tn<QT, 64>(p, scratch, split_mode, s);
+}
+
+}  // namespace
+
+// Scratch layout: [x_hi, x_lo: 2 M K f16][sub-block sums: 2 M (K/256) 64 f16][M float token factors].
+size_t gemm_exact_scratch_bytes(int K, int M) {
+    return exact_x_bytes(K, M) + exact_xs_bytes(K, M) + (size_t)M * sizeof(float);
+}
+
+cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
+                              int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
+                              cudaStream_t s, uint64_t *launches, const GemmGather *gather) {
+    if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
+    if (!scratch || M > GEMM_EXACT_MAX_TOKENS || K % QK_K) return cudaErrorInvalidValue;
+    if (wdtype != DT_Q4K && wdtype != DT_Q6K) return cudaErrorInvalidValue;
+    uint8_t *sb = (uint8_t *)scratch;
+    __half *x_f16 = (__half *)sb;
+    __half *xs = wdtype == DT_Q4K ? (__half *)(sb + exact_x_bytes(K, M)) : nullptr;
+    float *tok_scale = (float *)(sb + exact_x_bytes(K, M) + exact_xs_bytes(K, M));
+    activations_exact_kernel<<<(unsigned)M, 256, 0, s>>>(x, x_dtype == DT_BF16, K, M, x_f16, xs, tok_scale);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (launches) (*launches)++;
+    GemmParams p{};
+    p.W = w; p.Out = out; p.err = err_word.word; p.wait_limit = err_word.mbar_polls; p.gather_limit = err_word.gather_polls;
+    p.K = K; p.N = N; p.M = M; p.out_bf16 = out_dtype == DT_BF16;
+    p.tok_scale = tok_scale;
+    p.n_total = N;
+    if (gather && gather->world > 1) {
+        p.world = gather->world; p.rank = gather->rank; p.n_total = N * gather->world; p.row_offset = gather->rank * N;
+        p.done_counter = gather->done_counter; p.step_word = gather->step_word;
+        p.half_words = (size_t)gather->world * M * N;
+        for (int d = 0; d < gather->world; d++) p.peer_box[d] = (uint2 *)gather->peer_mailbox[d];
+    }
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&p.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    if (split_ws && 2 * p.sm_count * sizeof(uint32_t) <= gemm_split_counter_bytes()) {
+        p.ws_counters = (uint32_t *)split_ws;
+        p.ws_slots = (float *)((uint8_t *)split_ws + gemm_split_counter_bytes());
+    }
+    if (wdtype == DT_Q4K) {
+        p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
+        e = launch_exact_qt<0>(p, sb, split_mode, s);
+    } else {
+        p.row_stride = q6k_row_stride(K);
+        e = launch_exact_qt<1>(p, sb, split_mode, s);
+    }
+    if (e == cudaSuccess && launches) (*launches)++;
+    return e;
+}
+
+}  // namespace llmrs

@@ -186,13 +186,25 @@ cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype
                         int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
                         cudaStream_t s, uint64_t *launches, const GemmGather *gather = nullptr, bool two_term = false);
 
+// The small-batch matmul (up to GEMM_EXACT_MAX_TOKENS tokens) on the tensor cores at the decode
+// kernel's tolerance: the integer factors of the block formats (sc * q for Q4_K, sc * (q - 32) as an
+// exact hi + lo pair for Q6_K) are the f16 operand, the activations a hi + lo f16 pair, and the blocks'
+// d multiplies the per-block accumulators in float32 outside the tensor core (gemm_exact.cu).
+// `scratch`: gemm_exact_scratch_bytes() bytes; split_ws / split_mode / gather as for launch_gemm.
+constexpr int GEMM_EXACT_MAX_TOKENS = 64;
+size_t gemm_exact_scratch_bytes(int K, int M);
+cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
+                              int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
+                              cudaStream_t s, uint64_t *launches, const GemmGather *gather = nullptr);
+
 // The same GEMM with its scratch in a fixed 8 MiB device array that is part of the library image:
 // no allocation on this path.  `device` must be the current device; the first call on a device
-// resolves the array's address.  Fails with cudaErrorInvalidValue when gemm_scratch_bytes(K, M)
-// exceeds gemm_static_scratch_capacity().
+// resolves the array's address.  Fails with cudaErrorInvalidValue when the scratch the kernel needs
+// (gemm_scratch_bytes(K, M), or gemm_exact_scratch_bytes(K, M) with `exact`, which runs the kernel of
+// launch_gemm_exact) exceeds gemm_static_scratch_capacity().
 size_t gemm_static_scratch_capacity();
 cudaError_t launch_gemm_static_scratch(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out,
                                        int out_dtype, int K, int N, int M, int device, ErrSink err_word,
-                                       cudaStream_t s, uint64_t *launches, bool two_term = false);
+                                       cudaStream_t s, uint64_t *launches, bool two_term = false, bool exact = false);
 
 }  // namespace llmrs
