@@ -38,6 +38,9 @@ extern "C" {
 /* GGUF dtype ids used on this path (src/tensor/mod.rs:3-33). */
 enum llmrs_dtype {
     LLMRS_F32 = 0,
+    LLMRS_F16 = 1,      /* weights and embedding tables only */
+    LLMRS_Q4_0 = 2,     /* weights only; read as the reference's kernel reads it, see llmrs_cuda_matmul */
+    LLMRS_Q8_0 = 8,     /* weights only */
     LLMRS_Q4K = 12,
     LLMRS_Q6K = 14,
     LLMRS_I32 = 26,     /* index buffers (positions, slot mapping, page tables), as upload_u32 makes them */
@@ -54,7 +57,11 @@ enum llmrs_layout {
      *                         of block b (h = half of the block, c = 0,1),
      *   nbc*16 B: the int8 scales of block b at 16b,   nbc*2 B: the f16 d of block b at 2b.
      * Rows are round_up(210*K/256, 32) bytes apart. */
-    LLMRS_LAYOUT_Q6K_SLICES = 1
+    LLMRS_LAYOUT_Q6K_SLICES = 1,
+    /* Q8_0 / Q4_0 (32-weight blocks of 34 / 18 bytes, 2-byte aligned in the file) as two planes with
+     * 16-byte aligned rows: N rows of quant bytes in file order (Q8_0: K bytes, Q4_0: K/2 bytes per row,
+     * rows round_up(., 16) apart), then N rows of the blocks' f16 scales (round_up(K/16, 16) apart). */
+    LLMRS_LAYOUT_BLOCK32_PLANES = 2
 };
 
 enum llmrs_status {
@@ -110,7 +117,13 @@ int llmrs_cuda_wrap(llmrs_ctx *ctx, void *dptr, uint32_t dtype, const uint64_t *
 int llmrs_cuda_free(llmrs_ctx *ctx, llmrs_buf *buf);
 
 /* Replaces Backend::matmul (src/backend/mod.rs:29-34; metal/mod.rs:496-687):
- * out[s*N + r] = sum_k W[r,k] * in[s*K + k].  Weight dtype Q4_K or Q6_K; input
+ * out[s*N + r] = sum_k W[r,k] * in[s*K + k].  Weight dtype Q4_K or Q6_K (the path this library is built
+ * around), or one of the other types the reference's dispatcher takes (metal/mod.rs:503-518, 542-562):
+ * dense F32 / F16 / BF16 and Q8_0 / Q4_0, served by a streaming kernel up to 8 tokens and, for the dense
+ * types, a tcgen05 GEMM above (float32 accumulation; 16-bit operands on the tensor cores, tf32 for F32
+ * weights: 2e-3 class); K a multiple of 4 (F32), 8 (F16 / BF16) or 32 (Q8_0 / Q4_0).  Q4_0 is read as the
+ * reference's kernel reads it (shaders/ops.metal:161-190): element e of a block is the low nibble of byte
+ * e/2 for even e, the high nibble for odd e, minus 8 (ggml's Q4_0 orders the nibbles differently).  Input
  * and output each F32 or BF16 (read from the buffers).  Enqueues only.  The tensor-core path keeps
  * converted activations in a scratch buffer of the context, which grows (one cudaMalloc) the first
  * time a call needs more than any call before it: so there is no allocation once a call of the same
@@ -243,7 +256,7 @@ int llmrs_cuda_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w
                               const llmrs_buf *input);
 
 /* Replaces Backend::embed (src/backend/mod.rs:25-27; metal/mod.rs:841-878, kernels
- * shaders/ops.metal:917-965) for Q4_K / Q6_K tables: row tokens[s] of `table` ([dim, vocab], as
+ * shaders/ops.metal:878-965) for F32 / F16 / BF16 / Q4_K / Q6_K tables (the reference's list): row tokens[s] of `table` ([dim, vocab], as
  * uploaded by upload_tensor) is dequantised into column s of `out` ([dim] for one token, else
  * [dim, n_tokens]; F32 or BF16).  `tokens` is host memory, as in the trait (tokens: &[u32]); ids
  * are checked against the table before anything is enqueued.  The values are the float32
@@ -288,7 +301,7 @@ size_t llmrs_cuda_allgather_mailbox_bytes(uint32_t n_total, uint32_t tokens);
 #define LLMRS_ALLGATHER_MAX_TOKENS 128
 int llmrs_cuda_matmul_allgather_max_tokens(uint32_t weight_dtype, uint32_t in_features);
 
-/* Dequantises a Q4_K/Q6_K weight to float32 [N, K] in device memory `dev_out`
+/* Dequantises a weight (any type matmul takes) to float32 [N, K] in device memory `dev_out`
  * (N*K floats).  The reference has no such op; it exposes, for testing, the
  * values its kernels form in registers (tests/ops.rs:41-59, shaders/ops.metal:322-334). */
 int llmrs_cuda_dequantize(llmrs_ctx *ctx, const llmrs_buf *weight, float *dev_out);

@@ -27,16 +27,20 @@ LIB_PATH = os.path.join(_HERE, "libllmrs_cuda.so")
 class DType(enum.IntEnum):
     """GGUF dtype ids (src/tensor/mod.rs:3-33); only the ones this path handles."""
     F32 = 0
+    F16 = 1
+    Q4_0 = 2
+    Q8_0 = 8
     Q4K = 12
     Q6K = 14
     I32 = 26
     BF16 = 30
 
     def block_elems(self) -> int:                     # src/tensor/mod.rs:37-50
-        return 256 if self in (DType.Q4K, DType.Q6K) else 1
+        return 256 if self in (DType.Q4K, DType.Q6K) else 32 if self in (DType.Q4_0, DType.Q8_0) else 1
 
     def block_size_bytes(self) -> int:                # src/tensor/mod.rs:52-86
-        return {DType.F32: 4, DType.I32: 4, DType.BF16: 2, DType.Q4K: 144, DType.Q6K: 210}[self]
+        return {DType.F32: 4, DType.I32: 4, DType.BF16: 2, DType.F16: 2, DType.Q4_0: 18, DType.Q8_0: 34,
+                DType.Q4K: 144, DType.Q6K: 210}[self]
 
     def storage_size(self, n_elements: int) -> int:   # src/tensor/mod.rs:89-93
         be = self.block_elems()

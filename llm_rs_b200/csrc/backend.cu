@@ -171,10 +171,25 @@ bool storage_size(uint32_t dtype, uint64_t n_elems, size_t *out) {
         *out = (size_t)(n_elems / QK_K) * (dtype == LLMRS_Q4K ? Q4K_BLOCK_BYTES : Q6K_BLOCK_BYTES);
         return true;
     }
-    size_t eb = dtype == LLMRS_I32 ? 4 : dense_elem_bytes(dtype);
+    if (dtype == LLMRS_Q8_0 || dtype == LLMRS_Q4_0) {
+        if (n_elems % 32) return false;
+        *out = (size_t)(n_elems / 32) * (dtype == LLMRS_Q8_0 ? 34 : 18);
+        return true;
+    }
+    size_t eb = dtype == LLMRS_I32 ? 4 : dtype == LLMRS_F16 ? 2 : dense_elem_bytes(dtype);
     if (!eb) return false;
     *out = (size_t)n_elems * eb;
     return true;
+}
+
+bool is_kquant(uint32_t dtype) { return dtype == LLMRS_Q4K || dtype == LLMRS_Q6K; }
+bool is_block32(uint32_t dtype) { return dtype == LLMRS_Q8_0 || dtype == LLMRS_Q4_0; }
+// Weight types beside the K-quants that matmul takes: dense F32 / F16 / BF16 and Q8_0 / Q4_0.
+bool is_other_weight(uint32_t dtype) {
+    return dtype == LLMRS_F32 || dtype == LLMRS_F16 || dtype == LLMRS_BF16 || is_block32(dtype);
+}
+uint32_t weight_layout(uint32_t dtype) {
+    return dtype == LLMRS_Q6K ? LLMRS_LAYOUT_Q6K_SLICES : is_block32(dtype) ? LLMRS_LAYOUT_BLOCK32_PLANES : LLMRS_LAYOUT_RAW;
 }
 
 bool shape_dims(const uint64_t *shape, int ndims, uint32_t *d0, uint32_t *d1) {
@@ -235,6 +250,9 @@ const char *dtype_name(uint32_t dt) {
         case LLMRS_Q4K: return "q4_k";
         case LLMRS_Q6K: return "q6_k";
         case LLMRS_BF16: return "bf16";
+        case LLMRS_F16: return "f16";
+        case LLMRS_Q8_0: return "q8_0";
+        case LLMRS_Q4_0: return "q4_0";
         case LLMRS_I32: return "i32";
         default: return "?";
     }
@@ -446,30 +464,33 @@ int llmrs_cuda_upload_tensor(llmrs_ctx *ctx, uint32_t dtype, const uint64_t *sha
     const bool quant = dtype == LLMRS_Q4K || dtype == LLMRS_Q6K;
     if (quant && d0 % QK_K)
         return ctx->fail(LLMRS_ERR_SHAPE, "upload_tensor: in_features %u is not a multiple of 256", d0);
+    if (is_block32(dtype) && d0 % 32)
+        return ctx->fail(LLMRS_ERR_SHAPE, "upload_tensor: in_features %u is not a multiple of 32", d0);
     if (!storage_size(dtype, n_elems, &want))
-        return ctx->fail(LLMRS_ERR_DTYPE, "upload_tensor: dtype %u is not supported (F32, BF16, I32, Q4_K, Q6_K)", dtype);
+        return ctx->fail(LLMRS_ERR_DTYPE, "upload_tensor: dtype %u is not supported (F32, F16, BF16, I32, Q4_0, Q8_0, Q4_K, Q6_K)", dtype);
     if (want != nbytes)
         return ctx->fail(LLMRS_ERR_SHAPE, "upload_tensor: %zu bytes given, shape needs %zu", nbytes, want);
     DeviceGuard guard(ctx->device);
     const int K = (int)d0, N = (int)(d1 ? d1 : 1);
-    const size_t dev_bytes = quant ? weight_device_bytes((int)dtype, K, N) : nbytes;
+    const size_t dev_bytes = quant ? weight_device_bytes((int)dtype, K, N) : is_block32(dtype) ? block32_device_bytes((int)dtype, K, N) : nbytes;
     void *p = nullptr;
     cudaError_t e = cudaMalloc(&p, dev_bytes);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "upload_tensor: cudaMalloc");
-    uint32_t layout = LLMRS_LAYOUT_RAW;
-    if (dtype == LLMRS_Q6K) {
+    const uint32_t layout = weight_layout(dtype);
+    if (layout != LLMRS_LAYOUT_RAW) {
         // Re-layout on the device: raw bytes into a staging buffer, one kernel, staging freed.
         void *stage = nullptr;
         e = cudaMalloc(&stage, nbytes);
         if (e == cudaSuccess) e = cudaMemcpyAsync(stage, host, nbytes, cudaMemcpyHostToDevice, ctx->stream);
         if (e == cudaSuccess) {
-            e = launch_q6k_repack((const uint8_t *)stage, (uint8_t *)p, K, N, ctx->stream);
+            if (dtype == LLMRS_Q6K) e = launch_q6k_repack((const uint8_t *)stage, (uint8_t *)p, K, N, ctx->stream);
+            else e = launch_block32_repack((int)dtype, (const uint8_t *)stage, (uint8_t *)p,
+                                           (uint8_t *)p + (size_t)N * block32_quant_stride((int)dtype, K), K, N, ctx->stream);
             ctx->launches++;
         }
         cudaError_t e2 = cudaStreamSynchronize(ctx->stream);
         if (stage) cudaFree(stage);
         if (e == cudaSuccess) e = e2;
-        layout = LLMRS_LAYOUT_Q6K_SLICES;
     } else {
         e = cudaMemcpyAsync(p, host, nbytes, cudaMemcpyHostToDevice, ctx->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);   // host memory is not retained
@@ -506,9 +527,11 @@ int llmrs_cuda_upload_gguf_tensor_rows(llmrs_ctx *ctx, const llmrs_gguf *gf, con
     const bool quant = dtype == LLMRS_Q4K || dtype == LLMRS_Q6K;
     if (quant && d0 % QK_K)
         return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s: in_features %u is not a multiple of 256", name, d0);
+    if (is_block32(dtype) && d0 % 32)
+        return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s: in_features %u is not a multiple of 32", name, d0);
     size_t whole = 0;
     if (!storage_size(dtype, (uint64_t)d0 * (d1 ? d1 : 1), &whole))
-        return ctx->fail(LLMRS_ERR_DTYPE, "upload_gguf_tensor: %s: dtype %u is not supported (F32, BF16, I32, Q4_K, Q6_K)", name, dtype);
+        return ctx->fail(LLMRS_ERR_DTYPE, "upload_gguf_tensor: %s: dtype %u is not supported (F32, F16, BF16, I32, Q4_0, Q8_0, Q4_K, Q6_K)", name, dtype);
     if (whole != t->nbytes) return ctx->fail(LLMRS_ERR_SHAPE, "upload_gguf_tensor: %s: directory and shape disagree on the size", name);
     // a slice of the rows: rows [first_row, first_row + n_rows) of the outer dimension
     const uint64_t all_rows = d1 ? d1 : 1;
@@ -525,11 +548,11 @@ int llmrs_cuda_upload_gguf_tensor_rows(llmrs_ctx *ctx, const llmrs_gguf *gf, con
     for (int i = 0; i < 2 && e == cudaSuccess; i++) {
         if (!ctx->stage_host[i]) e = cudaHostAlloc((void **)&ctx->stage_host[i], ctx->upload_piece, cudaHostAllocDefault);
         if (e == cudaSuccess && !ctx->stage_done[i]) e = cudaEventCreateWithFlags(&ctx->stage_done[i], cudaEventDisableTiming);
-        if (e == cudaSuccess && dtype == LLMRS_Q6K && !ctx->stage_dev[i]) e = cudaMalloc((void **)&ctx->stage_dev[i], ctx->upload_piece);
+        if (e == cudaSuccess && weight_layout(dtype) != LLMRS_LAYOUT_RAW && !ctx->stage_dev[i]) e = cudaMalloc((void **)&ctx->stage_dev[i], ctx->upload_piece);
     }
     if (e != cudaSuccess) return ctx->cuda_fail(e, "upload_gguf_tensor: staging buffers");
     const int K = (int)d0, N = (int)(d1 ? d1 : 1);
-    const size_t dev_bytes = quant ? weight_device_bytes((int)dtype, K, N) : want;
+    const size_t dev_bytes = quant ? weight_device_bytes((int)dtype, K, N) : is_block32(dtype) ? block32_device_bytes((int)dtype, K, N) : want;
     uint8_t *p = nullptr;
     e = cudaMalloc((void **)&p, dev_bytes);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "upload_gguf_tensor: cudaMalloc");
@@ -550,10 +573,15 @@ int llmrs_cuda_upload_gguf_tensor_rows(llmrs_ctx *ctx, const llmrs_gguf *gf, con
         if (e != cudaSuccess) break;
         io_ok = llmrs::gguf_pread_parallel(g->fd, ctx->stage_host[sb], file_pos + row * row_bytes, bytes, ctx->upload_readers);
         if (!io_ok) break;
-        if (dtype == LLMRS_Q6K) {
+        if (weight_layout(dtype) != LLMRS_LAYOUT_RAW) {
             e = cudaMemcpyAsync(ctx->stage_dev[sb], ctx->stage_host[sb], bytes, cudaMemcpyHostToDevice, ctx->stream);
             if (e == cudaSuccess) {
-                e = launch_q6k_repack(ctx->stage_dev[sb], p + row * q6k_row_stride(K), K, (int)rows, ctx->stream);
+                if (dtype == LLMRS_Q6K)
+                    e = launch_q6k_repack(ctx->stage_dev[sb], p + row * q6k_row_stride(K), K, (int)rows, ctx->stream);
+                else
+                    e = launch_block32_repack((int)dtype, ctx->stage_dev[sb], p + row * block32_quant_stride((int)dtype, K),
+                                              p + (size_t)N * block32_quant_stride((int)dtype, K) + row * block32_scale_stride(K), K,
+                                              (int)rows, ctx->stream);
                 ctx->launches++;
             }
         } else {
@@ -568,8 +596,7 @@ int llmrs_cuda_upload_gguf_tensor_rows(llmrs_ctx *ctx, const llmrs_gguf *gf, con
         if (!io_ok) return ctx->fail(LLMRS_ERR_IO, "IO error: reading tensor %s", name);
         return ctx->cuda_fail(e, "upload_gguf_tensor: copy");
     }
-    *out = llmrs_buf{p, dev_bytes, dtype, d0, d1, dtype == LLMRS_Q6K ? (uint32_t)LLMRS_LAYOUT_Q6K_SLICES : (uint32_t)LLMRS_LAYOUT_RAW,
-                     1u, (uint32_t)ctx->device};
+    *out = llmrs_buf{p, dev_bytes, dtype, d0, d1, weight_layout(dtype), 1u, (uint32_t)ctx->device};
     return LLMRS_OK;
 }
 
@@ -629,14 +656,59 @@ static bool matmul_uses_decode_kernel(const llmrs_ctx *ctx, const llmrs_buf *wei
     return (int)M <= ctx->gemv_max_m || decode_kernel_cheaper(ctx, weight, M, K);
 }
 
+// matmul for the weight types beside the K-quants (metal/mod.rs:503-518, 542-562, 634-686): dense F32 / F16 /
+// BF16 and Q8_0 / Q4_0.  Up to 8 tokens the streaming kernel; dense weights from 9 tokens on run on the tensor
+// cores; the block formats take the streaming kernel in passes of 8 tokens (the reference runs one matvec per
+// position for them).
+static int matmul_other(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input) {
+    const uint32_t K = weight->dim0, N = weight->dim1 ? weight->dim1 : 1, M = input->dim1 ? input->dim1 : 1;
+    if (weight->layout != weight_layout(weight->dtype))
+        return ctx->fail(LLMRS_ERR_ARG, "matmul: weight was not created by upload_tensor (layout %u)", weight->layout);
+    if (!dense_elem_bytes(input->dtype) || !dense_elem_bytes(out->dtype))
+        return ctx->fail(LLMRS_ERR_DTYPE, "matmul: activations must be F32 or BF16 (got %u -> %u)", input->dtype, out->dtype);
+    if (!dense_gemv_shape_ok((int)weight->dtype, (int)K))
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u: a multiple of %d is needed for this weight type", K,
+                         is_block32(weight->dtype) ? 32 : weight->dtype == LLMRS_F32 ? 4 : 8);
+    if (input->dim0 != K)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul: input has %u features, weight expects %u", input->dim0, K);
+    if (out->dim0 != N || (out->dim1 ? out->dim1 : 1) != M)
+        return ctx->fail(LLMRS_ERR_SHAPE, "matmul: output is [%u, %u], expected [%u, %u]", out->dim0, out->dim1, N, M);
+    if (weight->device != (uint32_t)ctx->device || input->device != (uint32_t)ctx->device || out->device != (uint32_t)ctx->device)
+        return ctx->fail(LLMRS_ERR_ARG, "matmul: buffers belong to another device");
+    if ((reinterpret_cast<uintptr_t>(input->dptr) & 15) || (reinterpret_cast<uintptr_t>(weight->dptr) & 15))
+        return ctx->fail(LLMRS_ERR_ARG, "matmul: buffers must be 16-byte aligned");
+    DeviceGuard guard(ctx->device);
+    const bool tensor_cores = M > 8 && !is_block32(weight->dtype) && dense_gemm_shape_ok((int)weight->dtype, (int)K);
+    cudaError_t e = cudaSuccess;
+    if (tensor_cores) {
+        e = ctx->reserve_scratch(dense_gemm_scratch_bytes((int)weight->dtype, (int)K, (int)M));
+        if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: scratch (grow it with one call outside graph capture)");
+    }
+    e = ctx->begin_work();
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: event");
+    char perf_name[48];
+    if (ctx->perf) snprintf(perf_name, sizeof perf_name, "matmul %s %s", dtype_name(weight->dtype), tensor_cores ? "tensor cores" : "streaming kernel");
+    PerfScope perf(ctx, perf_name, matmul_bytes(weight, input, out), matmul_flops(weight, input));
+    if (tensor_cores)
+        e = launch_dense_gemm((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
+                              (int)out->dtype, (int)K, (int)N, (int)M, ctx->scratch, ctx->sm_count, ctx->sink(), ctx->stream,
+                              &ctx->launches);
+    else
+        e = launch_dense_gemv((int)weight->dtype, (const uint8_t *)weight->dptr, input->dptr, (int)input->dtype, out->dptr,
+                              (int)out->dtype, (int)K, (int)N, (int)M, ctx->sm_count, ctx->pdl, ctx->stream, &ctx->launches);
+    if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: launch");
+    return LLMRS_OK;
+}
+
 int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input) {
     if (!ctx) return LLMRS_ERR_ARG;
     if (!out || !weight || !input || !out->dptr || !weight->dptr || !input->dptr)
         return ctx->fail(LLMRS_ERR_ARG, "matmul: null buffer");
     // K = weight.dim0, N = weight.dim1, M = max(input.dim1, 1)  (metal/mod.rs:497-499)
     const uint32_t K = weight->dim0, N = weight->dim1 ? weight->dim1 : 1, M = input->dim1 ? input->dim1 : 1;
+    if (is_other_weight(weight->dtype)) return matmul_other(ctx, out, weight, input);
     if (weight->dtype != LLMRS_Q4K && weight->dtype != LLMRS_Q6K)
-        return ctx->fail(LLMRS_ERR_DTYPE, "matmul: weight dtype %u is not Q4_K/Q6_K", weight->dtype);
+        return ctx->fail(LLMRS_ERR_DTYPE, "matmul: weight dtype %u is not supported (F32, F16, BF16, Q4_0, Q8_0, Q4_K, Q6_K)", weight->dtype);
     const uint32_t want_layout = weight->dtype == LLMRS_Q6K ? LLMRS_LAYOUT_Q6K_SLICES : LLMRS_LAYOUT_RAW;
     if (weight->layout != want_layout)
         return ctx->fail(LLMRS_ERR_ARG, "matmul: weight was not created by upload_tensor (layout %u)", weight->layout);
@@ -948,9 +1020,22 @@ int llmrs_cuda_matmul_add(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weigh
     if (!decode) {                                   // tensor-core path: the matmul, then the add as its own kernel
         const uint8_t *r0 = (const uint8_t *)residual->dptr, *o0 = (const uint8_t *)out->dptr;
         const bool overlap = r0 < o0 + out->nbytes && o0 < r0 + residual->nbytes;
-        if (!overlap || !input || !quant || !out->dptr) {
+        if (!overlap || !input || !weight || !out->dptr) {
             int rc = llmrs_cuda_matmul(ctx, out, weight, input);
             return rc != LLMRS_OK ? rc : llmrs_cuda_add(ctx, out, out, residual);
+        }
+        if (!quant) {                                // another weight type: the product goes to a buffer of its own first
+            const size_t need = (size_t)out->dim0 * (out->dim1 ? out->dim1 : 1) * sizeof(float);
+            DeviceGuard guard(ctx->device);
+            cudaError_t e = ctx->grow(&ctx->norm_tmp, &ctx->norm_tmp_bytes, need);
+            if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_add: temporary (grow it with one call outside graph capture)");
+            llmrs_buf tmp = *out;
+            tmp.dptr = ctx->norm_tmp;
+            tmp.nbytes = need;
+            tmp.dtype = LLMRS_F32;
+            tmp.owned = 0;
+            int rc = llmrs_cuda_matmul(ctx, &tmp, weight, input);
+            return rc != LLMRS_OK ? rc : llmrs_cuda_add(ctx, out, &tmp, residual);
         }
         // The residual IS the output (x = x + matmul(w, h), the usual call): the product goes to float32
         // scratch behind the GEMM's own scratch first, because the GEMM would overwrite the residual.
@@ -1161,17 +1246,18 @@ int llmrs_cuda_embed(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *table, con
     if (!ctx) return LLMRS_ERR_ARG;
     if (!out || !table || !out->dptr || !table->dptr || (!tokens && n_tokens))
         return ctx->fail(LLMRS_ERR_ARG, "embed: null pointer");
-    if (table->dtype != LLMRS_Q4K && table->dtype != LLMRS_Q6K)
-        return ctx->fail(LLMRS_ERR_DTYPE, "embed: table dtype %u is not Q4_K/Q6_K", table->dtype);
+    const bool dense_table = table->dtype == LLMRS_F32 || table->dtype == LLMRS_F16 || table->dtype == LLMRS_BF16;
+    if (!dense_table && table->dtype != LLMRS_Q4K && table->dtype != LLMRS_Q6K)      // the reference's list: metal/mod.rs:852-859
+        return ctx->fail(LLMRS_ERR_DTYPE, "embed: table dtype %u is not F32/F16/BF16/Q4_K/Q6_K", table->dtype);
     if (table->dtype == LLMRS_Q6K && table->layout != LLMRS_LAYOUT_Q6K_SLICES)
         return ctx->fail(LLMRS_ERR_ARG, "embed: table was not created by upload_tensor");
     if (!dense_elem_bytes(out->dtype)) return ctx->fail(LLMRS_ERR_DTYPE, "embed: output must be F32 or BF16");
     const uint32_t K = table->dim0, vocab = table->dim1 ? table->dim1 : 1;
-    if (K % QK_K) return ctx->fail(LLMRS_ERR_SHAPE, "embed: dim %u is not a multiple of 256", K);
+    if (!dense_table && K % QK_K) return ctx->fail(LLMRS_ERR_SHAPE, "embed: dim %u is not a multiple of 256", K);
     if (out->dim0 != K || (out->dim1 ? out->dim1 : 1) != (n_tokens ? n_tokens : 1))
         return ctx->fail(LLMRS_ERR_SHAPE, "embed: output is [%u, %u], expected [%u, %u]", out->dim0, out->dim1, K, n_tokens);
     if (n_tokens > 65535) return ctx->fail(LLMRS_ERR_SHAPE, "embed: %u tokens in one call (at most 65535)", n_tokens);
-    if (reinterpret_cast<uintptr_t>(out->dptr) & 15) return ctx->fail(LLMRS_ERR_ARG, "embed: output must be 16-byte aligned");
+    if (!dense_table && (reinterpret_cast<uintptr_t>(out->dptr) & 15)) return ctx->fail(LLMRS_ERR_ARG, "embed: output must be 16-byte aligned");
     if (table->device != (uint32_t)ctx->device || out->device != (uint32_t)ctx->device)
         return ctx->fail(LLMRS_ERR_ARG, "embed: buffers belong to another device");
     if (n_tokens == 0) return LLMRS_OK;
@@ -1190,9 +1276,14 @@ int llmrs_cuda_embed(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *table, con
     }
     e = ctx->begin_work();
     if (e != cudaSuccess) return ctx->cuda_fail(e, "embed: event");
-    PerfScope perf(ctx, "embed", (double)n_tokens * K * ((table->dtype == LLMRS_Q4K ? 144.0 : 210.0) / 256.0 + dense_elem_bytes(out->dtype)), 0.0);
+    size_t table_row_bytes = 0;
+    storage_size(table->dtype, K, &table_row_bytes);
+    PerfScope perf(ctx, "embed", (double)n_tokens * ((double)table_row_bytes + (double)K * dense_elem_bytes(out->dtype)), 0.0);
     e = cudaMemcpyAsync(ctx->tokens, tokens, (size_t)n_tokens * sizeof(uint32_t), cudaMemcpyHostToDevice, ctx->stream);
-    if (e == cudaSuccess)
+    if (e == cudaSuccess && dense_table)
+        e = launch_dense_embed((int)table->dtype, (const uint8_t *)table->dptr, (int)K, vocab, ctx->tokens, (int)n_tokens, out->dptr,
+                               (int)out->dtype, ctx->dev_error, ctx->stream, false);
+    else if (e == cudaSuccess)
         e = launch_embed((int)table->dtype, (const uint8_t *)table->dptr, (int)K, vocab, ctx->tokens, (int)n_tokens,
                          out->dptr, (int)out->dtype, ctx->dev_error, ctx->stream);
     if (e != cudaSuccess) return ctx->cuda_fail(e, "embed: launch");
@@ -1304,11 +1395,15 @@ int llmrs_cuda_matmul_allgather_max_tokens(uint32_t weight_dtype, uint32_t in_fe
 int llmrs_cuda_dequantize(llmrs_ctx *ctx, const llmrs_buf *weight, float *dev_out) {
     if (!ctx) return LLMRS_ERR_ARG;
     if (!weight || !weight->dptr || !dev_out) return ctx->fail(LLMRS_ERR_ARG, "dequantize: null pointer");
-    if (weight->dtype != LLMRS_Q4K && weight->dtype != LLMRS_Q6K)
-        return ctx->fail(LLMRS_ERR_DTYPE, "dequantize: weight dtype %u is not Q4_K/Q6_K", weight->dtype);
+    if (!is_kquant(weight->dtype) && !is_other_weight(weight->dtype))
+        return ctx->fail(LLMRS_ERR_DTYPE, "dequantize: weight dtype %u is not supported", weight->dtype);
     DeviceGuard guard(ctx->device);
     cudaError_t e = ctx->begin_work();
-    if (e == cudaSuccess) {
+    if (e == cudaSuccess && is_other_weight(weight->dtype)) {
+        e = launch_dense_dequant((int)weight->dtype, (const uint8_t *)weight->dptr, (int)weight->dim0,
+                                 (int)(weight->dim1 ? weight->dim1 : 1), dev_out, ctx->stream);
+        ctx->launches++;
+    } else if (e == cudaSuccess) {
         e = launch_dequant((int)weight->dtype, (const uint8_t *)weight->dptr, (int)weight->dim0,
                            (int)(weight->dim1 ? weight->dim1 : 1), dev_out, ctx->stream);
         ctx->launches++;

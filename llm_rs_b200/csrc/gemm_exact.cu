@@ -288,38 +288,68 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
 
     if (warp < DEQ_WARPS) {
         // ---------------- raw bytes (shared memory) -> f16 operand (tensor memory) ----------------
+        // A thread keeps the raw bytes of its half-block in registers.  The bytes of the NEXT block are
+        // fetched from the ring right after the stores of this block have been issued, so that their
+        // shared-memory latency, the completion of the stores and the barrier round trip overlap.
         const int r = threadIdx.x & 127, g = threadIdx.x >> 7;
         const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + C::A_BASE_COL;
         bool ok = true;
         uint32_t it0 = 0, blk = 0;                    // stages / blocks of the units before this one
         UnitIter ui;
         Unit u;
-        while (ok && ui.next(sc, u)) {
-            for (int b = u.b0; b < u.b1; b++, blk++) {
-                const uint32_t rs = blk % R;
-                if (!mbar_wait(&raw_full[rs], (blk / R) & 1, p.wait_limit)) {
-                    report_error(p.err, KERR_FULL_WAIT);
-                    ok = false;
-                    break;
+        // raw bytes of the current block
+        uint4 hdr, q[4];                              // Q4_K: header, 64 quant bytes of this half
+        RawQ6Half raw6;                               // Q6_K
+        uint16_t dbits = 0;
+        auto fetch = [&](uint32_t bk, int b_in_row) -> bool {      // ring slot of block number bk -> registers
+            const uint32_t rs = bk % R;
+            if (!mbar_wait(&raw_full[rs], (bk / R) & 1, p.wait_limit)) {
+                report_error(p.err, KERR_FULL_WAIT);
+                return false;
+            }
+            const uint8_t *slot = raw_ring + (size_t)rs * C::RAW_SLOT_BYTES;
+            if constexpr (QT == 0) {
+                const uint8_t *rowp = slot + (size_t)r * Q4K_BLOCK_BYTES;
+                hdr = lds128(rowp);
+#pragma unroll
+                for (int i = 0; i < 4; i++) q[i] = lds128(rowp + 16 + 64 * g + 16 * i);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    const uint8_t *sl = slot + (size_t)(2 * g + c) * C::Q6_SLICE_BOX + (size_t)r * 48;
+                    raw6.ql0[c] = lds128(sl);
+                    raw6.ql1[c] = lds128(sl + 16);
+                    raw6.qh[c] = lds128(sl + 32);
                 }
-                const uint8_t *slot = raw_ring + (size_t)rs * C::RAW_SLOT_BYTES;
+                raw6.sc = *reinterpret_cast<const uint2 *>(slot + 4 * C::Q6_SLICE_BOX + (size_t)r * 16 + 8 * g);
+                dbits = *reinterpret_cast<const uint16_t *>(slot + 4 * C::Q6_SLICE_BOX + C::Q6_SMALL_BOX + (size_t)r * 16 +
+                                                            ((2 * (b_in_row & 15)) & 15));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&raw_empty[rs]);          // the slot may be refilled
+            return true;
+        };
+        bool have = false;
+        while (ok && ui.next(sc, u)) {
+            UnitIter peek = ui;
+            Unit un = u;
+            const bool has_next_unit = peek.next(sc, un);
+            if (!have) {
+                ok = fetch(blk, u.b0);
+                have = true;
+                if (!ok) break;
+            }
+            for (int b = u.b0; b < u.b1; b++, blk++) {
                 const uint32_t it = it0 + 2u * (uint32_t)(b - u.b0) + (uint32_t)g;
                 const uint32_t s = it % S;
                 const uint32_t a_taddr = lane_base + s * C::A_STAGE_COLS;
+                if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
+                    report_error(p.err, KERR_EMPTY_WAIT);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
                 if constexpr (QT == 0) {
-                    const uint8_t *rowp = slot + (size_t)r * Q4K_BLOCK_BYTES;
-                    const uint4 hdr = lds128(rowp);
-                    uint4 q[4];
-#pragma unroll
-                    for (int i = 0; i < 4; i++) q[i] = lds128(rowp + 16 + 64 * g + 16 * i);
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&raw_empty[rs]);          // the slot may be refilled
-                    if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
-                        report_error(p.err, KERR_EMPTY_WAIT);
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
                     if (g == 0) {
                         dequant_q4k_half_exact<0>(hdr, q, a_taddr);
                         min_operand_q4k(hdr, a_taddr + C::A_MAIN_COLS);
@@ -328,29 +358,17 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                         dequant_q4k_half_exact<1>(hdr, q, a_taddr);
                     }
                 } else {
-                    const int bl = b & 15;
-                    RawQ6Half raw;
-#pragma unroll
-                    for (int c = 0; c < 2; c++) {
-                        const uint8_t *sl = slot + (size_t)(2 * g + c) * C::Q6_SLICE_BOX + (size_t)r * 48;
-                        raw.ql0[c] = lds128(sl);
-                        raw.ql1[c] = lds128(sl + 16);
-                        raw.qh[c] = lds128(sl + 32);
-                    }
-                    raw.sc = *reinterpret_cast<const uint2 *>(slot + 4 * C::Q6_SLICE_BOX + (size_t)r * 16 + 8 * g);
-                    const uint16_t dbits = *reinterpret_cast<const uint16_t *>(slot + 4 * C::Q6_SLICE_BOX + C::Q6_SMALL_BOX +
-                                                                               (size_t)r * 16 + ((2 * bl) & 15));
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&raw_empty[rs]);          // the slot may be refilled
-                    if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
-                        report_error(p.err, KERR_EMPTY_WAIT);
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const bool any_lo = __any_sync(0xffffffffu, dequant_q6k_half_exact(raw, a_taddr) != 0u);
+                    const bool any_lo = __any_sync(0xffffffffu, dequant_q6k_half_exact(raw6, a_taddr) != 0u);
                     if (lane == 0) lo_flag[s * 4 + (warp & 3)] = any_lo ? 1u : 0u;
                     if (g == 0) d_ring[(blk % D_RING) * TILE_ROWS + r] = f16_bits_to_f32(dbits);
+                }
+                // the next block's bytes, while this block's stores complete
+                const bool more = b + 1 < u.b1 || has_next_unit;
+                if (more) {
+                    ok = fetch(blk + 1, b + 1 < u.b1 ? b + 1 : un.b0);
+                    if (!ok) break;
+                } else {
+                    have = false;
                 }
                 tmem_st_wait();                      // this warp's tensor-memory stores have landed
                 tc_fence_before();
@@ -361,23 +379,25 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         }
     } else if (warp == DEQ_WARPS) {
         // ---------------- TMA producer of the activation tiles ----------------
-        if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            UnitIter ui;
-            Unit u;
-            while (ok && ui.next(sc, u)) {
-                const int t0 = (u.tile / w_tiles) * TN;
-                for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
-                    const uint32_t s = it % S;
-                    if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
-                        report_error(p.err, KERR_EMPTY_WAIT);
-                        ok = false;
-                        break;
-                    }
-                    const bool with_sums = MIN && (st & 1) == 0;
+        // (the whole warp walks the loop, the elected lane issues: see the MMA warp)
+        const bool leader = elect_one();
+        uint32_t it = 0;
+        bool ok = true;
+        UnitIter ui;
+        Unit u;
+        while (ok && ui.next(sc, u)) {
+            const int t0 = (u.tile / w_tiles) * TN;
+            for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
+                const uint32_t s = it % S;
+                if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
+                    report_error(p.err, KERR_EMPTY_WAIT);
+                    ok = false;
+                    break;
+                }
+                const bool with_sums = MIN && (st & 1) == 0;
+                uint8_t *dst = tiles + s * C::STAGE_BYTES;
+                if (leader) {
                     mbar_arrive_expect_tx(&full[s], (with_sums ? 6 : 4) * C::SUBTILE_BYTES);
-                    uint8_t *dst = tiles + s * C::STAGE_BYTES;
 #pragma unroll
                     for (int us = 0; us < 2; us++) {     // x_hi tile, then x_lo tile, of each 64-wide K slice
                         tma_load_2d(dst + (2 * us) * C::SUBTILE_BYTES, &maps.x, st * 128 + us * BK, t0, &full[s]);
@@ -388,25 +408,27 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                         tma_load_2d(dst + 5 * C::SUBTILE_BYTES, &maps.xs, (st >> 1) * XS_SLOTS, p.M + t0, &full[s]);
                     }
                 }
+                __syncwarp();
             }
         }
     } else if (warp == RAW_WARP) {
         // ---------------- TMA producer of the raw weight blocks ----------------
-        if (lane == 0) {
-            uint32_t blk = 0;
-            bool ok = true;
-            UnitIter ui;
-            Unit u;
-            while (ok && ui.next(sc, u)) {
-                const int n0 = (u.tile % w_tiles) * TILE_ROWS;
-                for (int b = u.b0; b < u.b1; b++, blk++) {
-                    const uint32_t rs = blk % R;
-                    if (blk >= (uint32_t)R && !mbar_wait(&raw_empty[rs], ((blk / R) - 1) & 1, p.wait_limit)) {
-                        report_error(p.err, KERR_EMPTY_WAIT);
-                        ok = false;
-                        break;
-                    }
-                    uint8_t *slot = raw_ring + (size_t)rs * C::RAW_SLOT_BYTES;
+        const bool leader = elect_one();
+        uint32_t blk = 0;
+        bool ok = true;
+        UnitIter ui;
+        Unit u;
+        while (ok && ui.next(sc, u)) {
+            const int n0 = (u.tile % w_tiles) * TILE_ROWS;
+            for (int b = u.b0; b < u.b1; b++, blk++) {
+                const uint32_t rs = blk % R;
+                if (blk >= (uint32_t)R && !mbar_wait(&raw_empty[rs], ((blk / R) - 1) & 1, p.wait_limit)) {
+                    report_error(p.err, KERR_EMPTY_WAIT);
+                    ok = false;
+                    break;
+                }
+                uint8_t *slot = raw_ring + (size_t)rs * C::RAW_SLOT_BYTES;
+                if (leader) {
                     mbar_arrive_expect_tx(&raw_full[rs], C::RAW_SLOT_BYTES);
                     if constexpr (QT == 0) {
                         tma_load_2d(slot, &maps.w_a, b * Q4K_BLOCK_BYTES, n0, &raw_full[rs]);
@@ -422,6 +444,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                                     base + 208 * nbc + ((2 * bl) & ~15), n0, &raw_full[rs]);
                     }
                 }
+                __syncwarp();
             }
         }
     } else if (warp == DEQ_WARPS + 1) {

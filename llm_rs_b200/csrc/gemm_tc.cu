@@ -430,20 +430,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
         }
     } else if (warp == DEQ_WARPS) {
         // ---------------- TMA producer of the activation tiles ----------------
-        if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            UnitIter ui;
-            Unit u;
-            while (ok && ui.next(sc, u)) {
-                const int t0 = (u.tile / w_tiles) * TN;
-                for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
-                    const uint32_t s = it % S;
-                    if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
-                        report_error(p.err, KERR_EMPTY_WAIT);
-                        ok = false;
-                        break;
-                    }
+        // (the whole warp walks the loop, the elected lane issues: see the MMA warp)
+        const bool leader = elect_one();
+        uint32_t it = 0;
+        bool ok = true;
+        UnitIter ui;
+        Unit u;
+        while (ok && ui.next(sc, u)) {
+            const int t0 = (u.tile / w_tiles) * TN;
+            for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
+                const uint32_t s = it % S;
+                if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
+                    report_error(p.err, KERR_EMPTY_WAIT);
+                    ok = false;
+                    break;
+                }
+                if (leader) {
                     mbar_arrive_expect_tx(&full[s], C::STAGE_BYTES);
 #pragma unroll
                     for (int us = 0; us < C::KSUB; us++)
@@ -456,40 +458,46 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                                         st * C::STAGE_K + us * BK, p.M + t0, &full[s]);
                     }
                 }
+                __syncwarp();
             }
         }
     } else if (warp == DEQ_WARPS + 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            // Shared-memory descriptors differ only in their start-address field, so the loop adds to
-            // the low word of one prebuilt descriptor instead of rebuilding 64-bit values.
-            const uint64_t desc0 = umma_desc_sw128(smem_u32(tiles));
-            const uint32_t desc_hi = (uint32_t)(desc0 >> 32);
-            const uint32_t desc_lo0 = (uint32_t)desc0;
-            const uint32_t a_col0 = tmem_base + C::A_BASE_COL;
-            bool ok = true;
-            uint32_t it = 0, tcount = 0;
-            UnitIter ui;
-            Unit u;
-            for (; ok && ui.next(sc, u); tcount++) {
-                const uint32_t ab = tcount % AB;
-                // the epilogue must have read this accumulator out (unit tcount - AB) before it is overwritten
-                if (tcount >= (uint32_t)AB && !mbar_wait(&acc_empty[ab], ((tcount / AB) - 1) & 1, p.wait_limit)) {
-                    report_error(p.err, KERR_MMA_WAIT);
+        // The whole warp walks the schedule and waits on the barriers, so that descriptors and
+        // tensor-memory addresses are formed in warp-uniform code; the elected lane issues.  (With the
+        // loop under `if (lane == 0)` the issuing thread needed ~55 clocks per instruction.)
+        // Shared-memory descriptors differ only in their start-address field, so the loop adds to
+        // the low word of one prebuilt descriptor instead of rebuilding 64-bit values.
+        const bool leader = elect_one();
+        const uint64_t desc0 = umma_desc_sw128(smem_u32(tiles));
+        const uint32_t desc_hi = (uint32_t)(desc0 >> 32);
+        const uint32_t desc_lo0 = (uint32_t)desc0;
+        const uint32_t a_col0 = tmem_base + C::A_BASE_COL;
+        bool ok = true;
+        uint32_t it = 0, tcount = 0;
+        UnitIter ui;
+        Unit u;
+        for (; ok && ui.next(sc, u); tcount++) {
+            const uint32_t ab = tcount % AB;
+            // the epilogue must have read this accumulator out (unit tcount - AB) before it is overwritten
+            if (tcount >= (uint32_t)AB && !mbar_wait(&acc_empty[ab], ((tcount / AB) - 1) & 1, p.wait_limit)) {
+                report_error(p.err, KERR_MMA_WAIT);
+                break;
+            }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + ab * C::ACC_COLS;
+            for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
+                const uint32_t s = it % S;
+                if (!mbar_wait(&full[s], (it / S) & 1, p.wait_limit)) {
+                    report_error(p.err, KERR_FULL_WAIT);
+                    ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + ab * C::ACC_COLS;
-                for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
-                    const uint32_t s = it % S;
-                    if (!mbar_wait(&full[s], (it / S) & 1, p.wait_limit)) {
-                        report_error(p.err, KERR_FULL_WAIT);
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t lo_s = desc_lo0 + ((s * C::STAGE_BYTES) >> 4);
-                    const uint32_t a_s = a_col0 + s * C::A_STAGE_COLS;
+                const uint32_t lo_s = desc_lo0 + ((s * C::STAGE_BYTES) >> 4);
+                const uint32_t a_s = a_col0 + s * C::A_STAGE_COLS;
+                const uint32_t first = st == 2 * u.b0 ? 0u : 1u;
+                if (leader) {
 #pragma unroll
                     for (int us = 0; us < C::KSUB; us++)
 #pragma unroll
@@ -497,19 +505,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                             // 16 K elements further: 8 TMEM columns of A, 32 bytes inside B's swizzled row
                             const uint32_t lo = lo_s + (uint32_t)((us * C::SUBTILE_BYTES + kk * 32) >> 4);
                             const uint64_t b_desc = ((uint64_t)desc_hi << 32) | lo;
-                            umma_f16_ts(d_tmem, a_s + (uint32_t)(us * 32 + kk * 8), b_desc, IDESC,
-                                        ((st - 2 * u.b0) | us | kk) ? 1u : 0u);
+                            const uint32_t acc_flag = (us | kk) ? 1u : first;
+                            umma_f16_ts(d_tmem, a_s + (uint32_t)(us * 32 + kk * 8), b_desc, IDESC, acc_flag);
                             if constexpr (SPLIT) {       // w_lo x_hi + w_hi x_lo, into the accumulator behind the main one
                                 const uint64_t b_lo = ((uint64_t)desc_hi << 32) | (lo + (uint32_t)(C::HALF_STAGE_BYTES >> 4));
-                                umma_f16_ts(d_tmem + TN, a_s + C::A_HALF_COLS + (uint32_t)(us * 32 + kk * 8), b_desc, IDESC,
-                                            ((st - 2 * u.b0) | us | kk) ? 1u : 0u);
+                                umma_f16_ts(d_tmem + TN, a_s + C::A_HALF_COLS + (uint32_t)(us * 32 + kk * 8), b_desc, IDESC, acc_flag);
                                 umma_f16_ts(d_tmem + TN, a_s + (uint32_t)(us * 32 + kk * 8), b_lo, IDESC, 1u);
                             }
                         }
                     umma_commit(&empty[s]);        // stage free once these MMAs have read it
                 }
-                if (ok) umma_commit(&acc_full[ab]);   // accumulator of this unit complete
+                __syncwarp();
             }
+            if (ok && leader) umma_commit(&acc_full[ab]);   // accumulator of this unit complete
+            __syncwarp();
         }
     } else {
         // ---------------- epilogue: TMEM -> registers -> shared staging -> global ----------------
@@ -929,6 +938,13 @@ static size_t scratch_x_bytes(int K, int M) {
 }
 
 size_t gemm_scratch_bytes(int K, int M) { return scratch_x_bytes(K, M) + (size_t)M * sizeof(float); }
+
+cudaError_t launch_activations_to_f16(const void *x, int x_dtype, int K, int M, void *out_f16, float *tok_scale,
+                                      cudaStream_t s) {
+    if (K <= 0 || M <= 0 || K % 8) return cudaErrorInvalidValue;
+    activations_to_f16_kernel<<<(unsigned)M, 256, 0, s>>>(x, x_dtype == DT_BF16, K, (__half *)out_f16, nullptr, tok_scale);
+    return cudaGetLastError();
+}
 
 // Split workspace: [2 * sms counters in 4 KiB][2 * sms slots of 128 x 256 floats].
 size_t gemm_split_counter_bytes() { return 4096; }

@@ -26,7 +26,7 @@ struct ErrSink {
 };
 
 // GGUF dtype ids (src/tensor/mod.rs:3-33); same values as enum llmrs_dtype.
-constexpr int DT_F32 = 0, DT_Q4K = 12, DT_Q6K = 14, DT_BF16 = 30;
+constexpr int DT_F32 = 0, DT_F16 = 1, DT_Q4_0 = 2, DT_Q8_0 = 8, DT_Q4K = 12, DT_Q6K = 14, DT_BF16 = 30;
 
 // Device layout of Q6_K weights ("slice-major chunks", LLMRS_LAYOUT_Q6K_SLICES).  A row is cut
 // into chunks of 16 blocks (the last chunk of a row may hold fewer, nbc).  A chunk holds the same
@@ -196,6 +196,36 @@ size_t gemm_exact_scratch_bytes(int K, int M);
 cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                               int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
                               cudaStream_t s, uint64_t *launches, const GemmGather *gather = nullptr);
+
+// Activations -> per-token scaled f16 (one CTA per token): out_f16 [M, K], tok_scale[M] the factors that
+// undo the power-of-two scaling.  The conversion kernel of launch_gemm, for the dense F16 GEMM.
+cudaError_t launch_activations_to_f16(const void *x, int x_dtype, int K, int M, void *out_f16, float *tok_scale,
+                                      cudaStream_t s);
+
+// ---- the other weight types of the reference's matmul: dense F32 / F16 / BF16, Q8_0, Q4_0 (dense.cu) ----
+// Q8_0 / Q4_0 device layout ("planes"): [N rows of quants, block32_quant_stride() bytes apart][N rows of f16
+// scales, block32_scale_stride() bytes apart]; quant bytes in file order (Q8_0: K int8; Q4_0: K/2 bytes, byte
+// j of a block holding its elements 2j (low nibble) and 2j+1 (high nibble), minus 8, as the reference reads it).
+size_t block32_quant_stride(int dtype, int K);
+size_t block32_scale_stride(int K);
+size_t block32_device_bytes(int dtype, int K, int N);
+// `rows` rows of file blocks at raw -> quants at dev_q (first row), scales at dev_s (first row).
+cudaError_t launch_block32_repack(int dtype, const uint8_t *raw, uint8_t *dev_q, uint8_t *dev_s, int K, int rows,
+                                  cudaStream_t s);
+// Any of the five types -> float32 [N, K] (test aid; bit-exact with the CPU dequantisation).
+cudaError_t launch_dense_dequant(int wdtype, const uint8_t *w, int K, int N, float *out, cudaStream_t s);
+// Streaming matmul for up to 8 tokens per pass (more tokens: several passes).
+bool dense_gemv_shape_ok(int wdtype, int K);
+cudaError_t launch_dense_gemv(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype, int K,
+                              int N, int M, int sm_count, bool pdl, cudaStream_t s, uint64_t *launches);
+// Dense weights on the tensor cores (tcgen05, both operands through TMA into shared memory).
+bool dense_gemm_shape_ok(int wdtype, int K);
+size_t dense_gemm_scratch_bytes(int wdtype, int K, int M);
+cudaError_t launch_dense_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype, int K,
+                              int N, int M, void *scratch, int sm_count, ErrSink err_word, cudaStream_t s, uint64_t *launches);
+// Embedding lookup from a dense table.
+cudaError_t launch_dense_embed(int wdtype, const uint8_t *table, int K, uint32_t vocab, const uint32_t *dev_tokens, int n_tokens,
+                               void *out, int out_dtype, uint32_t *err_word, cudaStream_t s, bool pdl);
 
 // The same GEMM with its scratch in a fixed 8 MiB device array that is part of the library image:
 // no allocation on this path.  `device` must be the current device; the first call on a device

@@ -1,5 +1,6 @@
 /*
- * CPU oracle for the Q4_K / Q6_K dequantize-matmul of llm-rs.
+ * CPU oracle for the dequantize-matmul of llm-rs: Q4_K / Q6_K (the measured path) and the other
+ * weight types its dispatcher accepts (F32, F16, BF16, Q8_0, Q4_0).
  *
  * TEST INFRASTRUCTURE ONLY.  This file restates, in plain C, the CPU code the
  * reference checks its backends against.  It is linked by tests/, by
@@ -19,6 +20,12 @@
  *   dequant_q4k_row ........ tests/ops.rs:41-59
  *   q6k_elem ............... shaders/ops.metal:28-42
  *   dequant_q6k_row ........ shaders/ops.metal:322-334 and :953-964 (no CPU code exists upstream)
+ *   dense rows (F32/F16/BF16)  shaders/ops.metal:52-159 (weight widened to float, multiplied with the input)
+ *   dequant_q8_0_row ....... shaders/ops.metal:192-218 (34-byte blocks: f16 scale, 32 int8)
+ *   dequant_q4_0_row ....... shaders/ops.metal:161-190 (18-byte blocks: f16 scale, 16 bytes of nibbles;
+ *                            element e of a block is the LOW nibble of byte e/2 for even e and the
+ *                            HIGH nibble for odd e, minus 8 -- the reference's own order, which is
+ *                            not the order of ggml's Q4_0, where byte j holds elements j and j+16)
  *   matmul_ref_f32 ......... tests/ops.rs:116-136 (dequantise all rows, sequential f32 accumulate)
  *   Xor / random_* ......... tests/ops.rs:14-25, 66-85, 93
  */
@@ -158,20 +165,67 @@ void llmrs_oracle_dequant_q6k_row(const uint8_t *row, size_t n_blocks, float *ou
     }
 }
 
+/* ---------------- the other weight types ---------------- */
+
+/* Q8_0: blocks of 32 weights, 34 bytes: f16 scale then 32 int8. shaders/ops.metal:192-218 */
+void llmrs_oracle_dequant_q8_0_row(const uint8_t *row, size_t n_blocks, float *out) {
+    for (size_t b = 0; b < n_blocks; b++) {
+        const uint8_t *blk = row + b * 34;
+        float scale = llmrs_oracle_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+        for (int l = 0; l < 32; l++) out[b * 32 + l] = scale * (float)(int8_t)blk[2 + l];
+    }
+}
+
+/* Q4_0 as the reference's kernel reads it: blocks of 32 weights, 18 bytes: f16 scale then 16 bytes;
+ * element l: byte l/2, low nibble for even l, high nibble for odd l, minus 8. shaders/ops.metal:161-190 */
+void llmrs_oracle_dequant_q4_0_row(const uint8_t *row, size_t n_blocks, float *out) {
+    for (size_t b = 0; b < n_blocks; b++) {
+        const uint8_t *blk = row + b * 18;
+        float scale = llmrs_oracle_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+        for (int l = 0; l < 32; l++) {
+            uint8_t packed = blk[2 + l / 2];
+            int q = (l % 2 == 0) ? (int)(packed & 0x0F) - 8 : (int)(packed >> 4) - 8;
+            out[b * 32 + l] = scale * (float)q;
+        }
+    }
+}
+
+/* GGUF type ids (src/tensor/mod.rs:3-33): 0 F32, 1 F16, 2 Q4_0, 8 Q8_0, 12 Q4_K, 14 Q6_K, 30 BF16.
+ * Elements per block and bytes per block (src/tensor/mod.rs:37-86); 0 for a type this oracle lacks. */
+static size_t block_elems(int dtype) {
+    switch (dtype) { case 0: case 1: case 30: return 1; case 2: case 8: return 32; case 12: case 14: return QK_K; default: return 0; }
+}
+static size_t block_bytes(int dtype) {
+    switch (dtype) { case 0: return 4; case 1: case 30: return 2; case 2: return 18; case 8: return 34;
+                     case 12: return Q4K_BLOCK_BYTES; case 14: return Q6K_BLOCK_BYTES; default: return 0; }
+}
+size_t llmrs_oracle_row_bytes(int dtype, size_t K) {
+    size_t be = block_elems(dtype);
+    return be && K % be == 0 ? K / be * block_bytes(dtype) : 0;
+}
+/* One weight row of K elements -> floats (every widening is exact). */
+static void dequant_row(int dtype, const uint8_t *row, size_t K, float *out) {
+    switch (dtype) {
+    case 0: memcpy(out, row, K * 4); break;
+    case 1: for (size_t i = 0; i < K; i++) out[i] = llmrs_oracle_f16_to_f32((uint16_t)(row[2 * i] | (row[2 * i + 1] << 8))); break;
+    case 30: for (size_t i = 0; i < K; i++) out[i] = llmrs_oracle_bf16_to_f32((uint16_t)(row[2 * i] | (row[2 * i + 1] << 8))); break;
+    case 2: llmrs_oracle_dequant_q4_0_row(row, K / 32, out); break;
+    case 8: llmrs_oracle_dequant_q8_0_row(row, K / 32, out); break;
+    case 12: llmrs_oracle_dequant_q4k_row(row, K / QK_K, out); break;
+    default: llmrs_oracle_dequant_q6k_row(row, K / QK_K, out); break;
+    }
+}
+
 /* ---------------- dequantise a whole weight ---------------- */
 
-/* dtype: 12 = Q4_K, 14 = Q6_K (GGUF ids, src/tensor/mod.rs:14,16). Weight = N rows of K/256 blocks. */
+/* dtype: a GGUF id from the list above. Weight = N rows of K elements (K / block size consecutive blocks). */
 int llmrs_oracle_dequant(int dtype, const uint8_t *w, size_t K, size_t N, float *out, int threads) {
-    if (K % QK_K) return 1;
-    size_t nb = K / QK_K;
-    size_t bb = dtype == 12 ? Q4K_BLOCK_BYTES : dtype == 14 ? Q6K_BLOCK_BYTES : 0;
-    if (!bb) return 2;
+    size_t rb = llmrs_oracle_row_bytes(dtype, K);
+    if (!block_elems(dtype)) return 2;
+    if (!rb) return 1;
     (void)threads;
 #pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
-    for (long long r = 0; r < (long long)N; r++) {
-        if (dtype == 12) llmrs_oracle_dequant_q4k_row(w + (size_t)r * nb * bb, nb, out + (size_t)r * K);
-        else             llmrs_oracle_dequant_q6k_row(w + (size_t)r * nb * bb, nb, out + (size_t)r * K);
-    }
+    for (long long r = 0; r < (long long)N; r++) dequant_row(dtype, w + (size_t)r * rb, K, out + (size_t)r * K);
     return 0;
 }
 
@@ -186,10 +240,9 @@ int llmrs_oracle_dequant(int dtype, const uint8_t *w, size_t K, size_t N, float 
 int llmrs_oracle_matmul(int dtype, const uint8_t *w, size_t K, size_t N,
                         const float *x, size_t M, float *out,
                         size_t row_begin, size_t row_end, int acc_f64, int threads) {
-    if (K % QK_K) return 1;
-    size_t nb = K / QK_K;
-    size_t bb = dtype == 12 ? Q4K_BLOCK_BYTES : dtype == 14 ? Q6K_BLOCK_BYTES : 0;
-    if (!bb) return 2;
+    size_t rb = llmrs_oracle_row_bytes(dtype, K);
+    if (!block_elems(dtype)) return 2;
+    if (!rb) return 1;
     if (row_end > N) row_end = N;
     (void)threads;
 #pragma omp parallel num_threads(threads > 0 ? threads : 1)
@@ -197,8 +250,7 @@ int llmrs_oracle_matmul(int dtype, const uint8_t *w, size_t K, size_t N,
         float *wrow = (float *)malloc(K * sizeof(float));
 #pragma omp for schedule(static)
         for (long long r = (long long)row_begin; r < (long long)row_end; r++) {
-            if (dtype == 12) llmrs_oracle_dequant_q4k_row(w + (size_t)r * nb * bb, nb, wrow);
-            else             llmrs_oracle_dequant_q6k_row(w + (size_t)r * nb * bb, nb, wrow);
+            dequant_row(dtype, w + (size_t)r * rb, K, wrow);
             for (size_t s = 0; s < M; s++) {
                 const float *xs = x + s * K;
                 if (acc_f64) {
@@ -223,10 +275,9 @@ int llmrs_oracle_matmul(int dtype, const uint8_t *w, size_t K, size_t N,
 int llmrs_oracle_matmul_fast(int dtype, const uint8_t *w, size_t K, size_t N,
                              const float *x, size_t M, float *out,
                              size_t row_begin, size_t row_end, int threads) {
-    if (K % QK_K) return 1;
-    size_t nb = K / QK_K;
-    size_t bb = dtype == 12 ? Q4K_BLOCK_BYTES : dtype == 14 ? Q6K_BLOCK_BYTES : 0;
-    if (!bb) return 2;
+    size_t rb = llmrs_oracle_row_bytes(dtype, K);
+    if (!block_elems(dtype)) return 2;
+    if (!rb) return 1;
     if (row_end > N) row_end = N;
     (void)threads;
 #pragma omp parallel num_threads(threads > 0 ? threads : 1)
@@ -234,13 +285,14 @@ int llmrs_oracle_matmul_fast(int dtype, const uint8_t *w, size_t K, size_t N,
         float *wrow = (float *)malloc(K * sizeof(float));
 #pragma omp for schedule(static)
         for (long long r = (long long)row_begin; r < (long long)row_end; r++) {
-            if (dtype == 12) llmrs_oracle_dequant_q4k_row(w + (size_t)r * nb * bb, nb, wrow);
-            else             llmrs_oracle_dequant_q6k_row(w + (size_t)r * nb * bb, nb, wrow);
+            dequant_row(dtype, w + (size_t)r * rb, K, wrow);
             for (size_t s = 0; s < M; s++) {
                 const float *xs = x + s * K;
                 float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                for (size_t i = 0; i < K; i += 8)
+                size_t i = 0;
+                for (; i + 8 <= K; i += 8)
                     for (int l = 0; l < 8; l++) acc[l] += wrow[i + l] * xs[i + l];
+                for (; i < K; i++) acc[0] += wrow[i] * xs[i];
                 out[s * N + (size_t)r] =
                     ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
             }

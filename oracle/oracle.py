@@ -17,7 +17,9 @@ _SRC = os.path.join(_HERE, "llmrs_oracle.c")
 _LIB = os.path.join(_HERE, "libllmrs_oracle.so")
 
 Q4K, Q6K = 12, 14          # GGUF dtype ids (reference: src/tensor/mod.rs:14,16)
-BLOCK_BYTES = {Q4K: 144, Q6K: 210}
+F32, F16, Q4_0, Q8_0, BF16 = 0, 1, 2, 8, 30      # the other weight types the dispatcher accepts (src/tensor/mod.rs:3-33)
+BLOCK_BYTES = {Q4K: 144, Q6K: 210, F32: 4, F16: 2, BF16: 2, Q4_0: 18, Q8_0: 34}
+BLOCK_ELEMS = {Q4K: 256, Q6K: 256, F32: 1, F16: 1, BF16: 1, Q4_0: 32, Q8_0: 32}
 
 # -ffp-contract=off and no -ffast-math: every float operation happens as written.
 _FLAGS = ["-O2", "-march=native", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-shared", "-Wall"]
@@ -130,8 +132,9 @@ def q6k_elem(ql: np.ndarray, qh: np.ndarray, i: int) -> int:
 
 
 def _check_weight(dtype: int, w: np.ndarray, K: int, N: int) -> np.ndarray:
-    w = np.ascontiguousarray(w, dtype=np.uint8).reshape(-1)
-    assert K % 256 == 0 and w.size == N * (K // 256) * BLOCK_BYTES[dtype], (w.size, K, N)
+    w = np.ascontiguousarray(w).view(np.uint8).reshape(-1)
+    be = BLOCK_ELEMS[dtype]
+    assert K % be == 0 and w.size == N * (K // be) * BLOCK_BYTES[dtype], (w.size, K, N)
     return w
 
 
@@ -150,7 +153,7 @@ def embed(dtype: int, w: np.ndarray, K: int, N: int, tokens, *, bf16: bool = Fal
     of the reference's CPU dequantisation (tests/ops.rs:41-59), rounded to bf16 (round to nearest
     even, as half::bf16::from_f32) and widened again when bf16=True."""
     w = _check_weight(dtype, w, K, N)
-    row_bytes = (K // 256) * BLOCK_BYTES[dtype]
+    row_bytes = (K // BLOCK_ELEMS[dtype]) * BLOCK_BYTES[dtype]
     rows = np.stack([w[int(t) * row_bytes:(int(t) + 1) * row_bytes] for t in tokens]) if len(tokens) else \
         np.empty((0, row_bytes), dtype=np.uint8)
     out = dequant(dtype, np.ascontiguousarray(rows).reshape(-1), K, len(tokens)) if len(tokens) else \

@@ -236,7 +236,7 @@ def test_shape_and_dtype_errors(backend):
     with pytest.raises(BackendError):
         backend.matmul(out, w, x)                      # output is [N], needs [N, 3]
     with pytest.raises(BackendError) as e:
-        backend.matmul(out, x, x)                      # weight is not quantised
+        backend.matmul(out, backend.upload_u32([1, 2, 3]), x)          # an index buffer is no weight
     assert e.value.code == -3
     with pytest.raises(BackendError):
         backend.upload_tensor(TensorView("w", DType.Q4K, [300, 4], np.zeros(10, np.uint8)))

@@ -1,6 +1,8 @@
 """The CPU oracle against everything that pins it: IEEE conversions, hand-derived
 known-answer blocks, an independent pure-Python restatement of the reference's CPU code,
 the gguf-py golden fixtures, and the reference test's own generator and seven cases."""
+import os
+
 import numpy as np
 import pytest
 
@@ -303,3 +305,27 @@ def test_rope_scatter_gather_attention_known_values():
     q = np.ones((2, 32), np.float32)
     o = O.attention(q, k, v, [1], [0, 2], [2], 1, 1, 32, 2, 1)
     assert np.allclose(o[0], 1.0) and np.allclose(o[1], 2.0)
+
+
+# ---------- the other weight types (F16, BF16, Q8_0, Q4_0): gguf-py fixtures ----------
+
+@pytest.fixture(scope="module")
+def golden_other():
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "other_dtypes_golden.npz"))
+
+
+@pytest.mark.parametrize("K,N,M", [(64, 5, 1), (256, 8, 3), (1024, 17, 4)])
+def test_oracle_other_dtypes_vs_golden(golden_other, K, N, M):
+    g, tag = golden_other, f"{K}_{N}_{M}"
+    x = g[f"x_{tag}"]
+    for name, dt in (("q8_0", O.Q8_0), ("q4_0", O.Q4_0)):
+        blocks = g[f"{name}_{tag}_blocks"]
+        assert np.array_equal(O.dequant(dt, blocks, K, N).view(np.uint32), g[f"{name}_{tag}_dequant"].view(np.uint32)), name
+        assert O.rel_l2(O.matmul(dt, blocks, K, N, x, acc="f64"), g[f"{name}_{tag}_y"]) < 1e-6
+    # the reference reads Q4_0 in its own element order, not ggml's: the two differ by a fixed permutation
+    ggml = g[f"q4_0_{tag}_dequant_ggml_order"].reshape(-1, 32)
+    ours = O.dequant(O.Q4_0, g[f"q4_0_{tag}_blocks"], K, N).reshape(-1, 32)
+    assert np.array_equal(ours[:, 0::2], ggml[:, :16]) and np.array_equal(ours[:, 1::2], ggml[:, 16:])
+    for name, dt in (("f16", O.F16), ("bf16", O.BF16)):
+        bits = g[f"{name}_{tag}_bits"]
+        assert np.array_equal(O.dequant(dt, bits, K, N).view(np.uint32), g[f"{name}_{tag}_dequant"].view(np.uint32)), name
