@@ -175,15 +175,16 @@ __device__ __forceinline__ void min_operand_q4k(const uint4 &hdr, uint32_t a_tad
 // (g & 1), low half for g < 2 and high half for g >= 2, and bits 2g..2g+1 of qh; its group scale is
 // scales[8h + 2g + c] (shaders/ops.metal:28-42, 322-334).  K-local 32g + 16c + i -> column 16g + 8c + i/2.
 // Per pair of weights: q' = q - 32 (exact), hi = RN_f16(q' sc) (one multiply), and with -sc one fma gives
-// hi - q' sc = -lo exactly; the MMA that consumes the lo columns negates its A operand.
+// hi - q' sc = -lo exactly; the MMA that consumes the lo columns negates its A operand.  The lo terms are
+// formed, stored and multiplied only for stages in which some row has a scale above 64 in magnitude.
 struct RawQ6Half {
     uint4 ql0[2], ql1[2], qh[2];   // [c]: the two ql runs and the qh run of slice (h, c)
     uint2 sc;                      // int8 scales[8h .. 8h+8)
 };
-// Returns the OR of this row's lo terms: zero when sc (q - 32) was exact in f16 everywhere (always so
-// while |sc| <= 64), in which case the MMA warp skips the product of the lo columns for the stage.
-__device__ __forceinline__ uint32_t dequant_q6k_half_exact(const RawQ6Half &raw, uint32_t a_taddr) {
-    uint32_t any = 0u;
+// WITH_LO = false forms and stores the hi columns only: valid when every |sc| of the rows a warp handles is
+// at most 64, because then |sc (q - 32)| <= 2048 is exact in f16 and the lo terms are all zero.
+template <bool WITH_LO>
+__device__ __forceinline__ void dequant_q6k_half_exact(const RawQ6Half &raw, uint32_t a_taddr) {
     const uint2 scw = raw.sc;
     // the eight int8 scales of this half as f16 pairs: (sc + 128) as a byte in the mantissa of 1024, minus 1152
     const uint32_t s01 = scw.x ^ 0x80808080u, s23 = scw.y ^ 0x80808080u;
@@ -201,7 +202,7 @@ __device__ __forceinline__ uint32_t dequant_q6k_half_exact(const RawQ6Half &raw,
             s2[g] = c ? h2_bcast_hi(sp[g]) : h2_bcast_lo(sp[g]);
             ns2[g] = s2[g] ^ 0x80008000u;
         }
-        uint32_t hi[4][8], lo[4][8];
+        uint32_t hi[4][8], lo[WITH_LO ? 4 : 1][8];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             // four bytes of 6-bit quants for each of the four groups, 11 logic ops for 16 weights
@@ -218,18 +219,21 @@ __device__ __forceinline__ uint32_t dequant_q6k_half_exact(const RawQ6Half &raw,
                     const uint32_t q2 = h2_sub(e ? magic_hi(v[g]) : magic_lo(v[g]), H2_1056);   // (q - 32) pair
                     const uint32_t h = h2_mul(q2, s2[g]);
                     hi[g][2 * i + e] = h;
-                    lo[g][2 * i + e] = h2_fma(q2, ns2[g], h);                                 // hi - q' sc = -lo
-                    any |= lo[g][2 * i + e];
+                    if constexpr (WITH_LO) lo[g][2 * i + e] = h2_fma(q2, ns2[g], h);        // hi - q' sc = -lo
                 }
             }
         }
 #pragma unroll
         for (int g = 0; g < 4; g++) {
             tmem_st8(a_taddr + 16 * g + 8 * c, hi[g]);
-            tmem_st8(a_taddr + 64 + 16 * g + 8 * c, lo[g]);
+            if constexpr (WITH_LO) tmem_st8(a_taddr + 64 + 16 * g + 8 * c, lo[g]);
         }
     }
-    return any & 0x7FFF7FFFu;                          // a negative zero is a zero
+}
+// Does any of the eight int8 scales exceed 64 in magnitude?  (sc + 64) as an unsigned byte is above 128
+// exactly then.
+__device__ __forceinline__ bool q6k_scales_need_lo(uint2 sc) {
+    return (__vcmpgtu4(__vadd4(sc.x, 0x40404040u), 0x80808080u) | __vcmpgtu4(__vadd4(sc.y, 0x40404040u), 0x80808080u)) != 0u;
 }
 
 // ---- the kernel --------------------------------------------------------------------------------
@@ -358,7 +362,9 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                         dequant_q4k_half_exact<1>(hdr, q, a_taddr);
                     }
                 } else {
-                    const bool any_lo = __any_sync(0xffffffffu, dequant_q6k_half_exact(raw6, a_taddr) != 0u);
+                    const bool any_lo = __any_sync(0xffffffffu, q6k_scales_need_lo(raw6.sc));   // warp-uniform
+                    if (any_lo) dequant_q6k_half_exact<true>(raw6, a_taddr);
+                    else dequant_q6k_half_exact<false>(raw6, a_taddr);
                     if (lane == 0) lo_flag[s * 4 + (warp & 3)] = any_lo ? 1u : 0u;
                     if (g == 0) d_ring[(blk % D_RING) * TILE_ROWS + r] = f16_bits_to_f32(dbits);
                 }

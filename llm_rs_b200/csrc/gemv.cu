@@ -25,6 +25,7 @@
 // evaluation of the reference formula the result is within ~1e-6 relative L2.
 #include "kernels.h"
 #include "llmrs_common.cuh"
+#include <cstdlib>
 #include <type_traits>
 
 #include "pipeline.cuh"
@@ -741,7 +742,17 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
 // Launch
 // ---------------------------------------------------------------------------------------------
 constexpr int NCW_DEFAULT = 16;
-constexpr int PLANES_DEFAULT = 3;
+// Byte planes of the block-fixed-point activations.  Three planes (18 / 20-bit integers) put the result
+// within ~1e-6 of the float64 product; two planes (15 bits) within ~3e-5, still inside the 1e-4 this path
+// is held to, for a third less dot-product work and shared-memory traffic.  Q4_K, which is bound by
+// instruction issue, always takes two; Q6_K takes three at one token, where it already runs at the
+// speed of HBM, and two from two tokens on, where the plane reads bound it.  LLMRS_GEMV_PLANES=3 in the
+// environment (read once per process) keeps three planes everywhere.
+constexpr int planes_for(int QT, int MT) { return QT == 0 ? 2 : (MT == 1 ? 3 : 2); }
+static bool three_planes_everywhere() {
+    static const bool v = [] { const char *e = getenv("LLMRS_GEMV_PLANES"); return e && atoi(e) == 3; }();
+    return v;
+}
 constexpr size_t SMEM_LIMIT = 226 * 1024;       // 227 KB per CTA less the kernel's static shared memory
 
 template <int QT, int MT, int R, int NCW, int PLANES>
@@ -796,14 +807,19 @@ cudaError_t launch_cfg(const GemvParams &p0, int sm_count, int want_stages, cuda
 
 // Rows per warp: two rows share the staged activations in registers (measured best at every
 // shape tried); one row per warp when the larger ring does not fit beside the activations.
-template <int QT, int MT>
-cudaError_t launch_mt(const GemvParams &p, int sm_count, cudaStream_t s, bool *fits) {
-    constexpr int W = NCW_DEFAULT, P = PLANES_DEFAULT;
+template <int QT, int MT, int P>
+cudaError_t launch_mt_planes(const GemvParams &p, int sm_count, cudaStream_t s, bool *fits) {
+    constexpr int W = NCW_DEFAULT;
     *fits = true;
     if (ring_stages<QT, MT, 2, W, P>(p.K, 4) >= 2) return launch_cfg<QT, MT, 2, W, P>(p, sm_count, 4, s);
     if (!p.W2 && ring_stages<QT, MT, 1, W, P>(p.K, 4) >= 2) return launch_cfg<QT, MT, 1, W, P>(p, sm_count, 4, s);
     *fits = false;
     return cudaSuccess;
+}
+template <int QT, int MT>
+cudaError_t launch_mt(const GemvParams &p, int sm_count, cudaStream_t s, bool *fits) {
+    if (planes_for(QT, MT) == 3 || three_planes_everywhere()) return launch_mt_planes<QT, MT, 3>(p, sm_count, s, fits);
+    return launch_mt_planes<QT, MT, 2>(p, sm_count, s, fits);
 }
 
 template <int QT>
@@ -845,7 +861,7 @@ cudaError_t launch_fmt(GemvParams p, int M, int x_elem, int out_elem, int sm_cou
 size_t gemv_max_k() {
     // largest K whose single-token staging fits beside the smallest ring
     size_t k = 0;
-    while (ring_stages<1, 1, 1, NCW_DEFAULT, PLANES_DEFAULT>((int)(k + 256), 2) >= 2 && k < (1u << 20)) k += 256;
+    while (ring_stages<1, 1, 1, NCW_DEFAULT, 3>((int)(k + 256), 2) >= 2 && k < (1u << 20)) k += 256;
     return k;
 }
 
@@ -922,10 +938,10 @@ bool gemv_gate_up_fits(int wdtype, int K, int M) {
     auto fits = [&](auto qt) {
         constexpr int QT = decltype(qt)::value;
         switch (M) {
-            case 1: return ring_stages<QT, 1, 2, NCW_DEFAULT, PLANES_DEFAULT>(K, 4) >= 2;
-            case 2: return ring_stages<QT, 2, 2, NCW_DEFAULT, PLANES_DEFAULT>(K, 4) >= 2;
-            case 3: return ring_stages<QT, 3, 2, NCW_DEFAULT, PLANES_DEFAULT>(K, 4) >= 2;
-            default: return ring_stages<QT, 4, 2, NCW_DEFAULT, PLANES_DEFAULT>(K, 4) >= 2;
+            case 1: return ring_stages<QT, 1, 2, NCW_DEFAULT, 3>(K, 4) >= 2;
+            case 2: return ring_stages<QT, 2, 2, NCW_DEFAULT, 3>(K, 4) >= 2;
+            case 3: return ring_stages<QT, 3, 2, NCW_DEFAULT, 3>(K, 4) >= 2;
+            default: return ring_stages<QT, 4, 2, NCW_DEFAULT, 3>(K, 4) >= 2;
         }
     };
     if (wdtype == DT_Q4K) return fits(std::integral_constant<int, 0>{});
@@ -963,8 +979,8 @@ cudaError_t launch_gemv_gate_up(int wdtype, const uint8_t *w_gate, const uint8_t
 namespace {
 template <int QT, int MT>
 bool one_pass_fits(int K) {
-    return ring_stages<QT, MT, 2, NCW_DEFAULT, PLANES_DEFAULT>(K, 4) >= 2 ||
-           ring_stages<QT, MT, 1, NCW_DEFAULT, PLANES_DEFAULT>(K, 4) >= 2;
+    return ring_stages<QT, MT, 2, NCW_DEFAULT, 3>(K, 4) >= 2 ||
+           ring_stages<QT, MT, 1, NCW_DEFAULT, 3>(K, 4) >= 2;
 }
 template <int QT>
 int max_tokens_qt(int K) {
