@@ -44,6 +44,12 @@ struct llmrs_ctx {
                                      // LLMRS_TC_TWO_TERM=0: one term (2e-3 class, about half the time)
     void *scratch = nullptr;         // f16 copy of the activations for the tensor-core path
     size_t scratch_bytes = 0;
+    // Several weights multiplied with one input inside one call (q/k/v, gate/up) share the conversion of
+    // the activations the small-batch tensor-core kernel needs: acts_share is set for the length of
+    // such a call, acts_x/K/M/dtype say what the matmul scratch holds.
+    bool acts_share = false, acts_have = false;
+    const void *acts_x = nullptr;
+    uint32_t acts_K = 0, acts_M = 0, acts_dtype = 0;
     bool pdl = true;                 // decode kernels overlap their prologue with the previous kernel's tail (LLMRS_NO_PDL=1: off)
     int gemm_split = -1;             // LLMRS_GEMM_SPLIT at creation: 0 never, 1 always, otherwise the estimate decides
     const llmrs_buf *residual = nullptr;   // set by matmul_add around its call of matmul
@@ -114,6 +120,7 @@ struct llmrs_ctx {
         if (st != cudaStreamCaptureStatusNone) return cudaErrorStreamCaptureUnsupported;
         const size_t want = std::max(need, 2 * *have);
         void *fresh = nullptr;
+        acts_have = false;                               // whatever the old buffer held stays behind
         cudaError_t e = cudaMalloc(&fresh, want);
         if (e != cudaSuccess && want > need) {
             (void)cudaGetLastError();
@@ -620,11 +627,26 @@ static bool uses_exact_kernel(const llmrs_ctx *ctx, uint32_t M) {
 static size_t tc_scratch_bytes(const llmrs_ctx *ctx, uint32_t K, uint32_t M) {
     return uses_exact_kernel(ctx, M) ? gemm_exact_scratch_bytes((int)K, (int)M) : gemm_scratch_bytes((int)K, (int)M);
 }
+// For the length of one call that multiplies several weights with the same input.
+struct ActsShareScope {
+    llmrs_ctx *ctx;
+    explicit ActsShareScope(llmrs_ctx *c) : ctx(c) { ctx->acts_share = true; ctx->acts_have = false; }
+    ~ActsShareScope() { ctx->acts_share = false; ctx->acts_have = false; }
+};
 static cudaError_t tc_matmul(llmrs_ctx *ctx, uint32_t wdtype, const void *w, const void *x, uint32_t x_dtype, void *out,
                              uint32_t out_dtype, uint32_t K, uint32_t N, uint32_t M, const GemmGather *gather = nullptr) {
-    if (uses_exact_kernel(ctx, M))
+    if (uses_exact_kernel(ctx, M)) {
+        int acts_mode = EXACT_ACTS_CONVERT;
+        if (ctx->acts_share) {
+            const bool same = ctx->acts_have && ctx->acts_x == x && ctx->acts_K == K && ctx->acts_M == M && ctx->acts_dtype == x_dtype;
+            acts_mode = same ? EXACT_ACTS_REUSE : EXACT_ACTS_CONVERT_ALL;
+            ctx->acts_have = true; ctx->acts_x = x; ctx->acts_K = K; ctx->acts_M = M; ctx->acts_dtype = x_dtype;
+        }
         return launch_gemm_exact((int)wdtype, (const uint8_t *)w, x, (int)x_dtype, out, (int)out_dtype, (int)K, (int)N, (int)M,
-                                 ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->sink(), ctx->stream, &ctx->launches, gather);
+                                 ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->sink(), ctx->stream, &ctx->launches, gather,
+                                 ctx->pdl, ctx->sm_count, acts_mode);
+    }
+    ctx->acts_have = false;                              // the other kernel writes its own conversion into the scratch
     return launch_gemm((int)wdtype, (const uint8_t *)w, x, (int)x_dtype, out, (int)out_dtype, (int)K, (int)N, (int)M,
                        ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->sink(), ctx->stream, &ctx->launches, gather,
                        ctx->two_term);
@@ -681,6 +703,7 @@ static int matmul_other(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight,
     const bool tensor_cores = M > 8 && !is_block32(weight->dtype) && dense_gemm_shape_ok((int)weight->dtype, (int)K);
     cudaError_t e = cudaSuccess;
     if (tensor_cores) {
+        ctx->acts_have = false;                          // this kernel's conversion overwrites the shared scratch
         e = ctx->reserve_scratch(dense_gemm_scratch_bytes((int)weight->dtype, (int)K, (int)M));
         if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul: scratch (grow it with one call outside graph capture)");
     }
@@ -1126,6 +1149,7 @@ int llmrs_cuda_rms_norm_matmul_qkv(llmrs_ctx *ctx, llmrs_buf *out_q, llmrs_buf *
     if (!one_pass) {
         if ((int)M > ctx->gemv_max_m)                    // no kernel folds the norm in at this token count: normalise once
             return with_norm(ctx, "rms_norm_matmul_qkv", input, norm_weight, eps, false, [&](const llmrs_buf *x) {
+                ActsShareScope share(ctx);
                 int rc = LLMRS_OK;
                 for (int i = 0; i < 3 && rc == LLMRS_OK; i++) rc = llmrs_cuda_matmul(ctx, outs[i], ws[i], x);
                 return rc;
@@ -1225,6 +1249,7 @@ int llmrs_cuda_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w
     if (e != cudaSuccess) return ctx->cuda_fail(e, "matmul_gate_up: event");
     const llmrs_buf *ws[2] = {w_gate, w_up};
     float *dst[2] = {g, u};
+    ActsShareScope share(ctx);
     for (int i = 0; i < 2 && e == cudaSuccess; i++) {
         if (decode)
             e = launch_gemv((int)ws[i]->dtype, (const uint8_t *)ws[i]->dptr, input->dptr, (int)input->dtype, dst[i],

@@ -60,6 +60,7 @@ constexpr int XQ_THREADS = XQ_WARPS * 32;
 constexpr int RAW_WARP = DEQ_WARPS + 2 + EPI_WARPS;          // 14
 constexpr int D_RING = 4;                                     // blocks whose d values are kept for the epilogue
 constexpr int XS_SLOTS = 64;                                  // f16 slots per block in the sub-block sum tensor
+constexpr int SHARE_MIN_PIECES = 8;                           // a cut tile in this many pieces or more is summed by all of them
 
 template <int QT, int TN> struct ExactCfg {
     static constexpr bool MIN = QT == 0;                      // Q4_K carries a minimum term
@@ -75,20 +76,26 @@ template <int QT, int TN> struct ExactCfg {
     static constexpr uint32_t A_MAIN_COLS = QT == 0 ? 64 : 128;
     static constexpr uint32_t A_MIN_COLS = MIN ? 8 : 0;       // 16 K slots of the minimum term
     static constexpr uint32_t A_STAGE_COLS = A_MAIN_COLS + A_MIN_COLS;
-    static constexpr uint32_t ACC_BUF_COLS = 2 * TN;          // one block accumulator: A x_hi | A x_lo
+    // Up to 32 tokens the two products land side by side (one instruction per K step); at 64 tokens both
+    // are added into the same TN columns by two instructions, which leaves tensor memory for a third
+    // operand stage (the instructions are long enough there for their count not to matter).
+    static constexpr bool FUSE = TN <= 32;
+    static constexpr uint32_t ACC_BUF_COLS = FUSE ? 2 * TN : TN;   // one block accumulator: A x_hi | A x_lo, or their sum
     static constexpr uint32_t ACC_COLS = 2 * ACC_BUF_COLS;    // two buffers
     static constexpr uint32_t MACC_COLS = MIN ? TN : 0;       // minimum-term accumulator of the unit (one buffer)
     static constexpr uint32_t A_BASE_COL = ACC_COLS + MACC_COLS;
     static constexpr int TMEM_STAGES = (512 - (int)A_BASE_COL) / (int)A_STAGE_COLS;
-    static constexpr int STAGES = TMEM_STAGES < 4 ? TMEM_STAGES : 4;
-    static_assert(STAGES >= 2, "at least a double buffer");
     // raw ring: one slot = the bytes of one 256-weight block of 128 rows
     static constexpr int Q6_SLICE_BOX = TILE_ROWS * 48;       // one of the four 48-byte slices of a block, all rows
     static constexpr int Q6_SMALL_BOX = TILE_ROWS * 16;       // scales of the block / the 16-byte window holding its d
     static constexpr int RAW_SLOT_BYTES = QT == 0 ? TILE_ROWS * Q4K_BLOCK_BYTES : 4 * Q6_SLICE_BOX + 2 * Q6_SMALL_BOX;
     static constexpr size_t EPI_BYTES = (size_t)EPI_WARPS * (EPI_TOK * 32 * 4) + (size_t)EPI_WARPS * TN_PAD * 4;
-    static constexpr size_t FIXED = 1024 /* alignment slack */ + (size_t)STAGES * STAGE_BYTES + 512 /* barriers */ +
-                                    (size_t)D_RING * TILE_ROWS * 4 + EPI_BYTES;
+    static constexpr size_t OTHER = 1024 /* alignment slack */ + 512 /* barriers */ + (size_t)D_RING * TILE_ROWS * 4 + EPI_BYTES;
+    // stages: what tensor memory holds, what shared memory holds beside two raw slots, four at most
+    static constexpr int SMEM_STAGES = (int)((227 * 1024 - OTHER - 2 * (size_t)RAW_SLOT_BYTES) / STAGE_BYTES);
+    static constexpr int STAGES = TMEM_STAGES < SMEM_STAGES ? (TMEM_STAGES < 4 ? TMEM_STAGES : 4) : (SMEM_STAGES < 4 ? SMEM_STAGES : 4);
+    static_assert(STAGES >= 2, "at least a double buffer");
+    static constexpr size_t FIXED = OTHER + (size_t)STAGES * STAGE_BYTES;
     static constexpr int RAW_FIT = (int)((227 * 1024 - FIXED) / RAW_SLOT_BYTES);
     static constexpr int RAW_SLOTS = RAW_FIT < 4 ? RAW_FIT : 4;
     static_assert(RAW_SLOTS >= 2, "the raw ring needs two slots");
@@ -263,6 +270,11 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
     const Sched sc = make_sched(p, TN);
     const int w_tiles = sc.w_tiles;
 
+    // Programmatic dependent launch: this kernel may start while the kernel that converts its activations
+    // is still running.  Only the warps that touch what earlier kernels wrote (the activation producer
+    // and the epilogue) wait for them; the weight producer and the dequantising warps start at once,
+    // so the first operand stages are ready when the activations arrive.
+    pdl_trigger();
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
             mbar_init(&full[s], DEQ_WARPS / 2 + 1);   // the 4 warps of one dequantising group + the TMA thread (with its bytes)
@@ -391,6 +403,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         bool ok = true;
         UnitIter ui;
         Unit u;
+        pdl_wait();                                   // the converted activations are complete and visible
         while (ok && ui.next(sc, u)) {
             const int t0 = (u.tile / w_tiles) * TN;
             for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
@@ -507,7 +520,12 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                                 const uint32_t lo = lo_s + (uint32_t)((2 * us * C::SUBTILE_BYTES + kk * 32) >> 4);
                                 const uint64_t b_desc = ((uint64_t)desc_hi << 32) | lo;
                                 const uint32_t a = a_s + (uint32_t)(us * 32 + kk * 8);
-                                umma_f16_ts(d_tmem, a, b_desc, IDESC2, (half | us | kk) ? 1u : 0u);
+                                if constexpr (C::FUSE) {
+                                    umma_f16_ts(d_tmem, a, b_desc, IDESC2, (half | us | kk) ? 1u : 0u);
+                                } else {                     // x_hi rows, then the x_lo rows one sub-tile further, same columns
+                                    umma_f16_ts(d_tmem, a, b_desc, IDESC, (half | us | kk) ? 1u : 0u);
+                                    umma_f16_ts(d_tmem, a, b_desc + (uint64_t)(C::SUBTILE_BYTES >> 4), IDESC, 1u);
+                                }
                                 if constexpr (QT == 1) {     // the lo columns hold -lo: negate A; x_hi rows only
                                     if (need_lo) umma_f16_ts(d_tmem, a + C::A_TERM_COLS, b_desc, IDESC | IDESC_NEG_A, 1u);
                                 }
@@ -540,13 +558,15 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         const int row_in_tile = 32 * quarter + lane;
         uint8_t *stg = epi_stage + (size_t)ew * (EPI_TOK * 32 * 4);       // [EPI_TOK tokens][32 rows]
         float *scale_s = reinterpret_cast<float *>(epi_stage + EPI_WARPS * (EPI_TOK * 32 * 4)) + ew * TN_PAD;
-        uint32_t *ticket_s = tmem_slot + 2;
         constexpr int EPI_THREADS = EPI_WARPS * 32;
         uint32_t blk = 0, ucount = 0;
         bool dead = false;
         const bool gather = p.world > 1;
+        pdl_wait();                                   // token factors, exchange counters, mailbox step: all from earlier kernels
         const uint32_t gather_step = gather ? *reinterpret_cast<volatile uint32_t *>(p.step_word) + 1u : 0u;
         const uint32_t lane_off = (uint32_t)(32 * quarter) << 16;
+        struct Duty { int tt, c_first, pieces, n0, t0; } duty[2];      // the cut tiles this CTA holds a piece of
+        int n_duty = 0;
         UnitIter ui;
         Unit u;
         for (; !dead && ui.next(sc, u); ucount++) {
@@ -569,13 +589,21 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                 const uint32_t acc = tmem_base + ab * C::ACC_BUF_COLS + lane_off;
 #pragma unroll
                 for (int c = 0; c < TN / 16; c++) {
-                    uint32_t vh[16], vl[16];
-                    tmem_ld16(acc + 16 * c, vh);                  // A x_hi
-                    tmem_ld16(acc + TN + 16 * c, vl);             // A x_lo
-                    tmem_ld_wait();
+                    if constexpr (C::FUSE) {
+                        uint32_t vh[16], vl[16];
+                        tmem_ld16(acc + 16 * c, vh);              // A x_hi
+                        tmem_ld16(acc + TN + 16 * c, vl);         // A x_lo
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; j++)
-                        total[16 * c + j] = fmaf(d, __uint_as_float(vh[j]) + __uint_as_float(vl[j]), total[16 * c + j]);
+                        for (int j = 0; j < 16; j++)
+                            total[16 * c + j] = fmaf(d, __uint_as_float(vh[j]) + __uint_as_float(vl[j]), total[16 * c + j]);
+                    } else {
+                        uint32_t v[16];
+                        tmem_ld16(acc + 16 * c, v);               // A (x_hi + x_lo), summed by the tensor core
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; j++) total[16 * c + j] = fmaf(d, __uint_as_float(v[j]), total[16 * c + j]);
+                    }
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -603,70 +631,93 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
             }
             if (dead) break;
 
-            // ---- partial unit: who else works on this tile, and is this CTA the last to arrive? ----
-            bool deposit = false, combine = false;
-            int c_first = 0, c_last = -1, tt = 0, tb = 0;
+            // ---- partial unit: a tile cut along K ----
+            // Pieces are deposited straight from the registers (token-major, the rows of a warp side by
+            // side) and published with one release per CTA.  A tile in few pieces is summed by the CTA
+            // that holds its first block: the tile is the last unit of that CTA's range, while the CTAs
+            // after it meet the tile first (or have nothing else), so nobody waits long.  From
+            // SHARE_MIN_PIECES pieces on the sum is shared out instead: every piece is deposited and, once
+            // its own units are done, each of the P CTAs adds up one P-th of the tile over all deposits
+            // and writes that part of the output (the duties below), so that no CTA reads P tiles.
             if (partial) {
-                tt = u.tile - sc.n_full;
-                tb = tt * sc.nb;
-                const int te = tb + sc.nb;
-                int c = min(sc.gt - 1, (int)(((unsigned)tb * (unsigned)sc.gt) / (unsigned)sc.T));
-                while (c + 1 < sc.gt && tail_start(sc, c + 1) <= tb) c++;
-                while (c > 0 && tail_start(sc, c) > tb) c--;
-                c_first = c;
+                const int tt = u.tile - sc.n_full, tb = tt * sc.nb, te = tb + sc.nb;
+                const bool is_first = u.b0 == 0;
+                int c = (int)blockIdx.x;
+                if (!is_first) {                                 // the CTA that holds the tile's first block
+                    c = min(sc.gt - 1, (int)(((unsigned)tb * (unsigned)sc.gt) / (unsigned)sc.T));
+                    while (c + 1 < sc.gt && tail_start(sc, c + 1) <= tb) c++;
+                    while (c > 0 && tail_start(sc, c) > tb) c--;
+                }
+                const int c_first = c;
+                c = (int)blockIdx.x;
                 while (c + 1 < sc.gt && tail_start(sc, c + 1) < te) c++;
-                c_last = c;
-                const uint32_t pieces = (uint32_t)(c_last - c_first + 1);
-                if (ew == 0 && lane == 0) *ticket_s = atomicAdd(p.ws_counters + 2 * tt, 1u);
-                named_barrier_sync(2, EPI_THREADS);
-                deposit = *ticket_s + 1 < pieces;
-                combine = !deposit;
-                if (combine) {
-                    if (ew == 0 && lane == 0) {                  // every other piece has a ticket: wait for their deposits
-                        bool seen = false;
-                        for (uint32_t i = 0; i < p.wait_limit && !seen; i++) {
-                            uint32_t n;
-                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(n) : "l"(p.ws_counters + 2 * tt + 1) : "memory");
-                            seen = n + 1 >= pieces;
-                            if (!seen) __nanosleep(32);
-                        }
-                        if (!seen) report_error(p.err, KERR_SPLIT_WAIT);
-                    }
+                const int c_last = c, pieces = c_last - c_first + 1;
+                const bool shared_sum = pieces >= SHARE_MIN_PIECES;
+                uint32_t *cnt = p.ws_counters + 2 * tt;
+                if (!is_first || shared_sum) {
+                    const int k = is_first ? 1 : 0;              // a CTA's range starts inside at most one tile and ends inside at most one
+                    float *slot = p.ws_slots + (size_t)(2 * blockIdx.x + k) * (TILE_ROWS * TN) + row_in_tile;
+#pragma unroll
+                    for (int j = 0; j < TN; j++) __stcg(slot + j * TILE_ROWS, total[j]);
                     named_barrier_sync(2, EPI_THREADS);
+                    if (ew == 0 && lane == 0) {
+                        __threadfence();                         // the deposits of all four warps, device-wide
+                        atomicAdd(cnt, 1u);
+                    }
+                    if (shared_sum) {
+                        duty[n_duty].tt = tt; duty[n_duty].c_first = c_first; duty[n_duty].pieces = pieces;
+                        duty[n_duty].n0 = n0; duty[n_duty].t0 = t0;
+                        n_duty++;
+                    }
+                    continue;
+                }
+                // this CTA sums the tile: wait for the other pieces, add them, then write like a whole unit
+                if (ew == 0 && lane == 0) {
+                    bool seen = false;
+                    for (uint32_t i = 0; i < p.wait_limit && !seen; i++) {
+                        uint32_t n;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(n) : "l"(cnt) : "memory");
+                        seen = n + 1u >= (uint32_t)pieces;
+                        if (!seen) __nanosleep(32);
+                    }
+                    if (!seen) report_error(p.err, KERR_SPLIT_WAIT);
+                    *cnt = 0;                                    // zero again for the next launch
+                }
+                named_barrier_sync(2, EPI_THREADS);
+                constexpr int PU = TN <= 32 ? 4 : 2;             // pieces whose loads are in flight together
+#pragma unroll
+                for (int g0 = 0; g0 < TN; g0 += EPI_TOK) {
+                    for (int c0 = c_first + 1; c0 <= c_last; c0 += PU) {
+                        float add[PU][EPI_TOK];
+#pragma unroll
+                        for (int q = 0; q < PU; q++) {
+                            const float *sa = p.ws_slots + (size_t)(2 * min(c0 + q, c_last)) * (TILE_ROWS * TN) +
+                                              (size_t)g0 * TILE_ROWS + row_in_tile;
+#pragma unroll
+                            for (int j = 0; j < EPI_TOK; j++) add[q][j] = __ldcg(sa + j * TILE_ROWS);
+                        }
+#pragma unroll
+                        for (int q = 0; q < PU; q++)
+                            if (c0 + q <= c_last) {
+#pragma unroll
+                                for (int j = 0; j < EPI_TOK; j++) total[g0 + j] += add[q][j];
+                            }
+                    }
                 }
             }
 
             // ---- where this unit's values go ----
-            const bool o_bf16 = deposit ? false : (p.out_bf16 != 0);
+            const bool o_bf16 = p.out_bf16 != 0;
             const int esz = o_bf16 ? 2 : 4;
             uint8_t *o_ptr = (uint8_t *)p.Out;
-            size_t o_stride = (size_t)p.n_total;                // elements between tokens (n_total = N unless sharded)
-            int tok_base = t0, row_base = p.row_offset + n0 + 32 * quarter, tok_lim = p.M, row_lim = p.row_offset + p.N;
-            if (deposit) {
-                const int k = sc.tail_a >= tb ? 0 : 1;          // first or last piece of this CTA's range
-                o_ptr = (uint8_t *)(p.ws_slots + (size_t)(2 * blockIdx.x + k) * (TILE_ROWS * TN));
-                o_stride = TILE_ROWS;
-                tok_base = 0; row_base = 32 * quarter; tok_lim = TN; row_lim = TILE_ROWS;
-            }
+            const size_t o_stride = (size_t)p.n_total;          // elements between tokens (n_total = N unless sharded)
+            const int tok_base = t0, row_base = p.row_offset + n0 + 32 * quarter, tok_lim = p.M, row_lim = p.row_offset + p.N;
             const bool vec_ok = (o_stride % (size_t)(16 / esz)) == 0;
 #pragma unroll
             for (int g0 = 0; g0 < TN; g0 += EPI_TOK) {
-                if (combine) {
-                    // the deposits of the other CTAs, token by token (coalesced over the rows of the warp)
-                    for (int c = c_first; c <= c_last; c++) {
-                        if (c == (int)blockIdx.x) continue;
-                        const int k = tail_start(sc, c) >= tb ? 0 : 1;
-                        const float *sa = p.ws_slots + (size_t)(2 * c + k) * (TILE_ROWS * TN) + (size_t)g0 * TILE_ROWS + row_in_tile;
-                        float add[EPI_TOK];
-#pragma unroll
-                        for (int j = 0; j < EPI_TOK; j++) add[j] = __ldcg(sa + j * TILE_ROWS);
-#pragma unroll
-                        for (int j = 0; j < EPI_TOK; j++) total[g0 + j] += add[j];
-                    }
-                }
 #pragma unroll
                 for (int j = 0; j < EPI_TOK; j++) {
-                    const float val = deposit ? total[g0 + j] : total[g0 + j] * scale_s[g0 + j];
+                    const float val = total[g0 + j] * scale_s[g0 + j];
                     if (o_bf16) reinterpret_cast<__nv_bfloat16 *>(stg)[j * 32 + lane] = __float2bfloat16_rn(val);
                     else reinterpret_cast<float *>(stg)[j * 32 + lane] = val;
                 }
@@ -681,7 +732,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                         if (tok < tok_lim && row < row_lim) {
                             const uint4 dv = *reinterpret_cast<const uint4 *>(stg + (size_t)tl * 32 * esz + vv * 16);
                             *reinterpret_cast<uint4 *>(o_ptr + ((size_t)tok * o_stride + row) * esz) = dv;
-                            if (gather && !deposit) {            // the same values, as words, to every peer's mailbox
+                            if (gather) {                        // the same values, as words, to every peer's mailbox
                                 float f[8];
                                 const uint32_t w4[4] = {dv.x, dv.y, dv.z, dv.w};
                                 int nv;
@@ -720,7 +771,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                                 fv = reinterpret_cast<const float *>(stg)[tl * 32 + lane];
                                 ((float *)o_ptr)[(size_t)tok * o_stride + row] = fv;
                             }
-                            if (gather && !deposit) {
+                            if (gather) {
                                 const size_t word = (gather_step & 1u) * p.half_words +
                                                     ((size_t)p.rank * p.M + tok) * p.N + (row - p.row_offset);
                                 for (int dd = 0; dd < p.world; dd++)
@@ -731,17 +782,82 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                 }
                 __syncwarp();                                    // staging is reused by the next group
             }
-            if (partial) {
-                if (deposit) {
-                    __threadfence();                             // this thread's deposit is visible device-wide
-                    named_barrier_sync(2, EPI_THREADS);
-                    if (ew == 0 && lane == 0) atomicAdd(p.ws_counters + 2 * tt + 1, 1u);
-                } else {
-                    named_barrier_sync(2, EPI_THREADS);          // all deposits have been read
-                    if (ew == 0 && lane == 0) {                  // leave the counters at zero for the next launch
-                        p.ws_counters[2 * tt] = 0;
-                        p.ws_counters[2 * tt + 1] = 0;
+        }
+        // ---- duties: this CTA's share of the sums of the cut tiles it holds a piece of ----
+        for (int di = 0; di < n_duty && !dead; di++) {
+            const Duty dy = duty[di];
+            uint32_t *cnt = p.ws_counters + 2 * dy.tt;
+            if (ew == 0 && lane == 0) {
+                bool seen = false;
+                for (uint32_t i = 0; i < p.wait_limit && !seen; i++) {
+                    uint32_t n;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(n) : "l"(cnt) : "memory");
+                    seen = n >= (uint32_t)dy.pieces;
+                    if (!seen) __nanosleep(32);
+                }
+                if (!seen) report_error(p.err, KERR_SPLIT_WAIT);
+            }
+            named_barrier_sync(2, EPI_THREADS);
+            // the tile as TN * 32 groups of four rows; piece q of P takes groups [q * tot / P, (q + 1) * tot / P)
+            constexpr int TOT = TN * (TILE_ROWS / 4);
+            const int q = (int)blockIdx.x - dy.c_first;
+            const int e_lo = (int)(((long long)q * TOT) / dy.pieces), e_hi = (int)(((long long)(q + 1) * TOT) / dy.pieces);
+            const bool o_bf16 = p.out_bf16 != 0;
+            const bool vec_ok = (p.n_total & 3) == 0 && (p.row_offset & 3) == 0;
+            for (int e = e_lo + ew * 32 + lane; e < e_hi; e += EPI_THREADS) {
+                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int c0 = 0; c0 < dy.pieces; c0 += 4) {
+                    float4 v[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int c = dy.c_first + min(c0 + i, dy.pieces - 1);
+                        const int k = c == dy.c_first ? 1 : 0;   // the first piece is the end of its CTA's range
+                        v[i] = __ldcg(reinterpret_cast<const float4 *>(p.ws_slots + (size_t)(2 * c + k) * (TILE_ROWS * TN)) + e);
                     }
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        if (c0 + i < dy.pieces) { acc.x += v[i].x; acc.y += v[i].y; acc.z += v[i].z; acc.w += v[i].w; }
+                }
+                const int tok = dy.t0 + e / (TILE_ROWS / 4), row = p.row_offset + dy.n0 + 4 * (e % (TILE_ROWS / 4));
+                if (tok >= p.M || row >= p.row_offset + p.N) continue;
+                const float ts = __ldg(p.tok_scale + tok);
+                float f[4] = {acc.x * ts, acc.y * ts, acc.z * ts, acc.w * ts};
+                const int nv = min(4, p.row_offset + p.N - row);
+                const size_t o = (size_t)tok * p.n_total + row;
+                if (o_bf16) {
+                    __nv_bfloat16 hb[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        hb[i] = __float2bfloat16_rn(f[i]);
+                        f[i] = __bfloat162float(hb[i]);          // what the peers get is what this rank stores
+                    }
+                    if (vec_ok && nv == 4) {
+                        *reinterpret_cast<uint2 *>((__nv_bfloat16 *)p.Out + o) = *reinterpret_cast<const uint2 *>(hb);
+                    } else {
+                        for (int i = 0; i < nv; i++) ((__nv_bfloat16 *)p.Out)[o + i] = hb[i];
+                    }
+                } else {
+                    if (vec_ok && nv == 4) {
+                        *reinterpret_cast<float4 *>((float *)p.Out + o) = make_float4(f[0], f[1], f[2], f[3]);
+                    } else {
+                        for (int i = 0; i < nv; i++) ((float *)p.Out)[o + i] = f[i];
+                    }
+                }
+                if (gather) {                                    // the same values, as words, to every peer's mailbox
+                    const size_t word = (gather_step & 1u) * p.half_words + ((size_t)p.rank * p.M + tok) * p.N + (row - p.row_offset);
+                    for (int dd = 0; dd < p.world; dd++) {
+                        if (dd == p.rank) continue;
+                        uint2 *box = p.peer_box[dd] + word;
+                        for (int i = 0; i < nv; i++) mailbox_store(box + i, __float_as_uint(f[i]), gather_step);
+                    }
+                }
+            }
+            named_barrier_sync(2, EPI_THREADS);                  // every thread has read what it needs
+            if (ew == 0 && lane == 0) {
+                // the last of the P CTAs to finish leaves both counters at zero for the next launch
+                if (atomicAdd(cnt + 1, 1u) + 1u == (uint32_t)dy.pieces) {
+                    cnt[0] = 0;
+                    cnt[1] = 0;
                 }
             }
         }
@@ -811,10 +927,14 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
 // into `xs` ([2M rows]: hi parts in row token, lo parts in row M + token), 64 slots per 256-weight
 // block in the order the minimum operand expects (see min_operand_q4k): the sum of sub-block sb in
 // slot sb and again in slot 8 + sb, the rest zero.
-__global__ void __launch_bounds__(256)
+// The block size is chosen so that a thread holds at most ACT_KEEP 8-value pieces of the row, which then
+// stay in registers between the maximum and the conversion (longer rows are read again, from L1/L2).
+constexpr int ACT_KEEP = 2;
+__global__ void __launch_bounds__(1024)
 activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M, __half *__restrict__ out,
                          __half *__restrict__ xs, float *__restrict__ tok_scale) {
-    __shared__ float red[8];
+    __shared__ float red[32];
+    pdl_prologue();                  // the next kernel may start its prologue; the input is complete from here on
     const int tok = blockIdx.x;
     const size_t base = (size_t)tok * K;
     auto load8 = [&](int k, float (&v)[8]) {
@@ -832,8 +952,19 @@ activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M
             v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
         }
     };
+    const int step = (int)blockDim.x * 8;
+    float keep[ACT_KEEP][8];
     float amax = 0.0f;
-    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+#pragma unroll
+    for (int j = 0; j < ACT_KEEP; j++) {
+        const int k = (int)threadIdx.x * 8 + j * step;
+        if (k < K) {
+            load8(k, keep[j]);
+#pragma unroll
+            for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(keep[j][i]));
+        }
+    }
+    for (int k = (int)threadIdx.x * 8 + ACT_KEEP * step; k < K; k += step) {
         float v[8];
         load8(k, v);
 #pragma unroll
@@ -843,18 +974,17 @@ activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M
     for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
     __syncthreads();
-    amax = red[0];
+    const int n_warps = (int)(blockDim.x >> 5);
+    amax = (int)(threadIdx.x & 31) < n_warps ? red[threadIdx.x & 31] : 0.0f;
 #pragma unroll
-    for (int i = 1; i < 8; i++) amax = fmaxf(amax, red[i]);
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     const int eb = (int)((__float_as_uint(amax) >> 23) & 0xFFu);
     int e = 140 - eb;                                    // amax < 2^(eb-126): the scaled row stays below 2^14
     e = max(-126, min(126, e));
     if (amax == 0.0f || eb == 255) e = 0;                // all-zero row, or inf/nan: leave as is
     const float sc = exp2i(e);
     const int nb = K / QK_K;
-    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {   // second read comes from L1/L2
-        float v[8];
-        load8(k, v);
+    auto convert = [&](int k, const float (&v)[8]) {
         uint32_t h[4], l[4];
         float sum = 0.0f;
 #pragma unroll
@@ -869,7 +999,7 @@ activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M
         *reinterpret_cast<uint4 *>(out + base + k) = make_uint4(h[0], h[1], h[2], h[3]);
         *reinterpret_cast<uint4 *>(out + (size_t)M * K + base + k) = make_uint4(l[0], l[1], l[2], l[3]);
         if (xs) {
-            // four consecutive threads hold one sub-block of 32 values
+            // four consecutive threads hold one sub-block of 32 values (the block size is a multiple of 32)
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
             const int sb = k >> 5, blk = sb >> 3, j = sb & 7;
@@ -894,6 +1024,18 @@ activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M
                 row_lo[48 + tb] = zero;
             }
         }
+    };
+    // K is a multiple of 256 and the block a multiple of 32 threads: a warp is inside the row or outside
+    // it as a whole, so the shuffles above always see full warps.
+#pragma unroll
+    for (int j = 0; j < ACT_KEEP; j++) {
+        const int k = (int)threadIdx.x * 8 + j * step;
+        if (k < K) convert(k, keep[j]);
+    }
+    for (int k = (int)threadIdx.x * 8 + ACT_KEEP * step; k < K; k += step) {
+        float v[8];
+        load8(k, v);
+        convert(k, v);
     }
     if (threadIdx.x == 0) tok_scale[tok] = exp2i(-e);
 }
@@ -904,7 +1046,7 @@ size_t exact_x_bytes(int K, int M) { return ((size_t)2 * M * K * 2 + 255) / 256 
 size_t exact_xs_bytes(int K, int M) { return ((size_t)2 * M * (K / QK_K) * XS_SLOTS * 2 + 255) / 256 * 256; }
 
 template <int QT, int TN>
-cudaError_t launch_exact_tn(const GemmParams &p, const uint8_t *scratch, int split_mode, cudaStream_t s) {
+cudaError_t launch_exact_tn(const GemmParams &p, const uint8_t *scratch, int split_mode, cudaStream_t s, bool pdl) {
     using C = ExactCfg<QT, TN>;
     ExactMaps maps;
     const __half *x_f16 = (const __half *)scratch;
@@ -931,8 +1073,15 @@ cudaError_t launch_exact_tn(const GemmParams &p, const uint8_t *scratch, int spl
         if (e != cudaSuccess) return e;
     }
     auto kern = gemm_exact_kernel<QT, TN>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+    static bool smem_set[64] = {};                    // per instantiation and device: the attribute is kept by the function
+    int dev = 0;
+    e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || !smem_set[dev]) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) smem_set[dev] = true;
+    }
     const int n_tiles = ((p.N + TILE_ROWS - 1) / TILE_ROWS) * ((p.M + TN - 1) / TN);
     int grid = n_tiles < p.sm_count ? n_tiles : p.sm_count;
     GemmParams q = p;
@@ -949,15 +1098,14 @@ cudaError_t launch_exact_tn(const GemmParams &p, const uint8_t *scratch, int spl
         if (n_tiles < p.sm_count) grid = tail_blocks < p.sm_count ? tail_blocks : p.sm_count;
     }
     if (q.world > 1) grid = p.sm_count;      // CTAs without a tile still take their share of the mailbox
-    kern<<<grid, XQ_THREADS, C::SMEM, s>>>(maps, q);
-    return cudaGetLastError();
+    return launch_dependent(kern, dim3((unsigned)grid), dim3(XQ_THREADS), (size_t)C::SMEM, s, pdl, maps, q);
 }
 
 template <int QT>
-cudaError_t launch_exact_qt(const GemmParams &p, const uint8_t *scratch, int split_mode, cudaStream_t s) {
-    if (p.M <= 16) return launch_exact_tn<QT, 16>(p, scratch, split_mode, s);
-    if (p.M <= 32) return launch_exact_tn<QT, 32>(p, scratch, split_mode, s);
-    return launch_exact_tn<QT, 64>(p, scratch, split_mode, s);
+cudaError_t launch_exact_qt(const GemmParams &p, const uint8_t *scratch, int split_mode, cudaStream_t s, bool pdl) {
+    if (p.M <= 16) return launch_exact_tn<QT, 16>(p, scratch, split_mode, s, pdl);
+    if (p.M <= 32) return launch_exact_tn<QT, 32>(p, scratch, split_mode, s, pdl);
+    return launch_exact_tn<QT, 64>(p, scratch, split_mode, s, pdl);
 }
 
 }  // namespace
@@ -969,18 +1117,26 @@ size_t gemm_exact_scratch_bytes(int K, int M) {
 
 cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                               int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
-                              cudaStream_t s, uint64_t *launches, const GemmGather *gather) {
+                              cudaStream_t s, uint64_t *launches, const GemmGather *gather, bool pdl, int sm_count,
+                              int acts_mode) {
     if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
     if (!scratch || M > GEMM_EXACT_MAX_TOKENS || K % QK_K) return cudaErrorInvalidValue;
     if (wdtype != DT_Q4K && wdtype != DT_Q6K) return cudaErrorInvalidValue;
     uint8_t *sb = (uint8_t *)scratch;
     __half *x_f16 = (__half *)sb;
-    __half *xs = wdtype == DT_Q4K ? (__half *)(sb + exact_x_bytes(K, M)) : nullptr;
+    __half *xs = (__half *)(sb + exact_x_bytes(K, M));
     float *tok_scale = (float *)(sb + exact_x_bytes(K, M) + exact_xs_bytes(K, M));
-    activations_exact_kernel<<<(unsigned)M, 256, 0, s>>>(x, x_dtype == DT_BF16, K, M, x_f16, xs, tok_scale);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-    if (launches) (*launches)++;
+    cudaError_t e = cudaSuccess;
+    if (acts_mode != EXACT_ACTS_REUSE) {
+        // one CTA per token, at most ACT_KEEP 8-value pieces per thread up to 16384-element rows
+        int act_threads = ((K / 8 + ACT_KEEP - 1) / ACT_KEEP + 31) / 32 * 32;
+        act_threads = act_threads < 64 ? 64 : act_threads > 1024 ? 1024 : act_threads;
+        const bool sums = wdtype == DT_Q4K || acts_mode == EXACT_ACTS_CONVERT_ALL;
+        e = launch_dependent(activations_exact_kernel, dim3((unsigned)M), dim3((unsigned)act_threads), 0, s, pdl,
+                             x, (int)(x_dtype == DT_BF16), K, M, x_f16, sums ? xs : (__half *)nullptr, tok_scale);
+        if (e != cudaSuccess) return e;
+        if (launches) (*launches)++;
+    }
     GemmParams p{};
     p.W = w; p.Out = out; p.err = err_word.word; p.wait_limit = err_word.mbar_polls; p.gather_limit = err_word.gather_polls;
     p.K = K; p.N = N; p.M = M; p.out_bf16 = out_dtype == DT_BF16;
@@ -992,20 +1148,23 @@ cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x
         p.half_words = (size_t)gather->world * M * N;
         for (int d = 0; d < gather->world; d++) p.peer_box[d] = (uint2 *)gather->peer_mailbox[d];
     }
-    int dev = 0;
-    e = cudaGetDevice(&dev);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&p.sm_count, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return e;
+    p.sm_count = sm_count;
+    if (p.sm_count <= 0) {
+        int dev = 0;
+        e = cudaGetDevice(&dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&p.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+    }
     if (split_ws && 2 * p.sm_count * sizeof(uint32_t) <= gemm_split_counter_bytes()) {
         p.ws_counters = (uint32_t *)split_ws;
         p.ws_slots = (float *)((uint8_t *)split_ws + gemm_split_counter_bytes());
     }
     if (wdtype == DT_Q4K) {
         p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
-        e = launch_exact_qt<0>(p, sb, split_mode, s);
+        e = launch_exact_qt<0>(p, sb, split_mode, s, pdl);
     } else {
         p.row_stride = q6k_row_stride(K);
-        e = launch_exact_qt<1>(p, sb, split_mode, s);
+        e = launch_exact_qt<1>(p, sb, split_mode, s, pdl);
     }
     if (e == cudaSuccess && launches) (*launches)++;
     return e;

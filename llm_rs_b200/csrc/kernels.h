@@ -191,11 +191,19 @@ cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype
 // exact hi + lo pair for Q6_K) are the f16 operand, the activations a hi + lo f16 pair, and the blocks'
 // d multiplies the per-block accumulators in float32 outside the tensor core (gemm_exact.cu).
 // `scratch`: gemm_exact_scratch_bytes() bytes; split_ws / split_mode / gather as for launch_gemm.
+// `pdl`: both kernels are launched with programmatic stream serialization (the conversion of the
+// activations overlaps the tail of the kernel before it, the weight side of the matmul overlaps the
+// conversion); `sm_count` <= 0 asks the device.
+// `acts_mode`: several weights multiplied with one input share its conversion: the first call converts
+// with the sub-block sums whatever its format (EXACT_ACTS_CONVERT_ALL), the others reuse what the scratch
+// holds (EXACT_ACTS_REUSE: same scratch, same input, K and M, and nothing else run on the scratch since).
 constexpr int GEMM_EXACT_MAX_TOKENS = 64;
+enum { EXACT_ACTS_CONVERT = 0, EXACT_ACTS_CONVERT_ALL = 1, EXACT_ACTS_REUSE = 2 };
 size_t gemm_exact_scratch_bytes(int K, int M);
 cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                               int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
-                              cudaStream_t s, uint64_t *launches, const GemmGather *gather = nullptr);
+                              cudaStream_t s, uint64_t *launches, const GemmGather *gather = nullptr, bool pdl = false,
+                              int sm_count = 0, int acts_mode = EXACT_ACTS_CONVERT);
 
 // Activations -> per-token scaled f16 (one CTA per token): out_f16 [M, K], tok_scale[M] the factors that
 // undo the power-of-two scaling.  The conversion kernel of launch_gemm, for the dense F16 GEMM.

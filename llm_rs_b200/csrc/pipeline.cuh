@@ -121,9 +121,11 @@ __device__ __forceinline__ bool mailbox_wait(const uint2 *w, uint32_t tag, uint3
 // then waits until the predecessor has completed and its writes are visible.  Nothing is read or
 // written before that, so the semantics are those of a plain launch; what is saved is the launch
 // latency between dependent kernels (2-3 us each, several hundred kernels per decode step).
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_prologue() {
-    asm volatile("griddepcontrol.launch_dependents;");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    pdl_trigger();
+    pdl_wait();
 }
 
 template <typename... KArgs, typename... Args>
