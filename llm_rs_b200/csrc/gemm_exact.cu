@@ -22,23 +22,25 @@
 // K step is two (Q4_K) or three (Q6_K: A_lo x_lo is below 2^-22) products.  Nothing is rounded to
 // f16 that is not exact there, except x itself at 2^-22.
 //
-// Pipeline of one CTA (persistent, one per SM, 15 warps):
-//   warp 14     one lane copies the raw blocks of 128 weight rows into a shared-memory ring with tiled
+// Pipeline of one CTA (persistent, one per SM, 24 warps in six warpgroups):
+//   warp 18     one lane copies the raw blocks of 128 weight rows into a shared-memory ring with tiled
 //               TMA copies (cp.async.bulk.tensor.2d on the weight matrix seen as a 2-D byte tensor; no
 //               multicast): one 144-byte box per row for Q4_K (rows 144 bytes apart in shared memory,
 //               so the 16-byte reads of consecutive rows fall into distinct banks), boxes of 48 / 16
 //               bytes per row for the slices, scales and d of Q6_K's slice-major layout.
-//   warps 0-7   read their row's bytes from the ring (thread = weight row), build the f16 operand and
-//               store it into TENSOR MEMORY (tcgen05.st); two groups of four warps alternate the two
-//               128-weight halves of every block.
-//   warp 8      one lane issues the TMA copies of the stage's activation tiles (x_hi, x_lo and, for
+//   warps 0-15  read their row's bytes from the ring (thread = weight row), build the f16 operand and
+//               store it into TENSOR MEMORY (tcgen05.st); up to four groups of four warps take the
+//               operand stages (one 128-weight half of a block each) in turn.
+//   warp 16     one lane issues the TMA copies of the stage's activation tiles (x_hi, x_lo and, for
 //               Q4_K, the per-sub-block sums), 128-byte swizzle.
-//   warp 9      allocates TMEM; one lane issues tcgen05.mma (kind::f16, A from TMEM, B from shared
+//   warp 17     allocates TMEM; one lane issues tcgen05.mma (kind::f16, A from TMEM, B from shared
 //               memory, fp32 accumulators in TMEM) and the commits.
-//   warps 10-13 read the block accumulator out of TMEM after every block (tcgen05.ld), multiply by
+//   warps 20-23 read the block accumulator out of TMEM after every block (tcgen05.ld), multiply by
 //               d[r, b] and add into float32 registers; at the end of a unit they subtract the
 //               minimum term, scale by the token factor and write the results (transposed through
 //               shared memory: the output is token-major).
+// The kernel is launched with programmatic stream serialization: the weight side (warps 0-15, 18) starts
+// while the kernel that converts the activations still runs; warps 16 and 20-23 wait for it.
 // Work is cut as in the prefill kernel (umma.cuh: Sched): tiles of 128 rows x TN tokens; matrices with
 // fewer tiles than SMs are cut along K over all SMs, partial sums meeting in a workspace.
 // Every wait is bounded; a wait that gives up reports a KernelError and the CTA still releases its
@@ -55,9 +57,21 @@ namespace llmrs {
 
 namespace {
 
-constexpr int XQ_WARPS = DEQ_WARPS + 2 + EPI_WARPS + 1;      // 15
+// Six warpgroups.  Four dequantise: group grp = warp / 4 takes every G-th operand stage (half a block), so up
+// to four stages are in work at once and the latencies of one (barrier round trips, shared-memory loads,
+// tensor-memory stores) hide behind the arithmetic of the others.  The fifth holds the three single-warp
+// roles, the sixth is the epilogue.  Registers move from the fifth group to the sixth at the start.
+constexpr int XD_WARPS = 16;                                  // dequantising warps
+constexpr int ACT_WARP = XD_WARPS;                            // TMA producer of the activation tiles
+constexpr int MMA_WARP = XD_WARPS + 1;
+constexpr int RAW_WARP = XD_WARPS + 2;                        // TMA producer of the raw weight blocks
+constexpr int EPI_WARP0 = XD_WARPS + 4;                       // warp 19 has no role
+constexpr int XQ_WARPS = EPI_WARP0 + EPI_WARPS;               // 24
 constexpr int XQ_THREADS = XQ_WARPS * 32;
-constexpr int RAW_WARP = DEQ_WARPS + 2 + EPI_WARPS;          // 14
+// The launch bound gives every thread 80 registers; the fifth group drops to 40 and the epilogue takes the
+// 4 * 32 * 40 it frees, to 120.  (The pool is the CTA's own allocation: the launcher checks the 80.)
+constexpr int REGS_LAUNCH = 80, REGS_SMALL = 40, REGS_EPI = 120;
+static_assert(4 * (REGS_SMALL + REGS_EPI) <= 8 * REGS_LAUNCH, "register pool of the CTA");
 constexpr int D_RING = 4;                                     // blocks whose d values are kept for the epilogue
 constexpr int XS_SLOTS = 64;                                  // f16 slots per block in the sub-block sum tensor
 constexpr int SHARE_MIN_PIECES = 8;                           // a cut tile in this many pieces or more is summed by all of them
@@ -277,12 +291,12 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
     pdl_trigger();
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
-            mbar_init(&full[s], DEQ_WARPS / 2 + 1);   // the 4 warps of one dequantising group + the TMA thread (with its bytes)
+            mbar_init(&full[s], 4 + 1);               // the 4 warps of one dequantising group + the TMA thread (with its bytes)
             mbar_init(&empty[s], 1);                  // tcgen05.commit
         }
         for (int s = 0; s < R; s++) {
             mbar_init(&raw_full[s], 1);               // the weight TMA thread (with its bytes)
-            mbar_init(&raw_empty[s], DEQ_WARPS);      // every dequantising warp, once its bytes are in registers
+            mbar_init(&raw_empty[s], 8);              // the 8 warps that read a block (one group per half), once its bytes are in registers
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(&acc_full[a], 1);               // tcgen05.commit after a block's last MMA
@@ -292,7 +306,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         mbar_init(macc_empty, EPI_WARPS);
         mbar_init_fence();
     }
-    if (warp == DEQ_WARPS + 1) {                      // the MMA warp owns TMEM
+    if (warp == MMA_WARP) {                           // the MMA warp owns TMEM
         tmem_alloc(tmem_slot, C::TMEM_COLS);
         tmem_relinquish();
     }
@@ -302,22 +316,23 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
     const uint32_t tmem_base = *tmem_slot;
     const int nb = p.K / QK_K;
 
-    if (warp < DEQ_WARPS) {
+    if (warp < XD_WARPS) {
         // ---------------- raw bytes (shared memory) -> f16 operand (tensor memory) ----------------
-        // A thread keeps the raw bytes of its half-block in registers.  The bytes of the NEXT block are
-        // fetched from the ring right after the stores of this block have been issued, so that their
+        // A thread keeps the raw bytes of its half-block in registers.  The bytes of the group's NEXT stage
+        // are fetched from the ring right after the stores of this one have been issued, so that their
         // shared-memory latency, the completion of the stores and the barrier round trip overlap.
-        const int r = threadIdx.x & 127, g = threadIdx.x >> 7;
+        // Group grp takes the stages it = grp, grp + G, grp + 2G, ... (stage it = half (it & 1) of block
+        // it / 2).  G is at most the number of stages: a group that skipped more stages than there are
+        // could meet a barrier two phases behind it, where a parity wait answers for the wrong phase.
+        constexpr int G = S < XD_WARPS / 4 ? S : XD_WARPS / 4;
+        const int r = threadIdx.x & 127, grp = threadIdx.x >> 7;
         const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + C::A_BASE_COL;
-        bool ok = true;
-        uint32_t it0 = 0, blk = 0;                    // stages / blocks of the units before this one
-        UnitIter ui;
-        Unit u;
+        bool ok = grp < G;                            // with three stages the fourth group has nothing to do
         // raw bytes of the current block
         uint4 hdr, q[4];                              // Q4_K: header, 64 quant bytes of this half
         RawQ6Half raw6;                               // Q6_K
         uint16_t dbits = 0;
-        auto fetch = [&](uint32_t bk, int b_in_row) -> bool {      // ring slot of block number bk -> registers
+        auto fetch = [&](uint32_t bk, int b_in_row, int g) -> bool {   // half g of block number bk: ring slot -> registers
             const uint32_t rs = bk % R;
             if (!mbar_wait(&raw_full[rs], (bk / R) & 1, p.wait_limit)) {
                 report_error(p.err, KERR_FULL_WAIT);
@@ -345,57 +360,65 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
             if (lane == 0) mbar_arrive(&raw_empty[rs]);          // the slot may be refilled
             return true;
         };
-        bool have = false;
-        while (ok && ui.next(sc, u)) {
-            UnitIter peek = ui;
-            Unit un = u;
-            const bool has_next_unit = peek.next(sc, un);
-            if (!have) {
-                ok = fetch(blk, u.b0);
-                have = true;
-                if (!ok) break;
+        // the blocks of this CTA in order (across its units)
+        UnitIter ui;
+        Unit u;
+        bool valid = ui.next(sc, u);
+        int b = valid ? u.b0 : 0;
+        uint32_t blk = 0;
+        auto advance_to = [&](uint32_t target) {      // move to block number target (at most two on)
+            while (valid && blk < target) {
+                b++;
+                blk++;
+                if (b >= u.b1) {
+                    valid = ui.next(sc, u);
+                    b = valid ? u.b0 : 0;
+                }
             }
-            for (int b = u.b0; b < u.b1; b++, blk++) {
-                const uint32_t it = it0 + 2u * (uint32_t)(b - u.b0) + (uint32_t)g;
-                const uint32_t s = it % S;
-                const uint32_t a_taddr = lane_base + s * C::A_STAGE_COLS;
-                if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
-                    report_error(p.err, KERR_EMPTY_WAIT);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                if constexpr (QT == 0) {
-                    if (g == 0) {
-                        dequant_q4k_half_exact<0>(hdr, q, a_taddr);
-                        min_operand_q4k(hdr, a_taddr + C::A_MAIN_COLS);
-                        d_ring[(blk % D_RING) * TILE_ROWS + r] = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu));
-                    } else {
-                        dequant_q4k_half_exact<1>(hdr, q, a_taddr);
-                    }
-                } else {
-                    const bool any_lo = __any_sync(0xffffffffu, q6k_scales_need_lo(raw6.sc));   // warp-uniform
-                    if (any_lo) dequant_q6k_half_exact<true>(raw6, a_taddr);
-                    else dequant_q6k_half_exact<false>(raw6, a_taddr);
-                    if (lane == 0) lo_flag[s * 4 + (warp & 3)] = any_lo ? 1u : 0u;
-                    if (g == 0) d_ring[(blk % D_RING) * TILE_ROWS + r] = f16_bits_to_f32(dbits);
-                }
-                // the next block's bytes, while this block's stores complete
-                const bool more = b + 1 < u.b1 || has_next_unit;
-                if (more) {
-                    ok = fetch(blk + 1, b + 1 < u.b1 ? b + 1 : un.b0);
-                    if (!ok) break;
-                } else {
-                    have = false;
-                }
-                tmem_st_wait();                      // this warp's tensor-memory stores have landed
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&full[s]);
-            }
-            it0 += 2u * (uint32_t)(u.b1 - u.b0);
+        };
+        uint32_t it = (uint32_t)grp;
+        if (ok) {
+            advance_to(it >> 1);
+            if (valid) ok = fetch(blk, b, (int)(it & 1u));
         }
-    } else if (warp == DEQ_WARPS) {
+        while (ok && valid) {
+            const uint32_t cur = blk;
+            const int g = (int)(it & 1u);
+            const uint32_t s = it % S;
+            const uint32_t a_taddr = lane_base + s * C::A_STAGE_COLS;
+            if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
+                report_error(p.err, KERR_EMPTY_WAIT);
+                break;
+            }
+            tc_fence_after();
+            if constexpr (QT == 0) {
+                if (g == 0) {
+                    dequant_q4k_half_exact<0>(hdr, q, a_taddr);
+                    min_operand_q4k(hdr, a_taddr + C::A_MAIN_COLS);
+                    d_ring[(cur % D_RING) * TILE_ROWS + r] = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu));
+                } else {
+                    dequant_q4k_half_exact<1>(hdr, q, a_taddr);
+                }
+            } else {
+                const bool any_lo = __any_sync(0xffffffffu, q6k_scales_need_lo(raw6.sc));   // warp-uniform
+                if (any_lo) dequant_q6k_half_exact<true>(raw6, a_taddr);
+                else dequant_q6k_half_exact<false>(raw6, a_taddr);
+                if (lane == 0) lo_flag[s * 4 + (warp & 3)] = any_lo ? 1u : 0u;
+                if (g == 0) d_ring[(cur % D_RING) * TILE_ROWS + r] = f16_bits_to_f32(dbits);
+            }
+            // the group's next stage, while this one's stores complete
+            it += (uint32_t)G;
+            advance_to(it >> 1);
+            if (valid) ok = fetch(blk, b, (int)(it & 1u));
+            tmem_st_wait();                          // this warp's tensor-memory stores have landed
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
+        }
+    } else if (warp < EPI_WARP0) {
+      // registers: this warpgroup gives up what the epilogue's per-token totals need
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_SMALL));
+      if (warp == ACT_WARP) {
         // ---------------- TMA producer of the activation tiles ----------------
         // (the whole warp walks the loop, the elected lane issues: see the MMA warp)
         const bool leader = elect_one();
@@ -466,7 +489,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                 __syncwarp();
             }
         }
-    } else if (warp == DEQ_WARPS + 1) {
+    } else if (warp == MMA_WARP) {
         // ---------------- MMA issuer ----------------
         // The whole warp walks the schedule and waits on the barriers (warp-uniform control flow, so the
         // descriptors and tensor-memory addresses are formed once per warp); the elected lane issues.
@@ -546,7 +569,9 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
             if (MIN && ok && leader) umma_commit(macc_full);
             __syncwarp();
         }
+      }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_EPI));
         // ---------------- epilogue warps ----------------
         // A thread owns one weight row (its TMEM lane).  After every block it reads the block's
         // accumulator, multiplies by the row's d of that block and adds into its float32 totals; at
@@ -554,7 +579,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         // kernel's: scaled by the token factor, transposed through a per-warp staging block, written
         // as 16-byte vectors (or deposited / combined when the unit is part of a tile cut along K).
         const int quarter = warp & 3;                           // TMEM lanes this warp may read
-        const int ew = warp - (DEQ_WARPS + 2);
+        const int ew = warp - EPI_WARP0;
         const int row_in_tile = 32 * quarter + lane;
         uint8_t *stg = epi_stage + (size_t)ew * (EPI_TOK * 32 * 4);       // [EPI_TOK tokens][32 rows]
         float *scale_s = reinterpret_cast<float *>(epi_stage + EPI_WARPS * (EPI_TOK * 32 * 4)) + ew * TN_PAD;
@@ -913,7 +938,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
     // teardown: everyone meets here, also after an abandoned wait, so TMEM is always released
     tc_fence_before();
     __syncthreads();
-    if (warp == DEQ_WARPS + 1) {
+    if (warp == MMA_WARP) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
     }
@@ -1078,6 +1103,12 @@ cudaError_t launch_exact_tn(const GemmParams &p, const uint8_t *scratch, int spl
     e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64 || !smem_set[dev]) {
+        // the epilogue's register increase is served from the CTA's own allocation and would wait for ever
+        // if the kernel had been built with fewer registers per thread than the split assumes
+        cudaFuncAttributes fa;
+        e = cudaFuncGetAttributes(&fa, kern);
+        if (e != cudaSuccess) return e;
+        if (fa.numRegs < REGS_LAUNCH) return cudaErrorInvalidConfiguration;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) smem_set[dev] = true;
