@@ -73,7 +73,7 @@ constexpr int XQ_THREADS = XQ_WARPS * 32;
 constexpr int REGS_LAUNCH = 80, REGS_SMALL = 40, REGS_EPI = 120;
 static_assert(4 * (REGS_SMALL + REGS_EPI) <= 8 * REGS_LAUNCH, "register pool of the CTA");
 constexpr int D_RING = 4;                                     // blocks whose d values are kept for the epilogue
-constexpr int XS_SLOTS = 64;                                  // f16 slots per block in the sub-block sum tensor
+constexpr int X_BLOCK_SUBTILES = 10;                          // activation sub-tiles per 256-weight block in the converted layout
 constexpr int SHARE_MIN_PIECES = 8;                           // a cut tile in this many pieces or more is summed by all of them
 
 template <int QT, int TN> struct ExactCfg {
@@ -100,9 +100,11 @@ template <int QT, int TN> struct ExactCfg {
     static constexpr uint32_t A_BASE_COL = ACC_COLS + MACC_COLS;
     static constexpr int TMEM_STAGES = (512 - (int)A_BASE_COL) / (int)A_STAGE_COLS;
     // raw ring: one slot = the bytes of one 256-weight block of 128 rows
-    static constexpr int Q6_SLICE_BOX = TILE_ROWS * 48;       // one of the four 48-byte slices of a block, all rows
-    static constexpr int Q6_SMALL_BOX = TILE_ROWS * 16;       // scales of the block / the 16-byte window holding its d
-    static constexpr int RAW_SLOT_BYTES = QT == 0 ? TILE_ROWS * Q4K_BLOCK_BYTES : 4 * Q6_SLICE_BOX + 2 * Q6_SMALL_BOX;
+    // Q6_K: the 192 bytes of a block's four slices per row come as a 128-byte box and a 64-byte box, both
+    // swizzled (128-byte / 64-byte mode), so that the 16-byte reads of consecutive rows fall into distinct banks
+    static constexpr int Q6_BOX_A = TILE_ROWS * 128, Q6_BOX_B = TILE_ROWS * 64;
+    static constexpr int RAW_SLOT_BYTES = QT == 0 ? TILE_ROWS * Q4K_BLOCK_BYTES : Q6_BOX_A + Q6_BOX_B;
+    static_assert(RAW_SLOT_BYTES % 1024 == 0, "swizzled boxes start on 1024-byte boundaries");
     static constexpr size_t EPI_BYTES = (size_t)EPI_WARPS * (EPI_TOK * 32 * 4) + (size_t)EPI_WARPS * TN_PAD * 4;
     static constexpr size_t OTHER = 1024 /* alignment slack */ + 512 /* barriers */ + (size_t)D_RING * TILE_ROWS * 4 + EPI_BYTES;
     // stages: what tensor memory holds, what shared memory holds beside two raw slots, four at most
@@ -111,18 +113,24 @@ template <int QT, int TN> struct ExactCfg {
     static_assert(STAGES >= 2, "at least a double buffer");
     static constexpr size_t FIXED = OTHER + (size_t)STAGES * STAGE_BYTES;
     static constexpr int RAW_FIT = (int)((227 * 1024 - FIXED) / RAW_SLOT_BYTES);
-    static constexpr int RAW_SLOTS = RAW_FIT < 4 ? RAW_FIT : 4;
-    static_assert(RAW_SLOTS >= 2, "the raw ring needs two slots");
+    // Slots of the raw ring.  GROUPS dequantising groups take the operand stages in turn and each fetches the
+    // block of its next stage ahead of time.  Two rules keep every parity wait on a slot's barrier one
+    // phase from the barrier's own: 2 * slots >= GROUPS + STAGES (the fill before the one a group waits for
+    // has landed: it belongs to a stage the tensor core has already consumed), and 2 * slots a multiple of
+    // GROUPS (a slot is always read by the same two groups, so none of them ever skips a fill).  With three
+    // groups and four slots (the second rule broken) Q6_K at 64 tokens gave wrong rows on a B200.
+    static constexpr int GROUPS = STAGES < 4 ? STAGES : 4;
+    static constexpr int RAW_SLOTS = GROUPS == 3 ? 3 : 4;
+    static_assert(RAW_SLOTS <= RAW_FIT, "the raw ring does not fit");
+    static_assert(2 * RAW_SLOTS >= GROUPS + STAGES && (2 * RAW_SLOTS) % GROUPS == 0, "raw ring against the groups");
     static constexpr size_t SMEM = FIXED + (size_t)RAW_SLOTS * RAW_SLOT_BYTES;
     static constexpr uint32_t TMEM_COLS = 512;
     static_assert(A_BASE_COL + STAGES * A_STAGE_COLS <= 512, "tensor memory budget");
 };
 
 struct ExactMaps {
-    CUtensorMap x;       // [2M rows][K] f16: x_hi rows 0..M-1, x_lo rows M..2M-1; box 64 x TN, 128-byte swizzle
-    CUtensorMap xs;      // Q4_K: [2M rows][nb * 64] f16 sub-block sums (hi rows, then lo rows); same box
-    CUtensorMap w_a;     // weights as bytes [N rows][row stride]: box 144 x 128 (Q4_K) / 48 x 128 (Q6_K)
-    CUtensorMap w_b;     // Q6_K: box 16 x 128
+    CUtensorMap w_a;     // weights as bytes [N rows][row stride]: box 144 x 128 (Q4_K) / 128 x 128, 128-byte swizzle (Q6_K)
+    CUtensorMap w_b;     // Q6_K: box 64 x 128, 64-byte swizzle
 };
 
 __device__ __forceinline__ uint4 lds128(const uint8_t *p) { return *reinterpret_cast<const uint4 *>(p); }
@@ -270,15 +278,16 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     uint8_t *tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + S * C::STAGE_BYTES);
+    uint8_t *raw_ring = tiles + S * C::STAGE_BYTES;                              // 1024-byte aligned: the stage sizes are multiples
+    uint64_t *bars = reinterpret_cast<uint64_t *>(raw_ring + R * C::RAW_SLOT_BYTES);
     uint64_t *full = bars, *empty = full + S, *raw_full = empty + S, *raw_empty = raw_full + R;
     uint64_t *acc_full = raw_empty + R, *acc_empty = acc_full + 2, *macc_full = acc_empty + 2, *macc_empty = macc_full + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(macc_empty + 1);          // [0] TMEM base, [2] split ticket
     uint32_t *lo_flag = tmem_slot + 4;                                           // Q6_K: [stage][warp of the group]: any nonzero lo term
     static_assert((2 * 4 + 2 * 4 + 6) * 8 + 16 + 4 * 4 * 4 <= 512, "barrier area");
-    float *d_ring = reinterpret_cast<float *>(tiles + S * C::STAGE_BYTES + 512);   // [D_RING][128]
+    float *d_ring = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(bars) + 512);   // [D_RING][128]
     uint8_t *epi_stage = reinterpret_cast<uint8_t *>(d_ring + D_RING * TILE_ROWS);
-    uint8_t *raw_ring = epi_stage + C::EPI_BYTES;                                // 128-byte aligned: all sizes above are
+    static_assert(C::STAGE_BYTES % 1024 == 0, "stage images keep the swizzle alignment");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const Sched sc = make_sched(p, TN);
@@ -324,7 +333,8 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         // Group grp takes the stages it = grp, grp + G, grp + 2G, ... (stage it = half (it & 1) of block
         // it / 2).  G is at most the number of stages: a group that skipped more stages than there are
         // could meet a barrier two phases behind it, where a parity wait answers for the wrong phase.
-        constexpr int G = S < XD_WARPS / 4 ? S : XD_WARPS / 4;
+        constexpr int G = C::GROUPS;
+        static_assert(G <= XD_WARPS / 4, "one warpgroup per group");
         const int r = threadIdx.x & 127, grp = threadIdx.x >> 7;
         const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + C::A_BASE_COL;
         bool ok = grp < G;                            // with three stages the fourth group has nothing to do
@@ -332,6 +342,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         uint4 hdr, q[4];                              // Q4_K: header, 64 quant bytes of this half
         RawQ6Half raw6;                               // Q6_K
         uint16_t dbits = 0;
+        const uint8_t *w_row = p.W;                   // Q6_K: this thread's weight row of the current unit (see advance_to)
         auto fetch = [&](uint32_t bk, int b_in_row, int g) -> bool {   // half g of block number bk: ring slot -> registers
             const uint32_t rs = bk % R;
             if (!mbar_wait(&raw_full[rs], (bk / R) & 1, p.wait_limit)) {
@@ -345,16 +356,25 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
 #pragma unroll
                 for (int i = 0; i < 4; i++) q[i] = lds128(rowp + 16 + 64 * g + 16 * i);
             } else {
+                // 16-byte piece i (0..11) of the row's 192 bytes: pieces 0..7 in the 128-byte box, 8..11 in the
+                // 64-byte box, each at the place the copy's swizzle gave it
+                const uint8_t *box_a = slot + (size_t)r * 128, *box_b = slot + C::Q6_BOX_A + (size_t)r * 64;
+                const uint32_t sw_a = (uint32_t)r & 7u, sw_b = ((uint32_t)r >> 1) & 3u;
+                auto piece = [&](uint32_t i) { return i < 8u ? lds128(box_a + ((i ^ sw_a) << 4)) : lds128(box_b + (((i - 8u) ^ sw_b) << 4)); };
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
-                    const uint8_t *sl = slot + (size_t)(2 * g + c) * C::Q6_SLICE_BOX + (size_t)r * 48;
-                    raw6.ql0[c] = lds128(sl);
-                    raw6.ql1[c] = lds128(sl + 16);
-                    raw6.qh[c] = lds128(sl + 32);
+                    const uint32_t i0 = (uint32_t)(6 * g + 3 * c);
+                    raw6.ql0[c] = piece(i0);
+                    raw6.ql1[c] = piece(i0 + 1u);
+                    raw6.qh[c] = piece(i0 + 2u);
                 }
-                raw6.sc = *reinterpret_cast<const uint2 *>(slot + 4 * C::Q6_SLICE_BOX + (size_t)r * 16 + 8 * g);
-                dbits = *reinterpret_cast<const uint16_t *>(slot + 4 * C::Q6_SLICE_BOX + C::Q6_SMALL_BOX + (size_t)r * 16 +
-                                                            ((2 * (b_in_row & 15)) & 15));
+                // scales and d are too narrow for a tensor copy to pay (one request per row whatever its
+                // width): each thread reads its own 8 + 2 bytes from global memory, a stage ahead of their use
+                const int ci = b_in_row >> 4, bl = b_in_row & 15;
+                const int nbc = min(16, nb - 16 * ci);
+                const uint8_t *chunk = w_row + (size_t)3360 * ci;
+                raw6.sc = __ldg(reinterpret_cast<const uint2 *>(chunk + 192 * nbc + 16 * bl + 8 * g));
+                dbits = __ldg(reinterpret_cast<const uint16_t *>(chunk + 208 * nbc + 2 * bl));
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_empty[rs]);          // the slot may be refilled
@@ -366,6 +386,11 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         bool valid = ui.next(sc, u);
         int b = valid ? u.b0 : 0;
         uint32_t blk = 0;
+        auto set_row = [&]() {                        // rows past the matrix (a tile that overhangs N) read the last row
+            if (QT == 1 && valid)
+                w_row = p.W + (size_t)min((u.tile % w_tiles) * TILE_ROWS + r, p.N - 1) * p.row_stride;
+        };
+        set_row();
         auto advance_to = [&](uint32_t target) {      // move to block number target (at most two on)
             while (valid && blk < target) {
                 b++;
@@ -373,10 +398,12 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                 if (b >= u.b1) {
                     valid = ui.next(sc, u);
                     b = valid ? u.b0 : 0;
+                    set_row();
                 }
             }
         };
         uint32_t it = (uint32_t)grp;
+        uint32_t lo_dirty = (1u << S) - 1u;            // Q6_K: stages whose lo columns this warp has not cleared
         if (ok) {
             advance_to(it >> 1);
             if (valid) ok = fetch(blk, b, (int)(it & 1u));
@@ -400,9 +427,22 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                     dequant_q4k_half_exact<1>(hdr, q, a_taddr);
                 }
             } else {
+                // The tensor core takes the lo columns of a stage when ANY of its four warps needs them, so a
+                // warp that does not must leave zeros there: it clears the columns once after it (or the
+                // start of the kernel) left something else in them, and remembers per stage that they are clear.
                 const bool any_lo = __any_sync(0xffffffffu, q6k_scales_need_lo(raw6.sc));   // warp-uniform
-                if (any_lo) dequant_q6k_half_exact<true>(raw6, a_taddr);
-                else dequant_q6k_half_exact<false>(raw6, a_taddr);
+                if (any_lo) {
+                    dequant_q6k_half_exact<true>(raw6, a_taddr);
+                    lo_dirty |= 1u << s;
+                } else {
+                    dequant_q6k_half_exact<false>(raw6, a_taddr);
+                    if ((lo_dirty >> s) & 1u) {
+                        const uint32_t zeros[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+                        for (int i = 0; i < 8; i++) tmem_st8(a_taddr + C::A_TERM_COLS + 8 * i, zeros);
+                        lo_dirty &= ~(1u << s);
+                    }
+                }
                 if (lane == 0) lo_flag[s * 4 + (warp & 3)] = any_lo ? 1u : 0u;
                 if (g == 0) d_ring[(cur % D_RING) * TILE_ROWS + r] = f16_bits_to_f32(dbits);
             }
@@ -428,7 +468,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         Unit u;
         pdl_wait();                                   // the converted activations are complete and visible
         while (ok && ui.next(sc, u)) {
-            const int t0 = (u.tile / w_tiles) * TN;
+            const uint8_t *x_tile = p.x_tiles + (size_t)(u.tile / w_tiles) * nb * X_BLOCK_SUBTILES * C::SUBTILE_BYTES;
             for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
                 const uint32_t s = it % S;
                 if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) - 1) & 1, p.wait_limit)) {
@@ -436,19 +476,16 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                     ok = false;
                     break;
                 }
+                // The conversion kernel has written the stage as it must lie in shared memory (x_hi and x_lo
+                // tiles of both 64-wide K slices, 128-byte swizzled, then the sums of the block with its first
+                // half), so one untiled bulk copy brings it: the tiled copies it replaces cost one request per
+                // 128-byte row, which at 64 tokens was more than the weights' own.
                 const bool with_sums = MIN && (st & 1) == 0;
-                uint8_t *dst = tiles + s * C::STAGE_BYTES;
+                const uint32_t bytes = (with_sums ? 6 : 4) * C::SUBTILE_BYTES;
+                const uint8_t *src = x_tile + ((size_t)(st >> 1) * X_BLOCK_SUBTILES + (size_t)(st & 1) * 6) * C::SUBTILE_BYTES;
                 if (leader) {
-                    mbar_arrive_expect_tx(&full[s], (with_sums ? 6 : 4) * C::SUBTILE_BYTES);
-#pragma unroll
-                    for (int us = 0; us < 2; us++) {     // x_hi tile, then x_lo tile, of each 64-wide K slice
-                        tma_load_2d(dst + (2 * us) * C::SUBTILE_BYTES, &maps.x, st * 128 + us * BK, t0, &full[s]);
-                        tma_load_2d(dst + (2 * us + 1) * C::SUBTILE_BYTES, &maps.x, st * 128 + us * BK, p.M + t0, &full[s]);
-                    }
-                    if (with_sums) {
-                        tma_load_2d(dst + 4 * C::SUBTILE_BYTES, &maps.xs, (st >> 1) * XS_SLOTS, t0, &full[s]);
-                        tma_load_2d(dst + 5 * C::SUBTILE_BYTES, &maps.xs, (st >> 1) * XS_SLOTS, p.M + t0, &full[s]);
-                    }
+                    mbar_arrive_expect_tx(&full[s], bytes);
+                    bulk_copy_g2s(tiles + s * C::STAGE_BYTES, src, bytes, &full[s]);
                 }
                 __syncwarp();
             }
@@ -476,14 +513,9 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                         tma_load_2d(slot, &maps.w_a, b * Q4K_BLOCK_BYTES, n0, &raw_full[rs]);
                     } else {
                         const int ci = b >> 4, bl = b & 15;
-                        const int nbc = min(16, nb - 16 * ci);
                         const int base = 3360 * ci;
-#pragma unroll
-                        for (int j = 0; j < 4; j++)
-                            tma_load_2d(slot + j * C::Q6_SLICE_BOX, &maps.w_a, base + 192 * bl + 48 * j, n0, &raw_full[rs]);
-                        tma_load_2d(slot + 4 * C::Q6_SLICE_BOX, &maps.w_b, base + 192 * nbc + 16 * bl, n0, &raw_full[rs]);
-                        tma_load_2d(slot + 4 * C::Q6_SLICE_BOX + C::Q6_SMALL_BOX, &maps.w_b,
-                                    base + 208 * nbc + ((2 * bl) & ~15), n0, &raw_full[rs]);
+                        tma_load_2d(slot, &maps.w_a, base + 192 * bl, n0, &raw_full[rs]);
+                        tma_load_2d(slot + C::Q6_BOX_A, &maps.w_b, base + 192 * bl + 128, n0, &raw_full[rs]);
                     }
                 }
                 __syncwarp();
@@ -944,26 +976,39 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
     }
 }
 
-// ---- activations -> (x_hi, x_lo) f16 pairs, token factors and sub-block sums ---------------------
-// One CTA per token.  The token row is multiplied by a power of two that brings its largest magnitude
-// to [2^13, 2^14); x_hi = RN_f16(x * 2^e), x_lo = RN_f16(x * 2^e - x_hi); the inverse factor goes to
-// tok_scale[token].  For Q4_K the sums of every 32 consecutive scaled values (what the block's
-// minimum multiplies), divided by 32 so that they stay below 2^14, are written as hi + lo f16 pairs
-// into `xs` ([2M rows]: hi parts in row token, lo parts in row M + token), 64 slots per 256-weight
-// block in the order the minimum operand expects (see min_operand_q4k): the sum of sub-block sb in
-// slot sb and again in slot 8 + sb, the rest zero.
+// ---- activations -> stage images of (x_hi, x_lo) f16 pairs, token factors and sub-block sums --------
+// One CTA per token of the padded token range (whole tiles of TN tokens; the padding rows are zeros).
+// The token row is multiplied by a power of two that brings its largest magnitude to [2^13, 2^14);
+// x_hi = RN_f16(x * 2^e), x_lo = RN_f16(x * 2^e - x_hi); the inverse factor goes to tok_scale[token].
+// The output is laid out as the matmul kernel's shared-memory stages, so that a stage is one contiguous
+// piece: per token tile, per 256-weight block, X_BLOCK_SUBTILES sub-tiles of [TN rows][64 f16] with the
+// 16-byte pieces of a row XOR-swizzled by (row & 7) (the 128-byte swizzle of the tensor-core descriptor):
+//   0..3  x_hi, x_lo of K slice 0, x_hi, x_lo of K slice 1      (first half of the block)
+//   4, 5  the sums of every 32 consecutive scaled values (what Q4_K's minimum multiplies), divided by 32 so
+//         that they stay below 2^14, as hi and lo f16 parts: the sum of sub-block sb in element sb and again
+//         in element 8 + sb (the order min_operand_q4k expects; the tensor core reads those 16 only)
+//   6..9  x_hi, x_lo of K slice 2, x_hi, x_lo of K slice 3      (second half)
 // The block size is chosen so that a thread holds at most ACT_KEEP 8-value pieces of the row, which then
 // stay in registers between the maximum and the conversion (longer rows are read again, from L1/L2).
 constexpr int ACT_KEEP = 2;
 __global__ void __launch_bounds__(1024)
-activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M, __half *__restrict__ out,
-                         __half *__restrict__ xs, float *__restrict__ tok_scale) {
+activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M, int TN, uint8_t *__restrict__ out,
+                         int with_sums, float *__restrict__ tok_scale) {
     __shared__ float red[32];
     pdl_prologue();                  // the next kernel may start its prologue; the input is complete from here on
     const int tok = blockIdx.x;
+    const bool padding = tok >= M;
     const size_t base = (size_t)tok * K;
+    const int nb = K / QK_K;
+    const int sub_bytes = TN * 128;
+    const int j = tok % TN;
+    uint8_t *tile = out + (size_t)(tok / TN) * nb * X_BLOCK_SUBTILES * sub_bytes + (size_t)j * 128;
+    const int sw = j & 7;
     auto load8 = [&](int k, float (&v)[8]) {
-        if (x_is_bf16) {
+        if (padding) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = 0.0f;
+        } else if (x_is_bf16) {
             const uint4 u = __ldg(reinterpret_cast<const uint4 *>((const uint16_t *)x + base + k));
             const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -981,12 +1026,12 @@ activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M
     float keep[ACT_KEEP][8];
     float amax = 0.0f;
 #pragma unroll
-    for (int j = 0; j < ACT_KEEP; j++) {
-        const int k = (int)threadIdx.x * 8 + j * step;
+    for (int jj = 0; jj < ACT_KEEP; jj++) {
+        const int k = (int)threadIdx.x * 8 + jj * step;
         if (k < K) {
-            load8(k, keep[j]);
+            load8(k, keep[jj]);
 #pragma unroll
-            for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(keep[j][i]));
+            for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(keep[jj][i]));
         }
     }
     for (int k = (int)threadIdx.x * 8 + ACT_KEEP * step; k < K; k += step) {
@@ -1008,7 +1053,6 @@ activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M
     e = max(-126, min(126, e));
     if (amax == 0.0f || eb == 255) e = 0;                // all-zero row, or inf/nan: leave as is
     const float sc = exp2i(e);
-    const int nb = K / QK_K;
     auto convert = [&](int k, const float (&v)[8]) {
         uint32_t h[4], l[4];
         float sum = 0.0f;
@@ -1021,80 +1065,72 @@ activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M
             const float2 lowf = __half22float2(*reinterpret_cast<const __half2 *>(&l[i]));
             sum += (back.x + lowf.x) + (back.y + lowf.y);          // what the tensor core will see
         }
-        *reinterpret_cast<uint4 *>(out + base + k) = make_uint4(h[0], h[1], h[2], h[3]);
-        *reinterpret_cast<uint4 *>(out + (size_t)M * K + base + k) = make_uint4(l[0], l[1], l[2], l[3]);
-        if (xs) {
+        // block, half of the block, 64-wide K slice of the half, 16-byte piece of the slice's 128-byte row
+        const int blk = k >> 8, half = (k >> 7) & 1, us = (k >> 6) & 1, c = (k >> 3) & 7;
+        uint8_t *blockp = tile + (size_t)blk * X_BLOCK_SUBTILES * sub_bytes;
+        uint8_t *dst = blockp + (size_t)(half * 6 + 2 * us) * sub_bytes + ((c ^ sw) << 4);
+        *reinterpret_cast<uint4 *>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4 *>(dst + sub_bytes) = make_uint4(l[0], l[1], l[2], l[3]);
+        if (with_sums) {
             // four consecutive threads hold one sub-block of 32 values (the block size is a multiple of 32)
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            const int sb = k >> 5, blk = sb >> 3, j = sb & 7;
-            __half *row_hi = xs + ((size_t)tok * nb + blk) * XS_SLOTS;
-            __half *row_lo = xs + ((size_t)(M + tok) * nb + blk) * XS_SLOTS;
             if ((threadIdx.x & 3) == 0) {
+                const int sb = (k >> 5) & 7;
                 const float s32 = sum * 0.03125f;
                 const __half hi = __float2half_rn(s32);
                 const __half lo = __float2half_rn(s32 - __half2float(hi));
-                row_hi[j] = hi;
-                row_hi[8 + j] = hi;
-                row_lo[j] = lo;
-                row_lo[8 + j] = lo;
-            }
-            // the 32 threads of a block zero its unused slots 16..63
-            const int tb = (k >> 3) & 31;
-            const __half zero = __float2half_rn(0.0f);
-            row_hi[16 + tb] = zero;
-            row_lo[16 + tb] = zero;
-            if (tb < 16) {
-                row_hi[48 + tb] = zero;
-                row_lo[48 + tb] = zero;
+                __half *row_hi = reinterpret_cast<__half *>(blockp + (size_t)4 * sub_bytes);
+                __half *row_lo = reinterpret_cast<__half *>(blockp + (size_t)5 * sub_bytes);
+                const int e0 = ((0 ^ sw) << 3) + sb, e1 = ((1 ^ sw) << 3) + sb;      // f16 index inside the row
+                row_hi[e0] = hi;
+                row_hi[e1] = hi;
+                row_lo[e0] = lo;
+                row_lo[e1] = lo;
             }
         }
     };
     // K is a multiple of 256 and the block a multiple of 32 threads: a warp is inside the row or outside
     // it as a whole, so the shuffles above always see full warps.
 #pragma unroll
-    for (int j = 0; j < ACT_KEEP; j++) {
-        const int k = (int)threadIdx.x * 8 + j * step;
-        if (k < K) convert(k, keep[j]);
+    for (int jj = 0; jj < ACT_KEEP; jj++) {
+        const int k = (int)threadIdx.x * 8 + jj * step;
+        if (k < K) convert(k, keep[jj]);
     }
     for (int k = (int)threadIdx.x * 8 + ACT_KEEP * step; k < K; k += step) {
         float v[8];
         load8(k, v);
         convert(k, v);
     }
-    if (threadIdx.x == 0) tok_scale[tok] = exp2i(-e);
+    if (threadIdx.x == 0 && !padding) tok_scale[tok] = exp2i(-e);
 }
 
 // ---- host side ---------------------------------------------------------------------------------
 
-size_t exact_x_bytes(int K, int M) { return ((size_t)2 * M * K * 2 + 255) / 256 * 256; }
-size_t exact_xs_bytes(int K, int M) { return ((size_t)2 * M * (K / QK_K) * XS_SLOTS * 2 + 255) / 256 * 256; }
+int exact_tn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
+// the converted activations: whole token tiles, X_BLOCK_SUBTILES sub-tiles of TN x 128 bytes per block
+size_t exact_x_bytes(int K, int M) {
+    const int tn = exact_tn(M);
+    const size_t m_pad = (size_t)(M + tn - 1) / tn * tn;
+    return (m_pad * (size_t)(K / QK_K) * X_BLOCK_SUBTILES * 128 + 255) / 256 * 256;
+}
 
 template <int QT, int TN>
-cudaError_t launch_exact_tn(const GemmParams &p, const uint8_t *scratch, int split_mode, cudaStream_t s, bool pdl) {
+cudaError_t launch_exact_tn(const GemmParams &p, int split_mode, cudaStream_t s, bool pdl) {
     using C = ExactCfg<QT, TN>;
     ExactMaps maps;
-    const __half *x_f16 = (const __half *)scratch;
-    const __half *xs = (const __half *)(scratch + exact_x_bytes(p.K, p.M));
-    cudaError_t e = encode_2d(&maps.x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x_f16, (uint64_t)p.K, (uint64_t)p.M * 2,
-                              (uint64_t)p.K * 2, BK, TN, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (e != cudaSuccess) return e;
-    const int nb = p.K / QK_K;
+    cudaError_t e;
     if (QT == 0) {
-        e = encode_2d(&maps.xs, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, xs, (uint64_t)nb * XS_SLOTS, (uint64_t)p.M * 2,
-                      (uint64_t)nb * XS_SLOTS * 2, BK, TN, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (e != cudaSuccess) return e;
         e = encode_2d(&maps.w_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.W, (uint64_t)p.row_stride, (uint64_t)p.N,
                       (uint64_t)p.row_stride, Q4K_BLOCK_BYTES, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
         if (e != cudaSuccess) return e;
         maps.w_b = maps.w_a;
     } else {
-        maps.xs = maps.x;
         e = encode_2d(&maps.w_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.W, (uint64_t)p.row_stride, (uint64_t)p.N,
-                      (uint64_t)p.row_stride, 48, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+                      (uint64_t)p.row_stride, 128, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_128B);
         if (e != cudaSuccess) return e;
         e = encode_2d(&maps.w_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.W, (uint64_t)p.row_stride, (uint64_t)p.N,
-                      (uint64_t)p.row_stride, 16, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+                      (uint64_t)p.row_stride, 64, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_64B);
         if (e != cudaSuccess) return e;
     }
     auto kern = gemm_exact_kernel<QT, TN>;
@@ -1113,6 +1149,7 @@ cudaError_t launch_exact_tn(const GemmParams &p, const uint8_t *scratch, int spl
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) smem_set[dev] = true;
     }
+    const int nb = p.K / QK_K;
     const int n_tiles = ((p.N + TILE_ROWS - 1) / TILE_ROWS) * ((p.M + TN - 1) / TN);
     int grid = n_tiles < p.sm_count ? n_tiles : p.sm_count;
     GemmParams q = p;
@@ -1133,17 +1170,17 @@ cudaError_t launch_exact_tn(const GemmParams &p, const uint8_t *scratch, int spl
 }
 
 template <int QT>
-cudaError_t launch_exact_qt(const GemmParams &p, const uint8_t *scratch, int split_mode, cudaStream_t s, bool pdl) {
-    if (p.M <= 16) return launch_exact_tn<QT, 16>(p, scratch, split_mode, s, pdl);
-    if (p.M <= 32) return launch_exact_tn<QT, 32>(p, scratch, split_mode, s, pdl);
-    return launch_exact_tn<QT, 64>(p, scratch, split_mode, s, pdl);
+cudaError_t launch_exact_qt(const GemmParams &p, int split_mode, cudaStream_t s, bool pdl) {
+    if (p.M <= 16) return launch_exact_tn<QT, 16>(p, split_mode, s, pdl);
+    if (p.M <= 32) return launch_exact_tn<QT, 32>(p, split_mode, s, pdl);
+    return launch_exact_tn<QT, 64>(p, split_mode, s, pdl);
 }
 
 }  // namespace
 
-// Scratch layout: [x_hi, x_lo: 2 M K f16][sub-block sums: 2 M (K/256) 64 f16][M float token factors].
+// Scratch layout: [converted activations, see activations_exact_kernel][M float token factors].
 size_t gemm_exact_scratch_bytes(int K, int M) {
-    return exact_x_bytes(K, M) + exact_xs_bytes(K, M) + (size_t)M * sizeof(float);
+    return exact_x_bytes(K, M) + (size_t)M * sizeof(float);
 }
 
 cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
@@ -1154,17 +1191,16 @@ cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x
     if (!scratch || M > GEMM_EXACT_MAX_TOKENS || K % QK_K) return cudaErrorInvalidValue;
     if (wdtype != DT_Q4K && wdtype != DT_Q6K) return cudaErrorInvalidValue;
     uint8_t *sb = (uint8_t *)scratch;
-    __half *x_f16 = (__half *)sb;
-    __half *xs = (__half *)(sb + exact_x_bytes(K, M));
-    float *tok_scale = (float *)(sb + exact_x_bytes(K, M) + exact_xs_bytes(K, M));
+    float *tok_scale = (float *)(sb + exact_x_bytes(K, M));
+    const int tn = exact_tn(M), m_pad = (M + tn - 1) / tn * tn;
     cudaError_t e = cudaSuccess;
     if (acts_mode != EXACT_ACTS_REUSE) {
         // one CTA per token, at most ACT_KEEP 8-value pieces per thread up to 16384-element rows
         int act_threads = ((K / 8 + ACT_KEEP - 1) / ACT_KEEP + 31) / 32 * 32;
         act_threads = act_threads < 64 ? 64 : act_threads > 1024 ? 1024 : act_threads;
         const bool sums = wdtype == DT_Q4K || acts_mode == EXACT_ACTS_CONVERT_ALL;
-        e = launch_dependent(activations_exact_kernel, dim3((unsigned)M), dim3((unsigned)act_threads), 0, s, pdl,
-                             x, (int)(x_dtype == DT_BF16), K, M, x_f16, sums ? xs : (__half *)nullptr, tok_scale);
+        e = launch_dependent(activations_exact_kernel, dim3((unsigned)m_pad), dim3((unsigned)act_threads), 0, s, pdl,
+                             x, (int)(x_dtype == DT_BF16), K, M, tn, sb, (int)sums, tok_scale);
         if (e != cudaSuccess) return e;
         if (launches) (*launches)++;
     }
@@ -1172,6 +1208,7 @@ cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x
     p.W = w; p.Out = out; p.err = err_word.word; p.wait_limit = err_word.mbar_polls; p.gather_limit = err_word.gather_polls;
     p.K = K; p.N = N; p.M = M; p.out_bf16 = out_dtype == DT_BF16;
     p.tok_scale = tok_scale;
+    p.x_tiles = sb;
     p.n_total = N;
     if (gather && gather->world > 1) {
         p.world = gather->world; p.rank = gather->rank; p.n_total = N * gather->world; p.row_offset = gather->rank * N;
@@ -1192,10 +1229,10 @@ cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x
     }
     if (wdtype == DT_Q4K) {
         p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
-        e = launch_exact_qt<0>(p, sb, split_mode, s, pdl);
+        e = launch_exact_qt<0>(p, split_mode, s, pdl);
     } else {
         p.row_stride = q6k_row_stride(K);
-        e = launch_exact_qt<1>(p, sb, split_mode, s, pdl);
+        e = launch_exact_qt<1>(p, split_mode, s, pdl);
     }
     if (e == cudaSuccess && launches) (*launches)++;
     return e;

@@ -32,6 +32,7 @@ struct GemmParams {
     int sm_count;
     size_t row_stride;
     const float *tok_scale;   // per token: factor that undoes the power-of-two scaling of its f16 activations
+    const uint8_t *x_tiles;   // small-batch kernel: the activations as ready-made shared-memory stage images
     // Split of the last, partial wave of tiles along K (kernel: 0 = off; host: -1 = estimate decides), see Sched below.
     int split;
     uint32_t *ws_counters;    // [2 * sm_count] zero between launches: arrivals / deposits per tail tile

@@ -169,6 +169,45 @@ def test_small_batch_tensor_core_kernel_full_range_blocks(backend_tc, dt, K, N, 
     assert O.rel_l2(got, O.matmul(dt, w, K, N, x, acc="f64")) <= GEMV_TOL
 
 
+@pytest.mark.parametrize("M", [9, 33, 64])
+def test_small_batch_q6k_mixed_scale_ranges(backend_tc, M):
+    """Q6_K blocks whose scales mostly stay within +-63 (one f16 term per weight) with a few percent that
+    do not (two terms): the four warps that build one operand stage then disagree about the second term,
+    and the rows of those that do not need it must not pick up what an earlier stage left behind."""
+    K, N = 4096, 1536
+    rng = np.random.default_rng(77 + M)
+    w = synth.weight(O.Q6K, K, N, tid=2300 + M).reshape(-1, 210).copy()
+    big = rng.random(w.shape[0]) < 0.03
+    w[big, 192:208] = rng.integers(-128, 128, size=(int(big.sum()), 16), dtype=np.int16).astype(np.int8).view(np.uint8)
+    w = w.reshape(-1)
+    x = synth.activations(M, K, tid=2301 + M)
+    truth = O.matmul(O.Q6K, w, K, N, x, acc="f64")
+    wb = upload_weight(backend_tc, O.Q6K, w, K, N)
+    for _ in range(2):
+        got = run_matmul(backend_tc, wb, x, K, N, M)
+        assert O.rel_l2(got, truth) <= GEMV_TOL
+
+
+@pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
+@pytest.mark.parametrize("M", [17, 33, 48, 64])
+def test_small_batch_kernel_repeats(backend_tc, dt, M):
+    """Every SM busy, several blocks per CTA, the same call four times: each result within the tolerance row
+    by row (a pipeline hazard shows as a few rows that are off in some of the runs, which a relative L2
+    over the whole output can hide)."""
+    K, N = 4096, 8192
+    w = synth.weight(dt, K, N, tid=2400)
+    x = synth.activations(M, K, tid=2401 + M)
+    rows = np.arange(0, N, 5)
+    wq = w.reshape(N, -1)[rows].reshape(-1)
+    truth = O.matmul(dt, wq, K, len(rows), x, acc="f64")
+    floor = 1e-3 * float(np.abs(truth).mean())
+    wb = upload_weight(backend_tc, dt, w, K, N)
+    for rep in range(4):
+        got = run_matmul(backend_tc, wb, x, K, N, M)[:, rows]
+        bad = np.abs(got - truth) > floor
+        assert not bad.any(), f"run {rep}: {int(bad.any(axis=0).sum())} of {len(rows)} sampled rows are off"
+
+
 @pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
 @pytest.mark.parametrize("K,N,M", [(4096, 2049, 5), (4096, 300, 9), (4096, 129, 32), (1024, 96, 64), (14336, 40, 17)])
 def test_exact_kernel_up_to_64_tokens(cuda_lib, dt, K, N, M):
