@@ -100,11 +100,10 @@ template <int QT, int TN> struct ExactCfg {
     static constexpr uint32_t A_BASE_COL = ACC_COLS + MACC_COLS;
     static constexpr int TMEM_STAGES = (512 - (int)A_BASE_COL) / (int)A_STAGE_COLS;
     // raw ring: one slot = the bytes of one 256-weight block of 128 rows
-    // Q6_K: the 192 bytes of a block's four slices per row come as a 128-byte box and a 64-byte box, both
-    // swizzled (128-byte / 64-byte mode), so that the 16-byte reads of consecutive rows fall into distinct banks
-    static constexpr int Q6_BOX_A = TILE_ROWS * 128, Q6_BOX_B = TILE_ROWS * 64;
-    static constexpr int RAW_SLOT_BYTES = QT == 0 ? TILE_ROWS * Q4K_BLOCK_BYTES : Q6_BOX_A + Q6_BOX_B;
-    static_assert(RAW_SLOT_BYTES % 1024 == 0, "swizzled boxes start on 1024-byte boundaries");
+    static constexpr int Q6_SLICE_BOX = TILE_ROWS * 48;       // one of the four 48-byte slices of a block, all rows
+    static constexpr int Q6_SMALL_BOX = TILE_ROWS * 16;       // scales of the block / the 16-byte window holding its d
+    static constexpr int RAW_SLOT_BYTES = QT == 0 ? TILE_ROWS * Q4K_BLOCK_BYTES : 4 * Q6_SLICE_BOX + 2 * Q6_SMALL_BOX;
+    static_assert(RAW_SLOT_BYTES % 128 == 0, "tiled copies land on 128-byte boundaries");
     static constexpr size_t EPI_BYTES = (size_t)EPI_WARPS * (EPI_TOK * 32 * 4) + (size_t)EPI_WARPS * TN_PAD * 4;
     static constexpr size_t OTHER = 1024 /* alignment slack */ + 512 /* barriers */ + (size_t)D_RING * TILE_ROWS * 4 + EPI_BYTES;
     // stages: what tensor memory holds, what shared memory holds beside two raw slots, four at most
@@ -113,24 +112,23 @@ template <int QT, int TN> struct ExactCfg {
     static_assert(STAGES >= 2, "at least a double buffer");
     static constexpr size_t FIXED = OTHER + (size_t)STAGES * STAGE_BYTES;
     static constexpr int RAW_FIT = (int)((227 * 1024 - FIXED) / RAW_SLOT_BYTES);
-    // Slots of the raw ring.  GROUPS dequantising groups take the operand stages in turn and each fetches the
-    // block of its next stage ahead of time.  Two rules keep every parity wait on a slot's barrier one
-    // phase from the barrier's own: 2 * slots >= GROUPS + STAGES (the fill before the one a group waits for
-    // has landed: it belongs to a stage the tensor core has already consumed), and 2 * slots a multiple of
-    // GROUPS (a slot is always read by the same two groups, so none of them ever skips a fill).  With three
-    // groups and four slots (the second rule broken) Q6_K at 64 tokens gave wrong rows on a B200.
+    // Slots of the raw ring: as many as fit, up to six (a slot is busy from the issue of its copy, about 1.5 us
+    // under load, until both groups have taken its bytes into registers).  GROUPS dequantising groups take
+    // the operand stages in turn and each fetches the block of its next stage ahead of time; a group does not
+    // visit every fill of a slot, so its parity wait is only right if the fill BEFORE the one it waits for
+    // has certainly landed.  That fill belongs to a stage the tensor core has already consumed as long as
+    // 2 * slots >= GROUPS + STAGES.
     static constexpr int GROUPS = STAGES < 4 ? STAGES : 4;
-    static constexpr int RAW_SLOTS = GROUPS == 3 ? 3 : 4;
-    static_assert(RAW_SLOTS <= RAW_FIT, "the raw ring does not fit");
-    static_assert(2 * RAW_SLOTS >= GROUPS + STAGES && (2 * RAW_SLOTS) % GROUPS == 0, "raw ring against the groups");
+    static constexpr int RAW_SLOTS = RAW_FIT < 6 ? RAW_FIT : 6;
+    static_assert(RAW_SLOTS >= 2 && 2 * RAW_SLOTS >= GROUPS + STAGES, "raw ring against the groups' look-ahead");
     static constexpr size_t SMEM = FIXED + (size_t)RAW_SLOTS * RAW_SLOT_BYTES;
     static constexpr uint32_t TMEM_COLS = 512;
     static_assert(A_BASE_COL + STAGES * A_STAGE_COLS <= 512, "tensor memory budget");
 };
 
 struct ExactMaps {
-    CUtensorMap w_a;     // weights as bytes [N rows][row stride]: box 144 x 128 (Q4_K) / 128 x 128, 128-byte swizzle (Q6_K)
-    CUtensorMap w_b;     // Q6_K: box 64 x 128, 64-byte swizzle
+    CUtensorMap w_a;     // weights as bytes [N rows][row stride]: box 144 x 128 (Q4_K) / 48 x 128 (Q6_K)
+    CUtensorMap w_b;     // Q6_K: box 16 x 128
 };
 
 __device__ __forceinline__ uint4 lds128(const uint8_t *p) { return *reinterpret_cast<const uint4 *>(p); }
@@ -284,7 +282,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
     uint64_t *acc_full = raw_empty + R, *acc_empty = acc_full + 2, *macc_full = acc_empty + 2, *macc_empty = macc_full + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(macc_empty + 1);          // [0] TMEM base, [2] split ticket
     uint32_t *lo_flag = tmem_slot + 4;                                           // Q6_K: [stage][warp of the group]: any nonzero lo term
-    static_assert((2 * 4 + 2 * 4 + 6) * 8 + 16 + 4 * 4 * 4 <= 512, "barrier area");
+    static_assert((2 * S + 2 * R + 6) * 8 + 16 + 4 * 4 * 4 <= 512, "barrier area");
     float *d_ring = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(bars) + 512);   // [D_RING][128]
     uint8_t *epi_stage = reinterpret_cast<uint8_t *>(d_ring + D_RING * TILE_ROWS);
     static_assert(C::STAGE_BYTES % 1024 == 0, "stage images keep the swizzle alignment");
@@ -342,7 +340,6 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         uint4 hdr, q[4];                              // Q4_K: header, 64 quant bytes of this half
         RawQ6Half raw6;                               // Q6_K
         uint16_t dbits = 0;
-        const uint8_t *w_row = p.W;                   // Q6_K: this thread's weight row of the current unit (see advance_to)
         auto fetch = [&](uint32_t bk, int b_in_row, int g) -> bool {   // half g of block number bk: ring slot -> registers
             const uint32_t rs = bk % R;
             if (!mbar_wait(&raw_full[rs], (bk / R) & 1, p.wait_limit)) {
@@ -356,25 +353,16 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
 #pragma unroll
                 for (int i = 0; i < 4; i++) q[i] = lds128(rowp + 16 + 64 * g + 16 * i);
             } else {
-                // 16-byte piece i (0..11) of the row's 192 bytes: pieces 0..7 in the 128-byte box, 8..11 in the
-                // 64-byte box, each at the place the copy's swizzle gave it
-                const uint8_t *box_a = slot + (size_t)r * 128, *box_b = slot + C::Q6_BOX_A + (size_t)r * 64;
-                const uint32_t sw_a = (uint32_t)r & 7u, sw_b = ((uint32_t)r >> 1) & 3u;
-                auto piece = [&](uint32_t i) { return i < 8u ? lds128(box_a + ((i ^ sw_a) << 4)) : lds128(box_b + (((i - 8u) ^ sw_b) << 4)); };
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
-                    const uint32_t i0 = (uint32_t)(6 * g + 3 * c);
-                    raw6.ql0[c] = piece(i0);
-                    raw6.ql1[c] = piece(i0 + 1u);
-                    raw6.qh[c] = piece(i0 + 2u);
+                    const uint8_t *sl = slot + (size_t)(2 * g + c) * C::Q6_SLICE_BOX + (size_t)r * 48;
+                    raw6.ql0[c] = lds128(sl);
+                    raw6.ql1[c] = lds128(sl + 16);
+                    raw6.qh[c] = lds128(sl + 32);
                 }
-                // scales and d are too narrow for a tensor copy to pay (one request per row whatever its
-                // width): each thread reads its own 8 + 2 bytes from global memory, a stage ahead of their use
-                const int ci = b_in_row >> 4, bl = b_in_row & 15;
-                const int nbc = min(16, nb - 16 * ci);
-                const uint8_t *chunk = w_row + (size_t)3360 * ci;
-                raw6.sc = __ldg(reinterpret_cast<const uint2 *>(chunk + 192 * nbc + 16 * bl + 8 * g));
-                dbits = __ldg(reinterpret_cast<const uint16_t *>(chunk + 208 * nbc + 2 * bl));
+                raw6.sc = *reinterpret_cast<const uint2 *>(slot + 4 * C::Q6_SLICE_BOX + (size_t)r * 16 + 8 * g);
+                dbits = *reinterpret_cast<const uint16_t *>(slot + 4 * C::Q6_SLICE_BOX + C::Q6_SMALL_BOX + (size_t)r * 16 +
+                                                            ((2 * (b_in_row & 15)) & 15));
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_empty[rs]);          // the slot may be refilled
@@ -386,11 +374,6 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         bool valid = ui.next(sc, u);
         int b = valid ? u.b0 : 0;
         uint32_t blk = 0;
-        auto set_row = [&]() {                        // rows past the matrix (a tile that overhangs N) read the last row
-            if (QT == 1 && valid)
-                w_row = p.W + (size_t)min((u.tile % w_tiles) * TILE_ROWS + r, p.N - 1) * p.row_stride;
-        };
-        set_row();
         auto advance_to = [&](uint32_t target) {      // move to block number target (at most two on)
             while (valid && blk < target) {
                 b++;
@@ -398,7 +381,6 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                 if (b >= u.b1) {
                     valid = ui.next(sc, u);
                     b = valid ? u.b0 : 0;
-                    set_row();
                 }
             }
         };
@@ -513,9 +495,14 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                         tma_load_2d(slot, &maps.w_a, b * Q4K_BLOCK_BYTES, n0, &raw_full[rs]);
                     } else {
                         const int ci = b >> 4, bl = b & 15;
+                        const int nbc = min(16, nb - 16 * ci);
                         const int base = 3360 * ci;
-                        tma_load_2d(slot, &maps.w_a, base + 192 * bl, n0, &raw_full[rs]);
-                        tma_load_2d(slot + C::Q6_BOX_A, &maps.w_b, base + 192 * bl + 128, n0, &raw_full[rs]);
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            tma_load_2d(slot + j * C::Q6_SLICE_BOX, &maps.w_a, base + 192 * bl + 48 * j, n0, &raw_full[rs]);
+                        tma_load_2d(slot + 4 * C::Q6_SLICE_BOX, &maps.w_b, base + 192 * nbc + 16 * bl, n0, &raw_full[rs]);
+                        tma_load_2d(slot + 4 * C::Q6_SLICE_BOX + C::Q6_SMALL_BOX, &maps.w_b,
+                                    base + 208 * nbc + ((2 * bl) & ~15), n0, &raw_full[rs]);
                     }
                 }
                 __syncwarp();
@@ -1127,10 +1114,10 @@ cudaError_t launch_exact_tn(const GemmParams &p, int split_mode, cudaStream_t s,
         maps.w_b = maps.w_a;
     } else {
         e = encode_2d(&maps.w_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.W, (uint64_t)p.row_stride, (uint64_t)p.N,
-                      (uint64_t)p.row_stride, 128, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_128B);
+                      (uint64_t)p.row_stride, 48, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
         if (e != cudaSuccess) return e;
         e = encode_2d(&maps.w_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.W, (uint64_t)p.row_stride, (uint64_t)p.N,
-                      (uint64_t)p.row_stride, 64, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_64B);
+                      (uint64_t)p.row_stride, 16, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
         if (e != cudaSuccess) return e;
     }
     auto kern = gemm_exact_kernel<QT, TN>;
