@@ -681,13 +681,18 @@ def extra_measurements(be_factory, stream, peak_gbs):
                                    ("q4k_4096x14336", Q4K, 4096, 14336, (1,)),
                                    ("q6k_14336x4096", Q6K, 14336, 4096, (1,)),
                                    ("q4k_4096x128256", Q4K, 4096, 128256, (1,)),
-                                   ("q6k_4096x128256", Q6K, 4096, 128256, (1, 2, 4, 8, 32, 64))):
+                                   ("q4k_4096x4096", Q4K, 4096, 4096, (16, 64)),
+                                   ("q4k_4096x14336", Q4K, 4096, 14336, (16, 64)),
+                                   ("q6k_14336x4096", Q6K, 14336, 4096, (16, 64)),
+                                   ("q4k_4096x128256", Q4K, 4096, 128256, (8, 32, 64)),
+                                   ("q6k_4096x128256", Q6K, 4096, 128256, (1, 2, 4, 8, 16, 32, 64))):
             for M in Ms:
                 t = time_matmul(dt, K, N, M, DType.F32, DType.F32, 50 if N >= 100000 else 200)
                 alg = algorithmic_bytes(dt, K, N, M)
                 out["gemv"][f"{name}_m{M}"] = {"us": round(t * 1e6, 2), "GBps": round(alg / t / 1e9, 1),
                                                "frac_of_hbm_peak": round(alg / t / 1e9 / peak_gbs, 4),
-                                               "kernel": "exact" if M <= 4 else "tensor-core f16, two terms (1e-4 class)"}
+                                               "kernel": "decode kernel (dp4a, fixed-point activations)" if M <= 4
+                                               else "small-batch tensor-core kernel (exact integer operands, 1e-4 class)"}
         # the same output projection on the one-term tensor-core kernel (2e-3 class; LLMRS_TC_TWO_TERM=0)
         os.environ["LLMRS_TC_TWO_TERM"] = "0"
         try:

@@ -654,28 +654,43 @@ static cudaError_t tc_matmul(llmrs_ctx *ctx, uint32_t wdtype, const void *w, con
 
 // Between the decode kernel's token limit and 64 tokens both kernels meet the decode tolerance, so
 // the cheaper one runs.  The decode kernel streams the weights once per pass of up to four tokens
-// (fewer where the staged activations of four do not fit): about 2 us + 0.2 us per MB and token,
-// at least 4.5 us per pass.  The tensor-core kernel streams the weights once behind a floor (pipeline
-// fill, activation conversion): two-term max(47 us, 0.61 us/MB), or 27 us + 0.6 us/MB where its tiles
-// are cut along K over all SMs; one-term max(25 us, 0.31 us/MB).  Fitted on a B200 to 4096x1024 ..
-// 4096x128256 weights at 5 .. 64 tokens.
+// (fewer where the staged activations of four do not fit): about 2 us + 0.15 us per MB and token,
+// at least 4.4 us + 0.3 us per token a pass.  The small-batch tensor-core kernel streams the weights once behind a floor
+// (activation conversion, pipeline fill, the exchange of tiles cut along K): 8.3 us + 0.3 us/MB up to 16
+// tokens, rising to 11.2 us + 0.5 us/MB at 64 (fitted on a B200 to 4096x1024 .. 4096x128256 weights,
+// calls replayed from a CUDA graph).  The older kernels it replaces (LLMRS_TC_EXACT=0): two-term
+// max(47 us, 0.61 us/MB), or 27 us + 0.6 us/MB where its tiles are cut along K; one-term max(25 us, 0.31 us/MB).
 static bool decode_kernel_cheaper(const llmrs_ctx *ctx, const llmrs_buf *weight, uint32_t M, uint32_t K) {
-    if (!ctx->cost_rule || M > (uint32_t)GEMM_TWO_TERM_MAX_TOKENS || K > gemv_max_k()) return false;
+    if (M > (uint32_t)GEMM_TWO_TERM_MAX_TOKENS || K > gemv_max_k()) return false;
     const int per_pass = std::min(4, gemv_single_launch_max_tokens((int)weight->dtype, (int)K));
     if (per_pass <= 0) return false;
     const double mb = (double)weight->nbytes * 1e-6;
     // two-term: weights of up to half a wave of tiles and K >= 4096 are cut along K over all SMs
     const bool cut = ctx->split_ws && ctx->gemm_split != 0 && K >= 4096 && (weight->dim1 + 127) / 128 <= (uint32_t)ctx->sm_count / 2;
-    const double tc = !ctx->two_term ? std::max(25.0, 0.31 * mb) : cut ? 27.0 + 0.6 * mb : std::max(47.0, 0.61 * mb);
+    const double over16 = M > 16 ? (double)(M - 16) : 0.0;
+    const double per_mb = weight->dtype == LLMRS_Q6K ? 0.26 : 0.3;
+    const double tc = !ctx->two_term ? std::max(25.0, 0.31 * mb)
+                      : ctx->exact   ? (8.3 + 0.06 * over16) + (per_mb + 0.0042 * over16) * mb
+                      : cut          ? 27.0 + 0.6 * mb
+                                     : std::max(47.0, 0.61 * mb);
     double decode = 0.0;
-    for (uint32_t done = 0; done < M; done += (uint32_t)per_pass)
-        decode += std::max(4.5, 2.0 + 0.2 * mb * std::min<uint32_t>((uint32_t)per_pass, M - done));
+    for (uint32_t done = 0; done < M; done += (uint32_t)per_pass) {
+        const double t = (double)std::min<uint32_t>((uint32_t)per_pass, M - done);
+        decode += std::max(4.4 + 0.3 * t, 2.0 + 0.15 * mb * t);
+    }
     return decode < tc;
 }
 
 // The kernel llmrs_cuda_matmul picks for M tokens of this weight: the decode kernel or the tensor cores.
+// One token is always the decode kernel's.  With the estimate on (the default), two tokens and more go
+// to whichever the estimate makes cheaper, as long as the tensor-core kernel in use meets the decode
+// tolerance (the small-batch kernel does; the one-term kernel takes over only above gemv_max_m tokens).
+// LLMRS_GEMV_MAX_M fixes the border instead: the decode kernel up to that many tokens.
 static bool matmul_uses_decode_kernel(const llmrs_ctx *ctx, const llmrs_buf *weight, uint32_t M, uint32_t K) {
-    return (int)M <= ctx->gemv_max_m || decode_kernel_cheaper(ctx, weight, M, K);
+    if (M <= 1) return true;
+    if (!ctx->cost_rule) return (int)M <= ctx->gemv_max_m;
+    if ((int)M <= ctx->gemv_max_m && !(ctx->two_term && ctx->exact)) return true;
+    return decode_kernel_cheaper(ctx, weight, M, K);
 }
 
 // matmul for the weight types beside the K-quants (metal/mod.rs:503-518, 542-562, 634-686): dense F32 / F16 /
@@ -739,7 +754,8 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
         return ctx->fail(LLMRS_ERR_DTYPE, "matmul: activations must be F32 or BF16 (got %u -> %u)", input->dtype,
                          out->dtype);
     if (K % QK_K) return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u is not a multiple of 256", K);
-    const bool decode = matmul_uses_decode_kernel(ctx, weight, M, K);
+    // a caller that folded a norm or a residual into this call has already chosen the decode kernel
+    const bool decode = ctx->norm_w || ctx->residual || matmul_uses_decode_kernel(ctx, weight, M, K);
     if (decode && K > gemv_max_k())
         return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u exceeds the supported maximum %zu", K, gemv_max_k());
     if (input->dim0 != K)
