@@ -131,11 +131,16 @@ int llmrs_cuda_free(llmrs_ctx *ctx, llmrs_buf *buf);
  * made once outside capture (inside capture a needed growth fails with LLMRS_ERR_CUDA).  An outgrown
  * scratch buffer is kept until llmrs_cuda_destroy, so graphs captured earlier stay replayable.  The
  * same holds for the temporaries of attention, embed and the rms_norm_* calls.
- * Accuracy against the float64 product, as relative L2 error: up to 64 tokens 1e-4 or better (1..4 tokens
- * the decode kernel, exact integer dot products; 5..64 whichever of that kernel and the two-term
- * tensor-core kernel is cheaper for the shape); from 65 tokens 2e-3 (one-term tensor-core kernel, f16
- * operands, measured ~4e-4).  LLMRS_TC_TWO_TERM=0 at context creation extends the one-term kernel down
- * to 5 tokens; LLMRS_GEMV_MAX_M=m makes "decode kernel up to m tokens, tensor cores above" the rule. */
+ * Accuracy against the float64 product, as relative L2 error: up to 64 tokens 1e-4 or better (one token
+ * the decode kernel, integer dot products; 2..64 whichever of that kernel and the small-batch tensor-core
+ * kernel, which keeps the formats' integer factors exact in f16, an estimate makes cheaper for the shape);
+ * from 65 tokens 2e-3 (one-term tensor-core kernel, f16 operands, measured ~4e-4).  Environment, read at
+ * context creation: LLMRS_GEMV_MAX_M=m makes "decode kernel up to m tokens, tensor cores above" the rule;
+ * LLMRS_TC_EXACT=0 uses the older two-term kernel from 5 to 64 tokens; LLMRS_TC_TWO_TERM=0 extends the
+ * one-term kernel down to 5 tokens.
+ * Kernels that cut tiles along K exchange partial sums between the CTAs of one launch, which must all be
+ * resident: calls of two contexts (or streams) on one device must not overlap in time, or either may give
+ * up its bounded wait (LLMRS_ERR_KERNEL at the next sync; nothing hangs). */
 int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, const llmrs_buf *input);
 
 /* The same product as llmrs_cuda_matmul, computed by the tensor-core kernel for any M, with that
@@ -145,10 +150,11 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
  * they are running: a server that gave the whole GPU to its own memory pool, or a loop that cannot
  * take the device-wide synchronisation a cudaMalloc or cudaFree causes.  This call never allocates
  * or frees device memory.
- *   - Limit: gemm scratch = round_up(2*K*R, 256) + 4*M bytes, R = 2*M up to 64 tokens (hi and lo terms of
- *     the two-term kernel) and M above, must fit 8 MiB (for example 1023
- *     tokens at K=4096, 292 at K=14336); larger shapes fail with LLMRS_ERR_SHAPE and a message
- *     that names both sizes.
+ *   - Limit: the scratch must fit 8 MiB.  Up to 64 tokens (small-batch kernel, same accuracy as
+ *     llmrs_cuda_matmul) it is round_up(5*K*Mp, 256) + 4*M bytes, Mp = M rounded up to 16, 32 or 64 (the
+ *     converted activations are whole token tiles): 64 tokens up to K = 26112.  Above 64 tokens (one-term
+ *     kernel) it is round_up(2*K*M, 256) + 4*M bytes: 1023 tokens at K=4096, 292 at K=14336.  Larger
+ *     shapes fail with LLMRS_ERR_SHAPE and a message that names both sizes.
  *   - Every GPU that loads the library holds the 8 MiB until the process exits.
  *   - The first call on a device looks up the array's device address; make that first call
  *     before any stream capture.
