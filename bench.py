@@ -482,7 +482,6 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
             tf_peak = float(json.load(f).get("bf16_tflops", tf_peak))
     except Exception:  # noqa: BLE001
         pass
-    comm_stream = torch.cuda.Stream(device=dev)
     models = {
         "config4_llama8b": dict(hidden=4096, kv=1024, ffn=14336, vocab=128256, layers=32, Ms=(1, 4, 16, 64)),
         "config5_llama70b": dict(hidden=8192, kv=1024, ffn=28672, vocab=128256, layers=80, Ms=(1, 64, 512, 4096)),
@@ -524,24 +523,6 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
             fused = {N: FusedGather(be, N, M, out_dtype=torch.bfloat16) for N in dims} if fits else None
             fulls = {N: torch.empty(world, M, N // world, device=dev, dtype=torch.bfloat16) for N in dims}
 
-            # From 512 tokens on the NCCL all-gather of a matmul's output overlaps the matmul itself: the
-            # tokens are cut into chunks, chunk c's slices travel on a second stream while chunk c+1 is
-            # computed, and the next matmul waits for the last chunk (it would read the gathered output).
-            n_chunks = 4 if M >= 2048 else 2 if M >= 512 else 1
-            chunked = None
-            if n_chunks > 1 and world > 1:
-                stepc = M // n_chunks
-                xt = {K: torch.from_numpy(synth.bf16_bits(synth.activations(M, K, tid=K)).view(np.int16).reshape(M, K)).to(dev)
-                      for K in (H, F)}
-                chunked = {
-                    "x": {K: [be.wrap(xt[K][c * stepc:(c + 1) * stepc].data_ptr(), [K, stepc], DType.BF16, keepalive=xt[K])
-                              for c in range(n_chunks)] for K in (H, F)},
-                    "local": {N: [be.wrap(locals_[N][c * stepc:(c + 1) * stepc].data_ptr(), [N // world, stepc], DType.BF16,
-                                          keepalive=locals_[N]) for c in range(n_chunks)] for N in dims},
-                    "full": {N: [torch.empty(world, stepc, N // world, device=dev, dtype=torch.bfloat16) for _ in range(n_chunks)]
-                             for N in dims},
-                }
-
             def step(exchange=True):
                 for l in range(L):
                     for (dt, K, N), w in zip(layer, sets[l % n_sets]):
@@ -551,19 +532,6 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
             def run_one(w, dt, K, N, exchange):
                 if exchange and (dt, K, N) in fits:
                     fused[N](w, xs[K])
-                elif exchange and chunked is not None:
-                    stepc = M // n_chunks
-                    for c in range(n_chunks):
-                        be.matmul(chunked["local"][N][c], w, chunked["x"][K][c])
-                        ev = torch.cuda.Event()
-                        ev.record(stream)
-                        comm_stream.wait_event(ev)
-                        with torch.cuda.stream(comm_stream):
-                            dist.all_gather_into_tensor(chunked["full"][N][c].view(-1),
-                                                        locals_[N][c * stepc:(c + 1) * stepc].reshape(-1))
-                    done = torch.cuda.Event()
-                    done.record(comm_stream)
-                    stream.wait_event(done)              # the consumer of the gathered output comes next
                 else:
                     be.matmul(lbufs[N], w, xs[K])
                     if exchange:
@@ -620,16 +588,11 @@ def multi_gpu_stacks(be, stream, dev, rank, world, peak_gbs):
                             "frac_of_tensor_peak_x_gpus": round(flops_per_token * M / t / 1e12 / (tf_peak * world), 4),
                             "exchange": ("fused peer stores" if fits == kinds else
                                          "fused peer stores where a rank receives <= 256 K values per matmul, NCCL all-gather elsewhere" if fits
-                                         else "NCCL all-gather" + (f", overlapped with the matmul in {n_chunks} token chunks" if chunked else "")),
+                                         else "NCCL all-gather"),
                             "cuda_graph": graphed, "allgather_check": checks}
             for bfr in list(xs.values()) + list(lbufs.values()):
                 bfr.free()
-            if chunked is not None:
-                for group in (chunked["x"], chunked["local"]):
-                    for bl in group.values():
-                        for bfr in bl:
-                            bfr.free()
-            del fused, fulls, locals_, chunked
+            del fused, fulls, locals_
             torch.cuda.synchronize(dev)
         for st in sets:
             for bfr in st:
