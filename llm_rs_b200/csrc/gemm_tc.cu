@@ -342,6 +342,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + S * C::STAGE_BYTES);
     uint64_t *full = bars, *empty = bars + S, *acc_full = bars + 2 * S, *acc_empty = bars + 2 * S + AB;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * S + 2 * AB);
+    uint64_t *duty_bar = bars + 16;                             // the bulk copies that fetch deposits (see the duties)
+    static_assert((2 * S + 2 * AB) * 8 + 16 <= 128, "barrier area");
     uint8_t *epi_stage = tiles + S * C::STAGE_BYTES + 256;       // 256 bytes of barriers in front, 16-byte aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -357,6 +359,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
             mbar_init(&acc_full[a], 1);             // tcgen05.commit after the tile's last MMA
             mbar_init(&acc_empty[a], EPI_WARPS);    // epilogue warps, once they have read it out
         }
+        mbar_init(duty_bar, 1);
         mbar_init_fence();
     }
     if (warp == DEQ_WARPS + 1) {                    // the MMA warp owns TMEM
@@ -532,8 +535,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
         const int ew = warp - (DEQ_WARPS + 2);
         uint8_t *stg = epi_stage + (size_t)ew * (EPI_TOK * 32 * 4);       // [EPI_TOK tokens][32 rows]
         float *scale_s = reinterpret_cast<float *>(epi_stage + EPI_WARPS * (EPI_TOK * 32 * 4)) + ew * TN_PAD;
-        uint32_t *ticket_s = tmem_slot + 2;
         constexpr int EPI_THREADS = EPI_WARPS * 32;
+        struct Duty { int tt, c_first, pieces, n0, t0; } duty[2];      // the cut tiles this CTA holds a piece of
+        int n_duty = 0;
         uint32_t tcount = 0;
         bool dead = false;                                      // a wait gave up: no more memory traffic, barriers only
         const bool gather = p.world > 1;
@@ -553,52 +557,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
             }
             tc_fence_after();
 
-            // ---- partial unit: who else works on this tile, and is this CTA the last to arrive? ----
-            bool deposit = false, combine = false;
-            int c_first = 0, c_last = -1, tt = 0, tb = 0;
+            // ---- partial unit: a tile cut along K ----
+            // Every piece is deposited straight from the registers and published with one release per CTA;
+            // once its own units are done, each of the P CTAs that hold a piece adds up one P-th of the tile
+            // over all deposits and writes that part of the output (the duties below).  With tiles of up to
+            // 128 KB this beats one CTA reading all the pieces: no CTA reads more than one tile's worth.
+            const bool deposit = partial;
+            int tt = 0;
             if (partial) {
                 tt = u.tile - sc.n_full;
-                tb = tt * sc.nb;
-                const int te = tb + sc.nb;
-                // c_first: the CTA whose range holds block tb; c_last: the one that holds block te - 1
-                int c = min(sc.gt - 1, (int)(((unsigned)tb * (unsigned)sc.gt) / (unsigned)sc.T));
-                while (c + 1 < sc.gt && tail_start(sc, c + 1) <= tb) c++;
-                while (c > 0 && tail_start(sc, c) > tb) c--;
-                c_first = c;
-                while (c + 1 < sc.gt && tail_start(sc, c + 1) < te) c++;
-                c_last = c;
-                const uint32_t pieces = (uint32_t)(c_last - c_first + 1);
-                if (ew == 0 && lane == 0) *ticket_s = atomicAdd(p.ws_counters + 2 * tt, 1u);
-                named_barrier_sync(2, EPI_THREADS);
-                deposit = *ticket_s + 1 < pieces;
-                combine = !deposit;
-                if (combine) {
-                    if (ew == 0 && lane == 0) {                  // every other piece has a ticket: wait for their deposits
-                        bool seen = false;
-                        for (uint32_t i = 0; i < p.wait_limit && !seen; i++) {
-                            uint32_t n;
-                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(n) : "l"(p.ws_counters + 2 * tt + 1) : "memory");
-                            seen = n + 1 >= pieces;
-                            if (!seen) __nanosleep(32);
-                        }
-                        if (!seen) report_error(p.err, KERR_SPLIT_WAIT);
-                    }
-                    named_barrier_sync(2, EPI_THREADS);
+                const int tb = tt * sc.nb, te = tb + sc.nb;
+                int c = (int)blockIdx.x;
+                if (u.b0 != 0) {                                 // the CTA that holds the tile's first block
+                    c = min(sc.gt - 1, (int)(((unsigned)tb * (unsigned)sc.gt) / (unsigned)sc.T));
+                    while (c + 1 < sc.gt && tail_start(sc, c + 1) <= tb) c++;
+                    while (c > 0 && tail_start(sc, c) > tb) c--;
                 }
+                const int c_first = c;
+                c = (int)blockIdx.x;
+                while (c + 1 < sc.gt && tail_start(sc, c + 1) < te) c++;
+                duty[n_duty].tt = tt; duty[n_duty].c_first = c_first; duty[n_duty].pieces = c - c_first + 1;
+                duty[n_duty].n0 = n0; duty[n_duty].t0 = t0;
+                n_duty++;
             }
 
             // ---- where this unit's values go ----
-            const bool o_bf16 = deposit ? false : (p.out_bf16 != 0);
+            const bool o_bf16 = p.out_bf16 != 0;
             const int esz = o_bf16 ? 2 : 4;
             uint8_t *o_ptr = (uint8_t *)p.Out;
-            size_t o_stride = (size_t)p.n_total;                // elements between tokens (n_total = N unless sharded)
-            int tok_base = t0, row_base = p.row_offset + n0 + 32 * quarter, tok_lim = p.M, row_lim = p.row_offset + p.N;
-            if (deposit) {
-                const int k = sc.tail_a >= tb ? 0 : 1;          // first or last piece of this CTA's range
-                o_ptr = (uint8_t *)(p.ws_slots + (size_t)(2 * blockIdx.x + k) * (TILE_ROWS * TN));
-                o_stride = TILE_ROWS;
-                tok_base = 0; row_base = 32 * quarter; tok_lim = TN; row_lim = TILE_ROWS;
-            }
+            const size_t o_stride = (size_t)p.n_total;          // elements between tokens (n_total = N unless sharded)
+            const int tok_base = t0, row_base = p.row_offset + n0 + 32 * quarter, tok_lim = p.M, row_lim = p.row_offset + p.N;
+            // a deposit goes token-major into this CTA's slot: slot 1 for the piece that ends its range, else 0
+            float *dep = p.ws_slots + (size_t)(2 * blockIdx.x + (u.b0 != 0 ? 0 : 1)) * (TILE_ROWS * TN) + 32 * quarter + lane;
             const bool vec_ok = (o_stride % (size_t)(16 / esz)) == 0;     // 16-byte stores need whole vectors per token
             const uint32_t acc = tmem_base + ab * C::ACC_COLS + ((uint32_t)(32 * quarter) << 16);
 #pragma unroll 1
@@ -625,33 +615,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[ab]);
                 }
-                if (combine) {
-                    // the deposits of two other CTAs are loaded together: one trip to L2 per pair
-                    auto slot_of = [&](int c) {
-                        const int k = tail_start(sc, c) >= tb ? 0 : 1;
-                        return p.ws_slots + (size_t)(2 * c + k) * (TILE_ROWS * TN) + (size_t)g0 * TILE_ROWS + 32 * quarter + lane;
-                    };
-                    int c = c_first;
-                    while (c <= c_last) {
-                        if (c == (int)blockIdx.x) { c++; continue; }
-                        const float *sa = slot_of(c++);
-                        if (c <= c_last && c == (int)blockIdx.x) c++;
-                        const bool two = c <= c_last;
-                        const float *sb = two ? slot_of(c++) : sa;
-                        float add_a[GT], add_b[GT];
+                if (deposit) {                                   // straight from the registers, the rows of a warp side by side
 #pragma unroll
-                        for (int j = 0; j < GT; j++) add_a[j] = __ldcg(sa + j * TILE_ROWS);
-                        if (two) {
-#pragma unroll
-                            for (int j = 0; j < GT; j++) add_b[j] = __ldcg(sb + j * TILE_ROWS);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < GT; j++) add_b[j] = 0.0f;
-                        }
-#pragma unroll
-                        for (int j = 0; j < GT; j++)
-                            v[j / 16][j % 16] = __float_as_uint(__uint_as_float(v[j / 16][j % 16]) + add_a[j] + add_b[j]);
-                    }
+                    for (int j = 0; j < GT; j++) __stcg(dep + (size_t)(g0 + j) * TILE_ROWS, __uint_as_float(v[j / 16][j % 16]));
+                    continue;
                 }
 #pragma unroll
                 for (int c = 0; c < GT / 16; c++) {
@@ -662,8 +629,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
                             const int tl = 16 * c + 4 * j4 + j;                  // token within the group
-                            const float raw = __uint_as_float(v[c][4 * j4 + j]);
-                            const float val = deposit ? raw : raw * f[j];
+                            const float val = __uint_as_float(v[c][4 * j4 + j]) * f[j];
                             if (o_bf16) reinterpret_cast<__nv_bfloat16 *>(stg)[tl * 32 + lane] = __float2bfloat16_rn(val);
                             else reinterpret_cast<float *>(stg)[tl * 32 + lane] = val;
                         }
@@ -680,7 +646,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                         if (tok < tok_lim && row < row_lim) {
                             const uint4 d = *reinterpret_cast<const uint4 *>(stg + (size_t)tl * 32 * esz + vv * 16);
                             *reinterpret_cast<uint4 *>(o_ptr + ((size_t)tok * o_stride + row) * esz) = d;
-                            if (gather && !deposit) {            // the same values, as words, to every peer's mailbox
+                            if (gather) {                        // the same values, as words, to every peer's mailbox
                                 float f[8];
                                 const uint32_t w4[4] = {d.x, d.y, d.z, d.w};
                                 int nv;
@@ -719,7 +685,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                                 fv = reinterpret_cast<const float *>(stg)[tl * 32 + lane];
                                 ((float *)o_ptr)[(size_t)tok * o_stride + row] = fv;
                             }
-                            if (gather && !deposit) {
+                            if (gather) {
                                 const size_t word = (gather_step & 1u) * p.half_words +
                                                     ((size_t)p.rank * p.M + tok) * p.N + (row - p.row_offset);
                                 for (int dd = 0; dd < p.world; dd++)
@@ -731,17 +697,117 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                 }
                 __syncwarp();                                    // staging is reused by the next group
             }
-            if (partial) {
-                if (deposit) {
-                    __threadfence();                             // this thread's deposit is visible device-wide
-                    named_barrier_sync(2, EPI_THREADS);
-                    if (ew == 0 && lane == 0) atomicAdd(p.ws_counters + 2 * tt + 1, 1u);
-                } else {
-                    named_barrier_sync(2, EPI_THREADS);          // all deposits have been read
-                    if (ew == 0 && lane == 0) {                  // leave the counters at zero for the next launch
-                        p.ws_counters[2 * tt] = 0;
-                        p.ws_counters[2 * tt + 1] = 0;
+            if (deposit) {
+                named_barrier_sync(2, EPI_THREADS);
+                if (ew == 0 && lane == 0) {
+                    __threadfence();                             // the deposits of all four warps, device-wide
+                    atomicAdd(p.ws_counters + 2 * tt, 1u);
+                }
+            }
+        }
+        // ---- duties: this CTA's share of the sums of the cut tiles it holds a piece of ----
+        for (int di = 0; di < n_duty && !dead; di++) {
+            const Duty dy = duty[di];
+            uint32_t *cnt = p.ws_counters + 2 * dy.tt;
+            // the tile as TN * 32 groups of four rows; piece q of P takes groups [q * tot / P, (q + 1) * tot / P)
+            constexpr int TOT = TN * (TILE_ROWS / 4);
+            const int q = (int)blockIdx.x - dy.c_first;
+            const int e_lo = (int)(((long long)q * TOT) / dy.pieces), e_hi = (int)(((long long)(q + 1) * TOT) / dy.pieces);
+            const int n_e = e_hi - e_lo;
+            const uint32_t slice_bytes = (uint32_t)n_e * 16u;
+            // This CTA's share of every deposit comes into the (now idle) stage area by bulk copies: up to 128 KB
+            // behind one barrier instead of a trip to L2 per few values.  Every tensor-core instruction and
+            // tiled copy that used the stage area has completed: the last accumulator has been read.
+            if (ew == 0 && lane == 0) {
+                bool seen = false;
+                for (uint32_t i = 0; i < p.wait_limit && !seen; i++) {
+                    uint32_t n;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(n) : "l"(cnt) : "memory");
+                    seen = n >= (uint32_t)dy.pieces;
+                    if (!seen) __nanosleep(32);
+                }
+                if (!seen) report_error(p.err, KERR_SPLIT_WAIT);
+                asm volatile("fence.proxy.async;" ::: "memory");     // the copies below read what generic stores wrote
+                mbar_arrive_expect_tx(duty_bar, (uint32_t)dy.pieces * slice_bytes);
+                for (int ci = 0; ci < dy.pieces; ci++) {
+                    const int c = dy.c_first + ci;
+                    const int k = ci == 0 ? 1 : 0;               // the first piece is the end of its CTA's range
+                    const float4 *sl = reinterpret_cast<const float4 *>(p.ws_slots + (size_t)(2 * c + k) * (TILE_ROWS * TN)) + e_lo;
+                    bulk_copy_g2s(tiles + (size_t)ci * slice_bytes, sl, slice_bytes, duty_bar);
+                }
+            }
+            if (!mbar_wait(duty_bar, (uint32_t)di & 1u, p.wait_limit)) {
+                report_error(p.err, KERR_FULL_WAIT);
+                dead = true;
+                break;
+            }
+            const bool o_bf16 = p.out_bf16 != 0;
+            const bool vec_ok = (p.n_total & 3) == 0 && (p.row_offset & 3) == 0;
+            // EU groups per thread at a time, so that the shared-memory reads, the token factors and the stores
+            // of eight groups overlap (one group at a time, each step waited for the one before: 19 us per tile)
+            constexpr int EU = 8;
+            for (int el0 = ew * 32 + lane; el0 < n_e; el0 += EU * EPI_THREADS) {
+                float4 acc4[EU];
+                float ts[EU];
+#pragma unroll
+                for (int j = 0; j < EU; j++) {
+                    acc4[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    const int e = e_lo + min(el0 + j * EPI_THREADS, n_e - 1);
+                    ts[j] = __ldg(p.tok_scale + min(dy.t0 + e / (TILE_ROWS / 4), p.M - 1));
+                }
+                for (int ci = 0; ci < dy.pieces; ci++) {
+                    const uint8_t *sl = tiles + (size_t)ci * slice_bytes;
+#pragma unroll
+                    for (int j = 0; j < EU; j++) {
+                        const float4 v4 = *reinterpret_cast<const float4 *>(sl + (size_t)min(el0 + j * EPI_THREADS, n_e - 1) * 16);
+                        acc4[j].x += v4.x; acc4[j].y += v4.y; acc4[j].z += v4.z; acc4[j].w += v4.w;
                     }
+                }
+#pragma unroll
+                for (int j = 0; j < EU; j++) {
+                    const int el = el0 + j * EPI_THREADS;
+                    if (el >= n_e) continue;
+                    const int e = e_lo + el;
+                    const int tok = dy.t0 + e / (TILE_ROWS / 4), row = p.row_offset + dy.n0 + 4 * (e % (TILE_ROWS / 4));
+                    if (tok >= p.M || row >= p.row_offset + p.N) continue;
+                    float f[4] = {acc4[j].x * ts[j], acc4[j].y * ts[j], acc4[j].z * ts[j], acc4[j].w * ts[j]};
+                    const int nv = min(4, p.row_offset + p.N - row);
+                    const size_t o = (size_t)tok * p.n_total + row;
+                    if (o_bf16) {
+                        __nv_bfloat16 hb[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            hb[i] = __float2bfloat16_rn(f[i]);
+                            f[i] = __bfloat162float(hb[i]);      // what the peers get is what this rank stores
+                        }
+                        if (vec_ok && nv == 4) {
+                            *reinterpret_cast<uint2 *>((__nv_bfloat16 *)p.Out + o) = *reinterpret_cast<const uint2 *>(hb);
+                        } else {
+                            for (int i = 0; i < nv; i++) ((__nv_bfloat16 *)p.Out)[o + i] = hb[i];
+                        }
+                    } else {
+                        if (vec_ok && nv == 4) {
+                            *reinterpret_cast<float4 *>((float *)p.Out + o) = make_float4(f[0], f[1], f[2], f[3]);
+                        } else {
+                            for (int i = 0; i < nv; i++) ((float *)p.Out)[o + i] = f[i];
+                        }
+                    }
+                    if (gather) {                                // the same values, as words, to every peer's mailbox
+                        const size_t word = (gather_step & 1u) * p.half_words + ((size_t)p.rank * p.M + tok) * p.N + (row - p.row_offset);
+                        for (int dd = 0; dd < p.world; dd++) {
+                            if (dd == p.rank) continue;
+                            uint2 *box = p.peer_box[dd] + word;
+                            for (int i = 0; i < nv; i++) mailbox_store(box + i, __float_as_uint(f[i]), gather_step);
+                        }
+                    }
+                }
+            }
+            named_barrier_sync(2, EPI_THREADS);                  // every thread has read what it needs
+            if (ew == 0 && lane == 0) {
+                // the last of the P CTAs to finish leaves both counters at zero for the next launch
+                if (atomicAdd(cnt + 1, 1u) + 1u == (uint32_t)dy.pieces) {
+                    cnt[0] = 0;
+                    cnt[1] = 0;
                 }
             }
         }
@@ -877,21 +943,23 @@ activations_to_f16_kernel(const void *__restrict__ x, int x_is_bf16, int K, __ha
 
 // ---- host side ---------------------------------------------------------------------------------
 
-// Does cutting the last, partial wave of tiles along K pay?  The exchange is not free: a deposit
-// is a tile-sized fp32 store, and the last arriver reads the deposits back group by group, one
-// L2 round trip per two deposits.  Measured on a B200 (split / no split): K=14336, N=4096
-// (32 tiles up to 128 tokens, 64 at 512) 0.52 at 16 tokens, 0.61 at 64, 0.73 at 128, 0.94 at 512;
-// K=4096 shapes 0.92 .. 1.46; more than half a wave of 256-token tiles 1.04 .. 1.8.  So the split
-// is used where at least half of the SMs would otherwise idle through a long K loop.
-// The two-term kernel spends about twice as long on a K block, the exchange costs the same, so there
-// the split already pays at K=4096 (split / no split with up to 32 tiles: 0.57 .. 0.80 at 8 .. 64
-// tokens; K=14336: 0.36 .. 0.40; 112 tiles: 1.12).
+// Does cutting the last, partial wave of tiles along K pay?  The exchange is not free: every piece is a
+// tile-sized fp32 store from the registers, and the sum reads one tile's worth per CTA (a tile in two pieces
+// is summed by the CTA that holds its first block, more pieces share the sum out).  The two-term kernel
+// keeps the rule it was measured with (up to half a wave of tiles, K >= 4096).
 // `forced` = 0 / 1 overrides the rule (measurements and tests), -1 leaves it alone.
 bool split_pays(int n_tiles, int nb, int sms, int forced, bool two_term) {
     const int rest = n_tiles % sms;
     if (rest == 0 || nb < 2) return false;
     if (forced >= 0) return forced != 0;
-    return n_tiles <= sms / 2 && nb >= (two_term ? 16 : 32);
+    if (two_term) return n_tiles <= sms / 2 && nb >= 16;
+    // The last, partial wave runs `rest` tiles for nb block times; cut over all SMs it takes nb * rest / sms of
+    // them, but the exchange and the shorter units cost the equivalent of 15-20 block times at 128- and
+    // 256-token tiles (measured on a B200, split / unsplit: K=14336 -> 4096 0.55 at 128 tokens, 0.73 at 512,
+    // 1.03 at 2048; K=4096 -> 14336 1.36, 1.15, 0.97).  So: where at least 20 block times are saved, or at
+    // least 8 when the tail is so short that every CTA gets one block (one deposit, a small share of the sum).
+    const long long saved_x_sms = (long long)nb * (sms - rest);
+    return nb >= 4 && (saved_x_sms >= 20LL * sms || (saved_x_sms >= 8LL * sms && (long long)rest * nb <= sms));
 }
 
 template <int QT, int TN, bool SPLIT = false>
