@@ -121,6 +121,11 @@ template <int QT, int TN> struct ExactCfg {
     static constexpr int GROUPS = STAGES < 4 ? STAGES : 4;
     static constexpr int RAW_SLOTS = RAW_FIT < 6 ? RAW_FIT : 6;
     static_assert(RAW_SLOTS >= 2 && 2 * RAW_SLOTS >= GROUPS + STAGES, "raw ring against the groups' look-ahead");
+    // every stage belongs to one group (its warps track what they left in the stage's lo columns), and the d
+    // values of a block stay in their ring until the epilogue has used them: the dequantisation runs at most
+    // STAGES / 2 blocks ahead of the tensor core, which runs at most two blocks ahead of the epilogue
+    static_assert(GROUPS == STAGES, "one dequantising group per operand stage");
+    static_assert(D_RING >= 2 + (STAGES + 1) / 2, "ring of per-block d values");
     static constexpr size_t SMEM = FIXED + (size_t)RAW_SLOTS * RAW_SLOT_BYTES;
     static constexpr uint32_t TMEM_COLS = 512;
     static_assert(A_BASE_COL + STAGES * A_STAGE_COLS <= 512, "tensor memory budget");
