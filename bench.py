@@ -790,12 +790,18 @@ def extra_measurements(be_factory, stream, peak_gbs):
             xs = {4096: be.upload_tensor(TensorView("x", DType.BF16, shp(4096), synth.bf16_bits(synth.activations(M, 4096)))),
                   14336: be.upload_tensor(TensorView("x", DType.BF16, shp(14336), synth.bf16_bits(synth.activations(M, 14336))))}
             outs = {n: be.alloc(shp(n), DType.BF16) for n in (4096, 1024, 14336, 128256)}
+            outs_v = be.alloc(shp(1024), DType.BF16)
+            norm_w = be.upload_tensor(TensorView("g", DType.F32, [4096], np.ones(4096, np.float32)))
 
-            def step(one_call_ffn=False):
+            def step(one_call_ffn=False, one_call_qkv=False):
                 for l in range(32):
                     ws = sets[l % n_layer_sets]
                     for i, ((dt, K, N), wb) in enumerate(zip(layer, ws)):
-                        if one_call_ffn and i == 4:          # gate and up (and silu, mul) as one call
+                        if one_call_qkv and i == 0:          # norm + q, k, v projections as one call
+                            be.rms_norm_matmul_qkv(outs[4096], outs[1024], outs_v, ws[0], ws[1], ws[2], xs[K], norm_w, 1e-5)
+                        elif one_call_qkv and i in (1, 2):
+                            pass
+                        elif one_call_ffn and i == 4:        # gate and up (and silu, mul) as one call
                             be.matmul_gate_up(outs[N], ws[4], ws[5], xs[K])
                         elif not (one_call_ffn and i == 5):
                             be.matmul(outs[N], wb, xs[K])
@@ -822,6 +828,7 @@ def extra_measurements(be_factory, stream, peak_gbs):
 
             t = timed_graph(step)
             t_ffn = timed_graph(lambda: step(True))
+            t_both = timed_graph(lambda: step(True, True))
             out["decode_stack"][f"m{M}"] = {"ms_per_step": round(t * 1e3, 4), "tok_per_s": round(M / t, 1),
                                             "weight_GBps": round(weight_bytes / t / 1e9, 1),
                                             "frac_of_hbm_peak": round(weight_bytes / t / 1e9 / peak_gbs, 4),
@@ -829,8 +836,13 @@ def extra_measurements(be_factory, stream, peak_gbs):
                                             "with_gate_up_as_one_call": {
                                                 "ms_per_step": round(t_ffn * 1e3, 4), "tok_per_s": round(M / t_ffn, 1),
                                                 "frac_of_hbm_peak": round(weight_bytes / t_ffn / 1e9 / peak_gbs, 4),
-                                                "calls_per_step": 193}}
-            for b in list(xs.values()) + list(outs.values()):
+                                                "calls_per_step": 193},
+                                            "with_norm_qkv_and_gate_up_as_one_call_each": {
+                                                "ms_per_step": round(t_both * 1e3, 4), "tok_per_s": round(M / t_both, 1),
+                                                "frac_of_hbm_peak": round(weight_bytes / t_both / 1e9 / peak_gbs, 4),
+                                                "calls_per_step": 129,
+                                                "note": "the q/k/v call also computes the rms_norm in front of them"}}
+            for b in list(xs.values()) + list(outs.values()) + [outs_v, norm_w]:
                 b.free()
         # A whole decode step of the 8B shape through the trait: per layer rms_norm, q/k/v matmuls, rope,
         # scatter_kv, paged attention, wo matmul, add, rms_norm, gate/up + silu * mul as one call, down

@@ -652,6 +652,31 @@ static cudaError_t tc_matmul(llmrs_ctx *ctx, uint32_t wdtype, const void *w, con
                        ctx->two_term);
 }
 
+// Several K-quant weights of one format against one input on the small-batch tensor-core kernel, one launch.
+// The caller has checked shapes and devices; false: not eligible, use single calls.
+static bool tc_matmul_multi_ok(const llmrs_ctx *ctx, int n, const llmrs_buf *const *ws, const llmrs_buf *const *outs, uint32_t M) {
+    if (n < 2 || n > 3 || !uses_exact_kernel(ctx, M)) return false;
+    for (int i = 0; i < n; i++) {
+        if (ws[i]->dtype != ws[0]->dtype || ws[i]->dim0 != ws[0]->dim0 || outs[i]->dtype != outs[0]->dtype) return false;
+        if (ws[i]->dtype != LLMRS_Q4K && ws[i]->dtype != LLMRS_Q6K) return false;
+        if (ws[i]->layout != (ws[i]->dtype == LLMRS_Q6K ? LLMRS_LAYOUT_Q6K_SLICES : LLMRS_LAYOUT_RAW)) return false;
+    }
+    return true;
+}
+static cudaError_t tc_matmul_multi(llmrs_ctx *ctx, int n, const llmrs_buf *const *ws, void *const *outs, uint32_t out_dtype,
+                                   const void *x, uint32_t x_dtype, uint32_t K, uint32_t M) {
+    const uint8_t *wp[3];
+    int ns[3];
+    for (int i = 0; i < n; i++) {
+        wp[i] = (const uint8_t *)ws[i]->dptr;
+        ns[i] = (int)(ws[i]->dim1 ? ws[i]->dim1 : 1);
+    }
+    ctx->acts_have = false;
+    return launch_gemm_exact_multi((int)ws[0]->dtype, n, wp, ns, outs, x, (int)x_dtype, (int)out_dtype, (int)K, (int)M,
+                                   ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->sink(), ctx->stream, &ctx->launches,
+                                   ctx->pdl, ctx->sm_count);
+}
+
 // Between the decode kernel's token limit and 64 tokens both kernels meet the decode tolerance, so
 // the cheaper one runs.  The decode kernel streams the weights once per pass of up to four tokens
 // (fewer where the staged activations of four do not fit): about 2 us + 0.15 us per MB and token,
@@ -1165,6 +1190,29 @@ int llmrs_cuda_rms_norm_matmul_qkv(llmrs_ctx *ctx, llmrs_buf *out_q, llmrs_buf *
     if (!one_pass) {
         if ((int)M > ctx->gemv_max_m)                    // no kernel folds the norm in at this token count: normalise once
             return with_norm(ctx, "rms_norm_matmul_qkv", input, norm_weight, eps, false, [&](const llmrs_buf *x) {
+                // one launch over the three weights where they share a format; else three calls, one conversion
+                bool shapes_ok = true;
+                for (int i = 0; i < 3; i++) {
+                    const uint32_t n = ws[i]->dim1 ? ws[i]->dim1 : 1;
+                    shapes_ok = shapes_ok && ws[i]->dim0 == K && K % QK_K == 0 && outs[i]->dim0 == n &&
+                                (outs[i]->dim1 ? outs[i]->dim1 : 1) == M && dense_elem_bytes(outs[i]->dtype) &&
+                                dense_elem_bytes(x->dtype) && ws[i]->device == (uint32_t)ctx->device &&
+                                outs[i]->device == (uint32_t)ctx->device &&
+                                !(reinterpret_cast<uintptr_t>(ws[i]->dptr) & 15);
+                }
+                if (shapes_ok && tc_matmul_multi_ok(ctx, 3, ws, outs, M)) {
+                    DeviceGuard guard(ctx->device);
+                    cudaError_t e = ctx->reserve_scratch(tc_scratch_bytes(ctx, K, M));
+                    if (e != cudaSuccess) return ctx->cuda_fail(e, "rms_norm_matmul_qkv: scratch (grow it with one call outside graph capture)");
+                    e = ctx->begin_work();
+                    if (e != cudaSuccess) return ctx->cuda_fail(e, "rms_norm_matmul_qkv: event");
+                    PerfScope perf(ctx, "matmul q/k/v, one launch", matmul_bytes(wq, x, out_q) + matmul_bytes(wk, x, out_k) + matmul_bytes(wv, x, out_v),
+                                   matmul_flops(wq, x) + matmul_flops(wk, x) + matmul_flops(wv, x));
+                    void *op[3] = {out_q->dptr, out_k->dptr, out_v->dptr};
+                    e = tc_matmul_multi(ctx, 3, ws, op, outs[0]->dtype, x->dptr, x->dtype, K, M);
+                    if (e != cudaSuccess) return ctx->cuda_fail(e, "rms_norm_matmul_qkv: launch");
+                    return (int)LLMRS_OK;
+                }
                 ActsShareScope share(ctx);
                 int rc = LLMRS_OK;
                 for (int i = 0; i < 3 && rc == LLMRS_OK; i++) rc = llmrs_cuda_matmul(ctx, outs[i], ws[i], x);
@@ -1266,6 +1314,13 @@ int llmrs_cuda_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *w
     const llmrs_buf *ws[2] = {w_gate, w_up};
     float *dst[2] = {g, u};
     ActsShareScope share(ctx);
+    llmrs_buf gbuf = *out, ubuf = *out;              // float32 stand-ins for the eligibility check
+    gbuf.dtype = ubuf.dtype = LLMRS_F32;
+    const llmrs_buf *tmp_outs[2] = {&gbuf, &ubuf};
+    if (!decode && tc_matmul_multi_ok(ctx, 2, ws, tmp_outs, M)) {
+        void *op[2] = {g, u};
+        e = tc_matmul_multi(ctx, 2, ws, op, LLMRS_F32, input->dptr, input->dtype, K, M);
+    } else
     for (int i = 0; i < 2 && e == cudaSuccess; i++) {
         if (decode)
             e = launch_gemv((int)ws[i]->dtype, (const uint8_t *)ws[i]->dptr, input->dptr, (int)input->dtype, dst[i],

@@ -132,8 +132,8 @@ template <int QT, int TN> struct ExactCfg {
 };
 
 struct ExactMaps {
-    CUtensorMap w_a;     // weights as bytes [N rows][row stride]: box 144 x 128 (Q4_K) / 48 x 128 (Q6_K)
-    CUtensorMap w_b;     // Q6_K: box 16 x 128
+    CUtensorMap w_a[3];  // per weight of the launch: bytes [N rows][row stride], box 144 x 128 (Q4_K) / 48 x 128 (Q6_K)
+    CUtensorMap w_b[3];  // Q6_K: box 16 x 128
 };
 
 __device__ __forceinline__ uint4 lds128(const uint8_t *p) { return *reinterpret_cast<const uint4 *>(p); }
@@ -485,7 +485,10 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         UnitIter ui;
         Unit u;
         while (ok && ui.next(sc, u)) {
-            const int n0 = (u.tile % w_tiles) * TILE_ROWS;
+            const int wt = u.tile % w_tiles;
+            const int sg = (wt >= p.seg_tile[1]) + (wt >= p.seg_tile[2]);      // which weight of the launch
+            const int n0 = (wt - p.seg_tile[sg]) * TILE_ROWS;
+            const CUtensorMap *map_a = &maps.w_a[sg], *map_b = &maps.w_b[sg];
             for (int b = u.b0; b < u.b1; b++, blk++) {
                 const uint32_t rs = blk % R;
                 if (blk >= (uint32_t)R && !mbar_wait(&raw_empty[rs], ((blk / R) - 1) & 1, p.wait_limit)) {
@@ -497,16 +500,16 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                 if (leader) {
                     mbar_arrive_expect_tx(&raw_full[rs], C::RAW_SLOT_BYTES);
                     if constexpr (QT == 0) {
-                        tma_load_2d(slot, &maps.w_a, b * Q4K_BLOCK_BYTES, n0, &raw_full[rs]);
+                        tma_load_2d(slot, map_a, b * Q4K_BLOCK_BYTES, n0, &raw_full[rs]);
                     } else {
                         const int ci = b >> 4, bl = b & 15;
                         const int nbc = min(16, nb - 16 * ci);
                         const int base = 3360 * ci;
 #pragma unroll
                         for (int j = 0; j < 4; j++)
-                            tma_load_2d(slot + j * C::Q6_SLICE_BOX, &maps.w_a, base + 192 * bl + 48 * j, n0, &raw_full[rs]);
-                        tma_load_2d(slot + 4 * C::Q6_SLICE_BOX, &maps.w_b, base + 192 * nbc + 16 * bl, n0, &raw_full[rs]);
-                        tma_load_2d(slot + 4 * C::Q6_SLICE_BOX + C::Q6_SMALL_BOX, &maps.w_b,
+                            tma_load_2d(slot + j * C::Q6_SLICE_BOX, map_a, base + 192 * bl + 48 * j, n0, &raw_full[rs]);
+                        tma_load_2d(slot + 4 * C::Q6_SLICE_BOX, map_b, base + 192 * nbc + 16 * bl, n0, &raw_full[rs]);
+                        tma_load_2d(slot + 4 * C::Q6_SLICE_BOX + C::Q6_SMALL_BOX, map_b,
                                     base + 208 * nbc + ((2 * bl) & ~15), n0, &raw_full[rs]);
                     }
                 }
@@ -614,12 +617,14 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
         pdl_wait();                                   // token factors, exchange counters, mailbox step: all from earlier kernels
         const uint32_t gather_step = gather ? *reinterpret_cast<volatile uint32_t *>(p.step_word) + 1u : 0u;
         const uint32_t lane_off = (uint32_t)(32 * quarter) << 16;
-        struct Duty { int tt, c_first, pieces, n0, t0; } duty[2];      // the cut tiles this CTA holds a piece of
+        struct Duty { int tt, c_first, pieces, n0, t0, sg; } duty[2];  // the cut tiles this CTA holds a piece of
         int n_duty = 0;
         UnitIter ui;
         Unit u;
         for (; !dead && ui.next(sc, u); ucount++) {
-            const int n0 = (u.tile % w_tiles) * TILE_ROWS, t0 = (u.tile / w_tiles) * TN;
+            const int wt = u.tile % w_tiles, t0 = (u.tile / w_tiles) * TN;
+            const int sg = (wt >= p.seg_tile[1]) + (wt >= p.seg_tile[2]);      // which weight of the launch
+            const int n0 = (wt - p.seg_tile[sg]) * TILE_ROWS;
             const bool partial = u.b1 - u.b0 < sc.nb;
             for (int c = lane; c < TN; c += 32) scale_s[c] = (t0 + c < p.M) ? __ldg(p.tok_scale + t0 + c) : 0.0f;
             __syncwarp();
@@ -715,7 +720,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                     }
                     if (shared_sum) {
                         duty[n_duty].tt = tt; duty[n_duty].c_first = c_first; duty[n_duty].pieces = pieces;
-                        duty[n_duty].n0 = n0; duty[n_duty].t0 = t0;
+                        duty[n_duty].n0 = n0; duty[n_duty].t0 = t0; duty[n_duty].sg = sg;
                         n_duty++;
                     }
                     continue;
@@ -758,9 +763,12 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
             // ---- where this unit's values go ----
             const bool o_bf16 = p.out_bf16 != 0;
             const int esz = o_bf16 ? 2 : 4;
-            uint8_t *o_ptr = (uint8_t *)p.Out;
-            const size_t o_stride = (size_t)p.n_total;          // elements between tokens (n_total = N unless sharded)
-            const int tok_base = t0, row_base = p.row_offset + n0 + 32 * quarter, tok_lim = p.M, row_lim = p.row_offset + p.N;
+            // one weight: rows [row_offset, row_offset + N) of an n_total-row output; several: each its own output
+            const bool multi = p.n_seg > 1;
+            uint8_t *o_ptr = (uint8_t *)(multi ? p.seg_out[sg] : p.Out);
+            const int n_rows = multi ? p.seg_n[sg] : p.N, row_off = multi ? 0 : p.row_offset;
+            const size_t o_stride = (size_t)(multi ? n_rows : p.n_total);    // elements between tokens
+            const int tok_base = t0, row_base = row_off + n0 + 32 * quarter, tok_lim = p.M, row_lim = row_off + n_rows;
             const bool vec_ok = (o_stride % (size_t)(16 / esz)) == 0;
 #pragma unroll
             for (int g0 = 0; g0 < TN; g0 += EPI_TOK) {
@@ -852,7 +860,11 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
             const int q = (int)blockIdx.x - dy.c_first;
             const int e_lo = (int)(((long long)q * TOT) / dy.pieces), e_hi = (int)(((long long)(q + 1) * TOT) / dy.pieces);
             const bool o_bf16 = p.out_bf16 != 0;
-            const bool vec_ok = (p.n_total & 3) == 0 && (p.row_offset & 3) == 0;
+            const bool multi = p.n_seg > 1;
+            void *o_base = multi ? p.seg_out[dy.sg] : p.Out;
+            const int n_rows = multi ? p.seg_n[dy.sg] : p.N, row_off = multi ? 0 : p.row_offset;
+            const int n_tot = multi ? n_rows : p.n_total;
+            const bool vec_ok = (n_tot & 3) == 0 && (row_off & 3) == 0;
             for (int e = e_lo + ew * 32 + lane; e < e_hi; e += EPI_THREADS) {
                 float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 for (int c0 = 0; c0 < dy.pieces; c0 += 4) {
@@ -867,12 +879,12 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                     for (int i = 0; i < 4; i++)
                         if (c0 + i < dy.pieces) { acc.x += v[i].x; acc.y += v[i].y; acc.z += v[i].z; acc.w += v[i].w; }
                 }
-                const int tok = dy.t0 + e / (TILE_ROWS / 4), row = p.row_offset + dy.n0 + 4 * (e % (TILE_ROWS / 4));
-                if (tok >= p.M || row >= p.row_offset + p.N) continue;
+                const int tok = dy.t0 + e / (TILE_ROWS / 4), row = row_off + dy.n0 + 4 * (e % (TILE_ROWS / 4));
+                if (tok >= p.M || row >= row_off + n_rows) continue;
                 const float ts = __ldg(p.tok_scale + tok);
                 float f[4] = {acc.x * ts, acc.y * ts, acc.z * ts, acc.w * ts};
-                const int nv = min(4, p.row_offset + p.N - row);
-                const size_t o = (size_t)tok * p.n_total + row;
+                const int nv = min(4, row_off + n_rows - row);
+                const size_t o = (size_t)tok * n_tot + row;
                 if (o_bf16) {
                     __nv_bfloat16 hb[4];
 #pragma unroll
@@ -881,15 +893,15 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
                         f[i] = __bfloat162float(hb[i]);          // what the peers get is what this rank stores
                     }
                     if (vec_ok && nv == 4) {
-                        *reinterpret_cast<uint2 *>((__nv_bfloat16 *)p.Out + o) = *reinterpret_cast<const uint2 *>(hb);
+                        *reinterpret_cast<uint2 *>((__nv_bfloat16 *)o_base + o) = *reinterpret_cast<const uint2 *>(hb);
                     } else {
-                        for (int i = 0; i < nv; i++) ((__nv_bfloat16 *)p.Out)[o + i] = hb[i];
+                        for (int i = 0; i < nv; i++) ((__nv_bfloat16 *)o_base)[o + i] = hb[i];
                     }
                 } else {
                     if (vec_ok && nv == 4) {
-                        *reinterpret_cast<float4 *>((float *)p.Out + o) = make_float4(f[0], f[1], f[2], f[3]);
+                        *reinterpret_cast<float4 *>((float *)o_base + o) = make_float4(f[0], f[1], f[2], f[3]);
                     } else {
-                        for (int i = 0; i < nv; i++) ((float *)p.Out)[o + i] = f[i];
+                        for (int i = 0; i < nv; i++) ((float *)o_base)[o + i] = f[i];
                     }
                 }
                 if (gather) {                                    // the same values, as words, to every peer's mailbox
@@ -1099,6 +1111,12 @@ activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M
 
 // ---- host side ---------------------------------------------------------------------------------
 
+struct ExactWeights {            // the weights of one launch (one format, one K)
+    int n;
+    const uint8_t *w[3];
+    int rows[3];
+};
+
 int exact_tn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
 // the converted activations: whole token tiles, X_BLOCK_SUBTILES sub-tiles of TN x 128 bytes per block
 size_t exact_x_bytes(int K, int M) {
@@ -1108,22 +1126,25 @@ size_t exact_x_bytes(int K, int M) {
 }
 
 template <int QT, int TN>
-cudaError_t launch_exact_tn(const GemmParams &p, int split_mode, cudaStream_t s, bool pdl) {
+cudaError_t launch_exact_tn(const GemmParams &p, const ExactWeights &ws, int split_mode, cudaStream_t s, bool pdl) {
     using C = ExactCfg<QT, TN>;
     ExactMaps maps;
-    cudaError_t e;
-    if (QT == 0) {
-        e = encode_2d(&maps.w_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.W, (uint64_t)p.row_stride, (uint64_t)p.N,
-                      (uint64_t)p.row_stride, Q4K_BLOCK_BYTES, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
-        if (e != cudaSuccess) return e;
-        maps.w_b = maps.w_a;
-    } else {
-        e = encode_2d(&maps.w_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.W, (uint64_t)p.row_stride, (uint64_t)p.N,
-                      (uint64_t)p.row_stride, 48, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
-        if (e != cudaSuccess) return e;
-        e = encode_2d(&maps.w_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.W, (uint64_t)p.row_stride, (uint64_t)p.N,
-                      (uint64_t)p.row_stride, 16, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
-        if (e != cudaSuccess) return e;
+    cudaError_t e = cudaSuccess;
+    for (int i = 0; i < 3; i++) {
+        const int k = i < ws.n ? i : 0;               // unused entries repeat the first weight's maps
+        if (QT == 0) {
+            e = encode_2d(&maps.w_a[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, ws.w[k], (uint64_t)p.row_stride, (uint64_t)ws.rows[k],
+                          (uint64_t)p.row_stride, Q4K_BLOCK_BYTES, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+            if (e != cudaSuccess) return e;
+            maps.w_b[i] = maps.w_a[i];
+        } else {
+            e = encode_2d(&maps.w_a[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, ws.w[k], (uint64_t)p.row_stride, (uint64_t)ws.rows[k],
+                          (uint64_t)p.row_stride, 48, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+            if (e != cudaSuccess) return e;
+            e = encode_2d(&maps.w_b[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, ws.w[k], (uint64_t)p.row_stride, (uint64_t)ws.rows[k],
+                          (uint64_t)p.row_stride, 16, TILE_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+            if (e != cudaSuccess) return e;
+        }
     }
     auto kern = gemm_exact_kernel<QT, TN>;
     static bool smem_set[64] = {};                    // per instantiation and device: the attribute is kept by the function
@@ -1162,10 +1183,10 @@ cudaError_t launch_exact_tn(const GemmParams &p, int split_mode, cudaStream_t s,
 }
 
 template <int QT>
-cudaError_t launch_exact_qt(const GemmParams &p, int split_mode, cudaStream_t s, bool pdl) {
-    if (p.M <= 16) return launch_exact_tn<QT, 16>(p, split_mode, s, pdl);
-    if (p.M <= 32) return launch_exact_tn<QT, 32>(p, split_mode, s, pdl);
-    return launch_exact_tn<QT, 64>(p, split_mode, s, pdl);
+cudaError_t launch_exact_qt(const GemmParams &p, const ExactWeights &ws, int split_mode, cudaStream_t s, bool pdl) {
+    if (p.M <= 16) return launch_exact_tn<QT, 16>(p, ws, split_mode, s, pdl);
+    if (p.M <= 32) return launch_exact_tn<QT, 32>(p, ws, split_mode, s, pdl);
+    return launch_exact_tn<QT, 64>(p, ws, split_mode, s, pdl);
 }
 
 }  // namespace
@@ -1175,13 +1196,18 @@ size_t gemm_exact_scratch_bytes(int K, int M) {
     return exact_x_bytes(K, M) + (size_t)M * sizeof(float);
 }
 
-cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
-                              int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
-                              cudaStream_t s, uint64_t *launches, const GemmGather *gather, bool pdl, int sm_count,
-                              int acts_mode) {
-    if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
+static cudaError_t launch_exact_common(int wdtype, int nw, const uint8_t *const *ws, const int *ns, void *const *outs,
+                                       const void *x, int x_dtype, int out_dtype, int K, int M, void *scratch,
+                                       void *split_ws, int split_mode, ErrSink err_word, cudaStream_t s,
+                                       uint64_t *launches, const GemmGather *gather, bool pdl, int sm_count,
+                                       int acts_mode) {
+    if (nw < 1 || nw > 3) return cudaErrorInvalidValue;
+    if (K <= 0 || M <= 0) return cudaSuccess;
+    for (int i = 0; i < nw; i++)
+        if (ns[i] <= 0) return nw == 1 ? cudaSuccess : cudaErrorInvalidValue;
     if (!scratch || M > GEMM_EXACT_MAX_TOKENS || K % QK_K) return cudaErrorInvalidValue;
     if (wdtype != DT_Q4K && wdtype != DT_Q6K) return cudaErrorInvalidValue;
+    if (nw > 1 && gather && gather->world > 1) return cudaErrorInvalidValue;
     uint8_t *sb = (uint8_t *)scratch;
     float *tok_scale = (float *)(sb + exact_x_bytes(K, M));
     const int tn = exact_tn(M), m_pad = (M + tn - 1) / tn * tn;
@@ -1197,7 +1223,21 @@ cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x
         if (launches) (*launches)++;
     }
     GemmParams p{};
-    p.W = w; p.Out = out; p.err = err_word.word; p.wait_limit = err_word.mbar_polls; p.gather_limit = err_word.gather_polls;
+    ExactWeights ew{};
+    ew.n = nw;
+    int tiles = 0;
+    p.n_seg = nw;
+    for (int i = 0; i < 4; i++) p.seg_tile[i] = 0x7fffffff;
+    for (int i = 0; i < nw; i++) {
+        ew.w[i] = ws[i];
+        ew.rows[i] = ns[i];
+        p.seg_tile[i] = tiles;
+        p.seg_n[i] = ns[i];
+        p.seg_out[i] = outs[i];
+        tiles += (ns[i] + TILE_ROWS - 1) / TILE_ROWS;
+    }
+    const int N = nw == 1 ? ns[0] : tiles * TILE_ROWS;      // several weights: the tile space, each weight from a tile boundary
+    p.W = ws[0]; p.Out = outs[0]; p.err = err_word.word; p.wait_limit = err_word.mbar_polls; p.gather_limit = err_word.gather_polls;
     p.K = K; p.N = N; p.M = M; p.out_bf16 = out_dtype == DT_BF16;
     p.tok_scale = tok_scale;
     p.x_tiles = sb;
@@ -1221,13 +1261,29 @@ cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x
     }
     if (wdtype == DT_Q4K) {
         p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
-        e = launch_exact_qt<0>(p, split_mode, s, pdl);
+        e = launch_exact_qt<0>(p, ew, split_mode, s, pdl);
     } else {
         p.row_stride = q6k_row_stride(K);
-        e = launch_exact_qt<1>(p, split_mode, s, pdl);
+        e = launch_exact_qt<1>(p, ew, split_mode, s, pdl);
     }
     if (e == cudaSuccess && launches) (*launches)++;
     return e;
+}
+
+cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
+                              int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
+                              cudaStream_t s, uint64_t *launches, const GemmGather *gather, bool pdl, int sm_count,
+                              int acts_mode) {
+    return launch_exact_common(wdtype, 1, &w, &N, &out, x, x_dtype, out_dtype, K, M, scratch, split_ws, split_mode,
+                               err_word, s, launches, gather, pdl, sm_count, acts_mode);
+}
+
+cudaError_t launch_gemm_exact_multi(int wdtype, int nw, const uint8_t *const *ws, const int *ns, void *const *outs,
+                                    const void *x, int x_dtype, int out_dtype, int K, int M, void *scratch,
+                                    void *split_ws, int split_mode, ErrSink err_word, cudaStream_t s, uint64_t *launches,
+                                    bool pdl, int sm_count) {
+    return launch_exact_common(wdtype, nw, ws, ns, outs, x, x_dtype, out_dtype, K, M, scratch, split_ws, split_mode,
+                               err_word, s, launches, nullptr, pdl, sm_count, EXACT_ACTS_CONVERT);
 }
 
 }  // namespace llmrs

@@ -47,6 +47,14 @@ struct GemmParams {
     uint32_t *done_counter, *step_word;
     size_t half_words;
     int world, rank, n_total, row_offset;
+    // Small-batch kernel, several weights of one format and K multiplied with one input in one launch
+    // (n_seg > 1; no all-gather then): weight i owns the row tiles [seg_tile[i], seg_tile[i + 1]) of the
+    // launch's tile space, has seg_n[i] rows and writes to seg_out[i] ([M][seg_n[i]]).  N is then
+    // 128 x the number of row tiles.
+    int n_seg;
+    int seg_tile[4];
+    int seg_n[3];
+    void *seg_out[3];
 };
 
 // ---- work schedule -----------------------------------------------------------------------------
