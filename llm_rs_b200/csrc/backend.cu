@@ -57,6 +57,8 @@ struct llmrs_ctx {
     size_t norm_tmp_bytes = 0;
     const float *norm_w = nullptr;         // set by the rms_norm_matmul calls around theirs
     float norm_eps = 0.0f;
+    const float *conv_norm_w = nullptr;    // likewise, above four tokens: the norm rides in the small-batch kernel's conversion
+    float conv_norm_eps = 0.0f;
     float *att_ws = nullptr;         // partial results of attention over split sequences
     size_t att_ws_bytes = 0;
     uint32_t *argmax_out = nullptr;  // device word argmax writes its result to
@@ -644,7 +646,7 @@ static cudaError_t tc_matmul(llmrs_ctx *ctx, uint32_t wdtype, const void *w, con
         }
         return launch_gemm_exact((int)wdtype, (const uint8_t *)w, x, (int)x_dtype, out, (int)out_dtype, (int)K, (int)N, (int)M,
                                  ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->sink(), ctx->stream, &ctx->launches, gather,
-                                 ctx->pdl, ctx->sm_count, acts_mode);
+                                 ctx->pdl, ctx->sm_count, acts_mode, ctx->conv_norm_w, ctx->conv_norm_eps);
     }
     ctx->acts_have = false;                              // the other kernel writes its own conversion into the scratch
     return launch_gemm((int)wdtype, (const uint8_t *)w, x, (int)x_dtype, out, (int)out_dtype, (int)K, (int)N, (int)M,
@@ -674,7 +676,7 @@ static cudaError_t tc_matmul_multi(llmrs_ctx *ctx, int n, const llmrs_buf *const
     ctx->acts_have = false;
     return launch_gemm_exact_multi((int)ws[0]->dtype, n, wp, ns, outs, x, (int)x_dtype, (int)out_dtype, (int)K, (int)M,
                                    ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->sink(), ctx->stream, &ctx->launches,
-                                   ctx->pdl, ctx->sm_count);
+                                   ctx->pdl, ctx->sm_count, ctx->conv_norm_w, ctx->conv_norm_eps);
 }
 
 // Between the decode kernel's token limit and 64 tokens both kernels meet the decode tolerance, so
@@ -780,7 +782,7 @@ int llmrs_cuda_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weight, c
                          out->dtype);
     if (K % QK_K) return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u is not a multiple of 256", K);
     // a caller that folded a norm or a residual into this call has already chosen the decode kernel
-    const bool decode = ctx->norm_w || ctx->residual || matmul_uses_decode_kernel(ctx, weight, M, K);
+    const bool decode = !ctx->conv_norm_w && (ctx->norm_w || ctx->residual || matmul_uses_decode_kernel(ctx, weight, M, K));
     if (decode && K > gemv_max_k())
         return ctx->fail(LLMRS_ERR_SHAPE, "matmul: in_features %u exceeds the supported maximum %zu", K, gemv_max_k());
     if (input->dim0 != K)
@@ -1125,7 +1127,7 @@ int llmrs_cuda_matmul_add(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *weigh
 // rms_norm fused into the staging of the decode kernel where that kernel serves the call in one launch;
 // otherwise rms_norm into a temporary, then the plain call.
 static int with_norm(llmrs_ctx *ctx, const char *name, const llmrs_buf *input, const llmrs_buf *norm_weight, float eps,
-                     bool fused_ok, const std::function<int(const llmrs_buf *)> &call) {
+                     bool fused_ok, bool conv_ok, const std::function<int(const llmrs_buf *)> &call) {
     if (!norm_weight || !norm_weight->dptr || !input || !input->dptr) return ctx->fail(LLMRS_ERR_ARG, "%s: null buffer", name);
     if (norm_weight->dtype != LLMRS_F32 || norm_weight->dim0 != input->dim0)
         return ctx->fail(LLMRS_ERR_SHAPE, "%s: norm weight must be F32 [%u]", name, input->dim0);
@@ -1134,6 +1136,16 @@ static int with_norm(llmrs_ctx *ctx, const char *name, const llmrs_buf *input, c
         ctx->norm_eps = eps;
         int rc = call(input);
         ctx->norm_w = nullptr;
+        return rc;
+    }
+    // Above the decode kernel's token limit, where the small-batch tensor-core kernel will run: the norm is folded
+    // into that kernel's conversion of the activations (one kernel less, no rounding of the normalised values).
+    const uint32_t M_in = input->dim1 ? input->dim1 : 1;
+    if (conv_ok && (int)M_in > ctx->gemv_max_m && uses_exact_kernel(ctx, M_in) && dense_elem_bytes(input->dtype)) {
+        ctx->conv_norm_w = (const float *)norm_weight->dptr;
+        ctx->conv_norm_eps = eps;
+        int rc = call(input);
+        ctx->conv_norm_w = nullptr;
         return rc;
     }
     // the normalised activations go to a buffer of the context (grown outside stream capture only)
@@ -1160,7 +1172,8 @@ int llmrs_cuda_rms_norm_matmul(llmrs_ctx *ctx, llmrs_buf *out, const llmrs_buf *
     const uint32_t M = input && input->dim1 ? input->dim1 : 1;
     const bool fused = weight && input && (int)M <= ctx->gemv_max_m &&
                        (int)M <= gemv_single_launch_max_tokens((int)weight->dtype, (int)weight->dim0);
-    return with_norm(ctx, "rms_norm_matmul", input, norm_weight, eps, fused,
+    const bool kquant = weight && (weight->dtype == LLMRS_Q4K || weight->dtype == LLMRS_Q6K);
+    return with_norm(ctx, "rms_norm_matmul", input, norm_weight, eps, fused, kquant,
                      [&](const llmrs_buf *x) { return llmrs_cuda_matmul(ctx, out, weight, x); });
 }
 
@@ -1188,8 +1201,10 @@ int llmrs_cuda_rms_norm_matmul_qkv(llmrs_ctx *ctx, llmrs_buf *out_q, llmrs_buf *
                    w->device == (uint32_t)ctx->device && o->device == (uint32_t)ctx->device;
     }
     if (!one_pass) {
-        if ((int)M > ctx->gemv_max_m)                    // no kernel folds the norm in at this token count: normalise once
-            return with_norm(ctx, "rms_norm_matmul_qkv", input, norm_weight, eps, false, [&](const llmrs_buf *x) {
+        bool all_kquant = true;
+        for (int i = 0; i < 3; i++) all_kquant = all_kquant && (ws[i]->dtype == LLMRS_Q4K || ws[i]->dtype == LLMRS_Q6K);
+        if ((int)M > ctx->gemv_max_m)                    // above the decode kernel's limit: the norm once, in front (or in the conversion)
+            return with_norm(ctx, "rms_norm_matmul_qkv", input, norm_weight, eps, false, all_kquant, [&](const llmrs_buf *x) {
                 // one launch over the three weights where they share a format; else three calls, one conversion
                 bool shapes_ok = true;
                 for (int i = 0; i < 3; i++) {
@@ -1257,7 +1272,7 @@ int llmrs_cuda_rms_norm_matmul_gate_up(llmrs_ctx *ctx, llmrs_buf *out, const llm
     const uint32_t M = input && input->dim1 ? input->dim1 : 1;
     const bool fused = w_gate && input && (int)M <= ctx->gemv_max_m &&
                        gemv_gate_up_fits((int)w_gate->dtype, (int)w_gate->dim0, (int)M);
-    return with_norm(ctx, "rms_norm_matmul_gate_up", input, norm_weight, eps, fused,
+    return with_norm(ctx, "rms_norm_matmul_gate_up", input, norm_weight, eps, fused, true,
                      [&](const llmrs_buf *x) { return llmrs_cuda_matmul_gate_up(ctx, out, w_gate, w_up, x); });
 }
 

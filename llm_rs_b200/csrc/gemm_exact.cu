@@ -997,7 +997,7 @@ gemm_exact_kernel(const __grid_constant__ ExactMaps maps, const GemmParams p) {
 constexpr int ACT_KEEP = 2;
 __global__ void __launch_bounds__(1024)
 activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M, int TN, uint8_t *__restrict__ out,
-                         int with_sums, float *__restrict__ tok_scale) {
+                         int with_sums, float *__restrict__ tok_scale, const float *__restrict__ norm_w, float norm_eps) {
     __shared__ float red[32];
     pdl_prologue();                  // the next kernel may start its prologue; the input is complete from here on
     const int tok = blockIdx.x;
@@ -1027,13 +1027,68 @@ activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M
         }
     };
     const int step = (int)blockDim.x * 8;
+    const int n_warps = (int)(blockDim.x >> 5);
+    auto block_reduce = [&](float v, bool is_max) {   // every thread gets the block's sum or maximum
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, v, o);
+            v = is_max ? fmaxf(v, other) : v + other;
+        }
+        __syncthreads();                              // the previous reduction's readers are done
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+        __syncthreads();
+        v = (int)(threadIdx.x & 31) < n_warps ? red[threadIdx.x & 31] : (is_max ? 0.0f : 0.0f);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, v, o);
+            v = is_max ? fmaxf(v, other) : v + other;
+        }
+        return v;
+    };
+    // An rms_norm folded into the conversion (rms_norm_matmul* above four tokens): the row is multiplied by
+    // rsqrt(mean(x^2) + eps) * w before it is split, in float32 like the reference's kernel
+    // (shaders/ops.metal rms_norm), without the rounding to the activation type in between.
+    auto scale8 = [&](int k, float (&v)[8], float inv_rms) {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(norm_w + k)), b = __ldg(reinterpret_cast<const float4 *>(norm_w + k + 4));
+        const float w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = v[i] * inv_rms * w[i];
+    };
     float keep[ACT_KEEP][8];
+    float inv_rms = 1.0f;
+#pragma unroll
+    for (int jj = 0; jj < ACT_KEEP; jj++) {
+        const int k = (int)threadIdx.x * 8 + jj * step;
+        if (k < K) load8(k, keep[jj]);
+    }
+    if (norm_w) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int jj = 0; jj < ACT_KEEP; jj++) {
+            const int k = (int)threadIdx.x * 8 + jj * step;
+            if (k < K) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) ss = fmaf(keep[jj][i], keep[jj][i], ss);
+            }
+        }
+        for (int k = (int)threadIdx.x * 8 + ACT_KEEP * step; k < K; k += step) {
+            float v[8];
+            load8(k, v);
+#pragma unroll
+            for (int i = 0; i < 8; i++) ss = fmaf(v[i], v[i], ss);
+        }
+        inv_rms = rsqrtf(block_reduce(ss, false) / (float)K + norm_eps);
+#pragma unroll
+        for (int jj = 0; jj < ACT_KEEP; jj++) {
+            const int k = (int)threadIdx.x * 8 + jj * step;
+            if (k < K) scale8(k, keep[jj], inv_rms);
+        }
+    }
     float amax = 0.0f;
 #pragma unroll
     for (int jj = 0; jj < ACT_KEEP; jj++) {
         const int k = (int)threadIdx.x * 8 + jj * step;
         if (k < K) {
-            load8(k, keep[jj]);
 #pragma unroll
             for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(keep[jj][i]));
         }
@@ -1041,17 +1096,11 @@ activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M
     for (int k = (int)threadIdx.x * 8 + ACT_KEEP * step; k < K; k += step) {
         float v[8];
         load8(k, v);
+        if (norm_w) scale8(k, v, inv_rms);
 #pragma unroll
         for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
     }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    const int n_warps = (int)(blockDim.x >> 5);
-    amax = (int)(threadIdx.x & 31) < n_warps ? red[threadIdx.x & 31] : 0.0f;
-#pragma unroll
-    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    amax = block_reduce(amax, true);
     const int eb = (int)((__float_as_uint(amax) >> 23) & 0xFFu);
     int e = 140 - eb;                                    // amax < 2^(eb-126): the scaled row stays below 2^14
     e = max(-126, min(126, e));
@@ -1104,6 +1153,7 @@ activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M
     for (int k = (int)threadIdx.x * 8 + ACT_KEEP * step; k < K; k += step) {
         float v[8];
         load8(k, v);
+        if (norm_w) scale8(k, v, inv_rms);
         convert(k, v);
     }
     if (threadIdx.x == 0 && !padding) tok_scale[tok] = exp2i(-e);
@@ -1200,7 +1250,7 @@ static cudaError_t launch_exact_common(int wdtype, int nw, const uint8_t *const 
                                        const void *x, int x_dtype, int out_dtype, int K, int M, void *scratch,
                                        void *split_ws, int split_mode, ErrSink err_word, cudaStream_t s,
                                        uint64_t *launches, const GemmGather *gather, bool pdl, int sm_count,
-                                       int acts_mode) {
+                                       int acts_mode, const float *norm_w, float norm_eps) {
     if (nw < 1 || nw > 3) return cudaErrorInvalidValue;
     if (K <= 0 || M <= 0) return cudaSuccess;
     for (int i = 0; i < nw; i++)
@@ -1218,7 +1268,7 @@ static cudaError_t launch_exact_common(int wdtype, int nw, const uint8_t *const 
         act_threads = act_threads < 64 ? 64 : act_threads > 1024 ? 1024 : act_threads;
         const bool sums = wdtype == DT_Q4K || acts_mode == EXACT_ACTS_CONVERT_ALL;
         e = launch_dependent(activations_exact_kernel, dim3((unsigned)m_pad), dim3((unsigned)act_threads), 0, s, pdl,
-                             x, (int)(x_dtype == DT_BF16), K, M, tn, sb, (int)sums, tok_scale);
+                             x, (int)(x_dtype == DT_BF16), K, M, tn, sb, (int)sums, tok_scale, norm_w, norm_eps);
         if (e != cudaSuccess) return e;
         if (launches) (*launches)++;
     }
@@ -1273,17 +1323,17 @@ static cudaError_t launch_exact_common(int wdtype, int nw, const uint8_t *const 
 cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                               int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
                               cudaStream_t s, uint64_t *launches, const GemmGather *gather, bool pdl, int sm_count,
-                              int acts_mode) {
+                              int acts_mode, const float *norm_w, float norm_eps) {
     return launch_exact_common(wdtype, 1, &w, &N, &out, x, x_dtype, out_dtype, K, M, scratch, split_ws, split_mode,
-                               err_word, s, launches, gather, pdl, sm_count, acts_mode);
+                               err_word, s, launches, gather, pdl, sm_count, acts_mode, norm_w, norm_eps);
 }
 
 cudaError_t launch_gemm_exact_multi(int wdtype, int nw, const uint8_t *const *ws, const int *ns, void *const *outs,
                                     const void *x, int x_dtype, int out_dtype, int K, int M, void *scratch,
                                     void *split_ws, int split_mode, ErrSink err_word, cudaStream_t s, uint64_t *launches,
-                                    bool pdl, int sm_count) {
+                                    bool pdl, int sm_count, const float *norm_w, float norm_eps) {
     return launch_exact_common(wdtype, nw, ws, ns, outs, x, x_dtype, out_dtype, K, M, scratch, split_ws, split_mode,
-                               err_word, s, launches, nullptr, pdl, sm_count, EXACT_ACTS_CONVERT);
+                               err_word, s, launches, nullptr, pdl, sm_count, EXACT_ACTS_CONVERT, norm_w, norm_eps);
 }
 
 }  // namespace llmrs

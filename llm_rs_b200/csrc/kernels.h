@@ -203,13 +203,14 @@ size_t gemm_exact_scratch_bytes(int K, int M);
 cudaError_t launch_gemm_exact(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                               int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
                               cudaStream_t s, uint64_t *launches, const GemmGather *gather = nullptr, bool pdl = false,
-                              int sm_count = 0, int acts_mode = EXACT_ACTS_CONVERT);
+                              int sm_count = 0, int acts_mode = EXACT_ACTS_CONVERT, const float *norm_w = nullptr,
+                              float norm_eps = 0.0f);      // norm_w: an rms_norm of the input folded into its conversion
 // Up to three weights of one format and K against one input in ONE launch (q/k/v, gate/up): the weights' row
 // tiles form one tile space, cut over the SMs like a single matrix; output i is [M][ns[i]].  No all-gather.
 cudaError_t launch_gemm_exact_multi(int wdtype, int nw, const uint8_t *const *ws, const int *ns, void *const *outs,
                                     const void *x, int x_dtype, int out_dtype, int K, int M, void *scratch,
                                     void *split_ws, int split_mode, ErrSink err_word, cudaStream_t s, uint64_t *launches,
-                                    bool pdl = false, int sm_count = 0);
+                                    bool pdl = false, int sm_count = 0, const float *norm_w = nullptr, float norm_eps = 0.0f);
 
 // Activations -> per-token scaled f16 (one CTA per token): out_f16 [M, K], tok_scale[M] the factors that
 // undo the power-of-two scaling.  The conversion kernel of launch_gemm, for the dense F16 GEMM.

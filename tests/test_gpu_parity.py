@@ -417,8 +417,10 @@ def test_rms_norm_matmul(backend, dt, K, N, M):
     assert O.rel_l2(got, truth) <= tol_for(M)
 
 
-@pytest.mark.parametrize("M", [1, 4])
+@pytest.mark.parametrize("M", [1, 4, 9, 40])
 def test_rms_norm_matmul_gate_up(backend, M):
+    """Up to four tokens the norm is folded into the decode kernel, above into the conversion kernel of the
+    small-batch tensor-core kernel (gate and up in one launch)."""
     K, N = 4096, 640
     wg, wu = synth.weight(O.Q4K, K, N, tid=31), synth.weight(O.Q4K, K, N, tid=32)
     x = synth.activations(M, K, tid=4500 + M) * np.float32(7.0)
@@ -474,8 +476,9 @@ def test_rms_norm_matmul_qkv_equals_the_three_calls(backend, dts, K, Nq, Nkv, M,
 @pytest.mark.parametrize("dt", [O.Q4K, O.Q6K])
 @pytest.mark.parametrize("K,Nq,Nkv,M", [(4096, 4096, 1024, 9), (4096, 520, 130, 33), (2048, 1000, 300, 64)])
 def test_qkv_and_gate_up_one_launch_above_four_tokens(backend, dt, K, Nq, Nkv, M):
-    """q/k/v of one format above four tokens: one conversion and ONE launch of the small-batch kernel over the
-    three weights (their row tiles form one tile space, cut along K over all SMs); gate/up likewise.  Each
+    """q/k/v of one format above four tokens: one conversion (which applies the rms_norm) and ONE launch of the
+    small-batch kernel over the three weights (their row tiles form one tile space, cut along K over all SMs);
+    gate/up likewise.  Each
     output within the decode tolerance; row counts that are not multiples of the 128-row tile included."""
     ns = (Nq, Nkv, Nkv)
     ws = [synth.weight(dt, K, n, tid=2500 + i) for i, n in enumerate(ns)]
@@ -490,7 +493,7 @@ def test_qkv_and_gate_up_one_launch_above_four_tokens(backend, dt, K, Nq, Nkv, M
     before = backend.launch_count()
     backend.rms_norm_matmul_qkv(outs[0], outs[1], outs[2], wb[0], wb[1], wb[2], xb, gb, 1e-5)
     backend.sync()
-    assert backend.launch_count() - before == 3           # rms_norm, conversion, one matmul launch
+    assert backend.launch_count() - before == 2           # conversion (with the norm folded in), one matmul launch
     x64 = x.astype(np.float64)
     xn = (x64 / np.sqrt((x64 ** 2).mean(axis=1, keepdims=True) + 1e-5) * g).astype(np.float32)
     for o, w, n in zip(outs, ws, ns):
