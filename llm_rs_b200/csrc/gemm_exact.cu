@@ -170,11 +170,14 @@ __device__ __forceinline__ void dequant_q4k_half_exact(const uint4 &hdr, const u
         uint32_t lo[16], hi[16];
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            const uint32_t l4 = w[j] & 0x0F0F0F0Fu, h4 = w[j] & 0xF0F0F0F0u;
-            lo[2 * j] = h2_fma(magic_lo(l4), s_lo, c_lo);
-            lo[2 * j + 1] = h2_fma(magic_hi(l4), s_lo, c_lo);
-            hi[2 * j] = h2_fma(magic_lo(h4), s_hi, c_hi);
-            hi[2 * j + 1] = h2_fma(magic_hi(h4), s_hi, c_hi);
+            // K order inside every four weights is (0, 2, 1, 3) (the conversion kernel lays the activations
+            // out the same way): bytes 0 and 2 of a word are already one f16 pair apart, so a nibble becomes
+            // the mantissa of 1024.0 by ONE logic operation, and bytes 1 and 3 after one shift
+            const uint32_t w8 = w[j] >> 8;
+            lo[2 * j] = h2_fma((w[j] & 0x000F000Fu) | H2_1024, s_lo, c_lo);
+            lo[2 * j + 1] = h2_fma((w8 & 0x000F000Fu) | H2_1024, s_lo, c_lo);
+            hi[2 * j] = h2_fma((w[j] & 0x00F000F0u) | H2_1024, s_hi, c_hi);
+            hi[2 * j + 1] = h2_fma((w8 & 0x00F000F0u) | H2_1024, s_hi, c_hi);
         }
         tmem_st16(a_taddr + 32 * pr, lo);
         tmem_st16(a_taddr + 32 * pr + 16, hi);
@@ -205,7 +208,8 @@ __device__ __forceinline__ void min_operand_q4k(const uint4 &hdr, uint32_t a_tad
 // Staged bytes (slice-major layout, kernels.h): slices (h, c = 0, 1), each ql[64h+16c..+16) |
 // ql[64h+32+16c..+16) | qh[32h+16c..+16); weight 128h + 32g + 16c + i has its low nibble in ql run
 // (g & 1), low half for g < 2 and high half for g >= 2, and bits 2g..2g+1 of qh; its group scale is
-// scales[8h + 2g + c] (shaders/ops.metal:28-42, 322-334).  K-local 32g + 16c + i -> column 16g + 8c + i/2.
+// scales[8h + 2g + c] (shaders/ops.metal:28-42, 322-334).  K-local 32g + 16c + i -> column 16g + 8c + i/2
+// (with i taken in the order 0, 2, 1, 3 inside every four).
 // Per pair of weights: q' = q - 32 (exact), hi = RN_f16(q' sc) (one multiply), and with -sc one fma gives
 // hi - q' sc = -lo exactly; the MMA that consumes the lo columns negates its A operand.  The lo terms are
 // formed, stored and multiplied only for stages in which some row has a scale above 64 in magnitude.
@@ -213,6 +217,10 @@ struct RawQ6Half {
     uint4 ql0[2], ql1[2], qh[2];   // [c]: the two ql runs and the qh run of slice (h, c)
     uint2 sc;                      // int8 scales[8h .. 8h+8)
 };
+// bytes (0, 2) resp. (1, 3) of a word as the mantissas of (1024.0, 1024.0): the K order (0, 2, 1, 3) inside every
+// four weights that the Q4_K operand gets for free (see there) and the conversion kernel gives the activations
+__device__ __forceinline__ uint32_t magic_02(uint32_t bytes4) { return __byte_perm(bytes4, 0x64646464u, 0x5240u); }
+__device__ __forceinline__ uint32_t magic_13(uint32_t bytes4) { return __byte_perm(bytes4, 0x64646464u, 0x5341u); }
 // WITH_LO = false forms and stores the hi columns only: valid when every |sc| of the rows a warp handles is
 // at most 64, because then |sc (q - 32)| <= 2048 is exact in f16 and the lo terms are all zero.
 template <bool WITH_LO>
@@ -248,7 +256,7 @@ __device__ __forceinline__ void dequant_q6k_half_exact(const RawQ6Half &raw, uin
             for (int g = 0; g < 4; g++) {
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
-                    const uint32_t q2 = h2_sub(e ? magic_hi(v[g]) : magic_lo(v[g]), H2_1056);   // (q - 32) pair
+                    const uint32_t q2 = h2_sub(e ? magic_13(v[g]) : magic_02(v[g]), H2_1056);   // (q - 32) pair, K order (0, 2, 1, 3)
                     const uint32_t h = h2_mul(q2, s2[g]);
                     hi[g][2 * i + e] = h;
                     if constexpr (WITH_LO) lo[g][2 * i + e] = h2_fma(q2, ns2[g], h);        // hi - q' sc = -lo
@@ -1111,7 +1119,9 @@ activations_exact_kernel(const void *__restrict__ x, int x_is_bf16, int K, int M
         float sum = 0.0f;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const float a = v[2 * i] * sc, b = v[2 * i + 1] * sc;
+            // f16 pairs in the operand's K order (0, 2, 1, 3) inside every four values
+            const int ia = 4 * (i >> 1) + (i & 1), ib = ia + 2;
+            const float a = v[ia] * sc, b = v[ib] * sc;
             h[i] = pack_w(a, b);
             const float2 back = __half22float2(*reinterpret_cast<const __half2 *>(&h[i]));
             l[i] = pack_w(a - back.x, b - back.y);
