@@ -80,7 +80,9 @@ template <int PLANES> struct Fmt<1, PLANES> {          // Q6_K, slice-major chun
 // as one 64-bit relaxed system-scope access (mailbox_store / mailbox_load), which is a single access in
 // the memory model, so the call number doubles as the "this value has landed" flag and no fence is
 // needed anywhere: a system-scope fence was measured at 5-7 us on this machine, two of them
-// per matmul in an earlier store-then-flag version of this exchange.  When a CTA has finished
+// per matmul in an earlier store-then-flag version of this exchange.  The results of a row tile are
+// staged in shared memory and warp d posts the tile to rank d, a lane per row, so that the words cross
+// NVLink as 256-byte runs rather than one 8-byte packet per row and peer.  When a CTA has finished
 // its rows, its threads take a share of the mailbox words addressed to this rank, poll each until
 // it carries this call's number (bounded) and write the value into the local output.  The kernel
 // therefore completes on a rank only when that rank's output holds every slice, and stream order
@@ -498,9 +500,11 @@ template <int QT, int MT, int R, int NCW, int PLANES>
 __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParams p) {
     using F = Fmt<QT, PLANES>;
     constexpr int RT = R * NCW;
+    static_assert(NCW >= MAX_GATHER_RANKS, "the fused all-gather posts with one warp per rank");
     __shared__ float norm_red[NCW][4];
     __shared__ uint64_t consumers_done;                  // every consumer warp arrives here when it has finished
     __shared__ int gave_up;                              // a bounded wait ran out somewhere in this CTA
+    __shared__ float gather_out[2][MT][RT];              // fused all-gather: a row tile's results, two tiles in turn
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + MAX_STAGES;
@@ -595,14 +599,17 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
 
     uint32_t it = 0;
     bool ok = true;
-    for (int rt = blockIdx.x; rt < p.n_row_tiles && ok; rt += gridDim.x) {
+    // Every consumer warp walks every row tile of the CTA, also after a wait has run out (it then skips
+    // the work), because the fused all-gather meets at a barrier once per tile.
+    int tile_par = 0;
+    for (int rt = blockIdx.x; rt < p.n_row_tiles; rt += gridDim.x) {
         float total[R][MT];
 #pragma unroll
         for (int r = 0; r < R; r++)
 #pragma unroll
             for (int t = 0; t < MT; t++) total[r][t] = 0.0f;
 
-        for (int c = 0; c < p.n_chunks; c++, it++) {
+        for (int c = 0; c < p.n_chunks && ok; c++, it++) {
             const int s = it % S;
             if (!mbar_wait(&full[s], (it / S) & 1, p.wait_limit)) {
                 report_error(p.err, KERR_FULL_WAIT);
@@ -675,15 +682,36 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 1) gemv_kernel(const GemvParam
                             if (p.Residual) v += load_x(p.Residual, o, p.res_bf16);
                             store_out(p.Out, o, v, p.out_bf16);
                         }
-                    } else if (lane == p.g.rank) {        // this rank's own copy: straight into the output
-                        store_out(p.Out, (size_t)t * p.g.n_total + p.g.row_offset + out_row, v, p.out_bf16);
-                    } else if (lane < p.g.world) {        // lane d posts the value to rank d's mailbox
-                        uint2 *box = p.g.peer_box[lane] + (gather_step & 1u) * p.g.half_words +
-                                     ((size_t)p.g.rank * p.m_valid + t) * p.N + out_row;
-                        mailbox_store(box, __float_as_uint(v), gather_step);
+                    } else if (lane == 0) {               // fused all-gather: staged, posted a tile at a time
+                        gather_out[tile_par][t][warp * R + r] = v;
                     }
                 }
             }
+        if (p.g.world > 0) {
+            // Warp d takes the tile to rank d: its own rank's copy goes straight into the output, the
+            // others into the peer's mailbox, a lane per row, so that a tile travels as 256-byte runs of
+            // {value, call number} words instead of one 8-byte packet per row and peer.
+            named_barrier_sync(1, NCW * 32);
+            if (warp < p.g.world && !*(volatile int *)&gave_up) {
+#pragma unroll
+                for (int t = 0; t < MT; t++) {
+                    if (t >= p.m_valid) break;
+                    for (int l = lane; l < RT; l += 32) {
+                        const int out_row = rt * RT + l;
+                        if (out_row >= p.N) break;
+                        const float v = gather_out[tile_par][t][l];
+                        if (warp == p.g.rank) {
+                            store_out(p.Out, (size_t)t * p.g.n_total + p.g.row_offset + out_row, v, p.out_bf16);
+                        } else {
+                            uint2 *box = p.g.peer_box[warp] + (gather_step & 1u) * p.g.half_words +
+                                         ((size_t)p.g.rank * p.m_valid + t) * p.N + out_row;
+                            mailbox_store(box, __float_as_uint(v), gather_step);
+                        }
+                    }
+                }
+            }
+            tile_par ^= 1;   // the next tile's barrier comes before this buffer is written again
+        }
     }
 
     if (p.g.world > 1) {

@@ -27,8 +27,9 @@ def _worker(rank, world, port, q):
         with torch.cuda.stream(stream):
             be = CudaBackend(rank, stream=stream.cuda_stream)
             # (the last two run the tensor-core kernel, whose epilogue does the same exchange)
-            for dt, K, N, M in ((O.Q6K, 4096, 4096, 1), (O.Q4K, 2048, 1024, 3), (O.Q4K, 1024, 2048, 16),
-                                (O.Q6K, 8192, 512, 70)):
+            # (N = 1000: row tiles that end inside a rank's slice)
+            for dt, K, N, M in ((O.Q6K, 4096, 4096, 1), (O.Q4K, 2048, 1024, 3), (O.Q4K, 1024, 1000, 2),
+                                (O.Q4K, 1024, 2048, 16), (O.Q6K, 8192, 512, 70)):
                 tol = 1e-4 if M <= 4 else 2e-3
                 a, b = row_range(N, rank, world)
                 w_full = synth.weight(dt, K, N, tid=dt)
