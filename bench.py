@@ -33,7 +33,8 @@ K_IN, N_OUT = 4096, 128256
 Q6K, Q4K = 14, 12
 BLOCK_BYTES = {Q4K: 144, Q6K: 210}
 L2_BYTES = 126e6
-FUSED_GATHER_MAX_WORDS = 1 << 18      # values one rank receives from its peers per matmul, above which NCCL moves them
+# values one rank receives from its peers per matmul, above which NCCL moves them (LLMRS_BENCH_FUSED_WORDS overrides)
+FUSED_GATHER_MAX_WORDS = int(os.environ.get("LLMRS_BENCH_FUSED_WORDS", 1 << 18))
 
 
 def algorithmic_bytes(dtype: int, K: int, N: int, M: int, in_bytes: int = 4, out_bytes: int = 4) -> int:

@@ -646,53 +646,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                         if (tok < tok_lim && row < row_lim) {
                             const uint4 d = *reinterpret_cast<const uint4 *>(stg + (size_t)tl * 32 * esz + vv * 16);
                             *reinterpret_cast<uint4 *>(o_ptr + ((size_t)tok * o_stride + row) * esz) = d;
-                            if (gather) {                        // the same values, as words, to every peer's mailbox
-                                float f[8];
-                                const uint32_t w4[4] = {d.x, d.y, d.z, d.w};
-                                int nv;
-                                if (o_bf16) {
-                                    nv = 8;
-#pragma unroll
-                                    for (int j = 0; j < 4; j++) {
-                                        f[2 * j] = __uint_as_float(w4[j] << 16);
-                                        f[2 * j + 1] = __uint_as_float(w4[j] & 0xFFFF0000u);
-                                    }
-                                } else {
-                                    nv = 4;
-#pragma unroll
-                                    for (int j = 0; j < 4; j++) f[j] = __uint_as_float(w4[j]);
-                                }
-                                const size_t word = (gather_step & 1u) * p.half_words +
-                                                    ((size_t)p.rank * p.M + tok) * p.N + (row - p.row_offset);
-                                for (int dd = 0; dd < p.world; dd++) {
-                                    if (dd == p.rank) continue;
-                                    uint2 *box = p.peer_box[dd] + word;
-                                    for (int j = 0; j < nv; j++) mailbox_store(box + j, __float_as_uint(f[j]), gather_step);
-                                }
-                            }
                         }
                     }
                 } else {
                     for (int tl = 0; tl < GT; tl++) {
                         const int tok = tok_base + g0 + tl, row = row_base + lane;
                         if (tok < tok_lim && row < row_lim) {
-                            float fv;
                             if (o_bf16) {
-                                const uint16_t hb = reinterpret_cast<const uint16_t *>(stg)[tl * 32 + lane];
-                                ((uint16_t *)o_ptr)[(size_t)tok * o_stride + row] = hb;
-                                fv = __uint_as_float((uint32_t)hb << 16);
+                                ((uint16_t *)o_ptr)[(size_t)tok * o_stride + row] =
+                                    reinterpret_cast<const uint16_t *>(stg)[tl * 32 + lane];
                             } else {
-                                fv = reinterpret_cast<const float *>(stg)[tl * 32 + lane];
-                                ((float *)o_ptr)[(size_t)tok * o_stride + row] = fv;
-                            }
-                            if (gather) {
-                                const size_t word = (gather_step & 1u) * p.half_words +
-                                                    ((size_t)p.rank * p.M + tok) * p.N + (row - p.row_offset);
-                                for (int dd = 0; dd < p.world; dd++)
-                                    if (dd != p.rank)
-                                        mailbox_store(p.peer_box[dd] + word, __float_as_uint(fv), gather_step);
+                                ((float *)o_ptr)[(size_t)tok * o_stride + row] =
+                                    reinterpret_cast<const float *>(stg)[tl * 32 + lane];
                             }
                         }
+                    }
+                }
+                if (gather) {
+                    // The same values, as {value, call number} words, to every peer's mailbox: a lane per row,
+                    // so that a token's 32 rows cross NVLink as one 256-byte run per peer.
+                    const int row = row_base + lane;
+                    for (int tl = 0; tl < GT; tl++) {
+                        const int tok = tok_base + g0 + tl;
+                        if (tok >= tok_lim || row >= row_lim) continue;
+                        const uint32_t bits = o_bf16 ? (uint32_t)reinterpret_cast<const uint16_t *>(stg)[tl * 32 + lane] << 16
+                                                     : reinterpret_cast<const uint32_t *>(stg)[tl * 32 + lane];
+                        const size_t word = (gather_step & 1u) * p.half_words +
+                                            ((size_t)p.rank * p.M + tok) * p.N + (row - p.row_offset);
+                        for (int dd = 0; dd < p.world; dd++)
+                            if (dd != p.rank) mailbox_store(p.peer_box[dd] + word, bits, gather_step);
                     }
                 }
                 __syncwarp();                                    // staging is reused by the next group
@@ -797,7 +779,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
                         for (int dd = 0; dd < p.world; dd++) {
                             if (dd == p.rank) continue;
                             uint2 *box = p.peer_box[dd] + word;
-                            for (int i = 0; i < nv; i++) mailbox_store(box + i, __float_as_uint(f[i]), gather_step);
+                            if (nv == 4 && (word & 1) == 0) {             // the lane's four words as two 16-byte stores
+                                mailbox_store2(box, __float_as_uint(f[0]), __float_as_uint(f[1]), gather_step);
+                                mailbox_store2(box + 2, __float_as_uint(f[2]), __float_as_uint(f[3]), gather_step);
+                            } else {
+                                for (int i = 0; i < nv; i++) mailbox_store(box + i, __float_as_uint(f[i]), gather_step);
+                            }
                         }
                     }
                 }

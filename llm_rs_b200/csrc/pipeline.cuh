@@ -100,6 +100,13 @@ __device__ __forceinline__ void mailbox_store(uint2 *w, uint32_t value_bits, uin
     const unsigned long long word = ((unsigned long long)tag << 32) | (unsigned long long)value_bits;
     asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(w), "l"(word) : "memory");
 }
+// Two neighbouring words (w 16-byte aligned) in one 16-byte store.  A vector store is performed as one
+// access per element, here per 64-bit {value, tag} word, in no particular order: each word still arrives whole.
+__device__ __forceinline__ void mailbox_store2(uint2 *w, uint32_t v0, uint32_t v1, uint32_t tag) {
+    const unsigned long long w0 = ((unsigned long long)tag << 32) | (unsigned long long)v0;
+    const unsigned long long w1 = ((unsigned long long)tag << 32) | (unsigned long long)v1;
+    asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(w), "l"(w0), "l"(w1) : "memory");
+}
 __device__ __forceinline__ uint2 mailbox_load(const uint2 *w) {
     unsigned long long word;
     asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(word) : "l"(w) : "memory");
