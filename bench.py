@@ -632,10 +632,12 @@ def extra_measurements(be_factory, stream, peak_gbs):
                 be.matmul(o, ws[i % copies], x)
             be.sync()
             be.reset_gpu_secs()
+            n0 = be.launch_count()
             for i in range(iters):
                 be.matmul(o, ws[i % copies], x)
             be.sync()
             t = be.gpu_secs_total() / iters
+            time_matmul.launches_per_call = (be.launch_count() - n0) / iters
             for b in ws + [x, o]:
                 b.free()
             return t
@@ -655,7 +657,9 @@ def extra_measurements(be_factory, stream, peak_gbs):
                 alg = algorithmic_bytes(dt, K, N, M)
                 out["gemv"][f"{name}_m{M}"] = {"us": round(t * 1e6, 2), "GBps": round(alg / t / 1e9, 1),
                                                "frac_of_hbm_peak": round(alg / t / 1e9 / peak_gbs, 4),
-                                               "kernel": "decode kernel (dp4a, fixed-point activations)" if M <= 4
+                                               # one launch per call: the decode kernel; two: conversion + tensor-core kernel
+                                               "kernel": "decode kernel (dp4a, fixed-point activations)"
+                                               if time_matmul.launches_per_call < 1.5
                                                else "small-batch tensor-core kernel (exact integer operands, 1e-4 class)"}
         # the same output projection on the one-term tensor-core kernel (2e-3 class; LLMRS_TC_TWO_TERM=0)
         os.environ["LLMRS_TC_TWO_TERM"] = "0"
