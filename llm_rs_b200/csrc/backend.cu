@@ -651,7 +651,7 @@ static cudaError_t tc_matmul(llmrs_ctx *ctx, uint32_t wdtype, const void *w, con
     ctx->acts_have = false;                              // the other kernel writes its own conversion into the scratch
     return launch_gemm((int)wdtype, (const uint8_t *)w, x, (int)x_dtype, out, (int)out_dtype, (int)K, (int)N, (int)M,
                        ctx->scratch, ctx->split_ws, ctx->gemm_split, ctx->sink(), ctx->stream, &ctx->launches, gather,
-                       ctx->two_term);
+                       ctx->two_term, ctx->pdl);
 }
 
 // Several K-quant weights of one format against one input on the small-batch tensor-core kernel, one launch.

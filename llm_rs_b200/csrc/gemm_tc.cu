@@ -350,6 +350,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     const Sched sc = make_sched(p, TN);
     const int w_tiles = sc.w_tiles;
 
+    // Programmatic dependent launch: this kernel may start while the kernel that converts its activations
+    // is still running.  Only the warps that touch what earlier kernels wrote (the activation producer and
+    // the epilogue) wait for them; the dequantising warps read weights only and start at once, so the first
+    // operand stages are in tensor memory when the activations arrive.
+    pdl_trigger();
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
             mbar_init(&full[s], DEQ_WARPS / 2 + 1); // the 4 warps of one dequant group + the TMA thread (with its bytes)
@@ -439,6 +444,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
         bool ok = true;
         UnitIter ui;
         Unit u;
+        pdl_wait();                                   // the converted activations are complete and visible
         while (ok && ui.next(sc, u)) {
             const int t0 = (u.tile / w_tiles) * TN;
             for (int st = 2 * u.b0; st < 2 * u.b1; st++, it++) {
@@ -541,6 +547,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
         uint32_t tcount = 0;
         bool dead = false;                                      // a wait gave up: no more memory traffic, barriers only
         const bool gather = p.world > 1;
+        pdl_wait();                                   // token factors, exchange counters, mailbox step: all from earlier kernels
         const uint32_t gather_step = gather ? *reinterpret_cast<volatile uint32_t *>(p.step_word) + 1u : 0u;
         UnitIter ui;
         Unit u;
@@ -867,6 +874,7 @@ __global__ void __launch_bounds__(256)
 activations_to_f16_kernel(const void *__restrict__ x, int x_is_bf16, int K, __half *__restrict__ out,
                           __half *__restrict__ out_lo, float *__restrict__ tok_scale) {
     __shared__ float red[8];
+    pdl_prologue();                                   // the input is complete; the scratch's last reader has finished
     const int tok = blockIdx.x;
     const size_t base = (size_t)tok * K;
     // 8 consecutive values per thread and iteration (K is a multiple of 256)
@@ -950,7 +958,7 @@ bool split_pays(int n_tiles, int nb, int sms, int forced, bool two_term) {
 }
 
 template <int QT, int TN, bool SPLIT = false>
-cudaError_t launch_tn(const GemmParams &p, const void *x_f16, cudaStream_t s) {
+cudaError_t launch_tn(const GemmParams &p, const void *x_f16, cudaStream_t s, bool pdl) {
     CUtensorMap tmap;
     // two-term variant: rows M .. 2M-1 of the converted activations hold the lo terms
     cudaError_t e = encode_2d(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x_f16, (uint64_t)p.K,
@@ -970,17 +978,16 @@ cudaError_t launch_tn(const GemmParams &p, const void *x_f16, cudaStream_t s) {
         if (n_tiles < p.sm_count) grid = tail_blocks < p.sm_count ? tail_blocks : p.sm_count;
     }
     if (q.world > 1) grid = p.sm_count;      // CTAs without a tile still take their share of the mailbox
-    kern<<<grid, GEMM_THREADS, smem, s>>>(tmap, q);
-    return cudaGetLastError();
+    return launch_dependent(kern, dim3((unsigned)grid), dim3(GEMM_THREADS), smem, s, pdl, tmap, q);
 }
 
 template <int QT>
-cudaError_t launch_qt(const GemmParams &p, const void *x_f16, bool two_term, cudaStream_t s) {
-    if (two_term) return p.M <= 32 ? launch_tn<QT, 32, true>(p, x_f16, s) : launch_tn<QT, 64, true>(p, x_f16, s);
-    if (p.M <= 32) return launch_tn<QT, 32>(p, x_f16, s);
-    if (p.M <= 64) return launch_tn<QT, 64>(p, x_f16, s);
-    if (p.M <= 128) return launch_tn<QT, 128>(p, x_f16, s);
-    return launch_tn<QT, 256>(p, x_f16, s);
+cudaError_t launch_qt(const GemmParams &p, const void *x_f16, bool two_term, cudaStream_t s, bool pdl) {
+    if (two_term) return p.M <= 32 ? launch_tn<QT, 32, true>(p, x_f16, s, pdl) : launch_tn<QT, 64, true>(p, x_f16, s, pdl);
+    if (p.M <= 32) return launch_tn<QT, 32>(p, x_f16, s, pdl);
+    if (p.M <= 64) return launch_tn<QT, 64>(p, x_f16, s, pdl);
+    if (p.M <= 128) return launch_tn<QT, 128>(p, x_f16, s, pdl);
+    return launch_tn<QT, 256>(p, x_f16, s, pdl);
 }
 
 }  // namespace
@@ -1009,15 +1016,15 @@ size_t gemm_split_workspace_bytes(int sms) {
 
 cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                         int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
-                        cudaStream_t s, uint64_t *launches, const GemmGather *gather, bool two_term) {
+                        cudaStream_t s, uint64_t *launches, const GemmGather *gather, bool two_term, bool pdl) {
     if (K <= 0 || N <= 0 || M <= 0) return cudaSuccess;
     if (!scratch) return cudaErrorInvalidValue;
     two_term = two_term && M <= GEMM_TWO_TERM_MAX_TOKENS;
     __half *x_f16 = (__half *)scratch;
     float *tok_scale = (float *)((uint8_t *)scratch + scratch_x_bytes(K, M));
-    activations_to_f16_kernel<<<(unsigned)M, 256, 0, s>>>(x, x_dtype == DT_BF16, K, x_f16,
-                                                          two_term ? x_f16 + (size_t)M * K : nullptr, tok_scale);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_dependent(activations_to_f16_kernel, dim3((unsigned)M), dim3(256), 0, s, pdl, x,
+                                     (int)(x_dtype == DT_BF16), K, x_f16,
+                                     two_term ? x_f16 + (size_t)M * K : (__half *)nullptr, tok_scale);
     if (e != cudaSuccess) return e;
     if (launches) (*launches)++;
     GemmParams p{};
@@ -1041,10 +1048,10 @@ cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype
     }
     if (wdtype == DT_Q4K) {
         p.row_stride = (size_t)(K / QK_K) * Q4K_BLOCK_BYTES;
-        e = launch_qt<0>(p, x_f16, two_term, s);
+        e = launch_qt<0>(p, x_f16, two_term, s, pdl);
     } else if (wdtype == DT_Q6K) {
         p.row_stride = q6k_row_stride(K);
-        e = launch_qt<1>(p, x_f16, two_term, s);
+        e = launch_qt<1>(p, x_f16, two_term, s, pdl);
     } else {
         return cudaErrorInvalidValue;
     }

@@ -184,7 +184,8 @@ size_t gemm_split_workspace_bytes(int sms);
 size_t gemm_split_counter_bytes();      // the leading bytes of the workspace that must be zero
 cudaError_t launch_gemm(int wdtype, const uint8_t *w, const void *x, int x_dtype, void *out, int out_dtype,
                         int K, int N, int M, void *scratch, void *split_ws, int split_mode, ErrSink err_word,
-                        cudaStream_t s, uint64_t *launches, const GemmGather *gather = nullptr, bool two_term = false);
+                        cudaStream_t s, uint64_t *launches, const GemmGather *gather = nullptr, bool two_term = false,
+                        bool pdl = false);
 
 // The small-batch matmul (up to GEMM_EXACT_MAX_TOKENS tokens) on the tensor cores at the decode
 // kernel's tolerance: the integer factors of the block formats (sc * q for Q4_K, sc * (q - 32) as an
