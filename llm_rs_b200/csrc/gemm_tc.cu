@@ -981,12 +981,35 @@ cudaError_t launch_tn(const GemmParams &p, const void *x_f16, cudaStream_t s, bo
     return launch_dependent(kern, dim3((unsigned)grid), dim3(GEMM_THREADS), smem, s, pdl, tmap, q);
 }
 
+// Above 128 tokens: 256 or 128 tokens per tile?  A 256-token tile dequantises every weight half as often, a
+// 128-token tile costs 0.62 of its time (measured) and there are twice as many, which fills the last wave
+// better at some shapes: with 148 SMs, K=4096 -> 14336 at 384 tokens is 224 tiles of 256 (two waves, the
+// second half empty) or 336 of 128 (three waves of 0.62): 61 against 55 us; K=14336 -> 4096 at 512 tokens
+// 81 against 75 us.  The estimate counts block times of a 256-token tile: whole waves, the last one either cut
+// along K (where split_pays says so; the exchange costs about 17 block times of the tile, 8 when every CTA
+// gets one block) or run as a whole wave.
+int tokens_per_tile_above_128(const GemmParams &p) {
+    const int nb = p.K / QK_K, sms = p.sm_count > 0 ? p.sm_count : 148;
+    const int w_tiles = (p.N + TILE_ROWS - 1) / TILE_ROWS;
+    auto estimate = [&](int tn, double c) {
+        const int tiles = w_tiles * ((p.M + tn - 1) / tn);
+        const int full = tiles / sms, rest = tiles % sms;
+        if (rest == 0) return (double)full * nb * c;
+        if (p.ws_slots && split_pays(tiles, nb, sms, p.split, false)) {
+            const double exchange = (long long)nb * (sms - rest) >= 20LL * sms ? 17.0 : 8.0;
+            return ((double)full * nb + (double)rest * nb / sms + exchange) * c;
+        }
+        return (double)(full + 1) * nb * c;
+    };
+    return estimate(128, 0.62) < estimate(256, 1.0) ? 128 : 256;
+}
+
 template <int QT>
 cudaError_t launch_qt(const GemmParams &p, const void *x_f16, bool two_term, cudaStream_t s, bool pdl) {
     if (two_term) return p.M <= 32 ? launch_tn<QT, 32, true>(p, x_f16, s, pdl) : launch_tn<QT, 64, true>(p, x_f16, s, pdl);
     if (p.M <= 32) return launch_tn<QT, 32>(p, x_f16, s, pdl);
     if (p.M <= 64) return launch_tn<QT, 64>(p, x_f16, s, pdl);
-    if (p.M <= 128) return launch_tn<QT, 128>(p, x_f16, s, pdl);
+    if (p.M <= 128 || tokens_per_tile_above_128(p) == 128) return launch_tn<QT, 128>(p, x_f16, s, pdl);
     return launch_tn<QT, 256>(p, x_f16, s, pdl);
 }
 
