@@ -370,13 +370,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             return ms / steps
 
         def timed_in_graphs(fn, steps, warmup):
-            """The same K steps, enqueued as replays of one CUDA graph that holds `copies` of them (every
-            weight copy once, in rotation order) plus an eager remainder: with several GPUs a step is 20-40 us
+            """The same K steps, enqueued as replays of one CUDA graph that holds eight or more of them (whole
+            rotations of the weight copies) plus an eager remainder: with several GPUs a step is 20-40 us
             of device time and the Python call that launches it is no shorter, so eager timing measures
             the host.  Returns (ms per step, steps per graph)."""
             for i in range(warmup):
                 fn(i)
-            per_graph = copies
+            per_graph = copies * max(1, -(-8 // copies))    # whole rotations, eight steps at least
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 for i in range(per_graph):
@@ -392,9 +392,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             e1.record(stream)
             barrier()
             ms = e0.elapsed_time(e1)
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t.item()) / steps, per_graph
+            if world > 1:
+                t = torch.tensor([ms], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            return ms / steps, per_graph
 
         sampler = ClockSampler(local_rank)
         sampler.start()
@@ -402,15 +404,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         ms_step = timed(step, args.steps, max(args.warmup, 3))
         launches = be.launch_count() - n0 - max(args.warmup, 3)
         timing = "eager launches"
-        if world > 1:
-            try:
-                ms_graph, per_graph = timed_in_graphs(step, args.steps, max(args.warmup, 3))
-                if ms_graph < ms_step:
-                    timing = (f"{args.steps // per_graph} replays of a CUDA graph of {per_graph} steps"
-                              f" + {args.steps % per_graph} eager steps (eager launches: {ms_step * 1e3:.1f} us per step)")
-                    ms_step = ms_graph
-            except Exception as e:  # noqa: BLE001
-                print(f"[bench] graph timing unavailable ({e!r}); keeping the eager figure", file=sys.stderr)
+        try:
+            ms_graph, per_graph = timed_in_graphs(step, args.steps, max(args.warmup, 3))
+            if ms_graph < ms_step:
+                timing = (f"{args.steps // per_graph} replays of a CUDA graph of {per_graph} steps"
+                          f" + {args.steps % per_graph} eager steps (eager launches: {ms_step * 1e3:.1f} us per step)")
+                ms_step = ms_graph
+            else:
+                timing = f"eager launches (in CUDA graphs of {per_graph} steps: {ms_graph * 1e3:.1f} us per step)"
+        except Exception as e:  # noqa: BLE001
+            print(f"[bench] graph timing unavailable ({e!r}); keeping the eager figure", file=sys.stderr)
         # the dominant kernel alone (no collective), same rotation: its launch duration
         ms_kernel = timed(lambda i: be.matmul(obuf, weights[i % copies], xbuf), args.steps, 3)
         ms_e2e = timed(step_e2e, args.steps, max(args.warmup, 3))
