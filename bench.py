@@ -370,13 +370,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             return ms / steps
 
         def timed_in_graphs(fn, steps, warmup):
-            """The same K steps, enqueued as replays of one CUDA graph that holds eight or more of them (whole
+            """The same K steps, enqueued as replays of one CUDA graph that holds sixteen or more of them (whole
             rotations of the weight copies) plus an eager remainder: with several GPUs a step is 20-40 us
             of device time and the Python call that launches it is no shorter, so eager timing measures
             the host.  Returns (ms per step, steps per graph)."""
             for i in range(warmup):
                 fn(i)
-            per_graph = copies * max(1, -(-8 // copies))    # whole rotations, eight steps at least
+            per_graph = copies * max(1, -(-16 // copies))   # whole rotations, sixteen steps at least
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 for i in range(per_graph):
