@@ -8,7 +8,11 @@ Workload (the configuration the headline metric is quoted on): the Q6_K decode G
 a Llama-3-8B output projection, K=4096 -> N=128256, M tokens (default 1), synthetic seeded
 blocks and N(0,1) activations (llm_rs_b200/synth.py).  A step is one `Backend::matmul` call on
 that weight.  With N GPUs the weight rows are split N ways and the output slices are
-all-gathered over NCCL (strong scaling: the total work is fixed).
+all-gathered, inside the kernel over peer stores up to four tokens, over NCCL otherwise (strong
+scaling: the total work is fixed).  The K steps are timed twice, launched one by one and as
+replays of a CUDA graph of sixteen or more steps, and the faster figure is `value` (`config.timing`
+names the method and gives the other figure): with several GPUs a step is shorter than the
+Python call that launches it.
 
 One JSON line on stdout (rank 0).  `value` is algorithmic GB/s (GGUF weight bytes + input +
 output, per step) with everything resident in HBM; `e2e` is the same metric through the public
